@@ -1,0 +1,10 @@
+"""Import path kept from the reference (``gdnet.utils.sp``)."""
+
+from ..parallel.sp import (  # noqa: F401
+    clear_symm_handles,
+    flush_bwd_halos,
+    halo_exchange,
+    shard_range,
+    shard_sequence,
+    state_exchange,
+)
