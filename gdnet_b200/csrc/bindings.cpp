@@ -1,0 +1,468 @@
+// torch.ops.gdnet_b200.* : thin, checked bindings from tensors to the kernel launchers.
+// Every op validates device, dtype, contiguity of the innermost dimension and alignment on the
+// host, launches on the current CUDA stream and never synchronises.
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include "comm.h"
+#include "gemm_sm100.h"
+#include "kernels.h"
+
+namespace {
+
+using at::Tensor;
+using OptT = const std::optional<Tensor>&;
+
+#define GD_LAUNCH(expr)                                             \
+  do {                                                              \
+    const char* gd_err_ = (expr);                                   \
+    TORCH_CHECK(gd_err_ == nullptr, "gdnet_b200: ", gd_err_);       \
+  } while (0)
+
+cudaStream_t stream_of(const Tensor& t) { return c10::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.dim() == 0 || t.stride(-1) == 1 || t.size(-1) == 1, name, " must be contiguous in its last dim");
+}
+
+const __nv_bfloat16* bf16_ptr(const Tensor& t, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name, " must be 16-byte aligned");
+  return reinterpret_cast<const __nv_bfloat16*>(t.data_ptr());
+}
+__nv_bfloat16* bf16_mut(const Tensor& t, const char* name) { return const_cast<__nv_bfloat16*>(bf16_ptr(t, name)); }
+
+const float* f32_ptr(const Tensor& t, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
+  return t.data_ptr<float>();
+}
+float* f32_mut(const Tensor& t, const char* name) { return const_cast<float*>(f32_ptr(t, name)); }
+
+const float* opt_f32(OptT t, const char* name) { return t.has_value() ? f32_ptr(*t, name) : nullptr; }
+const __nv_bfloat16* opt_bf16(OptT t, const char* name) { return t.has_value() ? bf16_ptr(*t, name) : nullptr; }
+
+uint8_t* fp8_mut(const Tensor& t, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.element_size() == 1, name, " must be an 8-bit tensor");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name, " must be 16-byte aligned");
+  return reinterpret_cast<uint8_t*>(t.data_ptr());
+}
+
+Tensor& status_tensor(int device) {
+  static std::vector<Tensor> per_device(64);
+  TORCH_CHECK(device >= 0 && device < 64, "bad device index");
+  if (!per_device[device].defined())
+    per_device[device] = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  return per_device[device];
+}
+
+gd::Status* status_ptr(const Tensor& like) {
+  return reinterpret_cast<gd::Status*>(status_tensor(like.get_device()).data_ptr());
+}
+
+Tensor kernel_status(const Tensor& like) { return status_tensor(like.get_device()); }
+
+void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT bias, OptT row_scale, OptT ssq_in,
+                   int64_t norm_dim, double norm_eps, OptT aux, int64_t aux_mode, OptT rowcoef, OptT pre_out,
+                   int64_t act, OptT ssq_out, int64_t M, int64_t N) {
+  check_cuda(out, "out");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N, "out must be (M, N)");
+  e.out = out.data_ptr();
+  e.out_ld = out.stride(0);
+  e.out_f32 = out.scalar_type() == at::kFloat;
+  TORCH_CHECK(e.out_f32 || out.scalar_type() == at::kBFloat16, "out must be bfloat16 or float32");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0 && (e.out_ld * out.element_size()) % 16 == 0,
+              "out rows must be 16-byte aligned");
+  e.accumulate = accumulate;
+  e.bias = nullptr;
+  e.bias_f32 = 0;
+  if (bias.has_value()) {
+    check_cuda(*bias, "bias");
+    TORCH_CHECK(bias->numel() == N, "bias must have N elements");
+    e.bias = bias->data_ptr();
+    e.bias_f32 = bias->scalar_type() == at::kFloat;
+    TORCH_CHECK(e.bias_f32 || bias->scalar_type() == at::kBFloat16, "bias must be bfloat16 or float32");
+  }
+  e.row_scale = opt_f32(row_scale, "row_scale");
+  if (row_scale.has_value()) TORCH_CHECK(row_scale->numel() == M, "row_scale must have M elements");
+  e.ssq_in = opt_f32(ssq_in, "ssq_in");
+  e.ssq_parts = 0;
+  if (ssq_in.has_value()) {
+    TORCH_CHECK(ssq_in->dim() == 2 && ssq_in->size(0) == M && ssq_in->is_contiguous(), "ssq_in must be (M, parts)");
+    e.ssq_parts = (int)ssq_in->size(1);
+  }
+  e.norm_dim = (int)norm_dim;
+  e.norm_eps = (float)norm_eps;
+  e.aux = opt_bf16(aux, "aux");
+  e.aux_ld = 0;
+  e.aux_mode = (int)aux_mode;
+  if (aux.has_value()) {
+    TORCH_CHECK(aux->dim() == 2 && aux->size(0) == M && aux->size(1) == N, "aux must be (M, N)");
+    e.aux_ld = aux->stride(0);
+    TORCH_CHECK((e.aux_ld * 2) % 16 == 0, "aux rows must be 16-byte aligned");
+    TORCH_CHECK(aux_mode >= 1 && aux_mode <= 3, "aux_mode must be 1..3 when aux is given");
+  }
+  e.rowcoef = opt_f32(rowcoef, "rowcoef");
+  if (aux_mode == gd::AUX_RMS_SILU_BWD) TORCH_CHECK(rowcoef.has_value() && rowcoef->numel() == M, "rowcoef (M) needed");
+  e.pre_out = nullptr;
+  e.pre_ld = 0;
+  if (pre_out.has_value()) {
+    TORCH_CHECK(pre_out->dim() == 2 && pre_out->size(0) == M && pre_out->size(1) == N, "pre_out must be (M, N)");
+    e.pre_out = bf16_mut(*pre_out, "pre_out");
+    e.pre_ld = pre_out->stride(0);
+    TORCH_CHECK((e.pre_ld * 2) % 16 == 0, "pre_out rows must be 16-byte aligned");
+  }
+  e.act = (int)act;
+  e.ssq_out = nullptr;
+  if (ssq_out.has_value()) {
+    TORCH_CHECK(ssq_out->dim() == 2 && ssq_out->size(0) == M && ssq_out->is_contiguous(), "ssq_out must be (M, parts)");
+    TORCH_CHECK(!ssq_in.has_value() || ssq_in->size(1) == ssq_out->size(1), "ssq_in/ssq_out parts differ");
+    e.ssq_out = f32_mut(*ssq_out, "ssq_out");
+    e.ssq_parts = (int)ssq_out->size(1);
+  }
+}
+
+// D = A B^T. a: (M,K) [K-major] or (K,M) [a_mn]; b: (N,K) or (K,N) [b_mn].
+void gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, Tensor out, bool accumulate, OptT bias,
+               OptT row_scale, OptT ssq_in, int64_t norm_dim, double norm_eps, OptT aux, int64_t aux_mode,
+               OptT rowcoef, OptT pre_out, int64_t act, OptT ssq_out) {
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm operands must be 2-D");
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm: reduction sizes differ: ", K, " vs ", Kb);
+  gd::GemmOperands op{bf16_ptr(a, "a"), bf16_ptr(b, "b"), a.stride(0), b.stride(0)};
+  gd::GemmShape g{(int)M, (int)N, (int)K, a_mn, b_mn, nullptr, nullptr, 0};
+  gd::GemmEpilogue e;
+  fill_epilogue(e, out, accumulate, bias, row_scale, ssq_in, norm_dim, norm_eps, aux, aux_mode, rowcoef, pre_out, act,
+                ssq_out, M, N);
+  if (ssq_out.has_value()) TORCH_CHECK(ssq_out->size(1) == (N + 127) / 128, "bf16 gemm writes N/128 ssq partials");
+  GD_LAUNCH(gd::launch_gemm_bf16(op, g, e, status_ptr(a), stream_of(a)));
+}
+
+// a8: (M,K) e4m3 with sa (K/128, M); b8: (N,K) e4m3 with sb (N/128, K/128).
+void gemm_fp8(const Tensor& a8, const Tensor& sa, const Tensor& b8, const Tensor& sb, Tensor out, bool accumulate,
+              OptT bias, OptT row_scale, OptT aux, int64_t aux_mode, OptT pre_out, int64_t act) {
+  c10::cuda::CUDAGuard guard(a8.device());
+  TORCH_CHECK(a8.dim() == 2 && b8.dim() == 2, "gemm operands must be 2-D");
+  const int64_t M = a8.size(0), K = a8.size(1), N = b8.size(0);
+  TORCH_CHECK(b8.size(1) == K, "gemm_fp8: reduction sizes differ");
+  const int64_t KB = (K + 127) / 128, NB = (N + 127) / 128;
+  TORCH_CHECK(sa.dim() == 2 && sa.size(0) == KB && sa.size(1) >= M && sa.stride(1) == 1, "sa must be (K/128, M)");
+  TORCH_CHECK(sb.dim() == 2 && sb.size(0) == NB && sb.size(1) == KB && sb.is_contiguous(), "sb must be (N/128, K/128)");
+  gd::GemmOperands op{fp8_mut(a8, "a8"), fp8_mut(b8, "b8"), a8.stride(0), b8.stride(0)};
+  gd::GemmShape g{(int)M, (int)N, (int)K, 0, 0, f32_ptr(sa, "sa"), f32_ptr(sb, "sb"), sa.stride(0)};
+  gd::GemmEpilogue e;
+  std::optional<Tensor> none;
+  fill_epilogue(e, out, accumulate, bias, row_scale, none, 0, 0.0, aux, aux_mode, none, pre_out, act, none, M, N);
+  GD_LAUNCH(gd::launch_gemm_fp8(op, g, e, status_ptr(a8), stream_of(a8)));
+}
+
+void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 3 && out.dim() == 3, "dwconv: x and out must be (B, T, d)");
+  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(1);
+  TORCH_CHECK(w.dim() == 2 && w.size(0) == d && w.is_contiguous(), "dwconv: w must be (d, k) contiguous");
+  TORCH_CHECK(x.stride(0) == x.stride(1) * T && out.stride(0) == out.stride(1) * T, "dwconv: batch stride must be T rows");
+  TORCH_CHECK(out.size(0) == B && out.size(1) == T && out.size(2) == d, "dwconv: out shape");
+  if (halo.has_value()) TORCH_CHECK(halo->is_contiguous() && halo->size(0) == B && halo->size(1) == k - 1 && halo->size(2) == d, "dwconv: halo must be (B, k-1, d)");
+  TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (out.stride(1) * 2) % 16 == 0, "dwconv: rows must be 16-byte aligned");
+  gd::ConvArgs a{bf16_ptr(x, "x"), opt_bf16(halo, "halo"), f32_ptr(w, "w"), bf16_mut(out, "out"), B, T, d, k,
+                 x.stride(1), out.stride(1)};
+  GD_LAUNCH(gd::launch_dwconv_fwd(a, stream_of(x)));
+}
+
+void dwconv_bwd(const Tensor& dc, const Tensor& x, OptT halo, const Tensor& w, OptT tail_add, Tensor dx, OptT dhalo,
+                Tensor dw) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 3 && dc.dim() == 3 && dx.dim() == 3, "dwconv_bwd: tensors must be (B, T, d)");
+  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(1);
+  TORCH_CHECK(dx.is_contiguous() && dw.is_contiguous() && dw.size(0) == d && dw.size(1) == k, "dwconv_bwd: dx/dw layout");
+  TORCH_CHECK(x.stride(0) == x.stride(1) * T && dc.stride(0) == dc.stride(1) * T, "dwconv_bwd: batch stride must be T rows");
+  TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (dc.stride(1) * 2) % 16 == 0, "dwconv_bwd: rows must be 16-byte aligned");
+  if (halo.has_value()) TORCH_CHECK(halo->is_contiguous() && halo->size(1) == k - 1, "dwconv_bwd: halo");
+  if (tail_add.has_value()) TORCH_CHECK(tail_add->is_contiguous() && tail_add->size(1) == k - 1, "dwconv_bwd: tail_add");
+  if (dhalo.has_value()) TORCH_CHECK(dhalo->is_contiguous() && dhalo->size(1) == k - 1, "dwconv_bwd: dhalo");
+  gd::ConvBwdArgs a{bf16_ptr(dc, "dc"), bf16_ptr(x, "x"), opt_bf16(halo, "halo"), f32_ptr(w, "w"),
+                    opt_bf16(tail_add, "tail_add"), bf16_mut(dx, "dx"),
+                    dhalo.has_value() ? bf16_mut(*dhalo, "dhalo") : nullptr, f32_mut(dw, "dw"), B, T, d, k,
+                    dc.stride(1), x.stride(1)};
+  GD_LAUNCH(gd::launch_dwconv_bwd(a, stream_of(x)));
+}
+
+void gate_update_fwd(const Tensor& g_pre, const Tensor& z, const Tensor& c, const Tensor& s, const Tensor& w_r,
+                     Tensor fwd_out, Tensor side_out, OptT gate_out, OptT rstd_out, OptT gate_sum, double eps_r) {
+  c10::cuda::CUDAGuard guard(c.device());
+  const int64_t rows = g_pre.size(0);
+  const int d = (int)g_pre.size(1);
+  TORCH_CHECK(g_pre.is_contiguous() && z.is_contiguous() && fwd_out.is_contiguous() && side_out.is_contiguous(),
+              "gate_update: g_pre, z and outputs must be contiguous (rows, d)");
+  TORCH_CHECK(c.size(0) == rows && s.size(0) == rows && c.size(1) == d && s.size(1) == d && w_r.numel() == d, "gate_update: shapes");
+  gd::GateFwdArgs a{bf16_ptr(g_pre, "g_pre"), bf16_ptr(z, "z"), bf16_ptr(c, "c"), bf16_ptr(s, "s"), f32_ptr(w_r, "w_r"),
+                    bf16_mut(fwd_out, "fwd_out"), bf16_mut(side_out, "side_out"),
+                    gate_out.has_value() ? bf16_mut(*gate_out, "gate_out") : nullptr,
+                    rstd_out.has_value() ? f32_mut(*rstd_out, "rstd_out") : nullptr,
+                    gate_sum.has_value() ? f32_mut(*gate_sum, "gate_sum") : nullptr,
+                    rows, d, c.stride(0), s.stride(0), (float)eps_r};
+  GD_LAUNCH(gd::launch_gate_update_fwd(a, stream_of(c)));
+}
+
+void gate_update_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, const Tensor& z, const Tensor& c,
+                     const Tensor& s, const Tensor& w_r, const Tensor& b2g, const Tensor& rstd_z, const Tensor& ssq_g,
+                     double eps_g, OptT dgate_mean, Tensor dq, Tensor dz, Tensor dsc, Tensor rowcoef, Tensor db2g,
+                     Tensor dw_r, Tensor db2r) {
+  c10::cuda::CUDAGuard guard(c.device());
+  const int64_t rows = g_pre.size(0);
+  const int d = (int)g_pre.size(1);
+  TORCH_CHECK(g_pre.is_contiguous() && z.is_contiguous() && dq.is_contiguous() && dz.is_contiguous() && dsc.is_contiguous(),
+              "gate_update_bwd: contiguity");
+  TORCH_CHECK(dsc.size(0) == rows && dsc.size(1) == 2 * d, "gate_update_bwd: dsc must be (rows, 2d)");
+  TORCH_CHECK(ssq_g.dim() == 2 && ssq_g.size(0) == rows && ssq_g.is_contiguous(), "gate_update_bwd: ssq_g");
+  TORCH_CHECK(db2g.numel() == d && dw_r.numel() == d && db2r.numel() == d && rowcoef.numel() == rows, "gate_update_bwd: sizes");
+  gd::GateBwdArgs a{bf16_ptr(dF, "dF"), bf16_ptr(dS, "dS"), bf16_ptr(g_pre, "g_pre"), bf16_ptr(z, "z"), bf16_ptr(c, "c"),
+                    bf16_ptr(s, "s"), f32_ptr(w_r, "w_r"), f32_ptr(b2g, "b2g"), 1, f32_ptr(rstd_z, "rstd_z"),
+                    f32_ptr(ssq_g, "ssq_g"), (int)ssq_g.size(1), (float)eps_g, opt_f32(dgate_mean, "dgate_mean"),
+                    bf16_mut(dq, "dq"), bf16_mut(dz, "dz"), bf16_mut(dsc, "dsc"), f32_mut(rowcoef, "rowcoef"),
+                    f32_mut(db2g, "db2g"), f32_mut(dw_r, "dw_r"), f32_mut(db2r, "db2r"), rows, d,
+                    dF.stride(0), dS.stride(0), c.stride(0), s.stride(0)};
+  GD_LAUNCH(gd::launch_gate_update_bwd(a, stream_of(c)));
+}
+
+void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor y, OptT rstd, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.dim() == 2, "rmsnorm: (rows, d) contiguous");
+  GD_LAUNCH(gd::launch_rmsnorm_fwd(bf16_ptr(x, "x"), f32_ptr(w, "w"), bf16_mut(y, "y"),
+                                   rstd.has_value() ? f32_mut(*rstd, "rstd") : nullptr, x.size(0), (int)x.size(1),
+                                   (float)eps, stream_of(x)));
+}
+
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor dx, Tensor dw) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && x.dim() == 2, "rmsnorm_bwd: contiguity");
+  GD_LAUNCH(gd::launch_rmsnorm_bwd(bf16_ptr(dy, "dy"), bf16_ptr(x, "x"), f32_ptr(w, "w"), f32_ptr(rstd, "rstd"),
+                                   bf16_mut(dx, "dx"), f32_mut(dw, "dw"), x.size(0), (int)x.size(1), stream_of(x)));
+}
+
+void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t row_mode, OptT q_col, OptT s_col,
+                int64_t col_mode) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2, "quantise: x must be 2-D");
+  gd::QuantArgs a{};
+  a.x = bf16_ptr(x, "x");
+  a.rows = x.size(0);
+  a.cols = (int)x.size(1);
+  a.x_ld = x.stride(0);
+  TORCH_CHECK((a.x_ld * 2) % 16 == 0, "quantise: rows must be 16-byte aligned");
+  a.pre_silu = pre_silu;
+  a.row_mode = (int)row_mode;
+  a.col_mode = (int)col_mode;
+  const int64_t rb = (a.rows + 127) / 128, cb = (a.cols + 127) / 128;
+  if (q_row.has_value()) {
+    TORCH_CHECK(s_row.has_value(), "quantise: s_row needed with q_row");
+    TORCH_CHECK(q_row->dim() == 2 && q_row->size(0) == a.rows && q_row->size(1) == a.cols, "quantise: q_row shape");
+    a.q_row = fp8_mut(*q_row, "q_row");
+    a.q_row_ld = q_row->stride(0);
+    TORCH_CHECK(a.q_row_ld % 8 == 0, "quantise: q_row pitch must be a multiple of 8");
+    a.s_row = f32_mut(*s_row, "s_row");
+    if (row_mode == gd::QUANT_ROWS) {
+      TORCH_CHECK(s_row->dim() == 2 && s_row->size(0) == cb && s_row->size(1) >= a.rows && s_row->stride(1) == 1, "quantise: s_row must be (cols/128, rows)");
+      a.s_row_ld = s_row->stride(0);
+    } else {
+      TORCH_CHECK(row_mode == gd::QUANT_BLOCK && s_row->is_contiguous() && s_row->numel() == rb * cb, "quantise: s_row must be (rows/128, cols/128)");
+    }
+  }
+  if (q_col.has_value()) {
+    TORCH_CHECK(s_col.has_value(), "quantise: s_col needed with q_col");
+    TORCH_CHECK(q_col->dim() == 2 && q_col->size(0) == a.cols && q_col->size(1) == a.rows, "quantise: q_col shape");
+    a.q_col = fp8_mut(*q_col, "q_col");
+    a.q_col_ld = q_col->stride(0);
+    TORCH_CHECK(a.q_col_ld % 16 == 0, "quantise: q_col pitch must be a multiple of 16");
+    a.s_col = f32_mut(*s_col, "s_col");
+    if (col_mode == gd::QUANT_COLS) {
+      TORCH_CHECK(s_col->dim() == 2 && s_col->size(0) == rb && s_col->size(1) >= a.cols && s_col->stride(1) == 1, "quantise: s_col must be (rows/128, cols)");
+      a.s_col_ld = s_col->stride(0);
+    } else {
+      TORCH_CHECK(col_mode == gd::QUANT_BLOCK && s_col->is_contiguous() && s_col->numel() == rb * cb, "quantise: s_col must be (cols/128, rows/128)");
+    }
+  }
+  GD_LAUNCH(gd::launch_quant_tile(a, stream_of(x)));
+}
+
+void quant_tensor(const Tensor& x, const Tensor& scale, Tensor q_row, OptT q_col, OptT amax) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && q_row.is_contiguous(), "quant_tensor: contiguous 2-D");
+  if (q_col.has_value()) TORCH_CHECK(q_col->is_contiguous(), "quant_tensor: q_col contiguous");
+  GD_LAUNCH(gd::launch_quant_tensor(bf16_ptr(x, "x"), f32_ptr(scale, "scale"), fp8_mut(q_row, "q_row"),
+                                    q_col.has_value() ? fp8_mut(*q_col, "q_col") : nullptr,
+                                    amax.has_value() ? f32_mut(*amax, "amax") : nullptr, x.size(0), (int)x.size(1),
+                                    stream_of(x)));
+}
+
+void colsum(const Tensor& x, Tensor out) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && out.numel() == x.size(1), "colsum: shapes");
+  TORCH_CHECK((x.stride(0) * 2) % 16 == 0, "colsum: rows must be 16-byte aligned");
+  GD_LAUNCH(gd::launch_colsum(bf16_ptr(x, "x"), f32_mut(out, "out"), x.size(0), (int)x.size(1), x.stride(0), stream_of(x)));
+}
+
+void scale_cols(const Tensor& w, const Tensor& colw, Tensor out) {
+  c10::cuda::CUDAGuard guard(w.device());
+  TORCH_CHECK(w.is_contiguous() && out.is_contiguous() && w.dim() == 2 && colw.numel() == w.size(1), "scale_cols: shapes");
+  GD_LAUNCH(gd::launch_scale_cols(bf16_ptr(w, "w"), f32_ptr(colw, "colw"), bf16_mut(out, "out"), w.size(0), (int)w.size(1), stream_of(w)));
+}
+
+void unscale_cols_bwd(const Tensor& dW2w, const Tensor& W2, const Tensor& colw, Tensor dW2, Tensor dcolw) {
+  c10::cuda::CUDAGuard guard(W2.device());
+  TORCH_CHECK(dW2w.is_contiguous() && W2.is_contiguous() && dW2.is_contiguous(), "unscale_cols_bwd: contiguity");
+  GD_LAUNCH(gd::launch_unscale_cols_bwd(f32_ptr(dW2w, "dW2w"), bf16_ptr(W2, "W2"), f32_ptr(colw, "colw"),
+                                        f32_mut(dW2, "dW2"), f32_mut(dcolw, "dcolw"), (int)W2.size(0), (int)W2.size(1),
+                                        stream_of(W2)));
+}
+
+void cross_entropy(Tensor logits, const Tensor& targets, Tensor row_loss, const Tensor& inv_count, int64_t vocab,
+                   int64_t ignore_index, double grad_scale, bool write_grad) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && targets.scalar_type() == at::kLong && targets.is_contiguous(), "cross_entropy: inputs");
+  TORCH_CHECK(targets.numel() == logits.size(0) && row_loss.numel() == logits.size(0) && vocab <= logits.size(1), "cross_entropy: sizes");
+  GD_LAUNCH(gd::launch_cross_entropy(bf16_mut(logits, "logits"), targets.data_ptr<int64_t>(), f32_mut(row_loss, "row_loss"),
+                                     f32_ptr(inv_count, "inv_count"), logits.size(0), (int)vocab, logits.stride(0),
+                                     (int)ignore_index, (float)grad_scale, write_grad, stream_of(logits)));
+}
+
+void mem_read_fwd(const Tensor& q, const Tensor& gamma, const Tensor& e, const Tensor& tags, const Tensor& vals,
+                  const Tensor& alpha, Tensor w, Tensor out) {
+  c10::cuda::CUDAGuard guard(q.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&q, &gamma, &e, &tags, &vals, &w, &out}) TORCH_CHECK(t->is_contiguous(), "mem_read: contiguous inputs");
+  const int B = (int)tags.size(0), S = (int)tags.size(1), dsig = (int)tags.size(2), dc = (int)vals.size(2);
+  GD_LAUNCH(gd::launch_mem_read_fwd(f32_ptr(q, "q"), f32_ptr(gamma, "gamma"), f32_ptr(e, "e"), f32_ptr(tags, "tags"),
+                                    f32_ptr(vals, "vals"), f32_ptr(alpha, "alpha"), f32_mut(w, "w"), f32_mut(out, "out"),
+                                    B, S, dsig, dc, stream_of(q)));
+}
+
+void mem_read_bwd(const Tensor& d_out, const Tensor& q, const Tensor& gamma, const Tensor& e, const Tensor& tags,
+                  const Tensor& vals, const Tensor& w, const Tensor& alpha, Tensor d_q, Tensor d_gamma, Tensor d_e,
+                  Tensor d_tags, Tensor d_vals, Tensor d_alpha) {
+  c10::cuda::CUDAGuard guard(q.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&d_out, &q, &gamma, &e, &tags, &vals, &w, &d_q, &d_gamma, &d_e, &d_tags, &d_vals})
+    TORCH_CHECK(t->is_contiguous(), "mem_read_bwd: contiguous tensors");
+  const int B = (int)tags.size(0), S = (int)tags.size(1), dsig = (int)tags.size(2), dc = (int)vals.size(2);
+  GD_LAUNCH(gd::launch_mem_read_bwd(f32_ptr(d_out, "d_out"), f32_ptr(q, "q"), f32_ptr(gamma, "gamma"), f32_ptr(e, "e"),
+                                    f32_ptr(tags, "tags"), f32_ptr(vals, "vals"), f32_ptr(w, "w"), f32_ptr(alpha, "alpha"),
+                                    f32_mut(d_q, "d_q"), f32_mut(d_gamma, "d_gamma"), f32_mut(d_e, "d_e"),
+                                    f32_mut(d_tags, "d_tags"), f32_mut(d_vals, "d_vals"), f32_mut(d_alpha, "d_alpha"),
+                                    B, S, dsig, dc, stream_of(q)));
+}
+
+void grad_dots(const Tensor& gt, OptT gi, Tensor sums) {
+  c10::cuda::CUDAGuard guard(gt.device());
+  TORCH_CHECK(gt.is_contiguous() && sums.numel() >= 3, "grad_dots: inputs");
+  if (gi.has_value()) TORCH_CHECK(gi->is_contiguous() && gi->numel() == gt.numel(), "grad_dots: gi size");
+  GD_LAUNCH(gd::launch_grad_dots(f32_ptr(gt, "gt"), opt_f32(gi, "gi"), f32_mut(sums, "sums"), gt.numel(), stream_of(gt)));
+}
+
+void projected_adamw(Tensor p, const Tensor& gt, OptT gi, Tensor m, Tensor v, const Tensor& scalars, double beta_proj,
+                     double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step) {
+  c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.is_contiguous() && gt.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguity");
+  TORCH_CHECK(gt.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel() && scalars.numel() >= 2, "adamw: sizes");
+  gd::AdamWArgs a{};
+  if (p.scalar_type() == at::kBFloat16) a.p_bf16 = reinterpret_cast<__nv_bfloat16*>(p.data_ptr());
+  else { TORCH_CHECK(p.scalar_type() == at::kFloat, "adamw: params must be bf16 or fp32"); a.p_f32 = p.data_ptr<float>(); }
+  a.gt = f32_ptr(gt, "gt");
+  a.gi = opt_f32(gi, "gi");
+  a.m = f32_mut(m, "m");
+  a.v = f32_mut(v, "v");
+  a.scalars = f32_ptr(scalars, "scalars");
+  a.n = p.numel();
+  a.beta_proj = (float)beta_proj; a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2;
+  a.eps = (float)eps; a.weight_decay = (float)weight_decay;
+  a.bc1 = (float)(1.0 - std::pow(beta1, (double)step));
+  a.bc2 = (float)(1.0 - std::pow(beta2, (double)step));
+  GD_LAUNCH(gd::launch_projected_adamw(a, stream_of(p)));
+}
+
+// tables: int64 device tensors of pointers (mats, vecs, outs) and int32 (rows, cols, is_bf16)
+void batched_gemv(const Tensor& mats, const Tensor& vecs, const Tensor& outs, const Tensor& rows, const Tensor& cols,
+                  const Tensor& is_bf16, int64_t max_rows) {
+  c10::cuda::CUDAGuard guard(mats.device());
+  const int n = (int)mats.numel();
+  GD_LAUNCH(gd::launch_batched_gemv(reinterpret_cast<const void* const*>(mats.data_ptr<int64_t>()),
+                                    reinterpret_cast<const float* const*>(vecs.data_ptr<int64_t>()),
+                                    reinterpret_cast<float* const*>(outs.data_ptr<int64_t>()), rows.data_ptr<int>(),
+                                    cols.data_ptr<int>(), is_bf16.data_ptr<int>(), n, (int)max_rows, stream_of(mats)));
+}
+
+// ---- communication kernels over peer memory (comm.cu) -----------------------------------------
+void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, const Tensor& ptr_table_p,
+                     const Tensor& signal_table, Tensor m, Tensor v, const Tensor& scalars, int64_t n, int64_t rank,
+                     int64_t world, int64_t seq, int64_t phase, bool p_is_bf16, double beta_proj, double lr, double beta1,
+                     double beta2, double eps, double weight_decay, int64_t step, Tensor shard_sums) {
+  c10::cuda::CUDAGuard guard(m.device());
+  gd::FusedReduceAdamWArgs a{};
+  a.gt = reinterpret_cast<float* const*>(ptr_table_gt.data_ptr<int64_t>());
+  a.gi = reinterpret_cast<float* const*>(ptr_table_gi.data_ptr<int64_t>());
+  a.p = reinterpret_cast<void* const*>(ptr_table_p.data_ptr<int64_t>());
+  a.signals = reinterpret_cast<uint32_t* const*>(signal_table.data_ptr<int64_t>());
+  a.m = f32_mut(m, "m");
+  a.v = f32_mut(v, "v");
+  a.scalars = f32_ptr(scalars, "scalars");
+  a.shard_sums = f32_mut(shard_sums, "shard_sums");
+  a.n = n; a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq; a.phase = (int)phase; a.p_is_bf16 = p_is_bf16;
+  a.beta_proj = (float)beta_proj; a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2;
+  a.eps = (float)eps; a.weight_decay = (float)weight_decay;
+  a.bc1 = (float)(1.0 - std::pow(beta1, (double)step));
+  a.bc2 = (float)(1.0 - std::pow(beta2, (double)step));
+  a.status = status_ptr(m);
+  GD_LAUNCH(gd::launch_fused_reduce_adamw(a, stream_of(m)));
+}
+
+void halo_push_wait(const Tensor& tail, Tensor halo_out, const Tensor& slot_ptrs, const Tensor& flag_ptrs,
+                    int64_t slot_offset_bytes, int64_t flag_index, int64_t rank, int64_t world, int64_t seq,
+                    bool reverse) {
+  c10::cuda::CUDAGuard guard(tail.device());
+  TORCH_CHECK(tail.is_contiguous() && halo_out.is_contiguous() && tail.numel() == halo_out.numel(), "halo: shapes");
+  TORCH_CHECK((tail.numel() * tail.element_size()) % 16 == 0, "halo: message must be a multiple of 16 bytes");
+  gd::HaloArgs a{};
+  a.tail = tail.data_ptr();
+  a.halo_out = halo_out.data_ptr();
+  a.nbytes = tail.numel() * tail.element_size();
+  a.slots = reinterpret_cast<uint8_t* const*>(slot_ptrs.data_ptr<int64_t>());
+  a.flags = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
+  a.slot_offset = slot_offset_bytes;
+  a.flag_index = (int)flag_index;
+  a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq; a.reverse = reverse;
+  a.status = status_ptr(tail);
+  GD_LAUNCH(gd::launch_halo_push_wait(a, stream_of(tail)));
+}
+
+}  // namespace
+
+TORCH_LIBRARY(gdnet_b200, m) {
+  m.def("kernel_status(Tensor like) -> Tensor", &kernel_status);
+  m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? ssq_in, int norm_dim, float norm_eps, Tensor? aux, int aux_mode, Tensor? rowcoef, Tensor(b!)? pre_out, int act, Tensor(c!)? ssq_out) -> ()", &gemm_bf16);
+  m.def("gemm_fp8(Tensor a8, Tensor sa, Tensor b8, Tensor sb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8);
+  m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out) -> ()", &dwconv_fwd);
+  m.def("dwconv_bwd(Tensor dc, Tensor x, Tensor? halo, Tensor w, Tensor? tail_add, Tensor(a!) dx, Tensor(b!)? dhalo, Tensor(c!) dw) -> ()", &dwconv_bwd);
+  m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r) -> ()", &gate_update_fwd);
+  m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r) -> ()", &gate_update_bwd);
+  m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!)? rstd, float eps) -> ()", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw) -> ()", &rmsnorm_bwd);
+  m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode) -> ()", &quant_tile);
+  m.def("quant_tensor(Tensor x, Tensor scale, Tensor(a!) q_row, Tensor(b!)? q_col, Tensor(c!)? amax) -> ()", &quant_tensor);
+  m.def("colsum(Tensor x, Tensor(a!) out) -> ()", &colsum);
+  m.def("scale_cols(Tensor w, Tensor colw, Tensor(a!) out) -> ()", &scale_cols);
+  m.def("unscale_cols_bwd(Tensor dW2w, Tensor W2, Tensor colw, Tensor(a!) dW2, Tensor(b!) dcolw) -> ()", &unscale_cols_bwd);
+  m.def("cross_entropy(Tensor(a!) logits, Tensor targets, Tensor(b!) row_loss, Tensor inv_count, int vocab, int ignore_index, float grad_scale, bool write_grad) -> ()", &cross_entropy);
+  m.def("mem_read_fwd(Tensor q, Tensor gamma, Tensor e, Tensor tags, Tensor vals, Tensor alpha, Tensor(a!) w, Tensor(b!) out) -> ()", &mem_read_fwd);
+  m.def("mem_read_bwd(Tensor d_out, Tensor q, Tensor gamma, Tensor e, Tensor tags, Tensor vals, Tensor w, Tensor alpha, Tensor(a!) d_q, Tensor(b!) d_gamma, Tensor(c!) d_e, Tensor(d!) d_tags, Tensor(e!) d_vals, Tensor(f!) d_alpha) -> ()", &mem_read_bwd);
+  m.def("grad_dots(Tensor gt, Tensor? gi, Tensor(a!) sums) -> ()", &grad_dots);
+  m.def("projected_adamw(Tensor(a!) p, Tensor gt, Tensor? gi, Tensor(b!) m, Tensor(c!) v, Tensor scalars, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()", &projected_adamw);
+  m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
+  m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums) -> ()", &allreduce_adamw);
+  m.def("halo_push_wait(Tensor tail, Tensor(a!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, int slot_offset_bytes, int flag_index, int rank, int world, int seq, bool reverse) -> ()", &halo_push_wait);
+}

@@ -1,0 +1,61 @@
+// Kernels that fuse compute with communication over NVLink peer memory (comm.cu).
+//
+// Peer buffers are ordinary device pointers into other GPUs' memory (CUDA VMM mappings made
+// by torch's symmetric-memory allocator). The kernels read and write them with plain
+// vectorised loads and stores plus system-scope release/acquire flags; there is no bulk
+// tensor copy with a cluster-wide broadcast anywhere in this file.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gd {
+
+struct Status;
+
+// Gradient all-reduce (as reduce-scatter over peer memory) fused with the gradient projection,
+// the AdamW update of this rank's shard and the all-gather of the updated parameters.
+//
+//   phase 0: everything in one launch (no gradient clipping)
+//   phase 1: barrier, reduce this rank's shard of both gradients in place, shard dot products
+//   phase 2: AdamW on the shard (scalars now hold the clip factor), write the new parameters
+//            into every rank's parameter buffer, closing barrier
+struct FusedReduceAdamWArgs {
+  float* const* gt;        // [world] task-gradient buffers (fp32, n elements each)
+  float* const* gi;        // [world] info-gradient buffers
+  void* const* p;          // [world] parameter buffers (bf16 or fp32, n elements each)
+  uint32_t* const* signals;  // [world] flag words: signals[r][phase_slot * world + writer]
+  float* m;                // AdamW moments of the local shard (shard_len elements)
+  float* v;
+  const float* scalars;    // [coef, grad_scale]
+  float* shard_sums;       // [3] += sum GT^2, sum GT*GI, sum GI^2 over the reduced shard; [4] block counter
+  int64_t n;
+  int rank, world;
+  uint32_t seq;            // strictly increasing per call pair
+  int p_is_bf16;
+  int phase;
+  float beta_proj, lr, beta1, beta2, eps, weight_decay, bc1, bc2;
+  Status* status;
+};
+const char* launch_fused_reduce_adamw(const FusedReduceAdamWArgs& a, cudaStream_t st);
+
+// Sequence-parallel neighbour exchange: store `tail` into the next rank's slot, raise its flag,
+// wait (bounded) for this rank's own flag from the previous rank, copy the slot out.
+// reverse = true exchanges in the other direction (halo gradients).
+struct HaloArgs {
+  const void* tail;
+  void* halo_out;
+  int64_t nbytes;
+  uint8_t* const* slots;   // [world] base of every rank's slot area
+  uint32_t* const* flags;  // [world] base of every rank's flag area
+  int64_t slot_offset;     // byte offset of this exchange's slot
+  int flag_index;
+  int rank, world;
+  uint32_t seq;
+  int reverse;
+  Status* status;
+};
+const char* launch_halo_push_wait(const HaloArgs& a, cudaStream_t st);
+
+}  // namespace gd

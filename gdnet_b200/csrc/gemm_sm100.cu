@@ -1,0 +1,568 @@
+// Tensor-core GEMMs for sm_100a: D[M,N] = A[M,K] * B[N,K]^T with fused epilogues.
+//
+// Two persistent, warp-specialised kernels share one structure:
+//
+//   warp 0      TMA producer: tiled bulk tensor loads (128-byte swizzle) into a ring of
+//               shared-memory stages; one mbarrier pair (full/empty) per stage
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma with shared-memory
+//               descriptors; accumulators live in tensor memory (TMEM), which this warp
+//               allocates and frees; tcgen05.commit releases stages / publishes accumulators
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (a warp may only touch TMEM lanes
+//               32*(warp%4)..+31, so two warps share a lane quarter and split the columns),
+//               apply the fused epilogue, store to global memory
+//
+//   gemm_bf16_kernel   bf16 x bf16 -> fp32 in TMEM over the whole K; tile 128 x 256;
+//                      two accumulator stages so the epilogue of a tile overlaps the
+//                      main loop of the next. Operands may be K-major or MN-major (the
+//                      weight-gradient GEMM reduces over tokens and reads both of its
+//                      row-major operands MN-major, so nothing is transposed in memory).
+//   gemm_fp8_kernel    e4m3 x e4m3 with block scales (1x128 on A rows, 128x128 on B):
+//                      every 128-deep K block is a fresh accumulation in one of four
+//                      TMEM stages; the epilogue warps scale it by sa[m,kb]*sb[nb,kb] and
+//                      add it to fp32 registers (two-level accumulation); tile 128 x 128.
+//
+// Every wait is bounded (see common.cuh); on expiry the CTA records a status code,
+// raises a CTA-wide abort flag, drains, frees its TMEM and returns.
+#include "gemm_sm100.h"
+
+#include "common.cuh"
+
+namespace gd {
+
+constexpr int BM = 128;
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
+constexpr int STAGE_ROW_BYTES = 128;  // one swizzle row: 64 bf16 or 128 e4m3 along the box's inner dim
+
+struct __align__(8) PipeBars {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[4];
+  uint64_t tmem_empty[4];
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ bool aborted(const PipeBars* b) { return *((volatile const int*)&b->abort) != 0; }
+
+__device__ __forceinline__ void raise_abort(PipeBars* b, Status* st, int code, int site, int detail) {
+  report(st, code, site, detail);
+  *((volatile int*)&b->abort) = 1;
+}
+
+// ---------------------------------------------------------------------------------------
+// fused epilogue on one row x 32 columns held in registers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float load_bias(const GemmEpilogue& e, int n) {
+  if (e.bias == nullptr) return 0.0f;
+  return e.bias_f32 ? reinterpret_cast<const float*>(e.bias)[n]
+                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.bias)[n]);
+}
+
+__device__ __forceinline__ float row_scale_for(const GemmEpilogue& e, int m) {
+  if (e.row_scale != nullptr) return e.row_scale[m];
+  if (e.ssq_in != nullptr) {
+    float s = 0.0f;
+    for (int p = 0; p < e.ssq_parts; ++p) s += e.ssq_in[(size_t)m * e.ssq_parts + p];
+    return rsqrtf(s / (float)e.norm_dim + e.norm_eps);
+  }
+  return 1.0f;
+}
+
+// v: 32 consecutive columns starting at n0 of row m. Returns this chunk's sum of squares of
+// the stored values (for the RMSNorm that follows the activation).
+__device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, int N, int m, int n0, float rs,
+                                                float rowcoef, float (&v)[32]) {
+  float ssq = 0.0f;
+  if (m >= M || n0 >= N) return 0.0f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = v[j] * rs + load_bias(e, n0 + j);
+
+  if (e.aux != nullptr) {
+    const uint4* ap = reinterpret_cast<const uint4*>(e.aux + (size_t)m * e.aux_ld + n0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 u = ap[q];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 a = unpack_bf16x2(w[t]);
+        const int j = q * 8 + t * 2;
+        if (e.aux_mode == AUX_ADD) {
+          v[j] += a.x;
+          v[j + 1] += a.y;
+        } else if (e.aux_mode == AUX_MUL_SILU_GRAD) {
+          v[j] *= silu_grad_(a.x);
+          v[j + 1] *= silu_grad_(a.y);
+        } else {  // AUX_RMS_SILU_BWD: (v - silu(aux) * rowcoef) * silu'(aux)
+          v[j] = (v[j] - siluf_(a.x) * rowcoef) * silu_grad_(a.x);
+          v[j + 1] = (v[j + 1] - siluf_(a.y) * rowcoef) * silu_grad_(a.y);
+        }
+      }
+    }
+  }
+
+  if (e.pre_out != nullptr) {
+    uint4* pp = reinterpret_cast<uint4*>(e.pre_out + (size_t)m * e.pre_ld + n0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      pp[q] = make_uint4(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
+                         pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]));
+  }
+
+  if (e.act == ACT_SILU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = siluf_(v[j]);
+  }
+
+  if (e.out_f32) {
+    float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(e.out) + (size_t)m * e.out_ld + n0);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      if (e.accumulate) {
+        const float4 old = op[q];
+        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+      }
+      op[q] = o;
+    }
+  } else {
+    uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)m * e.out_ld + n0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float a = v[q * 8 + t * 2], b = v[q * 8 + t * 2 + 1];
+        w[t] = pack_bf16x2(a, b);
+        const float2 r = unpack_bf16x2(w[t]);
+        ssq += r.x * r.x + r.y * r.y;
+      }
+      if (e.accumulate) {
+        const uint4 old = op[q];
+        const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 o = unpack_bf16x2(ow[t]);
+          w[t] = pack_bf16x2(v[q * 8 + t * 2] + o.x, v[q * 8 + t * 2 + 1] + o.y);
+        }
+      }
+      op[q] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  return ssq;
+}
+
+// ---------------------------------------------------------------------------------------
+// shared prologue / teardown
+// ---------------------------------------------------------------------------------------
+template <int STAGES, int ACC_STAGES>
+__device__ __forceinline__ void pipe_setup(PipeBars* bars, int warp, int lane, uint32_t tmem_cols,
+                                           const CUtensorMap* ta, const CUtensorMap* tb) {
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(ta);
+    tma_prefetch_desc(tb);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < ACC_STAGES; ++a) {
+      mbar_init(smem_u32(&bars->tmem_full[a]), 1);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), EPI_WARPS);
+    }
+    bars->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&bars->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+}
+
+__device__ __forceinline__ void pipe_teardown(PipeBars* bars, int warp, uint32_t tmem_cols) {
+  tc_fence_before_sync();
+  __syncthreads();
+  if (aborted(bars)) {
+    // give bulk copies that are still in flight time to land before the CTA's shared
+    // memory is handed to another CTA (bounded: ~100 us)
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(bars->tmem_base, tmem_cols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// bf16 kernel
+// ---------------------------------------------------------------------------------------
+constexpr int BF16_BN = 256;
+constexpr int BF16_BK = 64;
+constexpr int BF16_STAGES = 4;
+constexpr int BF16_ACC = 2;
+constexpr int BF16_A_BYTES = BM * STAGE_ROW_BYTES;       // 16 KB
+constexpr int BF16_B_BYTES = BF16_BN * STAGE_ROW_BYTES;  // 32 KB
+constexpr int BF16_STAGE_BYTES = BF16_A_BYTES + BF16_B_BYTES;
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmShape g, const GemmEpilogue e, Status* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + BF16_STAGES * BF16_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  pipe_setup<BF16_STAGES, BF16_ACC>(bars, warp, lane, BF16_ACC * BF16_BN, &tmap_a, &tmap_b);
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int n_tiles_n = (g.N + BF16_BN - 1) / BF16_BN;
+  const int n_tiles = ((g.M + BM - 1) / BM) * n_tiles_n;
+  const int kblocks = (g.K + BF16_BK - 1) / BF16_BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
+        const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BF16_BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 10, s);
+            break;
+          }
+          if (aborted(bars)) break;
+          const uint32_t full = smem_u32(&bars->full[s]);
+          const uint32_t a_dst = smem_u32(smem + s * BF16_STAGE_BYTES);
+          const uint32_t b_dst = a_dst + BF16_A_BYTES;
+          mbar_arrive_expect_tx(full, BF16_STAGE_BYTES);
+          if (!g.a_mn) {
+            tma_load_2d(a_dst, &tmap_a, full, kb * BF16_BK, m0);
+          } else {
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d(a_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_a, full, m0 + i * 64, kb * BF16_BK);
+          }
+          if (!g.b_mn) {
+            tma_load_2d(b_dst, &tmap_b, full, kb * BF16_BK, n0);
+          } else {
+            for (int i = 0; i < BF16_BN / 64; ++i)
+              tma_load_2d(b_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_b, full, n0 + i * 64, kb * BF16_BK);
+          }
+          if (++s == BF16_STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc(1, 1, g.a_mn ? 1 : 0, g.b_mn ? 1 : 0, BM, BF16_BN);
+      const uint32_t a_lbo = g.a_mn ? BF16_BK * STAGE_ROW_BYTES : 16, b_lbo = g.b_mn ? BF16_BK * STAGE_ROW_BYTES : 16;
+      // K advance per MMA (UMMA_K = 16 elements): 32 B inside the swizzle row when K-major,
+      // 16 rows of 128 B when MN-major; in 16-byte units.
+      const uint32_t a_step = g.a_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2, b_step = g.b_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2;
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
+        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_ph ^ 1)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 11, acc);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BF16_BN;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->full[s]), ph) || aborted(bars)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 12, s);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * BF16_STAGE_BYTES);
+          const uint64_t adesc = make_smem_desc(a_addr, a_lbo, 1024);
+          const uint64_t bdesc = make_smem_desc(a_addr + BF16_A_BYTES, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BF16_BK / 16; ++k)
+            mma_bf16(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, (kb | k) != 0);
+          mma_commit(smem_u32(&bars->empty[s]));
+          if (++s == BF16_STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(smem_u32(&bars->tmem_full[acc]));
+        if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    const int quarter = warp & 3;        // TMEM lane quarter this warp may access
+    const int col_half = ew >> 2;        // which 128 of the tile's 256 columns
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
+      const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BF16_BN;
+      const int m = m0 + quarter * 32 + lane;
+      const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
+      const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
+      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_ph)) {
+        raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 13, acc);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BF16_BN + col_half * 128;
+      float ssq = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32(t_row + c * 32, raw);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        ssq += epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 128 + c * 32, rs, rc, v);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+      if (e.ssq_out != nullptr && m < g.M && n0 + col_half * 128 < g.N)
+        e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 128 + col_half)] = ssq;
+      if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+  pipe_teardown(bars, warp, BF16_ACC * BF16_BN);
+}
+
+// ---------------------------------------------------------------------------------------
+// block-scaled FP8 kernel
+// ---------------------------------------------------------------------------------------
+constexpr int FP8_BN = 128;
+constexpr int FP8_BK = 128;
+constexpr int FP8_STAGES = 6;
+constexpr int FP8_ACC = 4;
+constexpr int FP8_A_BYTES = BM * STAGE_ROW_BYTES;
+constexpr int FP8_B_BYTES = FP8_BN * STAGE_ROW_BYTES;
+constexpr int FP8_STAGE_BYTES = FP8_A_BYTES + FP8_B_BYTES;
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmShape g, const GemmEpilogue e, Status* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + FP8_STAGES * FP8_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  pipe_setup<FP8_STAGES, FP8_ACC>(bars, warp, lane, FP8_ACC * FP8_BN, &tmap_a, &tmap_b);
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int n_tiles_n = (g.N + FP8_BN - 1) / FP8_BN;
+  const int n_tiles = ((g.M + BM - 1) / BM) * n_tiles_n;
+  const int kblocks = (g.K + FP8_BK - 1) / FP8_BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
+        const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * FP8_BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 20, s);
+            break;
+          }
+          if (aborted(bars)) break;
+          const uint32_t full = smem_u32(&bars->full[s]);
+          const uint32_t a_dst = smem_u32(smem + s * FP8_STAGE_BYTES);
+          mbar_arrive_expect_tx(full, FP8_STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, full, kb * FP8_BK, m0);
+          tma_load_2d(a_dst + FP8_A_BYTES, &tmap_b, full, kb * FP8_BK, n0);
+          if (++s == FP8_STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc(0, 0, 0, 0, BM, FP8_BN);
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok && !aborted(bars); tile += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_ph ^ 1)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 21, acc);
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(smem_u32(&bars->full[s]), ph) || aborted(bars)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 22, s);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * FP8_STAGE_BYTES);
+          const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
+          const uint64_t bdesc = make_smem_desc(a_addr + FP8_A_BYTES, 16, 1024);
+          const uint32_t d_tmem = tmem_base + acc * FP8_BN;
+#pragma unroll
+          for (int k = 0; k < FP8_BK / 32; ++k)
+            mma_fp8(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, k != 0);
+          mma_commit(smem_u32(&bars->empty[s]));
+          mma_commit(smem_u32(&bars->tmem_full[acc]));
+          if (++s == FP8_STAGES) { s = 0; ph ^= 1; }
+          if (++acc == FP8_ACC) { acc = 0; acc_ph ^= 1; }
+        }
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int col_half = ew >> 2;  // which 64 of the tile's 128 columns
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok && !aborted(bars); tile += gridDim.x) {
+      const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * FP8_BN;
+      const int m = m0 + quarter * 32 + lane;
+      const int m_ld = (m < g.M) ? m : (g.M - 1);
+      const int nb = n0 / 128;
+      float accum[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) accum[j] = 0.0f;
+      float scale = g.sa[m_ld] * g.sb[(size_t)nb * kblocks];
+      for (int kb = 0; kb < kblocks; ++kb) {
+        float next_scale = 0.0f;
+        if (kb + 1 < kblocks) next_scale = g.sa[(size_t)(kb + 1) * g.sa_ld + m_ld] * g.sb[(size_t)nb * kblocks + kb + 1];
+        if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_ph)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 23, acc);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * FP8_BN + col_half * 64;
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(t_row, r0);
+        tmem_ld_32x32(t_row + 32, r1);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          accum[j] = fmaf(scale, __uint_as_float(r0[j]), accum[j]);
+          accum[32 + j] = fmaf(scale, __uint_as_float(r1[j]), accum[32 + j]);
+        }
+        scale = next_scale;
+        if (++acc == FP8_ACC) { acc = 0; acc_ph ^= 1; }
+      }
+      if (!ok) break;
+      const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
+      const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
+      float ssq = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = accum[c * 32 + j];
+        ssq += epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 64 + c * 32, rs, rc, v);
+      }
+      if (e.ssq_out != nullptr && m < g.M)
+        e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
+    }
+  }
+  pipe_teardown(bars, warp, FP8_ACC * FP8_BN);
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows][cols] with a row pitch of ld elements; box = box_rows x (128 bytes of cols).
+const char* make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, int64_t rows, int64_t cols,
+                               int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return "cuTensorMapEncodeTiled entry point not found";
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return "tensor base is not 16-byte aligned";
+  if ((ld * elem_bytes) % 16 != 0) return "row pitch is not a multiple of 16 bytes";
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld * elem_bytes)};
+  cuuint32_t box[2] = {(cuuint32_t)(STAGE_ROW_BYTES / elem_bytes), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
+                             cudaStream_t stream) {
+  if (g.K % 8 != 0 || g.N % 32 != 0) return "bf16 GEMM needs K % 8 == 0 and N % 32 == 0";
+  CUtensorMap ta, tb;
+  const char* err;
+  if (!g.a_mn) err = make_tensor_map_2d(&ta, op.a, 2, g.M, g.K, op.a_ld, BM);
+  else err = make_tensor_map_2d(&ta, op.a, 2, g.K, g.M, op.a_ld, BF16_BK);   // rows = reduction, cols = M
+  if (err) return err;
+  if (!g.b_mn) err = make_tensor_map_2d(&tb, op.b, 2, g.N, g.K, op.b_ld, BF16_BN);
+  else err = make_tensor_map_2d(&tb, op.b, 2, g.K, g.N, op.b_ld, BF16_BK);
+  if (err) return err;
+  static bool attr_set = false;
+  const int smem = BF16_STAGES * BF16_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return "cudaFuncSetAttribute(gemm_bf16_kernel) failed";
+    attr_set = true;
+  }
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BF16_BN - 1) / BF16_BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_bf16_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, g, e, status);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_bf16_kernel launch failed";
+}
+
+const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
+                            cudaStream_t stream) {
+  if (g.K % 128 != 0 || g.N % 64 != 0) return "fp8 GEMM needs K % 128 == 0 and N % 64 == 0";
+  if (g.sa == nullptr || g.sb == nullptr) return "fp8 GEMM needs block scales";
+  CUtensorMap ta, tb;
+  const char* err = make_tensor_map_2d(&ta, op.a, 1, g.M, g.K, op.a_ld, BM);
+  if (err) return err;
+  err = make_tensor_map_2d(&tb, op.b, 1, g.N, g.K, op.b_ld, FP8_BN);
+  if (err) return err;
+  static bool attr_set = false;
+  const int smem = FP8_STAGES * FP8_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return "cudaFuncSetAttribute(gemm_fp8_kernel) failed";
+    attr_set = true;
+  }
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + FP8_BN - 1) / FP8_BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_fp8_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, g, e, status);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_kernel launch failed";
+}
+
+}  // namespace gd

@@ -1,0 +1,65 @@
+// Host-visible interface of the sm_100a tensor-core GEMMs (gemm_sm100.cu).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gd {
+
+struct Status;
+
+enum AuxMode : int {
+  AUX_NONE = 0,
+  AUX_ADD = 1,            // v += aux
+  AUX_MUL_SILU_GRAD = 2,  // v *= silu'(aux)
+  AUX_RMS_SILU_BWD = 3,   // v = (v - silu(aux) * rowcoef[m]) * silu'(aux)
+};
+
+enum Activation : int { ACT_NONE = 0, ACT_SILU = 1 };
+
+struct GemmOperands {
+  const void* a;  // K-major: [M][K] row-major. MN-major: [K][M] row-major.
+  const void* b;  // K-major: [N][K] row-major. MN-major: [K][N] row-major.
+  int64_t a_ld;   // row pitch in elements
+  int64_t b_ld;
+};
+
+struct GemmShape {
+  int M, N, K;
+  int a_mn, b_mn;   // bf16 only: operand is MN-major in memory
+  const float* sa;  // fp8: scales of A, sa[kb * sa_ld + m]
+  const float* sb;  // fp8: scales of B, sb[(n / 128) * ceil(K/128) + kb]
+  int64_t sa_ld;
+};
+
+// Applied in this order to the fp32 accumulator of element (m, n):
+//   v = acc * row_scale(m) + bias[n];  aux;  pre_out = v;  v = act(v);  out (+)= v
+struct GemmEpilogue {
+  void* out;            // bf16 (default) or fp32 [M][out_ld]
+  int64_t out_ld;
+  int out_f32;
+  int accumulate;       // out += v instead of out = v
+  const void* bias;     // [N] bf16 or fp32, may be null
+  int bias_f32;
+  const float* row_scale;   // [M], may be null
+  const float* ssq_in;      // [M][ssq_parts]: row_scale = rsqrt(sum/norm_dim + norm_eps) when row_scale is null
+  int ssq_parts;
+  int norm_dim;
+  float norm_eps;
+  const __nv_bfloat16* aux; // [M][aux_ld], may be null
+  int64_t aux_ld;
+  int aux_mode;
+  const float* rowcoef;     // [M], used by AUX_RMS_SILU_BWD
+  __nv_bfloat16* pre_out;   // [M][pre_ld]: value before the activation, may be null
+  int64_t pre_ld;
+  int act;
+  float* ssq_out;           // [M][ssq_parts]: per-row partial sums of squares of the stored values
+};
+
+const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
+                             cudaStream_t stream);
+const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
+                            cudaStream_t stream);
+
+}  // namespace gd

@@ -1,0 +1,162 @@
+// Host-visible launchers of the memory-bound kernels (elementwise.cu, loss_optim.cu, comm.cu).
+// Every launcher returns nullptr on success or a static message naming what was wrong; none
+// of them allocates memory or synchronises.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gd {
+
+struct Status;
+
+// ---- causal depthwise conv ------------------------------------------------------------------
+struct ConvArgs {
+  const __nv_bfloat16* x;     // (B, T, d), row pitch x_ld
+  const __nv_bfloat16* halo;  // (B, k-1, d) or null (zeros)
+  const float* w;             // (d, k)
+  __nv_bfloat16* out;         // (B, T, d), row pitch out_ld
+  int B, T, d, k;
+  int64_t x_ld, out_ld;
+};
+
+struct ConvBwdArgs {
+  const __nv_bfloat16* dc;    // (B, T, d), row pitch dc_ld
+  const __nv_bfloat16* x;     // (B, T, d), row pitch x_ld
+  const __nv_bfloat16* halo;  // (B, k-1, d) or null
+  const float* w;             // (d, k)
+  const __nv_bfloat16* dx_tail_add;  // (B, k-1, d) or null: halo gradient from the next shard
+  __nv_bfloat16* dx;          // (B, T, d) contiguous
+  __nv_bfloat16* dhalo;       // (B, k-1, d) or null
+  float* dw;                  // (d, k), accumulated with atomics
+  int B, T, d, k;
+  int64_t dc_ld, x_ld;
+};
+
+const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st);
+const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st);
+
+// ---- gate / stream update ---------------------------------------------------------------------
+struct GateFwdArgs {
+  const __nv_bfloat16* g_pre;  // (rows, d)
+  const __nv_bfloat16* z;      // (rows, d) recovery pre-norm
+  const __nv_bfloat16* c;      // (rows, d) pitch c_ld
+  const __nv_bfloat16* s;      // (rows, d) pitch s_ld
+  const float* w_r;            // (d) recovery RMSNorm weight
+  __nv_bfloat16* fwd_out;      // (rows, d)
+  __nv_bfloat16* side_out;     // (rows, d)
+  __nv_bfloat16* gate_out;     // (rows, d) or null
+  float* rstd_out;             // (rows) or null
+  float* gate_sum;             // scalar accumulator or null
+  int64_t rows;
+  int d;
+  int64_t c_ld, s_ld;
+  float eps_r;
+};
+
+struct GateBwdArgs {
+  const __nv_bfloat16* dF;   // (rows, d) pitch dF_ld
+  const __nv_bfloat16* dS;   // (rows, d) pitch dS_ld
+  const __nv_bfloat16* g_pre;
+  const __nv_bfloat16* z;
+  const __nv_bfloat16* c;    // pitch c_ld
+  const __nv_bfloat16* s;    // pitch s_ld
+  const float* w_r;
+  const void* b2g;           // (d) gate W2 bias
+  int b2g_f32;
+  const float* rstd_z;       // (rows)
+  const float* ssq_g;        // (rows, ssq_parts) partial sums of squares of silu(W1 c + b1)
+  int ssq_parts;
+  float eps_g;
+  const float* dgate_mean;   // scalar d(loss)/d(mean gate) or null
+  __nv_bfloat16* dq;         // (rows, d)
+  __nv_bfloat16* dz;         // (rows, d)
+  __nv_bfloat16* dsc;        // (rows, 2d): [ds_dir | dc_dir]
+  float* rowcoef;            // (rows)
+  float* db2g;               // (d) accumulated
+  float* dw_r;               // (d) accumulated
+  float* db2r;               // (d) accumulated
+  int64_t rows;
+  int d;
+  int64_t dF_ld, dS_ld, c_ld, s_ld;
+};
+
+const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st);
+const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st);
+
+const char* launch_rmsnorm_fwd(const __nv_bfloat16* x, const float* w, __nv_bfloat16* y, float* rstd, int64_t rows,
+                               int d, float eps, cudaStream_t st);
+const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* rstd,
+                               __nv_bfloat16* dx, float* dw, int64_t rows, int d, cudaStream_t st);
+
+// ---- FP8 quantisation -------------------------------------------------------------------------
+enum QuantMode : int { QUANT_ROWS = 0, QUANT_COLS = 1, QUANT_BLOCK = 2 };
+
+struct QuantArgs {
+  const __nv_bfloat16* x;  // (rows, cols) pitch x_ld
+  int64_t rows;
+  int cols;
+  int64_t x_ld;
+  int pre_silu;            // quantise silu(x) instead of x
+  uint8_t* q_row;          // (rows, cols) pitch q_row_ld, or null
+  int64_t q_row_ld;
+  float* s_row;
+  int64_t s_row_ld;
+  int row_mode;            // QUANT_ROWS or QUANT_BLOCK
+  uint8_t* q_col;          // (cols, rows) pitch q_col_ld, or null
+  int64_t q_col_ld;
+  float* s_col;
+  int64_t s_col_ld;
+  int col_mode;            // QUANT_COLS or QUANT_BLOCK
+};
+
+const char* launch_quant_tile(const QuantArgs& a, cudaStream_t st);
+const char* launch_quant_tensor(const __nv_bfloat16* x, const float* scale, uint8_t* q_row, uint8_t* q_col,
+                                float* amax_out, int64_t rows, int cols, cudaStream_t st);
+
+// ---- reductions and small helpers -------------------------------------------------------------
+const char* launch_colsum(const __nv_bfloat16* x, float* out, int64_t rows, int cols, int64_t ld, cudaStream_t st);
+const char* launch_scale_cols(const __nv_bfloat16* w, const float* colw, __nv_bfloat16* out, int64_t rows, int cols,
+                              cudaStream_t st);
+const char* launch_unscale_cols_bwd(const float* dW2w, const __nv_bfloat16* W2, const float* colw, float* dW2,
+                                    float* dcolw, int rows, int cols, cudaStream_t st);
+
+// ---- loss, memory read, optimiser (loss_optim.cu) ------------------------------------------------
+// Cross-entropy over logits (rows, vocab_padded) bf16; only the first `vocab` columns take part.
+// Writes per-row loss (0 for ignored rows) and overwrites logits with d(mean loss)/d(logits) * grad_scale.
+const char* launch_cross_entropy(__nv_bfloat16* logits, const int64_t* targets, float* row_loss,
+                                 const float* inv_count, int64_t rows, int vocab, int64_t ld, int ignore_index,
+                                 float grad_scale, int write_grad, cudaStream_t st);
+
+const char* launch_mem_read_fwd(const float* q, const float* gamma, const float* e, const float* tags,
+                                const float* vals, const float* alpha, float* w, float* out, int B, int S, int dsig,
+                                int dc, cudaStream_t st);
+const char* launch_mem_read_bwd(const float* d_out, const float* q, const float* gamma, const float* e,
+                                const float* tags, const float* vals, const float* w, const float* alpha, float* d_q,
+                                float* d_gamma, float* d_e, float* d_tags, float* d_vals, float* d_alpha, int B, int S,
+                                int dsig, int dc, cudaStream_t st);
+
+// sums[0] += sum gt^2, sums[1] += sum gi*gt, sums[2] += sum gi^2 over n fp32 elements
+const char* launch_grad_dots(const float* gt, const float* gi, float* sums, int64_t n, cudaStream_t st);
+
+struct AdamWArgs {
+  __nv_bfloat16* p_bf16;   // parameters stored as bf16 (or null)
+  float* p_f32;            // parameters stored as fp32 (or null); exactly one of the two is set
+  const float* gt;         // task gradient
+  const float* gi;         // information gradient (may be null: plain AdamW on gt)
+  float* m;
+  float* v;
+  const float* scalars;    // device: [coef, grad_scale] (projection coefficient, 1/world * clip factor)
+  int64_t n;
+  float beta_proj, lr, beta1, beta2, eps, weight_decay;
+  float bc1, bc2;          // bias corrections 1-beta^t
+};
+const char* launch_projected_adamw(const AdamWArgs& a, cudaStream_t st);
+
+// y_i = W_i v_i for a batch of bf16/fp32 matrices given by pointer tables (spectral estimates)
+const char* launch_batched_gemv(const void* const* mats, const float* const* vecs, float* const* outs,
+                                const int* rows, const int* cols, const int* is_bf16, int n_mats, int max_rows,
+                                cudaStream_t st);
+
+}  // namespace gd
