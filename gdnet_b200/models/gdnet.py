@@ -107,7 +107,9 @@ class GDNet(nn.Module):
         return fwd, side, gate_vals
 
     def logits_from(self, fwd: torch.Tensor) -> torch.Tensor:
-        return self.head(self.proj_out(self.norm_out(fwd)))[..., : self.vocab_size]
+        eps = self.norm_out.eps if self.norm_out.eps is not None else float(torch.finfo(fwd.dtype).eps)
+        normed = ops.rmsnorm(fwd, self.norm_out.weight, eps)
+        return self.head(self.proj_out(normed))[..., : self.vocab_size]
 
     # -- public API -------------------------------------------------------------------
 

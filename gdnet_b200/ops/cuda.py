@@ -1,0 +1,855 @@
+"""CUDA (sm_100a) implementations of the GDNet ops and their autograd wiring.
+
+Everything here runs hand-written kernels from ``gdnet_b200/_C.so`` through
+``torch.ops.gdnet_b200``. The module refuses to import without the library. Layout:
+
+* thin wrappers that allocate outputs and call one kernel (``gemm``, ``quantize_*``, ...)
+* autograd Functions: ``causal_dwconv``, ``rmsnorm``, ``fused_mem_read``, ``cross_entropy``,
+  ``bf16_linear``, ``fp8_linear`` and the fused ``layer_step``
+* gradients of weights go to ``param.main_grad`` (fp32, accumulated by the GEMM epilogue)
+  when the training engine has installed it, else they are returned to autograd.
+
+Activations are bf16. Small vectors (biases, norm weights, conv taps) are read as fp32
+copies cached per parameter version.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _ext
+from . import reference as ref
+
+_ext.load()
+
+
+class _CountingOps:
+    """Proxy of ``torch.ops.gdnet_b200`` that counts kernel launches (every op launches exactly one
+    kernel of this library), so benchmarks can report how many of them ran."""
+
+    def __init__(self, ns):
+        self._ns = ns
+        self.launches = 0
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            op = getattr(self._ns, name)
+
+            def fn(*args, _op=op, **kw):
+                self.launches += 1
+                return _op(*args, **kw)
+
+            self._cache[name] = fn
+        return fn
+
+
+K = _CountingOps(torch.ops.gdnet_b200)
+
+
+def launch_count() -> int:
+    return K.launches
+
+AUX_ADD, AUX_MUL_SILU_GRAD, AUX_RMS_SILU_BWD = 1, 2, 3
+ACT_NONE, ACT_SILU = 0, 1
+Q_ROWS, Q_COLS, Q_BLOCK = 0, 1, 2
+BF16, F32, FP8 = torch.bfloat16, torch.float32, torch.float8_e4m3fn
+
+
+# --------------------------------------------------------------------------------------
+# caches keyed on (tensor identity, version): fp32 copies of small vectors and FP8 weights
+# --------------------------------------------------------------------------------------
+_f32_cache: dict[int, tuple] = {}
+_param_epoch = 0
+
+
+def invalidate_param_caches() -> None:
+    """Tell the caches that parameters changed behind autograd's back (the engine's fused
+    optimizer writes the flat buffer, which does not bump the version of the parameter views)."""
+    global _param_epoch
+    _param_epoch += 1
+
+
+def f32(t: torch.Tensor) -> torch.Tensor:
+    """fp32 contiguous copy of a small parameter, refreshed when the parameter changes."""
+    if t.dtype == F32 and t.is_contiguous():
+        return t.detach()
+    key = id(t)
+    hit = _f32_cache.get(key)
+    if hit is not None and hit[0] == (t._version, t.data_ptr(), _param_epoch):
+        return hit[1]
+    out = t.detach().to(F32).contiguous()
+    _f32_cache[key] = ((t._version, t.data_ptr(), _param_epoch), out)
+    return out
+
+
+class QuantizedWeight:
+    """e4m3 copies of a weight ``(N, K)`` with 128x128 block scales: ``q`` / ``s`` for the
+    forward GEMM and ``qt`` / ``st`` (the transposed matrix ``(K, N)``) for the data gradient."""
+
+    __slots__ = ("q", "s", "qt", "st", "version", "ptr")
+
+
+_wq_cache: dict[int, QuantizedWeight] = {}
+
+
+def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
+    key = id(w)
+    hit = _wq_cache.get(key)
+    stamp = (w._version, _param_epoch)
+    if hit is not None and hit.version == stamp and hit.ptr == w.data_ptr():
+        return hit
+    N, Kd = w.shape
+    nb, kb = (N + 127) // 128, (Kd + 127) // 128
+    qw = hit if hit is not None and hit.q.shape == w.shape else QuantizedWeight()
+    if hit is None or hit.q.shape != w.shape:
+        qw.q = torch.empty(N, Kd, dtype=FP8, device=w.device)
+        qw.s = torch.empty(nb, kb, dtype=F32, device=w.device)
+        qw.qt = torch.empty(Kd, N, dtype=FP8, device=w.device)
+        qw.st = torch.empty(kb, nb, dtype=F32, device=w.device)
+    K.quant_tile(w.detach(), False, qw.q, qw.s, Q_BLOCK, qw.qt, qw.st, Q_BLOCK)
+    qw.version, qw.ptr = stamp, w.data_ptr()
+    _wq_cache[key] = qw
+    return qw
+
+
+def clear_caches() -> None:
+    _f32_cache.clear()
+    _wq_cache.clear()
+
+
+# --------------------------------------------------------------------------------------
+# GEMM wrappers
+# --------------------------------------------------------------------------------------
+def gemm_bf16(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=BF16, accumulate=False, bias=None,
+              row_scale=None, ssq_in=None, norm_dim=0, norm_eps=0.0, aux=None, aux_mode=0, rowcoef=None,
+              pre_out=None, act=ACT_NONE, ssq_out=None):
+    """``D = A B^T`` on the tcgen05 tensor cores, bf16 operands, fp32 accumulation.
+
+    ``a`` is ``(M, K)`` (or ``(K, M)`` with ``a_mn``), ``b`` is ``(N, K)`` (or ``(K, N)`` with
+    ``b_mn``). See ``csrc/gemm_sm100.h`` for the epilogue order.
+    """
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    K.gemm_bf16(a, b, a_mn, b_mn, out, accumulate, bias, row_scale, ssq_in, norm_dim, norm_eps, aux, aux_mode,
+                rowcoef, pre_out, act, ssq_out)
+    return out
+
+
+def gemm_fp8(a8, sa, b8, sb, *, out=None, out_dtype=BF16, accumulate=False, bias=None, row_scale=None, aux=None,
+             aux_mode=0, pre_out=None, act=ACT_NONE):
+    """Block-scaled e4m3 GEMM: ``a8 (M,K)`` with ``sa (K/128, M)``, ``b8 (N,K)`` with ``sb (N/128, K/128)``."""
+    M, N = a8.shape[0], b8.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a8.device)
+    K.gemm_fp8(a8, sa, b8, sb, out, accumulate, bias, row_scale, aux, aux_mode, pre_out, act)
+    return out
+
+
+def gemm_ok_bf16(M: int, N: int, Kd: int) -> bool:
+    return Kd % 8 == 0 and N % 32 == 0 and M % 8 == 0
+
+
+def gemm_ok_fp8(M: int, N: int, Kd: int) -> bool:
+    return Kd % 128 == 0 and N % 128 == 0 and M % 16 == 0
+
+
+# --------------------------------------------------------------------------------------
+# quantisers
+# --------------------------------------------------------------------------------------
+def quantize_rows(x, pre_silu=False, q=None, s=None):
+    """1x128 blocks along the last dim: ``(q (M,K) e4m3, s (K/128, M) fp32)``."""
+    M, Kd = x.shape
+    if q is None:
+        q = torch.empty(M, Kd, dtype=FP8, device=x.device)
+    if s is None:
+        s = torch.empty((Kd + 127) // 128, M, dtype=F32, device=x.device)
+    K.quant_tile(x, pre_silu, q, s, Q_ROWS, None, None, Q_BLOCK)
+    return q, s
+
+
+def quantize_transposed(x, mode, pre_silu=False):
+    """``x (M,K)`` -> ``x^T (K,M)`` in e4m3.
+
+    ``mode=Q_COLS``: one scale per output row and 128 input rows, ``s (M/128, K)`` (the A operand
+    of a weight-gradient GEMM). ``mode=Q_BLOCK``: 128x128 blocks, ``s (K/128, M/128)`` (the B operand).
+    """
+    M, Kd = x.shape
+    qt = torch.empty(Kd, M, dtype=FP8, device=x.device)
+    if mode == Q_COLS:
+        st = torch.empty((M + 127) // 128, Kd, dtype=F32, device=x.device)
+    else:
+        st = torch.empty((Kd + 127) // 128, (M + 127) // 128, dtype=F32, device=x.device)
+    K.quant_tile(x, pre_silu, None, None, Q_ROWS, qt, st, mode)
+    return qt, st
+
+
+def quantize_rows_and_transposed(x, col_mode):
+    """Both copies from one read of ``x``: row-quantised ``(q, s)`` and transposed ``(qt, st)``."""
+    M, Kd = x.shape
+    q = torch.empty(M, Kd, dtype=FP8, device=x.device)
+    s = torch.empty((Kd + 127) // 128, M, dtype=F32, device=x.device)
+    qt = torch.empty(Kd, M, dtype=FP8, device=x.device)
+    if col_mode == Q_COLS:
+        st = torch.empty((M + 127) // 128, Kd, dtype=F32, device=x.device)
+    else:
+        st = torch.empty((Kd + 127) // 128, (M + 127) // 128, dtype=F32, device=x.device)
+    K.quant_tile(x, False, q, s, Q_ROWS, qt, st, col_mode)
+    return q, s, qt, st
+
+
+def quantize_fp8_tensor(x, scale, need_col=True, out_row=None, out_col=None, amax_buf=None):
+    """Per-tensor quantisation with a given scale (reference recipe,
+    gdnet/kernel/fp8_linear/quantize.py:59-113): ``(x_row, x_col, amax)``."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1]).contiguous()
+    M, Kd = x2.shape
+    q = out_row if out_row is not None else torch.empty(M, Kd, dtype=FP8, device=x.device)
+    qc = None
+    if need_col:
+        qc = out_col if out_col is not None else torch.empty(Kd, M, dtype=FP8, device=x.device)
+    amax = amax_buf if amax_buf is not None else torch.zeros(1, dtype=F32, device=x.device)
+    K.quant_tensor(x2, scale.reshape(-1).to(F32), q, qc, amax)
+    return q.reshape(shape), (qc if need_col else q), amax.squeeze()
+
+
+# --------------------------------------------------------------------------------------
+# gradient sinks: fp32 main_grad (training engine) or autograd
+# --------------------------------------------------------------------------------------
+def _main_grad(p):
+    return getattr(p, "main_grad", None)
+
+
+def _sink_vec(p, g32):
+    """Deliver the fp32 gradient of a small parameter: add to ``main_grad`` or return it."""
+    mg = _main_grad(p)
+    if mg is not None:
+        mg.add_(g32.view_as(mg))
+        return None
+    return g32.to(p.dtype).view_as(p)
+
+
+def _wgrad_target(p):
+    """(buffer to accumulate into, is_main_grad). Without main_grad a fresh zero fp32 buffer."""
+    mg = _main_grad(p)
+    if mg is not None:
+        return mg, True
+    return torch.zeros(p.shape, dtype=F32, device=p.device), False
+
+
+# --------------------------------------------------------------------------------------
+# causal depthwise conv
+# --------------------------------------------------------------------------------------
+class _CausalDWConvFn(torch.autograd.Function):
+    """x (B,T,d) bf16, w (d,k), halo (B,k-1,d) or None -> (B,T,d). The halo gets a gradient
+    (it is the previous shard's tail), delivered through the halo exchange."""
+
+    @staticmethod
+    def forward(ctx, x, w, halo):
+        xc = x if x.stride(-1) == 1 else x.contiguous()
+        out = torch.empty(x.shape, dtype=BF16, device=x.device)
+        K.dwconv_fwd(xc, halo, f32(w), out)
+        ctx.save_for_backward(xc, w, halo if halo is not None else xc.new_empty(0))
+        ctx.has_halo = halo is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dc):
+        x, w, halo = ctx.saved_tensors
+        halo = halo if ctx.has_halo else None
+        dc = dc if dc.stride(-1) == 1 else dc.contiguous()
+        dx = torch.empty(x.shape, dtype=BF16, device=x.device)
+        dw = torch.zeros(w.shape, dtype=F32, device=x.device)
+        dhalo = torch.empty_like(halo) if halo is not None else None
+        K.dwconv_bwd(dc, x, halo, f32(w), None, dx, dhalo, dw)
+        return dx, _sink_vec(w, dw), dhalo
+
+
+def causal_dwconv(x, w, halo=None):
+    if x.dtype != BF16:
+        return ref.causal_dwconv(x, w, halo)
+    return _CausalDWConvFn.apply(x, w, halo)
+
+
+# --------------------------------------------------------------------------------------
+# RMSNorm
+# --------------------------------------------------------------------------------------
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y = torch.empty_like(x2)
+        rstd = torch.empty(x2.shape[0], dtype=F32, device=x.device)
+        K.rmsnorm_fwd(x2, f32(w), y, rstd, eps)
+        ctx.save_for_backward(x2, w, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(x2.shape).contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.zeros(w.shape, dtype=F32, device=x2.device)
+        K.rmsnorm_bwd(dy2, x2, f32(w), rstd, dx, dw)
+        return dx.view(dy.shape), _sink_vec(w, dw), None
+
+
+def rmsnorm(x, w, eps):
+    if x.dtype != BF16 or x.shape[-1] % 8 != 0:
+        return ref.rmsnorm(x, w, eps)
+    return _RMSNormFn.apply(x, w, float(eps))
+
+
+# --------------------------------------------------------------------------------------
+# fused CAM read
+# --------------------------------------------------------------------------------------
+class _MemReadFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, gamma, e, tags, vals, alpha):
+        args = [t.detach().to(F32).contiguous() for t in (q, gamma, e, tags, vals)]
+        al = alpha.detach().to(F32).reshape(1).contiguous()
+        B, S, _ = args[3].shape
+        w = torch.empty(B, S, dtype=F32, device=q.device)
+        out = torch.empty(B, args[4].shape[2], dtype=F32, device=q.device)
+        K.mem_read_fwd(*args, al, w, out)
+        ctx.save_for_backward(*args, w, al)
+        ctx.dtypes = (q.dtype, gamma.dtype, e.dtype, tags.dtype, vals.dtype, alpha.dtype)
+        ctx.alpha_shape = alpha.shape
+        ctx.mark_non_differentiable(w)
+        return out.to(q.dtype), w
+
+    @staticmethod
+    def backward(ctx, d_out, _dw):
+        q, gamma, e, tags, vals, w, al = ctx.saved_tensors
+        d_q, d_gamma, d_e = torch.empty_like(q), torch.empty_like(gamma), torch.zeros_like(e)
+        d_tags, d_vals = torch.empty_like(tags), torch.empty_like(vals)
+        d_alpha = torch.zeros(1, dtype=F32, device=q.device)
+        K.mem_read_bwd(d_out.to(F32).contiguous(), q, gamma, e, tags, vals, w, al, d_q, d_gamma, d_e, d_tags,
+                       d_vals, d_alpha)
+        dt = ctx.dtypes
+        return (d_q.to(dt[0]), d_gamma.to(dt[1]), d_e.to(dt[2]), d_tags.to(dt[3]), d_vals.to(dt[4]),
+                d_alpha.to(dt[5]).view(ctx.alpha_shape))
+
+
+def fused_mem_read(q, gamma, e, tags, vals, alpha):
+    """``(retrieved (B,d_c) in q.dtype, w (B,S) fp32, no grad)``; one kernel forward, one backward
+    (reference: gdnet/kernel/fused_mem_read/function.py:8-56)."""
+    return _MemReadFn.apply(q, gamma, e, tags, vals, alpha)
+
+
+# --------------------------------------------------------------------------------------
+# cross-entropy (mean over non-ignored rows), gradient written in place of the logits
+# --------------------------------------------------------------------------------------
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, vocab, ignore_index):
+        n, _ = logits.shape
+        tgt = targets.reshape(-1).contiguous()
+        count = (tgt != ignore_index).sum().clamp(min=1).to(F32)
+        inv = (1.0 / count).reshape(1)
+        row_loss = torch.empty(n, dtype=F32, device=logits.device)
+        need_grad = logits.requires_grad
+        # the kernel overwrites the logits with d(mean loss)/d(logits): work on the caller's buffer when it
+        # is a bf16 temporary that nothing else will read, which is the case for the model's head output
+        buf = logits.detach()
+        K.cross_entropy(buf, tgt, row_loss, inv, vocab, ignore_index, 1.0, need_grad)
+        if need_grad:
+            ctx.save_for_backward(buf)
+        return row_loss.sum() * inv[0]
+
+    @staticmethod
+    def backward(ctx, g):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits * g.to(dlogits.dtype), None, None, None
+
+
+def cross_entropy(logits, targets, ignore_index=-100, vocab=None):
+    """Mean cross-entropy over ``logits (n, V)`` bf16. **Consumes** the logits buffer (it is
+    overwritten with the gradient). Columns ``>= vocab`` are excluded from the softmax."""
+    if logits.dtype != BF16 or logits.stride(-1) != 1 or logits.stride(0) % 8 != 0 or logits.dim() != 2:
+        lg = logits.reshape(-1, logits.shape[-1])
+        return ref.cross_entropy(lg if vocab is None else lg[:, :vocab], targets.reshape(-1), ignore_index)
+    return _CrossEntropyFn.apply(logits, targets, logits.shape[1] if vocab is None else vocab, ignore_index)
+
+
+# --------------------------------------------------------------------------------------
+# linears: bf16 and block-scaled FP8, tensor-core GEMMs for fprop, dgrad and wgrad
+# --------------------------------------------------------------------------------------
+def _wgrad_bf16(dy, x, w):
+    """``dW (N,K) += dy^T x``: reduction over tokens, both operands read MN-major in place."""
+    tgt, is_main = _wgrad_target(w)
+    gemm_bf16(dy, x, a_mn=True, b_mn=True, out=tgt, accumulate=True)
+    return None if is_main else tgt.to(w.dtype)
+
+
+def _bias_grad(dy, b):
+    if b is None:
+        return None
+    g = torch.zeros(b.shape, dtype=F32, device=dy.device)
+    K.colsum(dy, g)
+    return _sink_vec(b, g)
+
+
+class _LinearBf16Fn(torch.autograd.Function):
+    """y = x W^T + b with bf16 operands. dgrad reads W MN-major (no transposed copy)."""
+
+    @staticmethod
+    def forward(ctx, x2, w, b):
+        ctx.save_for_backward(x2, w, b if b is not None else x2.new_empty(0))
+        ctx.has_bias = b is not None
+        return gemm_bf16(x2, w, bias=b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, b = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm_bf16(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = _wgrad_bf16(dy, x2, w)
+        db = _bias_grad(dy, b if ctx.has_bias else None)
+        return dx, dw, db
+
+
+def linear_bf16(x, w, b=None):
+    """Tensor-core bf16 linear for any leading shape; weights are expected in bf16."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    M, Kd, N = x2.shape[0], shape[-1], w.shape[0]
+    if x2.dtype != BF16 or w.dtype != BF16 or not gemm_ok_bf16(M, N, Kd) or N % 8 or Kd % 32 or M % 32:
+        return torch.nn.functional.linear(x, w.to(x.dtype), None if b is None else b.to(x.dtype))
+    if x2.stride(-1) != 1 or (x2.stride(0) * 2) % 16:
+        x2 = x2.contiguous()
+    return _LinearBf16Fn.apply(x2, w, b).view(*shape[:-1], N)
+
+
+class _LinearFp8BlockFn(torch.autograd.Function):
+    """Block-scaled e4m3 linear (1x128 activations and gradients, 128x128 weights).
+
+    fprop: x8 (rows) x W8.  dgrad: dy8 (rows) x (W^T)8.  wgrad: (dy^T)8 (per column, 128 tokens)
+    x (x^T)8 (128x128), accumulated in fp32. The transposed e4m3 copy of x is made in forward
+    (one read of x yields both copies) and is what backward keeps instead of x.
+    """
+
+    @staticmethod
+    def forward(ctx, x2, w, b):
+        qw = quantize_weight(w)
+        if ctx.needs_input_grad[1]:
+            x8, sx, xt8, sxt = quantize_rows_and_transposed(x2, Q_BLOCK)
+        else:
+            x8, sx = quantize_rows(x2)
+            xt8 = sxt = x2.new_empty(0)
+        ctx.save_for_backward(xt8, sxt, w, b if b is not None else x2.new_empty(0))
+        ctx.has_bias = b is not None
+        return gemm_fp8(x8, sx, qw.q, qw.s, bias=b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xt8, sxt, w, b = ctx.saved_tensors
+        dy = dy.contiguous()
+        qw = quantize_weight(w)
+        dy8, sdy, dyt8, sdyt = quantize_rows_and_transposed(dy, Q_COLS)
+        dx = gemm_fp8(dy8, sdy, qw.qt, qw.st) if ctx.needs_input_grad[0] else None
+        tgt, is_main = _wgrad_target(w)
+        gemm_fp8(dyt8, sdyt, xt8, sxt, out=tgt, accumulate=True)
+        dw = None if is_main else tgt.to(w.dtype)
+        db = _bias_grad(dy, b if ctx.has_bias else None)
+        return dx, dw, db
+
+
+class _LinearFp8TensorFn(torch.autograd.Function):
+    """Per-tensor delayed scaling (the reference's recipe) on the same block-scaled kernel: the
+    block-scale arrays are filled with the one inverse scale."""
+
+    @staticmethod
+    def forward(ctx, x2, w, b, mod):
+        M, Kd = x2.shape
+        N = w.shape[0]
+        x8, xt8, _ = quantize_fp8_tensor(x2, mod.scale_x, True, amax_buf=mod._amax_x)
+        quantize_fp8_tensor(w.detach(), mod.scale_w, True, out_row=mod._w_fp8_row, out_col=mod._w_fp8_col,
+                            amax_buf=mod._amax_w)
+        sx = mod.inv_scale_x.to(F32).expand((Kd + 127) // 128, M).contiguous()
+        sw = mod.inv_scale_w.to(F32).expand((N + 127) // 128, (Kd + 127) // 128).contiguous()
+        ctx.save_for_backward(xt8, w, b if b is not None else x2.new_empty(0))
+        ctx.mod, ctx.has_bias = mod, b is not None
+        return gemm_fp8(x8, sx, mod._w_fp8_row, sw, bias=b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xt8, w, b = ctx.saved_tensors
+        mod = ctx.mod
+        dy = dy.contiguous()
+        M, N = dy.shape
+        Kd = w.shape[1]
+        scale_g = (ref.FP8_MAX / dy.abs().amax().float().clamp(min=1e-12)).reshape(1)
+        inv_g = scale_g.reciprocal()
+        dy8, dyt8, _ = quantize_fp8_tensor(dy, scale_g, True)
+        kb, nb, mb = (Kd + 127) // 128, (N + 127) // 128, (M + 127) // 128
+        dx = gemm_fp8(dy8, inv_g.expand(nb, M).contiguous(), mod._w_fp8_col,
+                      mod.inv_scale_w.to(F32).expand(kb, nb).contiguous())
+        tgt, is_main = _wgrad_target(w)
+        gemm_fp8(dyt8, inv_g.expand(mb, N).contiguous(), xt8,
+                 mod.inv_scale_x.to(F32).expand(kb, mb).contiguous(), out=tgt, accumulate=True)
+        dw = None if is_main else tgt.to(w.dtype)
+        db = _bias_grad(dy, b if ctx.has_bias else None)
+        return dx, dw, db, None
+
+
+def fp8_linear(x2, mod):
+    """Forward of an :class:`FP8Linear` on a ``(M, K)`` bf16 CUDA tensor."""
+    M, Kd = x2.shape
+    N = mod.out_features
+    if not gemm_ok_fp8(M, N, Kd) or M % 128:
+        return linear_bf16(x2, mod.weight, mod.bias)
+    if x2.stride(-1) != 1 or (x2.stride(0) * 2) % 16:
+        x2 = x2.contiguous()
+    if mod.recipe == "tensor":
+        return _LinearFp8TensorFn.apply(x2, mod.weight, mod.bias, mod)
+    return _LinearFp8BlockFn.apply(x2, mod.weight, mod.bias)
+
+
+# --------------------------------------------------------------------------------------
+# one fused GDLayer step
+# --------------------------------------------------------------------------------------
+_w2w_cache: dict[tuple[int, int], tuple] = {}
+
+
+def _folded_w2(W2, w_norm):
+    """``W2 * w_norm[None, :]`` in bf16, cached per version of both parameters: lets the RMSNorm
+    in front of ``W2`` become a per-row scale in the GEMM epilogue."""
+    key = (id(W2), id(w_norm))
+    hit = _w2w_cache.get(key)
+    stamp = (W2._version, w_norm._version, W2.data_ptr(), _param_epoch)
+    if hit is not None and hit[:3] == stamp[:3] and hit[4] == _param_epoch:
+        return hit[3]
+    out = hit[3] if hit is not None and hit[3].shape == W2.shape else torch.empty_like(W2, dtype=BF16)
+    K.scale_cols(W2.detach(), f32(w_norm), out)
+    _w2w_cache[key] = (W2._version, w_norm._version, W2.data_ptr(), out, _param_epoch)
+    return out
+
+
+class _LayerStepFn(torch.autograd.Function):
+    """conv -> recovery gate R -> forward gate g -> stream update, as one autograd node.
+
+    Inputs: x, s (B,T,d) bf16; halo (B,k-1,d) or None; the 11 parameters of the step.
+    Outputs: fwd', side' (B,T,d) bf16 and the sum of g over all elements (fp32 scalar; its mean
+    is the information-loss term). ``fp8`` selects block-scaled e4m3 GEMMs for the recovery MLP;
+    the gate MLP runs in bf16, as in the reference (gdnet/layer.py:130-139).
+    """
+
+    @staticmethod
+    def forward(ctx, x, s, halo, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1, gnw, gW2, gb2, fp8, eps_r, eps_g,
+                want_gate_sum):
+        B, T, d = x.shape
+        M = B * T
+        dev = x.device
+        train = any(ctx.needs_input_grad)
+        x = x if x.is_contiguous() else x.contiguous()
+        s2 = s.reshape(M, d) if s.stride(-1) == 1 else s.contiguous().reshape(M, d)
+        c3 = torch.empty(B, T, d, dtype=BF16, device=dev)
+        K.dwconv_fwd(x, halo, f32(conv_w), c3)
+        c = c3.view(M, d)
+
+        # recovery MLP: z = W2r silu(W1r [s ; c] + b1r) + b2r
+        h1_pre = torch.empty(M, d, dtype=BF16, device=dev)
+        if fp8:
+            kb = d // 128
+            u8 = torch.empty(M, 2 * d, dtype=FP8, device=dev)
+            su = torch.empty(2 * kb, M, dtype=F32, device=dev)
+            quantize_rows(s2, q=u8[:, :d], s=su[:kb])
+            quantize_rows(c, q=u8[:, d:], s=su[kb:])
+            q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
+            gemm_fp8(u8, su, q1.q, q1.s, out=h1_pre, bias=f32(rb1))
+            a8, sa = quantize_rows(h1_pre, pre_silu=True)
+            z = gemm_fp8(a8, sa, q2.q, q2.s, bias=f32(rb2))
+            a1 = None
+        else:
+            gemm_bf16(s2, rW1[:, :d], out=h1_pre)
+            a1 = torch.empty(M, d, dtype=BF16, device=dev)
+            gemm_bf16(c, rW1[:, d:], out=a1, bias=f32(rb1), aux=h1_pre, aux_mode=AUX_ADD, pre_out=h1_pre,
+                      act=ACT_SILU)
+            z = gemm_bf16(a1, rW2, bias=f32(rb2))
+
+        # gate MLP: g_pre = W2g RMSNorm(silu(W1g c + b1g)) + b2g, the norm folded into W2g and a row scale
+        parts = (d + 127) // 128
+        ssq = torch.empty(M, parts, dtype=F32, device=dev)
+        hg_pre = torch.empty(M, d, dtype=BF16, device=dev) if train else None
+        h = gemm_bf16(c, gW1, bias=f32(gb1), act=ACT_SILU, pre_out=hg_pre, ssq_out=ssq)
+        W2w = _folded_w2(gW2, gnw)
+        g_pre = gemm_bf16(h, W2w, bias=f32(gb2), ssq_in=ssq, norm_dim=d, norm_eps=eps_g)
+
+        fwd_out = torch.empty(B, T, d, dtype=BF16, device=dev)
+        side_out = torch.empty(B, T, d, dtype=BF16, device=dev)
+        rstd_z = torch.empty(M, dtype=F32, device=dev)
+        gate_sum = torch.zeros((), dtype=F32, device=dev)
+        K.gate_update_fwd(g_pre, z, c, s2, f32(rnw), fwd_out.view(M, d), side_out.view(M, d), None, rstd_z,
+                          gate_sum if want_gate_sum else None, eps_r)
+
+        if train:
+            empty = x.new_empty(0)
+            ctx.save_for_backward(x, s2, halo if halo is not None else empty, c, h1_pre, a1 if a1 is not None else empty,
+                                  z, hg_pre, h, ssq, g_pre, rstd_z, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1, gnw,
+                                  gW2, gb2)
+            ctx.cfg = (B, T, d, fp8, eps_g, halo is not None)
+        return fwd_out, side_out, gate_sum
+
+    @staticmethod
+    def backward(ctx, dF, dS, dgsum):
+        (x, s2, halo, c, h1_pre, a1, z, hg_pre, h, ssq, g_pre, rstd_z, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1,
+         gnw, gW2, gb2) = ctx.saved_tensors
+        B, T, d, fp8, eps_g, has_halo = ctx.cfg
+        M = B * T
+        dev = x.device
+        halo = halo if has_halo else None
+
+        def rows(t):
+            t = t.reshape(M, d) if t.stride(-1) == 1 else t.contiguous().reshape(M, d)
+            return t if (t.stride(0) * 2) % 16 == 0 else t.contiguous()
+
+        dF2 = rows(dF) if dF is not None else torch.zeros(M, d, dtype=BF16, device=dev)
+        dS2 = rows(dS) if dS is not None else torch.zeros(M, d, dtype=BF16, device=dev)
+        # d(loss)/d(mean g) = dgsum * (M*d) because gate_sum = (M*d) * mean
+        dgm = None
+        if dgsum is not None:
+            dgm = (dgsum.to(F32) * float(M * d)).reshape(1)
+
+        dq = torch.empty(M, d, dtype=BF16, device=dev)
+        dz = torch.empty(M, d, dtype=BF16, device=dev)
+        dsc = torch.empty(M, 2 * d, dtype=BF16, device=dev)
+        rowcoef = torch.empty(M, dtype=F32, device=dev)
+        db2g = torch.zeros(d, dtype=F32, device=dev)
+        dw_r = torch.zeros(d, dtype=F32, device=dev)
+        db2r = torch.zeros(d, dtype=F32, device=dev)
+        K.gate_update_bwd(dF2, dS2, g_pre, z, c, s2, f32(rnw), f32(gb2), rstd_z, ssq, eps_g, dgm, dq, dz, dsc, rowcoef,
+                          db2g, dw_r, db2r)
+
+        # ---- gate MLP ----
+        W2w = _folded_w2(gW2, gnw)
+        dW2w = gemm_bf16(dq, h, a_mn=True, b_mn=True, out_dtype=F32)
+        tgt2, main2 = _wgrad_target(gW2)
+        dgnw = torch.zeros(d, dtype=F32, device=dev)
+        K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), tgt2, dgnw)
+        dh_pre = gemm_bf16(dq, W2w, b_mn=True, aux=hg_pre, aux_mode=AUX_RMS_SILU_BWD, rowcoef=rowcoef)
+        db1g = torch.zeros(d, dtype=F32, device=dev)
+        K.colsum(dh_pre, db1g)
+        g_gW1 = _wgrad_bf16(dh_pre, c, gW1)
+        dc_view = dsc[:, d:]
+        gemm_bf16(dh_pre, gW1, b_mn=True, out=dc_view, aux=dc_view, aux_mode=AUX_ADD)
+
+        # ---- recovery MLP ----
+        db1r = torch.zeros(d, dtype=F32, device=dev)
+        if fp8:
+            q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
+            dz8, sdz, dzt8, sdzt = quantize_rows_and_transposed(dz, Q_COLS)
+            a1t8, sa1t = quantize_transposed(h1_pre, Q_BLOCK, pre_silu=True)
+            tgt, main_r2 = _wgrad_target(rW2)
+            gemm_fp8(dzt8, sdzt, a1t8, sa1t, out=tgt, accumulate=True)
+            g_rW2 = None if main_r2 else tgt.to(rW2.dtype)
+            dh1 = gemm_fp8(dz8, sdz, q2.qt, q2.st, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
+            K.colsum(dh1, db1r)
+            dh8, sdh, dht8, sdht = quantize_rows_and_transposed(dh1, Q_COLS)
+            kb, mb = d // 128, (M + 127) // 128
+            ut8 = torch.empty(2 * d, M, dtype=FP8, device=dev)
+            sut = torch.empty(2 * kb, mb, dtype=F32, device=dev)
+            K.quant_tile(s2, False, None, None, Q_ROWS, ut8[:d], sut[:kb], Q_BLOCK)
+            K.quant_tile(c, False, None, None, Q_ROWS, ut8[d:], sut[kb:], Q_BLOCK)
+            tgt, main_r1 = _wgrad_target(rW1)
+            gemm_fp8(dht8, sdht, ut8, sut, out=tgt, accumulate=True)
+            g_rW1 = None if main_r1 else tgt.to(rW1.dtype)
+            gemm_fp8(dh8, sdh, q1.qt, q1.st, out=dsc, aux=dsc, aux_mode=AUX_ADD)
+        else:
+            g_rW2 = _wgrad_bf16(dz, a1, rW2)
+            dh1 = gemm_bf16(dz, rW2, b_mn=True, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
+            K.colsum(dh1, db1r)
+            tgt, main_r1 = _wgrad_target(rW1)
+            gemm_bf16(dh1, s2, a_mn=True, b_mn=True, out=tgt[:, :d], accumulate=True)
+            gemm_bf16(dh1, c, a_mn=True, b_mn=True, out=tgt[:, d:], accumulate=True)
+            g_rW1 = None if main_r1 else tgt.to(rW1.dtype)
+            gemm_bf16(dh1, rW1, b_mn=True, out=dsc, aux=dsc, aux_mode=AUX_ADD)
+
+        # ---- conv ----
+        dx = torch.empty(B, T, d, dtype=BF16, device=dev)
+        dwc = torch.zeros(conv_w.shape, dtype=F32, device=dev)
+        dhalo = torch.empty_like(halo) if halo is not None else None
+        K.dwconv_bwd(dsc.view(B, T, 2 * d)[:, :, d:], x, halo, f32(conv_w), None, dx, dhalo, dwc)
+        ds = dsc.view(B, T, 2 * d)[:, :, :d]
+
+        g_gW2 = None if main2 else tgt2.to(gW2.dtype)
+        return (dx, ds, dhalo, _sink_vec(conv_w, dwc), g_rW1, _sink_vec(rb1, db1r), g_rW2, _sink_vec(rb2, db2r),
+                _sink_vec(rnw, dw_r), g_gW1, _sink_vec(gb1, db1g), _sink_vec(gnw, dgnw), g_gW2,
+                _sink_vec(gb2, db2g), None, None, None, None)
+
+
+def _fused_step_ok(fwd, side, layer, r) -> bool:
+    d = fwd.shape[-1]
+    M = fwd.shape[0] * fwd.shape[1]
+    return (fwd.dtype == BF16 and d % 128 == 0 and M % 128 == 0 and getattr(layer, f"{r}_W1").weight.dtype == BF16)
+
+
+def layer_step(fwd, side, layer, conv_name, g, r, sp_group=None, sp_slot=None, return_gate=False):
+    """CUDA implementation of :func:`gdnet_b200.ops.functional.layer_step`."""
+    from .fp8_linear import FP8Linear
+
+    conv = getattr(layer, conv_name)
+    k = conv.size
+    w1r, w2r, nr = getattr(layer, f"{r}_W1"), getattr(layer, f"{r}_W2"), getattr(layer, f"{r}_norm")
+    w1g, w2g, ng = getattr(layer, f"{g}_W1"), getattr(layer, f"{g}_W2"), getattr(layer, f"{g}_norm")
+    halo = None
+    if sp_group is not None and k > 1:
+        from ..parallel.sp import halo_exchange
+
+        halo = halo_exchange(ref.conv_tail(fwd, k).contiguous(), sp_group, sp_slot)
+
+    if return_gate is True or not _fused_step_ok(fwd, side, layer, r):
+        return _composed_step(fwd, side, halo, conv, w1r, w2r, nr, w1g, w2g, ng, return_gate)
+
+    fp8 = isinstance(w1r, FP8Linear) and isinstance(w2r, FP8Linear) and w1r.recipe == "block"
+    eps_r = nr.eps if nr.eps is not None else ref.default_rms_eps(BF16)
+    fo, so, gsum = _LayerStepFn.apply(
+        fwd, side.to(BF16), halo, conv.taps, w1r.weight, w1r.bias, w2r.weight, w2r.bias, nr.weight,
+        w1g.weight, w1g.bias, ng.weight, w2g.weight, w2g.bias, fp8, float(eps_r), ref.GATE_EPS,
+        return_gate == "mean",
+    )
+    if return_gate == "mean":
+        return fo, so, gsum / float(fo.numel())
+    return fo, so
+
+
+def _composed_step(fwd, side, halo, conv, w1r, w2r, nr, w1g, w2g, ng, return_gate):
+    """The same step from single ops (used for shapes the fused node does not cover and when the
+    caller wants the full gate tensor with gradients)."""
+    import torch.nn.functional as F
+
+    from .functional import _module_linear
+
+    c = causal_dwconv(fwd, conv.taps, halo)
+    s = side.to(c.dtype)
+    z = _module_linear(w2r, F.silu(_module_linear(w1r, torch.cat([s, c], dim=-1))))
+    eps_r = nr.eps if nr.eps is not None else ref.default_rms_eps(z.dtype)
+    R = torch.sigmoid(ref.rmsnorm(z, nr.weight, eps_r).float())
+    g_pre = ref.gate_pre(c, w1g.weight, w1g.bias, ng.weight, w2g.weight, w2g.bias)
+    fo, so, gate = ref.gate_stream_update(g_pre, c, s, R)
+    if return_gate == "mean":
+        return fo, so, gate.mean()
+    if return_gate:
+        return fo, so, gate.to(c.dtype)
+    return fo, so
+
+
+# --------------------------------------------------------------------------------------
+# spectral estimates: sigma_i = ||W_i v_i|| for all matrices in one launch
+# --------------------------------------------------------------------------------------
+def _ptr_table(tensors, device):
+    return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=device)
+
+
+class _SigmaFn(torch.autograd.Function):
+    """``sigma_i = ||W_i v_i||`` (fp32). Backward: ``dW_i = dsigma_i * (W_i v_i) v_i^T / sigma_i``,
+    a rank-1 update that is skipped for matrices whose ``dsigma`` is zero."""
+
+    @staticmethod
+    def forward(ctx, n, *args):
+        mats, vecs = args[:n], args[n:]
+        dev = mats[0].device
+        ys = [torch.empty(W.shape[0], dtype=F32, device=dev) for W in mats]
+        wd = [W.detach() for W in mats]
+        K.batched_gemv(
+            _ptr_table(wd, dev), _ptr_table(vecs, dev), _ptr_table(ys, dev),
+            torch.tensor([W.shape[0] for W in mats], dtype=torch.int32, device=dev),
+            torch.tensor([W.shape[1] for W in mats], dtype=torch.int32, device=dev),
+            torch.tensor([int(W.dtype == BF16) for W in mats], dtype=torch.int32, device=dev),
+            max(W.shape[0] for W in mats),
+        )
+        sig = torch.stack([y.norm() for y in ys])
+        ctx.n = n
+        ctx.save_for_backward(sig, *ys, *vecs)
+        ctx.mats = mats
+        return sig
+
+    @staticmethod
+    def backward(ctx, dsig):
+        n = ctx.n
+        saved = ctx.saved_tensors
+        sig, ys, vecs = saved[0], saved[1 : 1 + n], saved[1 + n :]
+        coef = dsig / sig.clamp(min=1e-12)
+        grads = []
+        for i, W in enumerate(ctx.mats):
+            mg = _main_grad(W)
+            if mg is not None:
+                mg.addr_(ys[i], vecs[i], alpha=1.0, beta=1.0) if False else mg.add_(torch.outer(ys[i] * coef[i], vecs[i]))
+                grads.append(None)
+            else:
+                grads.append(torch.outer(ys[i] * coef[i], vecs[i]).to(W.dtype))
+        return (None, *grads, *([None] * n))
+
+
+def sigma_estimates(mats, vecs):
+    ok = all(W.is_contiguous() and W.dtype in (BF16, F32) for W in mats)
+    if not ok:
+        return torch.stack([(W.float() @ v).norm() for W, v in zip(mats, vecs)])
+    return _SigmaFn.apply(len(mats), *mats, *[v.contiguous() for v in vecs])
+
+
+# --------------------------------------------------------------------------------------
+# sequence-parallel halo exchange over symmetric memory (push + flag + bounded wait in-kernel)
+# --------------------------------------------------------------------------------------
+HALO_RING = 8          # passes that may be in flight before a slot is reused
+HALO_SLOTS = 512       # exchanges per pass (2 * n_layers * n_cycles must not exceed this)
+_halo_state: dict = {}
+
+
+def _halo_ctx(group, nbytes, device):
+    import torch.distributed as dist
+
+    from ..parallel.symm import get_buffer
+
+    key = id(group)
+    st = _halo_state.get(key)
+    slot_bytes = -(-nbytes // 256) * 256
+    if st is None or st["slot_bytes"] < slot_bytes:
+        total = 2 * HALO_RING * HALO_SLOTS
+        data = get_buffer(("halo_data", slot_bytes), total * slot_bytes, group, device)
+        flags = get_buffer(("halo_flags", slot_bytes), total * 4, group, device)
+        st = {"slot_bytes": slot_bytes, "data": data, "flags": flags, "pass_fwd": {}, "rank": dist.get_rank(group),
+              "world": dist.get_world_size(group)}
+        _halo_state[key] = st
+    return st
+
+
+class _HaloExchangeSymm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tail, group, slot):
+        st = _halo_ctx(group, tail.numel() * tail.element_size(), tail.device)
+        # sequence number of this slot: how many times it has been used, counted identically on all ranks
+        n_use = st["pass_fwd"].get(slot, 0) + 1
+        st["pass_fwd"][slot] = n_use
+        ring = n_use % HALO_RING
+        idx = ring * HALO_SLOTS + slot
+        halo = torch.empty_like(tail)
+        K.halo_push_wait(tail.contiguous(), halo, st["data"].ptr_table, st["flags"].ptr_table,
+                         idx * st["slot_bytes"], idx, st["rank"], st["world"], n_use, False)
+        ctx.group, ctx.slot, ctx.n_use = group, slot, n_use
+        return halo
+
+    @staticmethod
+    def backward(ctx, d_halo):
+        st = _halo_state[id(ctx.group)]
+        # the backward of use n of a slot gets its own sequence number in the second half of the area
+        key = ("b", ctx.slot, ctx.n_use)
+        cnt = st["pass_fwd"].get(key, 0) + 1
+        st["pass_fwd"][key] = cnt
+        # a retained graph runs this backward up to twice per forward use; every run has its own
+        # sequence number and ring position, so a fast rank cannot overwrite an unread message
+        seq = ctx.n_use * 2 + min(cnt, 2) - 1
+        idx = HALO_RING * HALO_SLOTS + (seq % HALO_RING) * HALO_SLOTS + ctx.slot
+        d_tail = torch.empty_like(d_halo)
+        K.halo_push_wait(d_halo.contiguous(), d_tail, st["data"].ptr_table, st["flags"].ptr_table,
+                         idx * st["slot_bytes"], idx, st["rank"], st["world"], seq, True)
+        return d_tail, None, None
+
+
+def halo_exchange(tail, group, slot):
+    if slot is None or slot >= HALO_SLOTS:
+        raise ValueError("halo exchange over symmetric memory needs a slot index below HALO_SLOTS")
+    return _HaloExchangeSymm.apply(tail, group, int(slot))

@@ -1,0 +1,264 @@
+"""B200 training engine: flat buffers, fused projection + AdamW, fused gradient collective.
+
+The engine owns, per parameter dtype (bf16 matrices, fp32 vectors):
+
+* one flat parameter buffer (every ``nn.Parameter`` becomes a view into it),
+* two flat fp32 gradient buffers, ``g_task`` and ``g_info``; during a backward pass each
+  parameter carries ``main_grad`` = its view of the active buffer, and the weight-gradient
+  GEMM epilogues accumulate straight into it (gradients that autograd delivers through
+  ``.grad`` are folded in after the pass),
+* fp32 AdamW moments for the slice of the flat buffer this rank updates.
+
+One step = one forward, two backward passes (task; info + transition), then
+
+* 1 GPU: ``grad_dots`` + ``projected_adamw`` (two kernels per dtype group);
+* N GPUs, ``comm="fused"``: every rank reduces its shard of both gradient buffers by reading
+  the peers' buffers over NVLink, applies projection + AdamW to that shard and writes the new
+  parameters into every rank's parameter buffer, all in one kernel (``csrc/comm.cu``); the
+  buffers live in symmetric memory;
+* N GPUs, ``comm="nccl"``: NCCL all-reduce of the flat gradients, then the 1-GPU update.
+
+The projection coefficient uses the sum over ranks of the *local* dot products, exactly as
+the reference does (gdnet/loss.py:228-235), and the reduced gradient is the mean over ranks
+(gdnet/loss.py:241-251).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import functional as ops
+from ..utils.fp8 import autocast as make_autocast
+from .step import build_cam_buffer, info_losses, unwrap
+
+ALIGN = 128  # elements; keeps every parameter view 256-byte aligned in bf16
+
+
+class _Group:
+    """All parameters of one dtype, flattened."""
+
+    def __init__(self, params, dtype, device, world, rank, symmetric, pg):
+        self.params, self.dtype = params, dtype
+        offs, n = [], 0
+        for p in params:
+            offs.append(n)
+            n += -(-p.numel() // ALIGN) * ALIGN
+        per = -(-n // world)
+        per = -(-per // ALIGN) * ALIGN
+        self.n = per * world            # padded so every rank's shard has the same length
+        self.offsets = offs
+        self.shard = (rank * per, (rank + 1) * per)
+        item = 2 if dtype == torch.bfloat16 else 4
+        if symmetric:
+            from ..parallel.symm import SymmBuffer
+
+            self._sp = SymmBuffer(self.n * item, pg, device)
+            self._sgt = SymmBuffer(self.n * 4, pg, device)
+            self._sgi = SymmBuffer(self.n * 4, pg, device)
+            self.flat = self._sp.view(dtype, self.n)
+            self.g_task = self._sgt.view(torch.float32, self.n)
+            self.g_info = self._sgi.view(torch.float32, self.n)
+        else:
+            self.flat = torch.zeros(self.n, dtype=dtype, device=device)
+            self.g_task = torch.zeros(self.n, dtype=torch.float32, device=device)
+            self.g_info = torch.zeros(self.n, dtype=torch.float32, device=device)
+        with torch.no_grad():
+            for p, o in zip(params, offs):
+                view = self.flat[o : o + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+        m_len = per if symmetric else self.n   # fused mode updates only this rank's shard
+        self.m = torch.zeros(m_len, dtype=torch.float32, device=device)
+        self.v = torch.zeros(m_len, dtype=torch.float32, device=device)
+        self.sums = torch.zeros(8, dtype=torch.float32, device=device)
+
+    def views(self, flat):
+        return [flat[o : o + p.numel()].view(p.shape) for p, o in zip(self.params, self.offsets)]
+
+
+class TrainEngine(nn.Module):
+    """Wraps a GDNet for training on CUDA. ``engine(tokens, ...)`` forwards to the model;
+    ``engine.projected_step(...)`` (or ``gdnet_b200.loss.projected_step(engine, ...)``) runs a step."""
+
+    is_gdnet_engine = True
+
+    def __init__(self, model: nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 1e-2, precision: str = "fp8", process_group=None, sp_group=None,
+                 comm: str = "fused", broadcast: bool = True):
+        super().__init__()
+        self.module = model
+        self.precision = precision
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.sp_group = sp_group
+        self.step_count = 0
+        self.comm_seq = 0
+        dev = next(model.parameters()).device
+        self.device = dev
+        self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(process_group) > 1
+        self.pg = process_group if process_group is not None else (dist.group.WORLD if self.distributed else None)
+        self.world = dist.get_world_size(self.pg) if self.distributed else 1
+        self.rank = dist.get_rank(self.pg) if self.distributed else 0
+        self.comm = comm if self.distributed else "local"
+        if self.comm not in ("fused", "nccl", "local"):
+            raise ValueError(f"unknown comm backend {comm!r}")
+
+        params = [p for p in model.parameters() if p.requires_grad]
+        by_dtype: dict[torch.dtype, list] = {}
+        for p in params:
+            by_dtype.setdefault(p.dtype, []).append(p)
+        for dt in by_dtype:
+            if dt not in (torch.bfloat16, torch.float32):
+                raise TypeError(f"unsupported parameter dtype {dt}")
+        self.groups = [
+            _Group(ps, dt, dev, self.world, self.rank, self.comm == "fused", self.pg) for dt, ps in by_dtype.items()
+        ]
+        self.params = params
+        if self.distributed and broadcast:
+            src = dist.get_global_rank(self.pg, 0)
+            for g in self.groups:
+                dist.broadcast(g.flat, src=src, group=self.pg)
+            for b in model.buffers():
+                dist.broadcast(b, src=src, group=self.pg)
+        if self.comm == "fused":
+            from ..parallel.symm import SymmBuffer
+
+            self._flags = SymmBuffer(4096, self.pg, dev)
+            for g in self.groups:
+                g._sp.barrier()
+        self.scalars = torch.zeros(2, dtype=torch.float32, device=dev)
+
+    # -- nn.Module plumbing -----------------------------------------------------------------
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    def parameters_flat(self):
+        return [g.flat for g in self.groups]
+
+    # -- gradient buffers -------------------------------------------------------------------
+    def _point_main_grad(self, which: str) -> None:
+        for g in self.groups:
+            for p, v in zip(g.params, g.views(g.g_task if which == "task" else g.g_info)):
+                p.main_grad = v
+
+    def _fold_autograd_grads(self) -> None:
+        for p in self.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad)
+                p.grad = None
+
+    # -- the step ---------------------------------------------------------------------------
+    def projected_step(self, tokens, targets, beta: float = 0.1, write_chunks=None, grad_clip: float = 0.0,
+                       accum_steps: int = 1, loss_mask=None):
+        """One optimizer step. Returns the task loss as a 0-dim device tensor (no host sync)."""
+        model = self.module
+        base = unwrap(model)
+        B = tokens.shape[0]
+        if B % accum_steps:
+            raise ValueError(f"batch size {B} not divisible by accum_steps {accum_steps}")
+        mb = B // accum_steps
+        for g in self.groups:
+            g.g_task.zero_()
+            g.g_info.zero_()
+            g.sums.zero_()
+        total = torch.zeros((), dtype=torch.float32, device=tokens.device)
+        dev_type = tokens.device.type
+
+        for i in range(accum_steps):
+            sl = slice(i * mb, (i + 1) * mb)
+            tok_i, tgt_i = tokens[sl], targets[sl]
+            with make_autocast(self.precision, dev_type):
+                tags = vals = None
+                if write_chunks is not None and base.cam_enabled:
+                    tags, vals = build_cam_buffer(model, write_chunks[sl], sp_group=self.sp_group)
+                logits, side, _, _, gate_vals, _, _ = model(tok_i, tags, vals, return_gates="mean",
+                                                            sp_group=self.sp_group)
+                tgt = tgt_i.reshape(-1)
+                if loss_mask is not None:
+                    tgt = torch.where(loss_mask[sl].reshape(-1), tgt, torch.full_like(tgt, -100))
+                loss_task = ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt) / accum_steps
+            self._point_main_grad("task")
+            loss_task.backward(retain_graph=True)
+            self._fold_autograd_grads()
+            with make_autocast(self.precision, dev_type):
+                loss_info = info_losses(base, side, gate_vals, accum_steps)
+            self._point_main_grad("info")
+            loss_info.backward()
+            self._fold_autograd_grads()
+            total += loss_task.detach().float()
+
+        self._update(beta, grad_clip)
+        from ..ops import cuda as cu
+
+        cu.invalidate_param_caches()
+        return total
+
+    def _update(self, beta: float, grad_clip: float) -> None:
+        from ..ops import cuda as cu
+
+        self.step_count += 1
+        K = cu.K
+        # local dot products <gt,gt>, <gi,gt>, <gi,gi> over all groups
+        sums = torch.zeros(4, dtype=torch.float32, device=self.device)
+        for g in self.groups:
+            K.grad_dots(g.g_task, g.g_info, sums)
+        if self.distributed:
+            dist.all_reduce(sums, group=self.pg)
+        coef = sums[1] / sums[0].clamp(min=1e-8)
+        self.scalars[0] = coef
+        self.scalars[1] = 1.0
+        b1, b2 = self.betas
+        common = (beta, self.lr, b1, b2, self.eps, self.weight_decay, self.step_count)
+
+        if self.comm == "nccl":
+            for g in self.groups:
+                dist.all_reduce(g.g_task, group=self.pg)
+                dist.all_reduce(g.g_info, group=self.pg)
+            self.scalars[1] = 1.0 / self.world
+
+        if self.comm in ("local", "nccl"):
+            if grad_clip > 0.0:
+                red = torch.zeros(4, dtype=torch.float32, device=self.device)
+                for g in self.groups:
+                    K.grad_dots(g.g_task, g.g_info, red)
+                self.scalars[1] = self.scalars[1] * self._clip_factor(red * self.scalars[1] ** 2, coef, beta, grad_clip)
+            for g in self.groups:
+                K.projected_adamw(g.flat, g.g_task, g.g_info, g.m, g.v, self.scalars, *common)
+            return
+
+        # fused: reduce-scatter + projection + AdamW + all-gather over peer memory
+        self.comm_seq += 1
+        phases = (0,) if grad_clip <= 0.0 else (1, 2)
+        for phase in phases:
+            if phase == 2:
+                red = torch.zeros(4, dtype=torch.float32, device=self.device)
+                for g in self.groups:
+                    red[:3] += g.sums[:3]
+                dist.all_reduce(red, group=self.pg)
+                self.scalars[1] = self._clip_factor(red, coef, beta, grad_clip)
+            for gi, g in enumerate(self.groups):
+                K.allreduce_adamw(g._sgt.ptr_table, g._sgi.ptr_table, g._sp.ptr_table, self._flags.ptr_table,
+                                  g.m, g.v, self.scalars, g.n, self.rank, self.world,
+                                  self.comm_seq * 8 + gi, phase, g.dtype == torch.bfloat16, *common, g.sums)
+
+    @staticmethod
+    def _clip_factor(red, coef, beta, grad_clip):
+        """min(1, clip/||g||) for g = (1-beta*coef) gt + beta gi, from the three dot products."""
+        kt = 1.0 - beta * coef
+        norm2 = kt * kt * red[0] + 2.0 * kt * beta * red[1] + beta * beta * red[2]
+        return (grad_clip / (norm2.clamp(min=0).sqrt() + 1e-6)).clamp(max=1.0)
+
+    # -- optimizer-like helpers -------------------------------------------------------------
+    def set_lr(self, lr: float) -> None:
+        self.lr = float(lr)
+
+    def state_dict_optim(self) -> dict:
+        return {"step": self.step_count, "lr": self.lr,
+                "m": [g.m.clone() for g in self.groups], "v": [g.v.clone() for g in self.groups]}
+
+    def load_state_dict_optim(self, sd: dict) -> None:
+        self.step_count, self.lr = int(sd["step"]), float(sd["lr"])
+        for g, m, v in zip(self.groups, sd["m"], sd["v"]):
+            g.m.copy_(m)
+            g.v.copy_(v)

@@ -1,0 +1,183 @@
+"""GPU numerics of every sm_100a kernel against the plain-PyTorch fp32 statement of the same op."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from gdnet_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _cu():
+    from gdnet_b200.ops import cuda as cu
+
+    return cu
+
+
+def _close(got, want, atol, rtol, what=""):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = err > tol
+    if bad.any():
+        idx = bad.nonzero()[0].tolist()
+        raise AssertionError(
+            f"{what}: {int(bad.sum())}/{bad.numel()} mismatched, max err {float(err.max()):.4g} "
+            f"(ref max {float(want.abs().max()):.4g}), first bad at {idx}: got {float(got[tuple(idx)]):.5g} "
+            f"want {float(want[tuple(idx)]):.5g}"
+        )
+
+
+def _status_clean(t):
+    from gdnet_b200 import _ext
+
+    _ext.check_status(t)
+
+
+# ---------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 256, 128), (384, 512, 192), (1000, 128, 256), (4096, 1024, 1024)])
+def test_gemm_bf16_kmajor(M, N, K):
+    cu = _cu()
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    out = cu.gemm_bf16(a, b)
+    torch.cuda.synchronize()
+    _status_clean(a)
+    _close(out, a.float() @ b.float().t(), atol=0.05 * K ** 0.5, rtol=2e-2, what=f"bf16 gemm {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (1024, 1024, 4096)])
+def test_gemm_bf16_mn_major(a_mn, b_mn, M, N, K):
+    cu = _cu()
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    out = cu.gemm_bf16(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    _status_clean(a)
+    _close(out, a.float() @ b.float().t(), atol=0.05 * K ** 0.5, rtol=2e-2, what=f"mn gemm a_mn={a_mn} b_mn={b_mn}")
+
+
+def test_gemm_bf16_epilogues():
+    cu = _cu()
+    M, N, K = 512, 512, 256
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16) * 0.5
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device=DEV)
+    base = a.float() @ b.float().t()
+
+    # bias + silu + pre-activation copy + per-row partial sums of squares
+    pre = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ssq = torch.zeros(M, N // 128, device=DEV)
+    out = cu.gemm_bf16(a, b, bias=bias, act=cu.ACT_SILU, pre_out=pre, ssq_out=ssq)
+    want_pre = base + bias
+    _close(pre, want_pre, 2e-2, 2e-2, "pre_out")
+    _close(out, F.silu(want_pre), 2e-2, 2e-2, "silu out")
+    _close(ssq.sum(1), out.float().pow(2).sum(1), 1e-2, 1e-2, "ssq partials")
+
+    # row scale from ssq partials: rstd * acc + bias
+    out2 = cu.gemm_bf16(a, b, bias=bias, ssq_in=ssq, norm_dim=N, norm_eps=1e-6)
+    rstd = torch.rsqrt(ssq.sum(1) / N + 1e-6)
+    _close(out2, base * rstd[:, None] + bias, 2e-2, 2e-2, "row scale from ssq")
+
+    # explicit row scale, bf16 bias
+    rs = torch.rand(M, device=DEV) + 0.5
+    out3 = cu.gemm_bf16(a, b, bias=bias.bfloat16(), row_scale=rs)
+    _close(out3, base * rs[:, None] + bias.bfloat16().float(), 2e-2, 2e-2, "row scale")
+
+    # aux modes
+    aux = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    _close(cu.gemm_bf16(a, b, aux=aux, aux_mode=cu.AUX_ADD), base + aux.float(), 2e-2, 2e-2, "aux add")
+    sg = torch.sigmoid(aux.float())
+    dsilu = sg * (1 + aux.float() * (1 - sg))
+    _close(cu.gemm_bf16(a, b, aux=aux, aux_mode=cu.AUX_MUL_SILU_GRAD), base * dsilu, 2e-2, 2e-2, "aux silu grad")
+    rc = torch.randn(M, device=DEV) * 0.1
+    want = (base - F.silu(aux.float()) * rc[:, None]) * dsilu
+    _close(cu.gemm_bf16(a, b, aux=aux, aux_mode=cu.AUX_RMS_SILU_BWD, rowcoef=rc), want, 2e-2, 2e-2, "aux rms bwd")
+
+    # fp32 output with accumulation, strided output view
+    acc = torch.ones(M, 2 * N, device=DEV)
+    cu.gemm_bf16(a, b, out=acc[:, N:], accumulate=True)
+    _close(acc[:, N:], base + 1.0, 1e-2, 1e-2, "fp32 accumulate")
+    assert torch.all(acc[:, :N] == 1.0)
+    torch.cuda.synchronize()
+    _status_clean(a)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (4096, 1024, 2048), (1000, 256, 256)])
+def test_gemm_fp8_blockscaled(M, N, K):
+    cu = _cu()
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.2
+    a8, sa = ref.quantize_1x128(a.float())
+    b8, sb = ref.quantize_128x128(b.float())
+    want = ref.fp8_gemm_blockscaled(a8, sa, b8, sb, out_dtype=torch.float32)
+    out = cu.gemm_fp8(a8, sa.t().contiguous(), b8, sb.contiguous(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    _status_clean(a)
+    _close(out, want, 1e-2, 1e-3, f"fp8 gemm {M}x{N}x{K}")
+    bias = torch.randn(N, device=DEV)
+    out2 = cu.gemm_fp8(a8, sa.t().contiguous(), b8, sb.contiguous(), bias=bias, act=cu.ACT_SILU)
+    _close(out2, F.silu(want + bias), 3e-2, 2e-2, "fp8 gemm bias+silu")
+
+
+# ---------------------------------------------------------------------------------------
+# quantisers
+# ---------------------------------------------------------------------------------------
+def test_quantize_rows_matches_reference():
+    cu = _cu()
+    x = (torch.randn(384, 512, device=DEV) * 3).bfloat16()
+    q, s = cu.quantize_rows(x)
+    q_ref, s_ref = ref.quantize_1x128(x.float())
+    _close(s.t(), s_ref, 0, 1e-5, "row scales")
+    deq, deq_ref = ref.dequantize_1x128(q, s.t()), ref.dequantize_1x128(q_ref, s_ref)
+    assert (deq - deq_ref).abs().max() <= 0.07 * x.float().abs().max()
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    # silu fused in front of the quantiser
+    q2, s2 = cu.quantize_rows(x, pre_silu=True)
+    want = F.silu(x.float()).bfloat16().float()
+    _close(ref.dequantize_1x128(q2, s2.t()), want, 0.02, 0.07, "silu + quant")
+
+
+def test_quantize_transposed_modes():
+    cu = _cu()
+    x = (torch.randn(256, 384, device=DEV) * 2).bfloat16()
+    xt = x.float().t().contiguous()
+    qt, st = cu.quantize_transposed(x, cu.Q_BLOCK)
+    q_ref, s_ref = ref.quantize_128x128(xt)
+    _close(st, s_ref, 0, 1e-5, "block scales (transposed)")
+    _close(ref.dequantize_128x128(qt, st), xt, 0.02, 0.07, "block transposed dequant")
+    qc, sc = cu.quantize_transposed(x, cu.Q_COLS)
+    qr, sr = ref.quantize_1x128(xt)            # rows of x^T in blocks of 128 original rows
+    _close(sc.t(), sr, 0, 1e-5, "col scales")
+    _close(ref.dequantize_1x128(qc, sc.t()), xt, 0.02, 0.07, "cols transposed dequant")
+    q, s, qt2, st2 = cu.quantize_rows_and_transposed(x, cu.Q_COLS)
+    assert torch.equal(qt2.view(torch.uint8), qc.view(torch.uint8)) and torch.equal(st2, sc)
+    _close(ref.dequantize_1x128(q, s.t()), x.float(), 0.02, 0.07, "rows in combined call")
+
+
+def test_quantize_weight_both_layouts():
+    cu = _cu()
+    w = torch.randn(256, 512, device=DEV).bfloat16()
+    qw = cu.quantize_weight(w)
+    _close(ref.dequantize_128x128(qw.q, qw.s), w.float(), 0.02, 0.07, "weight")
+    _close(ref.dequantize_128x128(qw.qt, qw.st), w.float().t(), 0.02, 0.07, "weight^T")
+    assert cu.quantize_weight(w) is qw
+
+
+def test_quantize_per_tensor():
+    cu = _cu()
+    x = torch.randn(70, 130, device=DEV).bfloat16()
+    scale = torch.tensor([448.0 / 4.0], device=DEV)
+    q, qc, amax = cu.quantize_fp8_tensor(x, scale)
+    want = (x.float() * scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert (q.view(torch.uint8) != want.view(torch.uint8)).float().mean() < 1e-3
+    assert torch.equal(qc.view(torch.uint8), q.view(torch.uint8).t())
+    assert torch.allclose(amax, x.float().abs().max())

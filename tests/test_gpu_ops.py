@@ -1,0 +1,274 @@
+"""GPU numerics of the autograd-level ops (conv, norms, gate update, CAM read, loss, linears, the
+fused layer step) against autograd through the plain-PyTorch fp32 statement."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from gdnet_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def _cu():
+    from gdnet_b200.ops import cuda as cu
+
+    return cu
+
+
+def _rel(got, want):
+    got, want = got.float(), want.float()
+    return float((got - want).norm() / want.norm().clamp(min=1e-12))
+
+
+def _check(got, want, tol, what):
+    r = _rel(got, want)
+    assert r < tol, f"{what}: relative error {r:.4g} (tol {tol}); max abs {float((got.float()-want.float()).abs().max()):.4g}"
+
+
+@pytest.mark.parametrize("B,T,d,k", [(2, 64, 128, 4), (2, 300, 256, 7), (1, 129, 64, 9), (3, 40, 32, 1), (1, 5, 8, 4)])
+@pytest.mark.parametrize("use_halo", [False, True])
+def test_causal_dwconv_fwd_bwd(B, T, d, k, use_halo):
+    cu = _cu()
+    if k == 1 and use_halo:
+        pytest.skip("no halo for k=1")
+    x = torch.randn(B, T, d, device=DEV, dtype=BF, requires_grad=True)
+    w = torch.randn(d, k, device=DEV, requires_grad=True)
+    halo = torch.randn(B, k - 1, d, device=DEV, dtype=BF, requires_grad=True) if use_halo else None
+    out = cu.causal_dwconv(x, w, halo)
+    gy = torch.randn_like(out)
+    out.backward(gy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().clone().requires_grad_()
+    hr = halo.detach().float().requires_grad_() if use_halo else None
+    want = ref.causal_dwconv(xr, wr, hr)
+    want.backward(gy.float())
+    _check(out, want, 1e-2, "conv out")
+    _check(x.grad, xr.grad, 1e-2, "conv dx")
+    _check(w.grad, wr.grad, 2e-2, "conv dw")
+    if use_halo:
+        _check(halo.grad, hr.grad, 1e-2, "conv dhalo")
+
+
+def test_rmsnorm_fwd_bwd():
+    cu = _cu()
+    x = torch.randn(300, 256, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.rand(256, device=DEV) + 0.5).requires_grad_()
+    y = cu.rmsnorm(x, w, 1e-6)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    want = ref.rmsnorm(xr, wr, 1e-6)
+    want.backward(gy.float())
+    _check(y, want, 1e-2, "rmsnorm y")
+    _check(x.grad, xr.grad, 1e-2, "rmsnorm dx")
+    _check(w.grad, wr.grad, 1e-2, "rmsnorm dw")
+
+
+def test_fused_mem_read_fwd_bwd():
+    cu = _cu()
+    B, S, ds, dc = 5, 32, 64, 128
+    mk = lambda *s: torch.randn(*s, device=DEV, requires_grad=True)
+    q, gam, e, tags, vals = mk(B, ds), mk(B, ds), mk(S, ds), mk(B, S, ds), mk(B, S, dc)
+    alpha = torch.tensor([0.7], device=DEV, requires_grad=True)
+    out, w = cu.fused_mem_read(q, gam, e, tags, vals, alpha)
+    assert not w.requires_grad
+    gy = torch.randn_like(out)
+    out.backward(gy)
+    refs = [t.detach().clone().requires_grad_() for t in (q, gam, e, tags, vals, alpha)]
+    out_r, w_r = ref.fused_mem_read(*refs)
+    out_r.backward(gy)
+    _check(out, out_r, 1e-4, "mem_read out")
+    _check(w, w_r, 1e-4, "mem_read w")
+    for name, a, b in zip("q gamma e tags vals alpha".split(), (q, gam, e, tags, vals, alpha), refs):
+        _check(a.grad, b.grad, 1e-3, f"mem_read d{name}")
+
+
+@pytest.mark.parametrize("V,Vp", [(1000, 1000), (250, 256)])
+def test_cross_entropy(V, Vp):
+    cu = _cu()
+    n = 64
+    logits = (torch.randn(n, Vp, device=DEV) * 3).to(BF).requires_grad_()
+    tgt = torch.randint(0, V, (n,), device=DEV)
+    tgt[::7] = -100
+    lr = logits.detach().float()[:, :V].requires_grad_()
+    want = F.cross_entropy(lr, tgt, ignore_index=-100)
+    want.backward()
+    loss = cu.cross_entropy(logits.clone(), tgt, -100, vocab=V)      # clone: the op consumes its input
+    _check(loss, want, 2e-3, "ce loss")
+    x = logits.detach().clone().requires_grad_()
+    y = x * 1.0
+    loss2 = cu.cross_entropy(y, tgt, -100, vocab=V)
+    (2.0 * loss2).backward()
+    _check(x.grad[:, :V], 2.0 * lr.grad, 2e-2, "ce grad")
+    if Vp > V:
+        assert x.grad[:, V:].abs().max() == 0
+
+
+@pytest.mark.parametrize("M,K,N,bias", [(256, 128, 256, True), (512, 384, 128, False)])
+def test_linear_bf16_fwd_bwd(M, K, N, bias):
+    cu = _cu()
+    x = torch.randn(M, K, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(BF).requires_grad_()
+    b = torch.randn(N, device=DEV, dtype=BF, requires_grad=True) if bias else None
+    y = cu.linear_bf16(x, w, b)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    br = b.detach().float().requires_grad_() if bias else None
+    F.linear(xr, wr, br).backward(gy.float())
+    _check(y, F.linear(xr, wr, br), 1e-2, "linear y")
+    _check(x.grad, xr.grad, 1e-2, "linear dx")
+    _check(w.grad, wr.grad, 1e-2, "linear dw")
+    if bias:
+        _check(b.grad, br.grad, 1e-2, "linear db")
+
+
+@pytest.mark.parametrize("recipe", ["block", "tensor"])
+def test_fp8_linear_module_fwd_bwd(recipe):
+    from gdnet_b200.ops.fp8_linear import FP8Linear
+
+    M, K, N = 256, 256, 384
+    lin = torch.nn.Linear(K, N).to(DEV)
+    mod = FP8Linear(lin, recipe=recipe)
+    x = torch.randn(M, K, device=DEV, dtype=BF, requires_grad=True)
+    y = mod(x)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_()
+    wr, br = mod.weight.detach().float().requires_grad_(), mod.bias.detach().float().requires_grad_()
+    F.linear(xr, wr, br).backward(gy.float())
+    tol = 0.08 if recipe == "block" else 0.12
+    _check(y, F.linear(xr, wr, br), tol, "fp8 y")
+    _check(x.grad, xr.grad, tol, "fp8 dx")
+    _check(mod.weight.grad, wr.grad, tol, "fp8 dw")
+    _check(mod.bias.grad, br.grad, 2e-2, "fp8 db")
+    if recipe == "tensor":
+        assert float(mod._amax_x) > 0 and float(mod._amax_w) > 0
+
+
+def _make_layer(d, k, fp8):
+    from gdnet_b200.layer import GDLayer
+    from gdnet_b200.utils.fp8 import convert_to_fp8
+
+    torch.manual_seed(0)
+    layer = GDLayer(d, k)
+    with torch.no_grad():   # make both gates and the recovery path matter
+        for p in ("gf", "gb", "rf", "rb"):
+            getattr(layer, f"{p}_W2").weight.mul_(30.0)
+            getattr(layer, f"{p}_norm").weight.add_(torch.randn(d) * 0.2)
+    layer = layer.to(DEV)
+    if fp8:
+        convert_to_fp8(layer)
+    else:
+        layer.to(BF)
+    return layer
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("step", ["fwd", "bwd"])
+def test_layer_step_matches_reference(fp8, step):
+    """Fused CUDA step (values and every gradient) against the fp32 composition on the same weights."""
+    from gdnet_b200.models.layer import _STEP_PREFIXES
+
+    B, T, d, k = 2, 128, 256, 4
+    layer = _make_layer(d, k, fp8)
+    x = torch.randn(B, T, d, device=DEV, dtype=BF, requires_grad=True)
+    s = torch.randn(B, T, d, device=DEV, dtype=BF, requires_grad=True)
+    fo, so, gm = layer._step(step, x, s, return_gate="mean")
+    gF, gS = torch.randn_like(fo), torch.randn_like(so)
+    (fo.float() * gF).sum().add((so.float() * gS).sum()).add(3.0 * gm).backward()
+
+    conv, g, r = _STEP_PREFIXES[step]
+    P = lambda n: getattr(layer, n)
+    xr, sr = x.detach().float().requires_grad_(), s.detach().float().requires_grad_()
+    prm = {}
+    for name in (f"{r}_W1", f"{r}_W2", f"{g}_W1", f"{g}_W2"):
+        prm[name + ".w"] = P(name).weight.detach().float().requires_grad_()
+        prm[name + ".b"] = P(name).bias.detach().float().requires_grad_()
+    prm["rn"] = P(f"{r}_norm").weight.detach().float().requires_grad_()
+    prm["gn"] = P(f"{g}_norm").weight.detach().float().requires_grad_()
+    prm["cw"] = P(conv).taps.detach().float().requires_grad_()
+    fo_r, so_r, g_r, _ = ref.layer_step(
+        xr, sr, prm["cw"], prm[f"{r}_W1.w"], prm[f"{r}_W1.b"], prm[f"{r}_W2.w"], prm[f"{r}_W2.b"], prm["rn"],
+        prm[f"{g}_W1.w"], prm[f"{g}_W1.b"], prm["gn"], prm[f"{g}_W2.w"], prm[f"{g}_W2.b"],
+        r_eps=ref.default_rms_eps(BF))
+    (fo_r * gF.float()).sum().add((so_r * gS.float()).sum()).add(3.0 * g_r.mean()).backward()
+
+    tol = 0.12 if fp8 else 0.03
+    _check(fo, fo_r, tol, "fwd'")
+    _check(so, so_r, tol, "side'")
+    _check(gm, g_r.mean(), 1e-2, "gate mean")
+    _check(x.grad, xr.grad, tol * 2, "dx")
+    _check(s.grad, sr.grad, tol * 2, "ds")
+    pairs = [(P(conv).conv.weight.grad.squeeze(1), prm["cw"].grad, "dconv_w"),
+             (P(f"{r}_norm").weight.grad, prm["rn"].grad, "drnorm"),
+             (P(f"{g}_norm").weight.grad, prm["gn"].grad, "dgnorm")]
+    for name in (f"{r}_W1", f"{r}_W2", f"{g}_W1", f"{g}_W2"):
+        pairs.append((P(name).weight.grad, prm[name + ".w"].grad, f"d{name}.weight"))
+        pairs.append((P(name).bias.grad, prm[name + ".b"].grad, f"d{name}.bias"))
+    for got, want, what in pairs:
+        assert got is not None, what
+        _check(got, want, tol * 2.5, what)
+    # parameters of the other step stay untouched
+    other = "bwd" if step == "fwd" else "fwd"
+    assert getattr(layer, _STEP_PREFIXES[other][0]).conv.weight.grad is None
+
+
+def test_layer_step_main_grad_accumulates():
+    B, T, d, k = 1, 128, 128, 4
+    layer = _make_layer(d, k, True)
+    for p in layer.parameters():
+        p.main_grad = torch.zeros(p.shape, dtype=torch.float32, device=DEV)
+    x = torch.randn(B, T, d, device=DEV, dtype=BF, requires_grad=True)
+    s = torch.randn(B, T, d, device=DEV, dtype=BF, requires_grad=True)
+    for _ in range(2):
+        fo, so = layer.fwd_step(x, s)
+        (fo.float().sum() + so.float().pow(2).sum()).backward()
+    g2 = layer.rf_W1.weight.main_grad.clone()
+    assert layer.rf_W1.weight.grad is None and g2.abs().sum() > 0
+    for p in layer.parameters():
+        p.main_grad.zero_()
+    fo, so = layer.fwd_step(x, s)
+    (fo.float().sum() + so.float().pow(2).sum()).backward()
+    _check(g2, 2 * layer.rf_W1.weight.main_grad, 1e-3, "main_grad accumulates over two backward passes")
+
+
+def test_sigma_estimates_fwd_bwd():
+    cu = _cu()
+    mats = [torch.randn(64, 128, device=DEV).to(BF).requires_grad_(), torch.randn(32, 32, device=DEV).requires_grad_()]
+    vecs = [F.normalize(torch.randn(m.shape[1], device=DEV), dim=0) for m in mats]
+    sig = cu.sigma_estimates(mats, vecs)
+    (sig * torch.tensor([1.0, -2.0], device=DEV)).sum().backward()
+    refs = [m.detach().float().requires_grad_() for m in mats]
+    want = torch.stack([(W @ v).norm() for W, v in zip(refs, vecs)])
+    (want * torch.tensor([1.0, -2.0], device=DEV)).sum().backward()
+    _check(sig, want, 1e-3, "sigma")
+    for a, b in zip(mats, refs):
+        _check(a.grad, b.grad, 1e-2, "dsigma/dW")
+
+
+def test_optimizer_kernels():
+    cu = _cu()
+    n = 10_000
+    gt, gi = torch.randn(n, device=DEV), torch.randn(n, device=DEV)
+    sums = torch.zeros(4, device=DEV)
+    cu.K.grad_dots(gt, gi, sums)
+    assert torch.allclose(sums[:3], torch.stack([(gt * gt).sum(), (gt * gi).sum(), (gi * gi).sum()]), rtol=1e-4)
+    for dtype in (torch.bfloat16, torch.float32):
+        p = torch.randn(n, device=DEV).to(dtype)
+        p_ref = p.float().clone()
+        m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        m_r, v_r = m.clone(), v.clone()
+        coef = float(sums[1] / sums[0])
+        scal = torch.tensor([coef, 0.5], device=DEV)
+        for step in (1, 2):
+            cu.K.projected_adamw(p, gt, gi, m, v, scal, 0.1, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+            ref.projected_adamw_(p_ref, gt, gi, m_r, v_r, coef=coef, beta_proj=0.1, grad_scale=0.5, lr=1e-2,
+                                 beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+            if dtype == torch.bfloat16:
+                p_ref = p_ref.to(dtype).float()
+        assert torch.allclose(p.float(), p_ref, atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+        assert torch.allclose(m, m_r, atol=1e-6) and torch.allclose(v, v_r, atol=1e-6)
