@@ -79,6 +79,7 @@ void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT
   TORCH_CHECK((reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0 && (e.out_ld * out.element_size()) % 16 == 0,
               "out rows must be 16-byte aligned");
   e.accumulate = accumulate;
+  e.atomic = 0;
   e.bias = nullptr;
   e.bias_f32 = 0;
   if (bias.has_value()) {
@@ -137,7 +138,7 @@ void gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, Tensor ou
   const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
   TORCH_CHECK(K == Kb, "gemm: reduction sizes differ: ", K, " vs ", Kb);
   gd::GemmOperands op{bf16_ptr(a, "a"), bf16_ptr(b, "b"), a.stride(0), b.stride(0)};
-  gd::GemmShape g{(int)M, (int)N, (int)K, a_mn, b_mn, nullptr, nullptr, 0};
+  gd::GemmShape g{(int)M, (int)N, (int)K, a_mn, b_mn, nullptr, nullptr, 0, 1};
   gd::GemmEpilogue e;
   fill_epilogue(e, out, accumulate, bias, row_scale, ssq_in, norm_dim, norm_eps, aux, aux_mode, rowcoef, pre_out, act,
                 ssq_out, M, N);
@@ -156,7 +157,7 @@ void gemm_fp8(const Tensor& a8, const Tensor& sa, const Tensor& b8, const Tensor
   TORCH_CHECK(sa.dim() == 2 && sa.size(0) == KB && sa.size(1) >= M && sa.stride(1) == 1, "sa must be (K/128, M)");
   TORCH_CHECK(sb.dim() == 2 && sb.size(0) == NB && sb.size(1) == KB && sb.is_contiguous(), "sb must be (N/128, K/128)");
   gd::GemmOperands op{fp8_mut(a8, "a8"), fp8_mut(b8, "b8"), a8.stride(0), b8.stride(0)};
-  gd::GemmShape g{(int)M, (int)N, (int)K, 0, 0, f32_ptr(sa, "sa"), f32_ptr(sb, "sb"), sa.stride(0)};
+  gd::GemmShape g{(int)M, (int)N, (int)K, 0, 0, f32_ptr(sa, "sa"), f32_ptr(sb, "sb"), sa.stride(0), 1};
   gd::GemmEpilogue e;
   std::optional<Tensor> none;
   fill_epilogue(e, out, accumulate, bias, row_scale, none, 0, 0.0, aux, aux_mode, none, pre_out, act, none, M, N);

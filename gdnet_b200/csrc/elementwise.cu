@@ -17,7 +17,7 @@ namespace gd {
 // channels, and the 8 warps of a block take 8 consecutive row tiles of TT time steps, so a
 // block covers 8*TT rows x 32*CH channels of one batch row. Taps are padded at the front
 // to KMAX so the sliding window has a compile-time length.
-constexpr int CONV_TT = 32;
+constexpr int CONV_TT = 16;
 
 template <int CH> struct VecOf;
 template <> struct VecOf<8> { using type = uint4; };
@@ -235,8 +235,8 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
 const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   if (a.k < 1 || a.k > 16) return "dwconv: kernel width must be in [1, 16]";
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
-  if (a.k <= 4) return conv_bwd_launch<4, 8>(a, st);
-  if (a.k <= 8) return conv_bwd_launch<8, 4>(a, st);
+  if (a.k <= 4) return conv_bwd_launch<4, 4>(a, st);   // narrower vectors: two windows + dw accumulators per lane
+  if (a.k <= 8) return conv_bwd_launch<8, 2>(a, st);
   return conv_bwd_launch<16, 2>(a, st);
 }
 
@@ -321,11 +321,12 @@ const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st) {
 // rowcoef[row] = rstd_g^2 / d * T_row.
 __global__ void __launch_bounds__(256)
 gate_update_bwd_kernel(const GateBwdArgs a) {
-  extern __shared__ float colacc[];  // [3][d]: db2g, dw_r, db2r
+  extern __shared__ float colacc_all[];  // [warps][3][d]: db2g, dw_r, db2r; each warp owns a slab, no atomics
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int wpb = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) colacc[i] = 0.0f;
-  __syncthreads();
+  float* colacc = colacc_all + (size_t)warp * 3 * a.d;
+  for (int i = lane; i < 3 * a.d; i += 32) colacc[i] = 0.0f;
+  __syncwarp();
   const float dgm = (a.dgate_mean != nullptr) ? a.dgate_mean[0] / ((float)a.rows * (float)a.d) : 0.0f;
 
   for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < a.rows; row += (int64_t)gridDim.x * wpb) {
@@ -388,9 +389,9 @@ gate_update_bwd_kernel(const GateBwdArgs a) {
         dz[i] = dzv;
         dcd[i] = dF[i] * g + dS[i] * (1.0f - g);
         dsd[i] = dF[i] * R + dS[i] * (1.0f - R);
-        atomicAdd(&colacc[col + i], dgp);
-        atomicAdd(&colacc[a.d + col + i], dy * zh);
-        atomicAdd(&colacc[2 * a.d + col + i], dzv);
+        colacc[col + i] += dgp;                 // this lane is the only writer of these columns
+        colacc[a.d + col + i] += dy * zh;
+        colacc[2 * a.d + col + i] += dzv;
       }
       st8(a.dq + row * a.d + col, dq);
       st8(a.dz + row * a.d + col, dz);
@@ -399,25 +400,28 @@ gate_update_bwd_kernel(const GateBwdArgs a) {
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < a.d; i += blockDim.x) {
-    atomicAdd(a.db2g + i, colacc[i]);
-    atomicAdd(a.dw_r + i, colacc[a.d + i]);
-    atomicAdd(a.db2r + i, colacc[2 * a.d + i]);
+  for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) {
+    float t = 0.0f;
+    for (int w = 0; w < wpb; ++w) t += colacc_all[(size_t)w * 3 * a.d + i];
+    float* dst = i < a.d ? a.db2g + i : (i < 2 * a.d ? a.dw_r + (i - a.d) : a.db2r + (i - 2 * a.d));
+    atomicAdd(dst, t);
   }
 }
 
 const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update_bwd: d must be a multiple of 8";
-  const size_t smem = 3 * (size_t)a.d * sizeof(float);
-  if (smem > 96 * 1024) return "gate_update_bwd: d too large for the column accumulators";
+  int warps = 8;
+  while (warps > 1 && (size_t)warps * 3 * a.d * sizeof(float) > 100 * 1024) warps >>= 1;
+  const size_t smem = (size_t)warps * 3 * a.d * sizeof(float);
+  if (smem > 200 * 1024) return "gate_update_bwd: d too large for the column accumulators";
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(gate_update_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaFuncSetAttribute(gate_update_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr = true;
   }
-  const int64_t blocks = (a.rows + 7) / 8;
-  const int grid = (int)(blocks < 148 * 4 ? blocks : 148 * 4);
-  gate_update_bwd_kernel<<<grid, 256, smem, st>>>(a);
+  const int64_t blocks = (a.rows + warps - 1) / warps;
+  const int grid = (int)(blocks < 148 * 2 ? blocks : 148 * 2);
+  gate_update_bwd_kernel<<<grid, warps * 32, smem, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gate_update_bwd launch failed";
 }
 
@@ -524,7 +528,7 @@ quant_tile_kernel(const QuantArgs a) {
   __shared__ float s_colmax[16][128];
   __shared__ float s_scale_col[128];
   __shared__ float s_tilemax;
-  __shared__ __align__(16) uint8_t s_t[128][128 + 16];
+  __shared__ __align__(16) __nv_bfloat16 s_tile[128][128 + 8];
 
   const int tid = threadIdx.x;
   const int tr = tid >> 4;          // 0..15: row within a pass
@@ -610,25 +614,26 @@ quant_tile_kernel(const QuantArgs a) {
   }
 
   if (a.q_col != nullptr) {
-    float inv[8];
+    // stage the tile row-major as bf16 (16-byte stores, conflict free), then every thread walks half
+    // of one column: 64 values -> 64 output bytes of one transposed row
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float cm = s_scale_col[tc + i];
-      const float sc = a.col_mode == QUANT_COLS ? (cm > 0.0f ? cm / 448.0f : 1.0f) : tile_scale;
-      inv[i] = 1.0f / sc;
-    }
-#pragma unroll
-    for (int p = 0; p < 8; ++p)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s_t[tc + i][p * 16 + tr] = to_e4m3(v[p][i] * inv[i]);
+    for (int p = 0; p < 8; ++p) store_bf16_vec<8>(&s_tile[p * 16 + tr][tc], v[p]);
     __syncthreads();
-    // write 128 output rows (= input columns) of 128 bytes each; 8 threads x 16 B per row
-    for (int idx = tid; idx < 128 * 8; idx += 256) {
-      const int oc = idx >> 3, seg = (idx & 7) * 16;
-      const int c = c0 + oc;
-      const int64_t r = r0 + seg;
-      if (c < a.cols && r < a.rows)
-        *reinterpret_cast<uint4*>(a.q_col + (int64_t)c * a.q_col_ld + r) = *reinterpret_cast<const uint4*>(&s_t[oc][seg]);
+    const int oc = tid >> 1, half = tid & 1;
+    const float cm = s_scale_col[oc];
+    const float sc = a.col_mode == QUANT_COLS ? (cm > 0.0f ? cm / 448.0f : 1.0f) : tile_scale;
+    const float inv = 1.0f / sc;
+    const int c = c0 + oc;
+    const int64_t rbase = r0 + half * 64;
+    if (c < a.cols) {
+#pragma unroll
+      for (int seg = 0; seg < 4; ++seg) {
+        uint8_t q[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q[i] = to_e4m3(__bfloat162float(s_tile[half * 64 + seg * 16 + i][oc]) * inv);
+        if (rbase + seg * 16 < a.rows)
+          *reinterpret_cast<uint4*>(a.q_col + (int64_t)c * a.q_col_ld + rbase + seg * 16) = *reinterpret_cast<uint4*>(q);
+      }
     }
     if (a.col_mode == QUANT_COLS) {
       if (tid < 128 && c0 + tid < a.cols) {
@@ -641,8 +646,43 @@ quant_tile_kernel(const QuantArgs a) {
   }
 }
 
+// Row-only quantiser (1x128 blocks): 16 lanes own one block of one row (8 values each), the block
+// amax is a 4-step shuffle; no shared memory, every byte moved once with 16-byte loads.
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const QuantArgs a) {
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int groups_per_row = a.cols / 8;            // cols is a multiple of 128 here
+  const int c = (int)(gid % groups_per_row) * 8;
+  const bool live = gid / groups_per_row < a.rows;   // dead lanes stay for the shuffles, store nothing
+  const int64_t r = live ? gid / groups_per_row : a.rows - 1;
+  float v[8];
+  load_bf16_vec<8>(a.x + r * a.x_ld + c, v);
+  if (a.pre_silu) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(__float2bfloat16(siluf_(v[i])));
+  }
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float sc = m > 0.0f ? m / 448.0f : 1.0f;
+  const float inv = 1.0f / sc;
+  uint8_t q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[i] * inv);
+  if (!live) return;
+  *reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c) = *reinterpret_cast<uint2*>(q);
+  if ((threadIdx.x & 15) == 0) a.s_row[(int64_t)(c >> 7) * a.s_row_ld + r] = sc;
+}
+
 const char* launch_quant_tile(const QuantArgs& a, cudaStream_t st) {
   if (a.cols % 8 != 0) return "quantise: cols must be a multiple of 8";
+  if (a.q_col == nullptr && a.q_row != nullptr && a.row_mode == QUANT_ROWS && a.cols % 128 == 0) {
+    const int64_t threads = a.rows * (a.cols / 8);
+    quant_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "quant_rows launch failed";
+  }
   if (a.q_col != nullptr && a.rows % 16 != 0) return "quantise: transposed output needs rows % 16 == 0";
   dim3 grid((a.cols + 127) / 128, (unsigned)((a.rows + 127) / 128));
   quant_tile_kernel<<<grid, 256, 0, st>>>(a);

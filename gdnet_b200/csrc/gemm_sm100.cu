@@ -50,6 +50,20 @@ __device__ __forceinline__ void raise_abort(PipeBars* b, Status* st, int code, i
   *((volatile int*)&b->abort) = 1;
 }
 
+// Tile order: bands of RASTER_M row-blocks; inside a band consecutive tiles walk down the rows of one
+// column block first, so CTAs that run at the same time share a handful of A and B tiles in L2
+// (row-major order would stream the whole B matrix once per row block when N is large).
+constexpr int RASTER_M = 8;
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
+  const int band_tiles = RASTER_M * tiles_n;
+  const int band = tile / band_tiles;
+  const int in_band = tile - band * band_tiles;
+  const int rows_here = min(RASTER_M, tiles_m - band * RASTER_M);
+  nb = in_band / rows_here;
+  mb = band * RASTER_M + (in_band - nb * rows_here);
+}
+
 // ---------------------------------------------------------------------------------------
 // fused epilogue on one row x 32 columns held in registers
 // ---------------------------------------------------------------------------------------
@@ -120,6 +134,11 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      if (e.atomic) {   // split-K: several CTAs add their share of the reduction into the same tile
+        float* of = reinterpret_cast<float*>(op + q);
+        atomicAdd(of, o.x); atomicAdd(of + 1, o.y); atomicAdd(of + 2, o.z); atomicAdd(of + 3, o.w);
+        continue;
+      }
       if (e.accumulate) {
         const float4 old = op[q];
         o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
@@ -221,16 +240,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t tmem_base = bars->tmem_base;
 
   const int n_tiles_n = (g.N + BF16_BN - 1) / BF16_BN;
-  const int n_tiles = ((g.M + BM - 1) / BM) * n_tiles_n;
+  const int n_tiles_m = (g.M + BM - 1) / BM;
+  const int n_tiles = n_tiles_m * n_tiles_n;
   const int kblocks = (g.K + BF16_BK - 1) / BF16_BK;
+  const int kb_per = (kblocks + g.splits - 1) / g.splits;   // K blocks per split-K share
+  const int n_work = n_tiles * g.splits;
 
   if (warp == 0) {
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
-        const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BF16_BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+      for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+        int mb_, nb_;
+        tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+        const int m0 = mb_ * BM, n0 = nb_ * BF16_BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
             raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 10, s);
             break;
@@ -265,7 +290,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t a_step = g.a_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2, b_step = g.b_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2;
       int s = 0, acc = 0;
       uint32_t ph = 0, acc_ph = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
+      for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
         if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_ph ^ 1)) {
           raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 11, acc);
           break;
@@ -273,7 +299,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BF16_BN;
         bool ok = true;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bars->full[s]), ph) || aborted(bars)) {
             raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 12, s);
             ok = false;
@@ -285,7 +311,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint64_t bdesc = make_smem_desc(a_addr + BF16_A_BYTES, b_lbo, 1024);
 #pragma unroll
           for (int k = 0; k < BF16_BK / 16; ++k)
-            mma_bf16(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, (kb | k) != 0);
+            mma_bf16(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) != 0);
           mma_commit(smem_u32(&bars->empty[s]));
           if (++s == BF16_STAGES) { s = 0; ph ^= 1; }
         }
@@ -300,8 +326,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int col_half = ew >> 2;        // which 128 of the tile's 256 columns
     int acc = 0;
     uint32_t acc_ph = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
-      const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BF16_BN;
+    for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+      int mb_, nb_;
+      tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+      const int m0 = mb_ * BM, n0 = nb_ * BF16_BN;
       const int m = m0 + quarter * 32 + lane;
       const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
       const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
@@ -356,16 +385,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const uint32_t tmem_base = bars->tmem_base;
 
   const int n_tiles_n = (g.N + FP8_BN - 1) / FP8_BN;
-  const int n_tiles = ((g.M + BM - 1) / BM) * n_tiles_n;
+  const int n_tiles_m = (g.M + BM - 1) / BM;
+  const int n_tiles = n_tiles_m * n_tiles_n;
   const int kblocks = (g.K + FP8_BK - 1) / FP8_BK;
+  const int kb_per = (kblocks + g.splits - 1) / g.splits;
+  const int n_work = n_tiles * g.splits;
 
   if (warp == 0) {
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !aborted(bars); tile += gridDim.x) {
-        const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * FP8_BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+      for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+        int mb_, nb_;
+        tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+        const int m0 = mb_ * BM, n0 = nb_ * FP8_BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
             raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 20, s);
             break;
@@ -386,8 +421,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       int s = 0, acc = 0;
       uint32_t ph = 0, acc_ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok && !aborted(bars); tile += gridDim.x) {
-        for (int kb = 0; kb < kblocks; ++kb) {
+      for (int work = blockIdx.x; work < n_work && ok && !aborted(bars); work += gridDim.x) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_ph ^ 1)) {
             raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 21, acc);
             ok = false;
@@ -420,18 +456,28 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok && !aborted(bars); tile += gridDim.x) {
-      const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * FP8_BN;
+    for (int work = blockIdx.x; work < n_work && ok && !aborted(bars); work += gridDim.x) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+      int mb_, nb_;
+      tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+      const int m0 = mb_ * BM, n0 = nb_ * FP8_BN;
       const int m = m0 + quarter * 32 + lane;
       const int m_ld = (m < g.M) ? m : (g.M - 1);
-      const int nb = n0 / 128;
+      const float* sa_row = g.sa + m_ld;
+      const float* sb_row = g.sb + (size_t)nb_ * kblocks;
       float accum[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) accum[j] = 0.0f;
-      float scale = g.sa[m_ld] * g.sb[(size_t)nb * kblocks];
-      for (int kb = 0; kb < kblocks; ++kb) {
-        float next_scale = 0.0f;
-        if (kb + 1 < kblocks) next_scale = g.sa[(size_t)(kb + 1) * g.sa_ld + m_ld] * g.sb[(size_t)nb * kblocks + kb + 1];
+      // scales are fetched four K blocks ahead so their global-memory latency never sits on the
+      // accumulate path
+      float sq[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        sq[i] = (kb0 + i < kb1) ? sa_row[(size_t)(kb0 + i) * g.sa_ld] * sb_row[kb0 + i] : 0.0f;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const float scale = sq[0];
+        sq[0] = sq[1]; sq[1] = sq[2]; sq[2] = sq[3];
+        sq[3] = (kb + 4 < kb1) ? sa_row[(size_t)(kb + 4) * g.sa_ld] * sb_row[kb + 4] : 0.0f;
         if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_ph)) {
           raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 23, acc);
           ok = false;
@@ -451,7 +497,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           accum[j] = fmaf(scale, __uint_as_float(r0[j]), accum[j]);
           accum[32 + j] = fmaf(scale, __uint_as_float(r1[j]), accum[32 + j]);
         }
-        scale = next_scale;
         if (++acc == FP8_ACC) { acc = 0; acc_ph ^= 1; }
       }
       if (!ok) break;
@@ -519,6 +564,20 @@ static int sm_count() {
   return n;
 }
 
+// Split the reduction over several CTAs when the output has too few tiles to fill the GPU (weight
+// gradients: small output, reduction over all tokens). Only for a plain fp32 "out += acc" epilogue,
+// whose additions can be done with atomics in any order.
+static int pick_splits(int tiles, int kblocks, const GemmEpilogue& e) {
+  const bool plain = e.out_f32 && e.accumulate && e.bias == nullptr && e.aux == nullptr && e.pre_out == nullptr &&
+                     e.act == ACT_NONE && e.row_scale == nullptr && e.ssq_in == nullptr && e.ssq_out == nullptr;
+  if (!plain || tiles * 2 > sm_count()) return 1;
+  int s = sm_count() / tiles;
+  if (s > kblocks / 4) s = kblocks / 4;   // keep at least four K blocks per share
+  if (s < 1) return 1;
+  const int per = (kblocks + s - 1) / s;
+  return (kblocks + per - 1) / per;       // no share may be empty: an empty one would publish a stale accumulator
+}
+
 const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
                              cudaStream_t stream) {
   if (g.K % 8 != 0 || g.N % 32 != 0) return "bf16 GEMM needs K % 8 == 0 and N % 32 == 0";
@@ -538,8 +597,13 @@ const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const G
     attr_set = true;
   }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BF16_BN - 1) / BF16_BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_bf16_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, g, e, status);
+  GemmShape gs = g;
+  GemmEpilogue es = e;
+  gs.splits = pick_splits(tiles, (g.K + BF16_BK - 1) / BF16_BK, e);
+  es.atomic = gs.splits > 1;
+  const int work = tiles * gs.splits;
+  const int grid = work < sm_count() ? work : sm_count();
+  gemm_bf16_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, gs, es, status);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_bf16_kernel launch failed";
 }
 
@@ -560,8 +624,13 @@ const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const Ge
     attr_set = true;
   }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + FP8_BN - 1) / FP8_BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_fp8_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, g, e, status);
+  GemmShape gs = g;
+  GemmEpilogue es = e;
+  gs.splits = pick_splits(tiles, (g.K + FP8_BK - 1) / FP8_BK, e);
+  es.atomic = gs.splits > 1;
+  const int work = tiles * gs.splits;
+  const int grid = work < sm_count() ? work : sm_count();
+  gemm_fp8_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, gs, es, status);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_kernel launch failed";
 }
 

@@ -31,6 +31,7 @@ struct GemmShape {
   const float* sa;  // fp8: scales of A, sa[kb * sa_ld + m]
   const float* sb;  // fp8: scales of B, sb[(n / 128) * ceil(K/128) + kb]
   int64_t sa_ld;
+  int splits;       // split-K shares (set by the launcher)
 };
 
 // Applied in this order to the fp32 accumulator of element (m, n):
@@ -40,6 +41,7 @@ struct GemmEpilogue {
   int64_t out_ld;
   int out_f32;
   int accumulate;       // out += v instead of out = v
+  int atomic;           // fp32 out += v with atomics (set by the launcher for split-K)
   const void* bias;     // [N] bf16 or fp32, may be null
   int bias_f32;
   const float* row_scale;   // [M], may be null
