@@ -92,6 +92,30 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Non-suspending variant: polls with test_wait (the thread is never parked by the hardware).
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < 100000; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    for (int i = 0; i < 1024; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (globaltimer_ns() - t0 > GD_WAIT_BUDGET_NS) return false;
+  }
+}
+
 // Wait for the phase with the given parity to complete. Returns false when the time
 // budget ran out (the caller reports and leaves its loop); never spins forever.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -103,6 +127,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
       if (mbar_try_wait(bar, parity)) return true;
     if (globaltimer_ns() - t0 > GD_WAIT_BUDGET_NS) return false;
   }
+}
+
+// Whole-warp wait with a single polling lane: 32 lanes spinning on try_wait flood the shared-memory
+// pipeline and slow the one-thread producer and MMA loops that share the SM. Lane 0 polls (with a
+// short back-off), the result is broadcast, and the warp reconverges before touching the data.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    ok = 0;
+    for (int i = 0; i < 64 && !ok; ++i) ok = mbar_try_wait(bar, parity);
+    if (!ok) {
+      const uint64_t t0 = globaltimer_ns();
+      while (!(ok = mbar_try_wait(bar, parity))) {
+        __nanosleep(32);
+        if (globaltimer_ns() - t0 > GD_WAIT_BUDGET_NS) break;
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -218,6 +218,23 @@ __device__ __forceinline__ void pipe_teardown(PipeBars* bars, int warp, uint32_t
 }
 
 // ---------------------------------------------------------------------------------------
+// lean single-thread loops
+// ---------------------------------------------------------------------------------------
+// The producer and the MMA issuer are single threads: their loops are bound by the number of
+// dependent instructions per K block, so everything that can be computed once is hoisted (barrier
+// addresses, descriptor templates) and the time-budgeted wait lives out of line.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) { return mbar_wait(bar, parity); }
+
+__device__ __forceinline__ bool wait_fast(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity);
+}
+
+__device__ __forceinline__ uint64_t desc_at(uint32_t hi, uint32_t lo) {
+  return ((uint64_t)hi << 32) | (uint64_t)lo;
+}
+
+// ---------------------------------------------------------------------------------------
 // bf16 kernel
 // ---------------------------------------------------------------------------------------
 constexpr int BF16_BN = 256;
@@ -245,40 +262,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int kblocks = (g.K + BF16_BK - 1) / BF16_BK;
   const int kb_per = (kblocks + g.splits - 1) / g.splits;   // K blocks per split-K share
   const int n_work = n_tiles * g.splits;
+  const uint32_t smem0 = smem_u32(smem);
+  const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
+  const uint32_t tfull0 = smem_u32(&bars->tmem_full[0]), tempty0 = smem_u32(&bars->tmem_empty[0]);
 
   if (warp == 0) {
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
+      bool ok = true;
+      for (int work = blockIdx.x; work < n_work && ok; work += gridDim.x) {
         const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
         int mb_, nb_;
         tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
         const int m0 = mb_ * BM, n0 = nb_ * BF16_BN;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
+        int kx = kb0 * BF16_BK;
+        for (int kb = kb0; kb < kb1; ++kb, kx += BF16_BK) {
+          if (!wait_fast(empty0 + 8 * s, ph ^ 1)) {
             raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 10, s);
+            ok = false;
             break;
           }
-          if (aborted(bars)) break;
-          const uint32_t full = smem_u32(&bars->full[s]);
-          const uint32_t a_dst = smem_u32(smem + s * BF16_STAGE_BYTES);
+          const uint32_t full = full0 + 8 * s;
+          const uint32_t a_dst = smem0 + s * BF16_STAGE_BYTES;
           const uint32_t b_dst = a_dst + BF16_A_BYTES;
           mbar_arrive_expect_tx(full, BF16_STAGE_BYTES);
           if (!g.a_mn) {
-            tma_load_2d(a_dst, &tmap_a, full, kb * BF16_BK, m0);
+            tma_load_2d(a_dst, &tmap_a, full, kx, m0);
           } else {
+#pragma unroll
             for (int i = 0; i < BM / 64; ++i)
-              tma_load_2d(a_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_a, full, m0 + i * 64, kb * BF16_BK);
+              tma_load_2d(a_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_a, full, m0 + i * 64, kx);
           }
           if (!g.b_mn) {
-            tma_load_2d(b_dst, &tmap_b, full, kb * BF16_BK, n0);
+            tma_load_2d(b_dst, &tmap_b, full, kx, n0);
           } else {
+#pragma unroll
             for (int i = 0; i < BF16_BN / 64; ++i)
-              tma_load_2d(b_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_b, full, n0 + i * 64, kb * BF16_BK);
+              tma_load_2d(b_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_b, full, n0 + i * 64, kx);
           }
           if (++s == BF16_STAGES) { s = 0; ph ^= 1; }
         }
+        if (aborted(bars)) break;
       }
     }
   } else if (warp == 1) {
@@ -288,35 +313,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // K advance per MMA (UMMA_K = 16 elements): 32 B inside the swizzle row when K-major,
       // 16 rows of 128 B when MN-major; in 16-byte units.
       const uint32_t a_step = g.a_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2, b_step = g.b_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2;
+      const uint64_t a_tmpl = make_smem_desc(smem0, a_lbo, 1024), b_tmpl = make_smem_desc(smem0 + BF16_A_BYTES, b_lbo, 1024);
+      const uint32_t a_hi = (uint32_t)(a_tmpl >> 32), a_lo0 = (uint32_t)a_tmpl;
+      const uint32_t b_hi = (uint32_t)(b_tmpl >> 32), b_lo0 = (uint32_t)b_tmpl;
       int s = 0, acc = 0;
       uint32_t ph = 0, acc_ph = 0;
-      for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
-        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
-        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_ph ^ 1)) {
+      bool ok = true;
+      for (int work = blockIdx.x; work < n_work && ok; work += gridDim.x) {
+        const int nkb = min(kblocks, (work / n_tiles) * kb_per + kb_per) - (work / n_tiles) * kb_per;
+        if (!wait_fast(tempty0 + 8 * acc, acc_ph ^ 1)) {
           raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 11, acc);
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BF16_BN;
-        bool ok = true;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->full[s]), ph) || aborted(bars)) {
+        uint32_t accumulate = 0;
+        for (int i = 0; i < nkb; ++i) {
+          if (!wait_fast(full0 + 8 * s, ph)) {
             raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 12, s);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + s * BF16_STAGE_BYTES);
-          const uint64_t adesc = make_smem_desc(a_addr, a_lbo, 1024);
-          const uint64_t bdesc = make_smem_desc(a_addr + BF16_A_BYTES, b_lbo, 1024);
+          const uint32_t a_lo = a_lo0 + s * (BF16_STAGE_BYTES >> 4), b_lo = b_lo0 + s * (BF16_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BF16_BK / 16; ++k)
-            mma_bf16(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) != 0);
-          mma_commit(smem_u32(&bars->empty[s]));
+          for (int k = 0; k < BF16_BK / 16; ++k) {
+            mma_bf16(d_tmem, desc_at(a_hi, a_lo + k * a_step), desc_at(b_hi, b_lo + k * b_step), idesc, accumulate);
+            accumulate = 1;
+          }
+          mma_commit(empty0 + 8 * s);
           if (++s == BF16_STAGES) { s = 0; ph ^= 1; }
         }
-        if (!ok) break;
-        mma_commit(smem_u32(&bars->tmem_full[acc]));
+        if (!ok || aborted(bars)) break;
+        mma_commit(tfull0 + 8 * acc);
         if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
       }
     }
@@ -327,33 +356,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_ph = 0;
     for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
-        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+      const int tile = work % n_tiles;
       int mb_, nb_;
       tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
       const int m0 = mb_ * BM, n0 = nb_ * BF16_BN;
       const int m = m0 + quarter * 32 + lane;
       const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
       const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
-      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_ph)) {
+      if (!mbar_wait_warp(tfull0 + 8 * acc, acc_ph)) {
         raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 13, acc);
         break;
       }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BF16_BN + col_half * 128;
       float ssq = 0.0f;
-#pragma unroll 1
+      // two chunks are in flight: the TMEM load of the next chunk overlaps the math and stores of this one
+      uint32_t raw[2][32];
+      tmem_ld_32x32(t_row, raw[0]);
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t raw[32];
-        tmem_ld_32x32(t_row + c * 32, raw);
         tmem_ld_wait();
+        if (c + 1 < 4) tmem_ld_32x32(t_row + (c + 1) * 32, raw[(c + 1) & 1]);
+        if (c == 3) {   // everything is in registers: hand the accumulator back before the last chunk's stores
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+        }
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
         ssq += epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 128 + c * 32, rs, rc, v);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
       if (e.ssq_out != nullptr && m < g.M && n0 + col_half * 128 < g.N)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 128 + col_half)] = ssq;
       if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
@@ -390,63 +423,71 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const int kblocks = (g.K + FP8_BK - 1) / FP8_BK;
   const int kb_per = (kblocks + g.splits - 1) / g.splits;
   const int n_work = n_tiles * g.splits;
+  const uint32_t smem0 = smem_u32(smem);
+  const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
+  const uint32_t tfull0 = smem_u32(&bars->tmem_full[0]), tempty0 = smem_u32(&bars->tmem_empty[0]);
 
   if (warp == 0) {
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
+      bool ok = true;
+      for (int work = blockIdx.x; work < n_work && ok; work += gridDim.x) {
         const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
         int mb_, nb_;
         tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
         const int m0 = mb_ * BM, n0 = nb_ * FP8_BN;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
+        int kx = kb0 * FP8_BK;
+        for (int kb = kb0; kb < kb1; ++kb, kx += FP8_BK) {
+          if (!wait_fast(empty0 + 8 * s, ph ^ 1)) {
             raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 20, s);
+            ok = false;
             break;
           }
-          if (aborted(bars)) break;
-          const uint32_t full = smem_u32(&bars->full[s]);
-          const uint32_t a_dst = smem_u32(smem + s * FP8_STAGE_BYTES);
+          const uint32_t full = full0 + 8 * s;
+          const uint32_t a_dst = smem0 + s * FP8_STAGE_BYTES;
           mbar_arrive_expect_tx(full, FP8_STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, full, kb * FP8_BK, m0);
-          tma_load_2d(a_dst + FP8_A_BYTES, &tmap_b, full, kb * FP8_BK, n0);
+          tma_load_2d(a_dst, &tmap_a, full, kx, m0);
+          tma_load_2d(a_dst + FP8_A_BYTES, &tmap_b, full, kx, n0);
           if (++s == FP8_STAGES) { s = 0; ph ^= 1; }
         }
+        if (aborted(bars)) break;
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_instr_desc(0, 0, 0, 0, BM, FP8_BN);
+      const uint64_t a_tmpl = make_smem_desc(smem0, 16, 1024), b_tmpl = make_smem_desc(smem0 + FP8_A_BYTES, 16, 1024);
+      const uint32_t a_hi = (uint32_t)(a_tmpl >> 32), a_lo0 = (uint32_t)a_tmpl;
+      const uint32_t b_hi = (uint32_t)(b_tmpl >> 32), b_lo0 = (uint32_t)b_tmpl;
       int s = 0, acc = 0;
       uint32_t ph = 0, acc_ph = 0;
       bool ok = true;
-      for (int work = blockIdx.x; work < n_work && ok && !aborted(bars); work += gridDim.x) {
-        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_ph ^ 1)) {
+      for (int work = blockIdx.x; work < n_work && ok; work += gridDim.x) {
+        const int nkb = min(kblocks, (work / n_tiles) * kb_per + kb_per) - (work / n_tiles) * kb_per;
+        for (int i = 0; i < nkb; ++i) {
+          if (!wait_fast(tempty0 + 8 * acc, acc_ph ^ 1)) {
             raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 21, acc);
             ok = false;
             break;
           }
-          if (!mbar_wait(smem_u32(&bars->full[s]), ph) || aborted(bars)) {
+          if (!wait_fast(full0 + 8 * s, ph)) {
             raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 22, s);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + s * FP8_STAGE_BYTES);
-          const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(a_addr + FP8_A_BYTES, 16, 1024);
+          const uint32_t a_lo = a_lo0 + s * (FP8_STAGE_BYTES >> 4), b_lo = b_lo0 + s * (FP8_STAGE_BYTES >> 4);
           const uint32_t d_tmem = tmem_base + acc * FP8_BN;
 #pragma unroll
           for (int k = 0; k < FP8_BK / 32; ++k)
-            mma_fp8(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, k != 0);
-          mma_commit(smem_u32(&bars->empty[s]));
-          mma_commit(smem_u32(&bars->tmem_full[acc]));
+            mma_fp8(d_tmem, desc_at(a_hi, a_lo + k * 2), desc_at(b_hi, b_lo + k * 2), idesc, k != 0);
+          mma_commit(empty0 + 8 * s);
+          mma_commit(tfull0 + 8 * acc);
           if (++s == FP8_STAGES) { s = 0; ph ^= 1; }
           if (++acc == FP8_ACC) { acc = 0; acc_ph ^= 1; }
         }
+        if (aborted(bars)) break;
       }
     }
   } else {
@@ -456,8 +497,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
-    for (int work = blockIdx.x; work < n_work && ok && !aborted(bars); work += gridDim.x) {
-        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + col_half * 64;
+    for (int work = blockIdx.x; work < n_work && ok; work += gridDim.x) {
+      const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
       int mb_, nb_;
       tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
       const int m0 = mb_ * BM, n0 = nb_ * FP8_BN;
@@ -478,20 +520,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const float scale = sq[0];
         sq[0] = sq[1]; sq[1] = sq[2]; sq[2] = sq[3];
         sq[3] = (kb + 4 < kb1) ? sa_row[(size_t)(kb + 4) * g.sa_ld] * sb_row[kb + 4] : 0.0f;
-        if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_ph)) {
+        if (!wait_fast(tfull0 + 8 * acc, acc_ph)) {
           raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 23, acc);
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * FP8_BN + col_half * 64;
+        const uint32_t t_row = t_lane + acc * FP8_BN;
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(t_row, r0);
         tmem_ld_32x32(t_row + 32, r1);
         tmem_ld_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+        if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           accum[j] = fmaf(scale, __uint_as_float(r0[j]), accum[j]);
@@ -499,7 +541,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         if (++acc == FP8_ACC) { acc = 0; acc_ph ^= 1; }
       }
-      if (!ok) break;
+      if (!ok || aborted(bars)) break;
       const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
       const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
       float ssq = 0.0f;
