@@ -387,3 +387,73 @@ const char* launch_batched_gemv(const void* const* mats, const float* const* vec
 }
 
 }  // namespace gd
+
+// =======================================================================================
+// allocation-free mean cross-entropy (see noalloc.h; no counterpart in the reference)
+// =======================================================================================
+#include "noalloc.h"
+
+namespace gd {
+
+// Scratch of the allocation-free entry point: [0, MAX_ROWS) per-row losses, [MAX_ROWS] unused pad.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_noalloc_scratch[GD_NOALLOC_MAX_ROWS + 64];
+
+// One block: loss_out = sum(row_loss) / max(1, #targets != ignore_index). Reads every row loss the
+// preceding kernel wrote (rows beyond `rows` hold stale values from earlier calls and are not read).
+__global__ void __launch_bounds__(1024)
+noalloc_finalize_kernel(const float* __restrict__ row_loss, const int64_t* __restrict__ targets, int64_t rows,
+                        int ignore_index, float* __restrict__ loss_out) {
+  __shared__ float s_sum[32];
+  __shared__ float s_cnt[32];
+  float sum = 0.0f, cnt = 0.0f;
+  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
+    sum += row_loss[r];
+    cnt += targets[r] != ignore_index ? 1.0f : 0.0f;
+  }
+  sum = warp_sum(sum);
+  cnt = warp_sum(cnt);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { s_sum[warp] = sum; s_cnt[warp] = cnt; }
+  __syncthreads();
+  if (warp == 0) {
+    sum = s_sum[lane];
+    cnt = s_cnt[lane];
+    sum = warp_sum(sum);
+    cnt = warp_sum(cnt);
+    if (lane == 0) loss_out[0] = sum / fmaxf(cnt, 1.0f);
+  }
+}
+
+}  // namespace gd
+
+extern "C" int gd_cross_entropy_mean_noalloc(const void* logits_bf16, const int64_t* targets, int64_t rows, int vocab,
+                                             int64_t ld, int ignore_index, float* loss_out, void* stream) {
+  if (rows < 0 || rows > GD_NOALLOC_MAX_ROWS) return 1;
+  if (logits_bf16 == nullptr || targets == nullptr || loss_out == nullptr) return 2;
+  if ((reinterpret_cast<uintptr_t>(logits_bf16) & 15) != 0 || ld % 8 != 0 || vocab < 1 || vocab > ld) return 2;
+
+  // device address of the scratch array, looked up once per device with that device current
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 3;
+  if (scratch_of_device[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), gd::g_noalloc_scratch) != cudaSuccess || p == nullptr)
+      return 3;
+    scratch_of_device[dev] = p;
+  }
+  float* row_loss = scratch_of_device[dev];
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+  if (rows > 0) {
+    // write_grad = 0: the logits stay untouched and inv_count is not read; every row in [0, rows) is
+    // overwritten, so nothing of an earlier call survives where this call looks
+    gd::cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(
+        reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(logits_bf16)), targets, row_loss, row_loss, vocab, ld,
+        ignore_index, 1.0f, 0);
+    if (cudaGetLastError() != cudaSuccess) return 3;
+  }
+  gd::noalloc_finalize_kernel<<<1, 1024, 0, st>>>(row_loss, targets, rows, ignore_index, loss_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
