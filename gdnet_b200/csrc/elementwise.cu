@@ -13,11 +13,8 @@ namespace gd {
 // =======================================================================================
 // causal depthwise convolution
 // =======================================================================================
-// Block = 8 warps. A lane owns CH consecutive channels (one vector), a warp owns 32*CH
-// channels, and the 8 warps of a block take 8 consecutive row tiles of TT time steps, so a
-// block covers 8*TT rows x 32*CH channels of one batch row. Taps are padded at the front
-// to KMAX so the sliding window has a compile-time length.
-constexpr int CONV_TT = 16;
+// x is (B, T, d) with d contiguous; a lane always owns a vector of consecutive channels, so a warp
+// reads and writes 512 contiguous bytes of one row.
 
 template <int CH> struct VecOf;
 template <> struct VecOf<8> { using type = uint4; };
@@ -61,183 +58,164 @@ __device__ __forceinline__ void load_conv_row(const __nv_bfloat16* x, const __nv
   }
 }
 
-template <int KMAX, int CH>
+// ---------------------------------------------------------------------------------------
+// point-wise formulation: one thread per output vector (8 channels of one time step). Every load
+// is independent, so the kernels run at full occupancy with many loads in flight; the k-fold
+// re-read of neighbouring rows is served by L1/L2 (blocks cover consecutive time steps).
+// ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-dwconv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
-                  const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int B, int T, int d, int k,
-                  int64_t x_ld, int64_t out_ld) {
+dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
+                     const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int B, int T, int d, int k,
+                     int64_t x_ld, int64_t out_ld) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ch = (blockIdx.y * 32 + lane) * CH;
-  const int tiles_per_b = (T + 8 * CONV_TT - 1) / (8 * CONV_TT);
-  const int b = blockIdx.x / tiles_per_b;
-  const int t0 = ((blockIdx.x % tiles_per_b) * 8 + warp) * CONV_TT;
-  if (ch >= d || t0 >= T) return;
+  const int ch = (blockIdx.y * 32 + lane) * 8;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;      // 8 consecutive time steps per block
+  if (ch >= d || row >= (int64_t)B * T) return;
+  const int b = (int)(row / T), t = (int)(row % T);
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+  for (int i = 0; i < k; ++i) {
+    float in[8];
+    load_conv_row<8>(x, halo, x_ld, T, k, b, t - (k - 1) + i, ch, d, in);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = fmaf(w[(ch + c) * k + i], in[c], acc[c]);
+  }
+  store_bf16_vec<8>(out + row * out_ld + ch, acc);
+}
 
-  float taps[KMAX][CH];
+// dx[t] = sum_j w[k-1-j] dc[t+j] for t in [t_lo, T), t_lo = -(k-1) when the halo gradient is wanted
+__global__ void __launch_bounds__(256)
+dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ w,
+                    const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx,
+                    __nv_bfloat16* __restrict__ dhalo, int B, int T, int d, int k, int64_t dc_ld) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ch = (blockIdx.y * 32 + lane) * 8;
+  const int t_lo = dhalo != nullptr ? -(k - 1) : 0;
+  const int rows_per_b = T - t_lo;
+  const int64_t r = (int64_t)blockIdx.x * 8 + warp;
+  if (ch >= d || r >= (int64_t)B * rows_per_b) return;
+  const int b = (int)(r / rows_per_b), t = (int)(r % rows_per_b) + t_lo;
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+  for (int j = 0; j < k; ++j) {
+    const int tt = t + j;
+    if (tt < 0 || tt >= T) continue;
+    float g[8];
+    load_bf16_vec<8>(dc + ((int64_t)b * T + tt) * dc_ld + ch, g);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = fmaf(w[(ch + c) * k + (k - 1 - j)], g[c], acc[c]);
+  }
+  if (t >= 0) {
+    if (dx_tail_add != nullptr && t >= T - (k - 1)) {
+      float extra[8];
+      load_bf16_vec<8>(dx_tail_add + ((int64_t)b * (k - 1) + (t - (T - (k - 1)))) * d + ch, extra);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] += extra[c];
+    }
+    store_bf16_vec<8>(dx + ((int64_t)b * T + t) * d + ch, acc);
+  } else {
+    store_bf16_vec<8>(dhalo + ((int64_t)b * (k - 1) + (t + k - 1)) * d + ch, acc);
+  }
+}
+
+// dw[ch][i] += sum_{b,t} dc[b,t,ch] * xpad[b, t-(k-1)+i, ch]: a lane owns 4 channels and walks a strip of
+// DW_TT time steps with a sliding window of x; the 8 warps of a block (8 strips) are reduced in shared
+// memory before one atomic per (channel, tap).
+constexpr int DW_TT = 32;
+
+template <int KMAX>
+__global__ void __launch_bounds__(256)
+dwconv_dw_kernel(const __nv_bfloat16* __restrict__ dc, const __nv_bfloat16* __restrict__ x,
+                 const __nv_bfloat16* __restrict__ halo, float* __restrict__ dw, int B, int T, int d, int k,
+                 int64_t dc_ld, int64_t x_ld) {
+  constexpr bool BLOCK_REDUCE = KMAX <= 8;     // the widest window would not fit the static shared-memory limit
+  __shared__ float part[BLOCK_REDUCE ? 8 : 1][BLOCK_REDUCE ? KMAX : 1][128 + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ch = (blockIdx.y * 32 + lane) * 4;
+  const int strips_per_b = (T + DW_TT - 1) / DW_TT;
+  const int strip = blockIdx.x * 8 + warp;
+  const int b = strip / strips_per_b;
+  const int t0 = (strip % strips_per_b) * DW_TT;
+  float acc[KMAX][4];
 #pragma unroll
   for (int i = 0; i < KMAX; ++i)
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      const int src = i - (KMAX - k);
-      taps[i][c] = src >= 0 ? w[(ch + c) * k + src] : 0.0f;
-    }
-
-  float win[KMAX][CH];  // win[i] = input at t - (KMAX-1) + i
+    for (int c = 0; c < 4; ++c) acc[i][c] = 0.0f;
+  if (ch < d && b < B) {
+    float xw[KMAX][4];     // xw[i] = xpad[t - (KMAX-1) + i]
 #pragma unroll
-  for (int i = 0; i < KMAX - 1; ++i) load_conv_row<CH>(x, halo, x_ld, T, k, b, t0 - (KMAX - 1) + i, ch, d, win[i + 1]);
-
-  const int t_end = min(t0 + CONV_TT, T);
+    for (int i = 0; i < KMAX - 1; ++i) load_conv_row<4>(x, halo, x_ld, T, k, b, t0 - (KMAX - 1) + i, ch, d, xw[i + 1]);
+    const int t_end = min(t0 + DW_TT, T);
 #pragma unroll 4
-  for (int t = t0; t < t_end; ++t) {
+    for (int t = t0; t < t_end; ++t) {
 #pragma unroll
-    for (int i = 0; i < KMAX - 1; ++i)
+      for (int i = 0; i < KMAX - 1; ++i)
 #pragma unroll
-      for (int c = 0; c < CH; ++c) win[i][c] = win[i + 1][c];
-    load_bf16_vec<CH>(x + ((int64_t)b * T + t) * x_ld + ch, win[KMAX - 1]);
-    float acc[CH];
+        for (int c = 0; c < 4; ++c) xw[i][c] = xw[i + 1][c];
+      load_bf16_vec<4>(x + ((int64_t)b * T + t) * x_ld + ch, xw[KMAX - 1]);
+      float g[4];
+      load_bf16_vec<4>(dc + ((int64_t)b * T + t) * dc_ld + ch, g);
 #pragma unroll
-    for (int c = 0; c < CH; ++c) acc[c] = 0.0f;
+      for (int i = 0; i < KMAX; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[i][c] = fmaf(g[c], xw[i][c], acc[i][c]);
+    }
+  }
+  if constexpr (!BLOCK_REDUCE) {
 #pragma unroll
     for (int i = 0; i < KMAX; ++i)
 #pragma unroll
-      for (int c = 0; c < CH; ++c) acc[c] = fmaf(taps[i][c], win[i][c], acc[c]);
-    store_bf16_vec<CH>(out + ((int64_t)b * T + t) * out_ld + ch, acc);
+      for (int c = 0; c < 4; ++c) {
+        const int src = i - (KMAX - k);
+        if (src >= 0 && ch + c < d && acc[i][c] != 0.0f) atomicAdd(dw + (int64_t)(ch + c) * k + src, acc[i][c]);
+      }
+    return;
   }
-}
-
-// Backward. For every position t in [-(k-1), T): dx[t] = sum_j w[k-1-j] * dc[t+j] (dc outside
-// [0,T) is zero); positions t < 0 are the gradient of the halo rows. dw[ch][i] += sum_t dc[t] *
-// xpad[t-(k-1)+i]. `dx_tail_add` (B, k-1, d) holds the halo gradient received from the next
-// sequence shard; it is added to the last k-1 rows of dx here, before dx leaves the kernel.
-template <int KMAX, int CH>
-__global__ void __launch_bounds__(256)
-dwconv_bwd_kernel(const __nv_bfloat16* __restrict__ dc, const __nv_bfloat16* __restrict__ x,
-                  const __nv_bfloat16* __restrict__ halo, const float* __restrict__ w,
-                  const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx,
-                  __nv_bfloat16* __restrict__ dhalo, float* __restrict__ dw, int B, int T, int d, int k,
-                  int64_t dc_ld, int64_t x_ld) {
-  __shared__ float dw_part[8][KMAX][32 * CH + 1];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ch = (blockIdx.y * 32 + lane) * CH;
-  const int tiles_per_b = (T + (k - 1) + 8 * CONV_TT - 1) / (8 * CONV_TT);
-  const int b = blockIdx.x / tiles_per_b;
-  const int t0 = ((blockIdx.x % tiles_per_b) * 8 + warp) * CONV_TT - (k - 1);  // first tile starts in the halo
-  const bool active = ch < d && t0 < T;
-
-  float dwacc[KMAX][CH];
 #pragma unroll
   for (int i = 0; i < KMAX; ++i)
 #pragma unroll
-    for (int c = 0; c < CH; ++c) dwacc[i][c] = 0.0f;
-
-  if (active) {
-    float taps[KMAX][CH];  // taps[j] multiplies dc[t+j]: w[k-1-j], zero for j >= k
-#pragma unroll
-    for (int j = 0; j < KMAX; ++j)
-#pragma unroll
-      for (int c = 0; c < CH; ++c) taps[j][c] = j < k ? w[(ch + c) * k + (k - 1 - j)] : 0.0f;
-
-    float gwin[KMAX][CH];  // gwin[j] = dc[t + j]
-    float xwin[KMAX][CH];  // xwin[i] = xpad[t - (KMAX-1) + i]
-    auto load_dc = [&](int t, float (&o)[CH]) {
-      if (t >= 0 && t < T) load_bf16_vec<CH>(dc + ((int64_t)b * T + t) * dc_ld + ch, o);
-      else {
-#pragma unroll
-        for (int c = 0; c < CH; ++c) o[c] = 0.0f;
-      }
-    };
-#pragma unroll
-    for (int j = 0; j < KMAX - 1; ++j) load_dc(t0 + j, gwin[j + 1]);
-#pragma unroll
-    for (int i = 0; i < KMAX - 1; ++i) load_conv_row<CH>(x, halo, x_ld, T, k, b, t0 - (KMAX - 1) + i, ch, d, xwin[i + 1]);
-
-    const int t_end = min(t0 + CONV_TT, T);
-#pragma unroll 2
-    for (int t = t0; t < t_end; ++t) {
-#pragma unroll
-      for (int j = 0; j < KMAX - 1; ++j)
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          gwin[j][c] = gwin[j + 1][c];
-          xwin[j][c] = xwin[j + 1][c];
-        }
-      load_dc(t + KMAX - 1, gwin[KMAX - 1]);
-      load_conv_row<CH>(x, halo, x_ld, T, k, b, t, ch, d, xwin[KMAX - 1]);
-
-      float acc[CH];
-#pragma unroll
-      for (int c = 0; c < CH; ++c) acc[c] = 0.0f;
-#pragma unroll
-      for (int j = 0; j < KMAX; ++j)
-#pragma unroll
-        for (int c = 0; c < CH; ++c) acc[c] = fmaf(taps[j][c], gwin[j][c], acc[c]);
-
-      if (t >= 0) {
-        if (dx_tail_add != nullptr && t >= T - (k - 1)) {
-          float extra[CH];
-          load_bf16_vec<CH>(dx_tail_add + ((int64_t)b * (k - 1) + (t - (T - (k - 1)))) * d + ch, extra);
-#pragma unroll
-          for (int c = 0; c < CH; ++c) acc[c] += extra[c];
-        }
-        store_bf16_vec<CH>(dx + ((int64_t)b * T + t) * d + ch, acc);
-        // dw: dc[t] (= gwin[0]) times the window that produced out[t]
-#pragma unroll
-        for (int i = 0; i < KMAX; ++i)
-#pragma unroll
-          for (int c = 0; c < CH; ++c) dwacc[i][c] = fmaf(gwin[0][c], xwin[i][c], dwacc[i][c]);
-      } else if (dhalo != nullptr) {
-        store_bf16_vec<CH>(dhalo + ((int64_t)b * (k - 1) + (t + k - 1)) * d + ch, acc);
-      }
-    }
-  }
-
-  // reduce dw over the 8 warps (same channels, different row tiles), then one atomic per (ch, tap)
-#pragma unroll
-  for (int i = 0; i < KMAX; ++i)
-#pragma unroll
-    for (int c = 0; c < CH; ++c) dw_part[warp][i][lane * CH + c] = dwacc[i][c];
+    for (int c = 0; c < 4; ++c) part[BLOCK_REDUCE ? warp : 0][BLOCK_REDUCE ? i : 0][lane * 4 + c] = acc[i][c];
   __syncthreads();
-  for (int idx = threadIdx.x; idx < KMAX * 32 * CH; idx += blockDim.x) {
-    const int i = idx / (32 * CH), cc = idx % (32 * CH);
-    const int src = i - (KMAX - k);
-    const int chan = blockIdx.y * 32 * CH + cc;
+  for (int idx = threadIdx.x; idx < KMAX * 128; idx += blockDim.x) {
+    const int i = idx / 128, cc = idx % 128;
+    const int src = i - (KMAX - k);          // window slot i holds tap src (front-padded to KMAX)
+    const int chan = blockIdx.y * 128 + cc;
     if (src < 0 || chan >= d) continue;
-    float s = 0.0f;
+    float sum = 0.0f;
 #pragma unroll
-    for (int wq = 0; wq < 8; ++wq) s += dw_part[wq][i][cc];
-    if (s != 0.0f) atomicAdd(dw + (int64_t)chan * k + src, s);
+    for (int wq = 0; wq < 8; ++wq) sum += part[BLOCK_REDUCE ? wq : 0][BLOCK_REDUCE ? i : 0][cc];
+    if (sum != 0.0f) atomicAdd(dw + (int64_t)chan * k + src, sum);
   }
 }
 
-template <int KMAX, int CH>
-static const char* conv_fwd_launch(const ConvArgs& a, cudaStream_t st) {
-  dim3 grid(a.B * ((a.T + 8 * CONV_TT - 1) / (8 * CONV_TT)), (a.d + 32 * CH - 1) / (32 * CH));
-  dwconv_fwd_kernel<KMAX, CH><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
-  return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
-}
-
-template <int KMAX, int CH>
-static const char* conv_bwd_launch(const ConvBwdArgs& a, cudaStream_t st) {
-  dim3 grid(a.B * ((a.T + a.k - 1 + 8 * CONV_TT - 1) / (8 * CONV_TT)), (a.d + 32 * CH - 1) / (32 * CH));
-  dwconv_bwd_kernel<KMAX, CH><<<grid, 256, 0, st>>>(a.dc, a.x, a.halo, a.w, a.dx_tail_add, a.dx, a.dhalo, a.dw,
-                                                    a.B, a.T, a.d, a.k, a.dc_ld, a.x_ld);
-  return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_bwd launch failed";
+template <int KMAX>
+static const char* conv_dw_launch(const ConvBwdArgs& a, cudaStream_t st) {
+  const int strips = a.B * ((a.T + DW_TT - 1) / DW_TT);
+  dim3 grid((strips + 7) / 8, (a.d + 127) / 128);
+  dwconv_dw_kernel<KMAX><<<grid, 256, 0, st>>>(a.dc, a.x, a.halo, a.dw, a.B, a.T, a.d, a.k, a.dc_ld, a.x_ld);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_dw launch failed";
 }
 
 const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if (a.k < 1 || a.k > 16) return "dwconv: kernel width must be in [1, 16]";
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
-  if (a.k <= 4) return conv_fwd_launch<4, 8>(a, st);
-  if (a.k <= 8) return conv_fwd_launch<8, 4>(a, st);
-  return conv_fwd_launch<16, 2>(a, st);
+  dim3 grid((unsigned)(((int64_t)a.B * a.T + 7) / 8), (a.d + 255) / 256);
+  dwconv_fwd_pt_kernel<<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
 }
 
 const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   if (a.k < 1 || a.k > 16) return "dwconv: kernel width must be in [1, 16]";
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
-  if (a.k <= 4) return conv_bwd_launch<4, 4>(a, st);   // narrower vectors: two windows + dw accumulators per lane
-  if (a.k <= 8) return conv_bwd_launch<8, 2>(a, st);
-  return conv_bwd_launch<16, 2>(a, st);
+  const int rows_per_b = a.T + (a.dhalo != nullptr ? a.k - 1 : 0);
+  dim3 grid((unsigned)(((int64_t)a.B * rows_per_b + 7) / 8), (a.d + 255) / 256);
+  dwconv_dx_pt_kernel<<<grid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
+  if (cudaGetLastError() != cudaSuccess) return "dwconv_dx launch failed";
+  if (a.k <= 4) return conv_dw_launch<4>(a, st);
+  if (a.k <= 8) return conv_dw_launch<8>(a, st);
+  return conv_dw_launch<16>(a, st);
 }
 
 // =======================================================================================
@@ -309,65 +287,92 @@ const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? nullptr : "gate_update_fwd launch failed";
 }
 
-// Backward of the update and of both activations feeding it. Per row (one warp):
+// Backward of the update and of both activations feeding it.
 //   g = sigmoid(g_pre), zh = z*rstd, R = sigmoid(zh*w_r), D = dF - dS
 //   dg_pre = (D*c + dgm) * g(1-g)            dgm = d(loss)/d(mean g) / (rows*d)
 //   dq     = dg_pre * rstd_g                 (gradient of the un-normalised gate GEMM output)
 //   T_row  = sum_n dg_pre * (g_pre - b2g)    (for the rstd term of the gate RMSNorm)
 //   dc_dir = dF*g + dS*(1-g),  ds_dir = dF*R + dS*(1-R)
 //   dy = D*s*R(1-R),  dzh = dy*w_r,  dz = rstd*(dzh - zh*mean_n(dzh*zh))
-// Column sums: db2g += dg_pre, dw_r += dy*zh, db2r += dz (shared-memory partials, then atomics).
-// Outputs: dq (bf16), dz (bf16), dsc[:, :d] = ds_dir, dsc[:, d:] = dc_dir (bf16, row pitch 2d),
-// rowcoef[row] = rstd_g^2 / d * T_row.
+//   column sums: db2g += dg_pre, dw_r += dy*zh, db2r += dz
+// Two kernels. (1) row statistics, one warp per row: mean_n(dzh*zh), rstd_g and
+// rowcoef = rstd_g^2/d * T_row. (2) outputs and column sums: a lane owns 8 columns and walks a strip
+// of rows, so the three column sums live in registers; the 8 warps of a block (8 strips of the same
+// 256 columns) are reduced in shared memory before one atomic per column.
+struct GateElem {
+  float dgp, dy, zh, g, R;
+};
+
+__device__ __forceinline__ GateElem gate_elem(float dF, float dS, float z, float s, float gp, float c, float wr,
+                                              float rstd, float dgm) {
+  GateElem e;
+  e.zh = z * rstd;
+  e.R = sigmoidf_(e.zh * wr);
+  e.g = sigmoidf_(gp);
+  const float D = dF - dS;
+  e.dgp = (D * c + dgm) * e.g * (1.0f - e.g);
+  e.dy = D * s * e.R * (1.0f - e.R);
+  return e;
+}
+
 __global__ void __launch_bounds__(256)
-gate_update_bwd_kernel(const GateBwdArgs a) {
-  extern __shared__ float colacc_all[];  // [warps][3][d]: db2g, dw_r, db2r; each warp owns a slab, no atomics
+gate_bwd_rowstats_kernel(const GateBwdArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int wpb = blockDim.x >> 5;
-  float* colacc = colacc_all + (size_t)warp * 3 * a.d;
-  for (int i = lane; i < 3 * a.d; i += 32) colacc[i] = 0.0f;
-  __syncwarp();
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= a.rows) return;
   const float dgm = (a.dgate_mean != nullptr) ? a.dgate_mean[0] / ((float)a.rows * (float)a.d) : 0.0f;
-
-  for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < a.rows; row += (int64_t)gridDim.x * wpb) {
-    const float rstd = a.rstd_z[row];
-    float rstd_g;
-    {
-      float ssum = 0.0f;
-      for (int p = 0; p < a.ssq_parts; ++p) ssum += a.ssq_g[row * a.ssq_parts + p];
-      rstd_g = rsqrtf(ssum / (float)a.d + a.eps_g);
-    }
-    // pass 1: row reductions sum(dzh*zh) and T_row
-    float dot_z = 0.0f, t_row = 0.0f;
-    for (int col = lane * 8; col < a.d; col += 256) {
-      float dF[8], dS[8], zv[8], sv[8], gp[8], cv[8];
-      ld8(a.dF + row * a.dF_ld + col, dF);
-      ld8(a.dS + row * a.dS_ld + col, dS);
-      ld8(a.z + row * a.d + col, zv);
-      ld8(a.s + row * a.s_ld + col, sv);
-      ld8(a.g_pre + row * a.d + col, gp);
-      ld8(a.c + row * a.c_ld + col, cv);
+  const float rstd = a.rstd_z[row];
+  float ssum = 0.0f;
+  for (int p = lane; p < a.ssq_parts; p += 32) ssum += a.ssq_g[row * a.ssq_parts + p];
+  ssum = warp_sum(ssum);
+  const float rstd_g = rsqrtf(ssum / (float)a.d + a.eps_g);
+  float dot_z = 0.0f, t_row = 0.0f;
+  for (int col = lane * 8; col < a.d; col += 256) {
+    float dF[8], dS[8], zv[8], sv[8], gp[8], cv[8];
+    ld8(a.dF + row * a.dF_ld + col, dF);
+    ld8(a.dS + row * a.dS_ld + col, dS);
+    ld8(a.z + row * a.d + col, zv);
+    ld8(a.s + row * a.s_ld + col, sv);
+    ld8(a.g_pre + row * a.d + col, gp);
+    ld8(a.c + row * a.c_ld + col, cv);
+    const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(a.b2g + col), b1 = *reinterpret_cast<const float4*>(a.b2g + col + 4);
+    const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const float b2[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float wr = a.w_r[col + i];
-        const float zh = zv[i] * rstd;
-        const float R = sigmoidf_(zh * wr);
-        const float D = dF[i] - dS[i];
-        const float dzh = D * sv[i] * R * (1.0f - R) * wr;
-        dot_z = fmaf(dzh, zh, dot_z);
-        const float g = sigmoidf_(gp[i]);
-        const float dgp = (D * cv[i] + dgm) * g * (1.0f - g);
-        const float b2 = a.b2g_f32 ? reinterpret_cast<const float*>(a.b2g)[col + i]
-                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.b2g)[col + i]);
-        t_row = fmaf(dgp, gp[i] - b2, t_row);
-      }
+    for (int i = 0; i < 8; ++i) {
+      const GateElem e = gate_elem(dF[i], dS[i], zv[i], sv[i], gp[i], cv[i], wr[i], rstd, dgm);
+      dot_z = fmaf(e.dy * wr[i], e.zh, dot_z);
+      t_row = fmaf(e.dgp, gp[i] - b2[i], t_row);
     }
-    dot_z = warp_sum(dot_z) / (float)a.d;
-    t_row = warp_sum(t_row);
-    if (lane == 0) a.rowcoef[row] = rstd_g * rstd_g / (float)a.d * t_row;
+  }
+  dot_z = warp_sum(dot_z) / (float)a.d;
+  t_row = warp_sum(t_row);
+  if (lane == 0) {
+    a.rowcoef[row] = rstd_g * rstd_g / (float)a.d * t_row;
+    a.row_dotz[row] = dot_z;
+    a.row_rstdg[row] = rstd_g;
+  }
+}
 
-    // pass 2: outputs (inputs come back from L1/L2)
-    for (int col = lane * 8; col < a.d; col += 256) {
+constexpr int GATE_STRIP = 16;   // rows per warp in the column kernel
+
+__global__ void __launch_bounds__(256)
+gate_bwd_cols_kernel(const GateBwdArgs a) {
+  __shared__ float part[8][3][256 + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.y * 256 + lane * 8;
+  const int64_t r0 = ((int64_t)blockIdx.x * 8 + warp) * GATE_STRIP;
+  const float dgm = (a.dgate_mean != nullptr) ? a.dgate_mean[0] / ((float)a.rows * (float)a.d) : 0.0f;
+  float sg[8], sw[8], sb[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sg[i] = sw[i] = sb[i] = 0.0f;
+  if (col < a.d) {
+    const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
+    const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const int64_t r_end = r0 + GATE_STRIP < a.rows ? r0 + GATE_STRIP : a.rows;
+#pragma unroll 2
+    for (int64_t row = r0; row < r_end; ++row) {
       float dF[8], dS[8], zv[8], sv[8], gp[8], cv[8], dq[8], dz[8], dcd[8], dsd[8];
       ld8(a.dF + row * a.dF_ld + col, dF);
       ld8(a.dS + row * a.dS_ld + col, dS);
@@ -375,23 +380,18 @@ gate_update_bwd_kernel(const GateBwdArgs a) {
       ld8(a.s + row * a.s_ld + col, sv);
       ld8(a.g_pre + row * a.d + col, gp);
       ld8(a.c + row * a.c_ld + col, cv);
+      const float rstd = a.rstd_z[row], rstd_g = a.row_rstdg[row], dot_z = a.row_dotz[row];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float wr = a.w_r[col + i];
-        const float zh = zv[i] * rstd;
-        const float R = sigmoidf_(zh * wr);
-        const float g = sigmoidf_(gp[i]);
-        const float D = dF[i] - dS[i];
-        const float dgp = (D * cv[i] + dgm) * g * (1.0f - g);
-        const float dy = D * sv[i] * R * (1.0f - R);
-        const float dzv = rstd * (dy * wr - zh * dot_z);
-        dq[i] = dgp * rstd_g;
+        const GateElem e = gate_elem(dF[i], dS[i], zv[i], sv[i], gp[i], cv[i], wr[i], rstd, dgm);
+        const float dzv = rstd * (e.dy * wr[i] - e.zh * dot_z);
+        dq[i] = e.dgp * rstd_g;
         dz[i] = dzv;
-        dcd[i] = dF[i] * g + dS[i] * (1.0f - g);
-        dsd[i] = dF[i] * R + dS[i] * (1.0f - R);
-        colacc[col + i] += dgp;                 // this lane is the only writer of these columns
-        colacc[a.d + col + i] += dy * zh;
-        colacc[2 * a.d + col + i] += dzv;
+        dcd[i] = dF[i] * e.g + dS[i] * (1.0f - e.g);
+        dsd[i] = dF[i] * e.R + dS[i] * (1.0f - e.R);
+        sg[i] += e.dgp;
+        sw[i] = fmaf(e.dy, e.zh, sw[i]);
+        sb[i] += dzv;
       }
       st8(a.dq + row * a.d + col, dq);
       st8(a.dz + row * a.d + col, dz);
@@ -399,30 +399,37 @@ gate_update_bwd_kernel(const GateBwdArgs a) {
       st8(a.dsc + row * 2 * a.d + a.d + col, dcd);
     }
   }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    part[warp][0][lane * 8 + i] = sg[i];
+    part[warp][1][lane * 8 + i] = sw[i];
+    part[warp][2][lane * 8 + i] = sb[i];
+  }
   __syncthreads();
-  for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) {
-    float t = 0.0f;
-    for (int w = 0; w < wpb; ++w) t += colacc_all[(size_t)w * 3 * a.d + i];
-    float* dst = i < a.d ? a.db2g + i : (i < 2 * a.d ? a.dw_r + (i - a.d) : a.db2r + (i - 2 * a.d));
-    atomicAdd(dst, t);
+  const int c = blockIdx.y * 256 + threadIdx.x;
+  if (c < a.d) {
+    float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      t0 += part[w][0][threadIdx.x];
+      t1 += part[w][1][threadIdx.x];
+      t2 += part[w][2][threadIdx.x];
+    }
+    atomicAdd(a.db2g + c, t0);
+    atomicAdd(a.dw_r + c, t1);
+    atomicAdd(a.db2r + c, t2);
   }
 }
 
 const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update_bwd: d must be a multiple of 8";
-  int warps = 8;
-  while (warps > 1 && (size_t)warps * 3 * a.d * sizeof(float) > 100 * 1024) warps >>= 1;
-  const size_t smem = (size_t)warps * 3 * a.d * sizeof(float);
-  if (smem > 200 * 1024) return "gate_update_bwd: d too large for the column accumulators";
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(gate_update_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr = true;
-  }
-  const int64_t blocks = (a.rows + warps - 1) / warps;
-  const int grid = (int)(blocks < 148 * 2 ? blocks : 148 * 2);
-  gate_update_bwd_kernel<<<grid, warps * 32, smem, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_update_bwd launch failed";
+  if (!a.b2g_f32) return "gate_update_bwd: the gate bias must be fp32";
+  if (a.row_dotz == nullptr || a.row_rstdg == nullptr) return "gate_update_bwd: row scratch missing";
+  gate_bwd_rowstats_kernel<<<(unsigned)((a.rows + 7) / 8), 256, 0, st>>>(a);
+  if (cudaGetLastError() != cudaSuccess) return "gate_bwd_rowstats launch failed";
+  dim3 grid((unsigned)((a.rows + 8 * GATE_STRIP - 1) / (8 * GATE_STRIP)), (a.d + 255) / 256);
+  gate_bwd_cols_kernel<<<grid, 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_bwd_cols launch failed";
 }
 
 // =======================================================================================

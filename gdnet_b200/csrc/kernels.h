@@ -63,7 +63,7 @@ struct GateBwdArgs {
   const __nv_bfloat16* c;    // pitch c_ld
   const __nv_bfloat16* s;    // pitch s_ld
   const float* w_r;
-  const void* b2g;           // (d) gate W2 bias
+  const float* b2g;          // (d) gate W2 bias, fp32
   int b2g_f32;
   const float* rstd_z;       // (rows)
   const float* ssq_g;        // (rows, ssq_parts) partial sums of squares of silu(W1 c + b1)
@@ -74,6 +74,8 @@ struct GateBwdArgs {
   __nv_bfloat16* dz;         // (rows, d)
   __nv_bfloat16* dsc;        // (rows, 2d): [ds_dir | dc_dir]
   float* rowcoef;            // (rows)
+  float* row_dotz;           // (rows) scratch: mean_n(dzh*zh) per row
+  float* row_rstdg;          // (rows) scratch: rstd of the gate RMSNorm per row
   float* db2g;               // (d) accumulated
   float* dw_r;               // (d) accumulated
   float* db2r;               // (d) accumulated
