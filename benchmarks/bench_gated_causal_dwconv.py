@@ -44,7 +44,7 @@ def bench(B, T, d, k, hbm_gbs):
     n_sets = max(2, int(400e6 // (4 * unit)) + 1)
     mk = lambda: [torch.randn(B, T, d, device=dev, dtype=bf) for _ in range(n_sets)]
     x, s, gp, z, dF, dS = mk(), mk(), mk(), mk(), mk(), mk()
-    w = torch.randn(d, k, device=dev)
+    w = torch.randn(k, d, device=dev)      # the kernels read the taps transposed
     out = torch.empty(B, T, d, device=dev, dtype=bf)
     out2 = torch.empty_like(out)
     rows = []

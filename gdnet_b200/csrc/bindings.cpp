@@ -167,8 +167,8 @@ void gemm_fp8(const Tensor& a8, const Tensor& sa, const Tensor& b8, const Tensor
 void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 3 && out.dim() == 3, "dwconv: x and out must be (B, T, d)");
-  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(1);
-  TORCH_CHECK(w.dim() == 2 && w.size(0) == d && w.is_contiguous(), "dwconv: w must be (d, k) contiguous");
+  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv: taps must be (k, d) contiguous (transposed)");
   TORCH_CHECK(x.stride(0) == x.stride(1) * T && out.stride(0) == out.stride(1) * T, "dwconv: batch stride must be T rows");
   TORCH_CHECK(out.size(0) == B && out.size(1) == T && out.size(2) == d, "dwconv: out shape");
   if (halo.has_value()) TORCH_CHECK(halo->is_contiguous() && halo->size(0) == B && halo->size(1) == k - 1 && halo->size(2) == d, "dwconv: halo must be (B, k-1, d)");
@@ -182,7 +182,8 @@ void dwconv_bwd(const Tensor& dc, const Tensor& x, OptT halo, const Tensor& w, O
                 Tensor dw) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 3 && dc.dim() == 3 && dx.dim() == 3, "dwconv_bwd: tensors must be (B, T, d)");
-  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(1);
+  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv_bwd: taps must be (k, d) contiguous (transposed)");
   TORCH_CHECK(dx.is_contiguous() && dw.is_contiguous() && dw.size(0) == d && dw.size(1) == k, "dwconv_bwd: dx/dw layout");
   TORCH_CHECK(x.stride(0) == x.stride(1) * T && dc.stride(0) == dc.stride(1) * T, "dwconv_bwd: batch stride must be T rows");
   TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (dc.stride(1) * 2) % 16 == 0, "dwconv_bwd: rows must be 16-byte aligned");

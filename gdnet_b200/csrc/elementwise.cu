@@ -59,13 +59,14 @@ __device__ __forceinline__ void load_conv_row(const __nv_bfloat16* x, const __nv
 }
 
 // ---------------------------------------------------------------------------------------
-// point-wise formulation: one thread per output vector (8 channels of one time step). Every load
+// point-wise formulation: one thread per output vector (8 channels of one time step); the taps come
+// from a transposed table wt[k][d], so a warp reads them as contiguous vectors. Every load
 // is independent, so the kernels run at full occupancy with many loads in flight; the k-fold
 // re-read of neighbouring rows is served by L1/L2 (blocks cover consecutive time steps).
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
-                     const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int B, int T, int d, int k,
+                     const float* __restrict__ wt, __nv_bfloat16* __restrict__ out, int B, int T, int d, int k,
                      int64_t x_ld, int64_t out_ld) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
@@ -78,15 +79,18 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   for (int i = 0; i < k; ++i) {
     float in[8];
     load_conv_row<8>(x, halo, x_ld, T, k, b, t - (k - 1) + i, ch, d, in);
+    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch);
+    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch + 4);
+    const float tap[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-    for (int c = 0; c < 8; ++c) acc[c] = fmaf(w[(ch + c) * k + i], in[c], acc[c]);
+    for (int c = 0; c < 8; ++c) acc[c] = fmaf(tap[c], in[c], acc[c]);
   }
   store_bf16_vec<8>(out + row * out_ld + ch, acc);
 }
 
 // dx[t] = sum_j w[k-1-j] dc[t+j] for t in [t_lo, T), t_lo = -(k-1) when the halo gradient is wanted
 __global__ void __launch_bounds__(256)
-dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ w,
+dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ wt,
                     const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx,
                     __nv_bfloat16* __restrict__ dhalo, int B, int T, int d, int k, int64_t dc_ld) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -104,8 +108,11 @@ dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restric
     if (tt < 0 || tt >= T) continue;
     float g[8];
     load_bf16_vec<8>(dc + ((int64_t)b * T + tt) * dc_ld + ch, g);
+    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)(k - 1 - j) * d + ch);
+    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)(k - 1 - j) * d + ch + 4);
+    const float tap[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-    for (int c = 0; c < 8; ++c) acc[c] = fmaf(w[(ch + c) * k + (k - 1 - j)], g[c], acc[c]);
+    for (int c = 0; c < 8; ++c) acc[c] = fmaf(tap[c], g[c], acc[c]);
   }
   if (t >= 0) {
     if (dx_tail_add != nullptr && t >= T - (k - 1)) {

@@ -15,7 +15,7 @@ struct Status;
 struct ConvArgs {
   const __nv_bfloat16* x;     // (B, T, d), row pitch x_ld
   const __nv_bfloat16* halo;  // (B, k-1, d) or null (zeros)
-  const float* w;             // (d, k)
+  const float* w;             // taps transposed: (k, d)
   __nv_bfloat16* out;         // (B, T, d), row pitch out_ld
   int B, T, d, k;
   int64_t x_ld, out_ld;
@@ -25,7 +25,7 @@ struct ConvBwdArgs {
   const __nv_bfloat16* dc;    // (B, T, d), row pitch dc_ld
   const __nv_bfloat16* x;     // (B, T, d), row pitch x_ld
   const __nv_bfloat16* halo;  // (B, k-1, d) or null
-  const float* w;             // (d, k)
+  const float* w;             // taps transposed: (k, d)
   const __nv_bfloat16* dx_tail_add;  // (B, k-1, d) or null: halo gradient from the next shard
   __nv_bfloat16* dx;          // (B, T, d) contiguous
   __nv_bfloat16* dhalo;       // (B, k-1, d) or null

@@ -75,12 +75,27 @@ def f32(t: torch.Tensor) -> torch.Tensor:
     """fp32 contiguous copy of a small parameter, refreshed when the parameter changes."""
     if t.dtype == F32 and t.is_contiguous():
         return t.detach()
-    key = id(t)
+    key = (t.data_ptr(), t.numel(), t.dtype)      # views of a parameter are new objects every time: key on storage
     hit = _f32_cache.get(key)
     if hit is not None and hit[0] == (t._version, t.data_ptr(), _param_epoch):
         return hit[1]
     out = t.detach().to(F32).contiguous()
     _f32_cache[key] = ((t._version, t.data_ptr(), _param_epoch), out)
+    return out
+
+
+_taps_cache: dict[int, tuple] = {}
+
+
+def taps_t(w: torch.Tensor) -> torch.Tensor:
+    """Conv taps ``(d, k)`` as an fp32 ``(k, d)`` table (what the conv kernels read), cached per version."""
+    key = (w.data_ptr(), w.numel(), w.dtype)
+    stamp = (w._version, w.data_ptr(), _param_epoch)
+    hit = _taps_cache.get(key)
+    if hit is not None and hit[0] == stamp:
+        return hit[1]
+    out = w.detach().to(F32).t().contiguous()
+    _taps_cache[key] = (stamp, out)
     return out
 
 
@@ -95,7 +110,7 @@ _wq_cache: dict[int, QuantizedWeight] = {}
 
 
 def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
-    key = id(w)
+    key = (w.data_ptr(), w.numel(), w.dtype)
     hit = _wq_cache.get(key)
     stamp = (w._version, _param_epoch)
     if hit is not None and hit.version == stamp and hit.ptr == w.data_ptr():
@@ -117,6 +132,7 @@ def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
 def clear_caches() -> None:
     _f32_cache.clear()
     _wq_cache.clear()
+    _taps_cache.clear()
 
 
 # --------------------------------------------------------------------------------------
@@ -251,7 +267,7 @@ class _CausalDWConvFn(torch.autograd.Function):
     def forward(ctx, x, w, halo):
         xc = x if x.stride(-1) == 1 else x.contiguous()
         out = torch.empty(x.shape, dtype=BF16, device=x.device)
-        K.dwconv_fwd(xc, halo, f32(w), out)
+        K.dwconv_fwd(xc, halo, taps_t(w), out)
         ctx.save_for_backward(xc, w, halo if halo is not None else xc.new_empty(0))
         ctx.has_halo = halo is not None
         return out
@@ -264,7 +280,7 @@ class _CausalDWConvFn(torch.autograd.Function):
         dx = torch.empty(x.shape, dtype=BF16, device=x.device)
         dw = torch.zeros(w.shape, dtype=F32, device=x.device)
         dhalo = torch.empty_like(halo) if halo is not None else None
-        K.dwconv_bwd(dc, x, halo, f32(w), None, dx, dhalo, dw)
+        K.dwconv_bwd(dc, x, halo, taps_t(w), None, dx, dhalo, dw)
         return dx, _sink_vec(w, dw), dhalo
 
 
@@ -518,7 +534,7 @@ _w2w_cache: dict[tuple[int, int], tuple] = {}
 def _folded_w2(W2, w_norm):
     """``W2 * w_norm[None, :]`` in bf16, cached per version of both parameters: lets the RMSNorm
     in front of ``W2`` become a per-row scale in the GEMM epilogue."""
-    key = (id(W2), id(w_norm))
+    key = (W2.data_ptr(), w_norm.data_ptr(), W2.numel())
     hit = _w2w_cache.get(key)
     stamp = (W2._version, w_norm._version, W2.data_ptr(), _param_epoch)
     if hit is not None and hit[:3] == stamp[:3] and hit[4] == _param_epoch:
@@ -548,7 +564,7 @@ class _LayerStepFn(torch.autograd.Function):
         x = x if x.is_contiguous() else x.contiguous()
         s2 = s.reshape(M, d) if s.stride(-1) == 1 else s.contiguous().reshape(M, d)
         c3 = torch.empty(B, T, d, dtype=BF16, device=dev)
-        K.dwconv_fwd(x, halo, f32(conv_w), c3)
+        K.dwconv_fwd(x, halo, taps_t(conv_w), c3)
         c = c3.view(M, d)
 
         # recovery MLP: z = W2r silu(W1r [s ; c] + b1r) + b2r
@@ -672,7 +688,7 @@ class _LayerStepFn(torch.autograd.Function):
         dx = torch.empty(B, T, d, dtype=BF16, device=dev)
         dwc = torch.zeros(conv_w.shape, dtype=F32, device=dev)
         dhalo = torch.empty_like(halo) if halo is not None else None
-        K.dwconv_bwd(dsc.view(B, T, 2 * d)[:, :, d:], x, halo, f32(conv_w), None, dx, dhalo, dwc)
+        K.dwconv_bwd(dsc.view(B, T, 2 * d)[:, :, d:], x, halo, taps_t(conv_w), None, dx, dhalo, dwc)
         ds = dsc.view(B, T, 2 * d)[:, :, :d]
 
         g_gW2 = None if main2 else tgt2.to(gW2.dtype)
