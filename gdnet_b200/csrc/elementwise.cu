@@ -64,6 +64,7 @@ __device__ __forceinline__ void load_conv_row(const __nv_bfloat16* x, const __nv
 // is independent, so the kernels run at full occupancy with many loads in flight; the k-fold
 // re-read of neighbouring rows is served by L1/L2 (blocks cover consecutive time steps).
 // ---------------------------------------------------------------------------------------
+template <int KT>
 __global__ void __launch_bounds__(256)
 dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
                      const float* __restrict__ wt, __nv_bfloat16* __restrict__ out, int B, int T, int d, int k,
@@ -73,10 +74,12 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   const int64_t row = (int64_t)blockIdx.x * 8 + warp;      // 8 consecutive time steps per block
   if (ch >= d || row >= (int64_t)B * T) return;
   const int b = (int)(row / T), t = (int)(row % T);
+  if (KT > 0) k = KT;
   float acc[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
-  for (int i = 0; i < k; ++i) {
+#pragma unroll
+  for (int i = 0; i < (KT > 0 ? KT : k); ++i) {
     float in[8];
     load_conv_row<8>(x, halo, x_ld, T, k, b, t - (k - 1) + i, ch, d, in);
     const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch);
@@ -89,12 +92,14 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 }
 
 // dx[t] = sum_j w[k-1-j] dc[t+j] for t in [t_lo, T), t_lo = -(k-1) when the halo gradient is wanted
+template <int KT>
 __global__ void __launch_bounds__(256)
 dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ wt,
                     const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx,
                     __nv_bfloat16* __restrict__ dhalo, int B, int T, int d, int k, int64_t dc_ld) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
+  if (KT > 0) k = KT;
   const int t_lo = dhalo != nullptr ? -(k - 1) : 0;
   const int rows_per_b = T - t_lo;
   const int64_t r = (int64_t)blockIdx.x * 8 + warp;
@@ -103,11 +108,16 @@ dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restric
   float acc[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
-  for (int j = 0; j < k; ++j) {
+#pragma unroll
+  for (int j = 0; j < (KT > 0 ? KT : k); ++j) {
     const int tt = t + j;
-    if (tt < 0 || tt >= T) continue;
     float g[8];
-    load_bf16_vec<8>(dc + ((int64_t)b * T + tt) * dc_ld + ch, g);
+    if (tt >= 0 && tt < T) {
+      load_bf16_vec<8>(dc + ((int64_t)b * T + tt) * dc_ld + ch, g);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) g[c] = 0.0f;
+    }
     const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)(k - 1 - j) * d + ch);
     const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)(k - 1 - j) * d + ch + 4);
     const float tap[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
@@ -209,7 +219,8 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if (a.k < 1 || a.k > 16) return "dwconv: kernel width must be in [1, 16]";
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
   dim3 grid((unsigned)(((int64_t)a.B * a.T + 7) / 8), (a.d + 255) / 256);
-  dwconv_fwd_pt_kernel<<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
+  if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
+  else dwconv_fwd_pt_kernel<0><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
   return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
 }
 
@@ -218,7 +229,8 @@ const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
   const int rows_per_b = a.T + (a.dhalo != nullptr ? a.k - 1 : 0);
   dim3 grid((unsigned)(((int64_t)a.B * rows_per_b + 7) / 8), (a.d + 255) / 256);
-  dwconv_dx_pt_kernel<<<grid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
+  if (a.k == 4) dwconv_dx_pt_kernel<4><<<grid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
+  else dwconv_dx_pt_kernel<0><<<grid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
   if (cudaGetLastError() != cudaSuccess) return "dwconv_dx launch failed";
   if (a.k <= 4) return conv_dw_launch<4>(a, st);
   if (a.k <= 8) return conv_dw_launch<8>(a, st);

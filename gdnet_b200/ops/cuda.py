@@ -80,7 +80,8 @@ def f32(t: torch.Tensor) -> torch.Tensor:
     if hit is not None and hit[0] == (t._version, t.data_ptr(), _param_epoch):
         return hit[1]
     out = t.detach().to(F32).contiguous()
-    _f32_cache[key] = ((t._version, t.data_ptr(), _param_epoch), out)
+    # the entry keeps `t` alive, so its storage address cannot be handed to another tensor while cached
+    _f32_cache[key] = ((t._version, t.data_ptr(), _param_epoch), out, t)
     return out
 
 
@@ -95,7 +96,7 @@ def taps_t(w: torch.Tensor) -> torch.Tensor:
     if hit is not None and hit[0] == stamp:
         return hit[1]
     out = w.detach().to(F32).t().contiguous()
-    _taps_cache[key] = (stamp, out)
+    _taps_cache[key] = (stamp, out, w)
     return out
 
 
@@ -103,7 +104,7 @@ class QuantizedWeight:
     """e4m3 copies of a weight ``(N, K)`` with 128x128 block scales: ``q`` / ``s`` for the
     forward GEMM and ``qt`` / ``st`` (the transposed matrix ``(K, N)``) for the data gradient."""
 
-    __slots__ = ("q", "s", "qt", "st", "version", "ptr")
+    __slots__ = ("q", "s", "qt", "st", "version", "ptr", "source")
 
 
 _wq_cache: dict[int, QuantizedWeight] = {}
@@ -124,7 +125,7 @@ def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
         qw.qt = torch.empty(Kd, N, dtype=FP8, device=w.device)
         qw.st = torch.empty(kb, nb, dtype=F32, device=w.device)
     K.quant_tile(w.detach(), False, qw.q, qw.s, Q_BLOCK, qw.qt, qw.st, Q_BLOCK)
-    qw.version, qw.ptr = stamp, w.data_ptr()
+    qw.version, qw.ptr, qw.source = stamp, w.data_ptr(), w   # `source` pins the storage address
     _wq_cache[key] = qw
     return qw
 
@@ -133,6 +134,7 @@ def clear_caches() -> None:
     _f32_cache.clear()
     _wq_cache.clear()
     _taps_cache.clear()
+    _w2w_cache.clear()
 
 
 # --------------------------------------------------------------------------------------
@@ -541,7 +543,7 @@ def _folded_w2(W2, w_norm):
         return hit[3]
     out = hit[3] if hit is not None and hit[3].shape == W2.shape else torch.empty_like(W2, dtype=BF16)
     K.scale_cols(W2.detach(), f32(w_norm), out)
-    _w2w_cache[key] = (W2._version, w_norm._version, W2.data_ptr(), out, _param_epoch)
+    _w2w_cache[key] = (W2._version, w_norm._version, W2.data_ptr(), out, _param_epoch, W2, w_norm)
     return out
 
 

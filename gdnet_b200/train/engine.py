@@ -128,6 +128,10 @@ class TrainEngine(nn.Module):
             for g in self.groups:
                 g._sp.barrier()
         self.scalars = torch.zeros(2, dtype=torch.float32, device=dev)
+        if dev.type == "cuda":
+            from ..ops import cuda as cu
+
+            cu.clear_caches()     # cached copies made from the pre-flattening parameter storages
 
     # -- nn.Module plumbing -----------------------------------------------------------------
     def forward(self, *a, **kw):
