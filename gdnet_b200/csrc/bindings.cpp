@@ -138,7 +138,7 @@ void gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, Tensor ou
   const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
   TORCH_CHECK(K == Kb, "gemm: reduction sizes differ: ", K, " vs ", Kb);
   gd::GemmOperands op{bf16_ptr(a, "a"), bf16_ptr(b, "b"), a.stride(0), b.stride(0)};
-  gd::GemmShape g{(int)M, (int)N, (int)K, a_mn, b_mn, nullptr, nullptr, 0, 1};
+  gd::GemmShape g{(int)M, (int)N, (int)K, a_mn, b_mn, nullptr, nullptr, 0, 1, nullptr, nullptr};
   gd::GemmEpilogue e;
   fill_epilogue(e, out, accumulate, bias, row_scale, ssq_in, norm_dim, norm_eps, aux, aux_mode, rowcoef, pre_out, act,
                 ssq_out, M, N);
@@ -157,11 +157,29 @@ void gemm_fp8(const Tensor& a8, const Tensor& sa, const Tensor& b8, const Tensor
   TORCH_CHECK(sa.dim() == 2 && sa.size(0) == KB && sa.size(1) >= M && sa.stride(1) == 1, "sa must be (K/128, M)");
   TORCH_CHECK(sb.dim() == 2 && sb.size(0) == NB && sb.size(1) == KB && sb.is_contiguous(), "sb must be (N/128, K/128)");
   gd::GemmOperands op{fp8_mut(a8, "a8"), fp8_mut(b8, "b8"), a8.stride(0), b8.stride(0)};
-  gd::GemmShape g{(int)M, (int)N, (int)K, 0, 0, f32_ptr(sa, "sa"), f32_ptr(sb, "sb"), sa.stride(0), 1};
+  gd::GemmShape g{(int)M, (int)N, (int)K, 0, 0, f32_ptr(sa, "sa"), f32_ptr(sb, "sb"), sa.stride(0), 1, nullptr, nullptr};
   gd::GemmEpilogue e;
   std::optional<Tensor> none;
   fill_epilogue(e, out, accumulate, bias, row_scale, none, 0, 0.0, aux, aux_mode, none, pre_out, act, none, M, N);
   GD_LAUNCH(gd::launch_gemm_fp8(op, g, e, status_ptr(a8), stream_of(a8)));
+}
+
+// a8: (M,K) e4m3 with packed UE8M0 chunks pa (M/128, K/128, 512); b8: (N,K) with pb (N/128, K/128, 512).
+void gemm_fp8_mx(const Tensor& a8, const Tensor& pa, const Tensor& b8, const Tensor& pb, Tensor out, bool accumulate,
+                 OptT bias, OptT row_scale, OptT aux, int64_t aux_mode, OptT pre_out, int64_t act) {
+  c10::cuda::CUDAGuard guard(a8.device());
+  TORCH_CHECK(a8.dim() == 2 && b8.dim() == 2, "gemm operands must be 2-D");
+  const int64_t M = a8.size(0), K = a8.size(1), N = b8.size(0);
+  TORCH_CHECK(b8.size(1) == K, "gemm_fp8_mx: reduction sizes differ");
+  TORCH_CHECK(M % 128 == 0 && N % 128 == 0 && K % 128 == 0, "gemm_fp8_mx: M, N, K must be multiples of 128");
+  TORCH_CHECK(pa.is_contiguous() && pa.numel() == (M / 128) * (K / 128) * 512, "pa must hold M/128 * K/128 * 512 bytes");
+  TORCH_CHECK(pb.is_contiguous() && pb.numel() == (N / 128) * (K / 128) * 512, "pb must hold N/128 * K/128 * 512 bytes");
+  gd::GemmOperands op{fp8_mut(a8, "a8"), fp8_mut(b8, "b8"), a8.stride(0), b8.stride(0)};
+  gd::GemmShape g{(int)M, (int)N, (int)K, 0, 0, nullptr, nullptr, 0, 1, fp8_mut(pa, "pa"), fp8_mut(pb, "pb")};
+  gd::GemmEpilogue e;
+  std::optional<Tensor> none;
+  fill_epilogue(e, out, accumulate, bias, row_scale, none, 0, 0.0, aux, aux_mode, none, pre_out, act, none, M, N);
+  GD_LAUNCH(gd::launch_gemm_fp8_mx(op, g, e, status_ptr(a8), stream_of(a8)));
 }
 
 void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out) {
@@ -252,7 +270,7 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
 }
 
 void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t row_mode, OptT q_col, OptT s_col,
-                int64_t col_mode) {
+                int64_t col_mode, bool pow2, OptT p_row, OptT p_col) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 2, "quantise: x must be 2-D");
   gd::QuantArgs a{};
@@ -291,6 +309,18 @@ void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t 
       a.s_col_ld = s_col->stride(0);
     } else {
       TORCH_CHECK(col_mode == gd::QUANT_BLOCK && s_col->is_contiguous() && s_col->numel() == rb * cb, "quantise: s_col must be (cols/128, rows/128)");
+    }
+  }
+  a.pow2 = pow2;
+  if (p_row.has_value() || p_col.has_value()) {
+    TORCH_CHECK(pow2 && a.rows % 128 == 0 && a.cols % 128 == 0, "packed scales need pow2 scales and 128-multiples");
+    if (p_row.has_value()) {
+      TORCH_CHECK(q_row.has_value() && p_row->is_contiguous() && p_row->numel() == rb * cb * 512, "p_row must hold rows/128 * cols/128 * 512 bytes");
+      a.p_row = fp8_mut(*p_row, "p_row");
+    }
+    if (p_col.has_value()) {
+      TORCH_CHECK(q_col.has_value() && p_col->is_contiguous() && p_col->numel() == rb * cb * 512, "p_col must hold cols/128 * rows/128 * 512 bytes");
+      a.p_col = fp8_mut(*p_col, "p_col");
     }
   }
   GD_LAUNCH(gd::launch_quant_tile(a, stream_of(x)));
@@ -449,13 +479,14 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("kernel_status(Tensor like) -> Tensor", &kernel_status);
   m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? ssq_in, int norm_dim, float norm_eps, Tensor? aux, int aux_mode, Tensor? rowcoef, Tensor(b!)? pre_out, int act, Tensor(c!)? ssq_out) -> ()", &gemm_bf16);
   m.def("gemm_fp8(Tensor a8, Tensor sa, Tensor b8, Tensor sb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8);
+  m.def("gemm_fp8_mx(Tensor a8, Tensor pa, Tensor b8, Tensor pb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8_mx);
   m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out) -> ()", &dwconv_fwd);
   m.def("dwconv_bwd(Tensor dc, Tensor x, Tensor? halo, Tensor w, Tensor? tail_add, Tensor(a!) dx, Tensor(b!)? dhalo, Tensor(c!) dw) -> ()", &dwconv_bwd);
   m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r) -> ()", &gate_update_fwd);
   m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r) -> ()", &gate_update_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!)? rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw) -> ()", &rmsnorm_bwd);
-  m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode) -> ()", &quant_tile);
+  m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode, bool pow2=False, Tensor(e!)? p_row=None, Tensor(f!)? p_col=None) -> ()", &quant_tile);
   m.def("quant_tensor(Tensor x, Tensor scale, Tensor(a!) q_row, Tensor(b!)? q_col, Tensor(c!)? amax) -> ()", &quant_tensor);
   m.def("colsum(Tensor x, Tensor(a!) out) -> ()", &colsum);
   m.def("scale_cols(Tensor w, Tensor colw, Tensor(a!) out) -> ()", &scale_cols);

@@ -164,6 +164,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// Plain (untiled) bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned,
+// size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // tcgen05: TMEM allocation, MMA, commit, loads
 // ---------------------------------------------------------------------------------------
@@ -205,6 +214,38 @@ __device__ __forceinline__ void mma_fp8(uint32_t d_tmem, uint64_t adesc, uint64_
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// Block-scaled e4m3 MMA: every 32-deep K step of A (rows) and B (rows) is multiplied by a UE8M0
+// scale that the tensor core reads from TMEM (sfa/sfb), so block scaling costs no extra pass.
+__device__ __forceinline__ void mma_mxfp8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// Copy 32 rows x 16 bytes of scale factors from shared memory into 4 TMEM columns, replicated into
+// all four 32-lane quarters (one 512-byte packed chunk = 128 rows x 4 K steps).
+__device__ __forceinline__ void tmem_cp_scales(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// Shared-memory descriptor without swizzle: rows of 16 bytes, 8-row groups sbo_bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// Instruction descriptor of the block-scaled MMA (e4m3 x e4m3, UE8M0 scales, K-major operands).
+__host__ __device__ constexpr uint32_t make_instr_desc_mx(uint32_t M, uint32_t N, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return (b_sf_id << 4) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (a_sf_id << 29);
 }
 
 // The mbarrier receives one arrival once every MMA issued so far by this thread is done.

@@ -71,9 +71,9 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
                      int64_t x_ld, int64_t out_ld) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
-  const int64_t row = (int64_t)blockIdx.x * 8 + warp;      // 8 consecutive time steps per block
-  if (ch >= d || row >= (int64_t)B * T) return;
-  const int b = (int)(row / T), t = (int)(row % T);
+  const int row = blockIdx.x * 8 + warp;      // 8 consecutive time steps per block (B*T < 2^31, checked by the launcher)
+  if (ch >= d || row >= B * T) return;
+  const int b = row / T, t = row - b * T;
   if (KT > 0) k = KT;
   float acc[8];
 #pragma unroll
@@ -88,7 +88,7 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 #pragma unroll
     for (int c = 0; c < 8; ++c) acc[c] = fmaf(tap[c], in[c], acc[c]);
   }
-  store_bf16_vec<8>(out + row * out_ld + ch, acc);
+  store_bf16_vec<8>(out + (int64_t)row * out_ld + ch, acc);
 }
 
 // dx[t] = sum_j w[k-1-j] dc[t+j] for t in [t_lo, T), t_lo = -(k-1) when the halo gradient is wanted
@@ -102,9 +102,9 @@ dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restric
   if (KT > 0) k = KT;
   const int t_lo = dhalo != nullptr ? -(k - 1) : 0;
   const int rows_per_b = T - t_lo;
-  const int64_t r = (int64_t)blockIdx.x * 8 + warp;
-  if (ch >= d || r >= (int64_t)B * rows_per_b) return;
-  const int b = (int)(r / rows_per_b), t = (int)(r % rows_per_b) + t_lo;
+  const int r = blockIdx.x * 8 + warp;
+  if (ch >= d || r >= B * rows_per_b) return;
+  const int b = r / rows_per_b, t = r - b * rows_per_b + t_lo;
   float acc[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
@@ -218,6 +218,7 @@ static const char* conv_dw_launch(const ConvBwdArgs& a, cudaStream_t st) {
 const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if (a.k < 1 || a.k > 16) return "dwconv: kernel width must be in [1, 16]";
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
+  if ((int64_t)a.B * (a.T + 16) >= (1ll << 31)) return "dwconv: B*T must be below 2^31";
   dim3 grid((unsigned)(((int64_t)a.B * a.T + 7) / 8), (a.d + 255) / 256);
   if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
   else dwconv_fwd_pt_kernel<0><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
@@ -227,6 +228,7 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
 const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   if (a.k < 1 || a.k > 16) return "dwconv: kernel width must be in [1, 16]";
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
+  if ((int64_t)a.B * (a.T + 16) >= (1ll << 31)) return "dwconv: B*T must be below 2^31";
   const int rows_per_b = a.T + (a.dhalo != nullptr ? a.k - 1 : 0);
   dim3 grid((unsigned)(((int64_t)a.B * rows_per_b + 7) / 8), (a.d + 255) / 256);
   if (a.k == 4) dwconv_dx_pt_kernel<4><<<grid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
@@ -540,6 +542,33 @@ const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
 // =======================================================================================
 // FP8 (e4m3) block quantisation
 // =======================================================================================
+// Scale of a block with the given amax: amax/448, or, for the hardware block-scaled MMA, the next
+// power of two (UE8M0: the tensor core multiplies by 2^(e-127)); 1 for an all-zero block.
+__device__ __forceinline__ float block_scale(float amax, int pow2) {
+  if (!(amax > 0.0f)) return 1.0f;
+  const float s = amax / 448.0f;
+  if (!pow2) return s;
+  int e;
+  const float m = frexpf(s, &e);            // s = m * 2^e, m in [0.5, 1)
+  return ldexpf(1.0f, m == 0.5f ? e - 1 : e);
+}
+
+// UE8M0 byte of a power-of-two scale, replicated into the four bytes of a word: the four K steps of
+// a 128-deep block share the scale.
+__device__ __forceinline__ uint32_t ue8m0_word(float pow2_scale) {
+  int e;
+  frexpf(pow2_scale, &e);                   // pow2_scale = 0.5 * 2^e
+  int b = e - 1 + 127;
+  b = b < 0 ? 0 : (b > 254 ? 254 : b);
+  return (uint32_t)b * 0x01010101u;
+}
+
+// Packed scale chunks for tcgen05 block-scaled MMA: 512 bytes per (128 rows, 128-deep K block);
+// the four scale bytes of row r sit at (r % 32) * 16 + (r / 32) * 4.
+__device__ __forceinline__ void store_packed_scale(uint8_t* packed, int64_t chunk, int row_in_128, uint32_t word) {
+  *reinterpret_cast<uint32_t*>(packed + chunk * 512 + (row_in_128 & 31) * 16 + (row_in_128 >> 5) * 4) = word;
+}
+
 // One block quantises a 128 x 128 tile of a bf16 matrix x[rows][cols] (row pitch x_ld),
 // optionally through silu. Two independent outputs, each optional:
 //   row-major  q_row[r][c]  with scales per (row, 128-col block)   [ROWS]  or per tile [BLOCK]
@@ -593,14 +622,18 @@ quant_tile_kernel(const QuantArgs a) {
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
     if (a.q_row != nullptr && a.row_mode == QUANT_ROWS) {
-      const float sc = rmax > 0.0f ? rmax / 448.0f : 1.0f;
+      const float sc = block_scale(rmax, a.pow2);
       const float inv = 1.0f / sc;
       if (r < a.rows && c < a.cols) {
         uint8_t q[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[p][i] * inv);
         *reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c) = *reinterpret_cast<uint2*>(q);
-        if ((tid & 15) == 0) a.s_row[(int64_t)blockIdx.x * a.s_row_ld + r] = sc;
+        if ((tid & 15) == 0) {
+          a.s_row[(int64_t)blockIdx.x * a.s_row_ld + r] = sc;
+          if (a.p_row != nullptr)
+            store_packed_scale(a.p_row, (int64_t)blockIdx.y * gridDim.x + blockIdx.x, (int)(r - r0), ue8m0_word(sc));
+        }
       }
     }
   }
@@ -621,7 +654,7 @@ quant_tile_kernel(const QuantArgs a) {
     if (tid == 0) s_tilemax = m;
   }
   __syncthreads();
-  const float tile_scale = s_tilemax > 0.0f ? s_tilemax / 448.0f : 1.0f;
+  const float tile_scale = block_scale(s_tilemax, a.pow2);
 
   if (a.q_row != nullptr && a.row_mode == QUANT_BLOCK) {
     const float inv = 1.0f / tile_scale;
@@ -637,6 +670,8 @@ quant_tile_kernel(const QuantArgs a) {
       }
     }
     if (tid == 0) a.s_row[(int64_t)blockIdx.y * n_cb + blockIdx.x] = tile_scale;
+    if (a.p_row != nullptr && tid < 128)
+      reinterpret_cast<uint32_t*>(a.p_row + ((int64_t)blockIdx.y * n_cb + blockIdx.x) * 512)[tid] = ue8m0_word(tile_scale);
   }
 
   if (a.q_col != nullptr) {
@@ -647,7 +682,7 @@ quant_tile_kernel(const QuantArgs a) {
     __syncthreads();
     const int oc = tid >> 1, half = tid & 1;
     const float cm = s_scale_col[oc];
-    const float sc = a.col_mode == QUANT_COLS ? (cm > 0.0f ? cm / 448.0f : 1.0f) : tile_scale;
+    const float sc = a.col_mode == QUANT_COLS ? block_scale(cm, a.pow2) : tile_scale;
     const float inv = 1.0f / sc;
     const int c = c0 + oc;
     const int64_t rbase = r0 + half * 64;
@@ -663,11 +698,15 @@ quant_tile_kernel(const QuantArgs a) {
     }
     if (a.col_mode == QUANT_COLS) {
       if (tid < 128 && c0 + tid < a.cols) {
-        const float cm = s_scale_col[tid];
-        a.s_col[(int64_t)blockIdx.y * a.s_col_ld + c0 + tid] = cm > 0.0f ? cm / 448.0f : 1.0f;
+        const float sc_c = block_scale(s_scale_col[tid], a.pow2);
+        a.s_col[(int64_t)blockIdx.y * a.s_col_ld + c0 + tid] = sc_c;
+        if (a.p_col != nullptr)
+          store_packed_scale(a.p_col, (int64_t)blockIdx.x * n_rb + blockIdx.y, tid, ue8m0_word(sc_c));
       }
-    } else if (tid == 0) {
-      a.s_col[(int64_t)blockIdx.x * n_rb + blockIdx.y] = tile_scale;
+    } else {
+      if (tid == 0) a.s_col[(int64_t)blockIdx.x * n_rb + blockIdx.y] = tile_scale;
+      if (a.p_col != nullptr && tid < 128)
+        reinterpret_cast<uint32_t*>(a.p_col + ((int64_t)blockIdx.x * n_rb + blockIdx.y) * 512)[tid] = ue8m0_word(tile_scale);
     }
   }
 }
@@ -692,14 +731,18 @@ quant_rows_kernel(const QuantArgs a) {
   for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  const float sc = m > 0.0f ? m / 448.0f : 1.0f;
+  const float sc = block_scale(m, a.pow2);
   const float inv = 1.0f / sc;
   uint8_t q[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[i] * inv);
   if (!live) return;
   *reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c) = *reinterpret_cast<uint2*>(q);
-  if ((threadIdx.x & 15) == 0) a.s_row[(int64_t)(c >> 7) * a.s_row_ld + r] = sc;
+  if ((threadIdx.x & 15) == 0) {
+    a.s_row[(int64_t)(c >> 7) * a.s_row_ld + r] = sc;
+    if (a.p_row != nullptr)
+      store_packed_scale(a.p_row, (r >> 7) * (int64_t)(a.cols >> 7) + (c >> 7), (int)(r & 127), ue8m0_word(sc));
+  }
 }
 
 const char* launch_quant_tile(const QuantArgs& a, cudaStream_t st) {

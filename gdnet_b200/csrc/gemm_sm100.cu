@@ -560,6 +560,164 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------
+// hardware block-scaled FP8 kernel (UE8M0 scales applied by the tensor core)
+// ---------------------------------------------------------------------------------------
+// Same pipeline as the bf16 kernel (whole-K accumulation in TMEM, two accumulator stages). Each stage
+// also carries the two 512-byte packed scale chunks of its K block; the MMA thread copies them into
+// TMEM (tcgen05.cp) in front of the four MMAs that use them. Scales must be powers of two; with 1x128
+// activation and 128x128 weight blocks the four K steps of a stage share their scale bytes.
+constexpr int MX_BN = 128;
+constexpr int MX_BK = 128;
+constexpr int MX_STAGES = 6;
+constexpr int MX_ACC = 2;
+constexpr int MX_A_BYTES = BM * STAGE_ROW_BYTES;
+constexpr int MX_B_BYTES = MX_BN * STAGE_ROW_BYTES;
+constexpr int MX_SF_BYTES = 512;
+constexpr int MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 2 * MX_SF_BYTES;   // 33 KB, a multiple of 1024
+constexpr int MX_TMEM_COLS = 512;
+constexpr int MX_SF_COL0 = MX_ACC * MX_BN;                                   // scale columns follow the accumulators
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmShape g, const GemmEpilogue e, Status* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + MX_STAGES * MX_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  pipe_setup<MX_STAGES, MX_ACC>(bars, warp, lane, MX_TMEM_COLS, &tmap_a, &tmap_b);
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int n_tiles_n = (g.N + MX_BN - 1) / MX_BN;
+  const int n_tiles_m = (g.M + BM - 1) / BM;
+  const int n_tiles = n_tiles_m * n_tiles_n;
+  const int kblocks = (g.K + MX_BK - 1) / MX_BK;
+  const int kb_per = (kblocks + g.splits - 1) / g.splits;
+  const int n_work = n_tiles * g.splits;
+  const uint32_t smem0 = smem_u32(smem);
+  const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
+  const uint32_t tfull0 = smem_u32(&bars->tmem_full[0]), tempty0 = smem_u32(&bars->tmem_empty[0]);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; work < n_work && ok; work += gridDim.x) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+        int mb_, nb_;
+        tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+        const int m0 = mb_ * BM, n0 = nb_ * MX_BN;
+        const uint8_t* sfa = g.sfa_packed + ((size_t)mb_ * kblocks + kb0) * MX_SF_BYTES;
+        const uint8_t* sfb = g.sfb_packed + ((size_t)nb_ * kblocks + kb0) * MX_SF_BYTES;
+        int kx = kb0 * MX_BK;
+        for (int kb = kb0; kb < kb1; ++kb, kx += MX_BK, sfa += MX_SF_BYTES, sfb += MX_SF_BYTES) {
+          if (!wait_fast(empty0 + 8 * s, ph ^ 1)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 50, s);
+            ok = false;
+            break;
+          }
+          const uint32_t full = full0 + 8 * s;
+          const uint32_t a_dst = smem0 + s * MX_STAGE_BYTES;
+          mbar_arrive_expect_tx(full, MX_STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, full, kx, m0);
+          tma_load_2d(a_dst + MX_A_BYTES, &tmap_b, full, kx, n0);
+          bulk_load(a_dst + MX_A_BYTES + MX_B_BYTES, sfa, MX_SF_BYTES, full);
+          bulk_load(a_dst + MX_A_BYTES + MX_B_BYTES + MX_SF_BYTES, sfb, MX_SF_BYTES, full);
+          if (++s == MX_STAGES) { s = 0; ph ^= 1; }
+        }
+        if (aborted(bars)) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc_mx(BM, MX_BN, 0, 0);
+      const uint64_t a_tmpl = make_smem_desc(smem0, 16, 1024), b_tmpl = make_smem_desc(smem0 + MX_A_BYTES, 16, 1024);
+      const uint64_t sfa_tmpl = make_smem_desc_noswizzle(smem0 + MX_A_BYTES + MX_B_BYTES, 16, 128);
+      const uint32_t a_hi = (uint32_t)(a_tmpl >> 32), a_lo0 = (uint32_t)a_tmpl;
+      const uint32_t b_hi = (uint32_t)(b_tmpl >> 32), b_lo0 = (uint32_t)b_tmpl;
+      const uint32_t sf_hi = (uint32_t)(sfa_tmpl >> 32), sf_lo0 = (uint32_t)sfa_tmpl;
+      int s = 0, acc = 0, slot = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; work < n_work && ok; work += gridDim.x) {
+        const int nkb = min(kblocks, (work / n_tiles) * kb_per + kb_per) - (work / n_tiles) * kb_per;
+        if (!wait_fast(tempty0 + 8 * acc, acc_ph ^ 1)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 51, acc);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * MX_BN;
+        uint32_t accumulate = 0;
+        for (int i = 0; i < nkb; ++i) {
+          if (!wait_fast(full0 + 8 * s, ph)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 52, s);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t off = s * (MX_STAGE_BYTES >> 4);
+          const uint32_t sfa_t = tmem_base + MX_SF_COL0 + slot * 8, sfb_t = sfa_t + 4;
+          tmem_cp_scales(sfa_t, desc_at(sf_hi, sf_lo0 + off));
+          tmem_cp_scales(sfb_t, desc_at(sf_hi, sf_lo0 + off + (MX_SF_BYTES >> 4)));
+#pragma unroll
+          for (int k = 0; k < MX_BK / 32; ++k) {
+            mma_mxfp8(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2), idesc, accumulate,
+                      sfa_t, sfb_t);
+            accumulate = 1;
+          }
+          mma_commit(empty0 + 8 * s);
+          slot ^= 1;
+          if (++s == MX_STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok || aborted(bars)) break;
+        mma_commit(tfull0 + 8 * acc);
+        if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int col_half = ew >> 2;        // which 64 of the tile's 128 columns
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
+      const int tile = work % n_tiles;
+      int mb_, nb_;
+      tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+      const int m0 = mb_ * BM, n0 = nb_ * MX_BN;
+      const int m = m0 + quarter * 32 + lane;
+      const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
+      const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
+      if (!mbar_wait_warp(tfull0 + 8 * acc, acc_ph)) {
+        raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 53, acc);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * MX_BN + col_half * 64;
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(t_row, r0);
+      tmem_ld_32x32(t_row + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+      float ssq = epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 64, rs, rc, v);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+      ssq += epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 64 + 32, rs, rc, v);
+      if (e.ssq_out != nullptr && m < g.M)
+        e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
+      if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+  pipe_teardown(bars, warp, MX_TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -674,6 +832,33 @@ const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const Ge
   const int grid = work < sm_count() ? work : sm_count();
   gemm_fp8_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, gs, es, status);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_kernel launch failed";
+}
+
+const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
+                               cudaStream_t stream) {
+  if (g.K % 128 != 0 || g.N % 128 != 0 || g.M % 128 != 0) return "hardware-scaled fp8 GEMM needs M, N, K % 128 == 0";
+  if (g.sfa_packed == nullptr || g.sfb_packed == nullptr) return "hardware-scaled fp8 GEMM needs packed scales";
+  CUtensorMap ta, tb;
+  const char* err = make_tensor_map_2d(&ta, op.a, 1, g.M, g.K, op.a_ld, BM);
+  if (err) return err;
+  err = make_tensor_map_2d(&tb, op.b, 1, g.N, g.K, op.b_ld, MX_BN);
+  if (err) return err;
+  static bool attr_set = false;
+  const int smem = MX_STAGES * MX_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_fp8_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return "cudaFuncSetAttribute(gemm_fp8_mx_kernel) failed";
+    attr_set = true;
+  }
+  const int tiles = (g.M / BM) * (g.N / MX_BN);
+  GemmShape gs = g;
+  GemmEpilogue es = e;
+  gs.splits = pick_splits(tiles, g.K / MX_BK, e);
+  es.atomic = gs.splits > 1;
+  const int work = tiles * gs.splits;
+  const int grid = work < sm_count() ? work : sm_count();
+  gemm_fp8_mx_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, gs, es, status);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_mx_kernel launch failed";
 }
 
 }  // namespace gd

@@ -32,6 +32,8 @@ struct GemmShape {
   const float* sb;  // fp8: scales of B, sb[(n / 128) * ceil(K/128) + kb]
   int64_t sa_ld;
   int splits;       // split-K shares (set by the launcher)
+  const uint8_t* sfa_packed;  // hardware-scaled fp8: UE8M0 chunks of A, (M/128, K/128, 512) bytes
+  const uint8_t* sfb_packed;  // hardware-scaled fp8: UE8M0 chunks of B, (N/128, K/128, 512) bytes
 };
 
 // Applied in this order to the fp32 accumulator of element (m, n):
@@ -61,6 +63,8 @@ struct GemmEpilogue {
 
 const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
                              cudaStream_t stream);
+const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
+                               cudaStream_t stream);
 const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
                             cudaStream_t stream);
 

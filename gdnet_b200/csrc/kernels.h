@@ -111,6 +111,9 @@ struct QuantArgs {
   float* s_col;
   int64_t s_col_ld;
   int col_mode;            // QUANT_COLS or QUANT_BLOCK
+  int pow2;                // scales rounded up to powers of two (needed by the hardware block-scaled GEMM)
+  uint8_t* p_row;          // packed UE8M0 chunks for q_row, (rows/128, cols/128, 512) bytes, or null
+  uint8_t* p_col;          // packed UE8M0 chunks for q_col, (cols/128, rows/128, 512) bytes, or null
 };
 
 const char* launch_quant_tile(const QuantArgs& a, cudaStream_t st);

@@ -167,6 +167,17 @@ def gemm_fp8(a8, sa, b8, sb, *, out=None, out_dtype=BF16, accumulate=False, bias
     return out
 
 
+def gemm_fp8_mx(a8, pa, b8, pb, *, out=None, out_dtype=BF16, accumulate=False, bias=None, row_scale=None, aux=None,
+                aux_mode=0, pre_out=None, act=ACT_NONE):
+    """Hardware block-scaled e4m3 GEMM: power-of-two scales as packed UE8M0 chunks, ``pa (M/128, K/128, 512)``
+    and ``pb (N/128, K/128, 512)`` bytes, applied by the tensor core (no promotion pass)."""
+    M, N = a8.shape[0], b8.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a8.device)
+    K.gemm_fp8_mx(a8, pa, b8, pb, out, accumulate, bias, row_scale, aux, aux_mode, pre_out, act)
+    return out
+
+
 def gemm_ok_bf16(M: int, N: int, Kd: int) -> bool:
     return Kd % 8 == 0 and N % 32 == 0 and M % 8 == 0
 
@@ -178,15 +189,21 @@ def gemm_ok_fp8(M: int, N: int, Kd: int) -> bool:
 # --------------------------------------------------------------------------------------
 # quantisers
 # --------------------------------------------------------------------------------------
-def quantize_rows(x, pre_silu=False, q=None, s=None):
-    """1x128 blocks along the last dim: ``(q (M,K) e4m3, s (K/128, M) fp32)``."""
+def quantize_rows(x, pre_silu=False, q=None, s=None, pow2=False, packed=None):
+    """1x128 blocks along the last dim: ``(q (M,K) e4m3, s (K/128, M) fp32)``. With ``pow2`` the scales
+    are powers of two and ``packed`` (uint8 ``(M/128, K/128, 512)``) receives the UE8M0 chunks."""
     M, Kd = x.shape
     if q is None:
         q = torch.empty(M, Kd, dtype=FP8, device=x.device)
     if s is None:
         s = torch.empty((Kd + 127) // 128, M, dtype=F32, device=x.device)
-    K.quant_tile(x, pre_silu, q, s, Q_ROWS, None, None, Q_BLOCK)
+    K.quant_tile(x, pre_silu, q, s, Q_ROWS, None, None, Q_BLOCK, pow2, packed, None)
     return q, s
+
+
+def packed_buffer(rows: int, cols: int, device) -> torch.Tensor:
+    """Uninitialised buffer for the UE8M0 chunks of a ``(rows, cols)`` operand."""
+    return torch.empty(rows // 128, cols // 128, 512, dtype=torch.uint8, device=device)
 
 
 def quantize_transposed(x, mode, pre_silu=False):

@@ -171,7 +171,16 @@ def _pad_to(x: torch.Tensor, dim: int, mult: int) -> torch.Tensor:
     return torch.cat([x, x.new_zeros(shape)], dim=dim)
 
 
-def quantize_1x128(x: torch.Tensor):
+def _block_scale(amax: torch.Tensor, pow2: bool) -> torch.Tensor:
+    """``amax/448`` per block (1 for an all-zero block); with ``pow2`` rounded up to a power of two,
+    the form the tensor core's UE8M0 block scaling needs."""
+    s = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    if pow2:
+        s = torch.exp2(torch.ceil(torch.log2(s)))
+    return s
+
+
+def quantize_1x128(x: torch.Tensor, pow2: bool = False):
     """Row-wise blocks of 128 along the last dim.
 
     Returns ``(q (M,K) e4m3, s (M, ceil(K/128)) fp32)`` with ``x ~= q * s`` and
@@ -180,21 +189,42 @@ def quantize_1x128(x: torch.Tensor):
     M, K = x.shape
     xp = _pad_to(x.float(), 1, QBLOCK).view(M, -1, QBLOCK)
     amax = xp.abs().amax(dim=-1)
-    s = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    s = _block_scale(amax, pow2)
     q = (xp / s.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(FP8_DTYPE)
     return q.view(M, -1)[:, :K].contiguous(), s
 
 
-def quantize_128x128(w: torch.Tensor):
+def quantize_128x128(w: torch.Tensor, pow2: bool = False):
     """Square 128x128 blocks. Returns ``(q (N,K) e4m3, s (ceil(N/128), ceil(K/128)))``."""
     N, K = w.shape
     wp = _pad_to(_pad_to(w.float(), 0, QBLOCK), 1, QBLOCK)
     nb, kb = wp.shape[0] // QBLOCK, wp.shape[1] // QBLOCK
     blocks = wp.view(nb, QBLOCK, kb, QBLOCK)
     amax = blocks.abs().amax(dim=(1, 3))
-    s = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    s = _block_scale(amax, pow2)
     q = (blocks / s[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(FP8_DTYPE)
     return q.view(wp.shape)[:N, :K].contiguous(), s
+
+
+def pack_ue8m0_rows(s: torch.Tensor) -> torch.Tensor:
+    """Pack power-of-two row scales ``s (M, KB)`` (M a multiple of 128) into the 512-byte chunks the
+    block-scaled tensor-core MMA reads: chunk ``(m // 128, kb)``, the four bytes of row ``r = m % 128``
+    at ``(r % 32) * 16 + (r // 32) * 4``."""
+    M, KB = s.shape
+    e = (torch.log2(s.float()).round() + 127).clamp(0, 254).to(torch.uint8)          # (M, KB)
+    out = torch.zeros(M // 128, KB, 512, dtype=torch.uint8, device=s.device)
+    r = torch.arange(128, device=s.device)
+    pos = (r % 32) * 16 + (r // 32) * 4
+    blocks = e.view(M // 128, 128, KB).permute(0, 2, 1)                                # (MB, KB, 128)
+    for j in range(4):
+        out[:, :, pos + j] = blocks
+    return out
+
+
+def pack_ue8m0_blocks(s: torch.Tensor) -> torch.Tensor:
+    """Pack 128x128 block scales ``s (NB, KB)`` into constant-filled 512-byte chunks."""
+    e = (torch.log2(s.float()).round() + 127).clamp(0, 254).to(torch.uint8)
+    return e.unsqueeze(-1).expand(*s.shape, 512).contiguous()
 
 
 def dequantize_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:

@@ -181,3 +181,61 @@ def test_quantize_per_tensor():
     assert (q.view(torch.uint8) != want.view(torch.uint8)).float().mean() < 1e-3
     assert torch.equal(qc.view(torch.uint8), q.view(torch.uint8).t())
     assert torch.allclose(amax, x.float().abs().max())
+
+
+# ---------------------------------------------------------------------------------------
+# hardware block-scaled FP8 GEMM (UE8M0 scales applied by the tensor core)
+# ---------------------------------------------------------------------------------------
+def _mx_operands(M, N, K, vary_rows=True):
+    a = torch.randn(M, K, device=DEV)
+    if vary_rows:   # very different magnitudes per row and per K block, so a wrong scale mapping is visible
+        a = a * torch.exp2(torch.randint(-6, 7, (M, K // 128), device=DEV).float()).repeat_interleave(128, dim=1)
+    b = torch.randn(N, K, device=DEV) * 0.2
+    if vary_rows:
+        b = b * torch.exp2(torch.randint(-3, 4, (N // 128, K // 128), device=DEV).float()).repeat_interleave(
+            128, dim=0).repeat_interleave(128, dim=1)
+    a8, sa = ref.quantize_1x128(a, pow2=True)
+    b8, sb = ref.quantize_128x128(b, pow2=True)
+    return a8, sa, b8, sb
+
+
+@pytest.mark.parametrize("vary", [False, True])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (4096, 1024, 2048)])
+def test_gemm_fp8_mx_matches_oracle(M, N, K, vary):
+    cu = _cu()
+    a8, sa, b8, sb = _mx_operands(M, N, K, vary)
+    want = ref.fp8_gemm_blockscaled(a8, sa, b8, sb, out_dtype=torch.float32)
+    out = cu.gemm_fp8_mx(a8, ref.pack_ue8m0_rows(sa), b8, ref.pack_ue8m0_blocks(sb), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    _status_clean(a8)
+    _close(out, want, 1e-2 * float(want.abs().max()) * 1e-2 + 1e-3, 2e-3, f"mx gemm {M}x{N}x{K} vary={vary}")
+
+
+def test_quantizer_pow2_and_packed_chunks():
+    cu = _cu()
+    x = (torch.randn(256, 384, device=DEV) * torch.exp2(torch.randint(-4, 5, (256, 1), device=DEV).float())).bfloat16()
+    packed = cu.packed_buffer(256, 384, DEV)
+    q, s = cu.quantize_rows(x, pow2=True, packed=packed)
+    q_ref, s_ref = ref.quantize_1x128(x.float(), pow2=True)
+    _close(s.t(), s_ref, 0, 1e-6, "pow2 row scales")
+    assert torch.equal(packed, ref.pack_ue8m0_rows(s_ref)), "packed UE8M0 chunks differ"
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    # weights: both layouts, constant-filled chunks
+    w = torch.randn(256, 384, device=DEV).bfloat16()
+    wq = torch.empty(256, 384, dtype=torch.float8_e4m3fn, device=DEV)
+    ws = torch.empty(2, 3, device=DEV)
+    wt = torch.empty(384, 256, dtype=torch.float8_e4m3fn, device=DEV)
+    wts = torch.empty(3, 2, device=DEV)
+    pw, pwt = cu.packed_buffer(256, 384, DEV), cu.packed_buffer(384, 256, DEV)
+    cu.K.quant_tile(w, False, wq, ws, cu.Q_BLOCK, wt, wts, cu.Q_BLOCK, True, pw, pwt)
+    _, ws_ref = ref.quantize_128x128(w.float(), pow2=True)
+    _close(ws, ws_ref, 0, 1e-6, "pow2 block scales")
+    assert torch.equal(pw, ref.pack_ue8m0_blocks(ws_ref)) and torch.equal(pwt, ref.pack_ue8m0_blocks(ws_ref.t()))
+    # transposed with per-column scales (the A operand of a weight-gradient GEMM)
+    xt = torch.empty(384, 256, dtype=torch.float8_e4m3fn, device=DEV)
+    xts = torch.empty(2, 384, device=DEV)
+    pxt = cu.packed_buffer(384, 256, DEV)
+    cu.K.quant_tile(x, False, None, None, cu.Q_ROWS, xt, xts, cu.Q_COLS, True, None, pxt)
+    _, st_ref = ref.quantize_1x128(x.float().t().contiguous(), pow2=True)
+    _close(xts.t(), st_ref, 0, 1e-6, "pow2 col scales")
+    assert torch.equal(pxt, ref.pack_ue8m0_rows(st_ref))
