@@ -16,7 +16,7 @@ def main():
     from gdnet_b200.ops import cuda as cu
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kind", default="fp8", choices=["fp8", "bf16", "wgrad"])
+    ap.add_argument("--kind", default="fp8", choices=["fp8", "mx", "bf16", "wgrad"])
     ap.add_argument("--shape", default="32768,1024,1024")
     ap.add_argument("--iters", type=int, default=4)
     args = ap.parse_args()
@@ -29,6 +29,14 @@ def main():
         x8, sx = cu.quantize_rows(x)
         qw = cu.quantize_weight(w)
         fn = lambda: cu.gemm_fp8(x8, sx, qw.q, qw.s, out=out)
+    elif args.kind == "mx":
+        pa = cu.packed_buffer(M, K, dev)
+        x8, sx = cu.quantize_rows(x, pow2=True, packed=pa)
+        wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device=dev)
+        ws = torch.empty(N // 128, K // 128, device=dev)
+        pb = cu.packed_buffer(N, K, dev)
+        cu.K.quant_tile(w, False, wq, ws, cu.Q_BLOCK, None, None, cu.Q_BLOCK, True, pb, None)
+        fn = lambda: cu.gemm_fp8_mx(x8, pa, wq, pb, out=out)
     elif args.kind == "bf16":
         fn = lambda: cu.gemm_bf16(x, w, out=out)
     else:

@@ -315,8 +315,11 @@ void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t 
   if (p_row.has_value() || p_col.has_value()) {
     TORCH_CHECK(pow2 && a.rows % 128 == 0 && a.cols % 128 == 0, "packed scales need pow2 scales and 128-multiples");
     if (p_row.has_value()) {
-      TORCH_CHECK(q_row.has_value() && p_row->is_contiguous() && p_row->numel() == rb * cb * 512, "p_row must hold rows/128 * cols/128 * 512 bytes");
+      TORCH_CHECK(q_row.has_value() && p_row->dim() == 3 && p_row->size(0) == rb && p_row->size(1) == cb && p_row->size(2) == 512 &&
+                  p_row->stride(2) == 1 && p_row->stride(1) == 512 && p_row->stride(0) % 512 == 0,
+                  "p_row must be (rows/128, cols/128, 512) bytes, dense in its last two dims");
       a.p_row = fp8_mut(*p_row, "p_row");
+      a.p_row_stride = p_row->stride(0) / 512;
     }
     if (p_col.has_value()) {
       TORCH_CHECK(q_col.has_value() && p_col->is_contiguous() && p_col->numel() == rb * cb * 512, "p_col must hold cols/128 * rows/128 * 512 bytes");

@@ -632,7 +632,7 @@ quant_tile_kernel(const QuantArgs a) {
         if ((tid & 15) == 0) {
           a.s_row[(int64_t)blockIdx.x * a.s_row_ld + r] = sc;
           if (a.p_row != nullptr)
-            store_packed_scale(a.p_row, (int64_t)blockIdx.y * gridDim.x + blockIdx.x, (int)(r - r0), ue8m0_word(sc));
+            store_packed_scale(a.p_row, (int64_t)blockIdx.y * a.p_row_stride + blockIdx.x, (int)(r - r0), ue8m0_word(sc));
         }
       }
     }
@@ -671,7 +671,7 @@ quant_tile_kernel(const QuantArgs a) {
     }
     if (tid == 0) a.s_row[(int64_t)blockIdx.y * n_cb + blockIdx.x] = tile_scale;
     if (a.p_row != nullptr && tid < 128)
-      reinterpret_cast<uint32_t*>(a.p_row + ((int64_t)blockIdx.y * n_cb + blockIdx.x) * 512)[tid] = ue8m0_word(tile_scale);
+      reinterpret_cast<uint32_t*>(a.p_row + ((int64_t)blockIdx.y * a.p_row_stride + blockIdx.x) * 512)[tid] = ue8m0_word(tile_scale);
   }
 
   if (a.q_col != nullptr) {
@@ -741,7 +741,7 @@ quant_rows_kernel(const QuantArgs a) {
   if ((threadIdx.x & 15) == 0) {
     a.s_row[(int64_t)(c >> 7) * a.s_row_ld + r] = sc;
     if (a.p_row != nullptr)
-      store_packed_scale(a.p_row, (r >> 7) * (int64_t)(a.cols >> 7) + (c >> 7), (int)(r & 127), ue8m0_word(sc));
+      store_packed_scale(a.p_row, (r >> 7) * a.p_row_stride + (c >> 7), (int)(r & 127), ue8m0_word(sc));
   }
 }
 

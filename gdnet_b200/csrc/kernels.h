@@ -113,6 +113,7 @@ struct QuantArgs {
   int col_mode;            // QUANT_COLS or QUANT_BLOCK
   int pow2;                // scales rounded up to powers of two (needed by the hardware block-scaled GEMM)
   uint8_t* p_row;          // packed UE8M0 chunks for q_row, (rows/128, cols/128, 512) bytes, or null
+  int64_t p_row_stride;    // chunks between consecutive row blocks of p_row (cols/128 when dense)
   uint8_t* p_col;          // packed UE8M0 chunks for q_col, (cols/128, rows/128, 512) bytes, or null
 };
 

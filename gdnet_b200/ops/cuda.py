@@ -104,7 +104,7 @@ class QuantizedWeight:
     """e4m3 copies of a weight ``(N, K)`` with 128x128 block scales: ``q`` / ``s`` for the
     forward GEMM and ``qt`` / ``st`` (the transposed matrix ``(K, N)``) for the data gradient."""
 
-    __slots__ = ("q", "s", "qt", "st", "version", "ptr", "source")
+    __slots__ = ("q", "s", "qt", "st", "p", "pt", "version", "ptr", "source")
 
 
 _wq_cache: dict[int, QuantizedWeight] = {}
@@ -124,7 +124,11 @@ def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
         qw.s = torch.empty(nb, kb, dtype=F32, device=w.device)
         qw.qt = torch.empty(Kd, N, dtype=FP8, device=w.device)
         qw.st = torch.empty(kb, nb, dtype=F32, device=w.device)
-    K.quant_tile(w.detach(), False, qw.q, qw.s, Q_BLOCK, qw.qt, qw.st, Q_BLOCK)
+        mx = N % 128 == 0 and Kd % 128 == 0
+        qw.p = packed_buffer(N, Kd, w.device) if mx else None
+        qw.pt = packed_buffer(Kd, N, w.device) if mx else None
+    # power-of-two scales: the same copies serve the hardware-scaled and the software-scaled GEMM
+    K.quant_tile(w.detach(), False, qw.q, qw.s, Q_BLOCK, qw.qt, qw.st, Q_BLOCK, True, qw.p, qw.pt)
     qw.version, qw.ptr, qw.source = stamp, w.data_ptr(), w   # `source` pins the storage address
     _wq_cache[key] = qw
     return qw
@@ -234,6 +238,49 @@ def quantize_rows_and_transposed(x, col_mode):
         st = torch.empty((Kd + 127) // 128, (M + 127) // 128, dtype=F32, device=x.device)
     K.quant_tile(x, False, q, s, Q_ROWS, qt, st, col_mode)
     return q, s, qt, st
+
+
+def quantize_rows_mx(x, pre_silu=False, q=None, s=None, p=None):
+    """1x128 quantisation with power-of-two scales for the hardware-scaled GEMM:
+    ``(q (M,K), s (K/128, M) fp32, p (M/128, K/128, 512) packed UE8M0)``. ``q``/``s``/``p`` may be views
+    into wider buffers (an operand assembled from several sources along K)."""
+    M, Kd = x.shape
+    if q is None:
+        q = torch.empty(M, Kd, dtype=FP8, device=x.device)
+    if s is None:
+        s = torch.empty(Kd // 128, M, dtype=F32, device=x.device)
+    if p is None:
+        p = packed_buffer(M, Kd, x.device)
+    K.quant_tile(x, pre_silu, q, s, Q_ROWS, None, None, Q_BLOCK, True, p, None)
+    return q, s, p
+
+
+def quantize_transposed_mx(x, mode, pre_silu=False, qt=None, st=None, pt=None):
+    """``x (M,K)`` -> e4m3 ``x^T (K,M)`` with power-of-two scales and packed chunks ``pt (K/128, M/128, 512)``;
+    ``mode`` as in :func:`quantize_transposed`."""
+    M, Kd = x.shape
+    if qt is None:
+        qt = torch.empty(Kd, M, dtype=FP8, device=x.device)
+    if st is None:
+        st = torch.empty((M // 128, Kd) if mode == Q_COLS else (Kd // 128, M // 128), dtype=F32, device=x.device)
+    if pt is None:
+        pt = packed_buffer(Kd, M, x.device)
+    K.quant_tile(x, pre_silu, None, None, Q_ROWS, qt, st, mode, True, None, pt)
+    return qt, st, pt
+
+
+def quantize_both_mx(x, col_mode):
+    """Row-quantised and transposed copies from one read, power-of-two scales:
+    ``(q, p, qt, pt)`` (the fp32 scale arrays are written too but not returned)."""
+    M, Kd = x.shape
+    q = torch.empty(M, Kd, dtype=FP8, device=x.device)
+    s = torch.empty(Kd // 128, M, dtype=F32, device=x.device)
+    p = packed_buffer(M, Kd, x.device)
+    qt = torch.empty(Kd, M, dtype=FP8, device=x.device)
+    st = torch.empty((M // 128, Kd) if col_mode == Q_COLS else (Kd // 128, M // 128), dtype=F32, device=x.device)
+    pt = packed_buffer(Kd, M, x.device)
+    K.quant_tile(x, False, q, s, Q_ROWS, qt, st, col_mode, True, p, pt)
+    return q, p, qt, pt
 
 
 def quantize_fp8_tensor(x, scale, need_col=True, out_row=None, out_col=None, amax_buf=None):
@@ -471,23 +518,23 @@ class _LinearFp8BlockFn(torch.autograd.Function):
     def forward(ctx, x2, w, b):
         qw = quantize_weight(w)
         if ctx.needs_input_grad[1]:
-            x8, sx, xt8, sxt = quantize_rows_and_transposed(x2, Q_BLOCK)
+            x8, px, xt8, pxt = quantize_both_mx(x2, Q_BLOCK)
         else:
-            x8, sx = quantize_rows(x2)
-            xt8 = sxt = x2.new_empty(0)
-        ctx.save_for_backward(xt8, sxt, w, b if b is not None else x2.new_empty(0))
+            x8, _, px = quantize_rows_mx(x2)
+            xt8 = pxt = x2.new_empty(0)
+        ctx.save_for_backward(xt8, pxt, w, b if b is not None else x2.new_empty(0))
         ctx.has_bias = b is not None
-        return gemm_fp8(x8, sx, qw.q, qw.s, bias=b)
+        return gemm_fp8_mx(x8, px, qw.q, qw.p, bias=b)
 
     @staticmethod
     def backward(ctx, dy):
-        xt8, sxt, w, b = ctx.saved_tensors
+        xt8, pxt, w, b = ctx.saved_tensors
         dy = dy.contiguous()
         qw = quantize_weight(w)
-        dy8, sdy, dyt8, sdyt = quantize_rows_and_transposed(dy, Q_COLS)
-        dx = gemm_fp8(dy8, sdy, qw.qt, qw.st) if ctx.needs_input_grad[0] else None
+        dy8, pdy, dyt8, pdyt = quantize_both_mx(dy, Q_COLS)
+        dx = gemm_fp8_mx(dy8, pdy, qw.qt, qw.pt) if ctx.needs_input_grad[0] else None
         tgt, is_main = _wgrad_target(w)
-        gemm_fp8(dyt8, sdyt, xt8, sxt, out=tgt, accumulate=True)
+        gemm_fp8_mx(dyt8, pdyt, xt8, pxt, out=tgt, accumulate=True)
         dw = None if is_main else tgt.to(w.dtype)
         db = _bias_grad(dy, b if ctx.has_bias else None)
         return dx, dw, db
@@ -592,12 +639,13 @@ class _LayerStepFn(torch.autograd.Function):
             kb = d // 128
             u8 = torch.empty(M, 2 * d, dtype=FP8, device=dev)
             su = torch.empty(2 * kb, M, dtype=F32, device=dev)
-            quantize_rows(s2, q=u8[:, :d], s=su[:kb])
-            quantize_rows(c, q=u8[:, d:], s=su[kb:])
+            pu = packed_buffer(M, 2 * d, dev)
+            quantize_rows_mx(s2, q=u8[:, :d], s=su[:kb], p=pu[:, :kb])
+            quantize_rows_mx(c, q=u8[:, d:], s=su[kb:], p=pu[:, kb:])
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
-            gemm_fp8(u8, su, q1.q, q1.s, out=h1_pre, bias=f32(rb1))
-            a8, sa = quantize_rows(h1_pre, pre_silu=True)
-            z = gemm_fp8(a8, sa, q2.q, q2.s, bias=f32(rb2))
+            gemm_fp8_mx(u8, pu, q1.q, q1.p, out=h1_pre, bias=f32(rb1))
+            a8, _, pa = quantize_rows_mx(h1_pre, pre_silu=True)
+            z = gemm_fp8_mx(a8, pa, q2.q, q2.p, bias=f32(rb2))
             a1 = None
         else:
             gemm_bf16(s2, rW1[:, :d], out=h1_pre)
@@ -676,23 +724,24 @@ class _LayerStepFn(torch.autograd.Function):
         db1r = torch.zeros(d, dtype=F32, device=dev)
         if fp8:
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
-            dz8, sdz, dzt8, sdzt = quantize_rows_and_transposed(dz, Q_COLS)
-            a1t8, sa1t = quantize_transposed(h1_pre, Q_BLOCK, pre_silu=True)
+            dz8, pdz, dzt8, pdzt = quantize_both_mx(dz, Q_COLS)
+            a1t8, _, pa1t = quantize_transposed_mx(h1_pre, Q_BLOCK, pre_silu=True)
             tgt, main_r2 = _wgrad_target(rW2)
-            gemm_fp8(dzt8, sdzt, a1t8, sa1t, out=tgt, accumulate=True)
+            gemm_fp8_mx(dzt8, pdzt, a1t8, pa1t, out=tgt, accumulate=True)
             g_rW2 = None if main_r2 else tgt.to(rW2.dtype)
-            dh1 = gemm_fp8(dz8, sdz, q2.qt, q2.st, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
+            dh1 = gemm_fp8_mx(dz8, pdz, q2.qt, q2.pt, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
             K.colsum(dh1, db1r)
-            dh8, sdh, dht8, sdht = quantize_rows_and_transposed(dh1, Q_COLS)
-            kb, mb = d // 128, (M + 127) // 128
+            dh8, pdh, dht8, pdht = quantize_both_mx(dh1, Q_COLS)
+            kb, mb = d // 128, M // 128
             ut8 = torch.empty(2 * d, M, dtype=FP8, device=dev)
             sut = torch.empty(2 * kb, mb, dtype=F32, device=dev)
-            K.quant_tile(s2, False, None, None, Q_ROWS, ut8[:d], sut[:kb], Q_BLOCK)
-            K.quant_tile(c, False, None, None, Q_ROWS, ut8[d:], sut[kb:], Q_BLOCK)
+            put = packed_buffer(2 * d, M, dev)
+            quantize_transposed_mx(s2, Q_BLOCK, qt=ut8[:d], st=sut[:kb], pt=put[:kb])
+            quantize_transposed_mx(c, Q_BLOCK, qt=ut8[d:], st=sut[kb:], pt=put[kb:])
             tgt, main_r1 = _wgrad_target(rW1)
-            gemm_fp8(dht8, sdht, ut8, sut, out=tgt, accumulate=True)
+            gemm_fp8_mx(dht8, pdht, ut8, put, out=tgt, accumulate=True)
             g_rW1 = None if main_r1 else tgt.to(rW1.dtype)
-            gemm_fp8(dh8, sdh, q1.qt, q1.st, out=dsc, aux=dsc, aux_mode=AUX_ADD)
+            gemm_fp8_mx(dh8, pdh, q1.qt, q1.pt, out=dsc, aux=dsc, aux_mode=AUX_ADD)
         else:
             g_rW2 = _wgrad_bf16(dz, a1, rW2)
             dh1 = gemm_bf16(dz, rW2, b_mn=True, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
