@@ -67,6 +67,37 @@ gd::Status* status_ptr(const Tensor& like) {
 
 Tensor kernel_status(const Tensor& like) { return status_tensor(like.get_device()); }
 
+// Flat gradient buffers whose contents are spread over the ranks ("grad sinks"): a weight-gradient GEMM or a
+// peer_add whose destination lies inside a registered buffer adds into the owner rank's copy instead.
+struct GradSink {
+  uintptr_t base;
+  int64_t elems;
+  Tensor table;     // int64 device tensor: the buffer's address on every rank
+  int64_t shard_elems;
+};
+
+std::vector<GradSink>& grad_sinks() {
+  static std::vector<GradSink> sinks;
+  return sinks;
+}
+
+const GradSink* find_sink(const void* p) {
+  const uintptr_t u = reinterpret_cast<uintptr_t>(p);
+  for (const GradSink& s : grad_sinks())
+    if (u >= s.base && u < s.base + (uintptr_t)s.elems * 4) return &s;
+  return nullptr;
+}
+
+void register_grad_sink(const Tensor& flat, const Tensor& ptr_table, int64_t shard_elems) {
+  TORCH_CHECK(flat.is_cuda() && flat.scalar_type() == at::kFloat && flat.is_contiguous(), "grad sink must be flat fp32");
+  TORCH_CHECK(ptr_table.is_cuda() && ptr_table.scalar_type() == at::kLong, "ptr_table must be an int64 CUDA tensor");
+  TORCH_CHECK(shard_elems > 0 && shard_elems % 128 == 0, "shard_elems must be a positive multiple of 128");
+  TORCH_CHECK(flat.numel() <= shard_elems * ptr_table.numel(), "shards do not cover the buffer");
+  grad_sinks().push_back({reinterpret_cast<uintptr_t>(flat.data_ptr()), flat.numel(), ptr_table, shard_elems});
+}
+
+void clear_grad_sinks() { grad_sinks().clear(); }
+
 void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT bias, OptT row_scale, OptT ssq_in,
                    int64_t norm_dim, double norm_eps, OptT aux, int64_t aux_mode, OptT rowcoef, OptT pre_out,
                    int64_t act, OptT ssq_out, int64_t M, int64_t N) {
@@ -80,6 +111,18 @@ void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT
               "out rows must be 16-byte aligned");
   e.accumulate = accumulate;
   e.atomic = 0;
+  e.peer_out = nullptr;
+  e.flat_off = 0;
+  e.shard_elems = 1;
+  if (e.out_f32 && accumulate) {
+    if (const GradSink* s = find_sink(out.data_ptr())) {
+      TORCH_CHECK(out.is_contiguous() && N % 32 == 0, "a gradient inside a spread flat buffer must be contiguous, N % 32 == 0");
+      e.peer_out = reinterpret_cast<float* const*>(s->table.data_ptr<int64_t>());
+      e.flat_off = (int64_t)((reinterpret_cast<uintptr_t>(out.data_ptr()) - s->base) / 4);
+      e.shard_elems = s->shard_elems;
+      TORCH_CHECK(e.flat_off % 32 == 0, "gradient views must start at a multiple of 32 elements");
+    }
+  }
   e.bias = nullptr;
   e.bias_f32 = 0;
   if (bias.has_value()) {
@@ -457,6 +500,27 @@ void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, con
   GD_LAUNCH(gd::launch_fused_reduce_adamw(a, stream_of(m)));
 }
 
+// dst += src where dst is a view into a registered spread gradient buffer (else a plain local add)
+void peer_add(Tensor dst, const Tensor& src) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  TORCH_CHECK(dst.is_cuda() && dst.scalar_type() == at::kFloat && dst.is_contiguous(), "peer_add: dst must be contiguous fp32");
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.numel() == dst.numel(), "peer_add: src must match dst");
+  TORCH_CHECK(src.scalar_type() == at::kFloat || src.scalar_type() == at::kBFloat16, "peer_add: src must be fp32 or bf16");
+  const GradSink* s = find_sink(dst.data_ptr());
+  if (s == nullptr) {
+    dst.add_(src.view_as(dst));
+    return;
+  }
+  gd::PeerAddArgs a{};
+  a.src = src.data_ptr();
+  a.src_bf16 = src.scalar_type() == at::kBFloat16;
+  a.table = reinterpret_cast<float* const*>(s->table.data_ptr<int64_t>());
+  a.flat_off = (int64_t)((reinterpret_cast<uintptr_t>(dst.data_ptr()) - s->base) / 4);
+  a.n = dst.numel();
+  a.shard_elems = s->shard_elems;
+  GD_LAUNCH(gd::launch_peer_add(a, stream_of(dst)));
+}
+
 void halo_push_wait(const Tensor& tail, Tensor halo_out, const Tensor& slot_ptrs, const Tensor& flag_ptrs,
                     int64_t slot_offset_bytes, int64_t flag_index, int64_t rank, int64_t world, int64_t seq,
                     bool reverse) {
@@ -501,5 +565,8 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("projected_adamw(Tensor(a!) p, Tensor gt, Tensor? gi, Tensor(b!) m, Tensor(c!) v, Tensor scalars, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()", &projected_adamw);
   m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
   m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums) -> ()", &allreduce_adamw);
+  m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> ()", &register_grad_sink);
+  m.def("clear_grad_sinks() -> ()", &clear_grad_sinks);
+  m.def("peer_add(Tensor(a!) dst, Tensor src) -> ()", &peer_add);
   m.def("halo_push_wait(Tensor tail, Tensor(a!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, int slot_offset_bytes, int flag_index, int rank, int world, int seq, bool reverse) -> ()", &halo_push_wait);
 }

@@ -56,10 +56,16 @@ __global__ void __launch_bounds__(512)
 fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
   int64_t lo, hi;
   shard_range(a.n, a.rank, a.world, lo, hi);
-  const bool do_reduce = a.phase != 2, do_update = a.phase != 1;
+  // phases 0-2: the peers' buffers hold per-rank gradients and this kernel reduces them;
+  // phases 3-5: the shard already holds the sum over ranks (added there by the producers' epilogues)
+  const bool scattered = a.phase >= 3;
+  const bool do_open = a.phase == 0 || a.phase == 1 || a.phase == 3 || a.phase == 5;
+  const bool do_reduce = a.phase == 0 || a.phase == 1;
+  const bool do_dots = do_open;
+  const bool do_update = a.phase == 0 || a.phase == 2 || a.phase == 4 || a.phase == 5;
   const float inv_world = 1.0f / (float)a.world;
 
-  if (do_reduce) {
+  if (do_open) {
     __threadfence_system();
     if (!rank_barrier(a, 0, a.seq)) return;   // every rank's gradients are complete
   }
@@ -94,6 +100,19 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
     } else {
       T = *reinterpret_cast<const float4*>(a.gt[a.rank] + i);
       I = *reinterpret_cast<const float4*>(a.gi[a.rank] + i);
+      if (scattered) {
+        T.x *= inv_world; T.y *= inv_world; T.z *= inv_world; T.w *= inv_world;
+        I.x *= inv_world; I.y *= inv_world; I.z *= inv_world; I.w *= inv_world;
+        if (do_dots) {
+          s_tt += T.x * T.x + T.y * T.y + T.z * T.z + T.w * T.w;
+          s_ti += T.x * I.x + T.y * I.y + T.z * I.z + T.w * I.w;
+          s_ii += I.x * I.x + I.y * I.y + I.z * I.z + I.w * I.w;
+        }
+        if (do_update) {   // the shard is consumed: clear it for the next step's remote additions
+          *reinterpret_cast<float4*>(a.gt[a.rank] + i) = make_float4(0, 0, 0, 0);
+          *reinterpret_cast<float4*>(a.gi[a.rank] + i) = make_float4(0, 0, 0, 0);
+        }
+      }
     }
     if (do_update) {
       const float g[4] = {k_t * T.x + k_i * I.x, k_t * T.y + k_i * I.y, k_t * T.z + k_i * I.z, k_t * T.w + k_i * I.w};
@@ -131,7 +150,7 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
     }
   }
 
-  if (do_reduce) {
+  if (do_dots) {
     __shared__ float red[3][16];
     s_tt = warp_sum(s_tt); s_ti = warp_sum(s_ti); s_ii = warp_sum(s_ii);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -177,6 +196,35 @@ const char* launch_fused_reduce_adamw(const FusedReduceAdamWArgs& a, cudaStream_
   if (blocks < 1) blocks = 1;
   fused_reduce_adamw_kernel<<<(unsigned)blocks, 512, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? nullptr : "fused_reduce_adamw launch failed";
+}
+
+// ---------------------------------------------------------------------------------------
+// add a local gradient into the flat buffers of the ranks that own its range
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+peer_add_kernel(const PeerAddArgs a) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= a.n) return;
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  const int cnt = (a.n - i) < 4 ? (int)(a.n - i) : 4;
+  for (int q = 0; q < cnt; ++q)
+    v[q] = a.src_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.src)[i + q])
+                      : reinterpret_cast<const float*>(a.src)[i + q];
+  const int64_t idx = a.flat_off + i;                 // flat_off and shard_elems are multiples of 4
+  float* dst = a.table[idx / a.shard_elems] + idx;
+  if (cnt == 4) {
+    red_add_v4(dst, v[0], v[1], v[2], v[3]);
+  } else {
+    for (int q = 0; q < cnt; ++q) atomicAdd(dst + q, v[q]);
+  }
+}
+
+const char* launch_peer_add(const PeerAddArgs& a, cudaStream_t st) {
+  if (a.n <= 0) return nullptr;
+  if (a.flat_off % 4 != 0 || a.shard_elems % 4 != 0) return "peer_add: offsets must be multiples of 4 elements";
+  const int64_t blocks = (a.n + 1023) / 1024;
+  peer_add_kernel<<<(unsigned)blocks, 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "peer_add launch failed";
 }
 
 // ---------------------------------------------------------------------------------------

@@ -21,6 +21,12 @@ struct Status;
 //   phase 1: barrier, reduce this rank's shard of both gradients in place, shard dot products
 //   phase 2: AdamW on the shard (scalars now hold the clip factor), write the new parameters
 //            into every rank's parameter buffer, closing barrier
+//
+// When the producers have already added their gradients into the owner's shard (weight-gradient GEMM
+// epilogues and peer_add, i.e. the reduce-scatter happened tile by tile during backward):
+//   phase 3: barrier, shard dot products of the mean gradients
+//   phase 4: AdamW on the shard, all-gather of the parameters, shard cleared, closing barrier
+//   phase 5: 3 and 4 in one launch (scalars known beforehand)
 struct FusedReduceAdamWArgs {
   float* const* gt;        // [world] task-gradient buffers (fp32, n elements each)
   float* const* gi;        // [world] info-gradient buffers
@@ -39,6 +45,16 @@ struct FusedReduceAdamWArgs {
   Status* status;
 };
 const char* launch_fused_reduce_adamw(const FusedReduceAdamWArgs& a, cudaStream_t st);
+
+// dst_flat[flat_off + i] += src[i] for i < n, where dst_flat is the flat gradient buffer spread over the
+// ranks: element idx lives in table[idx / shard_elems] (vector atomics, local or over NVLink).
+struct PeerAddArgs {
+  const void* src;          // n contiguous fp32 or bf16 values
+  int src_bf16;
+  float* const* table;      // [world] flat fp32 gradient buffers
+  int64_t flat_off, n, shard_elems;
+};
+const char* launch_peer_add(const PeerAddArgs& a, cudaStream_t st);
 
 // Sequence-parallel neighbour exchange: store `tail` into the next rank's slot, raise its flag,
 // wait (bounded) for this rank's own flag from the previous rank, copy the slot out.

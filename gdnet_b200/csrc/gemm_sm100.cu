@@ -131,12 +131,16 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
 
   if (e.out_f32) {
     float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(e.out) + (size_t)m * e.out_ld + n0);
+    if (e.peer_out != nullptr) {
+      // gradient reduce-scatter from the epilogue: add this chunk into the owner rank's flat buffer
+      const int64_t idx = e.flat_off + (int64_t)m * e.out_ld + n0;
+      op = reinterpret_cast<float4*>(e.peer_out[idx / e.shard_elems] + idx);
+    }
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-      if (e.atomic) {   // split-K: several CTAs add their share of the reduction into the same tile
-        float* of = reinterpret_cast<float*>(op + q);
-        atomicAdd(of, o.x); atomicAdd(of + 1, o.y); atomicAdd(of + 2, o.z); atomicAdd(of + 3, o.w);
+      if (e.atomic || e.peer_out != nullptr) {   // split-K shares and peers add into the same tile
+        red_add_v4(reinterpret_cast<float*>(op + q), o.x, o.y, o.z, o.w);
         continue;
       }
       if (e.accumulate) {

@@ -44,6 +44,12 @@ struct GemmEpilogue {
   int out_f32;
   int accumulate;       // out += v instead of out = v
   int atomic;           // fp32 out += v with atomics (set by the launcher for split-K)
+  // Reduce-scatter from the epilogue: when peer_out is set, `out` is a view of this rank's flat fp32
+  // gradient buffer at element offset flat_off, and every 32-column chunk is added (vector atomics over
+  // NVLink) into the buffer of the rank that owns that part of the flat range: peer_out[idx / shard_elems] + idx.
+  float* const* peer_out;
+  int64_t flat_off;
+  int64_t shard_elems;
   const void* bias;     // [N] bf16 or fp32, may be null
   int bias_f32;
   const float* row_scale;   // [M], may be null

@@ -301,15 +301,33 @@ def quantize_fp8_tensor(x, scale, need_col=True, out_row=None, out_col=None, ama
 # --------------------------------------------------------------------------------------
 # gradient sinks: fp32 main_grad (training engine) or autograd
 # --------------------------------------------------------------------------------------
+_spread_grads = False
+
+
+def set_spread_grads(on: bool) -> None:
+    """Tell the gradient sinks that ``main_grad`` views belong to flat buffers spread over the ranks
+    (registered with ``register_grad_sink``): every addition then goes to the owner rank's copy."""
+    global _spread_grads
+    _spread_grads = bool(on)
+
+
 def _main_grad(p):
     return getattr(p, "main_grad", None)
+
+
+def accumulate_main_grad(mg, g) -> None:
+    """mg += g for a ``main_grad`` view; over NVLink into the owning rank's buffer when gradients are spread."""
+    if _spread_grads:
+        K.peer_add(mg, g.contiguous())
+    else:
+        mg.add_(g.view_as(mg))
 
 
 def _sink_vec(p, g32):
     """Deliver the fp32 gradient of a small parameter: add to ``main_grad`` or return it."""
     mg = _main_grad(p)
     if mg is not None:
-        mg.add_(g32.view_as(mg))
+        accumulate_main_grad(mg, g32)
         return None
     return g32.to(p.dtype).view_as(p)
 
@@ -712,7 +730,12 @@ class _LayerStepFn(torch.autograd.Function):
         dW2w = gemm_bf16(dq, h, a_mn=True, b_mn=True, out_dtype=F32)
         tgt2, main2 = _wgrad_target(gW2)
         dgnw = torch.zeros(d, dtype=F32, device=dev)
-        K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), tgt2, dgnw)
+        if main2 and _spread_grads:
+            dW2 = torch.zeros_like(dW2w)
+            K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), dW2, dgnw)
+            accumulate_main_grad(tgt2, dW2)
+        else:
+            K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), tgt2, dgnw)
         dh_pre = gemm_bf16(dq, W2w, b_mn=True, aux=hg_pre, aux_mode=AUX_RMS_SILU_BWD, rowcoef=rowcoef)
         db1g = torch.zeros(d, dtype=F32, device=dev)
         K.colsum(dh_pre, db1g)
@@ -861,7 +884,7 @@ class _SigmaFn(torch.autograd.Function):
         for i, W in enumerate(ctx.mats):
             mg = _main_grad(W)
             if mg is not None:
-                mg.addr_(ys[i], vecs[i], alpha=1.0, beta=1.0) if False else mg.add_(torch.outer(ys[i] * coef[i], vecs[i]))
+                accumulate_main_grad(mg, torch.outer(ys[i] * coef[i], vecs[i]))
                 grads.append(None)
             else:
                 grads.append(torch.outer(ys[i] * coef[i], vecs[i]).to(W.dtype))

@@ -16,6 +16,13 @@ One step = one forward, two backward passes (task; info + transition), then
   the peers' buffers over NVLink, applies projection + AdamW to that shard and writes the new
   parameters into every rank's parameter buffer, all in one kernel (``csrc/comm.cu``); the
   buffers live in symmetric memory;
+* N GPUs, ``comm="scatter"``: the reduce-scatter happens *during* backward, tile by tile: the flat
+  gradient buffers are spread over the ranks, and every weight-gradient GEMM epilogue (and every
+  small-parameter gradient) adds its values with vector atomics over NVLink straight into the shard
+  of the owning rank (``csrc/gemm_sm100.cu:epilogue_chunk``, ``csrc/comm.cu:peer_add_kernel``). After
+  backward each rank holds the sum over ranks of its shard; the update kernel then only does the
+  barrier, projection + AdamW on the shard and the parameter all-gather. The projection coefficient
+  in this mode is computed from the reduced gradients (no rank ever holds its full local gradient);
 * N GPUs, ``comm="nccl"``: NCCL all-reduce of the flat gradients, then the 1-GPU update.
 
 The projection coefficient uses the sum over ranks of the *local* dot products, exactly as
@@ -49,6 +56,7 @@ class _Group:
         per = -(-per // ALIGN) * ALIGN
         self.n = per * world            # padded so every rank's shard has the same length
         self.offsets = offs
+        self.per = per
         self.shard = (rank * per, (rank + 1) * per)
         item = 2 if dtype == torch.bfloat16 else 4
         if symmetric:
@@ -86,12 +94,17 @@ class TrainEngine(nn.Module):
 
     def __init__(self, model: nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 1e-2, precision: str = "fp8", process_group=None, sp_group=None,
-                 comm: str = "fused", broadcast: bool = True):
+                 comm: str = "fused", broadcast: bool = True, projection: str = "local"):
         super().__init__()
         self.module = model
         self.precision = precision
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.sp_group = sp_group
+        # "local": coefficient from the sum over ranks of per-rank dot products (gdnet/loss.py:228-235);
+        # "global": from the dot products of the reduced gradients (the only choice for comm="scatter")
+        if projection not in ("local", "global"):
+            raise ValueError(f"unknown projection {projection!r}")
+        self.projection = projection
         self.step_count = 0
         self.comm_seq = 0
         dev = next(model.parameters()).device
@@ -101,8 +114,9 @@ class TrainEngine(nn.Module):
         self.world = dist.get_world_size(self.pg) if self.distributed else 1
         self.rank = dist.get_rank(self.pg) if self.distributed else 0
         self.comm = comm if self.distributed else "local"
-        if self.comm not in ("fused", "nccl", "local"):
+        if self.comm not in ("fused", "scatter", "nccl", "local"):
             raise ValueError(f"unknown comm backend {comm!r}")
+        symmetric = self.comm in ("fused", "scatter")
 
         params = [p for p in model.parameters() if p.requires_grad]
         by_dtype: dict[torch.dtype, list] = {}
@@ -112,7 +126,7 @@ class TrainEngine(nn.Module):
             if dt not in (torch.bfloat16, torch.float32):
                 raise TypeError(f"unsupported parameter dtype {dt}")
         self.groups = [
-            _Group(ps, dt, dev, self.world, self.rank, self.comm == "fused", self.pg) for dt, ps in by_dtype.items()
+            _Group(ps, dt, dev, self.world, self.rank, symmetric, self.pg) for dt, ps in by_dtype.items()
         ]
         self.params = params
         if self.distributed and broadcast:
@@ -121,12 +135,20 @@ class TrainEngine(nn.Module):
                 dist.broadcast(g.flat, src=src, group=self.pg)
             for b in model.buffers():
                 dist.broadcast(b, src=src, group=self.pg)
-        if self.comm == "fused":
+        if symmetric:
             from ..parallel.symm import SymmBuffer
 
             self._flags = SymmBuffer(4096, self.pg, dev)
             for g in self.groups:
                 g._sp.barrier()
+        if self.comm == "scatter":
+            from ..ops import cuda as cu
+
+            cu.K.clear_grad_sinks()
+            for g in self.groups:
+                cu.K.register_grad_sink(g.g_task, g._sgt.ptr_table, g.per)
+                cu.K.register_grad_sink(g.g_info, g._sgi.ptr_table, g.per)
+            cu.set_spread_grads(True)
         self.scalars = torch.zeros(2, dtype=torch.float32, device=dev)
         if dev.type == "cuda":
             from ..ops import cuda as cu
@@ -149,7 +171,12 @@ class TrainEngine(nn.Module):
     def _fold_autograd_grads(self) -> None:
         for p in self.params:
             if p.grad is not None:
-                p.main_grad.add_(p.grad)
+                if self.comm == "scatter":
+                    from ..ops import cuda as cu
+
+                    cu.accumulate_main_grad(p.main_grad, p.grad)
+                else:
+                    p.main_grad.add_(p.grad)
                 p.grad = None
 
     # -- the step ---------------------------------------------------------------------------
@@ -163,8 +190,9 @@ class TrainEngine(nn.Module):
             raise ValueError(f"batch size {B} not divisible by accum_steps {accum_steps}")
         mb = B // accum_steps
         for g in self.groups:
-            g.g_task.zero_()
-            g.g_info.zero_()
+            if self.comm != "scatter":   # spread buffers are cleared by the update kernel that consumed them
+                g.g_task.zero_()
+                g.g_info.zero_()
             g.sums.zero_()
         total = torch.zeros((), dtype=torch.float32, device=tokens.device)
         dev_type = tokens.device.type
@@ -203,23 +231,36 @@ class TrainEngine(nn.Module):
 
         self.step_count += 1
         K = cu.K
-        # local dot products <gt,gt>, <gi,gt>, <gi,gi> over all groups
-        sums = torch.zeros(4, dtype=torch.float32, device=self.device)
-        for g in self.groups:
-            K.grad_dots(g.g_task, g.g_info, sums)
-        if self.distributed:
-            dist.all_reduce(sums, group=self.pg)
-        coef = sums[1] / sums[0].clamp(min=1e-8)
-        self.scalars[0] = coef
-        self.scalars[1] = 1.0
+        if self.comm == "scatter":
+            return self._update_scattered(beta, grad_clip)
+        glob = self.projection == "global" and self.distributed
         b1, b2 = self.betas
         common = (beta, self.lr, b1, b2, self.eps, self.weight_decay, self.step_count)
+        self.scalars[1] = 1.0
 
+        def dots():
+            sums = torch.zeros(4, dtype=torch.float32, device=self.device)
+            for g in self.groups:
+                K.grad_dots(g.g_task, g.g_info, sums)
+            return sums
+
+        coef = None
+        if not glob:
+            # sum over ranks of the local dot products <gt,gt>, <gi,gt>
+            sums = dots()
+            if self.distributed:
+                dist.all_reduce(sums, group=self.pg)
+            coef = sums[1] / sums[0].clamp(min=1e-8)
         if self.comm == "nccl":
             for g in self.groups:
                 dist.all_reduce(g.g_task, group=self.pg)
                 dist.all_reduce(g.g_info, group=self.pg)
             self.scalars[1] = 1.0 / self.world
+            if glob:
+                sums = dots()       # of the reduced gradients; the ratio does not depend on their scale
+                coef = sums[1] / sums[0].clamp(min=1e-8)
+        if coef is not None:
+            self.scalars[0] = coef
 
         if self.comm in ("local", "nccl"):
             if grad_clip > 0.0:
@@ -233,14 +274,41 @@ class TrainEngine(nn.Module):
 
         # fused: reduce-scatter + projection + AdamW + all-gather over peer memory
         self.comm_seq += 1
-        phases = (0,) if grad_clip <= 0.0 else (1, 2)
+        phases = (0,) if grad_clip <= 0.0 and not glob else (1, 2)
         for phase in phases:
             if phase == 2:
                 red = torch.zeros(4, dtype=torch.float32, device=self.device)
                 for g in self.groups:
                     red[:3] += g.sums[:3]
                 dist.all_reduce(red, group=self.pg)
-                self.scalars[1] = self._clip_factor(red, coef, beta, grad_clip)
+                if glob:
+                    coef = red[1] / red[0].clamp(min=1e-8)
+                    self.scalars[0] = coef
+                if grad_clip > 0.0:
+                    self.scalars[1] = self._clip_factor(red, coef, beta, grad_clip)
+            for gi, g in enumerate(self.groups):
+                K.allreduce_adamw(g._sgt.ptr_table, g._sgi.ptr_table, g._sp.ptr_table, self._flags.ptr_table,
+                                  g.m, g.v, self.scalars, g.n, self.rank, self.world,
+                                  self.comm_seq * 8 + gi, phase, g.dtype == torch.bfloat16, *common, g.sums)
+
+    def _update_scattered(self, beta: float, grad_clip: float) -> None:
+        """Gradients were reduce-scattered by the producers. Barrier + shard dot products, one tiny
+        all-reduce for the projection coefficient (and the clip factor), then AdamW + all-gather."""
+        from ..ops import cuda as cu
+
+        K = cu.K
+        b1, b2 = self.betas
+        common = (beta, self.lr, b1, b2, self.eps, self.weight_decay, self.step_count)
+        self.comm_seq += 1
+        for phase in (3, 4):
+            if phase == 4:
+                red = torch.zeros(4, dtype=torch.float32, device=self.device)
+                for g in self.groups:
+                    red[:3] += g.sums[:3]
+                dist.all_reduce(red, group=self.pg)
+                coef = red[1] / red[0].clamp(min=1e-8)
+                self.scalars[0] = coef
+                self.scalars[1] = self._clip_factor(red, coef, beta, grad_clip) if grad_clip > 0.0 else 1.0
             for gi, g in enumerate(self.groups):
                 K.allreduce_adamw(g._sgt.ptr_table, g._sgi.ptr_table, g._sp.ptr_table, self._flags.ptr_table,
                                   g.m, g.v, self.scalars, g.n, self.rank, self.world,

@@ -48,6 +48,40 @@ def engine_fused_vs_nccl(rank, world, dev):
         assert torch.equal(ref, a), "ranks hold different parameters after the fused all-gather"
 
 
+def engine_scatter_vs_nccl(rank, world, dev):
+    """Gradients reduce-scattered from the weight-gradient GEMM epilogues (NVLink atomics into the owner's
+    shard) against NCCL all-reduce, both with the projection coefficient of the reduced gradients."""
+    base = _model(dev)
+    e_nccl = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="nccl", projection="global")
+    e_fused = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="fused", projection="global")
+    e_sc = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="scatter")
+    g = torch.Generator(device="cpu").manual_seed(200 + rank)
+    from gdnet_b200.ops import cuda as cu
+
+    for step in range(3):
+        tok = torch.randint(0, 1024, (2, 256), generator=g).to(dev)
+        tgt = torch.randint(0, 1024, (2, 256), generator=g).to(dev)
+        clip = 1.0 if step == 2 else 0.0
+        losses = []
+        for eng in (e_nccl, e_fused, e_sc):
+            cu.set_spread_grads(eng.comm == "scatter")
+            torch.manual_seed(7 + step)
+            losses.append(float(eng.projected_step(tok, tgt, grad_clip=clip)))
+        assert max(losses) - min(losses) < 5e-2 * max(1.0, abs(losses[0])), losses
+    torch.cuda.synchronize()
+    _ext.check_status(tok)
+    for ga, gb, gc in zip(e_nccl.groups, e_fused.groups, e_sc.groups):
+        a, b, c = ga.flat.float(), gb.flat.float(), gc.flat.float()
+        assert (a - b).abs().max().item() < 3e-2, "fused(global) vs nccl(global) parameters differ"
+        err = (a - c).abs().max().item()
+        assert err < 3e-2, f"scatter vs nccl parameters differ by {err}"
+        ref = c.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(ref, c), "ranks hold different parameters after the all-gather"
+        lo, hi = gc.shard
+        assert float(gc.g_task[lo:hi].abs().max()) == 0.0, "the consumed shard was not cleared"
+
+
 def sp_matches_single(rank, world, dev):
     """Forward + backward of the model over a sequence split across ranks equals the unsplit run."""
     T = 256 * world

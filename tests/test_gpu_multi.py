@@ -30,6 +30,10 @@ def test_fused_collective_matches_nccl():
     _run("engine_fused_vs_nccl")
 
 
+def test_epilogue_reduce_scatter_matches_nccl():
+    _run("engine_scatter_vs_nccl")
+
+
 def test_sequence_parallel_matches_single_gpu():
     _run("sp_matches_single")
 
