@@ -83,45 +83,90 @@ __device__ __forceinline__ float row_scale_for(const GemmEpilogue& e, int m) {
   return 1.0f;
 }
 
-// v: 32 consecutive columns starting at n0 of row m. Returns this chunk's sum of squares of
-// the stored values (for the RMSNorm that follows the activation).
-__device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, int N, int m, int n0, float rs,
-                                                float rowcoef, float (&v)[32]) {
+// Per-warp staging area for the bf16 side of the epilogue: 32 rows x 64 bytes. A thread owns one row of the
+// accumulator, but a warp-wide store of one 16-byte piece per thread touches 32 different cache lines; the
+// rows therefore go through shared memory and leave (or arrive) as 8 rows x 64 contiguous bytes per
+// instruction. The 16-byte slots are XOR-swizzled so both access patterns are free of bank conflicts.
+constexpr int EPI_STAGE_BYTES_PER_WARP = 32 * 64;
+constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_STAGE_BYTES_PER_WARP;
+
+__device__ __forceinline__ uint32_t stage_off(int row, int slot) {
+  return (uint32_t)(row * 64 + ((slot ^ ((row >> 1) & 3)) << 4));
+}
+
+// this lane's row (32 bf16 in w) -> global rows base[row * ld + 0..31], rows < rows_valid
+__device__ __forceinline__ void store_rows_bf16(uint8_t* stage, int lane, const uint32_t (&w)[16],
+                                                __nv_bfloat16* base, int64_t ld, int rows_valid) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    *reinterpret_cast<uint4*>(stage + stage_off(lane, q)) = make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
+  __syncwarp();
+  const int r_in = lane >> 2, slot = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int row = r_in + 8 * j;
+    const uint4 u = *reinterpret_cast<const uint4*>(stage + stage_off(row, slot));
+    if (row < rows_valid) *reinterpret_cast<uint4*>(base + (size_t)row * ld + slot * 8) = u;
+  }
+  __syncwarp();
+}
+
+// global rows base[row * ld + 0..31] -> this lane's row in w (rows >= rows_valid read as zero)
+__device__ __forceinline__ void load_rows_bf16(uint8_t* stage, int lane, uint32_t (&w)[16],
+                                               const __nv_bfloat16* base, int64_t ld, int rows_valid) {
+  const int r_in = lane >> 2, slot = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int row = r_in + 8 * j;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (row < rows_valid) u = *reinterpret_cast<const uint4*>(base + (size_t)row * ld + slot * 8);
+    *reinterpret_cast<uint4*>(stage + stage_off(row, slot)) = u;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint4 u = *reinterpret_cast<const uint4*>(stage + stage_off(lane, q));
+    w[q * 4] = u.x; w[q * 4 + 1] = u.y; w[q * 4 + 2] = u.z; w[q * 4 + 3] = u.w;
+  }
+  __syncwarp();
+}
+
+// v: 32 consecutive columns starting at n0 of row m = m_warp + lane. Warp-collective (all lanes call it with
+// the same n0). Returns this chunk's sum of squares of the stored values (for the RMSNorm that follows).
+__device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, int N, int m_warp, int lane, int n0,
+                                                float rs, float rowcoef, float (&v)[32], uint8_t* stage) {
   float ssq = 0.0f;
-  if (m >= M || n0 >= N) return 0.0f;
+  if (m_warp >= M || n0 >= N) return 0.0f;   // warp-uniform
+  const int m = m_warp + lane;
+  const int rows_valid = min(32, M - m_warp);
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = v[j] * rs + load_bias(e, n0 + j);
 
   if (e.aux != nullptr) {
-    const uint4* ap = reinterpret_cast<const uint4*>(e.aux + (size_t)m * e.aux_ld + n0);
+    uint32_t w[16];
+    load_rows_bf16(stage, lane, w, e.aux + (size_t)m_warp * e.aux_ld + n0, e.aux_ld, rows_valid);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint4 u = ap[q];
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float2 a = unpack_bf16x2(w[t]);
-        const int j = q * 8 + t * 2;
-        if (e.aux_mode == AUX_ADD) {
-          v[j] += a.x;
-          v[j + 1] += a.y;
-        } else if (e.aux_mode == AUX_MUL_SILU_GRAD) {
-          v[j] *= silu_grad_(a.x);
-          v[j + 1] *= silu_grad_(a.y);
-        } else {  // AUX_RMS_SILU_BWD: (v - silu(aux) * rowcoef) * silu'(aux)
-          v[j] = (v[j] - siluf_(a.x) * rowcoef) * silu_grad_(a.x);
-          v[j + 1] = (v[j + 1] - siluf_(a.y) * rowcoef) * silu_grad_(a.y);
-        }
+    for (int t = 0; t < 16; ++t) {
+      const float2 a = unpack_bf16x2(w[t]);
+      const int j = t * 2;
+      if (e.aux_mode == AUX_ADD) {
+        v[j] += a.x;
+        v[j + 1] += a.y;
+      } else if (e.aux_mode == AUX_MUL_SILU_GRAD) {
+        v[j] *= silu_grad_(a.x);
+        v[j + 1] *= silu_grad_(a.y);
+      } else {  // AUX_RMS_SILU_BWD: (v - silu(aux) * rowcoef) * silu'(aux)
+        v[j] = (v[j] - siluf_(a.x) * rowcoef) * silu_grad_(a.x);
+        v[j + 1] = (v[j + 1] - siluf_(a.y) * rowcoef) * silu_grad_(a.y);
       }
     }
   }
 
   if (e.pre_out != nullptr) {
-    uint4* pp = reinterpret_cast<uint4*>(e.pre_out + (size_t)m * e.pre_ld + n0);
+    uint32_t w[16];
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
-      pp[q] = make_uint4(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
-                         pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]));
+    for (int t = 0; t < 16; ++t) w[t] = pack_bf16x2(v[t * 2], v[t * 2 + 1]);
+    store_rows_bf16(stage, lane, w, e.pre_out + (size_t)m_warp * e.pre_ld + n0, e.pre_ld, rows_valid);
   }
 
   if (e.act == ACT_SILU) {
@@ -130,6 +175,7 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
   }
 
   if (e.out_f32) {
+    if (m >= M) return 0.0f;
     float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(e.out) + (size_t)m * e.out_ld + n0);
     if (e.peer_out != nullptr) {
       // gradient reduce-scatter from the epilogue: add this chunk into the owner rank's flat buffer
@@ -150,28 +196,26 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
       op[q] = o;
     }
   } else {
-    uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)m * e.out_ld + n0);
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)m_warp * e.out_ld + n0;
+    if (e.accumulate) {
+      uint32_t old[16];
+      load_rows_bf16(stage, lane, old, ob, e.out_ld, rows_valid);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint32_t w[4];
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float a = v[q * 8 + t * 2], b = v[q * 8 + t * 2 + 1];
-        w[t] = pack_bf16x2(a, b);
-        const float2 r = unpack_bf16x2(w[t]);
-        ssq += r.x * r.x + r.y * r.y;
+      for (int t = 0; t < 16; ++t) {
+        const float2 o = unpack_bf16x2(old[t]);
+        v[t * 2] += o.x;
+        v[t * 2 + 1] += o.y;
       }
-      if (e.accumulate) {
-        const uint4 old = op[q];
-        const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 o = unpack_bf16x2(ow[t]);
-          w[t] = pack_bf16x2(v[q * 8 + t * 2] + o.x, v[q * 8 + t * 2 + 1] + o.y);
-        }
-      }
-      op[q] = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    uint32_t w[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      w[t] = pack_bf16x2(v[t * 2], v[t * 2 + 1]);
+      const float2 r = unpack_bf16x2(w[t]);
+      ssq += r.x * r.x + r.y * r.y;
+    }
+    store_rows_bf16(stage, lane, w, ob, e.out_ld, rows_valid);
+    if (m >= M) ssq = 0.0f;
   }
   return ssq;
 }
@@ -254,7 +298,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const GemmShape g, const GemmEpilogue e, Status* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + BF16_STAGES * BF16_STAGE_BYTES);
+  uint8_t* stage_all = smem + BF16_STAGES * BF16_STAGE_BYTES;
+  PipeBars* bars = reinterpret_cast<PipeBars*>(stage_all + EPI_STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pipe_setup<BF16_STAGES, BF16_ACC>(bars, warp, lane, BF16_ACC * BF16_BN, &tmap_a, &tmap_b);
@@ -355,6 +400,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     const int ew = warp - 2;
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;        // TMEM lane quarter this warp may access
     const int col_half = ew >> 2;        // which 128 of the tile's 256 columns
     int acc = 0;
@@ -389,7 +435,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
-        ssq += epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 128 + c * 32, rs, rc, v);
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage);
       }
       if (e.ssq_out != nullptr && m < g.M && n0 + col_half * 128 < g.N)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 128 + col_half)] = ssq;
@@ -415,7 +461,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 const GemmShape g, const GemmEpilogue e, Status* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + FP8_STAGES * FP8_STAGE_BYTES);
+  uint8_t* stage_all = smem + FP8_STAGES * FP8_STAGE_BYTES;
+  PipeBars* bars = reinterpret_cast<PipeBars*>(stage_all + EPI_STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pipe_setup<FP8_STAGES, FP8_ACC>(bars, warp, lane, FP8_ACC * FP8_BN, &tmap_a, &tmap_b);
@@ -496,6 +543,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else {
     const int ew = warp - 2;
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;
     const int col_half = ew >> 2;  // which 64 of the tile's 128 columns
     int acc = 0;
@@ -554,7 +602,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = accum[c * 32 + j];
-        ssq += epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 64 + c * 32, rs, rc, v);
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + c * 32, rs, rc, v, stage);
       }
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
@@ -586,7 +634,8 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                    const GemmShape g, const GemmEpilogue e, Status* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + MX_STAGES * MX_STAGE_BYTES);
+  uint8_t* stage_all = smem + MX_STAGES * MX_STAGE_BYTES;
+  PipeBars* bars = reinterpret_cast<PipeBars*>(stage_all + EPI_STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pipe_setup<MX_STAGES, MX_ACC>(bars, warp, lane, MX_TMEM_COLS, &tmap_a, &tmap_b);
@@ -681,6 +730,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
   } else {
     const int ew = warp - 2;
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;
     const int col_half = ew >> 2;        // which 64 of the tile's 128 columns
     int acc = 0;
@@ -709,10 +759,10 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
-      float ssq = epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 64, rs, rc, v);
+      float ssq = epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64, rs, rc, v, stage);
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
-      ssq += epilogue_chunk(e, g.M, g.N, m, n0 + col_half * 64 + 32, rs, rc, v);
+      ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, v, stage);
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
       if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
@@ -794,7 +844,7 @@ const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const G
   else err = make_tensor_map_2d(&tb, op.b, 2, g.K, g.N, op.b_ld, BF16_BK);
   if (err) return err;
   static bool attr_set = false;
-  const int smem = BF16_STAGES * BF16_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem = BF16_STAGES * BF16_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return "cudaFuncSetAttribute(gemm_bf16_kernel) failed";
@@ -821,7 +871,7 @@ const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const Ge
   err = make_tensor_map_2d(&tb, op.b, 1, g.N, g.K, op.b_ld, FP8_BN);
   if (err) return err;
   static bool attr_set = false;
-  const int smem = FP8_STAGES * FP8_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem = FP8_STAGES * FP8_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return "cudaFuncSetAttribute(gemm_fp8_kernel) failed";
@@ -848,7 +898,7 @@ const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const
   err = make_tensor_map_2d(&tb, op.b, 1, g.N, g.K, op.b_ld, MX_BN);
   if (err) return err;
   static bool attr_set = false;
-  const int smem = MX_STAGES * MX_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem = MX_STAGES * MX_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_fp8_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return "cudaFuncSetAttribute(gemm_fp8_mx_kernel) failed";

@@ -155,7 +155,13 @@ def gemm_bf16(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=BF16, accumul
     M = a.shape[1] if a_mn else a.shape[0]
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        if out_dtype == F32:
+            # a fresh fp32 result is a weight-gradient shape (few tiles, long reduction): start from zeros and
+            # accumulate, which lets the launcher split the reduction over the idle SMs
+            out = torch.zeros(M, N, dtype=F32, device=a.device)
+            accumulate = True
+        else:
+            out = torch.empty(M, N, dtype=out_dtype, device=a.device)
     K.gemm_bf16(a, b, a_mn, b_mn, out, accumulate, bias, row_scale, ssq_in, norm_dim, norm_eps, aux, aux_mode,
                 rowcoef, pre_out, act, ssq_out)
     return out
