@@ -39,6 +39,7 @@ struct __align__(8) PipeBars {
   uint64_t empty[8];
   uint64_t tmem_full[4];
   uint64_t tmem_empty[4];
+  uint64_t aux_full[8];    // one per epilogue warp: its slice of the next tile's auxiliary input has landed
   uint32_t tmem_base;
   int abort;
 };
@@ -67,10 +68,27 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // ---------------------------------------------------------------------------------------
 // fused epilogue on one row x 32 columns held in registers
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ float load_bias(const GemmEpilogue& e, int n) {
-  if (e.bias == nullptr) return 0.0f;
+__device__ __forceinline__ float load_bias(const GemmEpilogue& e, int n, int N) {
+  if (e.bias == nullptr || n >= N) return 0.0f;
   return e.bias_f32 ? reinterpret_cast<const float*>(e.bias)[n]
                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.bias)[n]);
+}
+
+constexpr int AUX_BOX_BYTES = 32 * 128;
+
+// A global load issued by an epilogue warp queues behind the bulk tensor loads the producer keeps in flight
+// (several stages, microseconds of traffic), so the epilogue must not wait for one per chunk. Per-row and
+// per-column vectors are fetched before the wait for the accumulator; the auxiliary matrix is fetched one
+// tile ahead by bulk tensor copies into a per-warp buffer (one thread, one or two boxes per tile).
+// `boxes` boxes of 32 rows x 64 bf16 columns (4 KB each, 128-byte swizzle) starting at (m_warp, nbase).
+__device__ __forceinline__ bool aux_prefetch(const CUtensorMap* tmap, int M, int N, int m_warp, int lane, int nbase,
+                                             int boxes, uint32_t buf, uint32_t bar) {
+  if (m_warp >= M || nbase >= N) return false;     // warp-uniform
+  if (lane == 0) {
+    mbar_arrive_expect_tx(bar, (uint32_t)(boxes * AUX_BOX_BYTES));
+    for (int b = 0; b < boxes; ++b) tma_load_2d(buf + b * AUX_BOX_BYTES, tmap, bar, nbase + b * 64, m_warp);
+  }
+  return true;
 }
 
 __device__ __forceinline__ float row_scale_for(const GemmEpilogue& e, int m) {
@@ -133,18 +151,31 @@ __device__ __forceinline__ void load_rows_bf16(uint8_t* stage, int lane, uint32_
 
 // v: 32 consecutive columns starting at n0 of row m = m_warp + lane. Warp-collective (all lanes call it with
 // the same n0). Returns this chunk's sum of squares of the stored values (for the RMSNorm that follows).
+//
+// bias_lane: the bias of column n0 + lane (0 without bias). aux_row: this lane's row inside the prefetched
+// box (128 bytes, 16-byte pieces XOR-swizzled with the row number), the chunk starting at piece aux_piece0;
+// null to read the auxiliary values from global memory here.
 __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, int N, int m_warp, int lane, int n0,
-                                                float rs, float rowcoef, float (&v)[32], uint8_t* stage) {
+                                                float rs, float rowcoef, float (&v)[32], uint8_t* stage,
+                                                float bias_lane, const uint8_t* aux_row, int aux_piece0) {
   float ssq = 0.0f;
   if (m_warp >= M || n0 >= N) return 0.0f;   // warp-uniform
   const int m = m_warp + lane;
   const int rows_valid = min(32, M - m_warp);
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = v[j] * rs + load_bias(e, n0 + j);
+  for (int j = 0; j < 32; ++j) v[j] = v[j] * rs + __shfl_sync(0xffffffffu, bias_lane, j);
 
   if (e.aux != nullptr) {
     uint32_t w[16];
-    load_rows_bf16(stage, lane, w, e.aux + (size_t)m_warp * e.aux_ld + n0, e.aux_ld, rows_valid);
+    if (aux_row != nullptr) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 u = *reinterpret_cast<const uint4*>(aux_row + (((aux_piece0 + q) ^ (lane & 7)) << 4));
+        w[q * 4] = u.x; w[q * 4 + 1] = u.y; w[q * 4 + 2] = u.z; w[q * 4 + 3] = u.w;
+      }
+    } else {
+      load_rows_bf16(stage, lane, w, e.aux + (size_t)m_warp * e.aux_ld + n0, e.aux_ld, rows_valid);
+    }
 #pragma unroll
     for (int t = 0; t < 16; ++t) {
       const float2 a = unpack_bf16x2(w[t]);
@@ -237,6 +268,7 @@ __device__ __forceinline__ void pipe_setup(PipeBars* bars, int warp, int lane, u
       mbar_init(smem_u32(&bars->tmem_full[a]), 1);
       mbar_init(smem_u32(&bars->tmem_empty[a]), EPI_WARPS);
     }
+    for (int w = 0; w < EPI_WARPS; ++w) mbar_init(smem_u32(&bars->aux_full[w]), 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -287,19 +319,23 @@ __device__ __forceinline__ uint64_t desc_at(uint32_t hi, uint32_t lo) {
 // ---------------------------------------------------------------------------------------
 constexpr int BF16_BN = 256;
 constexpr int BF16_BK = 64;
-constexpr int BF16_STAGES = 4;
 constexpr int BF16_ACC = 2;
+constexpr int BF16_AUX_BYTES = EPI_WARPS * 2 * AUX_BOX_BYTES;   // two boxes (128 columns) per epilogue warp
 constexpr int BF16_A_BYTES = BM * STAGE_ROW_BYTES;       // 16 KB
 constexpr int BF16_B_BYTES = BF16_BN * STAGE_ROW_BYTES;  // 32 KB
 constexpr int BF16_STAGE_BYTES = BF16_A_BYTES + BF16_B_BYTES;
 
+// AUX = the epilogue reads an auxiliary matrix: one pipeline stage is given up for the per-warp prefetch buffers.
+template <bool AUX>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmShape g, const GemmEpilogue e, Status* status) {
+                 const __grid_constant__ CUtensorMap tmap_aux, const GemmShape g, const GemmEpilogue e, Status* status) {
+  constexpr int BF16_STAGES = AUX ? 3 : 4;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_all = smem + BF16_STAGES * BF16_STAGE_BYTES;
-  PipeBars* bars = reinterpret_cast<PipeBars*>(stage_all + EPI_STAGE_BYTES);
+  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES;
+  PipeBars* bars = reinterpret_cast<PipeBars*>(aux_all + (AUX ? BF16_AUX_BYTES : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pipe_setup<BF16_STAGES, BF16_ACC>(bars, warp, lane, BF16_ACC * BF16_BN, &tmap_a, &tmap_b);
@@ -405,6 +441,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int col_half = ew >> 2;        // which 128 of the tile's 256 columns
     int acc = 0;
     uint32_t acc_ph = 0;
+    uint8_t* aux_buf = aux_all + ew * (2 * AUX_BOX_BYTES);
+    const uint32_t aux_bar = smem_u32(&bars->aux_full[ew]);
+    uint32_t aux_ph = 0;
+    bool aux_pending = false;
+    if (AUX && blockIdx.x < n_work) {
+      int mb_, nb_;
+      tile_coords(blockIdx.x % n_tiles, n_tiles_m, n_tiles_n, mb_, nb_);
+      aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb_ * BM + quarter * 32, lane, nb_ * BF16_BN + col_half * 128, 2,
+                                 smem_u32(aux_buf), aux_bar);
+    }
     for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
       const int tile = work % n_tiles;
       int mb_, nb_;
@@ -413,9 +459,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int m = m0 + quarter * 32 + lane;
       const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
       const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
+      float bias_c[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) bias_c[c] = load_bias(e, n0 + col_half * 128 + c * 32 + lane, g.N);
       if (!mbar_wait_warp(tfull0 + 8 * acc, acc_ph)) {
         raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 13, acc);
         break;
+      }
+      if (AUX && aux_pending) {
+        if (!mbar_wait_warp(aux_bar, aux_ph)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 14, ew);
+          break;
+        }
+        aux_ph ^= 1;
       }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BF16_BN + col_half * 128;
@@ -435,7 +491,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
-        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage);
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage,
+                              bias_c[c], AUX ? aux_buf + (c >> 1) * AUX_BOX_BYTES + lane * 128 : nullptr, (c & 1) * 4);
+      }
+      if (AUX) {   // this tile's slice is consumed: fetch the next tile's
+        __syncwarp();
+        aux_pending = false;
+        const int next = work + gridDim.x;
+        if (next < n_work) {
+          int mb2, nb2;
+          tile_coords(next % n_tiles, n_tiles_m, n_tiles_n, mb2, nb2);
+          aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb2 * BM + quarter * 32, lane,
+                                     nb2 * BF16_BN + col_half * 128, 2, smem_u32(aux_buf), aux_bar);
+        }
       }
       if (e.ssq_out != nullptr && m < g.M && n0 + col_half * 128 < g.N)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 128 + col_half)] = ssq;
@@ -602,7 +670,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = accum[c * 32 + j];
-        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + c * 32, rs, rc, v, stage);
+        const int nc = n0 + col_half * 64 + c * 32;
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, nc, rs, rc, v, stage, load_bias(e, nc + lane, g.N),
+                              nullptr, 0);
       }
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
@@ -620,8 +690,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 // activation and 128x128 weight blocks the four K steps of a stage share their scale bytes.
 constexpr int MX_BN = 128;
 constexpr int MX_BK = 128;
-constexpr int MX_STAGES = 6;
 constexpr int MX_ACC = 2;
+constexpr int MX_AUX_BYTES = EPI_WARPS * AUX_BOX_BYTES;        // one box (64 columns) per epilogue warp
 constexpr int MX_A_BYTES = BM * STAGE_ROW_BYTES;
 constexpr int MX_B_BYTES = MX_BN * STAGE_ROW_BYTES;
 constexpr int MX_SF_BYTES = 512;
@@ -629,13 +699,16 @@ constexpr int MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 2 * MX_SF_BYTES;   // 3
 constexpr int MX_TMEM_COLS = 512;
 constexpr int MX_SF_COL0 = MX_ACC * MX_BN;                                   // scale columns follow the accumulators
 
+template <bool AUX>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const GemmShape g, const GemmEpilogue e, Status* status) {
+                   const __grid_constant__ CUtensorMap tmap_aux, const GemmShape g, const GemmEpilogue e, Status* status) {
+  constexpr int MX_STAGES = AUX ? 5 : 6;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_all = smem + MX_STAGES * MX_STAGE_BYTES;
-  PipeBars* bars = reinterpret_cast<PipeBars*>(stage_all + EPI_STAGE_BYTES);
+  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES;
+  PipeBars* bars = reinterpret_cast<PipeBars*>(aux_all + (AUX ? MX_AUX_BYTES : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pipe_setup<MX_STAGES, MX_ACC>(bars, warp, lane, MX_TMEM_COLS, &tmap_a, &tmap_b);
@@ -735,6 +808,16 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int col_half = ew >> 2;        // which 64 of the tile's 128 columns
     int acc = 0;
     uint32_t acc_ph = 0;
+    uint8_t* aux_buf = aux_all + ew * AUX_BOX_BYTES;
+    const uint32_t aux_bar = smem_u32(&bars->aux_full[ew]);
+    uint32_t aux_ph = 0;
+    bool aux_pending = false;
+    if (AUX && blockIdx.x < n_work) {
+      int mb_, nb_;
+      tile_coords(blockIdx.x % n_tiles, n_tiles_m, n_tiles_n, mb_, nb_);
+      aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb_ * BM + quarter * 32, lane, nb_ * MX_BN + col_half * 64, 1,
+                                 smem_u32(aux_buf), aux_bar);
+    }
     for (int work = blockIdx.x; work < n_work && !aborted(bars); work += gridDim.x) {
       const int tile = work % n_tiles;
       int mb_, nb_;
@@ -743,9 +826,18 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       const int m = m0 + quarter * 32 + lane;
       const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
       const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
+      const float bias0 = load_bias(e, n0 + col_half * 64 + lane, g.N);
+      const float bias1 = load_bias(e, n0 + col_half * 64 + 32 + lane, g.N);
       if (!mbar_wait_warp(tfull0 + 8 * acc, acc_ph)) {
         raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 53, acc);
         break;
+      }
+      if (AUX && aux_pending) {
+        if (!mbar_wait_warp(aux_bar, aux_ph)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 54, ew);
+          break;
+        }
+        aux_ph ^= 1;
       }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * MX_BN + col_half * 64;
@@ -759,12 +851,26 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
-      float ssq = epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64, rs, rc, v, stage);
+      const uint8_t* aux_row = AUX ? aux_buf + lane * 128 : nullptr;
+      float ssq = epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64, rs, rc, v, stage, bias0,
+                                 aux_row, 0);
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
-      ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, v, stage);
+      ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, v, stage, bias1,
+                            aux_row, 4);
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
+      if (AUX) {   // this tile's slice is consumed: fetch the next tile's
+        __syncwarp();
+        aux_pending = false;
+        const int next = work + gridDim.x;
+        if (next < n_work) {
+          int mb2, nb2;
+          tile_coords(next % n_tiles, n_tiles_m, n_tiles_n, mb2, nb2);
+          aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb2 * BM + quarter * 32, lane, nb2 * MX_BN + col_half * 64, 1,
+                                     smem_u32(aux_buf), aux_bar);
+        }
+      }
       if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
     }
   }
@@ -844,9 +950,13 @@ const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const G
   else err = make_tensor_map_2d(&tb, op.b, 2, g.K, g.N, op.b_ld, BF16_BK);
   if (err) return err;
   static bool attr_set = false;
-  const int smem = BF16_STAGES * BF16_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const bool aux = e.aux != nullptr;
+  const int smem_plain = 4 * BF16_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_aux = 3 * BF16_STAGE_BYTES + EPI_STAGE_BYTES + BF16_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem = aux ? smem_aux : smem_plain;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_aux) != cudaSuccess)
       return "cudaFuncSetAttribute(gemm_bf16_kernel) failed";
     attr_set = true;
   }
@@ -857,7 +967,13 @@ const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const G
   es.atomic = gs.splits > 1;
   const int work = tiles * gs.splits;
   const int grid = work < sm_count() ? work : sm_count();
-  gemm_bf16_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, gs, es, status);
+  if (aux) {
+    CUtensorMap tx;
+    if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
+    gemm_bf16_kernel<true><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, tx, gs, es, status);
+  } else {
+    gemm_bf16_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, ta, gs, es, status);
+  }
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_bf16_kernel launch failed";
 }
 
@@ -898,9 +1014,13 @@ const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const
   err = make_tensor_map_2d(&tb, op.b, 1, g.N, g.K, op.b_ld, MX_BN);
   if (err) return err;
   static bool attr_set = false;
-  const int smem = MX_STAGES * MX_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const bool aux = e.aux != nullptr;
+  const int smem_plain = 6 * MX_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_aux = 5 * MX_STAGE_BYTES + EPI_STAGE_BYTES + MX_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem = aux ? smem_aux : smem_plain;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_fp8_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_fp8_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_fp8_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_aux) != cudaSuccess)
       return "cudaFuncSetAttribute(gemm_fp8_mx_kernel) failed";
     attr_set = true;
   }
@@ -911,7 +1031,13 @@ const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const
   es.atomic = gs.splits > 1;
   const int work = tiles * gs.splits;
   const int grid = work < sm_count() ? work : sm_count();
-  gemm_fp8_mx_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, gs, es, status);
+  if (aux) {
+    CUtensorMap tx;
+    if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
+    gemm_fp8_mx_kernel<true><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, tx, gs, es, status);
+  } else {
+    gemm_fp8_mx_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, ta, gs, es, status);
+  }
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_mx_kernel launch failed";
 }
 
