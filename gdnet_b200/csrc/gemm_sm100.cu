@@ -25,6 +25,8 @@
 // raises a CTA-wide abort flag, drains, frees its TMEM and returns.
 #include "gemm_sm100.h"
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace gd {
@@ -514,6 +516,249 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------------------
+// bf16 kernel on CTA pairs
+// ---------------------------------------------------------------------------------------
+// With a 1024-deep reduction these GEMMs are bound by the traffic from L2 into shared memory, not by the
+// tensor cores. A pair of CTAs on neighbouring SMs shares one 256 x 256 tile: each CTA loads its own 128 rows
+// of A but only half of B (128 of the 256 N rows), and tcgen05.mma.cta_group::2 reads both halves. Per CTA
+// and K block that is 32 KB instead of 48 KB for the same 128 x 256 accumulator.
+//
+// Barriers: full[s] lives in the rank-0 CTA and counts the bytes of both CTAs' loads; empty[s] and
+// tmem_full[a] exist in both CTAs and are signalled together by the commit of the MMA thread (rank 0);
+// tmem_empty[a] lives in rank 0 and collects the epilogue warps of both CTAs.
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_B_ROWS = 128;                               // N rows of B held by each CTA
+constexpr int PAIR_A_BYTES = BM * STAGE_ROW_BYTES;            // 16 KB
+constexpr int PAIR_B_BYTES = PAIR_B_ROWS * STAGE_ROW_BYTES;   // 16 KB
+constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_TMEM_COLS = BF16_ACC * PAIR_BN;
+
+template <bool AUX>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_aux, const GemmShape g, const GemmEpilogue e,
+                      Status* status) {
+  constexpr int STAGES = AUX ? 4 : 6;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_all = smem + STAGES * PAIR_STAGE_BYTES;
+  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES;
+  PipeBars* bars = reinterpret_cast<PipeBars*>(aux_all + (AUX ? BF16_AUX_BYTES : 0));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < BF16_ACC; ++a) {
+      mbar_init(smem_u32(&bars->tmem_full[a]), 1);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), 2 * EPI_WARPS);
+    }
+    for (int w = 0; w < EPI_WARPS; ++w) mbar_init(smem_u32(&bars->aux_full[w]), 1);
+    bars->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&bars->tmem_base), PAIR_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();     // the peer's barriers exist before anything of this CTA can signal them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int n_tiles_n = (g.N + PAIR_BN - 1) / PAIR_BN;
+  const int n_tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = n_tiles_m * n_tiles_n;
+  const int kblocks = (g.K + BF16_BK - 1) / BF16_BK;
+  const int kb_per = (kblocks + g.splits - 1) / g.splits;
+  const int n_work = n_tiles * g.splits;
+  const uint32_t smem0 = smem_u32(smem);
+  const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
+  const uint32_t tfull0 = smem_u32(&bars->tmem_full[0]), tempty0 = smem_u32(&bars->tmem_empty[0]);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t full_lead0 = map_to_cta(full0, 0);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int work = pair; work < n_work && ok; work += n_pairs) {
+        const int tile = work % n_tiles, kb0 = (work / n_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+        int mb_, nb_;
+        tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+        const int m0 = mb_ * 2 * BM + (int)rank * BM, nB = nb_ * PAIR_BN + (int)rank * PAIR_B_ROWS;
+        int kx = kb0 * BF16_BK;
+        for (int kb = kb0; kb < kb1; ++kb, kx += BF16_BK) {
+          if (!wait_fast(empty0 + 8 * s, ph ^ 1)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 60, s);
+            ok = false;
+            break;
+          }
+          const uint32_t full = full_lead0 + 8 * s;
+          const uint32_t a_dst = smem0 + s * PAIR_STAGE_BYTES;
+          const uint32_t b_dst = a_dst + PAIR_A_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
+          if (!g.a_mn) {
+            tma_load_2d_pair(a_dst, &tmap_a, full, kx, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d_pair(a_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_a, full, m0 + i * 64, kx);
+          }
+          if (!g.b_mn) {
+            tma_load_2d_pair(b_dst, &tmap_b, full, kx, nB);
+          } else {
+#pragma unroll
+            for (int i = 0; i < PAIR_B_ROWS / 64; ++i)
+              tma_load_2d_pair(b_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_b, full, nB + i * 64, kx);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (aborted(bars)) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_instr_desc(1, 1, g.a_mn ? 1 : 0, g.b_mn ? 1 : 0, 2 * BM, PAIR_BN);
+      const uint32_t a_lbo = g.a_mn ? BF16_BK * STAGE_ROW_BYTES : 16, b_lbo = g.b_mn ? BF16_BK * STAGE_ROW_BYTES : 16;
+      const uint32_t a_step = g.a_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2, b_step = g.b_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2;
+      const uint64_t a_tmpl = make_smem_desc(smem0, a_lbo, 1024), b_tmpl = make_smem_desc(smem0 + PAIR_A_BYTES, b_lbo, 1024);
+      const uint32_t a_hi = (uint32_t)(a_tmpl >> 32), a_lo0 = (uint32_t)a_tmpl;
+      const uint32_t b_hi = (uint32_t)(b_tmpl >> 32), b_lo0 = (uint32_t)b_tmpl;
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int work = pair; work < n_work && ok; work += n_pairs) {
+        const int nkb = min(kblocks, (work / n_tiles) * kb_per + kb_per) - (work / n_tiles) * kb_per;
+        if (!wait_fast(tempty0 + 8 * acc, acc_ph ^ 1)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 61, acc);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+        uint32_t accumulate = 0;
+        for (int i = 0; i < nkb; ++i) {
+          if (!wait_fast(full0 + 8 * s, ph)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 62, s);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_lo = a_lo0 + s * (PAIR_STAGE_BYTES >> 4), b_lo = b_lo0 + s * (PAIR_STAGE_BYTES >> 4);
+#pragma unroll
+          for (int k = 0; k < BF16_BK / 16; ++k) {
+            mma_bf16_pair(d_tmem, desc_at(a_hi, a_lo + k * a_step), desc_at(b_hi, b_lo + k * b_step), idesc, accumulate);
+            accumulate = 1;
+          }
+          mma_commit_pair(empty0 + 8 * s);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok || aborted(bars)) break;
+        mma_commit_pair(tfull0 + 8 * acc);
+        if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
+    const int quarter = warp & 3;        // TMEM lane quarter this warp may access
+    const int col_half = ew >> 2;        // which 128 of the tile's 256 columns
+    const uint32_t tempty_lead0 = map_to_cta(tempty0, 0);
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    uint8_t* aux_buf = aux_all + ew * (2 * AUX_BOX_BYTES);
+    const uint32_t aux_bar = smem_u32(&bars->aux_full[ew]);
+    uint32_t aux_ph = 0;
+    bool aux_pending = false;
+    if (AUX && pair < n_work) {
+      int mb_, nb_;
+      tile_coords(pair % n_tiles, n_tiles_m, n_tiles_n, mb_, nb_);
+      aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb_ * 2 * BM + (int)rank * BM + quarter * 32, lane,
+                                 nb_ * PAIR_BN + col_half * 128, 2, smem_u32(aux_buf), aux_bar);
+    }
+    for (int work = pair; work < n_work && !aborted(bars); work += n_pairs) {
+      const int tile = work % n_tiles;
+      int mb_, nb_;
+      tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+      const int m0 = mb_ * 2 * BM + (int)rank * BM, n0 = nb_ * PAIR_BN;
+      const int m = m0 + quarter * 32 + lane;
+      const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
+      const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
+      float bias_c[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) bias_c[c] = load_bias(e, n0 + col_half * 128 + c * 32 + lane, g.N);
+      if (!mbar_wait_warp(tfull0 + 8 * acc, acc_ph)) {
+        raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 63, acc);
+        break;
+      }
+      if (AUX && aux_pending) {
+        if (!mbar_wait_warp(aux_bar, aux_ph)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 64, ew);
+          break;
+        }
+        aux_ph ^= 1;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * PAIR_BN + col_half * 128;
+      float ssq = 0.0f;
+      uint32_t raw[2][32];
+      tmem_ld_32x32(t_row, raw[0]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c + 1 < 4) tmem_ld_32x32(t_row + (c + 1) * 32, raw[(c + 1) & 1]);
+        if (c == 3) {   // everything is in registers: hand the accumulator back before the last chunk's stores
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_lead0 + 8 * acc);
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage,
+                              bias_c[c], AUX ? aux_buf + (c >> 1) * AUX_BOX_BYTES + lane * 128 : nullptr, (c & 1) * 4);
+      }
+      if (AUX) {
+        __syncwarp();
+        aux_pending = false;
+        const int next = work + n_pairs;
+        if (next < n_work) {
+          int mb2, nb2;
+          tile_coords(next % n_tiles, n_tiles_m, n_tiles_n, mb2, nb2);
+          aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb2 * 2 * BM + (int)rank * BM + quarter * 32, lane,
+                                     nb2 * PAIR_BN + col_half * 128, 2, smem_u32(aux_buf), aux_bar);
+        }
+      }
+      if (e.ssq_out != nullptr && m < g.M && n0 + col_half * 128 < g.N)
+        e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 128 + col_half)] = ssq;
+      if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  // teardown: neither CTA may leave (or free its TMEM) while the other can still read its shared memory,
+  // write its TMEM or signal its barriers
+  tc_fence_before_sync();
+  __syncthreads();
+  if (aborted(bars)) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, PAIR_TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // block-scaled FP8 kernel
 // ---------------------------------------------------------------------------------------
 constexpr int FP8_BN = 128;
@@ -938,9 +1183,99 @@ static int pick_splits(int tiles, int kblocks, const GemmEpilogue& e) {
   return (kblocks + per - 1) / per;       // no share may be empty: an empty one would publish a stale accumulator
 }
 
+// CTA pairs that can be resident at once (a pair needs two free SMs of one TPC; fewer than sm_count / 2 when a
+// GPC has an odd number of usable SMs). 0 = cluster launch not possible, use the single-CTA kernel.
+template <typename KernelT>
+static int max_active_pairs(KernelT kernel, int smem) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(sm_count() & ~1));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+static bool pair_kernels_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("GDNET_GEMM_PAIR");
+    on = (v == nullptr || v[0] != '0') ? 1 : 0;
+  }
+  return on == 1;
+}
+
+static const char* launch_gemm_bf16_pair(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e,
+                                         Status* status, cudaStream_t stream, bool* launched) {
+  *launched = false;
+  static int pairs_plain = -1, pairs_aux = -1;
+  const bool aux = e.aux != nullptr;
+  const int smem_plain = 6 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_aux = 4 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + BF16_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
+  if (pairs_plain < 0) {
+    pairs_plain = pairs_aux = 0;
+    if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) == cudaSuccess &&
+        cudaFuncSetAttribute(gemm_bf16_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_aux) == cudaSuccess) {
+      pairs_plain = max_active_pairs(gemm_bf16_pair_kernel<false>, smem_plain);
+      pairs_aux = max_active_pairs(gemm_bf16_pair_kernel<true>, smem_aux);
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  const int max_pairs = aux ? pairs_aux : pairs_plain;
+  if (max_pairs < 1) return nullptr;
+  CUtensorMap ta, tb, tx;
+  const char* err;
+  if (!g.a_mn) err = make_tensor_map_2d(&ta, op.a, 2, g.M, g.K, op.a_ld, BM);
+  else err = make_tensor_map_2d(&ta, op.a, 2, g.K, g.M, op.a_ld, BF16_BK);
+  if (err) return err;
+  if (!g.b_mn) err = make_tensor_map_2d(&tb, op.b, 2, g.N, g.K, op.b_ld, PAIR_B_ROWS);
+  else err = make_tensor_map_2d(&tb, op.b, 2, g.K, g.N, op.b_ld, BF16_BK);
+  if (err) return err;
+  const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + PAIR_BN - 1) / PAIR_BN);
+  GemmShape gs = g;
+  GemmEpilogue es = e;
+  gs.splits = pick_splits(tiles * 2, (g.K + BF16_BK - 1) / BF16_BK, e);
+  es.atomic = gs.splits > 1;
+  const int work = tiles * gs.splits;
+  const int grid = 2 * (work < max_pairs ? work : max_pairs);
+  if (aux) {
+    if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
+    gemm_bf16_pair_kernel<true><<<grid, NUM_THREADS, smem_aux, stream>>>(ta, tb, tx, gs, es, status);
+  } else {
+    gemm_bf16_pair_kernel<false><<<grid, NUM_THREADS, smem_plain, stream>>>(ta, tb, ta, gs, es, status);
+  }
+  *launched = true;
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_bf16_pair_kernel launch failed";
+}
+
+int gemm_pair_capacity() {
+  const int smem_plain = 6 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  return max_active_pairs(gemm_bf16_pair_kernel<false>, smem_plain);
+}
+
 const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
                              cudaStream_t stream) {
   if (g.K % 8 != 0 || g.N % 32 != 0) return "bf16 GEMM needs K % 8 == 0 and N % 32 == 0";
+  if (pair_kernels_enabled() && g.M >= 2 * BM && g.N >= PAIR_BN / 2) {
+    bool launched = false;
+    const char* perr = launch_gemm_bf16_pair(op, g, e, status, stream, &launched);
+    if (perr != nullptr || launched) return perr;
+  }
   CUtensorMap ta, tb;
   const char* err;
   if (!g.a_mn) err = make_tensor_map_2d(&ta, op.a, 2, g.M, g.K, op.a_ld, BM);

@@ -74,4 +74,8 @@ const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const
 const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
                             cudaStream_t stream);
 
+// CTA pairs (two-SM tensor-core tiles) that can be resident at once on the current device; 0 or less when the
+// pair kernels cannot be launched and the single-CTA kernels are used instead.
+int gemm_pair_capacity();
+
 }  // namespace gd
