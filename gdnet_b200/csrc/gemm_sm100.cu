@@ -164,8 +164,13 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
   if (m_warp >= M || n0 >= N) return 0.0f;   // warp-uniform
   const int m = m_warp + lane;
   const int rows_valid = min(32, M - m_warp);
+  if (e.bias != nullptr) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = v[j] * rs + __shfl_sync(0xffffffffu, bias_lane, j);
+    for (int j = 0; j < 32; ++j) v[j] = v[j] * rs + __shfl_sync(0xffffffffu, bias_lane, j);
+  } else if (e.row_scale != nullptr || e.ssq_in != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= rs;
+  }
 
   if (e.aux != nullptr) {
     uint32_t w[16];
@@ -242,13 +247,15 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
     }
     uint32_t w[16];
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      w[t] = pack_bf16x2(v[t * 2], v[t * 2 + 1]);
-      const float2 r = unpack_bf16x2(w[t]);
-      ssq += r.x * r.x + r.y * r.y;
+    for (int t = 0; t < 16; ++t) w[t] = pack_bf16x2(v[t * 2], v[t * 2 + 1]);
+    if (e.ssq_out != nullptr && m < M) {   // of the rounded values, as the consumer of `out` will see them
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const float2 r = unpack_bf16x2(w[t]);
+        ssq += r.x * r.x + r.y * r.y;
+      }
     }
     store_rows_bf16(stage, lane, w, ob, e.out_ld, rows_valid);
-    if (m >= M) ssq = 0.0f;
   }
   return ssq;
 }
@@ -478,23 +485,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BF16_BN + col_half * 128;
       float ssq = 0.0f;
-      // two chunks are in flight: the TMEM load of the next chunk overlaps the math and stores of this one
-      uint32_t raw[2][32];
-      tmem_ld_32x32(t_row, raw[0]);
+      // two chunks are in flight: the TMEM load of the next chunk overlaps the math and stores of this one.
+      // The loop body covers two chunks (one per register buffer) and is not unrolled further: the epilogue
+      // warps are bound by instruction fetch and issue, so the code has to stay small.
+      uint32_t raw0[32], raw1[32];
+      auto do_chunk = [&](uint32_t (&raw)[32], int c, float bias) {
+        float v[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage, bias,
+                              AUX ? aux_buf + (c >> 1) * AUX_BOX_BYTES + lane * 128 : nullptr, (c & 1) * 4);
+      };
+      tmem_ld_32x32(t_row, raw0);
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
         tmem_ld_wait();
-        if (c + 1 < 4) tmem_ld_32x32(t_row + (c + 1) * 32, raw[(c + 1) & 1]);
-        if (c == 3) {   // everything is in registers: hand the accumulator back before the last chunk's stores
+        tmem_ld_32x32(t_row + (2 * cc + 1) * 32, raw1);
+        do_chunk(raw0, 2 * cc, cc ? bias_c[2] : bias_c[0]);
+        tmem_ld_wait();
+        if (cc == 0) {
+          tmem_ld_32x32(t_row + 64, raw0);
+        } else {   // everything is in registers: hand the accumulator back before the last chunk's stores
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
         }
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
-        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage,
-                              bias_c[c], AUX ? aux_buf + (c >> 1) * AUX_BOX_BYTES + lane * 128 : nullptr, (c & 1) * 4);
+        do_chunk(raw1, 2 * cc + 1, cc ? bias_c[3] : bias_c[1]);
       }
       if (AUX) {   // this tile's slice is consumed: fetch the next tile's
         __syncwarp();
@@ -708,22 +724,32 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * PAIR_BN + col_half * 128;
       float ssq = 0.0f;
-      uint32_t raw[2][32];
-      tmem_ld_32x32(t_row, raw[0]);
+      // two chunks are in flight: the TMEM load of the next chunk overlaps the math and stores of this one.
+      // The loop body covers two chunks (one per register buffer) and is not unrolled further: the epilogue
+      // warps are bound by instruction fetch and issue, so the code has to stay small.
+      uint32_t raw0[32], raw1[32];
+      auto do_chunk = [&](uint32_t (&raw)[32], int c, float bias) {
+        float v[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage, bias,
+                              AUX ? aux_buf + (c >> 1) * AUX_BOX_BYTES + lane * 128 : nullptr, (c & 1) * 4);
+      };
+      tmem_ld_32x32(t_row, raw0);
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
         tmem_ld_wait();
-        if (c + 1 < 4) tmem_ld_32x32(t_row + (c + 1) * 32, raw[(c + 1) & 1]);
-        if (c == 3) {   // everything is in registers: hand the accumulator back before the last chunk's stores
+        tmem_ld_32x32(t_row + (2 * cc + 1) * 32, raw1);
+        do_chunk(raw0, 2 * cc, cc ? bias_c[2] : bias_c[0]);
+        tmem_ld_wait();
+        if (cc == 0) {
+          tmem_ld_32x32(t_row + 64, raw0);
+        } else {   // everything is in registers: hand the accumulator back before the last chunk's stores
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(tempty_lead0 + 8 * acc);
         }
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c & 1][j]);
-        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage,
-                              bias_c[c], AUX ? aux_buf + (c >> 1) * AUX_BOX_BYTES + lane * 128 : nullptr, (c & 1) * 4);
+        do_chunk(raw1, 2 * cc + 1, cc ? bias_c[3] : bias_c[1]);
       }
       if (AUX) {
         __syncwarp();
