@@ -98,6 +98,28 @@ void register_grad_sink(const Tensor& flat, const Tensor& ptr_table, int64_t sha
 
 void clear_grad_sinks() { grad_sinks().clear(); }
 
+// Optional fused 1x128 FP8 copy of a (rows, cols) output: q (rows, cols) e4m3 (may be a column range of a wider
+// buffer), s (cols/128, rows) fp32 (rows of a taller buffer), p (rows/128, cols/128, 512) packed chunks.
+gd::RowQuantOut row_quant_out(OptT q, OptT s, OptT p, int64_t rows, int64_t cols) {
+  gd::RowQuantOut o{};
+  if (!q.has_value()) return o;
+  TORCH_CHECK(s.has_value() && p.has_value(), "a quantised output needs q, s and p");
+  TORCH_CHECK(rows % 128 == 0 && cols % 128 == 0, "a quantised output needs rows and cols to be multiples of 128");
+  TORCH_CHECK(q->dim() == 2 && q->size(0) == rows && q->size(1) == cols && q->stride(1) == 1, "q must be (rows, cols)");
+  TORCH_CHECK(s->dim() == 2 && s->size(0) == cols / 128 && s->size(1) == rows && s->stride(1) == 1 &&
+              s->scalar_type() == at::kFloat, "s must be (cols/128, rows) float32");
+  TORCH_CHECK(p->dim() == 3 && p->size(0) == rows / 128 && p->size(1) == cols / 128 && p->size(2) == 512 &&
+              p->stride(2) == 1 && p->stride(1) == 512 && p->stride(0) % 512 == 0, "p must be (rows/128, cols/128, 512) bytes");
+  o.q = fp8_mut(*q, "q");
+  TORCH_CHECK(q->stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(o.q) & 7) == 0, "q rows must be 8-byte aligned");
+  o.q_ld = q->stride(0);
+  o.s = s->data_ptr<float>();
+  o.s_ld = s->stride(0);
+  o.p = fp8_mut(*p, "p");
+  o.p_stride = p->stride(0) / 512;
+  return o;
+}
+
 void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT bias, OptT row_scale, OptT ssq_in,
                    int64_t norm_dim, double norm_eps, OptT aux, int64_t aux_mode, OptT rowcoef, OptT pre_out,
                    int64_t act, OptT ssq_out, int64_t M, int64_t N) {
@@ -225,7 +247,7 @@ void gemm_fp8_mx(const Tensor& a8, const Tensor& pa, const Tensor& b8, const Ten
   GD_LAUNCH(gd::launch_gemm_fp8_mx(op, g, e, status_ptr(a8), stream_of(a8)));
 }
 
-void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out) {
+void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out, OptT q, OptT qs, OptT qp) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 3 && out.dim() == 3, "dwconv: x and out must be (B, T, d)");
   const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
@@ -235,7 +257,7 @@ void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out) {
   if (halo.has_value()) TORCH_CHECK(halo->is_contiguous() && halo->size(0) == B && halo->size(1) == k - 1 && halo->size(2) == d, "dwconv: halo must be (B, k-1, d)");
   TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (out.stride(1) * 2) % 16 == 0, "dwconv: rows must be 16-byte aligned");
   gd::ConvArgs a{bf16_ptr(x, "x"), opt_bf16(halo, "halo"), f32_ptr(w, "w"), bf16_mut(out, "out"), B, T, d, k,
-                 x.stride(1), out.stride(1)};
+                 x.stride(1), out.stride(1), row_quant_out(q, qs, qp, (int64_t)B * T, d)};
   GD_LAUNCH(gd::launch_dwconv_fwd(a, stream_of(x)));
 }
 
@@ -259,7 +281,8 @@ void dwconv_bwd(const Tensor& dc, const Tensor& x, OptT halo, const Tensor& w, O
 }
 
 void gate_update_fwd(const Tensor& g_pre, const Tensor& z, const Tensor& c, const Tensor& s, const Tensor& w_r,
-                     Tensor fwd_out, Tensor side_out, OptT gate_out, OptT rstd_out, OptT gate_sum, double eps_r) {
+                     Tensor fwd_out, Tensor side_out, OptT gate_out, OptT rstd_out, OptT gate_sum, double eps_r, OptT q,
+                     OptT qs, OptT qp) {
   c10::cuda::CUDAGuard guard(c.device());
   const int64_t rows = g_pre.size(0);
   const int d = (int)g_pre.size(1);
@@ -271,7 +294,7 @@ void gate_update_fwd(const Tensor& g_pre, const Tensor& z, const Tensor& c, cons
                     gate_out.has_value() ? bf16_mut(*gate_out, "gate_out") : nullptr,
                     rstd_out.has_value() ? f32_mut(*rstd_out, "rstd_out") : nullptr,
                     gate_sum.has_value() ? f32_mut(*gate_sum, "gate_sum") : nullptr,
-                    rows, d, c.stride(0), s.stride(0), (float)eps_r};
+                    rows, d, c.stride(0), s.stride(0), (float)eps_r, row_quant_out(q, qs, qp, rows, d)};
   GD_LAUNCH(gd::launch_gate_update_fwd(a, stream_of(c)));
 }
 
@@ -547,9 +570,9 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? ssq_in, int norm_dim, float norm_eps, Tensor? aux, int aux_mode, Tensor? rowcoef, Tensor(b!)? pre_out, int act, Tensor(c!)? ssq_out) -> ()", &gemm_bf16);
   m.def("gemm_fp8(Tensor a8, Tensor sa, Tensor b8, Tensor sb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8);
   m.def("gemm_fp8_mx(Tensor a8, Tensor pa, Tensor b8, Tensor pb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8_mx);
-  m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out) -> ()", &dwconv_fwd);
+  m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out, Tensor(b!)? q=None, Tensor(c!)? qs=None, Tensor(d!)? qp=None) -> ()", &dwconv_fwd);
   m.def("dwconv_bwd(Tensor dc, Tensor x, Tensor? halo, Tensor w, Tensor? tail_add, Tensor(a!) dx, Tensor(b!)? dhalo, Tensor(c!) dw) -> ()", &dwconv_bwd);
-  m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r) -> ()", &gate_update_fwd);
+  m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r, Tensor(f!)? q=None, Tensor(g!)? qs=None, Tensor(h!)? qp=None) -> ()", &gate_update_fwd);
   m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r) -> ()", &gate_update_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!)? rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw) -> ()", &rmsnorm_bwd);

@@ -3,6 +3,8 @@
 // accumulators), bounded waits and the status word kernels report errors through.
 #pragma once
 
+#include "quant_out.h"
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -404,6 +406,59 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
 
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// ---------------------------------------------------------------------------------------
+// FP8 block quantisation helpers
+// ---------------------------------------------------------------------------------------
+// Scale of a block with the given amax: amax/448, or, for the hardware block-scaled MMA, the next
+// power of two (UE8M0: the tensor core multiplies by 2^(e-127)); 1 for an all-zero block.
+__device__ __forceinline__ float block_scale(float amax, int pow2) {
+  if (!(amax > 0.0f)) return 1.0f;
+  const float s = amax / 448.0f;
+  if (!pow2) return s;
+  int e;
+  const float m = frexpf(s, &e);            // s = m * 2^e, m in [0.5, 1)
+  return ldexpf(1.0f, m == 0.5f ? e - 1 : e);
+}
+
+// UE8M0 byte of a power-of-two scale, replicated into the four bytes of a word: the four K steps of
+// a 128-deep block share the scale.
+__device__ __forceinline__ uint32_t ue8m0_word(float pow2_scale) {
+  int e;
+  frexpf(pow2_scale, &e);                   // pow2_scale = 0.5 * 2^e
+  int b = e - 1 + 127;
+  b = b < 0 ? 0 : (b > 254 ? 254 : b);
+  return (uint32_t)b * 0x01010101u;
+}
+
+// Packed scale chunks for tcgen05 block-scaled MMA: 512 bytes per (128 rows, 128-deep K block);
+// the four scale bytes of row r sit at (r % 32) * 16 + (r / 32) * 4.
+__device__ __forceinline__ void store_packed_scale(uint8_t* packed, int64_t chunk, int row_in_128, uint32_t word) {
+  *reinterpret_cast<uint32_t*>(packed + chunk * 512 + (row_in_128 & 31) * 16 + (row_in_128 >> 5) * 4) = word;
+}
+
+// 16 consecutive lanes hold the 128 values of one block of row r (8 each, this lane's start at column c; the
+// values are already rounded to bf16). The 16 lanes of a group call together (the other half of the warp
+// need not); `live` = this lane's row exists.
+__device__ __forceinline__ void quant_emit_8(const RowQuantOut& o, const float (&v)[8], int64_t r, int c, bool live) {
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+  const uint32_t group = 0xffffu << (threadIdx.x & 16);
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(group, m, off));
+  const float sc = block_scale(m, 1);
+  const float inv = 1.0f / sc;
+  uint8_t q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[i] * inv);
+  if (!live) return;
+  *reinterpret_cast<uint2*>(o.q + r * o.q_ld + c) = *reinterpret_cast<uint2*>(q);
+  if ((threadIdx.x & 15) == 0) {
+    o.s[(int64_t)(c >> 7) * o.s_ld + r] = sc;
+    store_packed_scale(o.p, (r >> 7) * o.p_stride + (c >> 7), (int)(r & 127), ue8m0_word(sc));
+  }
 }
 
 }  // namespace gd

@@ -68,11 +68,14 @@ template <int KT>
 __global__ void __launch_bounds__(256)
 dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
                      const float* __restrict__ wt, __nv_bfloat16* __restrict__ out, int B, int T, int d, int k,
-                     int64_t x_ld, int64_t out_ld) {
+                     int64_t x_ld, int64_t out_ld, const RowQuantOut qo) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
   const int row = blockIdx.x * 8 + warp;      // 8 consecutive time steps per block (B*T < 2^31, checked by the launcher)
-  if (ch >= d || row >= B * T) return;
+  if (row >= B * T) return;                   // warp-uniform
+  if (ch >= d) {                              // with a quantised output d is a multiple of 128: whole 16-lane groups leave
+    return;
+  }
   const int b = row / T, t = row - b * T;
   if (KT > 0) k = KT;
   float acc[8];
@@ -89,6 +92,11 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     for (int c = 0; c < 8; ++c) acc[c] = fmaf(tap[c], in[c], acc[c]);
   }
   store_bf16_vec<8>(out + (int64_t)row * out_ld + ch, acc);
+  if (qo.q != nullptr) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = __bfloat162float(__float2bfloat16(acc[c]));
+    quant_emit_8(qo, acc, row, ch, true);
+  }
 }
 
 // dx[t] = sum_j w[k-1-j] dc[t+j] for t in [t_lo, T), t_lo = -(k-1) when the halo gradient is wanted
@@ -220,8 +228,9 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "dwconv: d must be a multiple of 8";
   if ((int64_t)a.B * (a.T + 16) >= (1ll << 31)) return "dwconv: B*T must be below 2^31";
   dim3 grid((unsigned)(((int64_t)a.B * a.T + 7) / 8), (a.d + 255) / 256);
-  if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
-  else dwconv_fwd_pt_kernel<0><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld);
+  if (a.quant.q != nullptr && a.d % 128 != 0) return "dwconv: a quantised output needs d % 128 == 0";
+  if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld, a.quant);
+  else dwconv_fwd_pt_kernel<0><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld, a.quant);
   return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
 }
 
@@ -285,6 +294,11 @@ gate_update_fwd_kernel(const GateFwdArgs a) {
       st8(a.fwd_out + row * a.d + col, fo);
       st8(a.side_out + row * a.d + col, so);
       if (a.gate_out != nullptr) st8(a.gate_out + row * a.d + col, gv);
+      if (a.quant.q != nullptr) {   // the next step's recovery GEMM reads the side stream in FP8
+#pragma unroll
+        for (int i = 0; i < 8; ++i) so[i] = __bfloat162float(__float2bfloat16(so[i]));
+        quant_emit_8(a.quant, so, row, col, true);
+      }
     }
   }
   if (a.gate_sum != nullptr) {
@@ -542,33 +556,6 @@ const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
 // =======================================================================================
 // FP8 (e4m3) block quantisation
 // =======================================================================================
-// Scale of a block with the given amax: amax/448, or, for the hardware block-scaled MMA, the next
-// power of two (UE8M0: the tensor core multiplies by 2^(e-127)); 1 for an all-zero block.
-__device__ __forceinline__ float block_scale(float amax, int pow2) {
-  if (!(amax > 0.0f)) return 1.0f;
-  const float s = amax / 448.0f;
-  if (!pow2) return s;
-  int e;
-  const float m = frexpf(s, &e);            // s = m * 2^e, m in [0.5, 1)
-  return ldexpf(1.0f, m == 0.5f ? e - 1 : e);
-}
-
-// UE8M0 byte of a power-of-two scale, replicated into the four bytes of a word: the four K steps of
-// a 128-deep block share the scale.
-__device__ __forceinline__ uint32_t ue8m0_word(float pow2_scale) {
-  int e;
-  frexpf(pow2_scale, &e);                   // pow2_scale = 0.5 * 2^e
-  int b = e - 1 + 127;
-  b = b < 0 ? 0 : (b > 254 ? 254 : b);
-  return (uint32_t)b * 0x01010101u;
-}
-
-// Packed scale chunks for tcgen05 block-scaled MMA: 512 bytes per (128 rows, 128-deep K block);
-// the four scale bytes of row r sit at (r % 32) * 16 + (r / 32) * 4.
-__device__ __forceinline__ void store_packed_scale(uint8_t* packed, int64_t chunk, int row_in_128, uint32_t word) {
-  *reinterpret_cast<uint32_t*>(packed + chunk * 512 + (row_in_128 & 31) * 16 + (row_in_128 >> 5) * 4) = word;
-}
-
 // One block quantises a 128 x 128 tile of a bf16 matrix x[rows][cols] (row pitch x_ld),
 // optionally through silu. Two independent outputs, each optional:
 //   row-major  q_row[r][c]  with scales per (row, 128-col block)   [ROWS]  or per tile [BLOCK]

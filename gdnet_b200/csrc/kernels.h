@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "quant_out.h"
+
 namespace gd {
 
 struct Status;
@@ -19,6 +21,7 @@ struct ConvArgs {
   __nv_bfloat16* out;         // (B, T, d), row pitch out_ld
   int B, T, d, k;
   int64_t x_ld, out_ld;
+  RowQuantOut quant;          // optional 1x128-quantised copy of out (d % 128 == 0)
 };
 
 struct ConvBwdArgs {
@@ -53,6 +56,7 @@ struct GateFwdArgs {
   int d;
   int64_t c_ld, s_ld;
   float eps_r;
+  RowQuantOut quant;           // optional 1x128-quantised copy of side_out (d % 128 == 0)
 };
 
 struct GateBwdArgs {

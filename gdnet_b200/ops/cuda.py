@@ -15,6 +15,8 @@ copies cached per parameter version.
 
 from __future__ import annotations
 
+import weakref
+
 import torch
 
 from .. import _ext
@@ -139,6 +141,7 @@ def clear_caches() -> None:
     _wq_cache.clear()
     _taps_cache.clear()
     _w2w_cache.clear()
+    _side_offers.clear()
 
 
 # --------------------------------------------------------------------------------------
@@ -635,6 +638,40 @@ def _folded_w2(W2, w_norm):
     return out
 
 
+# The update kernel of a step also writes the FP8 copy of its side output, straight into the operand buffer
+# of the step that will consume it. The hand-over is keyed on the identity (and version) of the side tensor.
+_side_offers: dict = {}     # id(side tensor) -> (weak reference, version, (u8, su, pu))
+_pending_q8 = None
+
+
+def _alloc_u8(M, d, dev):
+    kb = d // 128
+    return (torch.empty(M, 2 * d, dtype=FP8, device=dev), torch.empty(2 * kb, M, dtype=F32, device=dev),
+            packed_buffer(M, 2 * d, dev))
+
+
+def _offer_side_q8(side_out) -> None:
+    """After a step: remember the buffers its update kernel filled for ``side_out`` (every layer keeps its own
+    side stream, so several offers are open at a time; one dies with its tensor)."""
+    global _pending_q8
+    bufs, _pending_q8 = _pending_q8, None
+    if bufs is None:
+        return
+    key = id(side_out)
+    _side_offers[key] = (weakref.ref(side_out, lambda _r, k=key: _side_offers.pop(k, None)), side_out._version, bufs)
+
+
+def _claim_side_q8(side):
+    """Before a step: the (u8, su, pu) buffers whose s half already holds ``side`` in FP8, or None."""
+    o = _side_offers.pop(id(side), None)
+    if o is None or o[0]() is not side or o[1] != side._version:
+        return None
+    u8 = o[2][0]
+    if u8.shape[0] * u8.shape[1] != 2 * side.numel() or u8.shape[1] != 2 * side.shape[-1]:
+        return None
+    return o[2]
+
+
 class _LayerStepFn(torch.autograd.Function):
     """conv -> recovery gate R -> forward gate g -> stream update, as one autograd node.
 
@@ -646,7 +683,7 @@ class _LayerStepFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, s, halo, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1, gnw, gW2, gb2, fp8, eps_r, eps_g,
-                want_gate_sum):
+                want_gate_sum, side_q8=None):
         B, T, d = x.shape
         M = B * T
         dev = x.device
@@ -654,18 +691,23 @@ class _LayerStepFn(torch.autograd.Function):
         x = x if x.is_contiguous() else x.contiguous()
         s2 = s.reshape(M, d) if s.stride(-1) == 1 else s.contiguous().reshape(M, d)
         c3 = torch.empty(B, T, d, dtype=BF16, device=dev)
-        K.dwconv_fwd(x, halo, taps_t(conv_w), c3)
         c = c3.view(M, d)
+        kb = d // 128
+        if fp8:
+            # A operand of the first recovery GEMM: [s ; c] in e4m3. The conv kernel writes the c half itself;
+            # the s half usually comes from the step that produced s (its update kernel left it in the buffer)
+            if side_q8 is not None:
+                u8, su, pu = side_q8
+            else:
+                u8, su, pu = _alloc_u8(M, d, dev)
+                quantize_rows_mx(s2, q=u8[:, :d], s=su[:kb], p=pu[:, :kb])
+            K.dwconv_fwd(x, halo, taps_t(conv_w), c3, u8[:, d:], su[kb:], pu[:, kb:])
+        else:
+            K.dwconv_fwd(x, halo, taps_t(conv_w), c3)
 
         # recovery MLP: z = W2r silu(W1r [s ; c] + b1r) + b2r
         h1_pre = torch.empty(M, d, dtype=BF16, device=dev)
         if fp8:
-            kb = d // 128
-            u8 = torch.empty(M, 2 * d, dtype=FP8, device=dev)
-            su = torch.empty(2 * kb, M, dtype=F32, device=dev)
-            pu = packed_buffer(M, 2 * d, dev)
-            quantize_rows_mx(s2, q=u8[:, :d], s=su[:kb], p=pu[:, :kb])
-            quantize_rows_mx(c, q=u8[:, d:], s=su[kb:], p=pu[:, kb:])
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
             gemm_fp8_mx(u8, pu, q1.q, q1.p, out=h1_pre, bias=f32(rb1))
             a8, _, pa = quantize_rows_mx(h1_pre, pre_silu=True)
@@ -690,8 +732,15 @@ class _LayerStepFn(torch.autograd.Function):
         side_out = torch.empty(B, T, d, dtype=BF16, device=dev)
         rstd_z = torch.empty(M, dtype=F32, device=dev)
         gate_sum = torch.zeros((), dtype=F32, device=dev)
-        K.gate_update_fwd(g_pre, z, c, s2, f32(rnw), fwd_out.view(M, d), side_out.view(M, d), None, rstd_z,
-                          gate_sum if want_gate_sum else None, eps_r)
+        if fp8:
+            nu8, nsu, npu = _alloc_u8(M, d, dev)      # the next step's [s ; c] operand: this kernel fills the s half
+            K.gate_update_fwd(g_pre, z, c, s2, f32(rnw), fwd_out.view(M, d), side_out.view(M, d), None, rstd_z,
+                              gate_sum if want_gate_sum else None, eps_r, nu8[:, :d], nsu[:kb], npu[:, :kb])
+            global _pending_q8
+            _pending_q8 = (nu8, nsu, npu)
+        else:
+            K.gate_update_fwd(g_pre, z, c, s2, f32(rnw), fwd_out.view(M, d), side_out.view(M, d), None, rstd_z,
+                              gate_sum if want_gate_sum else None, eps_r)
 
         if train:
             empty = x.new_empty(0)
@@ -791,7 +840,7 @@ class _LayerStepFn(torch.autograd.Function):
         g_gW2 = None if main2 else tgt2.to(gW2.dtype)
         return (dx, ds, dhalo, _sink_vec(conv_w, dwc), g_rW1, _sink_vec(rb1, db1r), g_rW2, _sink_vec(rb2, db2r),
                 _sink_vec(rnw, dw_r), g_gW1, _sink_vec(gb1, db1g), _sink_vec(gnw, dgnw), g_gW2,
-                _sink_vec(gb2, db2g), None, None, None, None)
+                _sink_vec(gb2, db2g), None, None, None, None, None)
 
 
 def _fused_step_ok(fwd, side, layer, r) -> bool:
@@ -819,11 +868,14 @@ def layer_step(fwd, side, layer, conv_name, g, r, sp_group=None, sp_slot=None, r
 
     fp8 = isinstance(w1r, FP8Linear) and isinstance(w2r, FP8Linear) and w1r.recipe == "block"
     eps_r = nr.eps if nr.eps is not None else ref.default_rms_eps(BF16)
+    side_q8 = _claim_side_q8(side) if fp8 and side.dtype == BF16 and side.is_contiguous() else None
     fo, so, gsum = _LayerStepFn.apply(
         fwd, side.to(BF16), halo, conv.taps, w1r.weight, w1r.bias, w2r.weight, w2r.bias, nr.weight,
         w1g.weight, w1g.bias, ng.weight, w2g.weight, w2g.bias, fp8, float(eps_r), ref.GATE_EPS,
-        return_gate == "mean",
+        return_gate == "mean", side_q8,
     )
+    if fp8:
+        _offer_side_q8(so)
     if return_gate == "mean":
         return fo, so, gsum / float(fo.numel())
     return fo, so
