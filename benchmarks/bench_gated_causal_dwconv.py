@@ -79,6 +79,8 @@ def bench(B, T, d, k, hbm_gbs):
     sc = torch.empty(parts, M, device=dev)
     add("quant_rows_1x128", timeit(lambda i: cu.quantize_rows(x[i % n_sets].view(M, d), q=q, s=sc)), 1.5 * unit)
     add("quant_rows+transposed", timeit(lambda i: cu.quantize_rows_and_transposed(x[i % n_sets].view(M, d), cu.Q_COLS)), 2 * unit)
+    add("quant_rows+transposed mx", timeit(lambda i: cu.quantize_both_mx(x[i % n_sets].view(M, d), cu.Q_COLS)), 2 * unit)
+    add("quant_transposed_block mx", timeit(lambda i: cu.quantize_transposed_mx(x[i % n_sets].view(M, d), cu.Q_BLOCK)), 1.5 * unit)
     y = torch.empty(M, d, device=dev, dtype=bf)
     add("rmsnorm_fwd", timeit(lambda i: K.rmsnorm_fwd(x[i % n_sets].view(M, d), wr, y, rstd, 1e-6)), 2 * unit)
     cs = torch.zeros(d, device=dev)

@@ -136,6 +136,11 @@ void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT
   e.peer_out = nullptr;
   e.flat_off = 0;
   e.shard_elems = 1;
+  e.q8 = nullptr;
+  e.q8_ld = 0;
+  e.q8_p = nullptr;
+  e.q8_p_stride = 0;
+  e.q8_silu = 0;
   if (e.out_f32 && accumulate) {
     if (const GradSink* s = find_sink(out.data_ptr())) {
       TORCH_CHECK(out.is_contiguous() && N % 32 == 0, "a gradient inside a spread flat buffer must be contiguous, N % 32 == 0");
@@ -231,7 +236,8 @@ void gemm_fp8(const Tensor& a8, const Tensor& sa, const Tensor& b8, const Tensor
 
 // a8: (M,K) e4m3 with packed UE8M0 chunks pa (M/128, K/128, 512); b8: (N,K) with pb (N/128, K/128, 512).
 void gemm_fp8_mx(const Tensor& a8, const Tensor& pa, const Tensor& b8, const Tensor& pb, Tensor out, bool accumulate,
-                 OptT bias, OptT row_scale, OptT aux, int64_t aux_mode, OptT pre_out, int64_t act) {
+                 OptT bias, OptT row_scale, OptT aux, int64_t aux_mode, OptT pre_out, int64_t act, OptT q8, OptT q8_p,
+                 bool q8_silu, bool store_out) {
   c10::cuda::CUDAGuard guard(a8.device());
   TORCH_CHECK(a8.dim() == 2 && b8.dim() == 2, "gemm operands must be 2-D");
   const int64_t M = a8.size(0), K = a8.size(1), N = b8.size(0);
@@ -244,6 +250,24 @@ void gemm_fp8_mx(const Tensor& a8, const Tensor& pa, const Tensor& b8, const Ten
   gd::GemmEpilogue e;
   std::optional<Tensor> none;
   fill_epilogue(e, out, accumulate, bias, row_scale, none, 0, 0.0, aux, aux_mode, none, pre_out, act, none, M, N);
+  if (q8.has_value()) {
+    TORCH_CHECK(q8_p.has_value(), "q8 needs q8_p");
+    TORCH_CHECK(q8->dim() == 2 && q8->size(0) == M && q8->size(1) == N && q8->stride(1) == 1 && q8->stride(0) % 16 == 0,
+                "q8 must be (M, N) with 16-byte aligned rows");
+    TORCH_CHECK(q8_p->dim() == 3 && q8_p->size(0) == M / 128 && q8_p->size(1) == N / 128 && q8_p->size(2) == 512 &&
+                q8_p->stride(2) == 1 && q8_p->stride(1) == 512 && q8_p->stride(0) % 512 == 0,
+                "q8_p must be (M/128, N/128, 512) bytes");
+    TORCH_CHECK(!e.out_f32 && !accumulate, "a quantised copy needs a plain bf16 epilogue");
+    e.q8 = fp8_mut(*q8, "q8");
+    e.q8_ld = q8->stride(0);
+    e.q8_p = fp8_mut(*q8_p, "q8_p");
+    e.q8_p_stride = q8_p->stride(0) / 512;
+    e.q8_silu = q8_silu;
+  }
+  if (!store_out) {
+    TORCH_CHECK(q8.has_value() && !pre_out.has_value(), "store_out=False only makes sense with a quantised copy");
+    e.out = nullptr;
+  }
   GD_LAUNCH(gd::launch_gemm_fp8_mx(op, g, e, status_ptr(a8), stream_of(a8)));
 }
 
@@ -569,7 +593,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("kernel_status(Tensor like) -> Tensor", &kernel_status);
   m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? ssq_in, int norm_dim, float norm_eps, Tensor? aux, int aux_mode, Tensor? rowcoef, Tensor(b!)? pre_out, int act, Tensor(c!)? ssq_out) -> ()", &gemm_bf16);
   m.def("gemm_fp8(Tensor a8, Tensor sa, Tensor b8, Tensor sb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8);
-  m.def("gemm_fp8_mx(Tensor a8, Tensor pa, Tensor b8, Tensor pb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8_mx);
+  m.def("gemm_fp8_mx(Tensor a8, Tensor pa, Tensor b8, Tensor pb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act, Tensor(c!)? q8=None, Tensor(d!)? q8_p=None, bool q8_silu=False, bool store_out=True) -> ()", &gemm_fp8_mx);
   m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out, Tensor(b!)? q=None, Tensor(c!)? qs=None, Tensor(d!)? qp=None) -> ()", &dwconv_fwd);
   m.def("dwconv_bwd(Tensor dc, Tensor x, Tensor? halo, Tensor w, Tensor? tail_add, Tensor(a!) dx, Tensor(b!)? dhalo, Tensor(c!) dw) -> ()", &dwconv_bwd);
   m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r, Tensor(f!)? q=None, Tensor(g!)? qs=None, Tensor(h!)? qp=None) -> ()", &gate_update_fwd);

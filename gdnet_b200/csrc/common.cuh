@@ -417,19 +417,19 @@ __device__ __forceinline__ float block_scale(float amax, int pow2) {
   if (!(amax > 0.0f)) return 1.0f;
   const float s = amax / 448.0f;
   if (!pow2) return s;
-  int e;
-  const float m = frexpf(s, &e);            // s = m * 2^e, m in [0.5, 1)
-  return ldexpf(1.0f, m == 0.5f ? e - 1 : e);
+  // next power of two >= s, on the bits: exponent field + 1 unless the mantissa is zero
+  const uint32_t b = __float_as_uint(s);
+  uint32_t e = (b >> 23) + ((b & 0x7FFFFFu) != 0u ? 1u : 0u);
+  e = e < 1u ? 1u : (e > 254u ? 254u : e);
+  return __uint_as_float(e << 23);
 }
 
-// UE8M0 byte of a power-of-two scale, replicated into the four bytes of a word: the four K steps of
-// a 128-deep block share the scale.
+// UE8M0 byte of a power-of-two scale (its biased exponent), replicated into the four bytes of a word: the
+// four K steps of a 128-deep block share the scale.
 __device__ __forceinline__ uint32_t ue8m0_word(float pow2_scale) {
-  int e;
-  frexpf(pow2_scale, &e);                   // pow2_scale = 0.5 * 2^e
-  int b = e - 1 + 127;
-  b = b < 0 ? 0 : (b > 254 ? 254 : b);
-  return (uint32_t)b * 0x01010101u;
+  uint32_t e = __float_as_uint(pow2_scale) >> 23;
+  e = e > 254u ? 254u : e;
+  return e * 0x01010101u;
 }
 
 // Packed scale chunks for tcgen05 block-scaled MMA: 512 bytes per (128 rows, 128-deep K block);

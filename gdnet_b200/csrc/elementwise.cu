@@ -565,15 +565,18 @@ const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
 //   COLS : s_col[rb * s_col_ld + c]            (A operand of the weight-gradient GEMM)
 //   BLOCK (row-major) : s_row[rb * n_cb + cb]  (GEMM B operand: sb[nb*KB + kb])
 //   BLOCK (transposed): s_col[cb * n_rb + rb]
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 quant_tile_kernel(const QuantArgs a) {
   __shared__ float s_colmax[16][128];
   __shared__ float s_scale_col[128];
   __shared__ float s_tilemax;
-  __shared__ __align__(16) __nv_bfloat16 s_tile[128][128 + 8];
+  // e4m3 tile, transposed: row = source column, 128 bytes = the 128 source rows in 8-byte slots; the slot index
+  // is XORed with a function of the row so that the 8-byte column writes spread over the banks while every
+  // aligned pair of slots (16 bytes) stays contiguous for the row-wise reads
+  __shared__ __align__(16) uint8_t s_q8t[128][128];
 
   const int tid = threadIdx.x;
-  const int tr = tid >> 4;          // 0..15: row within a pass
+  const int tr = tid >> 4;          // 0..15: this thread's rows are tr*8 .. tr*8+7
   const int tc = (tid & 15) * 8;    // first of 8 columns
   const int64_t r0 = (int64_t)blockIdx.y * 128;
   const int c0 = blockIdx.x * 128;
@@ -584,19 +587,23 @@ quant_tile_kernel(const QuantArgs a) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) colmax[i] = 0.0f;
 
+  const int c = c0 + tc;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
-    const int64_t r = r0 + p * 16 + tr;
-    const int c = c0 + tc;
+    const int64_t r = r0 + tr * 8 + p;
     if (r < a.rows && c < a.cols) {
       load_bf16_vec<8>(a.x + r * a.x_ld + c, v[p]);
-      if (a.pre_silu) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[p][i] = __bfloat162float(__float2bfloat16(siluf_(v[p][i])));
-      }
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[p][i] = 0.0f;
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const int64_t r = r0 + tr * 8 + p;
+    if (a.pre_silu) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[p][i] = __bfloat162float(__float2bfloat16(siluf_(v[p][i])));
     }
     float rmax = 0.0f;
 #pragma unroll
@@ -605,10 +612,10 @@ quant_tile_kernel(const QuantArgs a) {
       rmax = fmaxf(rmax, av);
       colmax[i] = fmaxf(colmax[i], av);
     }
-    // row amax across the 16 threads that share this row
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
     if (a.q_row != nullptr && a.row_mode == QUANT_ROWS) {
+      // row amax across the 16 threads that share this row
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
       const float sc = block_scale(rmax, a.pow2);
       const float inv = 1.0f / sc;
       if (r < a.rows && c < a.cols) {
@@ -647,8 +654,7 @@ quant_tile_kernel(const QuantArgs a) {
     const float inv = 1.0f / tile_scale;
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
-      const int64_t r = r0 + p * 16 + tr;
-      const int c = c0 + tc;
+      const int64_t r = r0 + tr * 8 + p;
       if (r < a.rows && c < a.cols) {
         uint8_t q[8];
 #pragma unroll
@@ -662,26 +668,29 @@ quant_tile_kernel(const QuantArgs a) {
   }
 
   if (a.q_col != nullptr) {
-    // stage the tile row-major as bf16 (16-byte stores, conflict free), then every thread walks half
-    // of one column: 64 values -> 64 output bytes of one transposed row
+    // quantise in registers, then one 8-byte shared store per column: the thread's 8 consecutive rows of it
 #pragma unroll
-    for (int p = 0; p < 8; ++p) store_bf16_vec<8>(&s_tile[p * 16 + tr][tc], v[p]);
+    for (int i = 0; i < 8; ++i) {
+      const int col = tc + i;
+      const float sc = a.col_mode == QUANT_COLS ? block_scale(s_scale_col[col], a.pow2) : tile_scale;
+      const float inv = 1.0f / sc;
+      uint8_t q[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) q[p] = to_e4m3(v[p][i] * inv);
+      const int slot = tr ^ (((col >> 3) & 7) << 1);
+      *reinterpret_cast<uint2*>(&s_q8t[col][slot * 8]) = *reinterpret_cast<uint2*>(q);
+    }
     __syncthreads();
-    const int oc = tid >> 1, half = tid & 1;
-    const float cm = s_scale_col[oc];
-    const float sc = a.col_mode == QUANT_COLS ? block_scale(cm, a.pow2) : tile_scale;
-    const float inv = 1.0f / sc;
-    const int c = c0 + oc;
-    const int64_t rbase = r0 + half * 64;
-    if (c < a.cols) {
+    // rows of the transposed tile leave as full 128-byte lines: 8 threads per row, 4 rows per warp and pass
+    const int piece = tid & 7;
 #pragma unroll
-      for (int seg = 0; seg < 4; ++seg) {
-        uint8_t q[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) q[i] = to_e4m3(__bfloat162float(s_tile[half * 64 + seg * 16 + i][oc]) * inv);
-        if (rbase + seg * 16 < a.rows)
-          *reinterpret_cast<uint4*>(a.q_col + (int64_t)c * a.q_col_ld + rbase + seg * 16) = *reinterpret_cast<uint4*>(q);
-      }
+    for (int j = 0; j < 4; ++j) {
+      const int oc = j * 32 + (tid >> 3);
+      const int slot = (2 * piece) ^ (((oc >> 3) & 7) << 1);
+      const uint4 u = *reinterpret_cast<const uint4*>(&s_q8t[oc][slot * 8]);
+      const int64_t rr = r0 + piece * 16;
+      if (c0 + oc < a.cols && rr < a.rows)
+        *reinterpret_cast<uint4*>(a.q_col + (int64_t)(c0 + oc) * a.q_col_ld + rr) = u;
     }
     if (a.col_mode == QUANT_COLS) {
       if (tid < 128 && c0 + tid < a.cols) {

@@ -212,6 +212,7 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
     for (int j = 0; j < 32; ++j) v[j] = siluf_(v[j]);
   }
 
+  if (e.out == nullptr) return 0.0f;   // only the quantised copy is wanted (written by the caller)
   if (e.out_f32) {
     if (m >= M) return 0.0f;
     float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(e.out) + (size_t)m * e.out_ld + n0);
@@ -1119,16 +1120,51 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-      float v[32];
+      float va[32], vb[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+      for (int j = 0; j < 32; ++j) {
+        va[j] = __uint_as_float(r0[j]);
+        vb[j] = __uint_as_float(r1[j]);
+      }
       const uint8_t* aux_row = AUX ? aux_buf + lane * 128 : nullptr;
-      float ssq = epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64, rs, rc, v, stage, bias0,
+      float ssq = epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64, rs, rc, va, stage, bias0,
                                  aux_row, 0);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
-      ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, v, stage, bias1,
+      ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, vb, stage, bias1,
                             aux_row, 4);
+      if (e.q8 != nullptr && m0 + quarter * 32 < g.M && n0 + col_half * 64 < g.N) {
+        // e4m3 copy of this warp's 32 rows x 64 columns, one power-of-two scale per row
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x0 = __bfloat162float(__float2bfloat16(va[j])), x1 = __bfloat162float(__float2bfloat16(vb[j]));
+          if (e.q8_silu) {
+            x0 = __bfloat162float(__float2bfloat16(siluf_(x0)));
+            x1 = __bfloat162float(__float2bfloat16(siluf_(x1)));
+          }
+          va[j] = x0;
+          vb[j] = x1;
+          amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
+        }
+        const float sc = block_scale(amax, 1);
+        const float inv = 1.0f / sc;
+        uint32_t w[16];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          w[t] = (uint32_t)to_e4m3(va[4 * t] * inv) | ((uint32_t)to_e4m3(va[4 * t + 1] * inv) << 8) |
+                 ((uint32_t)to_e4m3(va[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(va[4 * t + 3] * inv) << 24);
+          w[8 + t] = (uint32_t)to_e4m3(vb[4 * t] * inv) | ((uint32_t)to_e4m3(vb[4 * t + 1] * inv) << 8) |
+                     ((uint32_t)to_e4m3(vb[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(vb[4 * t + 3] * inv) << 24);
+        }
+        // 32 rows x 64 bytes through the staging area (same shape as a 32-column bf16 chunk)
+        const int m_warp = m0 + quarter * 32, nq = n0 + col_half * 64;
+        store_rows_bf16(stage, lane, w, reinterpret_cast<__nv_bfloat16*>(e.q8 + (size_t)m_warp * e.q8_ld + nq),
+                        e.q8_ld / 2, min(32, g.M - m_warp));
+        if (m < g.M) {
+          uint8_t* chunk = e.q8_p + ((int64_t)(m >> 7) * e.q8_p_stride + (nq >> 7)) * 512;
+          *reinterpret_cast<uint16_t*>(chunk + (m & 31) * 16 + ((m >> 5) & 3) * 4 + col_half * 2) =
+              (uint16_t)(ue8m0_word(sc) & 0xFFFFu);
+        }
+      }
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
       if (AUX) {   // this tile's slice is consumed: fetch the next tile's

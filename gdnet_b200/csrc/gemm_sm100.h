@@ -50,6 +50,14 @@ struct GemmEpilogue {
   float* const* peer_out;
   int64_t flat_off;
   int64_t shard_elems;
+  // Hardware-scaled fp8 kernel only: also leave silu(v) (q8_silu) or v as the e4m3 A operand of the next GEMM,
+  // q8[m][n] with one power-of-two scale per 64 columns of a row, written as the two UE8M0 bytes of the packed
+  // chunk (m / 128, n / 128) that belong to these columns. out may then be null (nothing but q8 is wanted).
+  uint8_t* q8;
+  int64_t q8_ld;
+  uint8_t* q8_p;
+  int64_t q8_p_stride;
+  int q8_silu;
   const void* bias;     // [N] bf16 or fp32, may be null
   int bias_f32;
   const float* row_scale;   // [M], may be null

@@ -181,13 +181,17 @@ def gemm_fp8(a8, sa, b8, sb, *, out=None, out_dtype=BF16, accumulate=False, bias
 
 
 def gemm_fp8_mx(a8, pa, b8, pb, *, out=None, out_dtype=BF16, accumulate=False, bias=None, row_scale=None, aux=None,
-                aux_mode=0, pre_out=None, act=ACT_NONE):
+                aux_mode=0, pre_out=None, act=ACT_NONE, q8=None, q8_p=None, q8_silu=False, store_out=True):
     """Hardware block-scaled e4m3 GEMM: power-of-two scales as packed UE8M0 chunks, ``pa (M/128, K/128, 512)``
-    and ``pb (N/128, K/128, 512)`` bytes, applied by the tensor core (no promotion pass)."""
+    and ``pb (N/128, K/128, 512)`` bytes, applied by the tensor core (no promotion pass).
+
+    ``q8``/``q8_p``: the epilogue also writes the result (through silu with ``q8_silu``) as the e4m3 A operand of
+    the next GEMM, with one power-of-two scale per 64 columns of a row; ``store_out=False`` then skips ``out``."""
     M, N = a8.shape[0], b8.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a8.device)
-    K.gemm_fp8_mx(a8, pa, b8, pb, out, accumulate, bias, row_scale, aux, aux_mode, pre_out, act)
+    K.gemm_fp8_mx(a8, pa, b8, pb, out, accumulate, bias, row_scale, aux, aux_mode, pre_out, act, q8, q8_p, q8_silu,
+                  store_out)
     return out
 
 
@@ -709,8 +713,10 @@ class _LayerStepFn(torch.autograd.Function):
         h1_pre = torch.empty(M, d, dtype=BF16, device=dev)
         if fp8:
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
-            gemm_fp8_mx(u8, pu, q1.q, q1.p, out=h1_pre, bias=f32(rb1))
-            a8, _, pa = quantize_rows_mx(h1_pre, pre_silu=True)
+            # silu(h1) leaves the first GEMM already quantised for the second; h1 itself is kept for backward only
+            a8 = torch.empty(M, d, dtype=FP8, device=dev)
+            pa = packed_buffer(M, d, dev)
+            gemm_fp8_mx(u8, pu, q1.q, q1.p, out=h1_pre, bias=f32(rb1), q8=a8, q8_p=pa, q8_silu=True, store_out=train)
             z = gemm_fp8_mx(a8, pa, q2.q, q2.p, bias=f32(rb2))
             a1 = None
         else:

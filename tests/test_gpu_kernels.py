@@ -239,3 +239,42 @@ def test_quantizer_pow2_and_packed_chunks():
     _, st_ref = ref.quantize_1x128(x.float().t().contiguous(), pow2=True)
     _close(xts.t(), st_ref, 0, 1e-6, "pow2 col scales")
     assert torch.equal(pxt, ref.pack_ue8m0_rows(st_ref))
+
+
+def test_gemm_fp8_mx_quantised_output():
+    """The epilogue's e4m3 copy of silu(out): one power-of-two scale per 64 columns of a row, stored as the two
+    UE8M0 bytes of the packed chunk that belong to those columns."""
+    cu = _cu()
+    M, N, K = 256, 384, 256
+    a8, sa, b8, sb = _mx_operands(M, N, K, True)
+    bias = torch.randn(N, device=DEV)
+    q8 = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=DEV)
+    p8 = cu.packed_buffer(M, N, DEV)
+    out = cu.gemm_fp8_mx(a8, ref.pack_ue8m0_rows(sa), b8, ref.pack_ue8m0_blocks(sb), bias=bias, q8=q8, q8_p=p8,
+                         q8_silu=True)
+    torch.cuda.synchronize()
+    _status_clean(a8)
+    act = torch.nn.functional.silu(out.float()).bfloat16().float()
+    # scale byte of row r, 32-column step j of chunk (r // 128, c // 128): (r % 32) * 16 + (r % 128 // 32) * 4 + j
+    r = torch.arange(M, device=DEV)
+    off = (r % 32) * 16 + (r % 128 // 32) * 4
+    chunks = p8.view(M // 128, N // 128, 512)
+    scale = torch.empty(M, N // 32, device=DEV)
+    for cb in range(N // 128):
+        for j in range(4):
+            scale[:, cb * 4 + j] = torch.exp2(chunks[r // 128, cb, off + j].float() - 127.0)
+    assert torch.equal(scale[:, 0::2], scale[:, 1::2]), "both 32-column steps of a 64-column group share a scale"
+    amax = act.view(M, N // 64, 64).abs().amax(-1)
+    s64 = scale[:, 0::2]
+    ok = (s64 * 448.0 >= amax * (1 - 1e-3)) & ((s64 * 448.0 < 2.0 * amax * (1 + 1e-3)) | (amax == 0))
+    assert bool(ok.all()), "scales are not the next power of two above amax/448"
+    deq = q8.float().view(M, N // 64, 64) * s64[:, :, None]
+    err = float((deq.view(M, N) - act).norm() / act.norm())
+    assert err < 0.05, f"quantised copy differs from silu(out): rel err {err}"
+    # without storing out
+    q8b = torch.empty_like(q8)
+    p8b = cu.packed_buffer(M, N, DEV)
+    cu.gemm_fp8_mx(a8, ref.pack_ue8m0_rows(sa), b8, ref.pack_ue8m0_blocks(sb), bias=bias, q8=q8b, q8_p=p8b, q8_silu=True,
+                   store_out=False)
+    torch.cuda.synchronize()
+    assert torch.equal(q8b.view(torch.uint8), q8.view(torch.uint8)) and torch.equal(p8b, p8)
