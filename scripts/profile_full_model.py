@@ -59,6 +59,25 @@ def main():
              f"{'share':>6} {'ms/step':>9} {'calls/step':>10}  kernel"]
     for name, t, n in rows[: args.top]:
         lines.append(f"{100 * t / total:6.2f} {t / 1e3 / args.steps:9.3f} {n / args.steps:10.0f}  {name[:110]}")
+    # where the device waits for the host: idle time between consecutive kernels, charged to the kernel that
+    # follows the gap (only gaps above 5 us; under the profiler the host is slower than in a plain run)
+    evs = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                  if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start),
+                 key=lambda t: t[0])
+    gaps: dict[str, list] = {}
+    idle = 0.0
+    busy_until = evs[0][1] if evs else 0.0
+    for start, end, name in evs[1:]:
+        gap = start - busy_until
+        if gap > 5.0:
+            idle += gap
+            g = gaps.setdefault(name, [0.0, 0])
+            g[0] += gap
+            g[1] += 1
+        busy_until = max(busy_until, end)
+    lines.append(f"device idle between kernels: {idle / 1e3 / args.steps:.1f} ms/step; largest waits before:")
+    for name, (t, n) in sorted(gaps.items(), key=lambda kv: -kv[1][0])[:12]:
+        lines.append(f"       {t / 1e3 / args.steps:9.3f} ms {n / args.steps:8.0f} gaps  {name[:100]}")
     text = "\n".join(lines)
     print(text)
     if args.out:
