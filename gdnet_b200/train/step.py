@@ -69,22 +69,31 @@ def gate_info_loss_from_vals(gate_vals, n_layers: int) -> torch.Tensor:
 
 
 @torch.no_grad()
-def build_cam_buffer(model: nn.Module, write_chunks: torch.Tensor, sp_group=None):
-    """Fill the CAM by running the write chunks ``(B, n_write, T)`` in order, no graph.
+def build_cam_buffer(model: nn.Module, write_chunks: torch.Tensor, sp_group=None, max_rows: int = 1 << 18):
+    """Fill the CAM from the write chunks ``(B, n_write, T)``, in order, no graph.
 
     Only the chunk summary is needed, so the read-out (norm, projection, vocabulary
     GEMM) of these passes is skipped (reference: gdnet/loss.py:54-85 computes and
-    discards the logits).
+    discards the logits). Without the read-out the trunk does not look at the memory, so
+    the chunks are independent until the write: they run through the trunk stacked on the
+    batch dimension (as many at a time as ``max_rows`` token rows allow) and only the
+    cheap slot writes happen one after the other.
     """
     raw = unwrap(model)
-    B, n_write, _ = write_chunks.shape
+    B, n_write, T = write_chunks.shape
     dev = write_chunks.device
     tags = torch.zeros(B, raw.cam.n_slots, raw.cam.d_sig, device=dev)
     vals = torch.zeros(B, raw.cam.n_slots, raw.cam.d_c, device=dev)
-    for i in range(n_write):
-        _, side, _, _, _, _, fwd_last = raw(write_chunks[:, i], tags, vals, sp_group=sp_group,
-                                            need_logits=False)
-        tags, vals = raw.write_cam(fwd_last, side, tags, vals)
+    if not raw.cam_enabled:
+        return tags, vals
+    group = max(1, min(n_write, max_rows // max(1, B * T)))
+    for g0 in range(0, n_write, group):
+        n = min(group, n_write - g0)
+        stacked = write_chunks[:, g0 : g0 + n].transpose(0, 1).reshape(n * B, T)      # chunk-major
+        _, side, _, _, _, _, fwd_last = raw(stacked, None, None, sp_group=sp_group, need_logits=False)
+        summary = side[0].mean(dim=1)
+        for i in range(n):
+            tags, vals = raw.cam.write(fwd_last[i * B : (i + 1) * B], summary[i * B : (i + 1) * B], tags, vals)
     return tags, vals
 
 

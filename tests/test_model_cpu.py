@@ -215,3 +215,16 @@ def test_fp8_conversion_cpu_emulation_trains():
     l0 = projected_step(m, params, opt, tok, tgt, precision="fp8")
     l1 = projected_step(m, params, opt, tok, tgt, precision="fp8")
     assert l0 == l0 and l1 == l1
+
+
+def test_cam_buffer_stacked_chunks_match_sequential():
+    """The write chunks are independent until the slot write, so running them stacked on the batch dimension
+    gives the same buffer as one trunk pass per chunk (reference order: gdnet/loss.py:54-85)."""
+    torch.manual_seed(3)
+    model = GDNet(vocab_size=64, d_embed=16, d=32, n_layers=2, n_cycles=1, kernel_size=4, chunk_size=16)
+    chunks = torch.randint(0, 64, (3, 5, 16))
+    tags_a, vals_a = build_cam_buffer(model, chunks, max_rows=1)          # one chunk per pass
+    tags_b, vals_b = build_cam_buffer(model, chunks)                       # all stacked
+    tags_c, vals_c = build_cam_buffer(model, chunks, max_rows=2 * 3 * 16)  # groups of two
+    for got_t, got_v in ((tags_b, vals_b), (tags_c, vals_c)):
+        assert torch.allclose(got_t, tags_a, atol=1e-5) and torch.allclose(got_v, vals_a, atol=1e-5)
