@@ -99,6 +99,63 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
+// Sliding-window formulation of the forward conv: a thread owns 8 channels and TT consecutive time steps of one
+// sequence, keeps the last KT-1 input rows in registers and loads every further row once (TT + KT - 1 row loads
+// for TT outputs instead of KT per output). The loads of a strip are independent, so the compiler keeps them
+// all in flight.
+template <int KT, int TT>
+__global__ void __launch_bounds__(256)
+dwconv_fwd_sw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
+                     const float* __restrict__ wt, __nv_bfloat16* __restrict__ out, int B, int T, int d,
+                     int64_t x_ld, int64_t out_ld, const RowQuantOut qo) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ch = (blockIdx.y * 32 + lane) * 8;
+  const int strip = blockIdx.x * 8 + warp;          // T % TT == 0: a strip never crosses a sequence boundary
+  const int row0 = strip * TT;
+  if (row0 >= B * T || ch >= d) return;
+  const int b = row0 / T, t0 = row0 - b * T;
+  float tap[KT][8];
+#pragma unroll
+  for (int i = 0; i < KT; ++i) {
+    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch);
+    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch + 4);
+    tap[i][0] = w0.x; tap[i][1] = w0.y; tap[i][2] = w0.z; tap[i][3] = w0.w;
+    tap[i][4] = w1.x; tap[i][5] = w1.y; tap[i][6] = w1.z; tap[i][7] = w1.w;
+  }
+  uint4 in[TT + KT - 1];     // rows kept packed (bf16); unpacked at each use to stay within the register budget
+#pragma unroll
+  for (int i = 0; i < KT - 1; ++i) {
+    const int t = t0 - (KT - 1) + i;
+    in[i] = make_uint4(0, 0, 0, 0);
+    if (t >= 0) in[i] = *reinterpret_cast<const uint4*>(x + ((int64_t)b * T + t) * x_ld + ch);
+    else if (halo != nullptr) in[i] = *reinterpret_cast<const uint4*>(halo + ((int64_t)b * (KT - 1) + (t + KT - 1)) * d + ch);
+  }
+#pragma unroll
+  for (int j = 0; j < TT; ++j) in[KT - 1 + j] = *reinterpret_cast<const uint4*>(x + (int64_t)(row0 + j) * x_ld + ch);
+#pragma unroll
+  for (int j = 0; j < TT; ++j) {
+    float acc[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < KT; ++i) {
+      const uint32_t w[4] = {in[j + i].x, in[j + i].y, in[j + i].z, in[j + i].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 f = unpack_bf16x2(w[c]);
+        acc[2 * c] = fmaf(tap[i][2 * c], f.x, acc[2 * c]);
+        acc[2 * c + 1] = fmaf(tap[i][2 * c + 1], f.y, acc[2 * c + 1]);
+      }
+    }
+    store_bf16_vec<8>(out + (int64_t)(row0 + j) * out_ld + ch, acc);
+    if (qo.q != nullptr) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] = __bfloat162float(__float2bfloat16(acc[c]));
+      quant_emit_8(qo, acc, row0 + j, ch, true);
+    }
+  }
+}
+
 // dx[t] = sum_j w[k-1-j] dc[t+j] for t in [t_lo, T), t_lo = -(k-1) when the halo gradient is wanted
 template <int KT>
 __global__ void __launch_bounds__(256)
@@ -143,6 +200,85 @@ dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restric
   } else {
     store_bf16_vec<8>(dhalo + ((int64_t)b * (k - 1) + (t + k - 1)) * d + ch, acc);
   }
+}
+
+// Sliding-window form of dx for t in [0, T): a thread owns 8 channels and TT consecutive time steps and loads
+// the TT + KT - 1 rows of dc it needs once (rows past the end of the sequence are zero).
+template <int KT, int TT>
+__global__ void __launch_bounds__(256)
+dwconv_dx_sw_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ wt,
+                    const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx, int B, int T, int d,
+                    int64_t dc_ld) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ch = (blockIdx.y * 32 + lane) * 8;
+  const int strip = blockIdx.x * 8 + warp;
+  const int row0 = strip * TT;
+  if (row0 >= B * T || ch >= d) return;
+  const int b = row0 / T, t0 = row0 - b * T;
+  float tap[KT][8];      // tap[j] multiplies dc[t + j]: w[KT-1-j]
+#pragma unroll
+  for (int j = 0; j < KT; ++j) {
+    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)(KT - 1 - j) * d + ch);
+    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)(KT - 1 - j) * d + ch + 4);
+    tap[j][0] = w0.x; tap[j][1] = w0.y; tap[j][2] = w0.z; tap[j][3] = w0.w;
+    tap[j][4] = w1.x; tap[j][5] = w1.y; tap[j][6] = w1.z; tap[j][7] = w1.w;
+  }
+  uint4 g[TT + KT - 1];
+#pragma unroll
+  for (int i = 0; i < TT + KT - 1; ++i) {
+    g[i] = make_uint4(0, 0, 0, 0);
+    if (t0 + i < T) g[i] = *reinterpret_cast<const uint4*>(dc + (int64_t)(row0 + i) * dc_ld + ch);
+  }
+#pragma unroll
+  for (int i = 0; i < TT; ++i) {
+    float acc[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < KT; ++j) {
+      const uint32_t w[4] = {g[i + j].x, g[i + j].y, g[i + j].z, g[i + j].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 f = unpack_bf16x2(w[c]);
+        acc[2 * c] = fmaf(tap[j][2 * c], f.x, acc[2 * c]);
+        acc[2 * c + 1] = fmaf(tap[j][2 * c + 1], f.y, acc[2 * c + 1]);
+      }
+    }
+    const int t = t0 + i;
+    if (dx_tail_add != nullptr && t >= T - (KT - 1)) {
+      float extra[8];
+      load_bf16_vec<8>(dx_tail_add + ((int64_t)b * (KT - 1) + (t - (T - (KT - 1)))) * d + ch, extra);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] += extra[c];
+    }
+    store_bf16_vec<8>(dx + (int64_t)(row0 + i) * d + ch, acc);
+  }
+}
+
+// The k-1 halo-gradient rows of every sequence (t in [-(k-1), 0)), for the sequence-parallel exchange.
+__global__ void __launch_bounds__(256)
+dwconv_dhalo_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ wt, __nv_bfloat16* __restrict__ dhalo,
+                    int B, int T, int d, int k, int64_t dc_ld) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ch = (blockIdx.y * 32 + lane) * 8;
+  const int r = blockIdx.x * 8 + warp;
+  if (ch >= d || r >= B * (k - 1)) return;
+  const int b = r / (k - 1), t = r - b * (k - 1) - (k - 1);   // t in [-(k-1), 0)
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+  for (int j = 0; j < k; ++j) {
+    const int tt = t + j;
+    if (tt < 0 || tt >= T) continue;
+    float g[8];
+    load_bf16_vec<8>(dc + ((int64_t)b * T + tt) * dc_ld + ch, g);
+    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)(k - 1 - j) * d + ch);
+    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)(k - 1 - j) * d + ch + 4);
+    const float tap[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = fmaf(tap[c], g[c], acc[c]);
+  }
+  store_bf16_vec<8>(dhalo + ((int64_t)b * (k - 1) + (t + k - 1)) * d + ch, acc);
 }
 
 // dw[ch][i] += sum_{b,t} dc[b,t,ch] * xpad[b, t-(k-1)+i, ch]: a lane owns 4 channels and walks a strip of
@@ -229,6 +365,11 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if ((int64_t)a.B * (a.T + 16) >= (1ll << 31)) return "dwconv: B*T must be below 2^31";
   dim3 grid((unsigned)(((int64_t)a.B * a.T + 7) / 8), (a.d + 255) / 256);
   if (a.quant.q != nullptr && a.d % 128 != 0) return "dwconv: a quantised output needs d % 128 == 0";
+  if (a.k == 4 && a.T % 8 == 0) {
+    dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
+    dwconv_fwd_sw_kernel<4, 8><<<sgrid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
+  }
   if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld, a.quant);
   else dwconv_fwd_pt_kernel<0><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld, a.quant);
   return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
@@ -240,6 +381,16 @@ const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   if ((int64_t)a.B * (a.T + 16) >= (1ll << 31)) return "dwconv: B*T must be below 2^31";
   const int rows_per_b = a.T + (a.dhalo != nullptr ? a.k - 1 : 0);
   dim3 grid((unsigned)(((int64_t)a.B * rows_per_b + 7) / 8), (a.d + 255) / 256);
+  if (a.k == 4 && a.T % 8 == 0) {
+    dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
+    dwconv_dx_sw_kernel<4, 8><<<sgrid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.B, a.T, a.d, a.dc_ld);
+    if (a.dhalo != nullptr) {
+      dim3 hgrid((unsigned)((a.B * (a.k - 1) + 7) / 8), (a.d + 255) / 256);
+      dwconv_dhalo_kernel<<<hgrid, 256, 0, st>>>(a.dc, a.w, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
+    }
+    if (cudaGetLastError() != cudaSuccess) return "dwconv_dx launch failed";
+    return conv_dw_launch<4>(a, st);
+  }
   if (a.k == 4) dwconv_dx_pt_kernel<4><<<grid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
   else dwconv_dx_pt_kernel<0><<<grid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
   if (cudaGetLastError() != cudaSuccess) return "dwconv_dx launch failed";
