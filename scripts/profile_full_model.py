@@ -37,7 +37,7 @@ def main():
     batches = bench.make_batches(cfg, args.warmup + args.steps, seed=1)
 
     def run(b):
-        seq, wc = b[0].to(dev), b[1].to(dev)
+        seq, wc = b[0].to(dev), (b[1].to(dev) if b[1] is not None else None)
         return step(seq[:, :-1], seq[:, 1:], wc)
 
     for b in batches[: args.warmup]:
