@@ -436,6 +436,16 @@ void colsum(const Tensor& x, Tensor out) {
   GD_LAUNCH(gd::launch_colsum(bf16_ptr(x, "x"), f32_mut(out, "out"), x.size(0), (int)x.size(1), x.stride(0), stream_of(x)));
 }
 
+void segment_add(const Tensor& src, const Tensor& dst_addr, const Tensor& seg_off) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && dst_addr.is_cuda() && dst_addr.scalar_type() == at::kLong && dst_addr.is_contiguous(),
+              "segment_add: src contiguous, dst_addr int64 on the device");
+  TORCH_CHECK(seg_off.is_cuda() && seg_off.scalar_type() == at::kInt && seg_off.numel() == dst_addr.numel(),
+              "segment_add: one int32 offset per segment");
+  GD_LAUNCH(gd::launch_segment_add(f32_ptr(src, "src"), dst_addr.data_ptr<int64_t>(), seg_off.data_ptr<int>(),
+                                   (int)dst_addr.numel(), (int)src.numel(), stream_of(src)));
+}
+
 void scale_cols(const Tensor& w, const Tensor& colw, Tensor out) {
   c10::cuda::CUDAGuard guard(w.device());
   TORCH_CHECK(w.is_contiguous() && out.is_contiguous() && w.dim() == 2 && colw.numel() == w.size(1), "scale_cols: shapes");
@@ -603,6 +613,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode, bool pow2=False, Tensor(e!)? p_row=None, Tensor(f!)? p_col=None) -> ()", &quant_tile);
   m.def("quant_tensor(Tensor x, Tensor scale, Tensor(a!) q_row, Tensor(b!)? q_col, Tensor(c!)? amax) -> ()", &quant_tensor);
   m.def("colsum(Tensor x, Tensor(a!) out) -> ()", &colsum);
+  m.def("segment_add(Tensor src, Tensor dst_addr, Tensor seg_off) -> ()", &segment_add);
   m.def("scale_cols(Tensor w, Tensor colw, Tensor(a!) out) -> ()", &scale_cols);
   m.def("unscale_cols_bwd(Tensor dW2w, Tensor W2, Tensor colw, Tensor(a!) dW2, Tensor(b!) dcolw) -> ()", &unscale_cols_bwd);
   m.def("cross_entropy(Tensor(a!) logits, Tensor targets, Tensor(b!) row_loss, Tensor inv_count, int vocab, int ignore_index, float grad_scale, bool write_grad) -> ()", &cross_entropy);

@@ -996,6 +996,28 @@ const char* launch_colsum(const __nv_bfloat16* x, float* out, int64_t rows, int 
   return cudaGetLastError() == cudaSuccess ? nullptr : "colsum launch failed";
 }
 
+// dst_s[j] += src[off_s + j] for the segments s of a table: one launch delivers the gradients of all small
+// parameters of a layer step (biases, norm weights, conv taps) from one packed buffer to their places in the
+// flat gradient buffer.
+__global__ void __launch_bounds__(256)
+segment_add_kernel(const float* __restrict__ src, const int64_t* __restrict__ dst_addr, const int* __restrict__ seg_off,
+                   int n_seg, int total) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= total) return;
+  int s = 0;
+  while (s + 1 < n_seg && seg_off[s + 1] <= i) ++s;     // a handful of segments
+  float* dst = reinterpret_cast<float*>(dst_addr[s]);
+  dst[i - seg_off[s]] += src[i];
+}
+
+const char* launch_segment_add(const float* src, const int64_t* dst_addr, const int* seg_off, int n_seg, int total,
+                               cudaStream_t st) {
+  if (n_seg < 1 || n_seg > 64) return "segment_add: between 1 and 64 segments";
+  if (total <= 0) return nullptr;
+  segment_add_kernel<<<(total + 255) / 256, 256, 0, st>>>(src, dst_addr, seg_off, n_seg, total);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "segment_add launch failed";
+}
+
 // W2w[i][j] = W2[i][j] * w_norm[j]  (folds the RMSNorm weight into the GEMM that follows it)
 __global__ void scale_cols_kernel(const __nv_bfloat16* __restrict__ w, const float* __restrict__ colw,
                                   __nv_bfloat16* __restrict__ out, int64_t n, int cols) {

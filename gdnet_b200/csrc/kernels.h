@@ -127,6 +127,9 @@ const char* launch_quant_tensor(const __nv_bfloat16* x, const float* scale, uint
 
 // ---- reductions and small helpers -------------------------------------------------------------
 const char* launch_colsum(const __nv_bfloat16* x, float* out, int64_t rows, int cols, int64_t ld, cudaStream_t st);
+// dst_s[j] += src[seg_off[s] + j]; dst_addr holds absolute device addresses (fp32), seg_off is ascending from 0
+const char* launch_segment_add(const float* src, const int64_t* dst_addr, const int* seg_off, int n_seg, int total,
+                               cudaStream_t st);
 const char* launch_scale_cols(const __nv_bfloat16* w, const float* colw, __nv_bfloat16* out, int64_t rows, int cols,
                               cudaStream_t st);
 const char* launch_unscale_cols_bwd(const float* dW2w, const __nv_bfloat16* W2, const float* colw, float* dW2,

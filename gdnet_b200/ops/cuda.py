@@ -142,6 +142,7 @@ def clear_caches() -> None:
     _taps_cache.clear()
     _w2w_cache.clear()
     _side_offers.clear()
+    _seg_tables.clear()
 
 
 # --------------------------------------------------------------------------------------
@@ -343,6 +344,30 @@ def _sink_vec(p, g32):
         accumulate_main_grad(mg, g32)
         return None
     return g32.to(p.dtype).view_as(p)
+
+
+_seg_tables: dict = {}
+
+
+def _sink_vecs(params, packed, views):
+    """Deliver the gradients of several small parameters that sit back to back in ``packed`` (``views`` are the
+    per-parameter views of it): one ``segment_add`` launch into their ``main_grad`` places when the engine has
+    installed local fp32 gradient buffers, else one by one."""
+    mgs = [_main_grad(p) for p in params]
+    if _spread_grads or any(m is None or m.dtype != F32 or not m.is_contiguous() for m in mgs):
+        return [_sink_vec(p, v) for p, v in zip(params, views)]
+    key = tuple(m.data_ptr() for m in mgs)
+    tab = _seg_tables.get(key)
+    if tab is None:
+        offs, o = [], 0
+        for v in views:
+            offs.append(o)
+            o += v.numel()
+        tab = (torch.tensor(key, dtype=torch.int64, device=packed.device),
+               torch.tensor(offs, dtype=torch.int32, device=packed.device))
+        _seg_tables[key] = tab
+    K.segment_add(packed, tab[0], tab[1])
+    return [None] * len(params)
 
 
 def _wgrad_target(p):
@@ -737,7 +762,7 @@ class _LayerStepFn(torch.autograd.Function):
         fwd_out = torch.empty(B, T, d, dtype=BF16, device=dev)
         side_out = torch.empty(B, T, d, dtype=BF16, device=dev)
         rstd_z = torch.empty(M, dtype=F32, device=dev)
-        gate_sum = torch.zeros((), dtype=F32, device=dev)
+        gate_sum = torch.zeros((), dtype=F32, device=dev) if want_gate_sum else None
         if fp8:
             nu8, nsu, npu = _alloc_u8(M, d, dev)      # the next step's [s ; c] operand: this kernel fills the s half
             K.gate_update_fwd(g_pre, z, c, s2, f32(rnw), fwd_out.view(M, d), side_out.view(M, d), None, rstd_z,
@@ -780,9 +805,12 @@ class _LayerStepFn(torch.autograd.Function):
         dz = torch.empty(M, d, dtype=BF16, device=dev)
         dsc = torch.empty(M, 2 * d, dtype=BF16, device=dev)
         rowcoef = torch.empty(M, dtype=F32, device=dev)
-        db2g = torch.zeros(d, dtype=F32, device=dev)
-        dw_r = torch.zeros(d, dtype=F32, device=dev)
-        db2r = torch.zeros(d, dtype=F32, device=dev)
+        # gradients of the seven small parameters of the step live in one zeroed buffer (one fill, and one
+        # launch to deliver them): gb2, rnw, rb2, gnw, gb1, rb1, conv taps
+        k_taps = conv_w.shape[1]
+        vec = torch.zeros(6 * d + d * k_taps, dtype=F32, device=dev)
+        db2g, dw_r, db2r, dgnw, db1g, db1r = (vec[i * d : (i + 1) * d] for i in range(6))
+        dwc = vec[6 * d :].view(d, k_taps)
         K.gate_update_bwd(dF2, dS2, g_pre, z, c, s2, f32(rnw), f32(gb2), rstd_z, ssq, eps_g, dgm, dq, dz, dsc, rowcoef,
                           db2g, dw_r, db2r)
 
@@ -790,7 +818,6 @@ class _LayerStepFn(torch.autograd.Function):
         W2w = _folded_w2(gW2, gnw)
         dW2w = gemm_bf16(dq, h, a_mn=True, b_mn=True, out_dtype=F32)
         tgt2, main2 = _wgrad_target(gW2)
-        dgnw = torch.zeros(d, dtype=F32, device=dev)
         if main2 and _spread_grads:
             dW2 = torch.zeros_like(dW2w)
             K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), dW2, dgnw)
@@ -798,14 +825,12 @@ class _LayerStepFn(torch.autograd.Function):
         else:
             K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), tgt2, dgnw)
         dh_pre = gemm_bf16(dq, W2w, b_mn=True, aux=hg_pre, aux_mode=AUX_RMS_SILU_BWD, rowcoef=rowcoef)
-        db1g = torch.zeros(d, dtype=F32, device=dev)
         K.colsum(dh_pre, db1g)
         g_gW1 = _wgrad_bf16(dh_pre, c, gW1)
         dc_view = dsc[:, d:]
         gemm_bf16(dh_pre, gW1, b_mn=True, out=dc_view, aux=dc_view, aux_mode=AUX_ADD)
 
         # ---- recovery MLP ----
-        db1r = torch.zeros(d, dtype=F32, device=dev)
         if fp8:
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
             dz8, pdz, dzt8, pdzt = quantize_both_mx(dz, Q_COLS)
@@ -838,15 +863,15 @@ class _LayerStepFn(torch.autograd.Function):
 
         # ---- conv ----
         dx = torch.empty(B, T, d, dtype=BF16, device=dev)
-        dwc = torch.zeros(conv_w.shape, dtype=F32, device=dev)
         dhalo = torch.empty_like(halo) if halo is not None else None
         K.dwconv_bwd(dsc.view(B, T, 2 * d)[:, :, d:], x, halo, taps_t(conv_w), None, dx, dhalo, dwc)
         ds = dsc.view(B, T, 2 * d)[:, :, :d]
 
         g_gW2 = None if main2 else tgt2.to(gW2.dtype)
-        return (dx, ds, dhalo, _sink_vec(conv_w, dwc), g_rW1, _sink_vec(rb1, db1r), g_rW2, _sink_vec(rb2, db2r),
-                _sink_vec(rnw, dw_r), g_gW1, _sink_vec(gb1, db1g), _sink_vec(gnw, dgnw), g_gW2,
-                _sink_vec(gb2, db2g), None, None, None, None, None)
+        g_gb2, g_rnw, g_rb2, g_gnw, g_gb1, g_rb1, g_conv = _sink_vecs(
+            (gb2, rnw, rb2, gnw, gb1, rb1, conv_w), vec, (db2g, dw_r, db2r, dgnw, db1g, db1r, dwc))
+        return (dx, ds, dhalo, g_conv, g_rW1, g_rb1, g_rW2, g_rb2, g_rnw, g_gW1, g_gb1, g_gnw, g_gW2, g_gb2,
+                None, None, None, None, None)
 
 
 def _fused_step_ok(fwd, side, layer, r) -> bool:
