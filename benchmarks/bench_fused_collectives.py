@@ -1,0 +1,137 @@
+"""Device-timed microbenchmarks of the peer-memory collectives against their NCCL counterparts.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        benchmarks/bench_fused_collectives.py [--params 350e6] [--json out.json]
+
+* gradient reduce-scatter + projection + AdamW + parameter all-gather in one kernel
+  (``fused_reduce_adamw_kernel``) against NCCL all-reduce of both gradient buffers + the local AdamW kernel;
+* halo push/flag/wait kernel against ``dist.batch_isend_irecv`` of the same message;
+* one-shot MAX all-reduce of a small vector against ``dist.all_reduce(MAX)``.
+
+Times are CUDA events on the launching stream, max over ranks. The roofline of the update kernel is the
+slower direction of its NVLink traffic at 770 GB/s per direction: every rank pulls its shard of two fp32
+buffers from N-1 peers and pushes its updated bf16 shard to N-1 peers.
+"""
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def timed(fn, iters, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--params", type=float, default=350e6)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from gdnet_b200.ops import cuda as cu
+    from gdnet_b200.parallel.symm import SymmBuffer, max_allreduce_
+
+    K = cu.K
+    per = -(-int(args.params) // world)
+    per = -(-per // 128) * 128
+    n = per * world
+    grp = dist.group.WORLD
+    sp, sgt, sgi = SymmBuffer(n * 2, grp, dev), SymmBuffer(n * 4, grp, dev), SymmBuffer(n * 4, grp, dev)
+    flags = SymmBuffer(4096, grp, dev)
+    gt, gi = sgt.view(torch.float32, n), sgi.view(torch.float32, n)
+    gt.normal_()
+    gi.normal_()
+    m, v = torch.zeros(per, device=dev), torch.zeros(per, device=dev)
+    scalars = torch.tensor([0.1, 1.0], device=dev)
+    sums = torch.zeros(8, device=dev)
+    sp.barrier()
+    seq = [0]
+
+    def fused():
+        seq[0] += 1
+        K.allreduce_adamw(sgt.ptr_table, sgi.ptr_table, sp.ptr_table, flags.ptr_table, m, v, scalars, n, rank, world,
+                          seq[0] * 8, 0, True, 0.1, 1e-3, 0.9, 0.999, 1e-8, 0.01, seq[0], sums)
+
+    p_l = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    g1, g2 = torch.randn(n, device=dev), torch.randn(n, device=dev)
+    m2, v2 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+
+    def nccl():
+        dist.all_reduce(g1)
+        dist.all_reduce(g2)
+        K.projected_adamw(p_l, g1, g2, m2, v2, scalars, 0.1, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1)
+
+    res = {"world": world, "params": n}
+    res["fused_update_ms"] = timed(fused, args.iters)
+    res["nccl_allreduce_plus_adamw_ms"] = timed(nccl, args.iters)
+    link = 770e9
+    pulled, pushed = (world - 1) * per * 8, (world - 1) * per * 2      # bytes in / out per rank
+    nvlink_bytes = pulled + pushed
+    res["fused_nvlink_bytes_per_rank"] = nvlink_bytes
+    res["fused_roofline_ms"] = max(pulled, pushed) / link * 1e3
+    res["fused_fraction_of_nvlink_roofline"] = res["fused_roofline_ms"] / res["fused_update_ms"] if world > 1 else None
+
+    # halo exchange: (B, k-1, d) bf16 messages, as in the 1.3B sequence-parallel config
+    tail = torch.randn(1, 3, 2048, device=dev, dtype=torch.bfloat16)
+    slot = [0]
+
+    def halo_kernel():
+        slot[0] = (slot[0] + 1) % cu.HALO_SLOTS
+        cu.halo_exchange(tail, dist.group.WORLD, slot[0])
+
+    def halo_nccl():
+        ops, recv = [], torch.empty_like(tail)
+        if rank + 1 < world:
+            ops.append(dist.P2POp(dist.isend, tail, rank + 1))
+        if rank > 0:
+            ops.append(dist.P2POp(dist.irecv, recv, rank - 1))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+    with torch.no_grad():
+        res["halo_kernel_us"] = timed(halo_kernel, 50) * 1e3
+        res["halo_nccl_sendrecv_us"] = timed(halo_nccl, 50) * 1e3
+
+    vec = torch.rand(512, device=dev)
+    res["max_allreduce_kernel_us"] = timed(lambda: max_allreduce_(vec), 50) * 1e3
+    res["max_allreduce_nccl_us"] = timed(lambda: dist.all_reduce(vec, op=dist.ReduceOp.MAX), 50) * 1e3
+    torch.cuda.synchronize()
+    from gdnet_b200 import _ext
+
+    _ext.check_status(vec)
+    if rank == 0:
+        print(json.dumps(res, indent=1))
+        if args.json:
+            with open(args.json, "w") as f:
+                json.dump(res, f, indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -578,6 +578,22 @@ void peer_add(Tensor dst, const Tensor& src) {
   GD_LAUNCH(gd::launch_peer_add(a, stream_of(dst)));
 }
 
+void max_allreduce(Tensor vec, const Tensor& area_ptrs, const Tensor& flag_ptrs, int64_t slot_elems, int64_t rank,
+                   int64_t world, int64_t seq) {
+  c10::cuda::CUDAGuard guard(vec.device());
+  TORCH_CHECK(vec.is_contiguous() && vec.scalar_type() == at::kFloat, "max_allreduce: vec must be contiguous fp32");
+  TORCH_CHECK(area_ptrs.numel() == world && flag_ptrs.numel() == world, "max_allreduce: one pointer per rank");
+  gd::MaxAllReduceArgs a{};
+  a.vec = vec.data_ptr<float>();
+  a.n = (int)vec.numel();
+  a.areas = reinterpret_cast<float* const*>(area_ptrs.data_ptr<int64_t>());
+  a.flags = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
+  a.slot_elems = (int)slot_elems;
+  a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq;
+  a.status = status_ptr(vec);
+  GD_LAUNCH(gd::launch_max_allreduce(a, stream_of(vec)));
+}
+
 void halo_push_wait(const Tensor& tail, Tensor halo_out, const Tensor& slot_ptrs, const Tensor& flag_ptrs,
                     int64_t slot_offset_bytes, int64_t flag_index, int64_t rank, int64_t world, int64_t seq,
                     bool reverse) {
@@ -627,5 +643,6 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> ()", &register_grad_sink);
   m.def("clear_grad_sinks() -> ()", &clear_grad_sinks);
   m.def("peer_add(Tensor(a!) dst, Tensor src) -> ()", &peer_add);
+  m.def("max_allreduce(Tensor(a!) vec, Tensor area_ptrs, Tensor flag_ptrs, int slot_elems, int rank, int world, int seq) -> ()", &max_allreduce);
   m.def("halo_push_wait(Tensor tail, Tensor(a!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, int slot_offset_bytes, int flag_index, int rank, int world, int seq, bool reverse) -> ()", &halo_push_wait);
 }

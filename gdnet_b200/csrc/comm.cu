@@ -228,6 +228,48 @@ const char* launch_peer_add(const PeerAddArgs& a, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------------------
+// one-shot MAX all-reduce of a small vector
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+max_allreduce_kernel(const MaxAllReduceArgs a) {
+  // push: this rank's vector into slot `rank` of every rank's area (its own included). Two sets of slots
+  // alternate with the sequence number: a rank may already be pushing call k+1 while a slower one still reads
+  // call k, but it cannot reach call k+2 before every rank has started k+1, i.e. finished reading k.
+  const size_t set = (size_t)(a.seq & 1u) * a.world * a.slot_elems;
+  for (int r = 0; r < a.world; ++r) {
+    float* dst = a.areas[r] + set + (size_t)a.rank * a.slot_elems;
+    for (int i = threadIdx.x; i < a.n; i += blockDim.x) dst[i] = a.vec[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.world) st_release_sys(a.flags[threadIdx.x] + a.rank, a.seq);
+  __shared__ int ok_all;
+  if (threadIdx.x == 0) ok_all = 1;
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    if (!wait_flag_ge(a.flags[a.rank] + threadIdx.x, a.seq)) {
+      report(a.status, STATUS_TIMEOUT_PEER_FLAG, 50, (int)threadIdx.x);
+      ok_all = 0;
+    }
+  }
+  __syncthreads();
+  if (!ok_all) return;      // the vector keeps this rank's own values
+  const float* mine = a.areas[a.rank] + set;
+  for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
+    float m = __ldcv(mine + i);
+    for (int r = 1; r < a.world; ++r) m = fmaxf(m, __ldcv(mine + (size_t)r * a.slot_elems + i));
+    a.vec[i] = m;
+  }
+}
+
+const char* launch_max_allreduce(const MaxAllReduceArgs& a, cudaStream_t st) {
+  if (a.world < 1 || a.world > 64) return "max_allreduce: world size must be in [1, 64]";
+  if (a.n > a.slot_elems) return "max_allreduce: vector longer than a slot";
+  max_allreduce_kernel<<<1, 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "max_allreduce launch failed";
+}
+
+// ---------------------------------------------------------------------------------------
 // neighbour exchange for sequence parallelism
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)

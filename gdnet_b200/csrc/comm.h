@@ -56,6 +56,21 @@ struct PeerAddArgs {
 };
 const char* launch_peer_add(const PeerAddArgs& a, cudaStream_t st);
 
+// One-shot MAX all-reduce of a small fp32 vector (the amax windows of the per-tensor FP8 recipe): every rank
+// stores its vector into its slot of every rank's exchange area, raises a flag there, waits (bounded) for all
+// flags and takes the element-wise maximum. One launch, one block.
+struct MaxAllReduceArgs {
+  float* vec;               // n values, in place
+  int n;
+  float* const* areas;      // [world] exchange areas: 2 * world slots of `slot_elems` floats each
+  uint32_t* const* flags;   // [world] flag words: flags[r][writer]
+  int slot_elems;
+  int rank, world;
+  uint32_t seq;             // strictly increasing per call
+  Status* status;
+};
+const char* launch_max_allreduce(const MaxAllReduceArgs& a, cudaStream_t st);
+
 // Sequence-parallel neighbour exchange: store `tail` into the next rank's slot, raise its flag,
 // wait (bounded) for this rank's own flag from the previous rank, copy the slot out.
 // reverse = true exchanges in the other direction (halo gradients).

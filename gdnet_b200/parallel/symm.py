@@ -53,9 +53,35 @@ def get_buffer(key, nbytes: int, group, device) -> SymmBuffer:
 
 def release_all() -> None:
     _HANDLES.clear()
+    _MAXRED.clear()
 
 
 def halo_exchange_symm(tail: torch.Tensor, group, slot):
     from ..ops import cuda as cuda_ops
 
     return cuda_ops.halo_exchange(tail, group, slot)
+
+
+_MAXRED: dict = {}
+
+
+def max_allreduce_(vec: torch.Tensor, group=None) -> torch.Tensor:
+    """In-place element-wise MAX of a small fp32 CUDA vector over the ranks of ``group``: every rank stores
+    its vector into every peer's exchange area and waits (bounded) for the peers' flags, one kernel, no
+    NCCL call (``csrc/comm.cu:max_allreduce_kernel``). Reference counterpart: the MAX all-reduce of the amax
+    windows in gdnet/utils/fp8.py:16-44."""
+    from ..ops import cuda as cuda_ops
+
+    group = group if group is not None else dist.group.WORLD
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    n = vec.numel()
+    st = _MAXRED.get(id(group))
+    if st is None or st["slot"] < n:
+        slot = max(256, 1 << (n - 1).bit_length())
+        st = {"slot": slot, "area": SymmBuffer(2 * world * slot * 4, group, vec.device),
+              "flags": SymmBuffer(max(256, world * 4), group, vec.device), "seq": 0}
+        st["area"].barrier()
+        _MAXRED[id(group)] = st
+    st["seq"] += 1
+    cuda_ops.K.max_allreduce(vec, st["area"].ptr_table, st["flags"].ptr_table, st["slot"], rank, world, st["seq"])
+    return vec

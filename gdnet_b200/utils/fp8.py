@@ -79,6 +79,19 @@ def convert_to_fp8(model: nn.Module, recipe: str = "block", untie_head: bool = F
 
 
 @torch.no_grad()
+def _peer_max_ok() -> bool:
+    """The peer-memory MAX all-reduce needs torch's symmetric memory; ``GDNET_AMAX_NCCL=1`` forces NCCL."""
+    import os
+
+    if os.environ.get("GDNET_AMAX_NCCL", "0") == "1":
+        return False
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except Exception:
+        return False
+    return True
+
+
 def update_fp8_scales(model: nn.Module, group=None) -> None:
     """Refresh the delayed per-tensor scales from the amax windows (tensor recipe).
 
@@ -89,8 +102,13 @@ def update_fp8_scales(model: nn.Module, group=None) -> None:
     if not mods:
         return
     amax = torch.cat([t for m in mods for t in (m._amax_x, m._amax_w)]).clamp_(min=1e-12)
-    if dist.is_available() and dist.is_initialized():
-        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        if amax.is_cuda and _peer_max_ok():
+            from ..parallel.symm import max_allreduce_
+
+            max_allreduce_(amax, group)      # one peer-memory kernel instead of an NCCL call
+        else:
+            dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
     for i, m in enumerate(mods):
         m.scale_x.copy_(FP8_MAX / amax[2 * i])
         m.scale_w.copy_(FP8_MAX / amax[2 * i + 1])

@@ -82,6 +82,37 @@ def engine_scatter_vs_nccl(rank, world, dev):
         assert float(gc.g_task[lo:hi].abs().max()) == 0.0, "the consumed shard was not cleared"
 
 
+def peer_max_allreduce(rank, world, dev):
+    """One-kernel MAX all-reduce over peer memory against NCCL, repeated (the slot sets alternate), and through
+    update_fp8_scales on the per-tensor recipe."""
+    from gdnet_b200.parallel.symm import max_allreduce_
+
+    for it in range(5):
+        g = torch.Generator().manual_seed(1000 * it + rank)
+        v = torch.rand(300 + 17 * it, generator=g).to(dev)
+        want = v.clone()
+        dist.all_reduce(want, op=dist.ReduceOp.MAX)
+        got = max_allreduce_(v.clone())
+        torch.cuda.synchronize()
+        _ext.check_status(v)
+        assert torch.equal(got, want), f"iteration {it}: peer MAX all-reduce differs from NCCL"
+    from gdnet_b200.utils.fp8 import update_fp8_scales
+
+    torch.manual_seed(0)
+    m = GDNet(vocab_size=1024, d_embed=128, d=128, n_layers=1, n_cycles=1, kernel_size=4, chunk_size=256).to(dev)
+    cast_for_precision(m, "fp8", recipe="tensor")
+    tok = torch.randint(0, 1024, (2, 256), generator=torch.Generator().manual_seed(rank)).to(dev)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        m(tok)
+    update_fp8_scales(m)
+    torch.cuda.synchronize()
+    _ext.check_status(tok)
+    scales = torch.cat([b.reshape(-1) for n, b in m.named_buffers() if n.endswith("scale_x") or n.endswith("scale_w")])
+    ref = scales.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(ref, scales), "ranks disagree on the FP8 scales after the amax exchange"
+
+
 def sp_matches_single(rank, world, dev):
     """Forward + backward of the model over a sequence split across ranks equals the unsplit run."""
     T = 256 * world

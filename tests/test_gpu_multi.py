@@ -34,6 +34,10 @@ def test_epilogue_reduce_scatter_matches_nccl():
     _run("engine_scatter_vs_nccl")
 
 
+def test_peer_max_allreduce_matches_nccl():
+    _run("peer_max_allreduce")
+
+
 def test_sequence_parallel_matches_single_gpu():
     _run("sp_matches_single")
 
