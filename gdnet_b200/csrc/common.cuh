@@ -409,6 +409,19 @@ __device__ __forceinline__ uint8_t to_e4m3(float v) {
 }
 
 // ---------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------------------
+// Kernels launched through launch_pdl() (launch.h) may start while the previous kernel of the stream is still
+// draining: their blocks become resident as its blocks retire and run whatever does not touch global memory
+// (barrier setup, TMEM allocation). pdl_enter() is where they wait until the previous kernel has completed and
+// its memory operations are visible; every thread calls it before its first global access. It then lets the
+// next kernel do the same with this one. Without such a launch both instructions do nothing.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------
 // FP8 block quantisation helpers
 // ---------------------------------------------------------------------------------------
 // Scale of a block with the given amax: amax/448, or, for the hardware block-scaled MMA, the next

@@ -7,6 +7,7 @@
 #include "kernels.h"
 
 #include "common.cuh"
+#include "launch.h"
 
 namespace gd {
 
@@ -108,6 +109,7 @@ __global__ void __launch_bounds__(256)
 dwconv_fwd_sw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
                      const float* __restrict__ wt, __nv_bfloat16* __restrict__ out, int B, int T, int d,
                      int64_t x_ld, int64_t out_ld, const RowQuantOut qo) {
+  pdl_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
   const int strip = blockIdx.x * 8 + warp;          // T % TT == 0: a strip never crosses a sequence boundary
@@ -209,6 +211,7 @@ __global__ void __launch_bounds__(256)
 dwconv_dx_sw_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ wt,
                     const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx, int B, int T, int d,
                     int64_t dc_ld) {
+  pdl_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
   const int strip = blockIdx.x * 8 + warp;
@@ -291,6 +294,7 @@ __global__ void __launch_bounds__(256)
 dwconv_dw_kernel(const __nv_bfloat16* __restrict__ dc, const __nv_bfloat16* __restrict__ x,
                  const __nv_bfloat16* __restrict__ halo, float* __restrict__ dw, int B, int T, int d, int k,
                  int64_t dc_ld, int64_t x_ld) {
+  pdl_enter();
   constexpr bool BLOCK_REDUCE = KMAX <= 8;     // the widest window would not fit the static shared-memory limit
   __shared__ float part[BLOCK_REDUCE ? 8 : 1][BLOCK_REDUCE ? KMAX : 1][128 + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -355,7 +359,7 @@ template <int KMAX>
 static const char* conv_dw_launch(const ConvBwdArgs& a, cudaStream_t st) {
   const int strips = a.B * ((a.T + DW_TT - 1) / DW_TT);
   dim3 grid((strips + 7) / 8, (a.d + 127) / 128);
-  dwconv_dw_kernel<KMAX><<<grid, 256, 0, st>>>(a.dc, a.x, a.halo, a.dw, a.B, a.T, a.d, a.k, a.dc_ld, a.x_ld);
+  launch_pdl(dwconv_dw_kernel<KMAX>, grid, dim3(256), 0, st, a.dc, a.x, a.halo, a.dw, a.B, a.T, a.d, a.k, a.dc_ld, a.x_ld);
   return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_dw launch failed";
 }
 
@@ -367,7 +371,7 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if (a.quant.q != nullptr && a.d % 128 != 0) return "dwconv: a quantised output needs d % 128 == 0";
   if (a.k == 4 && a.T % 8 == 0) {
     dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
-    dwconv_fwd_sw_kernel<4, 8><<<sgrid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant);
+    launch_pdl(dwconv_fwd_sw_kernel<4, 8>, sgrid, dim3(256), 0, st, a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant);
     return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
   }
   if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld, a.quant);
@@ -383,7 +387,7 @@ const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   dim3 grid((unsigned)(((int64_t)a.B * rows_per_b + 7) / 8), (a.d + 255) / 256);
   if (a.k == 4 && a.T % 8 == 0) {
     dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
-    dwconv_dx_sw_kernel<4, 8><<<sgrid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.B, a.T, a.d, a.dc_ld);
+    launch_pdl(dwconv_dx_sw_kernel<4, 8>, sgrid, dim3(256), 0, st, a.dc, a.w, a.dx_tail_add, a.dx, a.B, a.T, a.d, a.dc_ld);
     if (a.dhalo != nullptr) {
       dim3 hgrid((unsigned)((a.B * (a.k - 1) + 7) / 8), (a.d + 255) / 256);
       dwconv_dhalo_kernel<<<hgrid, 256, 0, st>>>(a.dc, a.w, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
@@ -410,6 +414,7 @@ __device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&v)[8]) { sto
 // sum of g over the block's rows to gate_sum (for the mean forward-gate value).
 __global__ void __launch_bounds__(256)
 gate_update_fwd_kernel(const GateFwdArgs a) {
+  pdl_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int wpb = blockDim.x >> 5;
   float gsum = 0.0f;
@@ -469,7 +474,7 @@ const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update: d must be a multiple of 8";
   const int64_t blocks = (a.rows + 7) / 8;
   const int grid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
-  gate_update_fwd_kernel<<<grid, 256, 0, st>>>(a);
+  launch_pdl(gate_update_fwd_kernel, dim3(grid), dim3(256), 0, st, a);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gate_update_fwd launch failed";
 }
 
@@ -503,6 +508,7 @@ __device__ __forceinline__ GateElem gate_elem(float dF, float dS, float z, float
 
 __global__ void __launch_bounds__(256)
 gate_bwd_rowstats_kernel(const GateBwdArgs a) {
+  pdl_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t row = (int64_t)blockIdx.x * 8 + warp;
   if (row >= a.rows) return;
@@ -545,6 +551,7 @@ constexpr int GATE_STRIP = 16;   // rows per warp in the column kernel
 
 __global__ void __launch_bounds__(256)
 gate_bwd_cols_kernel(const GateBwdArgs a) {
+  pdl_enter();
   __shared__ float part[8][3][256 + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = blockIdx.y * 256 + lane * 8;
@@ -611,10 +618,10 @@ const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update_bwd: d must be a multiple of 8";
   if (!a.b2g_f32) return "gate_update_bwd: the gate bias must be fp32";
   if (a.row_dotz == nullptr || a.row_rstdg == nullptr) return "gate_update_bwd: row scratch missing";
-  gate_bwd_rowstats_kernel<<<(unsigned)((a.rows + 7) / 8), 256, 0, st>>>(a);
+  launch_pdl(gate_bwd_rowstats_kernel, dim3((unsigned)((a.rows + 7) / 8)), dim3(256), 0, st, a);
   if (cudaGetLastError() != cudaSuccess) return "gate_bwd_rowstats launch failed";
   dim3 grid((unsigned)((a.rows + 8 * GATE_STRIP - 1) / (8 * GATE_STRIP)), (a.d + 255) / 256);
-  gate_bwd_cols_kernel<<<grid, 256, 0, st>>>(a);
+  launch_pdl(gate_bwd_cols_kernel, grid, dim3(256), 0, st, a);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gate_bwd_cols launch failed";
 }
 
@@ -718,6 +725,7 @@ const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
 //   BLOCK (transposed): s_col[cb * n_rb + rb]
 __global__ void __launch_bounds__(256, 3)
 quant_tile_kernel(const QuantArgs a) {
+  pdl_enter();
   __shared__ float s_colmax[16][128];
   __shared__ float s_scale_col[128];
   __shared__ float s_tilemax;
@@ -862,6 +870,7 @@ quant_tile_kernel(const QuantArgs a) {
 // amax is a 4-step shuffle; no shared memory, every byte moved once with 16-byte loads.
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const QuantArgs a) {
+  pdl_enter();
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int groups_per_row = a.cols / 8;            // cols is a multiple of 128 here
   const int c = (int)(gid % groups_per_row) * 8;
@@ -896,12 +905,12 @@ const char* launch_quant_tile(const QuantArgs& a, cudaStream_t st) {
   if (a.cols % 8 != 0) return "quantise: cols must be a multiple of 8";
   if (a.q_col == nullptr && a.q_row != nullptr && a.row_mode == QUANT_ROWS && a.cols % 128 == 0) {
     const int64_t threads = a.rows * (a.cols / 8);
-    quant_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(a);
+    launch_pdl(quant_rows_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st, a);
     return cudaGetLastError() == cudaSuccess ? nullptr : "quant_rows launch failed";
   }
   if (a.q_col != nullptr && a.rows % 16 != 0) return "quantise: transposed output needs rows % 16 == 0";
   dim3 grid((a.cols + 127) / 128, (unsigned)((a.rows + 127) / 128));
-  quant_tile_kernel<<<grid, 256, 0, st>>>(a);
+  launch_pdl(quant_tile_kernel, grid, dim3(256), 0, st, a);
   return cudaGetLastError() == cudaSuccess ? nullptr : "quant_tile launch failed";
 }
 
@@ -960,6 +969,7 @@ const char* launch_quant_tensor(const __nv_bfloat16* x, const float* scale, uint
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int64_t rows, int cols, int64_t ld,
               int rows_per_block) {
+  pdl_enter();
   __shared__ float part[8][256 + 8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = blockIdx.x * 256 + lane * 8;
@@ -992,7 +1002,7 @@ const char* launch_colsum(const __nv_bfloat16* x, float* out, int64_t rows, int 
   if (cols % 8 != 0) return "colsum: cols must be a multiple of 8";
   const int rpb = 256;
   dim3 grid((cols + 255) / 256, (unsigned)((rows + rpb - 1) / rpb));
-  colsum_kernel<<<grid, 256, 0, st>>>(x, out, rows, cols, ld, rpb);
+  launch_pdl(colsum_kernel, grid, dim3(256), 0, st, x, out, rows, cols, ld, rpb);
   return cudaGetLastError() == cudaSuccess ? nullptr : "colsum launch failed";
 }
 
@@ -1002,6 +1012,7 @@ const char* launch_colsum(const __nv_bfloat16* x, float* out, int64_t rows, int 
 __global__ void __launch_bounds__(256)
 segment_add_kernel(const float* __restrict__ src, const int64_t* __restrict__ dst_addr, const int* __restrict__ seg_off,
                    int n_seg, int total) {
+  pdl_enter();
   const int i = blockIdx.x * 256 + threadIdx.x;
   if (i >= total) return;
   int s = 0;
@@ -1014,7 +1025,7 @@ const char* launch_segment_add(const float* src, const int64_t* dst_addr, const 
                                cudaStream_t st) {
   if (n_seg < 1 || n_seg > 64) return "segment_add: between 1 and 64 segments";
   if (total <= 0) return nullptr;
-  segment_add_kernel<<<(total + 255) / 256, 256, 0, st>>>(src, dst_addr, seg_off, n_seg, total);
+  launch_pdl(segment_add_kernel, dim3((total + 255) / 256), dim3(256), 0, st, src, dst_addr, seg_off, n_seg, total);
   return cudaGetLastError() == cudaSuccess ? nullptr : "segment_add launch failed";
 }
 
@@ -1044,6 +1055,7 @@ __global__ void __launch_bounds__(256)
 unscale_cols_bwd_kernel(const float* __restrict__ dW2w, const __nv_bfloat16* __restrict__ W2,
                         const float* __restrict__ colw, float* __restrict__ dW2, float* __restrict__ dcolw, int rows,
                         int cols) {
+  pdl_enter();
   const int c = blockIdx.x * 256 + threadIdx.x;
   if (c >= cols) return;
   const int r_begin = blockIdx.y * 64, r_end = min(r_begin + 64, rows);
@@ -1060,7 +1072,7 @@ unscale_cols_bwd_kernel(const float* __restrict__ dW2w, const __nv_bfloat16* __r
 const char* launch_unscale_cols_bwd(const float* dW2w, const __nv_bfloat16* W2, const float* colw, float* dW2,
                                     float* dcolw, int rows, int cols, cudaStream_t st) {
   dim3 grid((cols + 255) / 256, (rows + 63) / 64);
-  unscale_cols_bwd_kernel<<<grid, 256, 0, st>>>(dW2w, W2, colw, dW2, dcolw, rows, cols);
+  launch_pdl(unscale_cols_bwd_kernel, grid, dim3(256), 0, st, dW2w, W2, colw, dW2, dcolw, rows, cols);
   return cudaGetLastError() == cudaSuccess ? nullptr : "unscale_cols_bwd launch failed";
 }
 

@@ -28,6 +28,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "launch.h"
 
 namespace gd {
 
@@ -349,6 +350,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pipe_setup<BF16_STAGES, BF16_ACC>(bars, warp, lane, BF16_ACC * BF16_BN, &tmap_a, &tmap_b);
+  pdl_enter();
   const uint32_t tmem_base = bars->tmem_base;
 
   const int n_tiles_n = (g.N + BF16_BN - 1) / BF16_BN;
@@ -588,6 +590,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   __syncthreads();
   cluster_sync_all();     // the peer's barriers exist before anything of this CTA can signal them
   tc_fence_after_sync();
+  pdl_enter();
   const uint32_t tmem_base = bars->tmem_base;
 
   const int n_tiles_n = (g.N + PAIR_BN - 1) / PAIR_BN;
@@ -984,6 +987,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pipe_setup<MX_STAGES, MX_ACC>(bars, warp, lane, MX_TMEM_COLS, &tmap_a, &tmap_b);
+  pdl_enter();
   const uint32_t tmem_base = bars->tmem_base;
 
   const int n_tiles_n = (g.N + MX_BN - 1) / MX_BN;
@@ -1313,9 +1317,9 @@ static const char* launch_gemm_bf16_pair(const GemmOperands& op, const GemmShape
   const int grid = 2 * (work < max_pairs ? work : max_pairs);
   if (aux) {
     if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
-    gemm_bf16_pair_kernel<true><<<grid, NUM_THREADS, smem_aux, stream>>>(ta, tb, tx, gs, es, status);
+    launch_pdl(gemm_bf16_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tx, gs, es, status);
   } else {
-    gemm_bf16_pair_kernel<false><<<grid, NUM_THREADS, smem_plain, stream>>>(ta, tb, ta, gs, es, status);
+    launch_pdl(gemm_bf16_pair_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem_plain, stream, ta, tb, ta, gs, es, status);
   }
   *launched = true;
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_bf16_pair_kernel launch failed";
@@ -1367,9 +1371,9 @@ const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const G
   if (aux) {
     CUtensorMap tx;
     if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
-    gemm_bf16_kernel<true><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, tx, gs, es, status);
+    launch_pdl(gemm_bf16_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem, stream, ta, tb, tx, gs, es, status);
   } else {
-    gemm_bf16_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, ta, gs, es, status);
+    launch_pdl(gemm_bf16_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem, stream, ta, tb, ta, gs, es, status);
   }
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_bf16_kernel launch failed";
 }
@@ -1431,9 +1435,9 @@ const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const
   if (aux) {
     CUtensorMap tx;
     if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
-    gemm_fp8_mx_kernel<true><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, tx, gs, es, status);
+    launch_pdl(gemm_fp8_mx_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem, stream, ta, tb, tx, gs, es, status);
   } else {
-    gemm_fp8_mx_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, ta, gs, es, status);
+    launch_pdl(gemm_fp8_mx_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem, stream, ta, tb, ta, gs, es, status);
   }
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_mx_kernel launch failed";
 }

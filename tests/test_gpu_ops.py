@@ -272,3 +272,76 @@ def test_optimizer_kernels():
                 p_ref = p_ref.to(dtype).float()
         assert torch.allclose(p.float(), p_ref, atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
         assert torch.allclose(m, m_r, atol=1e-6) and torch.allclose(v, v_r, atol=1e-6)
+
+
+def _ptr_table(t):
+    return torch.tensor([t.data_ptr()], dtype=torch.int64, device=DEV)
+
+
+def _status(t):
+    from gdnet_b200 import _ext
+
+    _ext.check_status(t)
+
+
+def test_collective_kernels_single_rank():
+    """The peer-memory kernels with a world of one (every "peer" table holds this GPU's own buffer, so no kernel
+    waits for another): fused update against the plain optimizer kernel, in all phase combinations; gradient
+    sinks of the epilogue reduce-scatter; the MAX all-reduce."""
+    cu = _cu()
+    n = 128 * 64
+    torch.manual_seed(4)
+    for phases in ((0,), (1, 2), (3, 4), (5,)):
+        gt, gi = torch.randn(n, device=DEV), torch.randn(n, device=DEV)
+        gt0, gi0 = gt.clone(), gi.clone()
+        p = torch.randn(n, device=DEV).bfloat16()
+        p_ref = p.clone()
+        m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        m_r, v_r = m.clone(), v.clone()
+        flags = torch.zeros(1024, dtype=torch.int32, device=DEV)
+        scal = torch.tensor([0.3, 1.0], device=DEV)
+        sums = torch.zeros(8, device=DEV)
+        for ph in phases:
+            cu.K.allreduce_adamw(_ptr_table(gt), _ptr_table(gi), _ptr_table(p), _ptr_table(flags), m, v, scal, n, 0, 1,
+                                 8, ph, True, 0.1, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, sums)
+        cu.K.projected_adamw(p_ref, gt0, gi0, m_r, v_r, scal, 0.1, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1)
+        torch.cuda.synchronize()
+        assert torch.equal(p, p_ref), f"phases {phases}: parameters differ from the plain update"
+        assert torch.allclose(m, m_r, atol=1e-7) and torch.allclose(v, v_r, atol=1e-7)
+        if phases != (2,):
+            want = torch.stack([(gt0 * gt0).sum(), (gt0 * gi0).sum(), (gi0 * gi0).sum()])
+            assert torch.allclose(sums[:3], want, rtol=1e-3), f"phases {phases}: shard dot products"
+        if phases[-1] >= 4:
+            assert float(gt.abs().max()) == 0.0 and float(gi.abs().max()) == 0.0, "consumed shard not cleared"
+
+    # epilogue reduce-scatter with one rank: a weight-gradient GEMM into a registered flat buffer
+    flat = torch.zeros(4 * 256 * 128, device=DEV)
+    cu.K.clear_grad_sinks()
+    cu.K.register_grad_sink(flat, _ptr_table(flat), flat.numel())
+    try:
+        M, N, Kd = 512, 256, 128
+        dy, x = torch.randn(M, N, device=DEV, dtype=BF), torch.randn(M, Kd, device=DEV, dtype=BF)
+        view = flat[256 * 128 : 2 * 256 * 128].view(N, Kd)
+        cu.gemm_bf16(dy, x, a_mn=True, b_mn=True, out=view, accumulate=True)
+        cu.gemm_bf16(dy, x, a_mn=True, b_mn=True, out=view, accumulate=True)
+        small = torch.randn(1000, device=DEV)
+        cu.K.peer_add(flat[3 * 256 * 128 : 3 * 256 * 128 + 1000], small)
+        cu.K.peer_add(flat[3 * 256 * 128 : 3 * 256 * 128 + 1000], small.bfloat16())
+        torch.cuda.synchronize()
+        _status(dy)
+        _check(view, 2.0 * (dy.float().t() @ x.float()), 1e-2, "wgrad through a gradient sink")
+        assert float(flat[: 256 * 128].abs().max()) == 0.0, "the sink wrote outside the view"
+        assert torch.allclose(flat[3 * 256 * 128 : 3 * 256 * 128 + 1000], small + small.bfloat16().float(), atol=1e-6)
+    finally:
+        cu.K.clear_grad_sinks()
+
+    # MAX all-reduce, world of one: the vector comes back unchanged, twice (both slot sets)
+    area = torch.zeros(2 * 512, device=DEV)
+    fl = torch.zeros(64, dtype=torch.int32, device=DEV)
+    vec = torch.rand(300, device=DEV)
+    keep = vec.clone()
+    for seq in (1, 2, 3):
+        cu.K.max_allreduce(vec, _ptr_table(area), _ptr_table(fl), 512, 0, 1, seq)
+    torch.cuda.synchronize()
+    _status(vec)
+    assert torch.equal(vec, keep)
