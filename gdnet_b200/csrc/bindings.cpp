@@ -143,7 +143,8 @@ void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT
   e.q8_silu = 0;
   if (e.out_f32 && accumulate) {
     if (const GradSink* s = find_sink(out.data_ptr())) {
-      TORCH_CHECK(out.is_contiguous() && N % 32 == 0, "a gradient inside a spread flat buffer must be contiguous, N % 32 == 0");
+      TORCH_CHECK(out.stride(1) == 1 && out.stride(0) % 32 == 0 && N % 32 == 0,
+                  "a gradient inside a spread flat buffer needs unit column stride and 32-element granularity");
       e.peer_out = reinterpret_cast<float* const*>(s->table.data_ptr<int64_t>());
       e.flat_off = (int64_t)((reinterpret_cast<uintptr_t>(out.data_ptr()) - s->base) / 4);
       e.shard_elems = s->shard_elems;

@@ -523,6 +523,17 @@ def _wgrad_bf16(dy, x, w):
     return None if is_main else tgt.to(w.dtype)
 
 
+def _wgrad_bf16_cat(dy, xs, w):
+    """``dW (N, sum K_i) += dy^T [x_0 | x_1 | ...]`` without building the concatenation: one GEMM per column
+    range of the gradient."""
+    tgt, is_main = _wgrad_target(w)
+    o = 0
+    for x in xs:
+        gemm_bf16(dy, x, a_mn=True, b_mn=True, out=tgt[:, o : o + x.shape[1]], accumulate=True)
+        o += x.shape[1]
+    return None if is_main else tgt.to(w.dtype)
+
+
 def _bias_grad(dy, b):
     if b is None:
         return None
@@ -563,35 +574,32 @@ def linear_bf16(x, w, b=None):
 
 
 class _LinearFp8BlockFn(torch.autograd.Function):
-    """Block-scaled e4m3 linear (1x128 activations and gradients, 128x128 weights).
+    """Block-scaled e4m3 linear (1x128 activations and gradients, 128x128 weights, power-of-two scales).
 
-    fprop: x8 (rows) x W8.  dgrad: dy8 (rows) x (W^T)8.  wgrad: (dy^T)8 (per column, 128 tokens)
-    x (x^T)8 (128x128), accumulated in fp32. The transposed e4m3 copy of x is made in forward
-    (one read of x yields both copies) and is what backward keeps instead of x.
+    fprop: x8 (rows) x W8.  dgrad: dy8 (rows) x (W^T)8.  The weight gradient dy^T x runs in bf16 with both
+    operands read in place (MN-major), accumulated in fp32: it is as fast as the e4m3 form once the transposed
+    quantised copies that form needs are counted, and it is the more precise of the two.
     """
 
     @staticmethod
     def forward(ctx, x2, w, b):
         qw = quantize_weight(w)
-        if ctx.needs_input_grad[1]:
-            x8, px, xt8, pxt = quantize_both_mx(x2, Q_BLOCK)
-        else:
-            x8, _, px = quantize_rows_mx(x2)
-            xt8 = pxt = x2.new_empty(0)
-        ctx.save_for_backward(xt8, pxt, w, b if b is not None else x2.new_empty(0))
+        x8, _, px = quantize_rows_mx(x2)
+        ctx.save_for_backward(x2 if ctx.needs_input_grad[1] else x2.new_empty(0), w,
+                              b if b is not None else x2.new_empty(0))
         ctx.has_bias = b is not None
         return gemm_fp8_mx(x8, px, qw.q, qw.p, bias=b)
 
     @staticmethod
     def backward(ctx, dy):
-        xt8, pxt, w, b = ctx.saved_tensors
+        x2, w, b = ctx.saved_tensors
         dy = dy.contiguous()
-        qw = quantize_weight(w)
-        dy8, pdy, dyt8, pdyt = quantize_both_mx(dy, Q_COLS)
-        dx = gemm_fp8_mx(dy8, pdy, qw.qt, qw.pt) if ctx.needs_input_grad[0] else None
-        tgt, is_main = _wgrad_target(w)
-        gemm_fp8_mx(dyt8, pdyt, xt8, pxt, out=tgt, accumulate=True)
-        dw = None if is_main else tgt.to(w.dtype)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            qw = quantize_weight(w)
+            dy8, _, pdy = quantize_rows_mx(dy)
+            dx = gemm_fp8_mx(dy8, pdy, qw.qt, qw.pt)
+        dw = _wgrad_bf16(dy, x2, w) if ctx.needs_input_grad[1] else None
         db = _bias_grad(dy, b if ctx.has_bias else None)
         return dx, dw, db
 
@@ -738,12 +746,18 @@ class _LayerStepFn(torch.autograd.Function):
         h1_pre = torch.empty(M, d, dtype=BF16, device=dev)
         if fp8:
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
-            # silu(h1) leaves the first GEMM already quantised for the second; h1 itself is kept for backward only
+            # silu(h1) leaves the first GEMM already quantised for the second; h1 and silu(h1) in bf16 are
+            # written only when a backward will need them
             a8 = torch.empty(M, d, dtype=FP8, device=dev)
             pa = packed_buffer(M, d, dev)
-            gemm_fp8_mx(u8, pu, q1.q, q1.p, out=h1_pre, bias=f32(rb1), q8=a8, q8_p=pa, q8_silu=True, store_out=train)
+            if train:
+                a1 = torch.empty(M, d, dtype=BF16, device=dev)
+                gemm_fp8_mx(u8, pu, q1.q, q1.p, out=a1, bias=f32(rb1), pre_out=h1_pre, act=ACT_SILU, q8=a8, q8_p=pa)
+            else:
+                a1 = None
+                gemm_fp8_mx(u8, pu, q1.q, q1.p, out=h1_pre, bias=f32(rb1), q8=a8, q8_p=pa, q8_silu=True,
+                            store_out=False)
             z = gemm_fp8_mx(a8, pa, q2.q, q2.p, bias=f32(rb2))
-            a1 = None
         else:
             gemm_bf16(s2, rW1[:, :d], out=h1_pre)
             a1 = torch.empty(M, d, dtype=BF16, device=dev)
@@ -832,33 +846,21 @@ class _LayerStepFn(torch.autograd.Function):
 
         # ---- recovery MLP ----
         if fp8:
+            # data gradients in e4m3 (row-quantised dz, dh1); weight gradients in bf16 with both operands read
+            # in place, which needs no transposed quantised copies
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
-            dz8, pdz, dzt8, pdzt = quantize_both_mx(dz, Q_COLS)
-            a1t8, _, pa1t = quantize_transposed_mx(h1_pre, Q_BLOCK, pre_silu=True)
-            tgt, main_r2 = _wgrad_target(rW2)
-            gemm_fp8_mx(dzt8, pdzt, a1t8, pa1t, out=tgt, accumulate=True)
-            g_rW2 = None if main_r2 else tgt.to(rW2.dtype)
+            dz8, _, pdz = quantize_rows_mx(dz)
+            g_rW2 = _wgrad_bf16(dz, a1, rW2)
             dh1 = gemm_fp8_mx(dz8, pdz, q2.qt, q2.pt, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
             K.colsum(dh1, db1r)
-            dh8, pdh, dht8, pdht = quantize_both_mx(dh1, Q_COLS)
-            kb, mb = d // 128, M // 128
-            ut8 = torch.empty(2 * d, M, dtype=FP8, device=dev)
-            sut = torch.empty(2 * kb, mb, dtype=F32, device=dev)
-            put = packed_buffer(2 * d, M, dev)
-            quantize_transposed_mx(s2, Q_BLOCK, qt=ut8[:d], st=sut[:kb], pt=put[:kb])
-            quantize_transposed_mx(c, Q_BLOCK, qt=ut8[d:], st=sut[kb:], pt=put[kb:])
-            tgt, main_r1 = _wgrad_target(rW1)
-            gemm_fp8_mx(dht8, pdht, ut8, put, out=tgt, accumulate=True)
-            g_rW1 = None if main_r1 else tgt.to(rW1.dtype)
+            dh8, _, pdh = quantize_rows_mx(dh1)
+            g_rW1 = _wgrad_bf16_cat(dh1, (s2, c), rW1)
             gemm_fp8_mx(dh8, pdh, q1.qt, q1.pt, out=dsc, aux=dsc, aux_mode=AUX_ADD)
         else:
             g_rW2 = _wgrad_bf16(dz, a1, rW2)
             dh1 = gemm_bf16(dz, rW2, b_mn=True, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
             K.colsum(dh1, db1r)
-            tgt, main_r1 = _wgrad_target(rW1)
-            gemm_bf16(dh1, s2, a_mn=True, b_mn=True, out=tgt[:, :d], accumulate=True)
-            gemm_bf16(dh1, c, a_mn=True, b_mn=True, out=tgt[:, d:], accumulate=True)
-            g_rW1 = None if main_r1 else tgt.to(rW1.dtype)
+            g_rW1 = _wgrad_bf16_cat(dh1, (s2, c), rW1)
             gemm_bf16(dh1, rW1, b_mn=True, out=dsc, aux=dsc, aux_mode=AUX_ADD)
 
         # ---- conv ----
