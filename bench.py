@@ -36,9 +36,10 @@ CONFIGS = {
     "tiny": dict(vocab_size=4096, d_embed=256, d=256, n_layers=2, n_cycles=2, kernel_size=4, seq_len=512,
                  micro_batch=2, n_write=2),
     # ~1.3B, gradients and optimizer state sharded over the ranks: the weight-gradient GEMM epilogues add into the
-    # owner's shard over NVLink, the update kernel does AdamW on the shard and writes the new parameters to all ranks
+    # owner's shard over NVLink, the update kernel does AdamW on the shard and writes the new parameters to all ranks;
+    # every FP8 weight is quantised by one rank, whose kernel stores the e4m3 copies into all ranks' caches
     "1.3b": dict(vocab_size=32000, d_embed=2048, d=2048, n_layers=24, n_cycles=2, kernel_size=4, seq_len=8192,
-                 micro_batch=2, n_write=4, comm="scatter"),
+                 micro_batch=2, n_write=4, comm="scatter", share_fp8=True),
     # ~1.3B, one 65536-token sequence split into contiguous shards over the ranks (sequence parallel): conv halos
     # and their gradients cross ranks inside the push/flag/wait kernel
     "1.3b-sp": dict(vocab_size=32000, d_embed=2048, d=2048, n_layers=24, n_cycles=2, kernel_size=4, seq_len=65536,
@@ -138,8 +139,9 @@ def build_ours(cfg, device, world):
         import torch.distributed as dist
 
         sp_group = dist.group.WORLD
+    share = os.environ.get("GDNET_SHARE_FP8", "1" if cfg.get("share_fp8") else "0") == "1"
     engine = TrainEngine(model, lr=1e-3, precision="fp8", sp_group=sp_group,
-                         comm=os.environ.get("GDNET_COMM", cfg.get("comm", "fused")))
+                         comm=os.environ.get("GDNET_COMM", cfg.get("comm", "fused")), share_fp8_weights=share)
 
     def step(tokens, targets, write_chunks):
         return engine.projected_step(tokens, targets, write_chunks=write_chunks)

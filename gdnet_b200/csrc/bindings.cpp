@@ -361,7 +361,7 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
 }
 
 void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t row_mode, OptT q_col, OptT s_col,
-                int64_t col_mode, bool pow2, OptT p_row, OptT p_col) {
+                int64_t col_mode, bool pow2, OptT p_row, OptT p_col, OptT peer_delta) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 2, "quantise: x must be 2-D");
   gd::QuantArgs a{};
@@ -416,6 +416,12 @@ void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t 
       TORCH_CHECK(q_col.has_value() && p_col->is_contiguous() && p_col->numel() == rb * cb * 512, "p_col must hold cols/128 * rows/128 * 512 bytes");
       a.p_col = fp8_mut(*p_col, "p_col");
     }
+  }
+  if (peer_delta.has_value() && peer_delta->numel() > 0) {
+    TORCH_CHECK(peer_delta->is_cuda() && peer_delta->scalar_type() == at::kLong && peer_delta->is_contiguous(),
+                "peer_delta must be an int64 CUDA tensor");
+    a.peer_delta = peer_delta->data_ptr<int64_t>();
+    a.n_peer = (int)peer_delta->numel();
   }
   GD_LAUNCH(gd::launch_quant_tile(a, stream_of(x)));
 }
@@ -627,7 +633,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r) -> ()", &gate_update_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!)? rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw) -> ()", &rmsnorm_bwd);
-  m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode, bool pow2=False, Tensor(e!)? p_row=None, Tensor(f!)? p_col=None) -> ()", &quant_tile);
+  m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode, bool pow2=False, Tensor(e!)? p_row=None, Tensor(f!)? p_col=None, Tensor? peer_delta=None) -> ()", &quant_tile);
   m.def("quant_tensor(Tensor x, Tensor scale, Tensor(a!) q_row, Tensor(b!)? q_col, Tensor(c!)? amax) -> ()", &quant_tensor);
   m.def("colsum(Tensor x, Tensor(a!) out) -> ()", &colsum);
   m.def("segment_add(Tensor src, Tensor dst_addr, Tensor seg_off) -> ()", &segment_add);

@@ -723,6 +723,13 @@ const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
 //   COLS : s_col[rb * s_col_ld + c]            (A operand of the weight-gradient GEMM)
 //   BLOCK (row-major) : s_row[rb * n_cb + cb]  (GEMM B operand: sb[nb*KB + kb])
 //   BLOCK (transposed): s_col[cb * n_rb + rb]
+// store to the local output and to the same place in every peer copy (see QuantArgs::peer_delta)
+template <typename T>
+__device__ __forceinline__ void store_all(const QuantArgs& a, T* p, const T& v) {
+  *p = v;
+  for (int r = 0; r < a.n_peer; ++r) *reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(p) + a.peer_delta[r]) = v;
+}
+
 __global__ void __launch_bounds__(256, 3)
 quant_tile_kernel(const QuantArgs a) {
   pdl_enter();
@@ -781,9 +788,9 @@ quant_tile_kernel(const QuantArgs a) {
         uint8_t q[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[p][i] * inv);
-        *reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c) = *reinterpret_cast<uint2*>(q);
+        store_all(a, reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c), *reinterpret_cast<uint2*>(q));
         if ((tid & 15) == 0) {
-          a.s_row[(int64_t)blockIdx.x * a.s_row_ld + r] = sc;
+          store_all(a, a.s_row + (int64_t)blockIdx.x * a.s_row_ld + r, sc);
           if (a.p_row != nullptr)
             store_packed_scale(a.p_row, (int64_t)blockIdx.y * a.p_row_stride + blockIdx.x, (int)(r - r0), ue8m0_word(sc));
         }
@@ -818,12 +825,12 @@ quant_tile_kernel(const QuantArgs a) {
         uint8_t q[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[p][i] * inv);
-        *reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c) = *reinterpret_cast<uint2*>(q);
+        store_all(a, reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c), *reinterpret_cast<uint2*>(q));
       }
     }
-    if (tid == 0) a.s_row[(int64_t)blockIdx.y * n_cb + blockIdx.x] = tile_scale;
+    if (tid == 0) store_all(a, a.s_row + (int64_t)blockIdx.y * n_cb + blockIdx.x, tile_scale);
     if (a.p_row != nullptr && tid < 128)
-      reinterpret_cast<uint32_t*>(a.p_row + ((int64_t)blockIdx.y * a.p_row_stride + blockIdx.x) * 512)[tid] = ue8m0_word(tile_scale);
+      store_all(a, reinterpret_cast<uint32_t*>(a.p_row + ((int64_t)blockIdx.y * a.p_row_stride + blockIdx.x) * 512) + tid, ue8m0_word(tile_scale));
   }
 
   if (a.q_col != nullptr) {
@@ -849,19 +856,19 @@ quant_tile_kernel(const QuantArgs a) {
       const uint4 u = *reinterpret_cast<const uint4*>(&s_q8t[oc][slot * 8]);
       const int64_t rr = r0 + piece * 16;
       if (c0 + oc < a.cols && rr < a.rows)
-        *reinterpret_cast<uint4*>(a.q_col + (int64_t)(c0 + oc) * a.q_col_ld + rr) = u;
+        store_all(a, reinterpret_cast<uint4*>(a.q_col + (int64_t)(c0 + oc) * a.q_col_ld + rr), u);
     }
     if (a.col_mode == QUANT_COLS) {
       if (tid < 128 && c0 + tid < a.cols) {
         const float sc_c = block_scale(s_scale_col[tid], a.pow2);
-        a.s_col[(int64_t)blockIdx.y * a.s_col_ld + c0 + tid] = sc_c;
+        store_all(a, a.s_col + (int64_t)blockIdx.y * a.s_col_ld + c0 + tid, sc_c);
         if (a.p_col != nullptr)
           store_packed_scale(a.p_col, (int64_t)blockIdx.x * n_rb + blockIdx.y, tid, ue8m0_word(sc_c));
       }
     } else {
-      if (tid == 0) a.s_col[(int64_t)blockIdx.x * n_rb + blockIdx.y] = tile_scale;
+      if (tid == 0) store_all(a, a.s_col + (int64_t)blockIdx.x * n_rb + blockIdx.y, tile_scale);
       if (a.p_col != nullptr && tid < 128)
-        reinterpret_cast<uint32_t*>(a.p_col + ((int64_t)blockIdx.x * n_rb + blockIdx.y) * 512)[tid] = ue8m0_word(tile_scale);
+        store_all(a, reinterpret_cast<uint32_t*>(a.p_col + ((int64_t)blockIdx.x * n_rb + blockIdx.y) * 512) + tid, ue8m0_word(tile_scale));
     }
   }
 }
@@ -903,6 +910,8 @@ quant_rows_kernel(const QuantArgs a) {
 
 const char* launch_quant_tile(const QuantArgs& a, cudaStream_t st) {
   if (a.cols % 8 != 0) return "quantise: cols must be a multiple of 8";
+  if (a.n_peer > 0 && (a.q_col == nullptr || a.row_mode != QUANT_BLOCK || a.col_mode != QUANT_BLOCK))
+    return "quantise: peer copies are for weights (both outputs, 128x128 blocks)";
   if (a.q_col == nullptr && a.q_row != nullptr && a.row_mode == QUANT_ROWS && a.cols % 128 == 0) {
     const int64_t threads = a.rows * (a.cols / 8);
     launch_pdl(quant_rows_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st, a);

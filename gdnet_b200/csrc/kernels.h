@@ -119,6 +119,11 @@ struct QuantArgs {
   uint8_t* p_row;          // packed UE8M0 chunks for q_row, (rows/128, cols/128, 512) bytes, or null
   int64_t p_row_stride;    // chunks between consecutive row blocks of p_row (cols/128 when dense)
   uint8_t* p_col;          // packed UE8M0 chunks for q_col, (cols/128, rows/128, 512) bytes, or null
+  // Every store of an output is repeated at the same offset in n_peer other copies of the output buffers
+  // (other ranks' symmetric weight caches): address + peer_delta[r] bytes. Used by the owner of a weight to
+  // hand its e4m3 copies to all ranks from inside the quantisation kernel.
+  const int64_t* peer_delta;
+  int n_peer;
 };
 
 const char* launch_quant_tile(const QuantArgs& a, cudaStream_t st);

@@ -112,8 +112,90 @@ class QuantizedWeight:
 _wq_cache: dict[int, QuantizedWeight] = {}
 
 
+class SharedWeights:
+    """FP8 copies of the weights in symmetric memory, each weight quantised by ONE rank per parameter update.
+
+    The owner's quantisation kernel stores every output byte into the same place of every rank's arena (peer
+    stores over NVLink from inside ``quant_tile_kernel``), so the all-gather of the e4m3 weights is part of the
+    kernel that produces them and moves half the bytes of a bf16 gather; the GEMMs then read their local copy
+    through TMA. One bounded flag exchange per update tells every rank that all copies have landed.
+    """
+
+    ALIGN = 1024
+
+    def __init__(self, weights, group, device):
+        import torch.distributed as dist
+
+        from ..parallel.symm import SymmBuffer
+
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        plan, off = [], 0
+
+        def take(nbytes):
+            nonlocal off
+            o = off
+            off += -(-nbytes // self.ALIGN) * self.ALIGN
+            return o
+
+        for w in weights:
+            N, Kd = w.shape
+            nb, kb = N // 128, Kd // 128
+            plan.append((w, take(N * Kd), take(nb * kb * 4), take(N * Kd), take(nb * kb * 4), take(nb * kb * 512),
+                         take(nb * kb * 512)))
+        self.arena = SymmBuffer(max(off, self.ALIGN), group, device)
+        base = self.arena.ptrs[self.rank]
+        self.peer_delta = torch.tensor([p - base for r, p in enumerate(self.arena.ptrs) if r != self.rank],
+                                       dtype=torch.int64, device=device)
+        self.entries: dict = {}
+        self.owned = []
+        loc = self.arena.local
+        for i, (w, oq, os_, oqt, ost, op, opt) in enumerate(plan):
+            N, Kd = w.shape
+            nb, kb = N // 128, Kd // 128
+            qw = QuantizedWeight()
+            qw.q = loc[oq : oq + N * Kd].view(FP8).view(N, Kd)
+            qw.s = loc[os_ : os_ + nb * kb * 4].view(F32).view(nb, kb)
+            qw.qt = loc[oqt : oqt + N * Kd].view(FP8).view(Kd, N)
+            qw.st = loc[ost : ost + nb * kb * 4].view(F32).view(kb, nb)
+            qw.p = loc[op : op + nb * kb * 512].view(nb, kb, 512)
+            qw.pt = loc[opt : opt + nb * kb * 512].view(kb, nb, 512)
+            qw.version, qw.ptr, qw.source = None, w.data_ptr(), w
+            self.entries[(w.data_ptr(), w.numel(), w.dtype)] = qw
+            if i % self.world == self.rank:
+                self.owned.append((w, qw))
+        self.epoch = -1
+        self._token = torch.zeros(1, dtype=F32, device=device)
+        self.arena.barrier()
+
+    def refresh(self) -> None:
+        """Collective: every rank quantises the weights it owns into all arenas, then waits for the others."""
+        from ..parallel.symm import max_allreduce_
+
+        for w, qw in self.owned:
+            K.quant_tile(w.detach(), False, qw.q, qw.s, Q_BLOCK, qw.qt, qw.st, Q_BLOCK, True, qw.p, qw.pt, self.peer_delta)
+        max_allreduce_(self._token, self.group)      # flags + bounded waits: all peers' stores are complete and visible
+        self.epoch = _param_epoch
+
+
+_shared_weights: SharedWeights | None = None
+
+
+def share_fp8_weights(weights, group, device) -> SharedWeights:
+    """Install the shared FP8 weight cache for ``weights`` (2-D bf16, both dims multiples of 128)."""
+    global _shared_weights
+    _shared_weights = SharedWeights(list(weights), group, device)
+    return _shared_weights
+
+
 def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
     key = (w.data_ptr(), w.numel(), w.dtype)
+    if _shared_weights is not None:
+        ent = _shared_weights.entries.get(key)
+        if ent is not None:
+            if _shared_weights.epoch != _param_epoch:
+                _shared_weights.refresh()
+            return ent
     hit = _wq_cache.get(key)
     stamp = (w._version, _param_epoch)
     if hit is not None and hit.version == stamp and hit.ptr == w.data_ptr():
@@ -137,6 +219,8 @@ def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
 
 
 def clear_caches() -> None:
+    global _shared_weights
+    _shared_weights = None
     _f32_cache.clear()
     _wq_cache.clear()
     _taps_cache.clear()

@@ -94,7 +94,8 @@ class TrainEngine(nn.Module):
 
     def __init__(self, model: nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 1e-2, precision: str = "fp8", process_group=None, sp_group=None,
-                 comm: str = "fused", broadcast: bool = True, projection: str = "local"):
+                 comm: str = "fused", broadcast: bool = True, projection: str = "local",
+                 share_fp8_weights: bool = False):
         super().__init__()
         self.module = model
         self.precision = precision
@@ -154,6 +155,20 @@ class TrainEngine(nn.Module):
             from ..ops import cuda as cu
 
             cu.clear_caches()     # cached copies made from the pre-flattening parameter storages
+            if share_fp8_weights and symmetric and precision == "fp8":
+                # each FP8 weight is quantised by one rank per update and stored into every rank's cache by
+                # that rank's quantisation kernel (the all-gather of the e4m3 weights, inside the producer)
+                from ..ops.fp8_linear import FP8Linear
+
+                ws = [m.weight for m in model.modules() if isinstance(m, FP8Linear) and m.recipe == "block"
+                      and m.weight.dtype == torch.bfloat16 and m.weight.shape[0] % 128 == 0 and m.weight.shape[1] % 128 == 0]
+                seen, uniq = set(), []
+                for w in ws:
+                    if w.data_ptr() not in seen:
+                        seen.add(w.data_ptr())
+                        uniq.append(w)
+                if uniq:
+                    cu.share_fp8_weights(uniq, self.pg, dev)
 
     # -- nn.Module plumbing -----------------------------------------------------------------
     def forward(self, *a, **kw):

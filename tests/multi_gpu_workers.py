@@ -82,6 +82,52 @@ def engine_scatter_vs_nccl(rank, world, dev):
         assert float(gc.g_task[lo:hi].abs().max()) == 0.0, "the consumed shard was not cleared"
 
 
+def engine_shared_fp8_weights(rank, world, dev):
+    """FP8 weights quantised by their owner and stored into every rank's cache by the quantisation kernel:
+    same losses and bit-identical parameters as every rank quantising everything itself."""
+    from gdnet_b200.ops import cuda as cu
+
+    base = _model(dev)
+    g = torch.Generator(device="cpu").manual_seed(300 + rank)
+    data = [(torch.randint(0, 1024, (2, 256), generator=g).to(dev), torch.randint(0, 1024, (2, 256), generator=g).to(dev))
+            for _ in range(3)]
+    results = []
+    for shared in (False, True):
+        eng = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="fused", share_fp8_weights=shared)
+        assert (cu._shared_weights is not None) == shared
+        losses = []
+        for step, (tok, tgt) in enumerate(data):
+            torch.manual_seed(7 + step)
+            losses.append(float(eng.projected_step(tok, tgt)))
+        torch.cuda.synchronize()
+        _ext.check_status(tok)
+        results.append((losses, [gr.flat.clone() for gr in eng.groups]))
+        if shared:
+            assert len(cu._shared_weights.owned) < len(cu._shared_weights.entries), "this rank quantised every weight"
+    (l0, p0), (l1, p1) = results
+    # the weight-gradient GEMMs add their split-K shares with atomics, so two runs agree to rounding noise only
+    assert l0[0] == l1[0] and all(abs(a - b) < 5e-3 * abs(a) for a, b in zip(l0, l1)), (l0, l1)
+    for a, b in zip(p0, p1):
+        assert (a.float() - b.float()).abs().max().item() < 3e-2, "parameters differ between private and shared caches"
+    # the arena must hold exactly what a private quantisation of the current weights gives, on every rank
+    sw = cu._shared_weights
+    sw.refresh()
+    torch.cuda.synchronize()
+    for (_, _, _), qw in sw.entries.items():
+        w = qw.source
+        N, Kd = w.shape
+        q, qt = torch.empty_like(qw.q), torch.empty_like(qw.qt)
+        s_, st = torch.empty_like(qw.s), torch.empty_like(qw.st)
+        pp, pt = torch.empty_like(qw.p), torch.empty_like(qw.pt)
+        cu.K.quant_tile(w.detach(), False, q, s_, cu.Q_BLOCK, qt, st, cu.Q_BLOCK, True, pp, pt)
+        for got, want, what in ((qw.q, q, "q"), (qw.qt, qt, "qt"), (qw.p, pp, "p"), (qw.pt, pt, "pt")):
+            assert torch.equal(got.view(torch.uint8), want.view(torch.uint8)), f"shared copy {what} of a {N}x{Kd} weight is stale"
+        assert torch.equal(qw.s, s_) and torch.equal(qw.st, st)
+    _ext.check_status(tok)
+    dist.barrier()
+    cu.clear_caches()
+
+
 def peer_max_allreduce(rank, world, dev):
     """One-kernel MAX all-reduce over peer memory against NCCL, repeated (the slot sets alternate), and through
     update_fp8_scales on the per-tensor recipe."""

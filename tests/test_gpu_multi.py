@@ -34,6 +34,10 @@ def test_epilogue_reduce_scatter_matches_nccl():
     _run("engine_scatter_vs_nccl")
 
 
+def test_shared_fp8_weights_match_private_caches():
+    _run("engine_shared_fp8_weights")
+
+
 def test_peer_max_allreduce_matches_nccl():
     _run("peer_max_allreduce")
 
