@@ -326,7 +326,7 @@ void gate_update_fwd(const Tensor& g_pre, const Tensor& z, const Tensor& c, cons
 void gate_update_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, const Tensor& z, const Tensor& c,
                      const Tensor& s, const Tensor& w_r, const Tensor& b2g, const Tensor& rstd_z, const Tensor& ssq_g,
                      double eps_g, OptT dgate_mean, Tensor dq, Tensor dz, Tensor dsc, Tensor rowcoef, Tensor db2g,
-                     Tensor dw_r, Tensor db2r) {
+                     Tensor dw_r, Tensor db2r, OptT q, OptT qs, OptT qp) {
   c10::cuda::CUDAGuard guard(c.device());
   const int64_t rows = g_pre.size(0);
   const int d = (int)g_pre.size(1);
@@ -341,7 +341,7 @@ void gate_update_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, co
                     f32_ptr(ssq_g, "ssq_g"), (int)ssq_g.size(1), (float)eps_g, opt_f32(dgate_mean, "dgate_mean"),
                     bf16_mut(dq, "dq"), bf16_mut(dz, "dz"), bf16_mut(dsc, "dsc"), f32_mut(rowcoef, "rowcoef"),
                     row_scratch.data_ptr<float>(), row_scratch.data_ptr<float>() + rows, f32_mut(db2g, "db2g"), f32_mut(dw_r, "dw_r"), f32_mut(db2r, "db2r"), rows, d,
-                    dF.stride(0), dS.stride(0), c.stride(0), s.stride(0)};
+                    dF.stride(0), dS.stride(0), c.stride(0), s.stride(0), row_quant_out(q, qs, qp, rows, d)};
   GD_LAUNCH(gd::launch_gate_update_bwd(a, stream_of(c)));
 }
 
@@ -630,7 +630,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out, Tensor(b!)? q=None, Tensor(c!)? qs=None, Tensor(d!)? qp=None) -> ()", &dwconv_fwd);
   m.def("dwconv_bwd(Tensor dc, Tensor x, Tensor? halo, Tensor w, Tensor? tail_add, Tensor(a!) dx, Tensor(b!)? dhalo, Tensor(c!) dw) -> ()", &dwconv_bwd);
   m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r, Tensor(f!)? q=None, Tensor(g!)? qs=None, Tensor(h!)? qp=None) -> ()", &gate_update_fwd);
-  m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r) -> ()", &gate_update_bwd);
+  m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r, Tensor(h!)? q=None, Tensor(i!)? qs=None, Tensor(j!)? qp=None) -> ()", &gate_update_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!)? rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw) -> ()", &rmsnorm_bwd);
   m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode, bool pow2=False, Tensor(e!)? p_row=None, Tensor(f!)? p_col=None, Tensor? peer_delta=None) -> ()", &quant_tile);

@@ -590,6 +590,11 @@ gate_bwd_cols_kernel(const GateBwdArgs a) {
       st8(a.dz + row * a.d + col, dz);
       st8(a.dsc + row * 2 * a.d + col, dsd);
       st8(a.dsc + row * 2 * a.d + a.d + col, dcd);
+      if (a.quant_dz.q != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dz[i] = __bfloat162float(__float2bfloat16(dz[i]));
+        quant_emit_8(a.quant_dz, dz, row, col, true);
+      }
     }
   }
 #pragma unroll
@@ -618,6 +623,7 @@ const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update_bwd: d must be a multiple of 8";
   if (!a.b2g_f32) return "gate_update_bwd: the gate bias must be fp32";
   if (a.row_dotz == nullptr || a.row_rstdg == nullptr) return "gate_update_bwd: row scratch missing";
+  if (a.quant_dz.q != nullptr && a.d % 128 != 0) return "gate_update_bwd: a quantised dz needs d % 128 == 0";
   launch_pdl(gate_bwd_rowstats_kernel, dim3((unsigned)((a.rows + 7) / 8)), dim3(256), 0, st, a);
   if (cudaGetLastError() != cudaSuccess) return "gate_bwd_rowstats launch failed";
   dim3 grid((unsigned)((a.rows + 8 * GATE_STRIP - 1) / (8 * GATE_STRIP)), (a.d + 255) / 256);

@@ -86,6 +86,7 @@ struct GateBwdArgs {
   int64_t rows;
   int d;
   int64_t dF_ld, dS_ld, c_ld, s_ld;
+  RowQuantOut quant_dz;      // optional 1x128-quantised copy of dz (d % 128 == 0): A operand of the next data-gradient GEMM
 };
 
 const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st);

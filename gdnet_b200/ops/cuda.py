@@ -909,8 +909,15 @@ class _LayerStepFn(torch.autograd.Function):
         vec = torch.zeros(6 * d + d * k_taps, dtype=F32, device=dev)
         db2g, dw_r, db2r, dgnw, db1g, db1r = (vec[i * d : (i + 1) * d] for i in range(6))
         dwc = vec[6 * d :].view(d, k_taps)
-        K.gate_update_bwd(dF2, dS2, g_pre, z, c, s2, f32(rnw), f32(gb2), rstd_z, ssq, eps_g, dgm, dq, dz, dsc, rowcoef,
-                          db2g, dw_r, db2r)
+        if fp8:      # dz leaves the kernel already row-quantised for the data-gradient GEMM of the recovery MLP
+            dz8 = torch.empty(M, d, dtype=FP8, device=dev)
+            sdz = torch.empty(d // 128, M, dtype=F32, device=dev)
+            pdz = packed_buffer(M, d, dev)
+            K.gate_update_bwd(dF2, dS2, g_pre, z, c, s2, f32(rnw), f32(gb2), rstd_z, ssq, eps_g, dgm, dq, dz, dsc,
+                              rowcoef, db2g, dw_r, db2r, dz8, sdz, pdz)
+        else:
+            K.gate_update_bwd(dF2, dS2, g_pre, z, c, s2, f32(rnw), f32(gb2), rstd_z, ssq, eps_g, dgm, dq, dz, dsc,
+                              rowcoef, db2g, dw_r, db2r)
 
         # ---- gate MLP ----
         W2w = _folded_w2(gW2, gnw)
@@ -933,11 +940,11 @@ class _LayerStepFn(torch.autograd.Function):
             # data gradients in e4m3 (row-quantised dz, dh1); weight gradients in bf16 with both operands read
             # in place, which needs no transposed quantised copies
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
-            dz8, _, pdz = quantize_rows_mx(dz)
             g_rW2 = _wgrad_bf16(dz, a1, rW2)
-            dh1 = gemm_fp8_mx(dz8, pdz, q2.qt, q2.pt, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)
+            dh8 = torch.empty(M, d, dtype=FP8, device=dev)      # dh1 quantised by the GEMM that produces it
+            pdh = packed_buffer(M, d, dev)
+            dh1 = gemm_fp8_mx(dz8, pdz, q2.qt, q2.pt, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD, q8=dh8, q8_p=pdh)
             K.colsum(dh1, db1r)
-            dh8, _, pdh = quantize_rows_mx(dh1)
             g_rW1 = _wgrad_bf16_cat(dh1, (s2, c), rW1)
             gemm_fp8_mx(dh8, pdh, q1.qt, q1.pt, out=dsc, aux=dsc, aux_mode=AUX_ADD)
         else:
