@@ -6,6 +6,10 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <nvtx3/nvToolsExt.h>
+
+#include <cstdlib>
+
 #include "comm.h"
 #include "gemm_sm100.h"
 #include "kernels.h"
@@ -14,6 +18,25 @@ namespace {
 
 using at::Tensor;
 using OptT = const std::optional<Tensor>&;
+
+// NVTX range around every op (named after the binding), for timeline tools; on with GDNET_NVTX=1.
+struct OpRange {
+  bool on;
+  explicit OpRange(const char* name) : on(enabled()) {
+    if (on) nvtxRangePushA(name);
+  }
+  ~OpRange() {
+    if (on) nvtxRangePop();
+  }
+  static bool enabled() {
+    static int v = -1;
+    if (v < 0) {
+      const char* e = std::getenv("GDNET_NVTX");
+      v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+  }
+};
 
 #define GD_LAUNCH(expr)                                             \
   do {                                                              \
@@ -204,6 +227,7 @@ void gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, Tensor ou
                OptT row_scale, OptT ssq_in, int64_t norm_dim, double norm_eps, OptT aux, int64_t aux_mode,
                OptT rowcoef, OptT pre_out, int64_t act, OptT ssq_out) {
   c10::cuda::CUDAGuard guard(a.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm operands must be 2-D");
   const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
   const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
@@ -221,6 +245,7 @@ void gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, Tensor ou
 void gemm_fp8(const Tensor& a8, const Tensor& sa, const Tensor& b8, const Tensor& sb, Tensor out, bool accumulate,
               OptT bias, OptT row_scale, OptT aux, int64_t aux_mode, OptT pre_out, int64_t act) {
   c10::cuda::CUDAGuard guard(a8.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(a8.dim() == 2 && b8.dim() == 2, "gemm operands must be 2-D");
   const int64_t M = a8.size(0), K = a8.size(1), N = b8.size(0);
   TORCH_CHECK(b8.size(1) == K, "gemm_fp8: reduction sizes differ");
@@ -240,6 +265,7 @@ void gemm_fp8_mx(const Tensor& a8, const Tensor& pa, const Tensor& b8, const Ten
                  OptT bias, OptT row_scale, OptT aux, int64_t aux_mode, OptT pre_out, int64_t act, OptT q8, OptT q8_p,
                  bool q8_silu, bool store_out) {
   c10::cuda::CUDAGuard guard(a8.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(a8.dim() == 2 && b8.dim() == 2, "gemm operands must be 2-D");
   const int64_t M = a8.size(0), K = a8.size(1), N = b8.size(0);
   TORCH_CHECK(b8.size(1) == K, "gemm_fp8_mx: reduction sizes differ");
@@ -274,6 +300,7 @@ void gemm_fp8_mx(const Tensor& a8, const Tensor& pa, const Tensor& b8, const Ten
 
 void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out, OptT q, OptT qs, OptT qp) {
   c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(x.dim() == 3 && out.dim() == 3, "dwconv: x and out must be (B, T, d)");
   const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
   TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv: taps must be (k, d) contiguous (transposed)");
@@ -289,6 +316,7 @@ void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out, OptT q,
 void dwconv_bwd(const Tensor& dc, const Tensor& x, OptT halo, const Tensor& w, OptT tail_add, Tensor dx, OptT dhalo,
                 Tensor dw) {
   c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(x.dim() == 3 && dc.dim() == 3 && dx.dim() == 3, "dwconv_bwd: tensors must be (B, T, d)");
   const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
   TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv_bwd: taps must be (k, d) contiguous (transposed)");
@@ -309,6 +337,7 @@ void gate_update_fwd(const Tensor& g_pre, const Tensor& z, const Tensor& c, cons
                      Tensor fwd_out, Tensor side_out, OptT gate_out, OptT rstd_out, OptT gate_sum, double eps_r, OptT q,
                      OptT qs, OptT qp) {
   c10::cuda::CUDAGuard guard(c.device());
+  OpRange gd_range_(__func__);
   const int64_t rows = g_pre.size(0);
   const int d = (int)g_pre.size(1);
   TORCH_CHECK(g_pre.is_contiguous() && z.is_contiguous() && fwd_out.is_contiguous() && side_out.is_contiguous(),
@@ -328,6 +357,7 @@ void gate_update_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, co
                      double eps_g, OptT dgate_mean, Tensor dq, Tensor dz, Tensor dsc, Tensor rowcoef, Tensor db2g,
                      Tensor dw_r, Tensor db2r, OptT q, OptT qs, OptT qp) {
   c10::cuda::CUDAGuard guard(c.device());
+  OpRange gd_range_(__func__);
   const int64_t rows = g_pre.size(0);
   const int d = (int)g_pre.size(1);
   TORCH_CHECK(g_pre.is_contiguous() && z.is_contiguous() && dq.is_contiguous() && dz.is_contiguous() && dsc.is_contiguous(),
@@ -347,6 +377,7 @@ void gate_update_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, co
 
 void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor y, OptT rstd, double eps) {
   c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.dim() == 2, "rmsnorm: (rows, d) contiguous");
   GD_LAUNCH(gd::launch_rmsnorm_fwd(bf16_ptr(x, "x"), f32_ptr(w, "w"), bf16_mut(y, "y"),
                                    rstd.has_value() ? f32_mut(*rstd, "rstd") : nullptr, x.size(0), (int)x.size(1),
@@ -355,6 +386,7 @@ void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor y, OptT rstd, double e
 
 void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor dx, Tensor dw) {
   c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && x.dim() == 2, "rmsnorm_bwd: contiguity");
   GD_LAUNCH(gd::launch_rmsnorm_bwd(bf16_ptr(dy, "dy"), bf16_ptr(x, "x"), f32_ptr(w, "w"), f32_ptr(rstd, "rstd"),
                                    bf16_mut(dx, "dx"), f32_mut(dw, "dw"), x.size(0), (int)x.size(1), stream_of(x)));
@@ -363,6 +395,7 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
 void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t row_mode, OptT q_col, OptT s_col,
                 int64_t col_mode, bool pow2, OptT p_row, OptT p_col, OptT peer_delta) {
   c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(x.dim() == 2, "quantise: x must be 2-D");
   gd::QuantArgs a{};
   a.x = bf16_ptr(x, "x");
@@ -428,6 +461,7 @@ void quant_tile(const Tensor& x, bool pre_silu, OptT q_row, OptT s_row, int64_t 
 
 void quant_tensor(const Tensor& x, const Tensor& scale, Tensor q_row, OptT q_col, OptT amax) {
   c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && q_row.is_contiguous(), "quant_tensor: contiguous 2-D");
   if (q_col.has_value()) TORCH_CHECK(q_col->is_contiguous(), "quant_tensor: q_col contiguous");
   GD_LAUNCH(gd::launch_quant_tensor(bf16_ptr(x, "x"), f32_ptr(scale, "scale"), fp8_mut(q_row, "q_row"),
@@ -438,6 +472,7 @@ void quant_tensor(const Tensor& x, const Tensor& scale, Tensor q_row, OptT q_col
 
 void colsum(const Tensor& x, Tensor out) {
   c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(x.dim() == 2 && out.numel() == x.size(1), "colsum: shapes");
   TORCH_CHECK((x.stride(0) * 2) % 16 == 0, "colsum: rows must be 16-byte aligned");
   GD_LAUNCH(gd::launch_colsum(bf16_ptr(x, "x"), f32_mut(out, "out"), x.size(0), (int)x.size(1), x.stride(0), stream_of(x)));
@@ -445,6 +480,7 @@ void colsum(const Tensor& x, Tensor out) {
 
 void segment_add(const Tensor& src, const Tensor& dst_addr, const Tensor& seg_off) {
   c10::cuda::CUDAGuard guard(src.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(src.is_contiguous() && dst_addr.is_cuda() && dst_addr.scalar_type() == at::kLong && dst_addr.is_contiguous(),
               "segment_add: src contiguous, dst_addr int64 on the device");
   TORCH_CHECK(seg_off.is_cuda() && seg_off.scalar_type() == at::kInt && seg_off.numel() == dst_addr.numel(),
@@ -455,12 +491,14 @@ void segment_add(const Tensor& src, const Tensor& dst_addr, const Tensor& seg_of
 
 void scale_cols(const Tensor& w, const Tensor& colw, Tensor out) {
   c10::cuda::CUDAGuard guard(w.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(w.is_contiguous() && out.is_contiguous() && w.dim() == 2 && colw.numel() == w.size(1), "scale_cols: shapes");
   GD_LAUNCH(gd::launch_scale_cols(bf16_ptr(w, "w"), f32_ptr(colw, "colw"), bf16_mut(out, "out"), w.size(0), (int)w.size(1), stream_of(w)));
 }
 
 void unscale_cols_bwd(const Tensor& dW2w, const Tensor& W2, const Tensor& colw, Tensor dW2, Tensor dcolw) {
   c10::cuda::CUDAGuard guard(W2.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(dW2w.is_contiguous() && W2.is_contiguous() && dW2.is_contiguous(), "unscale_cols_bwd: contiguity");
   GD_LAUNCH(gd::launch_unscale_cols_bwd(f32_ptr(dW2w, "dW2w"), bf16_ptr(W2, "W2"), f32_ptr(colw, "colw"),
                                         f32_mut(dW2, "dW2"), f32_mut(dcolw, "dcolw"), (int)W2.size(0), (int)W2.size(1),
@@ -470,6 +508,7 @@ void unscale_cols_bwd(const Tensor& dW2w, const Tensor& W2, const Tensor& colw, 
 void cross_entropy(Tensor logits, const Tensor& targets, Tensor row_loss, const Tensor& inv_count, int64_t vocab,
                    int64_t ignore_index, double grad_scale, bool write_grad) {
   c10::cuda::CUDAGuard guard(logits.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(logits.dim() == 2 && targets.scalar_type() == at::kLong && targets.is_contiguous(), "cross_entropy: inputs");
   TORCH_CHECK(targets.numel() == logits.size(0) && row_loss.numel() == logits.size(0) && vocab <= logits.size(1), "cross_entropy: sizes");
   GD_LAUNCH(gd::launch_cross_entropy(bf16_mut(logits, "logits"), targets.data_ptr<int64_t>(), f32_mut(row_loss, "row_loss"),
@@ -480,6 +519,7 @@ void cross_entropy(Tensor logits, const Tensor& targets, Tensor row_loss, const 
 void mem_read_fwd(const Tensor& q, const Tensor& gamma, const Tensor& e, const Tensor& tags, const Tensor& vals,
                   const Tensor& alpha, Tensor w, Tensor out) {
   c10::cuda::CUDAGuard guard(q.device());
+  OpRange gd_range_(__func__);
   for (const Tensor* t : std::initializer_list<const Tensor*>{&q, &gamma, &e, &tags, &vals, &w, &out}) TORCH_CHECK(t->is_contiguous(), "mem_read: contiguous inputs");
   const int B = (int)tags.size(0), S = (int)tags.size(1), dsig = (int)tags.size(2), dc = (int)vals.size(2);
   GD_LAUNCH(gd::launch_mem_read_fwd(f32_ptr(q, "q"), f32_ptr(gamma, "gamma"), f32_ptr(e, "e"), f32_ptr(tags, "tags"),
@@ -491,6 +531,7 @@ void mem_read_bwd(const Tensor& d_out, const Tensor& q, const Tensor& gamma, con
                   const Tensor& vals, const Tensor& w, const Tensor& alpha, Tensor d_q, Tensor d_gamma, Tensor d_e,
                   Tensor d_tags, Tensor d_vals, Tensor d_alpha) {
   c10::cuda::CUDAGuard guard(q.device());
+  OpRange gd_range_(__func__);
   for (const Tensor* t : std::initializer_list<const Tensor*>{&d_out, &q, &gamma, &e, &tags, &vals, &w, &d_q, &d_gamma, &d_e, &d_tags, &d_vals})
     TORCH_CHECK(t->is_contiguous(), "mem_read_bwd: contiguous tensors");
   const int B = (int)tags.size(0), S = (int)tags.size(1), dsig = (int)tags.size(2), dc = (int)vals.size(2);
@@ -503,6 +544,7 @@ void mem_read_bwd(const Tensor& d_out, const Tensor& q, const Tensor& gamma, con
 
 void grad_dots(const Tensor& gt, OptT gi, Tensor sums) {
   c10::cuda::CUDAGuard guard(gt.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(gt.is_contiguous() && sums.numel() >= 3, "grad_dots: inputs");
   if (gi.has_value()) TORCH_CHECK(gi->is_contiguous() && gi->numel() == gt.numel(), "grad_dots: gi size");
   GD_LAUNCH(gd::launch_grad_dots(f32_ptr(gt, "gt"), opt_f32(gi, "gi"), f32_mut(sums, "sums"), gt.numel(), stream_of(gt)));
@@ -511,6 +553,7 @@ void grad_dots(const Tensor& gt, OptT gi, Tensor sums) {
 void projected_adamw(Tensor p, const Tensor& gt, OptT gi, Tensor m, Tensor v, const Tensor& scalars, double beta_proj,
                      double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step) {
   c10::cuda::CUDAGuard guard(p.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(p.is_contiguous() && gt.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguity");
   TORCH_CHECK(gt.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel() && scalars.numel() >= 2, "adamw: sizes");
   gd::AdamWArgs a{};
@@ -533,6 +576,7 @@ void projected_adamw(Tensor p, const Tensor& gt, OptT gi, Tensor m, Tensor v, co
 void batched_gemv(const Tensor& mats, const Tensor& vecs, const Tensor& outs, const Tensor& rows, const Tensor& cols,
                   const Tensor& is_bf16, int64_t max_rows) {
   c10::cuda::CUDAGuard guard(mats.device());
+  OpRange gd_range_(__func__);
   const int n = (int)mats.numel();
   GD_LAUNCH(gd::launch_batched_gemv(reinterpret_cast<const void* const*>(mats.data_ptr<int64_t>()),
                                     reinterpret_cast<const float* const*>(vecs.data_ptr<int64_t>()),
@@ -546,6 +590,7 @@ void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, con
                      int64_t world, int64_t seq, int64_t phase, bool p_is_bf16, double beta_proj, double lr, double beta1,
                      double beta2, double eps, double weight_decay, int64_t step, Tensor shard_sums) {
   c10::cuda::CUDAGuard guard(m.device());
+  OpRange gd_range_(__func__);
   gd::FusedReduceAdamWArgs a{};
   a.gt = reinterpret_cast<float* const*>(ptr_table_gt.data_ptr<int64_t>());
   a.gi = reinterpret_cast<float* const*>(ptr_table_gi.data_ptr<int64_t>());
@@ -567,6 +612,7 @@ void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, con
 // dst += src where dst is a view into a registered spread gradient buffer (else a plain local add)
 void peer_add(Tensor dst, const Tensor& src) {
   c10::cuda::CUDAGuard guard(dst.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(dst.is_cuda() && dst.scalar_type() == at::kFloat && dst.is_contiguous(), "peer_add: dst must be contiguous fp32");
   TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.numel() == dst.numel(), "peer_add: src must match dst");
   TORCH_CHECK(src.scalar_type() == at::kFloat || src.scalar_type() == at::kBFloat16, "peer_add: src must be fp32 or bf16");
@@ -588,6 +634,7 @@ void peer_add(Tensor dst, const Tensor& src) {
 void max_allreduce(Tensor vec, const Tensor& area_ptrs, const Tensor& flag_ptrs, int64_t slot_elems, int64_t rank,
                    int64_t world, int64_t seq) {
   c10::cuda::CUDAGuard guard(vec.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(vec.is_contiguous() && vec.scalar_type() == at::kFloat, "max_allreduce: vec must be contiguous fp32");
   TORCH_CHECK(area_ptrs.numel() == world && flag_ptrs.numel() == world, "max_allreduce: one pointer per rank");
   gd::MaxAllReduceArgs a{};
@@ -605,6 +652,7 @@ void halo_push_wait(const Tensor& tail, Tensor halo_out, const Tensor& slot_ptrs
                     int64_t slot_offset_bytes, int64_t flag_index, int64_t rank, int64_t world, int64_t seq,
                     bool reverse) {
   c10::cuda::CUDAGuard guard(tail.device());
+  OpRange gd_range_(__func__);
   TORCH_CHECK(tail.is_contiguous() && halo_out.is_contiguous() && tail.numel() == halo_out.numel(), "halo: shapes");
   TORCH_CHECK((tail.numel() * tail.element_size()) % 16 == 0, "halo: message must be a multiple of 16 bytes");
   gd::HaloArgs a{};
