@@ -573,6 +573,21 @@ void projected_adamw(Tensor p, const Tensor& gt, OptT gi, Tensor m, Tensor v, co
 }
 
 // tables: int64 device tensors of pointers (mats, vecs, outs) and int32 (rows, cols, is_bf16)
+void batched_outer_add(const Tensor& dsts, const Tensor& ys, const Tensor& vecs, const Tensor& coef, const Tensor& rows,
+                       const Tensor& cols, int64_t max_rows) {
+  c10::cuda::CUDAGuard guard(dsts.device());
+  OpRange gd_range_(__func__);
+  const int n = (int)dsts.numel();
+  TORCH_CHECK(ys.numel() == n && vecs.numel() == n && coef.numel() == n && rows.numel() == n && cols.numel() == n,
+              "batched_outer_add: one entry per matrix");
+  TORCH_CHECK(coef.is_contiguous() && coef.scalar_type() == at::kFloat, "batched_outer_add: coef must be fp32");
+  GD_LAUNCH(gd::launch_batched_outer_add(reinterpret_cast<float* const*>(dsts.data_ptr<int64_t>()),
+                                         reinterpret_cast<const float* const*>(ys.data_ptr<int64_t>()),
+                                         reinterpret_cast<const float* const*>(vecs.data_ptr<int64_t>()),
+                                         coef.data_ptr<float>(), rows.data_ptr<int>(), cols.data_ptr<int>(), n,
+                                         (int)max_rows, stream_of(dsts)));
+}
+
 void batched_gemv(const Tensor& mats, const Tensor& vecs, const Tensor& outs, const Tensor& rows, const Tensor& cols,
                   const Tensor& is_bf16, int64_t max_rows) {
   c10::cuda::CUDAGuard guard(mats.device());
@@ -692,6 +707,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("mem_read_bwd(Tensor d_out, Tensor q, Tensor gamma, Tensor e, Tensor tags, Tensor vals, Tensor w, Tensor alpha, Tensor(a!) d_q, Tensor(b!) d_gamma, Tensor(c!) d_e, Tensor(d!) d_tags, Tensor(e!) d_vals, Tensor(f!) d_alpha) -> ()", &mem_read_bwd);
   m.def("grad_dots(Tensor gt, Tensor? gi, Tensor(a!) sums) -> ()", &grad_dots);
   m.def("projected_adamw(Tensor(a!) p, Tensor gt, Tensor? gi, Tensor(b!) m, Tensor(c!) v, Tensor scalars, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()", &projected_adamw);
+  m.def("batched_outer_add(Tensor dsts, Tensor ys, Tensor vecs, Tensor coef, Tensor rows, Tensor cols, int max_rows) -> ()", &batched_outer_add);
   m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
   m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums) -> ()", &allreduce_adamw);
   m.def("gemm_pair_capacity() -> int", []() -> int64_t { return gd::gemm_pair_capacity(); });

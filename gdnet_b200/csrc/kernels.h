@@ -178,4 +178,9 @@ const char* launch_batched_gemv(const void* const* mats, const float* const* vec
                                 const int* rows, const int* cols, const int* is_bf16, int n_mats, int max_rows,
                                 cudaStream_t st);
 
+// dst_i (fp32, rows_i x cols_i) += coef[i] * y_i v_i^T for all i in one launch
+const char* launch_batched_outer_add(float* const* dsts, const float* const* ys, const float* const* vecs,
+                                     const float* coef, const int* rows, const int* cols, int n_mats, int max_rows,
+                                     cudaStream_t st);
+
 }  // namespace gd

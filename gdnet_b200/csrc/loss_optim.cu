@@ -386,6 +386,33 @@ const char* launch_batched_gemv(const void* const* mats, const float* const* vec
   return cudaGetLastError() == cudaSuccess ? nullptr : "batched_gemv launch failed";
 }
 
+// dst_i[r][c] += coef[i] * y_i[r] * v_i[c] for a batch of fp32 matrices given by pointer tables: the rank-1
+// gradients of all spectral estimates in one launch (one warp per row, lanes along the columns).
+__global__ void __launch_bounds__(256)
+batched_outer_add_kernel(float* const* __restrict__ dsts, const float* const* __restrict__ ys,
+                         const float* const* __restrict__ vecs, const float* __restrict__ coef,
+                         const int* __restrict__ rows, const int* __restrict__ cols) {
+  const int mi = blockIdx.y;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int R = rows[mi], C = cols[mi];
+  if (r >= R) return;
+  const float a = coef[mi] * ys[mi][r];
+  if (a == 0.0f) return;
+  const float* v = vecs[mi];
+  float* d = dsts[mi] + (int64_t)r * C;
+  for (int c = lane; c < C; c += 32) d[c] = fmaf(a, v[c], d[c]);
+}
+
+const char* launch_batched_outer_add(float* const* dsts, const float* const* ys, const float* const* vecs,
+                                     const float* coef, const int* rows, const int* cols, int n_mats, int max_rows,
+                                     cudaStream_t st) {
+  if (n_mats == 0) return nullptr;
+  dim3 grid((max_rows + 7) / 8, n_mats);
+  batched_outer_add_kernel<<<grid, 256, 0, st>>>(dsts, ys, vecs, coef, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "batched_outer_add launch failed";
+}
+
 }  // namespace gd
 
 // =======================================================================================

@@ -227,6 +227,7 @@ def clear_caches() -> None:
     _w2w_cache.clear()
     _side_offers.clear()
     _seg_tables.clear()
+    _sigma_plans.clear()
 
 
 # --------------------------------------------------------------------------------------
@@ -1033,51 +1034,130 @@ def _ptr_table(tensors, device):
     return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=device)
 
 
+class _SigmaPlan:
+    """Everything about a set of matrices that does not change between calls: the pointer tables of the
+    batched kernels and persistent buffers for the probe vectors and the products ``y_i = W_i v_i``."""
+
+    def __init__(self, mats):
+        dev = mats[0].device
+        self.n = len(mats)
+        self.rows = [W.shape[0] for W in mats]
+        self.cols = [W.shape[1] for W in mats]
+        self.v_flat = torch.empty(sum(self.cols), dtype=F32, device=dev)
+        self.y_flat = torch.empty(sum(self.rows), dtype=F32, device=dev)
+        self.v_views, self.y_views, o = [], [], 0
+        for c in self.cols:
+            self.v_views.append(self.v_flat[o : o + c])
+            o += c
+        o = 0
+        for r in self.rows:
+            self.y_views.append(self.y_flat[o : o + r])
+            o += r
+        i64, i32 = torch.int64, torch.int32
+        self.t_mats = torch.tensor([W.data_ptr() for W in mats], dtype=i64, device=dev)
+        self.t_v = torch.tensor([v.data_ptr() for v in self.v_views], dtype=i64, device=dev)
+        self.t_y = torch.tensor([y.data_ptr() for y in self.y_views], dtype=i64, device=dev)
+        self.t_rows = torch.tensor(self.rows, dtype=i32, device=dev)
+        self.t_cols = torch.tensor(self.cols, dtype=i32, device=dev)
+        self.t_bf16 = torch.tensor([int(W.dtype == BF16) for W in mats], dtype=i32, device=dev)
+        self.max_rows = max(self.rows)
+        self.same_rows = len(set(self.rows)) == 1
+        self.same_cols = len(set(self.cols)) == 1
+        self.sources = list(mats)           # pins the storages the pointer table refers to
+        self.mg_tables: dict = {}
+
+    def mg_table(self, mgs):
+        key = tuple(m.data_ptr() for m in mgs)
+        t = self.mg_tables.get(key)
+        if t is None:
+            t = torch.tensor(key, dtype=torch.int64, device=self.v_flat.device)
+            self.mg_tables[key] = t
+        return t
+
+
+_sigma_plans: dict = {}
+
+
+def _sigma_plan(mats) -> _SigmaPlan:
+    key = tuple((W.data_ptr(), W.shape[0], W.shape[1], W.dtype) for W in mats)
+    plan = _sigma_plans.get(key)
+    if plan is None:
+        plan = _SigmaPlan(mats)
+        _sigma_plans[key] = plan
+    return plan
+
+
 class _SigmaFn(torch.autograd.Function):
-    """``sigma_i = ||W_i v_i||`` (fp32). Backward: ``dW_i = dsigma_i * (W_i v_i) v_i^T / sigma_i``,
-    a rank-1 update that is skipped for matrices whose ``dsigma`` is zero."""
+    """``sigma_i = ||W_i v_i||`` (fp32) for all matrices in one matrix-vector launch. Backward:
+    ``dW_i = dsigma_i * (W_i v_i) v_i^T / sigma_i``, all rank-1 updates in one launch when the training engine
+    has installed fp32 gradient buffers. The probe vectors were written into the plan's buffer by the caller."""
 
     @staticmethod
-    def forward(ctx, n, *args):
-        mats, vecs = args[:n], args[n:]
-        dev = mats[0].device
-        ys = [torch.empty(W.shape[0], dtype=F32, device=dev) for W in mats]
-        wd = [W.detach() for W in mats]
-        K.batched_gemv(
-            _ptr_table(wd, dev), _ptr_table(vecs, dev), _ptr_table(ys, dev),
-            torch.tensor([W.shape[0] for W in mats], dtype=torch.int32, device=dev),
-            torch.tensor([W.shape[1] for W in mats], dtype=torch.int32, device=dev),
-            torch.tensor([int(W.dtype == BF16) for W in mats], dtype=torch.int32, device=dev),
-            max(W.shape[0] for W in mats),
-        )
-        sig = torch.stack([y.norm() for y in ys])
-        ctx.n = n
-        ctx.save_for_backward(sig, *ys, *vecs)
+    def forward(ctx, plan, *mats):
+        K.batched_gemv(plan.t_mats, plan.t_v, plan.t_y, plan.t_rows, plan.t_cols, plan.t_bf16, plan.max_rows)
+        if plan.same_rows:
+            sig = plan.y_flat.view(plan.n, plan.rows[0]).norm(dim=1)
+        else:
+            sig = torch.stack([y.norm() for y in plan.y_views])
+        ctx.plan = plan
         ctx.mats = mats
+        # the buffers are reused by the next call: keep this call's values for backward
+        ctx.save_for_backward(sig, plan.y_flat.clone(), plan.v_flat.clone())
         return sig
 
     @staticmethod
     def backward(ctx, dsig):
-        n = ctx.n
-        saved = ctx.saved_tensors
-        sig, ys, vecs = saved[0], saved[1 : 1 + n], saved[1 + n :]
-        coef = dsig / sig.clamp(min=1e-12)
-        grads = []
-        for i, W in enumerate(ctx.mats):
-            mg = _main_grad(W)
-            if mg is not None:
-                accumulate_main_grad(mg, torch.outer(ys[i] * coef[i], vecs[i]))
+        plan, mats = ctx.plan, ctx.mats
+        sig, y_flat, v_flat = ctx.saved_tensors
+        coef = (dsig / sig.clamp(min=1e-12)).to(F32).contiguous()
+        mgs = [_main_grad(W) for W in mats]
+        if not _spread_grads and all(m is not None and m.dtype == F32 and m.is_contiguous() for m in mgs):
+            # rebuild the y / v pointer tables for the saved copies (same layout, different base)
+            dy = y_flat.data_ptr() - plan.y_flat.data_ptr()
+            dv = v_flat.data_ptr() - plan.v_flat.data_ptr()
+            K.batched_outer_add(plan.mg_table(mgs), plan.t_y + dy, plan.t_v + dv, coef, plan.t_rows, plan.t_cols,
+                                plan.max_rows)
+            return (None, *([None] * len(mats)))
+        grads, oy, ov = [], 0, 0
+        for i, W in enumerate(mats):
+            y, v = y_flat[oy : oy + plan.rows[i]], v_flat[ov : ov + plan.cols[i]]
+            oy, ov = oy + plan.rows[i], ov + plan.cols[i]
+            g = torch.outer(y * coef[i], v)
+            if mgs[i] is not None:
+                accumulate_main_grad(mgs[i], g)
                 grads.append(None)
             else:
-                grads.append(torch.outer(ys[i] * coef[i], vecs[i]).to(W.dtype))
-        return (None, *grads, *([None] * n))
+                grads.append(g.to(W.dtype))
+        return (None, *grads)
 
 
-def sigma_estimates(mats, vecs):
+def sigma_estimates(mats, vecs=None, generator=None):
+    """``||W_i v_i||`` for unit vectors ``v_i`` (given, or drawn here: one normal draw for all matrices,
+    normalised per matrix)."""
     ok = all(W.is_contiguous() and W.dtype in (BF16, F32) for W in mats)
     if not ok:
+        if vecs is None:
+            vecs = [torch.nn.functional.normalize(torch.randn(W.shape[1], device=W.device, generator=generator), dim=0)
+                    for W in mats]
         return torch.stack([(W.float() @ v).norm() for W, v in zip(mats, vecs)])
-    return _SigmaFn.apply(len(mats), *mats, *[v.contiguous() for v in vecs])
+    plan = _sigma_plan(mats)
+    with torch.no_grad():
+        if vecs is not None:
+            torch.cat([v.reshape(-1).to(F32) for v in vecs], out=plan.v_flat)
+        else:
+            plan.v_flat.normal_(generator=generator)
+            if plan.same_cols:
+                v2 = plan.v_flat.view(plan.n, plan.cols[0])
+                v2.div_(v2.norm(dim=1, keepdim=True))
+            else:
+                # two or more widths (d and 2d): normalise each width group in one go
+                for c in sorted(set(plan.cols)):
+                    idx = [i for i, cc in enumerate(plan.cols) if cc == c]
+                    grp = torch.stack([plan.v_views[i] for i in idx])
+                    grp = grp / grp.norm(dim=1, keepdim=True)
+                    for j, i in enumerate(idx):
+                        plan.v_views[i].copy_(grp[j])
+    return _SigmaFn.apply(plan, *mats)
 
 
 # --------------------------------------------------------------------------------------

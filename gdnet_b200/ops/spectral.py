@@ -21,9 +21,9 @@ def _unit_vectors(mats, generator=None):
 
 def sigma_estimates(mats, generator: torch.Generator | None = None, vectors=None) -> torch.Tensor:
     """fp32 tensor ``(len(mats),)`` of ``||W_i v_i||``; differentiable w.r.t. each ``W_i``."""
-    vs = vectors if vectors is not None else _unit_vectors(mats, generator)
     if mats and mats[0].is_cuda:
         from . import cuda as cuda_ops
 
-        return cuda_ops.sigma_estimates(mats, vs)
+        return cuda_ops.sigma_estimates(mats, vectors, generator)      # probe vectors drawn in one batch
+    vs = vectors if vectors is not None else _unit_vectors(mats, generator)
     return torch.stack([(W.float() @ v).norm() for W, v in zip(mats, vs)])
