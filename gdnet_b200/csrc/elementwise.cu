@@ -549,10 +549,12 @@ gate_bwd_rowstats_kernel(const GateBwdArgs a) {
 
 constexpr int GATE_STRIP = 16;   // rows per warp in the column kernel
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 gate_bwd_cols_kernel(const GateBwdArgs a) {
   pdl_enter();
-  __shared__ float part[8][3][256 + 1];
+  __shared__ float part[3][256];     // column sums of the block's 8 strips, added with shared-memory atomics
+  for (int i = threadIdx.x; i < 3 * 256; i += 256) (&part[0][0])[i] = 0.0f;
+  __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = blockIdx.y * 256 + lane * 8;
   const int64_t r0 = ((int64_t)blockIdx.x * 8 + warp) * GATE_STRIP;
@@ -597,25 +599,20 @@ gate_bwd_cols_kernel(const GateBwdArgs a) {
       }
     }
   }
+  // element i of lane l is column l * 8 + i; stored at i * 32 + l so that the lanes of a warp hit different banks
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    part[warp][0][lane * 8 + i] = sg[i];
-    part[warp][1][lane * 8 + i] = sw[i];
-    part[warp][2][lane * 8 + i] = sb[i];
+    atomicAdd(&part[0][i * 32 + lane], sg[i]);
+    atomicAdd(&part[1][i * 32 + lane], sw[i]);
+    atomicAdd(&part[2][i * 32 + lane], sb[i]);
   }
   __syncthreads();
   const int c = blockIdx.y * 256 + threadIdx.x;
   if (c < a.d) {
-    float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      t0 += part[w][0][threadIdx.x];
-      t1 += part[w][1][threadIdx.x];
-      t2 += part[w][2][threadIdx.x];
-    }
-    atomicAdd(a.db2g + c, t0);
-    atomicAdd(a.dw_r + c, t1);
-    atomicAdd(a.db2r + c, t2);
+    const int slot = (threadIdx.x & 7) * 32 + (threadIdx.x >> 3);
+    atomicAdd(a.db2g + c, part[0][slot]);
+    atomicAdd(a.dw_r + c, part[1][slot]);
+    atomicAdd(a.db2r + c, part[2][slot]);
   }
 }
 
