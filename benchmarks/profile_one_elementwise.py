@@ -1,6 +1,6 @@
 """Launch one memory-bound kernel a few times on the training shape, for an ncu capture of a small case.
 
-    python benchmarks/profile_one_elementwise.py --kernel conv_fwd|conv_bwd|gate_fwd|gate_bwd|quant_rows|quant_tile|rmsnorm|cross_entropy|mem_read
+    python benchmarks/profile_one_elementwise.py --kernel conv_fwd|conv_bwd|gate_fwd|gate_bwd|quant_rows|quant_tile|rmsnorm|cross_entropy|mem_read|adamw|gemv
                                                  [--B 8] [--T 4096] [--d 1024] [--iters 3]
 
 Inputs of one launch are a few hundred MB (larger than L2); nothing else runs before the kernel of interest
@@ -80,6 +80,17 @@ def main():
         q, gamma, e, tags, vals, alpha = f(Bq, dsig), f(Bq, 1), f(S, dsig), f(Bq, S, dsig), f(Bq, S, dc), f(1)
         wts, out = torch.empty(Bq, S, device=dev), torch.empty(Bq, dc, device=dev)
         fn = lambda: K.mem_read_fwd(q, gamma, e, tags, vals, alpha, wts, out)
+    elif args.kernel == "adamw":
+        n = 128 * 1024 * 1024
+        p_ = torch.zeros(n, device=dev, dtype=bf)
+        gt, gi, m_, v_ = (torch.randn(n, device=dev) for _ in range(4))
+        v_.abs_()
+        scal = torch.tensor([0.1, 1.0], device=dev)
+        fn = lambda: K.projected_adamw(p_, gt, gi, m_, v_, scal, 0.1, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1)
+    elif args.kernel == "gemv":
+        mats = [rnd(d, 2 * d) for _ in range(96)]
+        vecs = [torch.nn.functional.normalize(torch.randn(2 * d, device=dev), dim=0) for _ in mats]
+        fn = lambda: cu.sigma_estimates(mats, vecs)
     else:
         raise SystemExit(f"unknown kernel {args.kernel}")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
