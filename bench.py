@@ -151,6 +151,7 @@ def build_ours(cfg, device, world):
 
         return cu.launch_count()
 
+    step.engine = engine
     return step, launches
 
 
@@ -277,6 +278,9 @@ def main() -> None:
     dev_batches = [to_device(b) for b in batches[W : W + K]]
     sync_all()
     n0 = launches()
+    eng = getattr(step, "engine", None)
+    if eng is not None:
+        eng.time_updates = True
     sampler = ClockSampler(local_rank)
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -288,6 +292,11 @@ def main() -> None:
     clocks = sampler.stop()
     n_launch = launches() - n0
     ms_dev = ev0.elapsed_time(ev1) / K
+    update_ms = None
+    if eng is not None:
+        ts = sorted(eng.update_times_ms())
+        eng.time_updates = False
+        update_ms = ts[len(ts) // 2] if ts else None
 
     # (2) end to end through the public step call: H2D of the step's inputs, D2H of its loss
     sync_all()
@@ -299,10 +308,11 @@ def main() -> None:
     sync_all()
     ms_e2e = (time.perf_counter() - t0) * 1000.0 / K
 
-    t = torch.tensor([ms_dev, ms_e2e], device=device, dtype=torch.float64)
+    t = torch.tensor([ms_dev, ms_e2e, update_ms if update_ms is not None else -1.0], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_dev, ms_e2e = float(t[0]), float(t[1])
+    update_ms = float(t[2]) if float(t[2]) >= 0 else None
     global_batch = cfg["micro_batch"] * (1 if sp else world)     # sequences per step over the whole job
     value = global_batch * T / (ms_dev / 1000.0)
     e2e = global_batch * T / (ms_e2e / 1000.0)
@@ -327,6 +337,9 @@ def main() -> None:
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4},
             "gpu_launches": n_launch,
+            # device time of the update phase per step (gradient collective + projection + AdamW + parameter
+            # all-gather, waits for slower ranks included), max over ranks; on one GPU it is the optimizer alone
+            "update_phase_ms": update_ms,
             "last_loss": last,
         }))
     if world > 1:

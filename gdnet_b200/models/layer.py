@@ -38,7 +38,13 @@ class CausalDepthWiseConv1d(nn.Module):
 
     @property
     def taps(self) -> torch.Tensor:
-        return self.conv.weight.squeeze(1)
+        """The ``(d, k)`` view of the conv weight. It remembers the parameter it views (``base_param``), so a
+        kernel's backward can look up the flat fp32 gradient buffer a training engine has installed on the
+        parameter at that time (``main_grad``) and add the tap gradients in place."""
+        w = self.conv.weight
+        t = w.squeeze(1)
+        t.base_param = w
+        return t
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.causal_dwconv(x, self.taps)

@@ -434,25 +434,37 @@ def _sink_vec(p, g32):
 _seg_tables: dict = {}
 
 
-def _sink_vecs(params, packed, views):
+def _sink_vecs(params, packed, views, mgs=None):
     """Deliver the gradients of several small parameters that sit back to back in ``packed`` (``views`` are the
-    per-parameter views of it): one ``segment_add`` launch into their ``main_grad`` places when the engine has
-    installed local fp32 gradient buffers, else one by one."""
-    mgs = [_main_grad(p) for p in params]
-    if _spread_grads or any(m is None or m.dtype != F32 or not m.is_contiguous() for m in mgs):
-        return [_sink_vec(p, v) for p, v in zip(params, views)]
-    key = tuple(m.data_ptr() for m in mgs)
-    tab = _seg_tables.get(key)
-    if tab is None:
-        offs, o = [], 0
-        for v in views:
-            offs.append(o)
-            o += v.numel()
-        tab = (torch.tensor(key, dtype=torch.int64, device=packed.device),
-               torch.tensor(offs, dtype=torch.int32, device=packed.device))
-        _seg_tables[key] = tab
-    K.segment_add(packed, tab[0], tab[1])
-    return [None] * len(params)
+    per-parameter views of it): one ``segment_add`` launch for all of them that have a local fp32 ``main_grad``
+    (installed by the training engine); the others (no ``main_grad``, e.g. a derived view such as the conv taps,
+    or gradients spread over ranks) go one by one."""
+    if mgs is None:
+        mgs = [_main_grad(p) for p in params]
+    batch = [] if _spread_grads else [i for i, m in enumerate(mgs) if m is not None and m.dtype == F32 and m.is_contiguous()]
+    out = [None] * len(params)
+    for i, (p, v) in enumerate(zip(params, views)):
+        if i not in batch:
+            out[i] = _sink_vec(p, v)
+    if batch:
+        key = tuple(mgs[i].data_ptr() for i in batch) + tuple(batch)
+        tab = _seg_tables.get(key)
+        if tab is None:
+            offs, o = [], 0
+            for v in views:
+                offs.append(o)
+                o += v.numel()
+            # segments must be ascending and cover [first offset, total): give the skipped ranges a dummy target
+            addrs, segs = [], []
+            scratch = torch.zeros(max(v.numel() for v in views), dtype=F32, device=packed.device)
+            for i, v in enumerate(views):
+                addrs.append(mgs[i].data_ptr() if i in batch else scratch.data_ptr())
+                segs.append(offs[i])
+            tab = (torch.tensor(addrs, dtype=torch.int64, device=packed.device),
+                   torch.tensor(segs, dtype=torch.int32, device=packed.device), scratch)
+            _seg_tables[key] = tab
+        K.segment_add(packed, tab[0], tab[1])
+    return out
 
 
 def _wgrad_target(p):
@@ -878,6 +890,7 @@ class _LayerStepFn(torch.autograd.Function):
                                   z, hg_pre, h, ssq, g_pre, rstd_z, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1, gnw,
                                   gW2, gb2)
             ctx.cfg = (B, T, d, fp8, eps_g, halo is not None)
+            ctx.conv_param = getattr(conv_w, "base_param", None)   # the taps are a view of this parameter
         return fwd_out, side_out, gate_sum
 
     @staticmethod
@@ -962,8 +975,14 @@ class _LayerStepFn(torch.autograd.Function):
         ds = dsc.view(B, T, 2 * d)[:, :, :d]
 
         g_gW2 = None if main2 else tgt2.to(gW2.dtype)
+        smalls = (gb2, rnw, rb2, gnw, gb1, rb1, conv_w)
+        mgs = [_main_grad(p) for p in smalls]
+        if mgs[-1] is None and ctx.conv_param is not None:
+            mg = _main_grad(ctx.conv_param)          # the buffer installed for THIS backward pass
+            if mg is not None and not _spread_grads:
+                mgs[-1] = mg.view(conv_w.shape)
         g_gb2, g_rnw, g_rb2, g_gnw, g_gb1, g_rb1, g_conv = _sink_vecs(
-            (gb2, rnw, rb2, gnw, gb1, rb1, conv_w), vec, (db2g, dw_r, db2r, dgnw, db1g, db1r, dwc))
+            smalls, vec, (db2g, dw_r, db2r, dgnw, db1g, db1r, dwc), mgs)
         return (dx, ds, dhalo, g_conv, g_rW1, g_rb1, g_rW2, g_rb2, g_rnw, g_gW1, g_gb1, g_gnw, g_gW2, g_gb2,
                 None, None, None, None, None)
 

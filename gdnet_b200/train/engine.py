@@ -108,6 +108,8 @@ class TrainEngine(nn.Module):
         self.projection = projection
         self.step_count = 0
         self.comm_seq = 0
+        self.time_updates = False
+        self._update_events: list = []
         dev = next(model.parameters()).device
         self.device = dev
         self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(process_group) > 1
@@ -235,11 +237,26 @@ class TrainEngine(nn.Module):
             self._fold_autograd_grads()
             total += loss_task.detach().float()
 
+        timed = self.time_updates and self.device.type == "cuda"
+        if timed:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         self._update(beta, grad_clip)
+        if timed:
+            ev1.record()
+            self._update_events.append((ev0, ev1))
         from ..ops import cuda as cu
 
         cu.invalidate_param_caches()
         return total
+
+    def update_times_ms(self) -> list[float]:
+        """Device time of the update phase (gradient collective + projection + AdamW + parameter all-gather,
+        including any wait for slower ranks) of every step since the last call; needs ``time_updates=True``."""
+        torch.cuda.synchronize(self.device)
+        out = [a.elapsed_time(b) for a, b in self._update_events]
+        self._update_events.clear()
+        return out
 
     def _update(self, beta: float, grad_clip: float) -> None:
         from ..ops import cuda as cu

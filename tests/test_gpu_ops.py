@@ -345,3 +345,53 @@ def test_collective_kernels_single_rank():
     torch.cuda.synchronize()
     _status(vec)
     assert torch.equal(vec, keep)
+
+
+def test_engine_gradient_buffers_match_autograd():
+    """Every parameter's task and information gradient, as the engine's kernels leave them in the two flat
+    fp32 buffers (weight-gradient epilogues, packed small-parameter delivery, conv taps through their base
+    parameter, batched spectral-penalty gradients), against plain autograd on the same model, over two steps
+    (the second step would expose a gradient that went to the buffer of the other pass)."""
+    import copy
+
+    from gdnet_b200.model import GDNet
+    from gdnet_b200.train.engine import TrainEngine
+    from gdnet_b200.train.step import info_losses
+    from gdnet_b200.utils.fp8 import autocast, cast_for_precision
+
+    torch.manual_seed(0)
+    base = GDNet(vocab_size=1024, d_embed=128, d=128, n_layers=2, n_cycles=2, kernel_size=4, chunk_size=256).to(DEV)
+    cast_for_precision(base, "fp8")
+    ref_model = copy.deepcopy(base)
+    eng = TrainEngine(copy.deepcopy(base), precision="fp8")
+    eng._update = lambda *a, **k: None            # keep the parameters: only the gradient buffers are compared
+    g = torch.Generator().manual_seed(3)
+    for step in range(2):
+        tok = torch.randint(0, 1024, (2, 257), generator=g).to(DEV)
+        inp, tgt = tok[:, :-1], tok[:, 1:]
+        torch.manual_seed(100 + step)             # same random probe vectors of the spectral penalty in both runs
+        eng.projected_step(inp, tgt)
+        got = {}
+        for which in ("task", "info"):
+            eng._point_main_grad(which)
+            got[which] = {n: p.main_grad.clone() for n, p in eng.module.named_parameters()}
+        torch.manual_seed(100 + step)
+        with autocast("fp8", "cuda"):
+            logits, side, _, _, gate_vals, _, _ = ref_model(inp, None, None, return_gates="mean")
+            loss_task = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), tgt.reshape(-1))
+        params = dict(ref_model.named_parameters())
+        names = list(params)
+        g_task = torch.autograd.grad(loss_task, [params[n] for n in names], retain_graph=True, allow_unused=True)
+        with autocast("fp8", "cuda"):
+            loss_info = info_losses(ref_model, side, gate_vals)
+        g_info = torch.autograd.grad(loss_info, [params[n] for n in names], allow_unused=True)
+        for which, grads in (("task", g_task), ("info", g_info)):
+            for n, gr in zip(names, grads):
+                have = got[which][n].float()
+                want = torch.zeros_like(have) if gr is None else gr.float()
+                scale = float(want.norm())
+                if scale < 1e-6:
+                    assert float(have.norm()) < 1e-4, f"step {step} {which} {n}: expected no gradient"
+                else:
+                    rel = float((have - want).norm()) / scale
+                    assert rel < 0.08, f"step {step} {which} gradient of {n}: relative error {rel:.3f}"
