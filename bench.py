@@ -141,7 +141,8 @@ def build_ours(cfg, device, world):
         sp_group = dist.group.WORLD
     share = os.environ.get("GDNET_SHARE_FP8", "1" if cfg.get("share_fp8") else "0") == "1"
     engine = TrainEngine(model, lr=1e-3, precision="fp8", sp_group=sp_group,
-                         comm=os.environ.get("GDNET_COMM", cfg.get("comm", "fused")), share_fp8_weights=share)
+                         comm=os.environ.get("GDNET_COMM", cfg.get("comm", "fused")), share_fp8_weights=share,
+                         fused_ce=os.environ.get("GDNET_FUSED_CE", "1") == "1")
 
     def step(tokens, targets, write_chunks):
         return engine.projected_step(tokens, targets, write_chunks=write_chunks)

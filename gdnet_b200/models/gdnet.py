@@ -106,22 +106,27 @@ class GDNet(nn.Module):
             )
         return fwd, side, gate_vals
 
-    def logits_from(self, fwd: torch.Tensor) -> torch.Tensor:
+    def features_from(self, fwd: torch.Tensor) -> torch.Tensor:
+        """Input of the vocabulary projection: ``proj_out(norm_out(fwd))``."""
         eps = self.norm_out.eps if self.norm_out.eps is not None else float(torch.finfo(fwd.dtype).eps)
-        normed = ops.rmsnorm(fwd, self.norm_out.weight, eps)
-        return self.head(self.proj_out(normed))[..., : self.vocab_size]
+        return self.proj_out(ops.rmsnorm(fwd, self.norm_out.weight, eps))
+
+    def logits_from(self, fwd: torch.Tensor) -> torch.Tensor:
+        return self.head(self.features_from(fwd))[..., : self.vocab_size]
 
     # -- public API -------------------------------------------------------------------
 
     def forward(self, tokens, buffer_tags=None, buffer_vals=None, return_gates: bool | str = False,
-                sp_group=None, need_logits: bool = True):
+                sp_group=None, need_logits: bool | str = True):
         """Returns ``(logits, side, buffer_tags, buffer_vals, gate_vals, cam_weights, fwd_last)``.
 
         ``return_gates=True`` collects the forward-gate tensors ``(B,T,d)`` of every
         forward step (gradients flow through them); ``return_gates="mean"`` collects
         only their means (0-dim tensors), which is what the information loss needs.
         ``need_logits=False`` skips the read-out (logits is None) for callers that only
-        want the chunk summary, e.g. the memory-filling passes.
+        want the chunk summary, e.g. the memory-filling passes; ``need_logits="features"`` returns
+        the input of the vocabulary projection in place of the logits (the caller fuses the
+        projection with the loss, ``ops.linear_cross_entropy``).
         """
         B, T = tokens.shape
         fwd, side, gate_vals = self.trunk(tokens, return_gates, sp_group)
@@ -137,7 +142,8 @@ class GDNet(nn.Module):
         if need_logits:
             if self.cam_enabled:
                 fwd, cam_weights = self.cam.read(fwd, side[0], buffer_tags, buffer_vals)
-            logits = self.logits_from(fwd)
+            # "features": stop before the vocabulary projection (the caller fuses it with the loss)
+            logits = self.features_from(fwd) if need_logits == "features" else self.logits_from(fwd)
         return logits, side, buffer_tags, buffer_vals, gate_vals, cam_weights, fwd_last
 
     def write_cam(self, fwd_last, side, buffer_tags, buffer_vals):

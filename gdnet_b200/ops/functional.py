@@ -53,6 +53,23 @@ def cross_entropy(logits, targets, ignore_index: int = -100):
     return ref.cross_entropy(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1), ignore_index)
 
 
+def linear_cross_entropy(x, head, targets, vocab: int, ignore_index: int = -100):
+    """Mean cross-entropy of ``head(x)[..., :vocab]`` against ``targets``. On CUDA, for a bias-free bf16 or
+    block-scaled FP8 head, the projection, the loss and the head's gradients run chunk by chunk over the rows
+    without ever holding all logits (``ops/cuda.py:_LinearCrossEntropyFn``)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if _on_gpu(x2) and ignore_index == -100 and getattr(head, "bias", None) is None:
+        from .fp8_linear import FP8Linear
+
+        cu = _cuda()
+        fp8 = isinstance(head, FP8Linear) and head.recipe == "block"
+        plain = type(head) is torch.nn.Linear or fp8
+        if plain and cu.linear_cross_entropy_ok(x2, head.weight, fp8):
+            return cu.linear_cross_entropy(x2, head.weight, targets, vocab, fp8)
+    logits = head(x)[..., :vocab]
+    return cross_entropy(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1), ignore_index)
+
+
 def sample_top_p(logits: torch.Tensor, top_p: float, generator=None) -> torch.Tensor:
     """Nucleus sampling of one id from ``logits (1, V)``."""
     probs = F.softmax(logits, dim=-1)

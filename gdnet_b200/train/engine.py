@@ -95,7 +95,7 @@ class TrainEngine(nn.Module):
     def __init__(self, model: nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 1e-2, precision: str = "fp8", process_group=None, sp_group=None,
                  comm: str = "fused", broadcast: bool = True, projection: str = "local",
-                 share_fp8_weights: bool = False):
+                 share_fp8_weights: bool = False, fused_ce: bool = True):
         super().__init__()
         self.module = model
         self.precision = precision
@@ -108,6 +108,8 @@ class TrainEngine(nn.Module):
         self.projection = projection
         self.step_count = 0
         self.comm_seq = 0
+        # project to the vocabulary and take the loss chunk by chunk, never holding all logits
+        self.fused_ce = bool(fused_ce)
         self.time_updates = False
         self._update_events: list = []
         dev = next(model.parameters()).device
@@ -222,11 +224,15 @@ class TrainEngine(nn.Module):
                 if write_chunks is not None and base.cam_enabled:
                     tags, vals = build_cam_buffer(model, write_chunks[sl], sp_group=self.sp_group)
                 logits, side, _, _, gate_vals, _, _ = model(tok_i, tags, vals, return_gates="mean",
-                                                            sp_group=self.sp_group)
+                                                            sp_group=self.sp_group,
+                                                            need_logits="features" if self.fused_ce else True)
                 tgt = tgt_i.reshape(-1)
                 if loss_mask is not None:
                     tgt = torch.where(loss_mask[sl].reshape(-1), tgt, torch.full_like(tgt, -100))
-                loss_task = ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt) / accum_steps
+                if self.fused_ce:
+                    loss_task = ops.linear_cross_entropy(logits, base.head, tgt, base.vocab_size) / accum_steps
+                else:
+                    loss_task = ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt) / accum_steps
             self._point_main_grad("task")
             loss_task.backward(retain_graph=True)
             self._fold_autograd_grads()

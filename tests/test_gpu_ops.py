@@ -395,3 +395,30 @@ def test_engine_gradient_buffers_match_autograd():
                 else:
                     rel = float((have - want).norm()) / scale
                     assert rel < 0.08, f"step {step} {which} gradient of {n}: relative error {rel:.3f}"
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_linear_cross_entropy_chunked(fp8):
+    """Projection + loss in row chunks against the unfused path: loss, gradient of the input, gradient of the
+    head (through autograd and through an installed fp32 gradient buffer)."""
+    cu = _cu()
+    M, Kd, V, Vp = 512, 256, 1000, 1024
+    torch.manual_seed(1)
+    x = torch.randn(M, Kd, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(Vp, Kd, device=DEV) * 0.05).to(BF).requires_grad_()
+    tgt = torch.randint(0, V, (M,), device=DEV)
+    tgt[::7] = -100
+    loss = cu.linear_cross_entropy(x, w, tgt, V, fp8, chunk_rows=128)
+    (2.0 * loss).backward()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    want = F.cross_entropy((xr @ wr.t())[:, :V], tgt, ignore_index=-100)
+    (2.0 * want).backward()
+    tol = 0.08 if fp8 else 0.02
+    assert abs(float(loss) - float(want)) < tol * abs(float(want))
+    _check(x.grad, xr.grad, tol, "d loss / d x")
+    _check(w.grad, wr.grad, tol, "d loss / d W")
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.zeros(Vp, Kd, device=DEV)
+    cu.linear_cross_entropy(x.detach(), w2, tgt, V, fp8, chunk_rows=256).backward()
+    assert w2.grad is None
+    _check(w2.main_grad, 0.5 * wr.grad, tol, "head gradient in the fp32 buffer")
