@@ -711,6 +711,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
   m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums) -> ()", &allreduce_adamw);
   m.def("gemm_pair_capacity() -> int", []() -> int64_t { return gd::gemm_pair_capacity(); });
+  m.def("gemm_set_mx_pair(int on) -> ()", [](int64_t on) { gd::gemm_set_mx_pair((int)on); });
   m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> ()", &register_grad_sink);
   m.def("clear_grad_sinks() -> ()", &clear_grad_sinks);
   m.def("peer_add(Tensor(a!) dst, Tensor src) -> ()", &peer_add);

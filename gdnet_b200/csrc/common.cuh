@@ -314,6 +314,23 @@ __device__ __forceinline__ void mma_bf16_pair(uint32_t d_tmem, uint64_t adesc, u
       : "memory");
 }
 
+// Block-scaled e4m3 MMA over the CTA pair: D is 256 rows (128 per CTA); each CTA reads its scale factors from its
+// own TMEM at the given column addresses.
+__device__ __forceinline__ void mma_mxfp8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// Scale-factor copy in both CTAs of the pair: each copies the chunk at this offset of its own shared memory
+// into its own TMEM.
+__device__ __forceinline__ void tmem_cp_scales_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 // One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair once every MMA issued so
 // far by this thread is done (a signal to two barriers, not a data transfer).
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {

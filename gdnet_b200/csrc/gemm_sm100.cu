@@ -974,6 +974,44 @@ constexpr int MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 2 * MX_SF_BYTES;   // 3
 constexpr int MX_TMEM_COLS = 512;
 constexpr int MX_SF_COL0 = MX_ACC * MX_BN;                                   // scale columns follow the accumulators
 
+// e4m3 copy of one epilogue warp's 32 rows x 64 columns (va: columns nq..nq+31 of row m_warp + lane, vb: the next
+// 32), one power-of-two scale per row, for the GEMM that consumes this output as its A operand. The values are
+// the bf16-rounded outputs (after silu when q8_silu is set). Warp-collective.
+__device__ __forceinline__ void mx_emit_q8(const GemmEpilogue& e, int M, int m_warp, int nq, int lane, int col_half,
+                                           float (&va)[32], float (&vb)[32], uint8_t* stage) {
+  const int m = m_warp + lane;
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x0 = __bfloat162float(__float2bfloat16(va[j])), x1 = __bfloat162float(__float2bfloat16(vb[j]));
+    if (e.q8_silu) {
+      x0 = __bfloat162float(__float2bfloat16(siluf_(x0)));
+      x1 = __bfloat162float(__float2bfloat16(siluf_(x1)));
+    }
+    va[j] = x0;
+    vb[j] = x1;
+    amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
+  }
+  const float sc = block_scale(amax, 1);
+  const float inv = 1.0f / sc;
+  uint32_t w[16];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    w[t] = (uint32_t)to_e4m3(va[4 * t] * inv) | ((uint32_t)to_e4m3(va[4 * t + 1] * inv) << 8) |
+           ((uint32_t)to_e4m3(va[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(va[4 * t + 3] * inv) << 24);
+    w[8 + t] = (uint32_t)to_e4m3(vb[4 * t] * inv) | ((uint32_t)to_e4m3(vb[4 * t + 1] * inv) << 8) |
+               ((uint32_t)to_e4m3(vb[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(vb[4 * t + 3] * inv) << 24);
+  }
+  // 32 rows x 64 bytes through the staging area (same shape as a 32-column bf16 chunk)
+  store_rows_bf16(stage, lane, w, reinterpret_cast<__nv_bfloat16*>(e.q8 + (size_t)m_warp * e.q8_ld + nq),
+                  e.q8_ld / 2, min(32, M - m_warp));
+  if (m < M) {
+    uint8_t* chunk = e.q8_p + ((int64_t)(m >> 7) * e.q8_p_stride + (nq >> 7)) * 512;
+    *reinterpret_cast<uint16_t*>(chunk + (m & 31) * 16 + ((m >> 5) & 3) * 4 + col_half * 2) =
+        (uint16_t)(ue8m0_word(sc) & 0xFFFFu);
+  }
+}
+
 template <bool AUX>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -1135,40 +1173,8 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                                  aux_row, 0);
       ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, vb, stage, bias1,
                             aux_row, 4);
-      if (e.q8 != nullptr && m0 + quarter * 32 < g.M && n0 + col_half * 64 < g.N) {
-        // e4m3 copy of this warp's 32 rows x 64 columns, one power-of-two scale per row
-        float amax = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x0 = __bfloat162float(__float2bfloat16(va[j])), x1 = __bfloat162float(__float2bfloat16(vb[j]));
-          if (e.q8_silu) {
-            x0 = __bfloat162float(__float2bfloat16(siluf_(x0)));
-            x1 = __bfloat162float(__float2bfloat16(siluf_(x1)));
-          }
-          va[j] = x0;
-          vb[j] = x1;
-          amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
-        }
-        const float sc = block_scale(amax, 1);
-        const float inv = 1.0f / sc;
-        uint32_t w[16];
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          w[t] = (uint32_t)to_e4m3(va[4 * t] * inv) | ((uint32_t)to_e4m3(va[4 * t + 1] * inv) << 8) |
-                 ((uint32_t)to_e4m3(va[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(va[4 * t + 3] * inv) << 24);
-          w[8 + t] = (uint32_t)to_e4m3(vb[4 * t] * inv) | ((uint32_t)to_e4m3(vb[4 * t + 1] * inv) << 8) |
-                     ((uint32_t)to_e4m3(vb[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(vb[4 * t + 3] * inv) << 24);
-        }
-        // 32 rows x 64 bytes through the staging area (same shape as a 32-column bf16 chunk)
-        const int m_warp = m0 + quarter * 32, nq = n0 + col_half * 64;
-        store_rows_bf16(stage, lane, w, reinterpret_cast<__nv_bfloat16*>(e.q8 + (size_t)m_warp * e.q8_ld + nq),
-                        e.q8_ld / 2, min(32, g.M - m_warp));
-        if (m < g.M) {
-          uint8_t* chunk = e.q8_p + ((int64_t)(m >> 7) * e.q8_p_stride + (nq >> 7)) * 512;
-          *reinterpret_cast<uint16_t*>(chunk + (m & 31) * 16 + ((m >> 5) & 3) * 4 + col_half * 2) =
-              (uint16_t)(ue8m0_word(sc) & 0xFFFFu);
-        }
-      }
+      if (e.q8 != nullptr && m0 + quarter * 32 < g.M && n0 + col_half * 64 < g.N)
+        mx_emit_q8(e, g.M, m0 + quarter * 32, n0 + col_half * 64, lane, col_half, va, vb, stage);
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
       if (AUX) {   // this tile's slice is consumed: fetch the next tile's
@@ -1186,6 +1192,243 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
   }
   pipe_teardown(bars, warp, MX_TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------
+// hardware block-scaled FP8 kernel on CTA pairs
+// ---------------------------------------------------------------------------------------
+// The single-CTA kernel above is bound by the shared-memory fill: a 128 x 128 tile needs 32 KB of operands per
+// 128-deep K block, the ring holds about 200 KB, and at the latency of a loaded L2 that caps the rate at which
+// stages turn over. Here one MMA spans two CTAs (tcgen05 cta_group::2, 256 x 128 pair tile): each CTA loads its
+// own 128 rows of A and 64 of the 128 rows of B, 24 KB per K block for the same 128 x 128 of output, so a ring
+// of the same size feeds a third more math. Every CTA needs the scale factors of its own A rows and of all 128
+// B rows in its own TMEM; both load the B chunk, and the leader's tcgen05.cp copies them in both CTAs. All
+// loads count their bytes on the leader's barrier (the cta_group::2 form of the tiled load, which no
+// plain bulk copy has: the scale chunks are therefore fetched through a tensor map over 256-byte rows).
+constexpr int MXP_B_ROWS = MX_BN / 2;
+constexpr int MXP_B_BYTES = MXP_B_ROWS * STAGE_ROW_BYTES;
+constexpr int MXP_STAGE_BYTES = MX_A_BYTES + MXP_B_BYTES + 2 * MX_SF_BYTES;   // 25 KB, a multiple of 1024
+constexpr int MXP_STAGES_PLAIN = 8;
+constexpr int MXP_STAGES_AUX = 7;
+
+template <bool AUX>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                        const __grid_constant__ CUtensorMap tmap_aux, const GemmShape g, const GemmEpilogue e,
+                        Status* status) {
+  constexpr int STAGES = AUX ? MXP_STAGES_AUX : MXP_STAGES_PLAIN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_all = smem + STAGES * MXP_STAGE_BYTES;
+  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES;
+  PipeBars* bars = reinterpret_cast<PipeBars*>(aux_all + (AUX ? MX_AUX_BYTES : 0));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < MX_ACC; ++a) {
+      mbar_init(smem_u32(&bars->tmem_full[a]), 1);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), 2 * EPI_WARPS);
+    }
+    for (int w = 0; w < EPI_WARPS; ++w) mbar_init(smem_u32(&bars->aux_full[w]), 1);
+    bars->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&bars->tmem_base), MX_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();     // the peer's barriers exist before anything of this CTA can signal them
+  tc_fence_after_sync();
+  pdl_enter();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int n_tiles_n = g.N / MX_BN;
+  const int n_tiles_m = g.M / (2 * BM);
+  const int n_tiles = n_tiles_m * n_tiles_n;
+  const int kblocks = g.K / MX_BK;
+  const uint32_t smem0 = smem_u32(smem);
+  const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
+  const uint32_t tfull0 = smem_u32(&bars->tmem_full[0]), tempty0 = smem_u32(&bars->tmem_empty[0]);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t full_lead0 = map_to_cta(full0, 0);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        int mb_, nb_;
+        tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+        const int mblk = mb_ * 2 + (int)rank;                       // this CTA's 128-row block of A
+        const int m0 = mblk * BM, nB = nb_ * MX_BN + (int)rank * MXP_B_ROWS;
+        int sfa_row = mblk * kblocks * 2, sfb_row = nb_ * kblocks * 2;   // 256-byte rows of the packed scale arrays
+        int kx = 0;
+        for (int kb = 0; kb < kblocks; ++kb, kx += MX_BK, sfa_row += 2, sfb_row += 2) {
+          if (!wait_fast(empty0 + 8 * s, ph ^ 1)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 70, s);
+            ok = false;
+            break;
+          }
+          const uint32_t full = full_lead0 + 8 * s;
+          const uint32_t a_dst = smem0 + s * MXP_STAGE_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * MXP_STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &tmap_a, full, kx, m0);
+          tma_load_2d_pair(a_dst + MX_A_BYTES, &tmap_b, full, kx, nB);
+          tma_load_2d_pair(a_dst + MX_A_BYTES + MXP_B_BYTES, &tmap_sfa, full, 0, sfa_row);
+          tma_load_2d_pair(a_dst + MX_A_BYTES + MXP_B_BYTES + MX_SF_BYTES, &tmap_sfb, full, 0, sfb_row);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (aborted(bars)) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_instr_desc_mx(2 * BM, MX_BN, 0, 0);
+      const uint64_t a_tmpl = make_smem_desc(smem0, 16, 1024), b_tmpl = make_smem_desc(smem0 + MX_A_BYTES, 16, 1024);
+      const uint64_t sfa_tmpl = make_smem_desc_noswizzle(smem0 + MX_A_BYTES + MXP_B_BYTES, 16, 128);
+      const uint32_t a_hi = (uint32_t)(a_tmpl >> 32), a_lo0 = (uint32_t)a_tmpl;
+      const uint32_t b_hi = (uint32_t)(b_tmpl >> 32), b_lo0 = (uint32_t)b_tmpl;
+      const uint32_t sf_hi = (uint32_t)(sfa_tmpl >> 32), sf_lo0 = (uint32_t)sfa_tmpl;
+      int s = 0, acc = 0, slot = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        if (!wait_fast(tempty0 + 8 * acc, acc_ph ^ 1)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 71, acc);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * MX_BN;
+        uint32_t accumulate = 0;
+        for (int i = 0; i < kblocks; ++i) {
+          if (!wait_fast(full0 + 8 * s, ph)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 72, s);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t off = s * (MXP_STAGE_BYTES >> 4);
+          const uint32_t sfa_t = tmem_base + MX_SF_COL0 + slot * 8, sfb_t = sfa_t + 4;
+          tmem_cp_scales_pair(sfa_t, desc_at(sf_hi, sf_lo0 + off));
+          tmem_cp_scales_pair(sfb_t, desc_at(sf_hi, sf_lo0 + off + (MX_SF_BYTES >> 4)));
+#pragma unroll
+          for (int k = 0; k < MX_BK / 32; ++k) {
+            mma_mxfp8_pair(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2), idesc,
+                           accumulate, sfa_t, sfb_t);
+            accumulate = 1;
+          }
+          mma_commit_pair(empty0 + 8 * s);
+          slot ^= 1;
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok || aborted(bars)) break;
+        mma_commit_pair(tfull0 + 8 * acc);
+        if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
+    const int quarter = warp & 3;
+    const int col_half = ew >> 2;        // which 64 of the tile's 128 columns
+    const uint32_t tempty_lead0 = map_to_cta(tempty0, 0);
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    uint8_t* aux_buf = aux_all + ew * AUX_BOX_BYTES;
+    const uint32_t aux_bar = smem_u32(&bars->aux_full[ew]);
+    uint32_t aux_ph = 0;
+    bool aux_pending = false;
+    if (AUX && pair < n_tiles) {
+      int mb_, nb_;
+      tile_coords(pair, n_tiles_m, n_tiles_n, mb_, nb_);
+      aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, (mb_ * 2 + (int)rank) * BM + quarter * 32, lane,
+                                 nb_ * MX_BN + col_half * 64, 1, smem_u32(aux_buf), aux_bar);
+    }
+    for (int tile = pair; tile < n_tiles && !aborted(bars); tile += n_pairs) {
+      int mb_, nb_;
+      tile_coords(tile, n_tiles_m, n_tiles_n, mb_, nb_);
+      const int m0 = (mb_ * 2 + (int)rank) * BM, n0 = nb_ * MX_BN;
+      const int m = m0 + quarter * 32 + lane;
+      const float rs = (m < g.M) ? row_scale_for(e, m) : 1.0f;
+      const float rc = (e.rowcoef != nullptr && m < g.M) ? e.rowcoef[m] : 0.0f;
+      const float bias0 = load_bias(e, n0 + col_half * 64 + lane, g.N);
+      const float bias1 = load_bias(e, n0 + col_half * 64 + 32 + lane, g.N);
+      if (!mbar_wait_warp(tfull0 + 8 * acc, acc_ph)) {
+        raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 73, acc);
+        break;
+      }
+      if (AUX && aux_pending) {
+        if (!mbar_wait_warp(aux_bar, aux_ph)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 74, ew);
+          break;
+        }
+        aux_ph ^= 1;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * MX_BN + col_half * 64;
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(t_row, r0);
+      tmem_ld_32x32(t_row + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_lead0 + 8 * acc);
+      float va[32], vb[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        va[j] = __uint_as_float(r0[j]);
+        vb[j] = __uint_as_float(r1[j]);
+      }
+      const uint8_t* aux_row = AUX ? aux_buf + lane * 128 : nullptr;
+      float ssq = epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64, rs, rc, va, stage, bias0,
+                                 aux_row, 0);
+      ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, vb, stage, bias1,
+                            aux_row, 4);
+      if (e.q8 != nullptr) mx_emit_q8(e, g.M, m0 + quarter * 32, n0 + col_half * 64, lane, col_half, va, vb, stage);
+      if (e.ssq_out != nullptr && m < g.M)
+        e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
+      if (AUX) {   // this tile's slice is consumed: fetch the next tile's
+        __syncwarp();
+        aux_pending = false;
+        const int next = tile + n_pairs;
+        if (next < n_tiles) {
+          int mb2, nb2;
+          tile_coords(next, n_tiles_m, n_tiles_n, mb2, nb2);
+          aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, (mb2 * 2 + (int)rank) * BM + quarter * 32, lane,
+                                     nb2 * MX_BN + col_half * 64, 1, smem_u32(aux_buf), aux_bar);
+        }
+      }
+      if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  // teardown: neither CTA may leave (or free its TMEM) while the other can still read its shared memory,
+  // write its TMEM or signal its barriers
+  tc_fence_before_sync();
+  __syncthreads();
+  if (aborted(bars)) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, MX_TMEM_COLS);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1223,6 +1466,22 @@ const char* make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_byte
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
+}
+
+// Packed UE8M0 scale chunks (512 bytes each, n_chunks of them back to back) as a tensor of 256-byte rows: a box
+// of two rows is one chunk and lands in shared memory exactly as it lies in global memory (no swizzle).
+static const char* make_tensor_map_chunks(CUtensorMap* out, const void* base, int64_t n_chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return "cuTensorMapEncodeTiled entry point not found";
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return "packed scales are not 16-byte aligned";
+  cuuint64_t dims[2] = {256, (cuuint64_t)(n_chunks * 2)};
+  cuuint64_t strides[1] = {256};
+  cuuint32_t box[2] = {256, 2};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed (scale chunks)";
 }
 
 static int sm_count() {
@@ -1405,10 +1664,73 @@ const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const Ge
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_kernel launch failed";
 }
 
+static int g_mx_pair = -1;   // -1: take GDNET_MX_PAIR from the environment on first use
+
+void gemm_set_mx_pair(int on) { g_mx_pair = on ? 1 : 0; }
+
+static bool mx_pair_enabled() {
+  if (g_mx_pair < 0) {
+    const char* v = getenv("GDNET_MX_PAIR");
+    g_mx_pair = (v != nullptr && v[0] == '1') ? 1 : 0;
+  }
+  return g_mx_pair == 1 && pair_kernels_enabled();
+}
+
+// CTA-pair form of the hardware-scaled FP8 GEMM (256 x 128 pair tiles). *launched stays false when pairs cannot
+// be launched on this device; the caller then uses the single-CTA kernel.
+static const char* launch_gemm_fp8_mx_pair(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e,
+                                           Status* status, cudaStream_t stream, bool* launched) {
+  *launched = false;
+  static int pairs_plain = -1, pairs_aux = -1;
+  const bool aux = e.aux != nullptr;
+  const int smem_plain = MXP_STAGES_PLAIN * MXP_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_aux = MXP_STAGES_AUX * MXP_STAGE_BYTES + EPI_STAGE_BYTES + MX_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
+  if (pairs_plain < 0) {
+    pairs_plain = pairs_aux = 0;
+    if (cudaFuncSetAttribute(gemm_fp8_mx_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) == cudaSuccess &&
+        cudaFuncSetAttribute(gemm_fp8_mx_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_aux) == cudaSuccess) {
+      pairs_plain = max_active_pairs(gemm_fp8_mx_pair_kernel<false>, smem_plain);
+      pairs_aux = max_active_pairs(gemm_fp8_mx_pair_kernel<true>, smem_aux);
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  const int max_pairs = aux ? pairs_aux : pairs_plain;
+  if (max_pairs < 1) return nullptr;
+  CUtensorMap ta, tb, tsa, tsb, tx;
+  const char* err;
+  if ((err = make_tensor_map_2d(&ta, op.a, 1, g.M, g.K, op.a_ld, BM)) != nullptr) return err;
+  if ((err = make_tensor_map_2d(&tb, op.b, 1, g.N, g.K, op.b_ld, MXP_B_ROWS)) != nullptr) return err;
+  const int64_t kblocks = g.K / MX_BK;
+  if ((err = make_tensor_map_chunks(&tsa, g.sfa_packed, (g.M / BM) * kblocks)) != nullptr) return err;
+  if ((err = make_tensor_map_chunks(&tsb, g.sfb_packed, (g.N / MX_BN) * kblocks)) != nullptr) return err;
+  const int tiles = (g.M / (2 * BM)) * (g.N / MX_BN);
+  GemmShape gs = g;
+  GemmEpilogue es = e;
+  gs.splits = 1;
+  es.atomic = 0;
+  const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
+  if (aux) {
+    if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
+    launch_pdl(gemm_fp8_mx_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tsa, tsb, tx, gs, es,
+               status);
+  } else {
+    launch_pdl(gemm_fp8_mx_pair_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem_plain, stream, ta, tb, tsa, tsb, ta, gs,
+               es, status);
+  }
+  *launched = true;
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_mx_pair_kernel launch failed";
+}
+
 const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
                                cudaStream_t stream) {
   if (g.K % 128 != 0 || g.N % 128 != 0 || g.M % 128 != 0) return "hardware-scaled fp8 GEMM needs M, N, K % 128 == 0";
   if (g.sfa_packed == nullptr || g.sfb_packed == nullptr) return "hardware-scaled fp8 GEMM needs packed scales";
+  if (mx_pair_enabled() && g.M % (2 * BM) == 0 && pick_splits((g.M / BM) * (g.N / MX_BN), g.K / MX_BK, e) == 1) {
+    bool launched = false;
+    const char* perr = launch_gemm_fp8_mx_pair(op, g, e, status, stream, &launched);
+    if (perr != nullptr || launched) return perr;
+  }
   CUtensorMap ta, tb;
   const char* err = make_tensor_map_2d(&ta, op.a, 1, g.M, g.K, op.a_ld, BM);
   if (err) return err;

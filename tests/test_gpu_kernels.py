@@ -278,3 +278,32 @@ def test_gemm_fp8_mx_quantised_output():
                    store_out=False)
     torch.cuda.synchronize()
     assert torch.equal(q8b.view(torch.uint8), q8.view(torch.uint8)) and torch.equal(p8b, p8)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 128), (512, 384, 1024), (4096, 1024, 2048)])
+def test_gemm_fp8_mx_pair_matches_single_cta(M, N, K):
+    """The CTA-pair form (256 x 128 pair tiles, scale chunks fetched through a tensor map) against the single-CTA
+    kernel on the same operands, plain and with bias + auxiliary add + quantised output."""
+    cu = _cu()
+    a8, sa, b8, sb = _mx_operands(M, N, K, True)
+    pa, pb = ref.pack_ue8m0_rows(sa), ref.pack_ue8m0_blocks(sb)
+    bias = torch.randn(N, device=DEV)
+    aux = torch.randn(M, N, device=DEV).bfloat16()
+    res = {}
+    try:
+        for pair in (0, 1):
+            cu.K.gemm_set_mx_pair(pair)
+            plain = cu.gemm_fp8_mx(a8, pa, b8, pb, out_dtype=torch.float32)
+            q8 = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=DEV)
+            p8 = cu.packed_buffer(M, N, DEV).zero_()
+            fused = cu.gemm_fp8_mx(a8, pa, b8, pb, bias=bias, aux=aux, aux_mode=1, q8=q8, q8_p=p8)
+            torch.cuda.synchronize()
+            _status_clean(a8)
+            res[pair] = (plain, fused, q8.view(torch.uint8).clone(), p8.clone())
+    finally:
+        cu.K.gemm_set_mx_pair(0)
+    want = ref.fp8_gemm_blockscaled(a8, sa, b8, sb, out_dtype=torch.float32)
+    _close(res[1][0], want, 1e-2 * float(want.abs().max()) * 1e-2 + 1e-3, 2e-3, f"mx pair gemm {M}x{N}x{K}")
+    _close(res[1][0], res[0][0], 1e-5 * float(want.abs().max()), 1e-5, "pair against single CTA")
+    _close(res[1][1].float(), res[0][1].float(), 1e-2 * float(want.abs().max()), 1e-2, "pair against single CTA, fused epilogue")
+    assert (res[1][2] != res[0][2]).float().mean() < 1e-3 and torch.equal(res[1][3], res[0][3])
