@@ -151,6 +151,20 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// One lane of a converged warp (all 32 lanes must call it). The producer and MMA loops run warp-wide with
+// uniform control flow and only the instruction that starts an asynchronous operation sits behind this
+// predicate: loop counters, shared-memory addresses and descriptors then stay warp-uniform values, which the
+// bulk-copy and tensor-core instructions take directly. Inside `if (lane == 0)` the same values are per-thread
+// values that have to be moved over for every operand of every instruction, which made each issue cost
+// 100-200 cycles of the single thread.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // TMA: tiled bulk tensor loads into this CTA's shared memory
 // ---------------------------------------------------------------------------------------

@@ -1264,7 +1264,7 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const uint32_t tfull0 = smem_u32(&bars->tmem_full[0]), tempty0 = smem_u32(&bars->tmem_empty[0]);
 
   if (warp == 0) {
-    if (lane == 0) {
+    {   // all 32 lanes run the loop; one elected lane issues the loads
       const uint32_t full_lead0 = map_to_cta(full0, 0);
       int s = 0;
       uint32_t ph = 0;
@@ -1277,25 +1277,28 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         int sfa_row = mblk * kblocks * 2, sfb_row = nb_ * kblocks * 2;   // 256-byte rows of the packed scale arrays
         int kx = 0;
         for (int kb = 0; kb < kblocks; ++kb, kx += MX_BK, sfa_row += 2, sfb_row += 2) {
-          if (!wait_fast(empty0 + 8 * s, ph ^ 1)) {
-            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 70, s);
+          if (!__all_sync(0xffffffffu, wait_fast(empty0 + 8 * s, ph ^ 1))) {
+            if (lane == 0) raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 70, s);
             ok = false;
             break;
           }
           const uint32_t full = full_lead0 + 8 * s;
           const uint32_t a_dst = smem0 + s * MXP_STAGE_BYTES;
-          if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * MXP_STAGE_BYTES);
-          tma_load_2d_pair(a_dst, &tmap_a, full, kx, m0);
-          tma_load_2d_pair(a_dst + MX_A_BYTES, &tmap_b, full, kx, nB);
-          tma_load_2d_pair(a_dst + MX_A_BYTES + MXP_B_BYTES, &tmap_sfa, full, 0, sfa_row);
-          tma_load_2d_pair(a_dst + MX_A_BYTES + MXP_B_BYTES + MX_SF_BYTES, &tmap_sfb, full, 0, sfb_row);
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * MXP_STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &tmap_a, full, kx, m0);
+            tma_load_2d_pair(a_dst + MX_A_BYTES, &tmap_b, full, kx, nB);
+            tma_load_2d_pair(a_dst + MX_A_BYTES + MXP_B_BYTES, &tmap_sfa, full, 0, sfa_row);
+            tma_load_2d_pair(a_dst + MX_A_BYTES + MXP_B_BYTES + MX_SF_BYTES, &tmap_sfb, full, 0, sfb_row);
+          }
+          __syncwarp();
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (aborted(bars)) break;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {   // the leader's warp runs the loop with all lanes; one elected lane issues
       const uint32_t idesc = make_instr_desc_mx(2 * BM, MX_BN, 0, 0);
       const uint64_t a_tmpl = make_smem_desc(smem0, 16, 1024), b_tmpl = make_smem_desc(smem0 + MX_A_BYTES, 16, 1024);
       const uint64_t sfa_tmpl = make_smem_desc_noswizzle(smem0 + MX_A_BYTES + MXP_B_BYTES, 16, 128);
@@ -1306,36 +1309,39 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       uint32_t ph = 0, acc_ph = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-        if (!wait_fast(tempty0 + 8 * acc, acc_ph ^ 1)) {
-          raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 71, acc);
+        if (!__all_sync(0xffffffffu, wait_fast(tempty0 + 8 * acc, acc_ph ^ 1))) {
+          if (lane == 0) raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 71, acc);
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * MX_BN;
         uint32_t accumulate = 0;
         for (int i = 0; i < kblocks; ++i) {
-          if (!wait_fast(full0 + 8 * s, ph)) {
-            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 72, s);
+          if (!__all_sync(0xffffffffu, wait_fast(full0 + 8 * s, ph))) {
+            if (lane == 0) raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 72, s);
             ok = false;
             break;
           }
           tc_fence_after_sync();
           const uint32_t off = s * (MXP_STAGE_BYTES >> 4);
           const uint32_t sfa_t = tmem_base + MX_SF_COL0 + slot * 8, sfb_t = sfa_t + 4;
-          tmem_cp_scales_pair(sfa_t, desc_at(sf_hi, sf_lo0 + off));
-          tmem_cp_scales_pair(sfb_t, desc_at(sf_hi, sf_lo0 + off + (MX_SF_BYTES >> 4)));
+          if (elect_one()) {
+            tmem_cp_scales_pair(sfa_t, desc_at(sf_hi, sf_lo0 + off));
+            tmem_cp_scales_pair(sfb_t, desc_at(sf_hi, sf_lo0 + off + (MX_SF_BYTES >> 4)));
 #pragma unroll
-          for (int k = 0; k < MX_BK / 32; ++k) {
-            mma_mxfp8_pair(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2), idesc,
-                           accumulate, sfa_t, sfb_t);
-            accumulate = 1;
+            for (int k = 0; k < MX_BK / 32; ++k)
+              mma_mxfp8_pair(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2), idesc,
+                             (k == 0) ? accumulate : 1u, sfa_t, sfb_t);
+            mma_commit_pair(empty0 + 8 * s);
           }
-          mma_commit_pair(empty0 + 8 * s);
+          __syncwarp();
+          accumulate = 1;
           slot ^= 1;
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok || aborted(bars)) break;
-        mma_commit_pair(tfull0 + 8 * acc);
+        if (elect_one()) mma_commit_pair(tfull0 + 8 * acc);
+        __syncwarp();
         if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
       }
     }
@@ -1671,7 +1677,7 @@ void gemm_set_mx_pair(int on) { g_mx_pair = on ? 1 : 0; }
 static bool mx_pair_enabled() {
   if (g_mx_pair < 0) {
     const char* v = getenv("GDNET_MX_PAIR");
-    g_mx_pair = (v != nullptr && v[0] == '1') ? 1 : 0;
+    g_mx_pair = (v == nullptr || v[0] != '0') ? 1 : 0;
   }
   return g_mx_pair == 1 && pair_kernels_enabled();
 }

@@ -86,8 +86,7 @@ const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const Ge
 // pair kernels cannot be launched and the single-CTA kernels are used instead.
 int gemm_pair_capacity();
 
-// Use (1) or bypass (0) the CTA-pair form of the hardware-scaled FP8 GEMM; default from GDNET_MX_PAIR (off unless it is 1: measured level with the
-// single-CTA kernel on the layer shapes).
+// Use (1) or bypass (0) the CTA-pair form of the hardware-scaled FP8 GEMM; default from GDNET_MX_PAIR (on unless it is 0).
 void gemm_set_mx_pair(int on);
 
 }  // namespace gd

@@ -301,7 +301,7 @@ def test_gemm_fp8_mx_pair_matches_single_cta(M, N, K):
             _status_clean(a8)
             res[pair] = (plain, fused, q8.view(torch.uint8).clone(), p8.clone())
     finally:
-        cu.K.gemm_set_mx_pair(0)
+        cu.K.gemm_set_mx_pair(1)
     want = ref.fp8_gemm_blockscaled(a8, sa, b8, sb, out_dtype=torch.float32)
     _close(res[1][0], want, 1e-2 * float(want.abs().max()) * 1e-2 + 1e-3, 2e-3, f"mx pair gemm {M}x{N}x{K}")
     _close(res[1][0], res[0][0], 1e-5 * float(want.abs().max()), 1e-5, "pair against single CTA")
