@@ -85,6 +85,46 @@ def main():
             lambda i: cu.gemm_fp8_mx(g8[i][2], g8[i][3], ut8[i][0], ut8[i][2], out=dw2[i], accumulate=True)),
     }
 
+    # the same GEMMs with the epilogues the fused layer step gives them
+    FP8 = torch.float8_e4m3fn
+    q8s = [torch.empty(M, d, dtype=FP8, device=dev) for _ in range(R)]
+    p8s = [cu.packed_buffer(M, d, dev) for _ in range(R)]
+    ssq = [torch.empty(M, (d + 127) // 128, dtype=f32, device=dev) for _ in range(R)]
+    rowc = torch.zeros(M, dtype=f32, device=dev)
+    variants.update({
+        "mx   fprop  (M,2d)x(2d,d) bias+silu+pre_out+q8 (train)": (
+            4.0 * M * d * d,
+            lambda i: cu.gemm_fp8_mx(u8[i][0], u8[i][2], qwr[i].q, qwr[i].p, out=outs[i], bias=bias,
+                                     pre_out=outs[(i + 1) % R], act=cu.ACT_SILU, q8=q8s[i], q8_p=p8s[i])),
+        "mx   fprop  (M,2d)x(2d,d) bias+q8(silu) only (no-grad)": (
+            4.0 * M * d * d,
+            lambda i: cu.gemm_fp8_mx(u8[i][0], u8[i][2], qwr[i].q, qwr[i].p, out=outs[i], bias=bias, q8=q8s[i],
+                                     q8_p=p8s[i], q8_silu=True, store_out=False)),
+        "mx   fprop  (M,d)x(d,d)  bias": (
+            2.0 * M * d * d, lambda i: cu.gemm_fp8_mx(a8[i][0], a8[i][2], qw[i].q, qw[i].p, out=outs[i], bias=bias)),
+        "mx   dgrad  (M,d)x(d,d)  aux silu' + q8": (
+            2.0 * M * d * d,
+            lambda i: cu.gemm_fp8_mx(g8[i][0], g8[i][1], qw[i].qt, qw[i].pt, out=outs[i], aux=acts[i],
+                                     aux_mode=cu.AUX_MUL_SILU_GRAD, q8=q8s[i], q8_p=p8s[i])),
+        "bf16 fprop  (M,d)x(d,d)  bias+silu+pre_out+ssq_out (train)": (
+            2.0 * M * d * d,
+            lambda i: cu.gemm_bf16(acts[i], w1[i], out=outs[i], bias=bias, pre_out=outs[(i + 1) % R], act=cu.ACT_SILU,
+                                   ssq_out=ssq[i])),
+        "bf16 fprop  (M,d)x(d,d)  bias+silu+ssq_out (no-grad)": (
+            2.0 * M * d * d,
+            lambda i: cu.gemm_bf16(acts[i], w1[i], out=outs[i], bias=bias, act=cu.ACT_SILU, ssq_out=ssq[i])),
+        "bf16 fprop  (M,d)x(d,d)  bias + row scale from ssq": (
+            2.0 * M * d * d,
+            lambda i: cu.gemm_bf16(acts[i], w1[i], out=outs[i], bias=bias, ssq_in=ssq[i], norm_dim=d, norm_eps=1e-6)),
+        "bf16 dgrad  (M,d)x(d,d)  aux rms/silu backward": (
+            2.0 * M * d * d,
+            lambda i: cu.gemm_bf16(grads[i], w1[i], b_mn=True, out=outs[i], aux=acts[i],
+                                   aux_mode=cu.AUX_RMS_SILU_BWD, rowcoef=rowc)),
+        "bf16 dgrad  (M,d)x(d,d)  aux add in place": (
+            2.0 * M * d * d,
+            lambda i: cu.gemm_bf16(grads[i], w1[i], b_mn=True, out=outs[i], aux=outs[i], aux_mode=cu.AUX_ADD)),
+    })
+
     results = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for name, (flops, fn) in variants.items():

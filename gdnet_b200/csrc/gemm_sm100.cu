@@ -42,7 +42,7 @@ struct __align__(8) PipeBars {
   uint64_t empty[8];
   uint64_t tmem_full[4];
   uint64_t tmem_empty[4];
-  uint64_t aux_full[8];    // one per epilogue warp: its slice of the next tile's auxiliary input has landed
+  uint64_t aux_full[32];   // up to four per epilogue warp: a slice of the next tile's auxiliary input has landed
   uint32_t tmem_base;
   int abort;
 };
@@ -92,6 +92,21 @@ __device__ __forceinline__ bool aux_prefetch(const CUtensorMap* tmap, int M, int
     for (int b = 0; b < boxes; ++b) tma_load_2d(buf + b * AUX_BOX_BYTES, tmap, bar, nbase + b * 64, m_warp);
   }
   return true;
+}
+
+// One chunk of the auxiliary matrix (32 rows x 32 bf16 columns, 2 KB, 64-byte swizzle) into a slot of its own with
+// a barrier of its own. A slot is asked for again as soon as its chunk has been consumed, so every chunk of the next
+// tile has a whole tile's time to arrive (a request made only when the whole tile was done left the epilogue waiting
+// out the memory latency at the start of every tile once the epilogue, not the main loop, set the pace). Rows or
+// columns outside the matrix read as zero. Warp-collective.
+constexpr int AUX_CHUNK_BYTES = 32 * 64;
+
+__device__ __forceinline__ void aux_request(const CUtensorMap* tmap, int m_warp, int ncol, uint32_t slot, uint32_t bar) {
+  if (elect_one()) {
+    mbar_arrive_expect_tx(bar, (uint32_t)AUX_CHUNK_BYTES);
+    tma_load_2d(slot, tmap, bar, ncol, m_warp);
+  }
+  __syncwarp();
 }
 
 __device__ __forceinline__ float row_scale_for(const GemmEpilogue& e, int m) {
@@ -160,7 +175,8 @@ __device__ __forceinline__ void load_rows_bf16(uint8_t* stage, int lane, uint32_
 // null to read the auxiliary values from global memory here.
 __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, int N, int m_warp, int lane, int n0,
                                                 float rs, float rowcoef, float (&v)[32], uint8_t* stage,
-                                                float bias_lane, const uint8_t* aux_row, int aux_piece0) {
+                                                float bias_lane, const uint8_t* aux_row, int aux_piece0,
+                                                bool aux64 = false) {
   float ssq = 0.0f;
   if (m_warp >= M || n0 >= N) return 0.0f;   // warp-uniform
   const int m = m_warp + lane;
@@ -178,25 +194,37 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
     if (aux_row != nullptr) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint4 u = *reinterpret_cast<const uint4*>(aux_row + (((aux_piece0 + q) ^ (lane & 7)) << 4));
+        // aux64: a box of 32 rows x 64 bytes of its own per chunk (64-byte swizzle), aux_row = this lane's row
+        const int piece = aux64 ? (q ^ ((lane >> 1) & 3)) : ((aux_piece0 + q) ^ (lane & 7));
+        const uint4 u = *reinterpret_cast<const uint4*>(aux_row + (piece << 4));
         w[q * 4] = u.x; w[q * 4 + 1] = u.y; w[q * 4 + 2] = u.z; w[q * 4 + 3] = u.w;
       }
     } else {
       load_rows_bf16(stage, lane, w, e.aux + (size_t)m_warp * e.aux_ld + n0, e.aux_ld, rows_valid);
     }
+    // one loop per mode (the mode is the same for the whole launch): with the test inside the loop the compiler
+    // evaluated all three forms for every element and selected, so a plain add paid for two sigmoids
+    if (e.aux_mode == AUX_ADD) {
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const float2 a = unpack_bf16x2(w[t]);
-      const int j = t * 2;
-      if (e.aux_mode == AUX_ADD) {
-        v[j] += a.x;
-        v[j + 1] += a.y;
-      } else if (e.aux_mode == AUX_MUL_SILU_GRAD) {
-        v[j] *= silu_grad_(a.x);
-        v[j + 1] *= silu_grad_(a.y);
-      } else {  // AUX_RMS_SILU_BWD: (v - silu(aux) * rowcoef) * silu'(aux)
-        v[j] = (v[j] - siluf_(a.x) * rowcoef) * silu_grad_(a.x);
-        v[j + 1] = (v[j + 1] - siluf_(a.y) * rowcoef) * silu_grad_(a.y);
+      for (int t = 0; t < 16; ++t) {
+        const float2 a = unpack_bf16x2(w[t]);
+        v[2 * t] += a.x;
+        v[2 * t + 1] += a.y;
+      }
+    } else if (e.aux_mode == AUX_MUL_SILU_GRAD) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const float2 a = unpack_bf16x2(w[t]);
+        v[2 * t] *= silu_grad_(a.x);
+        v[2 * t + 1] *= silu_grad_(a.y);
+      }
+    } else {  // AUX_RMS_SILU_BWD: (v - silu(aux) * rowcoef) * silu'(aux)
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const float2 a = unpack_bf16x2(w[t]);
+        const float s0 = sigmoidf_(a.x), s1 = sigmoidf_(a.y);
+        v[2 * t] = (v[2 * t] - a.x * s0 * rowcoef) * (s0 * (1.0f + a.x * (1.0f - s0)));
+        v[2 * t + 1] = (v[2 * t + 1] - a.y * s1 * rowcoef) * (s1 * (1.0f + a.y * (1.0f - s1)));
       }
     }
   }
@@ -578,7 +606,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       mbar_init(smem_u32(&bars->tmem_full[a]), 1);
       mbar_init(smem_u32(&bars->tmem_empty[a]), 2 * EPI_WARPS);
     }
-    for (int w = 0; w < EPI_WARPS; ++w) mbar_init(smem_u32(&bars->aux_full[w]), 1);
+    for (int w = 0; w < 4 * EPI_WARPS; ++w) mbar_init(smem_u32(&bars->aux_full[w]), 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -604,7 +632,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t tfull0 = smem_u32(&bars->tmem_full[0]), tempty0 = smem_u32(&bars->tmem_empty[0]);
 
   if (warp == 0) {
-    if (lane == 0) {
+    {   // all 32 lanes run the loop; one elected lane issues the loads (see elect_one)
       const uint32_t full_lead0 = map_to_cta(full0, 0);
       int s = 0;
       uint32_t ph = 0;
@@ -616,36 +644,39 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int m0 = mb_ * 2 * BM + (int)rank * BM, nB = nb_ * PAIR_BN + (int)rank * PAIR_B_ROWS;
         int kx = kb0 * BF16_BK;
         for (int kb = kb0; kb < kb1; ++kb, kx += BF16_BK) {
-          if (!wait_fast(empty0 + 8 * s, ph ^ 1)) {
-            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 60, s);
+          if (!__all_sync(0xffffffffu, wait_fast(empty0 + 8 * s, ph ^ 1))) {
+            if (lane == 0) raise_abort(bars, status, STATUS_TIMEOUT_SMEM_EMPTY, 60, s);
             ok = false;
             break;
           }
           const uint32_t full = full_lead0 + 8 * s;
           const uint32_t a_dst = smem0 + s * PAIR_STAGE_BYTES;
           const uint32_t b_dst = a_dst + PAIR_A_BYTES;
-          if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
-          if (!g.a_mn) {
-            tma_load_2d_pair(a_dst, &tmap_a, full, kx, m0);
-          } else {
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
+            if (!g.a_mn) {
+              tma_load_2d_pair(a_dst, &tmap_a, full, kx, m0);
+            } else {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i)
-              tma_load_2d_pair(a_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_a, full, m0 + i * 64, kx);
-          }
-          if (!g.b_mn) {
-            tma_load_2d_pair(b_dst, &tmap_b, full, kx, nB);
-          } else {
+              for (int i = 0; i < BM / 64; ++i)
+                tma_load_2d_pair(a_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_a, full, m0 + i * 64, kx);
+            }
+            if (!g.b_mn) {
+              tma_load_2d_pair(b_dst, &tmap_b, full, kx, nB);
+            } else {
 #pragma unroll
-            for (int i = 0; i < PAIR_B_ROWS / 64; ++i)
-              tma_load_2d_pair(b_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_b, full, nB + i * 64, kx);
+              for (int i = 0; i < PAIR_B_ROWS / 64; ++i)
+                tma_load_2d_pair(b_dst + i * (BF16_BK * STAGE_ROW_BYTES), &tmap_b, full, nB + i * 64, kx);
+            }
           }
+          __syncwarp();
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (aborted(bars)) break;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {   // the leader's warp runs the loop with all lanes; one elected lane issues
       const uint32_t idesc = make_instr_desc(1, 1, g.a_mn ? 1 : 0, g.b_mn ? 1 : 0, 2 * BM, PAIR_BN);
       const uint32_t a_lbo = g.a_mn ? BF16_BK * STAGE_ROW_BYTES : 16, b_lbo = g.b_mn ? BF16_BK * STAGE_ROW_BYTES : 16;
       const uint32_t a_step = g.a_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2, b_step = g.b_mn ? (16 * STAGE_ROW_BYTES) >> 4 : 2;
@@ -657,31 +688,35 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = true;
       for (int work = pair; work < n_work && ok; work += n_pairs) {
         const int nkb = min(kblocks, (work / n_tiles) * kb_per + kb_per) - (work / n_tiles) * kb_per;
-        if (!wait_fast(tempty0 + 8 * acc, acc_ph ^ 1)) {
-          raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 61, acc);
+        if (!__all_sync(0xffffffffu, wait_fast(tempty0 + 8 * acc, acc_ph ^ 1))) {
+          if (lane == 0) raise_abort(bars, status, STATUS_TIMEOUT_TMEM_EMPTY, 61, acc);
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
         uint32_t accumulate = 0;
         for (int i = 0; i < nkb; ++i) {
-          if (!wait_fast(full0 + 8 * s, ph)) {
-            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 62, s);
+          if (!__all_sync(0xffffffffu, wait_fast(full0 + 8 * s, ph))) {
+            if (lane == 0) raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 62, s);
             ok = false;
             break;
           }
           tc_fence_after_sync();
           const uint32_t a_lo = a_lo0 + s * (PAIR_STAGE_BYTES >> 4), b_lo = b_lo0 + s * (PAIR_STAGE_BYTES >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BF16_BK / 16; ++k) {
-            mma_bf16_pair(d_tmem, desc_at(a_hi, a_lo + k * a_step), desc_at(b_hi, b_lo + k * b_step), idesc, accumulate);
-            accumulate = 1;
+            for (int k = 0; k < BF16_BK / 16; ++k)
+              mma_bf16_pair(d_tmem, desc_at(a_hi, a_lo + k * a_step), desc_at(b_hi, b_lo + k * b_step), idesc,
+                            (k == 0) ? accumulate : 1u);
+            mma_commit_pair(empty0 + 8 * s);
           }
-          mma_commit_pair(empty0 + 8 * s);
+          __syncwarp();
+          accumulate = 1;
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok || aborted(bars)) break;
-        mma_commit_pair(tfull0 + 8 * acc);
+        if (elect_one()) mma_commit_pair(tfull0 + 8 * acc);
+        __syncwarp();
         if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
       }
     }
@@ -693,15 +728,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t tempty_lead0 = map_to_cta(tempty0, 0);
     int acc = 0;
     uint32_t acc_ph = 0;
-    uint8_t* aux_buf = aux_all + ew * (2 * AUX_BOX_BYTES);
-    const uint32_t aux_bar = smem_u32(&bars->aux_full[ew]);
+    const uint32_t aux_slot0 = smem_u32(aux_all + ew * (4 * AUX_CHUNK_BYTES));   // four chunk slots per warp
+    const uint8_t* aux_mine = aux_all + ew * (4 * AUX_CHUNK_BYTES) + lane * 64;
+    const uint32_t aux_bar0 = smem_u32(&bars->aux_full[ew * 4]);
     uint32_t aux_ph = 0;
-    bool aux_pending = false;
+    bool aux_ok = true;
     if (AUX && pair < n_work) {
       int mb_, nb_;
       tile_coords(pair % n_tiles, n_tiles_m, n_tiles_n, mb_, nb_);
-      aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb_ * 2 * BM + (int)rank * BM + quarter * 32, lane,
-                                 nb_ * PAIR_BN + col_half * 128, 2, smem_u32(aux_buf), aux_bar);
+      for (int c = 0; c < 4; ++c)
+        aux_request(&tmap_aux, mb_ * 2 * BM + (int)rank * BM + quarter * 32, nb_ * PAIR_BN + col_half * 128 + c * 32,
+                    aux_slot0 + c * AUX_CHUNK_BYTES, aux_bar0 + 8 * c);
     }
     for (int work = pair; work < n_work && !aborted(bars); work += n_pairs) {
       const int tile = work % n_tiles;
@@ -718,12 +755,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 63, acc);
         break;
       }
-      if (AUX && aux_pending) {
-        if (!mbar_wait_warp(aux_bar, aux_ph)) {
-          raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 64, ew);
-          break;
-        }
-        aux_ph ^= 1;
+      // where the next tile's chunks go (a slot is asked for again as soon as its chunk has been read)
+      const int next = work + n_pairs;
+      int m_next = 0, n_next = 0;
+      if (AUX && next < n_work) {
+        int mb2, nb2;
+        tile_coords(next % n_tiles, n_tiles_m, n_tiles_n, mb2, nb2);
+        m_next = mb2 * 2 * BM + (int)rank * BM + quarter * 32;
+        n_next = nb2 * PAIR_BN + col_half * 128;
       }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * PAIR_BN + col_half * 128;
@@ -736,8 +775,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        if (AUX && aux_ok && !mbar_wait_warp(aux_bar0 + 8 * c, aux_ph)) {
+          raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 64, ew);
+          aux_ok = false;
+        }
         ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage, bias,
-                              AUX ? aux_buf + (c >> 1) * AUX_BOX_BYTES + lane * 128 : nullptr, (c & 1) * 4);
+                              AUX ? aux_mine + c * AUX_CHUNK_BYTES : nullptr, 0, true);
+        if (AUX && aux_ok && next < n_work) {
+          __syncwarp();
+          aux_request(&tmap_aux, m_next, n_next + c * 32, aux_slot0 + c * AUX_CHUNK_BYTES, aux_bar0 + 8 * c);
+        }
       };
       tmem_ld_32x32(t_row, raw0);
 #pragma unroll 1
@@ -755,17 +802,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         do_chunk(raw1, 2 * cc + 1, cc ? bias_c[3] : bias_c[1]);
       }
-      if (AUX) {
-        __syncwarp();
-        aux_pending = false;
-        const int next = work + n_pairs;
-        if (next < n_work) {
-          int mb2, nb2;
-          tile_coords(next % n_tiles, n_tiles_m, n_tiles_n, mb2, nb2);
-          aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, mb2 * 2 * BM + (int)rank * BM + quarter * 32, lane,
-                                     nb2 * PAIR_BN + col_half * 128, 2, smem_u32(aux_buf), aux_bar);
-        }
-      }
+      aux_ph ^= 1;
+      if (!aux_ok) break;
       if (e.ssq_out != nullptr && m < g.M && n0 + col_half * 128 < g.N)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 128 + col_half)] = ssq;
       if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
@@ -981,13 +1019,16 @@ __device__ __forceinline__ void mx_emit_q8(const GemmEpilogue& e, int M, int m_w
                                            float (&va)[32], float (&vb)[32], uint8_t* stage) {
   const int m = m_warp + lane;
   float amax = 0.0f;
+  if (e.q8_silu) {   // tested once, not per element (see the auxiliary modes in epilogue_chunk)
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      va[j] = siluf_(__bfloat162float(__float2bfloat16(va[j])));
+      vb[j] = siluf_(__bfloat162float(__float2bfloat16(vb[j])));
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    float x0 = __bfloat162float(__float2bfloat16(va[j])), x1 = __bfloat162float(__float2bfloat16(vb[j]));
-    if (e.q8_silu) {
-      x0 = __bfloat162float(__float2bfloat16(siluf_(x0)));
-      x1 = __bfloat162float(__float2bfloat16(siluf_(x1)));
-    }
+    const float x0 = __bfloat162float(__float2bfloat16(va[j])), x1 = __bfloat162float(__float2bfloat16(vb[j]));
     va[j] = x0;
     vb[j] = x1;
     amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
@@ -1240,7 +1281,7 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       mbar_init(smem_u32(&bars->tmem_full[a]), 1);
       mbar_init(smem_u32(&bars->tmem_empty[a]), 2 * EPI_WARPS);
     }
-    for (int w = 0; w < EPI_WARPS; ++w) mbar_init(smem_u32(&bars->aux_full[w]), 1);
+    for (int w = 0; w < 4 * EPI_WARPS; ++w) mbar_init(smem_u32(&bars->aux_full[w]), 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -1353,15 +1394,16 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const uint32_t tempty_lead0 = map_to_cta(tempty0, 0);
     int acc = 0;
     uint32_t acc_ph = 0;
-    uint8_t* aux_buf = aux_all + ew * AUX_BOX_BYTES;
-    const uint32_t aux_bar = smem_u32(&bars->aux_full[ew]);
+    const uint32_t aux_slot0 = smem_u32(aux_all + ew * (2 * AUX_CHUNK_BYTES));   // two chunk slots per warp
+    const uint8_t* aux_mine = aux_all + ew * (2 * AUX_CHUNK_BYTES) + lane * 64;
+    const uint32_t aux_bar0 = smem_u32(&bars->aux_full[ew * 4]);
     uint32_t aux_ph = 0;
-    bool aux_pending = false;
     if (AUX && pair < n_tiles) {
       int mb_, nb_;
       tile_coords(pair, n_tiles_m, n_tiles_n, mb_, nb_);
-      aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, (mb_ * 2 + (int)rank) * BM + quarter * 32, lane,
-                                 nb_ * MX_BN + col_half * 64, 1, smem_u32(aux_buf), aux_bar);
+      for (int c = 0; c < 2; ++c)
+        aux_request(&tmap_aux, (mb_ * 2 + (int)rank) * BM + quarter * 32, nb_ * MX_BN + col_half * 64 + c * 32,
+                    aux_slot0 + c * AUX_CHUNK_BYTES, aux_bar0 + 8 * c);
     }
     for (int tile = pair; tile < n_tiles && !aborted(bars); tile += n_pairs) {
       int mb_, nb_;
@@ -1375,13 +1417,6 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       if (!mbar_wait_warp(tfull0 + 8 * acc, acc_ph)) {
         raise_abort(bars, status, STATUS_TIMEOUT_TMEM_FULL, 73, acc);
         break;
-      }
-      if (AUX && aux_pending) {
-        if (!mbar_wait_warp(aux_bar, aux_ph)) {
-          raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 74, ew);
-          break;
-        }
-        aux_ph ^= 1;
       }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * MX_BN + col_half * 64;
@@ -1398,25 +1433,38 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         va[j] = __uint_as_float(r0[j]);
         vb[j] = __uint_as_float(r1[j]);
       }
-      const uint8_t* aux_row = AUX ? aux_buf + lane * 128 : nullptr;
-      float ssq = epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64, rs, rc, va, stage, bias0,
-                                 aux_row, 0);
-      ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + 32, rs, rc, vb, stage, bias1,
-                            aux_row, 4);
+      // where the next tile's chunks go (the slots are asked for again as soon as they have been read)
+      const int next = tile + n_pairs;
+      int m_next = 0, n_next = 0;
+      if (AUX && next < n_tiles) {
+        int mb2, nb2;
+        tile_coords(next, n_tiles_m, n_tiles_n, mb2, nb2);
+        m_next = (mb2 * 2 + (int)rank) * BM + quarter * 32;
+        n_next = nb2 * MX_BN + col_half * 64;
+      }
+      float ssq = 0.0f;
+      bool aux_ok = true;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (AUX) {
+          if (!mbar_wait_warp(aux_bar0 + 8 * c, aux_ph)) {
+            raise_abort(bars, status, STATUS_TIMEOUT_SMEM_FULL, 74, ew);
+            aux_ok = false;
+            break;
+          }
+        }
+        ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + c * 32, rs, rc, c ? vb : va, stage,
+                              c ? bias1 : bias0, AUX ? aux_mine + c * AUX_CHUNK_BYTES : nullptr, 0, true);
+        if (AUX && next < n_tiles) {
+          __syncwarp();
+          aux_request(&tmap_aux, m_next, n_next + c * 32, aux_slot0 + c * AUX_CHUNK_BYTES, aux_bar0 + 8 * c);
+        }
+      }
+      if (!aux_ok) break;
+      aux_ph ^= 1;
       if (e.q8 != nullptr) mx_emit_q8(e, g.M, m0 + quarter * 32, n0 + col_half * 64, lane, col_half, va, vb, stage);
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
-      if (AUX) {   // this tile's slice is consumed: fetch the next tile's
-        __syncwarp();
-        aux_pending = false;
-        const int next = tile + n_pairs;
-        if (next < n_tiles) {
-          int mb2, nb2;
-          tile_coords(next, n_tiles_m, n_tiles_n, mb2, nb2);
-          aux_pending = aux_prefetch(&tmap_aux, g.M, g.N, (mb2 * 2 + (int)rank) * BM + quarter * 32, lane,
-                                     nb2 * MX_BN + col_half * 64, 1, smem_u32(aux_buf), aux_bar);
-        }
-      }
       if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
     }
   }
@@ -1472,6 +1520,23 @@ const char* make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_byte
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
+}
+
+// The auxiliary matrix [rows][cols] bf16 as boxes of 32 rows x 32 columns (64 bytes, 64-byte swizzle): one box per
+// epilogue chunk (see aux_request).
+static const char* make_tensor_map_aux64(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return "cuTensorMapEncodeTiled entry point not found";
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return "auxiliary matrix is not 16-byte aligned";
+  if ((ld * 2) % 16 != 0) return "auxiliary row pitch is not a multiple of 16 bytes";
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld * 2)};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed (auxiliary matrix)";
 }
 
 // Packed UE8M0 scale chunks (512 bytes each, n_chunks of them back to back) as a tensor of 256-byte rows: a box
@@ -1581,7 +1646,7 @@ static const char* launch_gemm_bf16_pair(const GemmOperands& op, const GemmShape
   const int work = tiles * gs.splits;
   const int grid = 2 * (work < max_pairs ? work : max_pairs);
   if (aux) {
-    if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
+    if ((err = make_tensor_map_aux64(&tx, e.aux, g.M, g.N, e.aux_ld)) != nullptr) return err;
     launch_pdl(gemm_bf16_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tx, gs, es, status);
   } else {
     launch_pdl(gemm_bf16_pair_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem_plain, stream, ta, tb, ta, gs, es, status);
@@ -1717,7 +1782,7 @@ static const char* launch_gemm_fp8_mx_pair(const GemmOperands& op, const GemmSha
   es.atomic = 0;
   const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
   if (aux) {
-    if ((err = make_tensor_map_2d(&tx, e.aux, 2, g.M, g.N, e.aux_ld, 32)) != nullptr) return err;
+    if ((err = make_tensor_map_aux64(&tx, e.aux, g.M, g.N, e.aux_ld)) != nullptr) return err;
     launch_pdl(gemm_fp8_mx_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tsa, tsb, tx, gs, es,
                status);
   } else {
