@@ -406,7 +406,14 @@ __host__ __device__ constexpr uint32_t make_instr_desc(uint32_t fmt_a, uint32_t 
 // ---------------------------------------------------------------------------------------
 // small math helpers
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// sigmoid(x) = 0.5 + 0.5 tanh(x / 2): one special-function operation (tanh.approx, relative error about 2^-11)
+// instead of two (exp and reciprocal). The fused epilogues and the gate kernels evaluate one or two sigmoids per
+// element and the special-function unit issues 16 results per cycle per SM, which made it their bottleneck.
+__device__ __forceinline__ float sigmoidf_(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
 __device__ __forceinline__ float siluf_(float x) { return x * sigmoidf_(x); }
 __device__ __forceinline__ float silu_grad_(float x) {
   const float s = sigmoidf_(x);
