@@ -213,6 +213,7 @@ void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT
     TORCH_CHECK((e.pre_ld * 2) % 16 == 0, "pre_out rows must be 16-byte aligned");
   }
   e.act = (int)act;
+  e.tma_mask = 0;   // chosen by the launcher
   e.ssq_out = nullptr;
   if (ssq_out.has_value()) {
     TORCH_CHECK(ssq_out->dim() == 2 && ssq_out->size(0) == M && ssq_out->is_contiguous(), "ssq_out must be (M, parts)");

@@ -131,8 +131,35 @@ __device__ __forceinline__ uint32_t stage_off(int row, int slot) {
 }
 
 // this lane's row (32 bf16 in w) -> global rows base[row * ld + 0..31], rows < rows_valid
+// The staging area may still be the source of a bulk store issued by this warp's elected lane (store_rows_tma):
+// that lane waits until the store has read it before anyone overwrites it. Warp-collective.
+__device__ __forceinline__ void stage_acquire() {
+  if (elect_one()) bulk_wait_read_all();
+  __syncwarp();
+}
+
+// this lane's row (32 bf16, or 64 e4m3, in w) -> the box of 32 rows x 64 bytes at column x (elements), row m_warp of
+// the tensor behind tmap, as one tiled bulk store: the rows are laid down in the staging area in the 64-byte-swizzle
+// order and an elected lane hands them to the copy engine, so the warp neither reads them back nor issues the
+// global stores itself. Rows and columns outside the tensor are clipped by the copy. Warp-collective.
+__device__ __forceinline__ void store_rows_tma(uint8_t* stage, int lane, const uint32_t (&w)[16], const CUtensorMap* tmap,
+                                               int x, int m_warp) {
+  stage_acquire();
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    *reinterpret_cast<uint4*>(stage + stage_off(lane, q)) = make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (elect_one()) {
+    tma_store_2d(tmap, smem_u32(stage), x, m_warp);
+    bulk_commit_group();
+  }
+  __syncwarp();
+}
+
 __device__ __forceinline__ void store_rows_bf16(uint8_t* stage, int lane, const uint32_t (&w)[16],
                                                 __nv_bfloat16* base, int64_t ld, int rows_valid) {
+  stage_acquire();
 #pragma unroll
   for (int q = 0; q < 4; ++q)
     *reinterpret_cast<uint4*>(stage + stage_off(lane, q)) = make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
@@ -150,6 +177,7 @@ __device__ __forceinline__ void store_rows_bf16(uint8_t* stage, int lane, const 
 // global rows base[row * ld + 0..31] -> this lane's row in w (rows >= rows_valid read as zero)
 __device__ __forceinline__ void load_rows_bf16(uint8_t* stage, int lane, uint32_t (&w)[16],
                                                const __nv_bfloat16* base, int64_t ld, int rows_valid) {
+  stage_acquire();
   const int r_in = lane >> 2, slot = lane & 3;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -176,7 +204,8 @@ __device__ __forceinline__ void load_rows_bf16(uint8_t* stage, int lane, uint32_
 __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, int N, int m_warp, int lane, int n0,
                                                 float rs, float rowcoef, float (&v)[32], uint8_t* stage,
                                                 float bias_lane, const uint8_t* aux_row, int aux_piece0,
-                                                bool aux64 = false) {
+                                                bool aux64 = false, const CUtensorMap* t_out = nullptr,
+                                                const CUtensorMap* t_pre = nullptr) {
   float ssq = 0.0f;
   if (m_warp >= M || n0 >= N) return 0.0f;   // warp-uniform
   const int m = m_warp + lane;
@@ -233,7 +262,8 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
     uint32_t w[16];
 #pragma unroll
     for (int t = 0; t < 16; ++t) w[t] = pack_bf16x2(v[t * 2], v[t * 2 + 1]);
-    store_rows_bf16(stage, lane, w, e.pre_out + (size_t)m_warp * e.pre_ld + n0, e.pre_ld, rows_valid);
+    if (t_pre != nullptr) store_rows_tma(stage, lane, w, t_pre, n0, m_warp);
+    else store_rows_bf16(stage, lane, w, e.pre_out + (size_t)m_warp * e.pre_ld + n0, e.pre_ld, rows_valid);
   }
 
   if (e.act == ACT_SILU) {
@@ -285,7 +315,8 @@ __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, in
         ssq += r.x * r.x + r.y * r.y;
       }
     }
-    store_rows_bf16(stage, lane, w, ob, e.out_ld, rows_valid);
+    if (t_out != nullptr) store_rows_tma(stage, lane, w, t_out, n0, m_warp);
+    else store_rows_bf16(stage, lane, w, ob, e.out_ld, rows_valid);
   }
   return ssq;
 }
@@ -583,7 +614,8 @@ constexpr int PAIR_TMEM_COLS = BF16_ACC * PAIR_BN;
 template <bool AUX>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_aux, const GemmShape g, const GemmEpilogue e,
+                      const __grid_constant__ CUtensorMap tmap_aux, const __grid_constant__ CUtensorMap tmap_out,
+                      const __grid_constant__ CUtensorMap tmap_pre, const GemmShape g, const GemmEpilogue e,
                       Status* status) {
   constexpr int STAGES = AUX ? 4 : 6;
   extern __shared__ uint8_t smem_raw[];
@@ -780,7 +812,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           aux_ok = false;
         }
         ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 128 + c * 32, rs, rc, v, stage, bias,
-                              AUX ? aux_mine + c * AUX_CHUNK_BYTES : nullptr, 0, true);
+                              AUX ? aux_mine + c * AUX_CHUNK_BYTES : nullptr, 0, true,
+                              (e.tma_mask & 1) ? &tmap_out : nullptr, (e.tma_mask & 2) ? &tmap_pre : nullptr);
         if (AUX && aux_ok && next < n_work) {
           __syncwarp();
           aux_request(&tmap_aux, m_next, n_next + c * 32, aux_slot0 + c * AUX_CHUNK_BYTES, aux_bar0 + 8 * c);
@@ -808,6 +841,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 128 + col_half)] = ssq;
       if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
     }
+    stage_acquire();   // the last bulk stores have read the staging area
   }
 
   // teardown: neither CTA may leave (or free its TMEM) while the other can still read its shared memory,
@@ -1016,7 +1050,8 @@ constexpr int MX_SF_COL0 = MX_ACC * MX_BN;                                   // 
 // 32), one power-of-two scale per row, for the GEMM that consumes this output as its A operand. The values are
 // the bf16-rounded outputs (after silu when q8_silu is set). Warp-collective.
 __device__ __forceinline__ void mx_emit_q8(const GemmEpilogue& e, int M, int m_warp, int nq, int lane, int col_half,
-                                           float (&va)[32], float (&vb)[32], uint8_t* stage) {
+                                           float (&va)[32], float (&vb)[32], uint8_t* stage,
+                                           const CUtensorMap* t_q8 = nullptr) {
   const int m = m_warp + lane;
   float amax = 0.0f;
   if (e.q8_silu) {   // tested once, not per element (see the auxiliary modes in epilogue_chunk)
@@ -1044,8 +1079,11 @@ __device__ __forceinline__ void mx_emit_q8(const GemmEpilogue& e, int M, int m_w
                ((uint32_t)to_e4m3(vb[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(vb[4 * t + 3] * inv) << 24);
   }
   // 32 rows x 64 bytes through the staging area (same shape as a 32-column bf16 chunk)
-  store_rows_bf16(stage, lane, w, reinterpret_cast<__nv_bfloat16*>(e.q8 + (size_t)m_warp * e.q8_ld + nq),
-                  e.q8_ld / 2, min(32, M - m_warp));
+  if (t_q8 != nullptr)
+    store_rows_tma(stage, lane, w, t_q8, nq, m_warp);
+  else
+    store_rows_bf16(stage, lane, w, reinterpret_cast<__nv_bfloat16*>(e.q8 + (size_t)m_warp * e.q8_ld + nq),
+                    e.q8_ld / 2, min(32, M - m_warp));
   if (m < M) {
     uint8_t* chunk = e.q8_p + ((int64_t)(m >> 7) * e.q8_p_stride + (nq >> 7)) * 512;
     *reinterpret_cast<uint16_t*>(chunk + (m & 31) * 16 + ((m >> 5) & 3) * 4 + col_half * 2) =
@@ -1256,8 +1294,9 @@ template <bool AUX>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                        const __grid_constant__ CUtensorMap tmap_aux, const GemmShape g, const GemmEpilogue e,
-                        Status* status) {
+                        const __grid_constant__ CUtensorMap tmap_aux, const __grid_constant__ CUtensorMap tmap_out,
+                        const __grid_constant__ CUtensorMap tmap_pre, const __grid_constant__ CUtensorMap tmap_q8,
+                        const GemmShape g, const GemmEpilogue e, Status* status) {
   constexpr int STAGES = AUX ? MXP_STAGES_AUX : MXP_STAGES_PLAIN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1454,7 +1493,8 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           }
         }
         ssq += epilogue_chunk(e, g.M, g.N, m0 + quarter * 32, lane, n0 + col_half * 64 + c * 32, rs, rc, c ? vb : va, stage,
-                              c ? bias1 : bias0, AUX ? aux_mine + c * AUX_CHUNK_BYTES : nullptr, 0, true);
+                              c ? bias1 : bias0, AUX ? aux_mine + c * AUX_CHUNK_BYTES : nullptr, 0, true,
+                              (e.tma_mask & 1) ? &tmap_out : nullptr, (e.tma_mask & 2) ? &tmap_pre : nullptr);
         if (AUX && next < n_tiles) {
           __syncwarp();
           aux_request(&tmap_aux, m_next, n_next + c * 32, aux_slot0 + c * AUX_CHUNK_BYTES, aux_bar0 + 8 * c);
@@ -1462,11 +1502,14 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
       if (!aux_ok) break;
       aux_ph ^= 1;
-      if (e.q8 != nullptr) mx_emit_q8(e, g.M, m0 + quarter * 32, n0 + col_half * 64, lane, col_half, va, vb, stage);
+      if (e.q8 != nullptr)
+        mx_emit_q8(e, g.M, m0 + quarter * 32, n0 + col_half * 64, lane, col_half, va, vb, stage,
+                   (e.tma_mask & 4) ? &tmap_q8 : nullptr);
       if (e.ssq_out != nullptr && m < g.M)
         e.ssq_out[(size_t)m * e.ssq_parts + (n0 / 64 + col_half)] = ssq;
       if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
     }
+    stage_acquire();   // the last bulk stores have read the staging area
   }
 
   // teardown: neither CTA may leave (or free its TMEM) while the other can still read its shared memory,
@@ -1522,21 +1565,44 @@ const char* make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_byte
   return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
 }
 
-// The auxiliary matrix [rows][cols] bf16 as boxes of 32 rows x 32 columns (64 bytes, 64-byte swizzle): one box per
-// epilogue chunk (see aux_request).
-static const char* make_tensor_map_aux64(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+// A row-major matrix [rows][cols] (bf16, or bytes with elem_bytes = 1) as boxes of 32 rows x 64 bytes with the 64-byte
+// swizzle: the unit of the epilogue's auxiliary loads (aux_request) and bulk stores (store_rows_tma).
+static const char* make_tensor_map_box64(CUtensorMap* out, const void* base, int elem_bytes, int64_t rows, int64_t cols,
+                                         int64_t ld) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return "cuTensorMapEncodeTiled entry point not found";
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return "auxiliary matrix is not 16-byte aligned";
-  if ((ld * 2) % 16 != 0) return "auxiliary row pitch is not a multiple of 16 bytes";
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return "matrix is not 16-byte aligned";
+  if ((ld * elem_bytes) % 16 != 0) return "row pitch is not a multiple of 16 bytes";
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)(ld * 2)};
-  cuuint32_t box[2] = {32, 32};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld * elem_bytes)};
+  cuuint32_t box[2] = {(cuuint32_t)(64 / elem_bytes), 32};
   cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed (auxiliary matrix)";
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed (64-byte boxes)";
+}
+
+static const char* make_tensor_map_aux64(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+  return make_tensor_map_box64(out, base, 2, rows, cols, ld);
+}
+
+// Tensor maps for the outputs that can leave through bulk stores (bf16 out without accumulation, pre_out, q8);
+// sets es.tma_mask. An output whose base or pitch does not meet the 16-byte rules simply keeps the plain stores.
+static void make_store_maps(const GemmShape& g, GemmEpilogue& es, CUtensorMap* t_out, CUtensorMap* t_pre, CUtensorMap* t_q8) {
+  es.tma_mask = 0;
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("GDNET_TMA_STORE");
+    on = (v == nullptr || v[0] != '0') ? 1 : 0;
+  }
+  if (!on) return;
+  if (es.out != nullptr && !es.out_f32 && !es.accumulate &&
+      make_tensor_map_box64(t_out, es.out, 2, g.M, g.N, es.out_ld) == nullptr)
+    es.tma_mask |= 1;
+  if (es.pre_out != nullptr && make_tensor_map_box64(t_pre, es.pre_out, 2, g.M, g.N, es.pre_ld) == nullptr)
+    es.tma_mask |= 2;
+  if (es.q8 != nullptr && make_tensor_map_box64(t_q8, es.q8, 1, g.M, g.N, es.q8_ld) == nullptr) es.tma_mask |= 4;
 }
 
 // Packed UE8M0 scale chunks (512 bytes each, n_chunks of them back to back) as a tensor of 256-byte rows: a box
@@ -1643,13 +1709,15 @@ static const char* launch_gemm_bf16_pair(const GemmOperands& op, const GemmShape
   GemmEpilogue es = e;
   gs.splits = pick_splits(tiles * 2, (g.K + BF16_BK - 1) / BF16_BK, e);
   es.atomic = gs.splits > 1;
+  CUtensorMap to = ta, tp = ta, tq = ta;
+  make_store_maps(g, es, &to, &tp, &tq);
   const int work = tiles * gs.splits;
   const int grid = 2 * (work < max_pairs ? work : max_pairs);
   if (aux) {
     if ((err = make_tensor_map_aux64(&tx, e.aux, g.M, g.N, e.aux_ld)) != nullptr) return err;
-    launch_pdl(gemm_bf16_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tx, gs, es, status);
+    launch_pdl(gemm_bf16_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tx, to, tp, gs, es, status);
   } else {
-    launch_pdl(gemm_bf16_pair_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem_plain, stream, ta, tb, ta, gs, es, status);
+    launch_pdl(gemm_bf16_pair_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem_plain, stream, ta, tb, ta, to, tp, gs, es, status);
   }
   *launched = true;
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_bf16_pair_kernel launch failed";
@@ -1780,14 +1848,16 @@ static const char* launch_gemm_fp8_mx_pair(const GemmOperands& op, const GemmSha
   GemmEpilogue es = e;
   gs.splits = 1;
   es.atomic = 0;
+  CUtensorMap to = ta, tp = ta, tq = ta;
+  make_store_maps(g, es, &to, &tp, &tq);
   const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
   if (aux) {
     if ((err = make_tensor_map_aux64(&tx, e.aux, g.M, g.N, e.aux_ld)) != nullptr) return err;
-    launch_pdl(gemm_fp8_mx_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tsa, tsb, tx, gs, es,
-               status);
-  } else {
-    launch_pdl(gemm_fp8_mx_pair_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem_plain, stream, ta, tb, tsa, tsb, ta, gs,
+    launch_pdl(gemm_fp8_mx_pair_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem_aux, stream, ta, tb, tsa, tsb, tx, to, tp, tq, gs,
                es, status);
+  } else {
+    launch_pdl(gemm_fp8_mx_pair_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem_plain, stream, ta, tb, tsa, tsb, ta, to, tp, tq,
+               gs, es, status);
   }
   *launched = true;
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_mx_pair_kernel launch failed";

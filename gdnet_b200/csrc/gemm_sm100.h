@@ -73,6 +73,7 @@ struct GemmEpilogue {
   int64_t pre_ld;
   int act;
   float* ssq_out;           // [M][ssq_parts]: per-row partial sums of squares of the stored values
+  int tma_mask;             // set by the launcher: bit 0 out, bit 1 pre_out, bit 2 q8 leave through tiled bulk stores
 };
 
 const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const GemmEpilogue& e, Status* status,
