@@ -457,6 +457,20 @@ __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
+// Four values -> four e4m3 bytes (a in the lowest byte), two conversions of a pair each: same rounding and
+// saturation as to_e4m3, half the conversion instructions and no byte shuffling.
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// Eight values times inv -> eight e4m3 bytes as they lie in memory.
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&v)[8], float inv) {
+  return make_uint2(pack4_e4m3(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                    pack4_e4m3(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+}
+
 // ---------------------------------------------------------------------------------------
 // programmatic dependent launch
 // ---------------------------------------------------------------------------------------
@@ -512,11 +526,8 @@ __device__ __forceinline__ void quant_emit_8(const RowQuantOut& o, const float (
   for (int off = 8; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(group, m, off));
   const float sc = block_scale(m, 1);
   const float inv = 1.0f / sc;
-  uint8_t q[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[i] * inv);
   if (!live) return;
-  *reinterpret_cast<uint2*>(o.q + r * o.q_ld + c) = *reinterpret_cast<uint2*>(q);
+  *reinterpret_cast<uint2*>(o.q + r * o.q_ld + c) = pack8_e4m3(v, inv);
   if ((threadIdx.x & 15) == 0) {
     o.s[(int64_t)(c >> 7) * o.s_ld + r] = sc;
     store_packed_scale(o.p, (r >> 7) * o.p_stride + (c >> 7), (int)(r & 127), ue8m0_word(sc));

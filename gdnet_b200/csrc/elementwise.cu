@@ -788,10 +788,7 @@ quant_tile_kernel(const QuantArgs a) {
       const float sc = block_scale(rmax, a.pow2);
       const float inv = 1.0f / sc;
       if (r < a.rows && c < a.cols) {
-        uint8_t q[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[p][i] * inv);
-        store_all(a, reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c), *reinterpret_cast<uint2*>(q));
+        store_all(a, reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c), pack8_e4m3(v[p], inv));
         if ((tid & 15) == 0) {
           store_all(a, a.s_row + (int64_t)blockIdx.x * a.s_row_ld + r, sc);
           if (a.p_row != nullptr)
@@ -825,10 +822,7 @@ quant_tile_kernel(const QuantArgs a) {
     for (int p = 0; p < 8; ++p) {
       const int64_t r = r0 + tr * 8 + p;
       if (r < a.rows && c < a.cols) {
-        uint8_t q[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[p][i] * inv);
-        store_all(a, reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c), *reinterpret_cast<uint2*>(q));
+        store_all(a, reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c), pack8_e4m3(v[p], inv));
       }
     }
     if (tid == 0) store_all(a, a.s_row + (int64_t)blockIdx.y * n_cb + blockIdx.x, tile_scale);
@@ -899,11 +893,8 @@ quant_rows_kernel(const QuantArgs a) {
   for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   const float sc = block_scale(m, a.pow2);
   const float inv = 1.0f / sc;
-  uint8_t q[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = to_e4m3(v[i] * inv);
   if (!live) return;
-  *reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c) = *reinterpret_cast<uint2*>(q);
+  *reinterpret_cast<uint2*>(a.q_row + r * a.q_row_ld + c) = pack8_e4m3(v, inv);
   if ((threadIdx.x & 15) == 0) {
     a.s_row[(int64_t)(c >> 7) * a.s_row_ld + r] = sc;
     if (a.p_row != nullptr)

@@ -1080,10 +1080,8 @@ __device__ __forceinline__ void mx_emit_q8(const GemmEpilogue& e, int M, int m_w
   uint32_t w[16];
 #pragma unroll
   for (int t = 0; t < 8; ++t) {
-    w[t] = (uint32_t)to_e4m3(va[4 * t] * inv) | ((uint32_t)to_e4m3(va[4 * t + 1] * inv) << 8) |
-           ((uint32_t)to_e4m3(va[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(va[4 * t + 3] * inv) << 24);
-    w[8 + t] = (uint32_t)to_e4m3(vb[4 * t] * inv) | ((uint32_t)to_e4m3(vb[4 * t + 1] * inv) << 8) |
-               ((uint32_t)to_e4m3(vb[4 * t + 2] * inv) << 16) | ((uint32_t)to_e4m3(vb[4 * t + 3] * inv) << 24);
+    w[t] = pack4_e4m3(va[4 * t] * inv, va[4 * t + 1] * inv, va[4 * t + 2] * inv, va[4 * t + 3] * inv);
+    w[8 + t] = pack4_e4m3(vb[4 * t] * inv, vb[4 * t + 1] * inv, vb[4 * t + 2] * inv, vb[4 * t + 3] * inv);
   }
   // 32 rows x 64 bytes through the staging area (same shape as a 32-column bf16 chunk)
   if (t_q8 != nullptr)
