@@ -280,7 +280,7 @@ def test_gemm_fp8_mx_quantised_output():
     assert torch.equal(q8b.view(torch.uint8), q8.view(torch.uint8)) and torch.equal(p8b, p8)
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 128, 128), (512, 384, 1024), (4096, 1024, 2048)])
+@pytest.mark.parametrize("M,N,K", [(256, 128, 128), (256, 128, 640), (512, 256, 1536), (512, 384, 1024), (4096, 1024, 2048)])
 def test_gemm_fp8_mx_pair_matches_single_cta(M, N, K):
     """The CTA-pair form (256 x 128 pair tiles, scale chunks fetched through a tensor map) against the single-CTA
     kernel on the same operands, plain and with bias + auxiliary add + quantised output."""
