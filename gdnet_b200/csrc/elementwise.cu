@@ -1054,27 +1054,42 @@ const char* launch_scale_cols(const __nv_bfloat16* w, const float* colw, __nv_bf
 }
 
 // Backward of the folding: given dW2w (fp32), dW2 += dW2w * w_norm[j], dw_norm[j] += sum_i dW2w[i][j] * W2[i][j]
+constexpr int UNSCALE_ROWS = 8;
+
 __global__ void __launch_bounds__(256)
 unscale_cols_bwd_kernel(const float* __restrict__ dW2w, const __nv_bfloat16* __restrict__ W2,
                         const float* __restrict__ colw, float* __restrict__ dW2, float* __restrict__ dcolw, int rows,
                         int cols) {
   pdl_enter();
+  // 8 rows per block (64 left most SMs idle on a 1024 x 1024 matrix and made every thread a chain of 64 dependent
+  // read-modify-writes); all loads of a thread are issued before the first use
   const int c = blockIdx.x * 256 + threadIdx.x;
   if (c >= cols) return;
-  const int r_begin = blockIdx.y * 64, r_end = min(r_begin + 64, rows);
+  const int r_begin = blockIdx.y * UNSCALE_ROWS;
   const float wn = colw[c];
+  float g[UNSCALE_ROWS], old[UNSCALE_ROWS], w[UNSCALE_ROWS];
+#pragma unroll
+  for (int i = 0; i < UNSCALE_ROWS; ++i) {
+    const int r = r_begin + i;
+    const bool live = r < rows;
+    const int64_t idx = (int64_t)(live ? r : 0) * cols + c;
+    g[i] = live ? dW2w[idx] : 0.0f;
+    old[i] = live ? dW2[idx] : 0.0f;
+    w[i] = live ? __bfloat162float(W2[idx]) : 0.0f;
+  }
   float acc = 0.0f;
-  for (int r = r_begin; r < r_end; ++r) {
-    const float g = dW2w[(int64_t)r * cols + c];
-    dW2[(int64_t)r * cols + c] += g * wn;
-    acc = fmaf(g, __bfloat162float(W2[(int64_t)r * cols + c]), acc);
+#pragma unroll
+  for (int i = 0; i < UNSCALE_ROWS; ++i) {
+    const int r = r_begin + i;
+    if (r < rows) dW2[(int64_t)r * cols + c] = old[i] + g[i] * wn;
+    acc = fmaf(g[i], w[i], acc);
   }
   atomicAdd(dcolw + c, acc);
 }
 
 const char* launch_unscale_cols_bwd(const float* dW2w, const __nv_bfloat16* W2, const float* colw, float* dW2,
                                     float* dcolw, int rows, int cols, cudaStream_t st) {
-  dim3 grid((cols + 255) / 256, (rows + 63) / 64);
+  dim3 grid((cols + 255) / 256, (rows + UNSCALE_ROWS - 1) / UNSCALE_ROWS);
   launch_pdl(unscale_cols_bwd_kernel, grid, dim3(256), 0, st, dW2w, W2, colw, dW2, dcolw, rows, cols);
   return cudaGetLastError() == cudaSuccess ? nullptr : "unscale_cols_bwd launch failed";
 }
