@@ -307,3 +307,27 @@ def test_gemm_fp8_mx_pair_matches_single_cta(M, N, K):
     _close(res[1][0], res[0][0], 1e-5 * float(want.abs().max()), 1e-5, "pair against single CTA")
     _close(res[1][1].float(), res[0][1].float(), 1e-2 * float(want.abs().max()), 1e-2, "pair against single CTA, fused epilogue")
     assert (res[1][2] != res[0][2]).float().mean() < 1e-3 and torch.equal(res[1][3], res[0][3])
+
+
+def test_gemm_bf16_strided_outputs_and_edges():
+    """Outputs that are column slices of a wider buffer (the layer step writes into halves of its gradient buffer, in
+    place over the auxiliary input) and shapes whose last tiles are partial: the bulk stores must clip at the matrix
+    edge and leave the neighbouring columns alone."""
+    cu = _cu()
+    for M, N, K in ((1000, 160, 256), (512, 256, 128)):
+        a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16) * 0.5
+        b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.1
+        base = a.float() @ b.float().t()
+        wide = torch.randn(M, 2 * N, device=DEV, dtype=torch.bfloat16)
+        keep, add = wide[:, :N].clone(), wide[:, N:].float().clone()
+        view = wide[:, N:]
+        cu.gemm_bf16(a, b, out=view, aux=view, aux_mode=cu.AUX_ADD)          # in place over the auxiliary input
+        pre = torch.full((M, 2 * N), 7.0, device=DEV, dtype=torch.bfloat16)
+        out = cu.gemm_bf16(a, b, pre_out=pre[:, :N], act=cu.ACT_SILU)
+        torch.cuda.synchronize()
+        _status_clean(a)
+        _close(wide[:, N:], base + add, 3e-2, 2e-2, f"in-place aux add into a column slice {M}x{N}")
+        assert torch.equal(wide[:, :N], keep), "columns beside the output slice were touched"
+        _close(pre[:, :N], base, 2e-2, 2e-2, "pre_out slice")
+        assert torch.all(pre[:, N:] == 7.0), "columns beside the pre_out slice were touched"
+        _close(out, F.silu(base), 2e-2, 2e-2, "silu out")
