@@ -59,24 +59,12 @@ __device__ __forceinline__ void raise_abort(PipeBars* b, Status* st, int code, i
 // (row-major order would stream the whole B matrix once per row block when N is large).
 constexpr int RASTER_M = 8;
 
-// a / b for 0 <= a < 2^22, 0 < b: a float multiply and one correction step instead of the emulated integer division
-// (every role recomputes its tile coordinates once per tile, the eight epilogue warps included, and the epilogue is
-// the slowest part of most launches).
-__device__ __forceinline__ int fast_div(int a, int b) {
-  if (a >= (1 << 22)) return a / b;
-  int q = __float2int_rz(__int2float_rn(a) * __frcp_rn(__int2float_rn(b)));
-  const int r = a - q * b;
-  if (r < 0) --q;
-  else if (r >= b) ++q;
-  return q;
-}
-
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
   const int band_tiles = RASTER_M * tiles_n;
-  const int band = fast_div(tile, band_tiles);
+  const int band = tile / band_tiles;
   const int in_band = tile - band * band_tiles;
   const int rows_here = min(RASTER_M, tiles_m - band * RASTER_M);
-  nb = fast_div(in_band, rows_here);
+  nb = in_band / rows_here;
   mb = band * RASTER_M + (in_band - nb * rows_here);
 }
 
