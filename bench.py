@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 350m|tiny]
 
-Config (BASELINE.json, config 3): d_model 1024, 24 layers, 2 cycles, dwconv width 4, vocab 32000,
+Config: d_model 1024, 24 layers, 2 cycles, dwconv width 4, vocab 32000,
 seq_len 4096, micro-batch 8 per GPU, FP8 e4m3 linears, AdamW, projected-gradient step with 4
 memory write chunks (as the reference's scripts/throughput.py:218-316 runs it), data parallel over
 N GPUs (weak scaling). Synthetic packed tokens (geometric document lengths, EOS=0), random-init
@@ -331,7 +331,8 @@ def main() -> None:
             "config": {"model": f"gdnet-{args.config} d={cfg['d']} L={cfg['n_layers']} cycles={cfg['n_cycles']} "
                                 f"k={cfg['kernel_size']} vocab={cfg['vocab_size']}",
                        "global_batch": global_batch, "seq_len": T,
-                       "parallelism": (f"sp{world}" if sp else f"dp{world}") + (f" comm={comm}" if args.impl == "ours" else ""),
+                       "parallelism": f"sp{world}" if sp else f"dp{world}",
+                       "comm": comm if args.impl == "ours" else "nccl",
                        "step": f"projected_step, {cfg['n_write']} CAM write chunks, AdamW",
                        "l2": "working set per step > 50 GB, far larger than L2"},
             "clocks": clocks,

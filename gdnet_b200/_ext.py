@@ -45,6 +45,11 @@ class KernelTimeout(RuntimeError):
     """A bounded wait inside a kernel ran out; the kernel returned early."""
 
 
+class KernelArgumentError(ValueError):
+    """A kernel met data it refuses to use (e.g. a class index outside the vocabulary); it skipped the
+    offending element instead of touching memory out of bounds."""
+
+
 _STATUS_NAMES = {
     1: "TMA stage never arrived (consumer wait)",
     2: "shared-memory stage never released (producer wait)",
@@ -62,6 +67,11 @@ def check_status(like: torch.Tensor, reset: bool = True) -> None:
     if code != 0:
         if reset:
             st.zero_()
+        if code == 6:
+            raise KernelArgumentError(
+                f"kernel status 6 (bad argument) at site {site}, block {block}, detail {detail}"
+                + (": cross-entropy target outside [0, vocab); that row was ignored" if site == 60 else "")
+            )
         raise KernelTimeout(
             f"kernel status {code} ({_STATUS_NAMES.get(code, '?')}) at site {site}, block {block}, detail {detail}"
         )

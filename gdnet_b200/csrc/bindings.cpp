@@ -514,7 +514,8 @@ void cross_entropy(Tensor logits, const Tensor& targets, Tensor row_loss, const 
   TORCH_CHECK(targets.numel() == logits.size(0) && row_loss.numel() == logits.size(0) && vocab <= logits.size(1), "cross_entropy: sizes");
   GD_LAUNCH(gd::launch_cross_entropy(bf16_mut(logits, "logits"), targets.data_ptr<int64_t>(), f32_mut(row_loss, "row_loss"),
                                      f32_ptr(inv_count, "inv_count"), logits.size(0), (int)vocab, logits.stride(0),
-                                     (int)ignore_index, (float)grad_scale, write_grad, stream_of(logits)));
+                                     (int)ignore_index, (float)grad_scale, write_grad, status_ptr(logits),
+                                     stream_of(logits)));
 }
 
 void mem_read_fwd(const Tensor& q, const Tensor& gamma, const Tensor& e, const Tensor& tags, const Tensor& vals,

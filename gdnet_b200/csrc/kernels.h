@@ -144,9 +144,11 @@ const char* launch_unscale_cols_bwd(const float* dW2w, const __nv_bfloat16* W2, 
 // ---- loss, memory read, optimiser (loss_optim.cu) ------------------------------------------------
 // Cross-entropy over logits (rows, vocab_padded) bf16; only the first `vocab` columns take part.
 // Writes per-row loss (0 for ignored rows) and overwrites logits with d(mean loss)/d(logits) * grad_scale.
+// A target outside [0, vocab) other than ignore_index is treated as ignored and reported through `status`
+// (STATUS_BAD_ARGUMENT, site 60, detail = row); it is never used as an index.
 const char* launch_cross_entropy(__nv_bfloat16* logits, const int64_t* targets, float* row_loss,
                                  const float* inv_count, int64_t rows, int vocab, int64_t ld, int ignore_index,
-                                 float grad_scale, int write_grad, cudaStream_t st);
+                                 float grad_scale, int write_grad, Status* status, cudaStream_t st);
 
 const char* launch_mem_read_fwd(const float* q, const float* gamma, const float* e, const float* tags,
                                 const float* vals, const float* alpha, float* w, float* out, int B, int S, int dsig,

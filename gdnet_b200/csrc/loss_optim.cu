@@ -11,14 +11,18 @@ namespace gd {
 __global__ void __launch_bounds__(256)
 cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
                      float* __restrict__ row_loss, const float* __restrict__ inv_count, int vocab, int64_t ld,
-                     int ignore_index, float grad_scale, int write_grad) {
+                     int ignore_index, float grad_scale, int write_grad, Status* status) {
   __shared__ float red[8];
   __shared__ float s_max, s_sum;
   const int64_t row = blockIdx.x;
   __nv_bfloat16* lr = logits + row * ld;
   const int64_t tgt = targets[row];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool ignored = tgt == ignore_index;
+  // a target outside [0, vocab) that is not the ignore index is never used as an index: the row counts as
+  // ignored (loss 0, gradient 0) and the status word records it for the host
+  const bool out_of_range = tgt != ignore_index && (tgt < 0 || tgt >= vocab);
+  if (out_of_range && threadIdx.x == 0) report(status, STATUS_BAD_ARGUMENT, 60, (int)row);
+  const bool ignored = tgt == ignore_index || out_of_range;
 
   if (ignored && !write_grad) {
     if (threadIdx.x == 0) row_loss[row] = 0.0f;
@@ -115,11 +119,11 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restri
 
 const char* launch_cross_entropy(__nv_bfloat16* logits, const int64_t* targets, float* row_loss,
                                  const float* inv_count, int64_t rows, int vocab, int64_t ld, int ignore_index,
-                                 float grad_scale, int write_grad, cudaStream_t st) {
+                                 float grad_scale, int write_grad, Status* status, cudaStream_t st) {
   if (ld % 8 != 0) return "cross_entropy: row pitch must be a multiple of 8";
   if (rows == 0) return nullptr;
   cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(logits, targets, row_loss, inv_count, vocab, ld, ignore_index,
-                                                       grad_scale, write_grad);
+                                                       grad_scale, write_grad, status);
   return cudaGetLastError() == cudaSuccess ? nullptr : "cross_entropy launch failed";
 }
 
@@ -420,6 +424,8 @@ const char* launch_batched_outer_add(float* const* dsts, const float* const* ys,
 // =======================================================================================
 #include "noalloc.h"
 
+#include <atomic>
+
 namespace gd {
 
 // Scratch of the allocation-free entry point: [0, MAX_ROWS) per-row losses, [MAX_ROWS] unused pad.
@@ -430,13 +436,14 @@ static __device__ __align__(256) float g_noalloc_scratch[GD_NOALLOC_MAX_ROWS + 6
 // preceding kernel wrote (rows beyond `rows` hold stale values from earlier calls and are not read).
 __global__ void __launch_bounds__(1024)
 noalloc_finalize_kernel(const float* __restrict__ row_loss, const int64_t* __restrict__ targets, int64_t rows,
-                        int ignore_index, float* __restrict__ loss_out) {
+                        int ignore_index, int vocab, float* __restrict__ loss_out) {
   __shared__ float s_sum[32];
   __shared__ float s_cnt[32];
   float sum = 0.0f, cnt = 0.0f;
   for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
     sum += row_loss[r];
-    cnt += targets[r] != ignore_index ? 1.0f : 0.0f;
+    const int64_t t = targets[r];      // rows with a target outside [0, vocab) contribute nothing, like ignored rows
+    cnt += (t != ignore_index && t >= 0 && t < vocab) ? 1.0f : 0.0f;
   }
   sum = warp_sum(sum);
   cnt = warp_sum(cnt);
@@ -461,16 +468,18 @@ extern "C" int gd_cross_entropy_mean_noalloc(const void* logits_bf16, const int6
   if ((reinterpret_cast<uintptr_t>(logits_bf16) & 15) != 0 || ld % 8 != 0 || vocab < 1 || vocab > ld) return 2;
 
   // device address of the scratch array, looked up once per device with that device current
-  static float* scratch_of_device[64] = {nullptr};
+  // (atomic slots: host threads that make their first call on a device at the same time all store the same value)
+  static std::atomic<float*> scratch_of_device[64];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 3;
-  if (scratch_of_device[dev] == nullptr) {
+  float* row_loss = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (row_loss == nullptr) {
     float* p = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), gd::g_noalloc_scratch) != cudaSuccess || p == nullptr)
       return 3;
-    scratch_of_device[dev] = p;
+    scratch_of_device[dev].store(p, std::memory_order_release);
+    row_loss = p;
   }
-  float* row_loss = scratch_of_device[dev];
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
   if (rows > 0) {
@@ -478,9 +487,9 @@ extern "C" int gd_cross_entropy_mean_noalloc(const void* logits_bf16, const int6
     // overwritten, so nothing of an earlier call survives where this call looks
     gd::cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(
         reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(logits_bf16)), targets, row_loss, row_loss, vocab, ld,
-        ignore_index, 1.0f, 0);
+        ignore_index, 1.0f, 0, nullptr);
     if (cudaGetLastError() != cudaSuccess) return 3;
   }
-  gd::noalloc_finalize_kernel<<<1, 1024, 0, st>>>(row_loss, targets, rows, ignore_index, loss_out);
+  gd::noalloc_finalize_kernel<<<1, 1024, 0, st>>>(row_loss, targets, rows, ignore_index, vocab, loss_out);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

@@ -16,6 +16,9 @@
 //
 // logits: device, bf16, `rows` rows of pitch `ld` elements (ld % 8 == 0, 16-byte aligned base);
 // only the first `vocab` columns take part. targets: device int64[rows]. loss_out: device float[1].
+// A target that is neither `ignore_index` nor inside [0, vocab) is never used as an index: its row is
+// left out of the sum and of the count, exactly like an ignored row (this entry point has no status
+// word to report it through, so validate targets on the caller's side if bad ids must be noticed).
 // stream: a cudaStream_t (as void*), may be null for the default stream. The logits are not modified.
 //
 // Return value: 0 on success, otherwise

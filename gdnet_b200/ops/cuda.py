@@ -188,6 +188,14 @@ def share_fp8_weights(weights, group, device) -> SharedWeights:
     return _shared_weights
 
 
+def refresh_shared_weights() -> None:
+    """Collective: bring the shared FP8 weight cache up to date now. The training engine calls this right after
+    every optimizer update, where all ranks are in lockstep, so that a later forward on one rank only (an
+    evaluation on rank 0) never reaches the collective refresh by itself."""
+    if _shared_weights is not None and _shared_weights.epoch != _param_epoch:
+        _shared_weights.refresh()
+
+
 def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
     key = (w.data_ptr(), w.numel(), w.dtype)
     if _shared_weights is not None:
@@ -583,7 +591,8 @@ class _CrossEntropyFn(torch.autograd.Function):
     def forward(ctx, logits, targets, vocab, ignore_index):
         n, _ = logits.shape
         tgt = targets.reshape(-1).contiguous()
-        count = (tgt != ignore_index).sum().clamp(min=1).to(F32)
+        # rows whose target is out of range are dropped by the kernel (and reported in the status word)
+        count = ((tgt != ignore_index) & (tgt >= 0) & (tgt < vocab)).sum().clamp(min=1).to(F32)
         inv = (1.0 / count).reshape(1)
         row_loss = torch.empty(n, dtype=F32, device=logits.device)
         need_grad = logits.requires_grad
@@ -622,7 +631,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         Vp = w.shape[0]
         dev = x2.device
         tgt = targets.reshape(-1).contiguous()
-        count = (tgt != -100).sum().clamp(min=1).to(F32)
+        count = ((tgt >= 0) & (tgt < vocab)).sum().clamp(min=1).to(F32)    # -100 (ignored) and bad ids drop out
         inv = (1.0 / count).reshape(1)
         row_loss = torch.empty(M, dtype=F32, device=dev)
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
@@ -1296,7 +1305,12 @@ class _HaloExchangeSymm(torch.autograd.Function):
         # the backward of use n of a slot gets its own sequence number in the second half of the area
         key = ("b", ctx.slot, ctx.n_use)
         cnt = st["pass_fwd"].get(key, 0) + 1
-        st["pass_fwd"][key] = cnt
+        if cnt >= 2:
+            st["pass_fwd"].pop(key, None)      # a forward use is differentiated at most twice: drop its counter
+        else:
+            st["pass_fwd"][key] = cnt
+            for old in [k for k in st["pass_fwd"] if isinstance(k, tuple) and k[1] == ctx.slot and k[2] < ctx.n_use - HALO_RING]:
+                del st["pass_fwd"][old]        # counters of uses that were differentiated only once
         # a retained graph runs this backward up to twice per forward use; every run has its own
         # sequence number and ring position, so a fast rank cannot overwrite an unread message
         seq = ctx.n_use * 2 + min(cnt, 2) - 1

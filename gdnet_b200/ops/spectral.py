@@ -2,7 +2,8 @@
 
 ``sigma_estimates`` evaluates ``||W_i v_i||`` for a fresh random unit vector per matrix
 (reference: gdnet/loss.py:15-31). On CUDA all matrices are handled by one batched
-matrix-vector kernel and its rank-1 backward (``csrc/spectral.cu``); on CPU it is a
+matrix-vector kernel and its rank-1 backward (``csrc/loss_optim.cu``: ``batched_gemv_kernel``,
+``batched_outer_add_kernel``); on CPU it is a
 loop of fp32 matvecs.
 """
 

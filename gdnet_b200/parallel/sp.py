@@ -111,6 +111,22 @@ def state_exchange(summary: torch.Tensor, group) -> torch.Tensor:
 
 # -- names kept from the reference ---------------------------------------------------
 
+class FusedHaloConvSP:
+    """Sequence-parallel causal conv under the reference's name and call form
+    (gdnet/utils/sp.py:102-170): ``FusedHaloConvSP.apply(x, W_conv, T, k, BLOCK_T, sp_group)`` exchanges the
+    ``k-1`` tail rows with the neighbours and convolves with the received halo. ``T`` and ``BLOCK_T`` are
+    accepted for call-site compatibility (the kernels here pick their own tiling). Differentiable in ``x``,
+    ``W_conv`` and, through the exchange, the previous rank's tail rows."""
+
+    @staticmethod
+    def apply(x, W_conv, T, k, BLOCK_T, sp_group, slot: int = 0):
+        from ..ops import functional as ops
+        from ..ops import reference as ref
+
+        halo = halo_exchange(ref.conv_tail(x, k).contiguous(), sp_group, slot) if k > 1 else None
+        return ops.causal_dwconv(x, W_conv, halo)
+
+
 def flush_bwd_halos(sp_group) -> None:
     """No-op: halo gradients are applied inside the exchange's backward."""
     return None

@@ -254,6 +254,7 @@ class TrainEngine(nn.Module):
         from ..ops import cuda as cu
 
         cu.invalidate_param_caches()
+        cu.refresh_shared_weights()     # collective, here where every rank is at the same point of the step
         return total
 
     def update_times_ms(self) -> list[float]:

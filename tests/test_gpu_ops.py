@@ -107,6 +107,34 @@ def test_cross_entropy(V, Vp):
         assert x.grad[:, V:].abs().max() == 0
 
 
+def test_cross_entropy_out_of_range_target_is_ignored_and_reported():
+    """A class id outside [0, vocab) that is not the ignore index must never be used as an index: the row gives
+    loss 0 and gradient 0, is left out of the mean, and the status word makes the host raise."""
+    from gdnet_b200 import _ext
+
+    cu = _cu()
+    n, V, Vp = 32, 250, 256
+    logits = (torch.randn(n, Vp, device=DEV) * 3).to(BF)
+    tgt = torch.randint(0, V, (n,), device=DEV)
+    tgt[3], tgt[5], tgt[9] = V, -7, 10**9          # first padded column, negative, far out of range
+    good = tgt.clone()
+    good[[3, 5, 9]] = -100
+    want = F.cross_entropy(logits.float()[:, :V], good, ignore_index=-100)
+    x = logits.clone().requires_grad_()
+    loss = cu.cross_entropy(x * 1.0, tgt, -100, vocab=V)
+    loss.backward()
+    torch.cuda.synchronize()
+    with pytest.raises(_ext.KernelArgumentError):
+        _ext.check_status(logits)
+    _ext.check_status(logits)                      # the status word was reset by the failed check
+    _check(loss, want, 2e-3, "ce loss with bad targets dropped")
+    assert float(x.grad[[3, 5, 9]].abs().max()) == 0.0
+    # the kernels stay usable afterwards
+    loss2 = cu.cross_entropy(logits.clone(), good, -100, vocab=V)
+    _check(loss2, want, 2e-3, "ce after a reported bad target")
+    _ext.check_status(logits)
+
+
 @pytest.mark.parametrize("M,K,N,bias", [(256, 128, 256, True), (512, 384, 128, False)])
 def test_linear_bf16_fwd_bwd(M, K, N, bias):
     cu = _cu()

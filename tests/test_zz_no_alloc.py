@@ -70,3 +70,23 @@ def test_noalloc_rejects_bad_sizes_and_arguments():
     assert fn(None, targets.data_ptr(), 8, 64, 64, -100, out.data_ptr(), stream) == 2
     assert fn(logits.data_ptr(), targets.data_ptr(), 8, 64, 64, -100, out.data_ptr(), stream) == 0
     torch.cuda.synchronize()
+
+
+def test_noalloc_ignores_out_of_range_targets():
+    """Targets outside [0, vocab) are left out of the sum and the count, like ignored rows, and are never
+    used to index the logits."""
+    import torch.nn.functional as F
+
+    fn = _lib()
+    dev = "cuda"
+    rows, vocab, vp = 64, 250, 256
+    logits = (torch.randn(rows, vp, device=dev) * 3).to(torch.bfloat16)
+    targets = torch.randint(0, vocab, (rows,), device=dev)
+    targets[1], targets[2], targets[40] = vocab + 3, -5, 1 << 40
+    good = targets.clone()
+    good[[1, 2, 40]] = -100
+    out = torch.zeros(1, device=dev)
+    assert _call(fn, logits, targets, vocab, -100, out) == 0
+    torch.cuda.synchronize()
+    want = F.cross_entropy(logits.float()[:, :vocab], good, ignore_index=-100)
+    assert abs(float(out) - float(want)) <= 2e-3 * max(1.0, abs(float(want))), (float(out), float(want))
