@@ -107,7 +107,7 @@ std::vector<GradSink>& grad_sinks() {
 const GradSink* find_sink(const void* p) {
   const uintptr_t u = reinterpret_cast<uintptr_t>(p);
   for (const GradSink& s : grad_sinks())
-    if (u >= s.base && u < s.base + (uintptr_t)s.elems * 4) return &s;
+    if (s.elems > 0 && u >= s.base && u < s.base + (uintptr_t)s.elems * 4) return &s;
   return nullptr;
 }
 
@@ -119,7 +119,77 @@ void register_grad_sink(const Tensor& flat, const Tensor& ptr_table, int64_t sha
   grad_sinks().push_back({reinterpret_cast<uintptr_t>(flat.data_ptr()), flat.numel(), ptr_table, shard_elems});
 }
 
+// A sink without a local full-size buffer (parameters sharded over the ranks: every rank holds only its own
+// shard of the flat gradient). Gradients are addressed by (sink index, flat element offset); ptr_table[r] is
+// rank r's shard base minus r * shard_elems elements, so that table[idx / shard_elems] + idx is element idx.
+int64_t register_virtual_grad_sink(const Tensor& ptr_table, int64_t total_elems, int64_t shard_elems) {
+  TORCH_CHECK(ptr_table.is_cuda() && ptr_table.scalar_type() == at::kLong, "ptr_table must be an int64 CUDA tensor");
+  TORCH_CHECK(shard_elems > 0 && shard_elems % 128 == 0, "shard_elems must be a positive multiple of 128");
+  TORCH_CHECK(total_elems <= shard_elems * ptr_table.numel(), "shards do not cover the buffer");
+  grad_sinks().push_back({0, -total_elems, ptr_table, shard_elems});     // elems < 0: never matched by address
+  return (int64_t)grad_sinks().size() - 1;
+}
+
+const GradSink& sink_at(int64_t i) {
+  TORCH_CHECK(i >= 0 && i < (int64_t)grad_sinks().size(), "unknown gradient sink ", i);
+  return grad_sinks()[(size_t)i];
+}
+
+// One-shot attachments for the next tensor-core GEMM launched from this thread: a list of peer -> local gather
+// jobs that the launch carries, and the counters that tell the hardware-scaled fp8 GEMM when its own B has landed.
+struct PendingGather {
+  std::optional<Tensor> jobs, b_ready, sfb_ready;
+  int64_t b_target = 0, sfb_target = 0;
+};
+PendingGather& pending_gather() {
+  static thread_local PendingGather p;
+  return p;
+}
+
+void attach_gather_jobs(const Tensor& jobs) {
+  TORCH_CHECK(jobs.is_cuda() && jobs.scalar_type() == at::kLong && jobs.is_contiguous() && jobs.dim() == 2 && jobs.size(1) == 4,
+              "gather jobs must be a contiguous int64 CUDA tensor (n, 4): src, dst, counter, 16-byte vectors");
+  pending_gather().jobs = jobs;
+}
+
+void attach_b_ready(const Tensor& b_ready, const Tensor& sfb_ready, int64_t b_target, int64_t sfb_target) {
+  TORCH_CHECK(b_ready.is_cuda() && sfb_ready.is_cuda() && b_ready.scalar_type() == at::kInt &&
+              sfb_ready.scalar_type() == at::kInt && b_ready.is_contiguous() && sfb_ready.is_contiguous(),
+              "ready counters must be contiguous int32 CUDA tensors");
+  PendingGather& p = pending_gather();
+  p.b_ready = b_ready;
+  p.sfb_ready = sfb_ready;
+  p.b_target = b_target;
+  p.sfb_target = sfb_target;
+}
+
+void take_pending_gather(gd::GemmShape& g, int64_t n_blocks, bool may_wait) {
+  PendingGather& p = pending_gather();
+  if (p.jobs.has_value()) {
+    g.jobs = p.jobs->data_ptr<int64_t>();
+    g.n_jobs = (int)p.jobs->size(0);
+    p.jobs.reset();
+  }
+  if (p.b_ready.has_value()) {
+    TORCH_CHECK(may_wait, "only the hardware-scaled fp8 GEMM can wait for a gathered B operand");
+    TORCH_CHECK(p.b_ready->numel() >= n_blocks && p.sfb_ready->numel() >= n_blocks, "one ready counter per 128 rows of B");
+    g.b_ready = reinterpret_cast<const uint32_t*>(p.b_ready->data_ptr<int>());
+    g.sfb_ready = reinterpret_cast<const uint32_t*>(p.sfb_ready->data_ptr<int>());
+    g.b_target = (uint32_t)p.b_target;
+    g.sfb_target = (uint32_t)p.sfb_target;
+    p.b_ready.reset();
+    p.sfb_ready.reset();
+  }
+}
+
 void clear_grad_sinks() { grad_sinks().clear(); }
+
+void gather_jobs(const Tensor& jobs) {
+  c10::cuda::CUDAGuard guard(jobs.device());
+  TORCH_CHECK(jobs.is_cuda() && jobs.scalar_type() == at::kLong && jobs.is_contiguous() && jobs.dim() == 2 && jobs.size(1) == 4,
+              "gather jobs must be a contiguous int64 CUDA tensor (n, 4)");
+  GD_LAUNCH(gd::launch_gather_jobs(jobs.data_ptr<int64_t>(), (int)jobs.size(0), stream_of(jobs)));
+}
 
 // Optional fused 1x128 FP8 copy of a (rows, cols) output: q (rows, cols) e4m3 (may be a column range of a wider
 // buffer), s (cols/128, rows) fp32 (rows of a taller buffer), p (rows/128, cols/128, 512) packed chunks.
@@ -226,7 +296,7 @@ void fill_epilogue(gd::GemmEpilogue& e, const Tensor& out, bool accumulate, OptT
 // D = A B^T. a: (M,K) [K-major] or (K,M) [a_mn]; b: (N,K) or (K,N) [b_mn].
 void gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, Tensor out, bool accumulate, OptT bias,
                OptT row_scale, OptT ssq_in, int64_t norm_dim, double norm_eps, OptT aux, int64_t aux_mode,
-               OptT rowcoef, OptT pre_out, int64_t act, OptT ssq_out) {
+               OptT rowcoef, OptT pre_out, int64_t act, OptT ssq_out, int64_t sink, int64_t sink_off, int64_t sink_ld) {
   c10::cuda::CUDAGuard guard(a.device());
   OpRange gd_range_(__func__);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm operands must be 2-D");
@@ -236,9 +306,29 @@ void gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, Tensor ou
   gd::GemmOperands op{bf16_ptr(a, "a"), bf16_ptr(b, "b"), a.stride(0), b.stride(0)};
   gd::GemmShape g{(int)M, (int)N, (int)K, a_mn, b_mn, nullptr, nullptr, 0, 1, nullptr, nullptr};
   gd::GemmEpilogue e;
-  fill_epilogue(e, out, accumulate, bias, row_scale, ssq_in, norm_dim, norm_eps, aux, aux_mode, rowcoef, pre_out, act,
-                ssq_out, M, N);
+  if (sink >= 0) {
+    // fp32 accumulation into a gradient that lives sharded over the ranks: `out` only gives the shape
+    const GradSink& gs = sink_at(sink);
+    TORCH_CHECK(gs.elems < 0, "explicit gradient offsets need a virtual sink");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N, "out must be (M, N)");
+    TORCH_CHECK(sink_ld >= N && sink_ld % 32 == 0 && N % 32 == 0 && sink_off % 32 == 0 && sink_off >= 0 &&
+                sink_off + (M - 1) * sink_ld + N <= -gs.elems, "gradient range outside the sink");
+    TORCH_CHECK(!bias.has_value() && !aux.has_value() && !pre_out.has_value() && !row_scale.has_value() &&
+                !ssq_in.has_value() && !ssq_out.has_value() && act == 0, "a sharded gradient takes a plain epilogue");
+    e = gd::GemmEpilogue{};
+    e.out = gs.table.data_ptr();      // non-null, never dereferenced: every chunk goes through peer_out
+    e.out_ld = sink_ld;
+    e.out_f32 = 1;
+    e.accumulate = 1;
+    e.peer_out = reinterpret_cast<float* const*>(gs.table.data_ptr<int64_t>());
+    e.flat_off = sink_off;
+    e.shard_elems = gs.shard_elems;
+  } else {
+    fill_epilogue(e, out, accumulate, bias, row_scale, ssq_in, norm_dim, norm_eps, aux, aux_mode, rowcoef, pre_out, act,
+                  ssq_out, M, N);
+  }
   if (ssq_out.has_value()) TORCH_CHECK(ssq_out->size(1) == (N + 127) / 128, "bf16 gemm writes N/128 ssq partials");
+  take_pending_gather(g, 0, false);
   GD_LAUNCH(gd::launch_gemm_bf16(op, g, e, status_ptr(a), stream_of(a)));
 }
 
@@ -296,6 +386,7 @@ void gemm_fp8_mx(const Tensor& a8, const Tensor& pa, const Tensor& b8, const Ten
     TORCH_CHECK(q8.has_value() && !pre_out.has_value(), "store_out=False only makes sense with a quantised copy");
     e.out = nullptr;
   }
+  take_pending_gather(g, N / 128, true);
   GD_LAUNCH(gd::launch_gemm_fp8_mx(op, g, e, status_ptr(a8), stream_of(a8)));
 }
 
@@ -605,7 +696,7 @@ void batched_gemv(const Tensor& mats, const Tensor& vecs, const Tensor& outs, co
 void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, const Tensor& ptr_table_p,
                      const Tensor& signal_table, Tensor m, Tensor v, const Tensor& scalars, int64_t n, int64_t rank,
                      int64_t world, int64_t seq, int64_t phase, bool p_is_bf16, double beta_proj, double lr, double beta1,
-                     double beta2, double eps, double weight_decay, int64_t step, Tensor shard_sums) {
+                     double beta2, double eps, double weight_decay, int64_t step, Tensor shard_sums, bool gather_params) {
   c10::cuda::CUDAGuard guard(m.device());
   OpRange gd_range_(__func__);
   gd::FusedReduceAdamWArgs a{};
@@ -618,6 +709,7 @@ void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, con
   a.scalars = f32_ptr(scalars, "scalars");
   a.shard_sums = f32_mut(shard_sums, "shard_sums");
   a.n = n; a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq; a.phase = (int)phase; a.p_is_bf16 = p_is_bf16;
+  a.gather_params = gather_params;
   a.beta_proj = (float)beta_proj; a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2;
   a.eps = (float)eps; a.weight_decay = (float)weight_decay;
   a.bc1 = (float)(1.0 - std::pow(beta1, (double)step));
@@ -648,8 +740,27 @@ void peer_add(Tensor dst, const Tensor& src) {
   GD_LAUNCH(gd::launch_peer_add(a, stream_of(dst)));
 }
 
+// sink[off : off + n] += src for a gradient that lives sharded over the ranks (see register_virtual_grad_sink)
+void peer_add_at(int64_t sink, int64_t off, const Tensor& src) {
+  c10::cuda::CUDAGuard guard(src.device());
+  OpRange gd_range_(__func__);
+  const GradSink& s = sink_at(sink);
+  TORCH_CHECK(s.elems < 0, "peer_add_at needs a virtual sink");
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "peer_add_at: src must be a contiguous CUDA tensor");
+  TORCH_CHECK(src.scalar_type() == at::kFloat || src.scalar_type() == at::kBFloat16, "peer_add_at: src must be fp32 or bf16");
+  TORCH_CHECK(off >= 0 && off % 4 == 0 && off + src.numel() <= -s.elems, "peer_add_at: range outside the sink");
+  gd::PeerAddArgs a{};
+  a.src = src.data_ptr();
+  a.src_bf16 = src.scalar_type() == at::kBFloat16;
+  a.table = reinterpret_cast<float* const*>(s.table.data_ptr<int64_t>());
+  a.flat_off = off;
+  a.n = src.numel();
+  a.shard_elems = s.shard_elems;
+  GD_LAUNCH(gd::launch_peer_add(a, stream_of(src)));
+}
+
 void max_allreduce(Tensor vec, const Tensor& area_ptrs, const Tensor& flag_ptrs, int64_t slot_elems, int64_t rank,
-                   int64_t world, int64_t seq) {
+                   int64_t world, int64_t seq, int64_t budget_ns) {
   c10::cuda::CUDAGuard guard(vec.device());
   OpRange gd_range_(__func__);
   TORCH_CHECK(vec.is_contiguous() && vec.scalar_type() == at::kFloat, "max_allreduce: vec must be contiguous fp32");
@@ -661,13 +772,14 @@ void max_allreduce(Tensor vec, const Tensor& area_ptrs, const Tensor& flag_ptrs,
   a.flags = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
   a.slot_elems = (int)slot_elems;
   a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq;
+  a.budget_ns = budget_ns > 0 ? (uint64_t)budget_ns : 0;
   a.status = status_ptr(vec);
   GD_LAUNCH(gd::launch_max_allreduce(a, stream_of(vec)));
 }
 
 void halo_push_wait(const Tensor& tail, Tensor halo_out, const Tensor& slot_ptrs, const Tensor& flag_ptrs,
                     int64_t slot_offset_bytes, int64_t flag_index, int64_t rank, int64_t world, int64_t seq,
-                    bool reverse) {
+                    bool reverse, int64_t budget_ns) {
   c10::cuda::CUDAGuard guard(tail.device());
   OpRange gd_range_(__func__);
   TORCH_CHECK(tail.is_contiguous() && halo_out.is_contiguous() && tail.numel() == halo_out.numel(), "halo: shapes");
@@ -681,6 +793,7 @@ void halo_push_wait(const Tensor& tail, Tensor halo_out, const Tensor& slot_ptrs
   a.slot_offset = slot_offset_bytes;
   a.flag_index = (int)flag_index;
   a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq; a.reverse = reverse;
+  a.budget_ns = budget_ns > 0 ? (uint64_t)budget_ns : 0;
   a.status = status_ptr(tail);
   GD_LAUNCH(gd::launch_halo_push_wait(a, stream_of(tail)));
 }
@@ -689,7 +802,7 @@ void halo_push_wait(const Tensor& tail, Tensor halo_out, const Tensor& slot_ptrs
 
 TORCH_LIBRARY(gdnet_b200, m) {
   m.def("kernel_status(Tensor like) -> Tensor", &kernel_status);
-  m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? ssq_in, int norm_dim, float norm_eps, Tensor? aux, int aux_mode, Tensor? rowcoef, Tensor(b!)? pre_out, int act, Tensor(c!)? ssq_out) -> ()", &gemm_bf16);
+  m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? ssq_in, int norm_dim, float norm_eps, Tensor? aux, int aux_mode, Tensor? rowcoef, Tensor(b!)? pre_out, int act, Tensor(c!)? ssq_out, int sink=-1, int sink_off=0, int sink_ld=0) -> ()", &gemm_bf16);
   m.def("gemm_fp8(Tensor a8, Tensor sa, Tensor b8, Tensor sb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act) -> ()", &gemm_fp8);
   m.def("gemm_fp8_mx(Tensor a8, Tensor pa, Tensor b8, Tensor pb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act, Tensor(c!)? q8=None, Tensor(d!)? q8_p=None, bool q8_silu=False, bool store_out=True) -> ()", &gemm_fp8_mx);
   m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out, Tensor(b!)? q=None, Tensor(c!)? qs=None, Tensor(d!)? qp=None) -> ()", &dwconv_fwd);
@@ -711,12 +824,17 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("projected_adamw(Tensor(a!) p, Tensor gt, Tensor? gi, Tensor(b!) m, Tensor(c!) v, Tensor scalars, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()", &projected_adamw);
   m.def("batched_outer_add(Tensor dsts, Tensor ys, Tensor vecs, Tensor coef, Tensor rows, Tensor cols, int max_rows) -> ()", &batched_outer_add);
   m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
-  m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums) -> ()", &allreduce_adamw);
+  m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums, bool gather_params=True) -> ()", &allreduce_adamw);
   m.def("gemm_pair_capacity() -> int", []() -> int64_t { return gd::gemm_pair_capacity(); });
   m.def("gemm_set_mx_pair(int on) -> ()", [](int64_t on) { gd::gemm_set_mx_pair((int)on); });
   m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> ()", &register_grad_sink);
   m.def("clear_grad_sinks() -> ()", &clear_grad_sinks);
+  m.def("register_virtual_grad_sink(Tensor ptr_table, int total_elems, int shard_elems) -> int", &register_virtual_grad_sink);
+  m.def("peer_add_at(int sink, int off, Tensor src) -> ()", &peer_add_at);
+  m.def("attach_gather_jobs(Tensor jobs) -> ()", &attach_gather_jobs);
+  m.def("attach_b_ready(Tensor b_ready, Tensor sfb_ready, int b_target, int sfb_target) -> ()", &attach_b_ready);
+  m.def("gather_jobs(Tensor jobs) -> ()", &gather_jobs);
   m.def("peer_add(Tensor(a!) dst, Tensor src) -> ()", &peer_add);
-  m.def("max_allreduce(Tensor(a!) vec, Tensor area_ptrs, Tensor flag_ptrs, int slot_elems, int rank, int world, int seq) -> ()", &max_allreduce);
-  m.def("halo_push_wait(Tensor tail, Tensor(a!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, int slot_offset_bytes, int flag_index, int rank, int world, int seq, bool reverse) -> ()", &halo_push_wait);
+  m.def("max_allreduce(Tensor(a!) vec, Tensor area_ptrs, Tensor flag_ptrs, int slot_elems, int rank, int world, int seq, int budget_ns=0) -> ()", &max_allreduce);
+  m.def("halo_push_wait(Tensor tail, Tensor(a!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, int slot_offset_bytes, int flag_index, int rank, int world, int seq, bool reverse, int budget_ns=0) -> ()", &halo_push_wait);
 }

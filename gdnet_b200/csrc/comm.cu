@@ -15,7 +15,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 
 // Bounded wait until *p >= want (sequence numbers only grow). false = budget exhausted.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want) {
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, uint64_t budget_ns = GD_WAIT_BUDGET_NS) {
   for (int i = 0; i < 2048; ++i)
     if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
@@ -24,8 +24,12 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want) {
       if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
       __nanosleep(200);
     }
-    if (globaltimer_ns() - t0 > GD_WAIT_BUDGET_NS) return false;
+    if (globaltimer_ns() - t0 > budget_ns) return false;
   }
+}
+
+__device__ __forceinline__ uint64_t budget_or_default(uint64_t budget_ns) {
+  return budget_ns != 0 ? budget_ns : (uint64_t)GD_WAIT_BUDGET_NS;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -133,7 +137,8 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
         const float2 p01 = unpack_bf16x2(old.x), p23 = unpack_bf16x2(old.y);
         const uint2 nw = make_uint2(pack_bf16x2(p01.x * decay - upd[0], p01.y * decay - upd[1]),
                                     pack_bf16x2(p23.x * decay - upd[2], p23.y * decay - upd[3]));
-        for (int r = 0; r < a.world; ++r) {
+        const int n_dst = a.gather_params ? a.world : 1;
+        for (int r = 0; r < n_dst; ++r) {
           const int peer = (a.rank + r) % a.world;
           *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.p[peer]) + i) = nw;
         }
@@ -142,7 +147,8 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
         const float4 old = *reinterpret_cast<const float4*>(pl);
         const float4 nw = make_float4(old.x * decay - upd[0], old.y * decay - upd[1], old.z * decay - upd[2],
                                       old.w * decay - upd[3]);
-        for (int r = 0; r < a.world; ++r) {
+        const int n_dst = a.gather_params ? a.world : 1;
+        for (int r = 0; r < n_dst; ++r) {
           const int peer = (a.rank + r) % a.world;
           *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.p[peer]) + i) = nw;
         }
@@ -247,7 +253,7 @@ max_allreduce_kernel(const MaxAllReduceArgs a) {
   if (threadIdx.x == 0) ok_all = 1;
   __syncthreads();
   if (threadIdx.x < a.world) {
-    if (!wait_flag_ge(a.flags[a.rank] + threadIdx.x, a.seq)) {
+    if (!wait_flag_ge(a.flags[a.rank] + threadIdx.x, a.seq, budget_or_default(a.budget_ns))) {
       report(a.status, STATUS_TIMEOUT_PEER_FLAG, 50, (int)threadIdx.x);
       ok_all = 0;
     }
@@ -289,7 +295,7 @@ halo_push_wait_kernel(const HaloArgs a) {
   if (src >= 0 && src < a.world) {
     __shared__ int ok;
     if (threadIdx.x == 0) {
-      ok = wait_flag_ge(a.flags[a.rank] + a.flag_index, a.seq) ? 1 : 0;
+      ok = wait_flag_ge(a.flags[a.rank] + a.flag_index, a.seq, budget_or_default(a.budget_ns)) ? 1 : 0;
       if (!ok) report(a.status, STATUS_TIMEOUT_PEER_FLAG, 40, src);
     }
     __syncthreads();

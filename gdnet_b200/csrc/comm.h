@@ -40,6 +40,8 @@ struct FusedReduceAdamWArgs {
   int rank, world;
   uint32_t seq;            // strictly increasing per call pair
   int p_is_bf16;
+  int gather_params;       // 1: store the updated shard into every rank's parameter buffer; 0: this rank's only
+                           // (parameters sharded over the ranks: p[rank] is the shard base minus the shard offset)
   int phase;
   float beta_proj, lr, beta1, beta2, eps, weight_decay, bc1, bc2;
   Status* status;
@@ -67,6 +69,7 @@ struct MaxAllReduceArgs {
   int slot_elems;
   int rank, world;
   uint32_t seq;             // strictly increasing per call
+  uint64_t budget_ns;       // time limit of the wait for the peers' flags; 0 = the library default (2 s)
   Status* status;
 };
 const char* launch_max_allreduce(const MaxAllReduceArgs& a, cudaStream_t st);
@@ -85,6 +88,7 @@ struct HaloArgs {
   int rank, world;
   uint32_t seq;
   int reverse;
+  uint64_t budget_ns;      // time limit of the wait for the neighbour's flag; 0 = the library default (2 s)
   Status* status;
 };
 const char* launch_halo_push_wait(const HaloArgs& a, cudaStream_t st);

@@ -55,6 +55,68 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 #endif
 
 // ---------------------------------------------------------------------------------------
+// flags in global memory (sequence numbers that only grow) and peer -> local gather jobs
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Orders generic-proxy accesses to global memory against bulk tensor copies (async proxy) of the same data.
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+
+// Bounded wait until *p >= want, written by another CTA of this GPU. false = the budget ran out.
+__device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* p, uint32_t want, uint64_t budget_ns) {
+  for (int i = 0; i < 1024; ++i)
+    if ((int32_t)(ld_acquire_gpu(p) - want) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    for (int i = 0; i < 128; ++i) {
+      if ((int32_t)(ld_acquire_gpu(p) - want) >= 0) return true;
+      __nanosleep(100);
+    }
+    if (globaltimer_ns() - t0 > budget_ns) return false;
+  }
+}
+
+// A gather job copies `n_vec` 16-byte vectors from `src` (usually another GPU's memory, read with plain
+// uncached loads over NVLink) to `dst` (this GPU's memory) and then adds one to the counter `*flag` (release,
+// device scope; may be null). Jobs are four int64 words each: src, dst, flag, n_vec. A range that a consumer
+// waits for is cut into several jobs that share one counter, so the consumer waits for the counter to reach
+// (uses so far) x (jobs per range). One warp works through jobs worker, worker + n_workers, ... with sixteen
+// loads per lane in flight.
+__device__ __forceinline__ void run_gather_jobs(const int64_t* __restrict__ jobs, int n_jobs, int worker,
+                                                int n_workers, int lane) {
+  for (int j = worker; j < n_jobs; j += n_workers) {
+    const uint4* src = reinterpret_cast<const uint4*>(jobs[4 * j]);
+    uint4* dst = reinterpret_cast<uint4*>(jobs[4 * j + 1]);
+    uint32_t* flag = reinterpret_cast<uint32_t*>(jobs[4 * j + 2]);
+    const int64_t n = jobs[4 * j + 3];
+    int64_t i = lane;
+    for (; i + 15 * 32 < n; i += 16 * 32) {
+      uint4 v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) v[u] = __ldcv(src + i + u * 32);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) dst[i + u * 32] = v[u];
+    }
+    for (; i < n; i += 32) dst[i] = __ldcv(src + i);
+    __threadfence();
+    fence_proxy_async_global();     // the consumer reads these bytes with bulk tensor copies
+    __syncwarp();
+    if (lane == 0 && flag != nullptr)
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // shared memory / mbarrier
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

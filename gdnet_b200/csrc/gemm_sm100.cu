@@ -758,6 +758,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         __syncwarp();
         if (++acc == BF16_ACC) { acc = 0; acc_ph ^= 1; }
       }
+    } else if (g.jobs != nullptr) {
+      // the second CTA's warp 1 issues no MMAs: it pulls parameter ranges from their owner ranks
+      run_gather_jobs(g.jobs, g.n_jobs, pair, n_pairs, lane);
     }
   } else {
     const int ew = warp - 2;
@@ -1366,6 +1369,20 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const int mblk = mb_ * 2 + (int)rank;                       // this CTA's 128-row block of A
         const int m0 = mblk * BM, nB = nb_ * MX_BN + (int)rank * MXP_B_ROWS;
         int sfa_row = mblk * kblocks * 2, sfb_row = nb_ * kblocks * 2;   // 256-byte rows of the packed scale arrays
+        if (g.b_ready != nullptr) {
+          // this launch gathers its own B: column block nb_ must have landed in the staging area
+          uint32_t there = 1;
+          if (lane == 0)
+            there = wait_flag_ge_gpu(g.b_ready + nb_, g.b_target, GD_WAIT_BUDGET_NS) &&
+                    wait_flag_ge_gpu(g.sfb_ready + nb_, g.sfb_target, GD_WAIT_BUDGET_NS);
+          there = __shfl_sync(0xffffffffu, there, 0);
+          if (!there) {
+            if (lane == 0) raise_abort(bars, status, STATUS_TIMEOUT_PEER_FLAG, 75, nb_);
+            ok = false;
+            break;
+          }
+          fence_proxy_async_global();
+        }
         int kx = 0;
         for (int kb = 0; kb < kblocks; ++kb, kx += MX_BK, sfa_row += 2, sfb_row += 2) {
           if (!__all_sync(0xffffffffu, wait_fast(empty0 + 8 * s, ph ^ 1))) {
@@ -1435,6 +1452,9 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         __syncwarp();
         if (++acc == MX_ACC) { acc = 0; acc_ph ^= 1; }
       }
+    } else if (g.jobs != nullptr) {
+      // the second CTA's warp 1 issues no MMAs: it pulls parameter ranges from their owner ranks
+      run_gather_jobs(g.jobs, g.n_jobs, pair, n_pairs, lane);
     }
   } else {
     const int ew = warp - 2;
@@ -1537,6 +1557,12 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, MX_TMEM_COLS);
   }
+}
+
+// Stand-alone gather: four warps per block, every warp a worker of run_gather_jobs.
+__global__ void __launch_bounds__(128)
+gather_jobs_kernel(const int64_t* __restrict__ jobs, int n_jobs) {
+  run_gather_jobs(jobs, n_jobs, (int)(blockIdx.x * 4 + (threadIdx.x >> 5)), (int)(gridDim.x * 4), (int)(threadIdx.x & 31));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1755,6 +1781,7 @@ const char* launch_gemm_bf16(const GemmOperands& op, const GemmShape& g, const G
   }
   CUtensorMap ta, tb;
   const char* err;
+  if (g.jobs != nullptr && (err = launch_gather_jobs(g.jobs, g.n_jobs, stream)) != nullptr) return err;
   if (!g.a_mn) err = make_tensor_map_2d(&ta, op.a, 2, g.M, g.K, op.a_ld, BM);
   else err = make_tensor_map_2d(&ta, op.a, 2, g.K, g.M, op.a_ld, BF16_BK);   // rows = reduction, cols = M
   if (err) return err;
@@ -1814,6 +1841,14 @@ const char* launch_gemm_fp8(const GemmOperands& op, const GemmShape& g, const Ge
   const int grid = work < sm_count() ? work : sm_count();
   gemm_fp8_kernel<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, gs, es, status);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm_fp8_kernel launch failed";
+}
+
+const char* launch_gather_jobs(const int64_t* jobs, int n_jobs, cudaStream_t stream) {
+  if (n_jobs <= 0) return nullptr;
+  int blocks = (n_jobs + 3) / 4;
+  if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+  gather_jobs_kernel<<<blocks, 128, 0, stream>>>(jobs, n_jobs);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gather_jobs_kernel launch failed";
 }
 
 static int g_mx_pair = -1;   // -1: take GDNET_MX_PAIR from the environment on first use
@@ -1886,7 +1921,10 @@ const char* launch_gemm_fp8_mx(const GemmOperands& op, const GemmShape& g, const
     if (perr != nullptr || launched) return perr;
   }
   CUtensorMap ta, tb;
-  const char* err = make_tensor_map_2d(&ta, op.a, 1, g.M, g.K, op.a_ld, BM);
+  const char* err;
+  // the single-CTA kernel carries no gather jobs: copy first, in stream order (its B is then complete)
+  if (g.jobs != nullptr && (err = launch_gather_jobs(g.jobs, g.n_jobs, stream)) != nullptr) return err;
+  err = make_tensor_map_2d(&ta, op.a, 1, g.M, g.K, op.a_ld, BM);
   if (err) return err;
   err = make_tensor_map_2d(&tb, op.b, 1, g.N, g.K, op.b_ld, MX_BN);
   if (err) return err;

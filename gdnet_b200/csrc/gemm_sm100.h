@@ -34,7 +34,23 @@ struct GemmShape {
   int splits;       // split-K shares (set by the launcher)
   const uint8_t* sfa_packed;  // hardware-scaled fp8: UE8M0 chunks of A, (M/128, K/128, 512) bytes
   const uint8_t* sfb_packed;  // hardware-scaled fp8: UE8M0 chunks of B, (N/128, K/128, 512) bytes
+  // Parameter all-gather carried by the GEMM (CTA-pair kernels; the launcher runs a plain copy kernel first when
+  // another kernel form is chosen). `jobs`: n_jobs x 4 int64 words (src, dst, counter, 16-byte vectors), see
+  // run_gather_jobs: the second CTA of every pair has an idle warp (only the leader issues the MMAs) that pulls
+  // the listed ranges from their owners' memory into this GPU's staging area while the tensor cores work, and
+  // adds one to each job's counter when its bytes have landed.
+  const int64_t* jobs;
+  int n_jobs;
+  // Hardware-scaled fp8 pair kernel: when set, rows [128 nb, 128 nb + 128) of B and chunk row nb of its packed
+  // scales are being gathered by this very launch; the producer warp waits (bounded) for the counters b_ready[nb]
+  // and sfb_ready[nb] to reach b_target and sfb_target before the first bulk copy of a tile in column block nb.
+  const uint32_t* b_ready;
+  const uint32_t* sfb_ready;
+  uint32_t b_target, sfb_target;
 };
+
+// Stand-alone form of the gather jobs (one warp per job slot), for launches that cannot carry them.
+const char* launch_gather_jobs(const int64_t* jobs, int n_jobs, cudaStream_t stream);
 
 // Applied in this order to the fp32 accumulator of element (m, n):
 //   v = acc * row_scale(m) + bias[n];  aux;  pre_out = v;  v = act(v);  out (+)= v

@@ -227,8 +227,9 @@ def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
 
 
 def clear_caches() -> None:
-    global _shared_weights
+    global _shared_weights, _weight_stream
     _shared_weights = None
+    _weight_stream = None
     _f32_cache.clear()
     _wq_cache.clear()
     _taps_cache.clear()
@@ -236,6 +237,52 @@ def clear_caches() -> None:
     _side_offers.clear()
     _seg_tables.clear()
     _sigma_plans.clear()
+
+
+# --------------------------------------------------------------------------------------
+# fully sharded parameters: gradient handles and the weight stream
+# --------------------------------------------------------------------------------------
+class GradRef:
+    """Handle of a gradient that lives sharded over the ranks (no local full-size buffer): a registered virtual
+    sink, the flat element offset of the matrix in it, its shape and row pitch. Stands where a ``main_grad``
+    tensor would; the weight-gradient GEMM epilogue and ``peer_add_at`` add into the owner rank's shard."""
+
+    __slots__ = ("sink", "off", "rows", "cols", "ld")
+
+    def __init__(self, sink, off, rows, cols, ld=None):
+        self.sink, self.off, self.rows, self.cols, self.ld = int(sink), int(off), int(rows), int(cols), int(ld or cols)
+
+    def col_range(self, c0, n):
+        return GradRef(self.sink, self.off + c0, self.rows, n, self.ld)
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+
+_weight_stream = None
+_shape_dummies: dict = {}
+
+
+def _shape_only(device, M, N):
+    """A (M, N) fp32 tensor without storage of its own (one element, stride 0): carries a shape to a binding."""
+    d = _shape_dummies.get(device)
+    if d is None:
+        d = torch.zeros(1, dtype=F32, device=device)
+        _shape_dummies[device] = d
+    return d.expand(M, N)
+
+
+def set_weight_stream(ws) -> None:
+    """Install (or remove, with None) the provider of fully sharded layer weights
+    (:class:`gdnet_b200.parallel.weight_stream.WeightStream`)."""
+    global _weight_stream
+    _weight_stream = ws
+
+
+def _attach_gather() -> None:
+    if _weight_stream is not None:
+        _weight_stream.attach()
 
 
 # --------------------------------------------------------------------------------------
@@ -251,6 +298,12 @@ def gemm_bf16(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=BF16, accumul
     """
     M = a.shape[1] if a_mn else a.shape[0]
     N = b.shape[1] if b_mn else b.shape[0]
+    _attach_gather()
+    if isinstance(out, GradRef):
+        # fp32 accumulation into the owner rank's shard of a gradient (the tensor only carries the shape)
+        K.gemm_bf16(a, b, a_mn, b_mn, _shape_only(a.device, M, N), True, None, None, None, 0, 0.0, None, 0, None, None, 0,
+                    None, out.sink, out.off, out.ld)
+        return out
     if out is None:
         if out_dtype == F32:
             # a fresh fp32 result is a weight-gradient shape (few tiles, long reduction): start from zeros and
@@ -284,6 +337,7 @@ def gemm_fp8_mx(a8, pa, b8, pb, *, out=None, out_dtype=BF16, accumulate=False, b
     M, N = a8.shape[0], b8.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a8.device)
+    _attach_gather()
     K.gemm_fp8_mx(a8, pa, b8, pb, out, accumulate, bias, row_scale, aux, aux_mode, pre_out, act, q8, q8_p, q8_silu,
                   store_out)
     return out
@@ -424,6 +478,14 @@ def _main_grad(p):
 
 def accumulate_main_grad(mg, g) -> None:
     """mg += g for a ``main_grad`` view; over NVLink into the owning rank's buffer when gradients are spread."""
+    if isinstance(mg, GradRef):
+        g = g.reshape(mg.rows, mg.cols)
+        if mg.ld == mg.cols:
+            K.peer_add_at(mg.sink, mg.off, g.contiguous())
+        else:
+            for r in range(mg.rows):
+                K.peer_add_at(mg.sink, mg.off + r * mg.ld, g[r].contiguous())
+        return
     if _spread_grads:
         K.peer_add(mg, g.contiguous())
     else:
@@ -449,7 +511,8 @@ def _sink_vecs(params, packed, views, mgs=None):
     or gradients spread over ranks) go one by one."""
     if mgs is None:
         mgs = [_main_grad(p) for p in params]
-    batch = [] if _spread_grads else [i for i, m in enumerate(mgs) if m is not None and m.dtype == F32 and m.is_contiguous()]
+    batch = [] if _spread_grads else [i for i, m in enumerate(mgs) if m is not None and not isinstance(m, GradRef)
+                                      and m.dtype == F32 and m.is_contiguous()]
     out = [None] * len(params)
     for i, (p, v) in enumerate(zip(params, views)):
         if i not in batch:
@@ -705,7 +768,8 @@ def _wgrad_bf16_cat(dy, xs, w):
     tgt, is_main = _wgrad_target(w)
     o = 0
     for x in xs:
-        gemm_bf16(dy, x, a_mn=True, b_mn=True, out=tgt[:, o : o + x.shape[1]], accumulate=True)
+        part = tgt.col_range(o, x.shape[1]) if isinstance(tgt, GradRef) else tgt[:, o : o + x.shape[1]]
+        gemm_bf16(dy, x, a_mn=True, b_mn=True, out=part, accumulate=True)
         o += x.shape[1]
     return None if is_main else tgt.to(w.dtype)
 
@@ -920,20 +984,31 @@ class _LayerStepFn(torch.autograd.Function):
 
         # recovery MLP: z = W2r silu(W1r [s ; c] + b1r) + b2r
         h1_pre = torch.empty(M, d, dtype=BF16, device=dev)
-        if fp8:
+        # fully sharded weights: the operands of this step come from the weight stream (gathered from their owners
+        # by the GEMMs themselves); otherwise they are derived from the local parameters and cached
+        W = None
+        if _weight_stream is not None and _weight_stream.owns(rW1):
+            if not fp8:
+                raise RuntimeError("fully sharded layer weights need the FP8 block recipe for the recovery MLP")
+            W = _weight_stream.acquire(rW1, "F")
+        if fp8 and W is not None:
+            q1q, q1p, q2q, q2p = W.q1, W.p1, W.q2, W.p2
+        elif fp8:
             q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
+            q1q, q1p, q2q, q2p = q1.q, q1.p, q2.q, q2.p
+        if fp8:
             # silu(h1) leaves the first GEMM already quantised for the second; h1 and silu(h1) in bf16 are
             # written only when a backward will need them
             a8 = torch.empty(M, d, dtype=FP8, device=dev)
             pa = packed_buffer(M, d, dev)
             if train:
                 a1 = torch.empty(M, d, dtype=BF16, device=dev)
-                gemm_fp8_mx(u8, pu, q1.q, q1.p, out=a1, bias=f32(rb1), pre_out=h1_pre, act=ACT_SILU, q8=a8, q8_p=pa)
+                gemm_fp8_mx(u8, pu, q1q, q1p, out=a1, bias=f32(rb1), pre_out=h1_pre, act=ACT_SILU, q8=a8, q8_p=pa)
             else:
                 a1 = None
-                gemm_fp8_mx(u8, pu, q1.q, q1.p, out=h1_pre, bias=f32(rb1), q8=a8, q8_p=pa, q8_silu=True,
+                gemm_fp8_mx(u8, pu, q1q, q1p, out=h1_pre, bias=f32(rb1), q8=a8, q8_p=pa, q8_silu=True,
                             store_out=False)
-            z = gemm_fp8_mx(a8, pa, q2.q, q2.p, bias=f32(rb2))
+            z = gemm_fp8_mx(a8, pa, q2q, q2p, bias=f32(rb2))
         else:
             gemm_bf16(s2, rW1[:, :d], out=h1_pre)
             a1 = torch.empty(M, d, dtype=BF16, device=dev)
@@ -945,8 +1020,8 @@ class _LayerStepFn(torch.autograd.Function):
         parts = (d + 127) // 128
         ssq = torch.empty(M, parts, dtype=F32, device=dev)
         hg_pre = torch.empty(M, d, dtype=BF16, device=dev) if train else None
-        h = gemm_bf16(c, gW1, bias=f32(gb1), act=ACT_SILU, pre_out=hg_pre, ssq_out=ssq)
-        W2w = _folded_w2(gW2, gnw)
+        h = gemm_bf16(c, gW1 if W is None else W.gW1, bias=f32(gb1), act=ACT_SILU, pre_out=hg_pre, ssq_out=ssq)
+        W2w = _folded_w2(gW2, gnw) if W is None else W.W2w
         g_pre = gemm_bf16(h, W2w, bias=f32(gb2), ssq_in=ssq, norm_dim=d, norm_eps=eps_g)
 
         fwd_out = torch.empty(B, T, d, dtype=BF16, device=dev)
@@ -1013,33 +1088,42 @@ class _LayerStepFn(torch.autograd.Function):
                               rowcoef, db2g, dw_r, db2r)
 
         # ---- gate MLP ----
-        W2w = _folded_w2(gW2, gnw)
+        W = None
+        if _weight_stream is not None and _weight_stream.owns(rW1):
+            W = _weight_stream.acquire(rW1, "B")       # gathered by the first GEMM below (or prefetched by the last step)
+        W2w = _folded_w2(gW2, gnw) if W is None else W.W2w
+        gW1_op = gW1 if W is None else W.gW1
+        gW2_raw = gW2.detach() if W is None else W.gW2
         dW2w = gemm_bf16(dq, h, a_mn=True, b_mn=True, out_dtype=F32)
         tgt2, main2 = _wgrad_target(gW2)
         if main2 and _spread_grads:
             dW2 = torch.zeros_like(dW2w)
-            K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), dW2, dgnw)
+            K.unscale_cols_bwd(dW2w, gW2_raw, f32(gnw), dW2, dgnw)
             accumulate_main_grad(tgt2, dW2)
         else:
-            K.unscale_cols_bwd(dW2w, gW2.detach(), f32(gnw), tgt2, dgnw)
+            K.unscale_cols_bwd(dW2w, gW2_raw, f32(gnw), tgt2, dgnw)
         dh_pre = gemm_bf16(dq, W2w, b_mn=True, aux=hg_pre, aux_mode=AUX_RMS_SILU_BWD, rowcoef=rowcoef)
         K.colsum(dh_pre, db1g)
         g_gW1 = _wgrad_bf16(dh_pre, c, gW1)
         dc_view = dsc[:, d:]
-        gemm_bf16(dh_pre, gW1, b_mn=True, out=dc_view, aux=dc_view, aux_mode=AUX_ADD)
+        gemm_bf16(dh_pre, gW1_op, b_mn=True, out=dc_view, aux=dc_view, aux_mode=AUX_ADD)
 
         # ---- recovery MLP ----
         if fp8:
             # data gradients in e4m3 (row-quantised dz, dh1); weight gradients in bf16 with both operands read
             # in place, which needs no transposed quantised copies
-            q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
+            if W is not None:
+                q1t, p1t, q2t, p2t = W.q1, W.p1, W.q2, W.p2
+            else:
+                q1, q2 = quantize_weight(rW1), quantize_weight(rW2)
+                q1t, p1t, q2t, p2t = q1.qt, q1.pt, q2.qt, q2.pt
             g_rW2 = _wgrad_bf16(dz, a1, rW2)
             dh8 = torch.empty(M, d, dtype=FP8, device=dev)      # dh1 quantised by the GEMM that produces it
             pdh = packed_buffer(M, d, dev)
-            dh1 = gemm_fp8_mx(dz8, pdz, q2.qt, q2.pt, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD, q8=dh8, q8_p=pdh)
+            dh1 = gemm_fp8_mx(dz8, pdz, q2t, p2t, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD, q8=dh8, q8_p=pdh)
             K.colsum(dh1, db1r)
             g_rW1 = _wgrad_bf16_cat(dh1, (s2, c), rW1)
-            gemm_fp8_mx(dh8, pdh, q1.qt, q1.pt, out=dsc, aux=dsc, aux_mode=AUX_ADD)
+            gemm_fp8_mx(dh8, pdh, q1t, p1t, out=dsc, aux=dsc, aux_mode=AUX_ADD)
         else:
             g_rW2 = _wgrad_bf16(dz, a1, rW2)
             dh1 = gemm_bf16(dz, rW2, b_mn=True, aux=h1_pre, aux_mode=AUX_MUL_SILU_GRAD)

@@ -44,7 +44,9 @@ ALIGN = 128  # elements; keeps every parameter view 256-byte aligned in bf16
 
 
 class _Group:
-    """All parameters of one dtype, flattened."""
+    """All parameters of one dtype, flattened; every rank holds all of them."""
+
+    sharded = False
 
     def __init__(self, params, dtype, device, world, rank, symmetric, pg):
         self.params, self.dtype = params, dtype
@@ -81,9 +83,84 @@ class _Group:
         self.m = torch.zeros(m_len, dtype=torch.float32, device=device)
         self.v = torch.zeros(m_len, dtype=torch.float32, device=device)
         self.sums = torch.zeros(8, dtype=torch.float32, device=device)
+        if symmetric:
+            self.tab_p, self.tab_gt, self.tab_gi = self._sp.ptr_table, self._sgt.ptr_table, self._sgi.ptr_table
+        self.p_range = (0, self.n)                                   # flat range of the parameters held locally
+        self.mv_range = self.shard if symmetric else (0, self.n)     # flat range the moments cover
 
     def views(self, flat):
         return [flat[o : o + p.numel()].view(p.shape) for p, o in zip(self.params, self.offsets)]
+
+
+class _ShardedGroup:
+    """Large bf16 matrices spread over the ranks, whole matrices, balanced by size: a rank holds the bf16 masters,
+    the two fp32 gradient buffers and the AdamW moments of the matrices it owns and nothing of the others.
+
+    The flat index space is ``world`` segments of ``per`` elements, segment ``r`` holding rank ``r``'s matrices back
+    to back, so everything that works on "this rank's shard of the flat range" (the update kernel, the gradient
+    sinks of the weight-gradient epilogues) applies unchanged. The pointer tables handed to the kernels hold every
+    rank's shard base *minus* that rank's segment offset: ``table[idx / per] + idx`` is element ``idx``.
+    A parameter this rank does not own becomes a one-element placeholder of the right shape (stride 0); its
+    gradient handle is a :class:`gdnet_b200.ops.cuda.GradRef`."""
+
+    sharded = True
+
+    def __init__(self, params, device, world, rank, pg, broadcast_src=None):
+        from ..ops import cuda as cu
+        from ..parallel.symm import SymmBuffer
+
+        self.params, self.dtype = params, torch.bfloat16
+        sizes = [-(-p.numel() // ALIGN) * ALIGN for p in params]
+        load = [0] * world
+        owner = [0] * len(params)
+        for i in sorted(range(len(params)), key=lambda i: (-sizes[i], i)):      # largest first, to the lightest rank
+            r = min(range(world), key=lambda r: (load[r], r))
+            owner[i] = r
+            load[r] += sizes[i]
+        per = -(-max(max(load), ALIGN) // ALIGN) * ALIGN
+        fill = [0] * world
+        offs = []
+        for i in range(len(params)):
+            offs.append(owner[i] * per + fill[owner[i]])
+            fill[owner[i]] += sizes[i]
+        self.owner, self.offsets, self.per, self.n = owner, offs, per, per * world
+        self.shard = (rank * per, (rank + 1) * per)
+        self.index = {id(p): (o, f) for p, o, f in zip(params, owner, offs)}
+        self._sp = SymmBuffer(per * 2, pg, device)
+        self._sgt = SymmBuffer(per * 4, pg, device)
+        self._sgi = SymmBuffer(per * 4, pg, device)
+        self.flat = self._sp.view(torch.bfloat16, per)            # this rank's shard only
+        self.g_task = self._sgt.view(torch.float32, per)
+        self.g_info = self._sgi.view(torch.float32, per)
+
+        def biased(buf, item):
+            return torch.tensor([p - r * per * item for r, p in enumerate(buf.ptrs)], dtype=torch.int64, device=device)
+
+        self.tab_p, self.tab_gt, self.tab_gi = biased(self._sp, 2), biased(self._sgt, 4), biased(self._sgi, 4)
+        self.sink_task = int(cu.K.register_virtual_grad_sink(self.tab_gt, self.n, per))
+        self.sink_info = int(cu.K.register_virtual_grad_sink(self.tab_gi, self.n, per))
+        with torch.no_grad():
+            for p, o, f in zip(params, owner, offs):
+                if broadcast_src is not None:
+                    dist.broadcast(p.data, src=broadcast_src, group=pg)
+                if o == rank:
+                    view = self.flat[f - rank * per : f - rank * per + p.numel()].view(p.shape)
+                    view.copy_(p.data)
+                    p.data = view
+                else:
+                    p.data = torch.zeros(1, dtype=p.dtype, device=device).expand(p.shape)
+                p._gd_owner, p._gd_world, p._gd_rank = o, world, rank
+        self.m = torch.zeros(per, dtype=torch.float32, device=device)
+        self.v = torch.zeros(per, dtype=torch.float32, device=device)
+        self.sums = torch.zeros(8, dtype=torch.float32, device=device)
+        self.p_range = self.shard
+        self.mv_range = self.shard
+
+    def grad_refs(self, which: str):
+        from ..ops.cuda import GradRef
+
+        sink = self.sink_task if which == "task" else self.sink_info
+        return [GradRef(sink, f, p.shape[0], p.shape[1]) for p, f in zip(self.params, self.offsets)]
 
 
 class TrainEngine(nn.Module):
@@ -95,7 +172,7 @@ class TrainEngine(nn.Module):
     def __init__(self, model: nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 1e-2, precision: str = "fp8", process_group=None, sp_group=None,
                  comm: str = "fused", broadcast: bool = True, projection: str = "local",
-                 share_fp8_weights: bool = False, fused_ce: bool = True):
+                 share_fp8_weights: bool = False, fused_ce: bool = True, shard: str = "none"):
         super().__init__()
         self.module = model
         self.precision = precision
@@ -121,25 +198,45 @@ class TrainEngine(nn.Module):
         self.comm = comm if self.distributed else "local"
         if self.comm not in ("fused", "scatter", "nccl", "local"):
             raise ValueError(f"unknown comm backend {comm!r}")
+        if shard not in ("none", "full"):
+            raise ValueError(f"unknown shard mode {shard!r}")
+        # "full": the large layer matrices live on one owner rank each (masters, gradients, moments); the GEMMs
+        # gather the operands they need from the owners (parallel/weight_stream.py). A single GPU has nothing to shard.
+        self.shard = shard if self.distributed else "none"
+        if self.shard == "full":
+            if dev.type != "cuda" or precision != "fp8":
+                raise ValueError('shard="full" needs CUDA and precision="fp8"')
+            self.comm = "scatter"           # gradients go to their owner from the weight-gradient epilogues
         symmetric = self.comm in ("fused", "scatter")
+        if self.comm == "scatter":
+            from ..ops import cuda as cu
+
+            cu.K.clear_grad_sinks()
 
         params = [p for p in model.parameters() if p.requires_grad]
+        sharded_params = self._layer_matrices(model) if self.shard == "full" else []
+        taken = {id(p) for p in sharded_params}
         by_dtype: dict[torch.dtype, list] = {}
         for p in params:
-            by_dtype.setdefault(p.dtype, []).append(p)
+            if id(p) not in taken:
+                by_dtype.setdefault(p.dtype, []).append(p)
         for dt in by_dtype:
             if dt not in (torch.bfloat16, torch.float32):
                 raise TypeError(f"unsupported parameter dtype {dt}")
+        src0 = dist.get_global_rank(self.pg, 0) if self.distributed else None
         self.groups = [
             _Group(ps, dt, dev, self.world, self.rank, symmetric, self.pg) for dt, ps in by_dtype.items()
         ]
+        if sharded_params:
+            self.groups.append(_ShardedGroup(sharded_params, dev, self.world, self.rank, self.pg,
+                                             broadcast_src=src0 if broadcast else None))
         self.params = params
         if self.distributed and broadcast:
-            src = dist.get_global_rank(self.pg, 0)
             for g in self.groups:
-                dist.broadcast(g.flat, src=src, group=self.pg)
+                if not g.sharded:
+                    dist.broadcast(g.flat, src=src0, group=self.pg)
             for b in model.buffers():
-                dist.broadcast(b, src=src, group=self.pg)
+                dist.broadcast(b, src=src0, group=self.pg)
         if symmetric:
             from ..parallel.symm import SymmBuffer
 
@@ -149,15 +246,16 @@ class TrainEngine(nn.Module):
         if self.comm == "scatter":
             from ..ops import cuda as cu
 
-            cu.K.clear_grad_sinks()
             for g in self.groups:
-                cu.K.register_grad_sink(g.g_task, g._sgt.ptr_table, g.per)
-                cu.K.register_grad_sink(g.g_info, g._sgi.ptr_table, g.per)
+                if not g.sharded:
+                    cu.K.register_grad_sink(g.g_task, g._sgt.ptr_table, g.per)
+                    cu.K.register_grad_sink(g.g_info, g._sgi.ptr_table, g.per)
             cu.set_spread_grads(True)
         self.scalars = torch.zeros(2, dtype=torch.float32, device=dev)
         if dev.type == "cuda":
             from ..ops import cuda as cu
 
+            cu.set_spread_grads(self.comm == "scatter")
             cu.clear_caches()     # cached copies made from the pre-flattening parameter storages
             if share_fp8_weights and symmetric and precision == "fp8":
                 # each FP8 weight is quantised by one rank per update and stored into every rank's cache by
@@ -173,6 +271,55 @@ class TrainEngine(nn.Module):
                         uniq.append(w)
                 if uniq:
                     cu.share_fp8_weights(uniq, self.pg, dev)
+            self.weight_stream = None
+            if self.shard == "full":
+                from ..parallel.weight_stream import LayerSet, WeightStream
+
+                sets = []
+                for layer in model.layers:
+                    for g_, r_ in (("gf", "rf"), ("gb", "rb")):
+                        sets.append(LayerSet(getattr(layer, f"{r_}_W1").weight, getattr(layer, f"{r_}_W2").weight,
+                                             getattr(layer, f"{g_}_W1").weight, getattr(layer, f"{g_}_W2").weight,
+                                             getattr(layer, f"{g_}_norm").weight))
+                self.weight_stream = WeightStream(self.pg, dev, self.groups[-1], sets)
+                cu.set_weight_stream(self.weight_stream)
+
+    @staticmethod
+    def _layer_matrices(model):
+        """The parameters that ``shard="full"`` spreads over the ranks: the eight large matrices of every GDLayer."""
+        out = []
+        for layer in getattr(model, "layers", []):
+            for prefix in ("gf", "gb", "rf", "rb"):
+                for which in ("W1", "W2"):
+                    w = getattr(layer, f"{prefix}_{which}").weight
+                    if w.dtype != torch.bfloat16 or w.dim() != 2 or w.shape[0] % 128 or w.shape[1] % 128:
+                        raise ValueError('shard="full" needs bf16 layer matrices with dimensions that are multiples of 128')
+                    out.append(w)
+        return out
+
+    def full_state_dict(self) -> dict:
+        """The model's ``state_dict`` with every parameter complete on every rank. Collective when matrices are
+        sharded (each is broadcast by its owner); otherwise the plain ``state_dict``."""
+        base = unwrap(self.module)
+        sd = base.state_dict()
+        names = {id(p): n for n, p in base.named_parameters()}
+        for g in self.groups:
+            if not g.sharded:
+                continue
+            for p, o in zip(g.params, g.owner):
+                t = p.data.clone() if o == self.rank else torch.empty(p.shape, dtype=p.dtype, device=self.device)
+                dist.broadcast(t, src=dist.get_global_rank(self.pg, o), group=self.pg)
+                sd[names[id(p)]] = t
+        return sd
+
+    def resident_bytes(self) -> dict:
+        """Bytes of parameters, gradients and optimizer state this rank holds (for reports and tests)."""
+        out = {"params": 0, "grads": 0, "optimizer": 0}
+        for g in self.groups:
+            out["params"] += g.flat.numel() * g.flat.element_size()
+            out["grads"] += (g.g_task.numel() + g.g_info.numel()) * 4
+            out["optimizer"] += (g.m.numel() + g.v.numel()) * 4
+        return out
 
     # -- nn.Module plumbing -----------------------------------------------------------------
     def forward(self, *a, **kw):
@@ -184,7 +331,8 @@ class TrainEngine(nn.Module):
     # -- gradient buffers -------------------------------------------------------------------
     def _point_main_grad(self, which: str) -> None:
         for g in self.groups:
-            for p, v in zip(g.params, g.views(g.g_task if which == "task" else g.g_info)):
+            handles = g.grad_refs(which) if g.sharded else g.views(g.g_task if which == "task" else g.g_info)
+            for p, v in zip(g.params, handles):
                 p.main_grad = v
 
     def _fold_autograd_grads(self) -> None:
@@ -255,6 +403,9 @@ class TrainEngine(nn.Module):
 
         cu.invalidate_param_caches()
         cu.refresh_shared_weights()     # collective, here where every rank is at the same point of the step
+        if getattr(self, "weight_stream", None) is not None:
+            self.weight_stream.refresh()    # owners re-derive the GEMM operands of their matrices (collective)
+            self.weight_stream.end_step()
         return total
 
     def update_times_ms(self) -> list[float]:
@@ -326,7 +477,7 @@ class TrainEngine(nn.Module):
                 if grad_clip > 0.0:
                     self.scalars[1] = self._clip_factor(red, coef, beta, grad_clip)
             for gi, g in enumerate(self.groups):
-                K.allreduce_adamw(g._sgt.ptr_table, g._sgi.ptr_table, g._sp.ptr_table, self._flags.ptr_table,
+                K.allreduce_adamw(g.tab_gt, g.tab_gi, g.tab_p, self._flags.ptr_table,
                                   g.m, g.v, self.scalars, g.n, self.rank, self.world,
                                   self.comm_seq * 8 + gi, phase, g.dtype == torch.bfloat16, *common, g.sums)
 
@@ -349,9 +500,10 @@ class TrainEngine(nn.Module):
                 self.scalars[0] = coef
                 self.scalars[1] = self._clip_factor(red, coef, beta, grad_clip) if grad_clip > 0.0 else 1.0
             for gi, g in enumerate(self.groups):
-                K.allreduce_adamw(g._sgt.ptr_table, g._sgi.ptr_table, g._sp.ptr_table, self._flags.ptr_table,
+                K.allreduce_adamw(g.tab_gt, g.tab_gi, g.tab_p, self._flags.ptr_table,
                                   g.m, g.v, self.scalars, g.n, self.rank, self.world,
-                                  self.comm_seq * 8 + gi, phase, g.dtype == torch.bfloat16, *common, g.sums)
+                                  self.comm_seq * 8 + gi, phase, g.dtype == torch.bfloat16, *common, g.sums,
+                                  not g.sharded)
 
     @staticmethod
     def _clip_factor(red, coef, beta, grad_clip):
@@ -365,10 +517,20 @@ class TrainEngine(nn.Module):
         self.lr = float(lr)
 
     def state_dict_optim(self) -> dict:
-        return {"step": self.step_count, "lr": self.lr,
+        return {"step": self.step_count, "lr": self.lr, "world": self.world, "rank": self.rank,
                 "m": [g.m.clone() for g in self.groups], "v": [g.v.clone() for g in self.groups]}
 
     def load_state_dict_optim(self, sd: dict) -> None:
+        """Inverse of :meth:`state_dict_optim` for the same world size and sharding (the moments are this rank's
+        own); anything else goes through ``runtime.ckpt.save_sharded`` / ``load_sharded``, which re-slice."""
+        if len(sd["m"]) != len(self.groups):
+            raise ValueError(f"optimizer state has {len(sd['m'])} groups, the engine {len(self.groups)}")
+        if int(sd.get("world", self.world)) != self.world or int(sd.get("rank", self.rank)) != self.rank:
+            raise ValueError(f"optimizer state of rank {sd.get('rank')} / world {sd.get('world')} cannot be loaded into "
+                             f"rank {self.rank} / world {self.world}: use a sharded checkpoint")
+        for g, m, v in zip(self.groups, sd["m"], sd["v"]):
+            if m.numel() != g.m.numel() or v.numel() != g.v.numel():
+                raise ValueError(f"optimizer moments have {m.numel()} elements, this rank holds {g.m.numel()}")
         self.step_count, self.lr = int(sd["step"]), float(sd["lr"])
         for g, m, v in zip(self.groups, sd["m"], sd["v"]):
             g.m.copy_(m)

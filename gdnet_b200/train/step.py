@@ -55,6 +55,15 @@ def sn_soft_penalty(layers, scale: float = 0.1, generator: torch.Generator | Non
     (reference: gdnet/loss.py:15-31).
     """
     mats = [getattr(layer, a).weight for layer in layers for a in SN_ATTRS]
+    if mats and getattr(mats[0], "_gd_owner", None) is not None:
+        # matrices spread over the ranks (full-shard engine): every matrix is probed by its owner alone. The
+        # ranks' gradients are averaged afterwards, so the owner's term counts `world` times to weigh the same
+        # as in the replicated case, where every rank adds it.
+        world = mats[0]._gd_world
+        mats = [W for W in mats if W._gd_owner == W._gd_rank]
+        if not mats:
+            return torch.zeros((), device=layers[0].gf_norm.weight.device)
+        scale = scale * world
     sig = spectral.sigma_estimates(mats, generator=generator)
     return scale * torch.relu(sig - 1.0).pow(2).sum()
 

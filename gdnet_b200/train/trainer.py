@@ -29,7 +29,7 @@ from ..data import (CopyTaskDataset, FineWebEduDataset, NemotronDataset, PackedT
                     SyntheticPackedDataset)
 from ..models.gdnet import GDNet
 from ..parallel import groups
-from ..runtime.ckpt import load_ckpt, save_ckpt
+from ..runtime.ckpt import load_ckpt, load_sharded, save_ckpt, save_sharded
 from ..runtime.metrics import MetricsLog, StepTimer
 from ..runtime.watchdog import Heartbeat, Watchdog
 from ..utils.fp8 import cast_for_precision, update_fp8_scales
@@ -240,7 +240,7 @@ def train(cfg: Config, interactive: bool = True) -> State:
         from .engine import TrainEngine
 
         runner = TrainEngine(model, lr=cfg.lr, betas=(cfg.beta1, cfg.beta2), weight_decay=cfg.weight_decay,
-                             precision=cfg.precision, sp_group=sp_group, comm=cfg.comm)
+                             precision=cfg.precision, sp_group=sp_group, comm=cfg.comm, shard=cfg.shard)
         optimizer, params = None, None
         set_lr, get_lr = runner.set_lr, (lambda: runner.lr)
     else:
@@ -259,11 +259,19 @@ def train(cfg: Config, interactive: bool = True) -> State:
 
         get_lr = lambda: optimizer.param_groups[0]["lr"]
 
+    # With several GPUs the engine keeps AdamW moments (and, fully sharded, the layer matrices) only for its own
+    # shard, so a checkpoint is a directory to which every rank writes its part; one GPU writes the single file.
+    sharded_ckpt = use_engine and world > 1
     step, cursor = 0, {}
     if cfg.resume:
-        step, cursor = load_ckpt(Path(cfg.resume), model, optimizer)
-        if use_engine and cursor.get("engine_optim"):
-            runner.load_state_dict_optim(cursor["engine_optim"])
+        if Path(cfg.resume).is_dir():
+            if not use_engine:
+                raise ValueError("a sharded checkpoint directory can only be resumed by the training engine")
+            step, cursor = load_sharded(Path(cfg.resume), runner)
+        else:
+            step, cursor = load_ckpt(Path(cfg.resume), model, optimizer)
+            if use_engine and cursor.get("engine_optim"):
+                runner.load_state_dict_optim(cursor["engine_optim"])
 
     ckpt_dir = Path(cfg.ckpt_dir)
     state = State(total_steps=cfg.total_steps, step=step)
@@ -282,12 +290,29 @@ def train(cfg: Config, interactive: bool = True) -> State:
             watchdog.start()
 
     def checkpoint(tag: str, windows_done: int, phase_idx: int) -> None:
+        """Every rank calls this at the same step. One GPU: the reference's single file, written by the only
+        rank. Several GPUs with the engine: a directory with one shard file per rank."""
+        if sharded_ckpt:
+            extra = {"phase": phase_idx, "windows_done": windows_done}
+            save_sharded(ckpt_dir / f"step_{step:07d}{tag}", step, runner, extra)
+            return
+        if not main_proc:
+            return
         extra = {"phase": phase_idx, "windows_done": windows_done, "rng": torch.get_rng_state()}
         if use_engine:
             extra["engine_optim"] = runner.state_dict_optim()
         save_ckpt(ckpt_dir / f"step_{step:07d}{tag}.pt", step, model, optimizer, None, extra)
 
+    def agree(flags: list[bool]) -> list[bool]:
+        """Rank 0's decisions (stop, manual save), made known to every rank: they come from its console."""
+        if world == 1:
+            return flags
+        t = torch.tensor([int(f) for f in flags], device=device, dtype=torch.int32)
+        dist.broadcast(t, src=0)
+        return [bool(x) for x in t.tolist()]
+
     windows_done, phase_idx = 0, 0
+    stopping, clean_exit = False, False
     try:
         phase_start = 0
         for phase_idx, phase in enumerate(cfg.phases):
@@ -317,7 +342,7 @@ def train(cfg: Config, interactive: bool = True) -> State:
             cols = slice(sp_rank * T_local, (sp_rank + 1) * T_local)
 
             for batch in CudaPrefetcher(loader, device):
-                if step >= phase_end or stop_event.is_set():
+                if step >= phase_end or stopping:
                     break
                 mask = None
                 if isinstance(batch, (tuple, list)):          # copy task: (tokens, targets, loss mask)
@@ -351,17 +376,28 @@ def train(cfg: Config, interactive: bool = True) -> State:
                         metrics.log(step, loss=loss_val, lr=state.lr, tok_per_sec=state.tok_per_sec,
                                     ms_per_step=wall_ms, device_ms_per_step=dev_ms)
                     timer.start()
-                if main_proc and step % cfg.ckpt_every == 0:
+                if step % cfg.ckpt_every == 0:
                     checkpoint("", windows_done, phase_idx)
-                if main_proc and save_event.is_set():
-                    save_event.clear()
-                    checkpoint("_manual", windows_done, phase_idx)
-            if stop_event.is_set():
+                if step % cfg.log_every == 0 or world == 1:
+                    # the console commands of rank 0 take effect on all ranks at the same step
+                    stopping, manual = agree([stop_event.is_set(), save_event.is_set()])
+                    if manual:
+                        save_event.clear()
+                        checkpoint("_manual", windows_done, phase_idx)
+            if stopping:
                 break
             phase_start = phase_end
+        clean_exit = True
     finally:
-        if main_proc:
+        # after an error the ranks are no longer in step: each writes what it can on its own, which for a sharded
+        # checkpoint is its own shard file (the manifest comes from rank 0)
+        try:
             checkpoint("_final", windows_done, phase_idx)
+        except Exception as exc:                      # never mask the error that ended the run
+            if clean_exit:
+                raise
+            print(f"[rank {rank}] final checkpoint failed: {exc}", flush=True)
+        if main_proc:
             stop_event.set()
             metrics.close()
             if watchdog is not None:

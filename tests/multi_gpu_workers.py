@@ -208,6 +208,105 @@ def sp_engine_step(rank, world, dev):
     assert losses[-1] < losses[0] + 1.0
 
 
+def engine_full_shard_vs_replicated(rank, world, dev):
+    """Layer matrices, their gradients and AdamW moments spread over the ranks, operands gathered by the GEMMs that
+    consume them, against the same engine with everything replicated (both reduce gradients from the epilogues):
+    same losses, same parameters after three steps with memory write chunks, 1/world of the matrices resident."""
+    from gdnet_b200.ops import cuda as cu
+
+    base = _model(dev)
+    g = torch.Generator(device="cpu").manual_seed(400 + rank)
+    data = [(torch.randint(0, 1024, (2, 256), generator=g).to(dev), torch.randint(0, 1024, (2, 256), generator=g).to(dev),
+             torch.randint(0, 1024, (2, 2, 256), generator=g).to(dev)) for _ in range(3)]
+    results = {}
+    for shard in ("none", "full"):
+        eng = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="scatter", shard=shard)
+        losses = []
+        for step, (tok, tgt, wc) in enumerate(data):
+            torch.manual_seed(7 + step)
+            losses.append(float(eng.projected_step(tok, tgt, write_chunks=wc, grad_clip=1.0 if step == 2 else 0.0)))
+        torch.cuda.synchronize()
+        _ext.check_status(tok)
+        sd = {k: v.float().clone() for k, v in eng.full_state_dict().items() if v.is_floating_point()}
+        results[shard] = (losses, sd, eng.resident_bytes())
+        if shard == "full":
+            ws = eng.weight_stream
+            assert ws is not None and ws.order, "the order of the layer sets was not learnt"
+            assert ws.gathered_bytes > 0, "nothing was gathered from the owner ranks"
+            sg = eng.groups[-1]
+            assert sg.sharded and sg.flat.numel() * world == sg.n
+            owned = sum(o == rank for o in sg.owner)
+            assert 0 < owned < len(sg.owner), "this rank owns all or none of the layer matrices"
+            # a forward outside the training step (other order of requests) still finds its weights
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                out = eng(tok)[0]
+            assert bool(torch.isfinite(out.float()).all())
+            torch.cuda.synchronize()
+            _ext.check_status(tok)
+        dist.barrier()
+        cu.set_weight_stream(None)
+        cu.clear_caches()
+        del eng
+    (l0, p0, b0), (l1, p1, b1) = results["none"], results["full"]
+    assert all(abs(a - b) < 5e-3 * max(1.0, abs(a)) for a, b in zip(l0, l1)), (l0, l1)
+    worst = max((p0[k] - p1[k]).abs().max().item() for k in p0)
+    assert worst < 2e-2, f"full-shard and replicated parameters differ by {worst}"
+    layer_bytes = sum(v.numel() * 2 for k, v in p1.items() if k.startswith("layers.") and v.dim() == 2 and v.shape[0] >= 128)
+    assert b0["params"] - b1["params"] >= layer_bytes * (world - 1) // world - 4096 * world, (b0, b1, layer_bytes)
+    if rank == 0:
+        print(f"full-shard: losses {l1}, max parameter difference {worst:.3g}, resident bytes {b1} against {b0}")
+
+
+def engine_ckpt_roundtrip(rank, world, dev):
+    """Step, save a sharded checkpoint, step again; then a fresh engine loads the checkpoint and takes the same
+    step: both end with the same parameters and moments (every rank holds only its shard of the moments, so a
+    checkpoint that kept one rank's moments for everybody would show here)."""
+    import tempfile
+
+    from gdnet_b200.ops import cuda as cu
+    from gdnet_b200.runtime.ckpt import load_sharded, save_sharded
+
+    base = _model(dev)
+    g = torch.Generator(device="cpu").manual_seed(500 + rank)
+    data = [(torch.randint(0, 1024, (2, 256), generator=g).to(dev), torch.randint(0, 1024, (2, 256), generator=g).to(dev))
+            for _ in range(3)]
+    box = [tempfile.mkdtemp() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    path = box[0]
+    for shard in ("none", "full"):
+        eng = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="scatter" if shard == "full" else "fused", shard=shard)
+        for step in range(2):
+            torch.manual_seed(7 + step)
+            eng.projected_step(*data[step])
+        save_sharded(os.path.join(path, shard), 2, eng, {"cursor": 5})
+        torch.manual_seed(9)
+        eng.projected_step(*data[2])
+        torch.cuda.synchronize()
+        want_p = {k: v.float().clone() for k, v in eng.full_state_dict().items() if v.is_floating_point()}
+        want_m = [gr.m.clone() for gr in eng.groups]
+        dist.barrier()
+        cu.set_weight_stream(None)
+        cu.clear_caches()
+        del eng
+        torch.manual_seed(123)       # other initial weights: everything must come from the checkpoint
+        eng2 = TrainEngine(_model(dev, seed=1), lr=1e-2, precision="fp8", comm="scatter" if shard == "full" else "fused", shard=shard)
+        step, extra = load_sharded(os.path.join(path, shard), eng2)
+        assert step == 2 and extra == {"cursor": 5} and eng2.step_count == 2
+        torch.manual_seed(9)
+        eng2.projected_step(*data[2])
+        torch.cuda.synchronize()
+        _ext.check_status(data[0][0])
+        got_p = {k: v.float() for k, v in eng2.full_state_dict().items() if v.is_floating_point()}
+        worst = max((want_p[k] - got_p[k]).abs().max().item() for k in want_p)
+        assert worst < 1e-2, f"{shard}: parameters after resume differ by {worst}"
+        for a, b in zip(want_m, [gr.m for gr in eng2.groups]):
+            assert (a - b).abs().max().item() < 1e-3 * (a.abs().max().item() + 1e-6) + 1e-6, f"{shard}: AdamW moments differ after resume"
+        dist.barrier()
+        cu.set_weight_stream(None)
+        cu.clear_caches()
+        del eng2
+
+
 if __name__ == "__main__":
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])

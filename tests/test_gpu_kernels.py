@@ -331,3 +331,96 @@ def test_gemm_bf16_strided_outputs_and_edges():
         _close(pre[:, :N], base, 2e-2, 2e-2, "pre_out slice")
         assert torch.all(pre[:, N:] == 7.0), "columns beside the pre_out slice were touched"
         _close(out, F.silu(base), 2e-2, 2e-2, "silu out")
+
+
+# ---------------------------------------------------------------------------------------
+# parameter gather carried by the GEMMs
+# ---------------------------------------------------------------------------------------
+def _jobs(src, dst, counters, first, chunks, chunk_bytes, subs):
+    """Job rows (src, dst, counter, 16-byte vectors) for `chunks` ranges of `chunk_bytes`, each cut in `subs` pieces."""
+    rows = []
+    piece = chunk_bytes // subs
+    for c in range(chunks):
+        for j in range(subs):
+            o = c * chunk_bytes + j * piece
+            rows.append([src.data_ptr() + o, dst.data_ptr() + o, counters.data_ptr() + 4 * (first + c) if counters is not None else 0,
+                         piece // 16])
+    return rows
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 256, 256), (4096, 1024, 2048), (384, 256, 256)])
+def test_gemm_fp8_mx_gathers_its_own_b_operand(M, N, K):
+    """The hardware-scaled FP8 GEMM with its B operand (e4m3 rows and packed scales) arriving through gather jobs
+    that the same launch carries: the producer warp waits for the per-128-row counters, so the result must equal
+    the GEMM on the source buffers. The "owner's" memory is this GPU's own; M = 384 takes the single-CTA kernel,
+    where the launcher copies first."""
+    cu = _cu()
+    a8, sa, b8, sb = _mx_operands(M, N, K, True)
+    pa, pb = ref.pack_ue8m0_rows(sa), ref.pack_ue8m0_blocks(sb)
+    want = cu.gemm_fp8_mx(a8, pa, b8, pb, out_dtype=torch.float32)
+    nb = N // 128
+    stage_q = torch.zeros_like(b8.view(torch.uint8))
+    stage_p = torch.zeros_like(pb)
+    cnt = torch.zeros(2 * nb, dtype=torch.int32, device=DEV)
+    rows = _jobs(b8.view(torch.uint8), stage_q, cnt, 0, nb, 128 * K, 2) + _jobs(pb, stage_p, cnt, nb, nb, (K // 128) * 512, 1)
+    table = torch.tensor(rows, dtype=torch.int64, device=DEV)
+    for use in (1, 2):
+        stage_q.zero_()
+        stage_p.zero_()
+        cu.K.attach_gather_jobs(table)
+        cu.K.attach_b_ready(cnt[:nb], cnt[nb:], 2 * use, use)
+        got = cu.gemm_fp8_mx(a8, pa, stage_q.view(torch.float8_e4m3fn), stage_p, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        _status_clean(a8)
+        assert torch.equal(stage_q, b8.view(torch.uint8)) and torch.equal(stage_p, pb), "gathered bytes differ from the source"
+        assert torch.equal(got, want), f"use {use}: GEMM on the gathered operand differs"
+        assert cnt[:nb].tolist() == [2 * use] * nb and cnt[nb:].tolist() == [use] * nb
+
+
+def test_gather_jobs_ride_on_bf16_gemm_and_stand_alone():
+    cu = _cu()
+    src = torch.randint(0, 255, (3 * 1024 * 1024 + 4096,), dtype=torch.uint8, device=DEV)
+    dst = torch.zeros_like(src)
+    cnt = torch.zeros(4, dtype=torch.int32, device=DEV)
+    rows = _jobs(src, dst, cnt, 0, 3, 1024 * 1024, 16) + _jobs(src[3 * 1024 * 1024 :], dst[3 * 1024 * 1024 :], None, 0, 1, 4096, 1)
+    table = torch.tensor(rows, dtype=torch.int64, device=DEV)
+    a = torch.randn(1024, 512, device=DEV).bfloat16()
+    b = torch.randn(256, 512, device=DEV).bfloat16()
+    want = cu.gemm_bf16(a, b)
+    cu.K.attach_gather_jobs(table)
+    got = cu.gemm_bf16(a, b)
+    torch.cuda.synchronize()
+    _status_clean(a)
+    assert torch.equal(got, want) and torch.equal(dst, src)
+    assert cnt.tolist() == [16, 16, 16, 0]
+    dst.zero_()
+    cu.K.gather_jobs(table)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src) and cnt.tolist() == [32, 32, 32, 0]
+
+
+def test_wgrad_into_virtual_gradient_sink():
+    """A weight-gradient GEMM whose fp32 destination is addressed as (sink, flat offset) instead of a tensor: the
+    form used when gradients are sharded over the ranks and no rank holds a full-size buffer."""
+    cu = _cu()
+    per = 4 * 256 * 128
+    shard = torch.zeros(per, device=DEV)
+    # a world of one whose shard starts at flat offset 0: the biased table is the plain address
+    table = torch.tensor([shard.data_ptr()], dtype=torch.int64, device=DEV)
+    cu.K.clear_grad_sinks()
+    try:
+        sink = int(cu.K.register_virtual_grad_sink(table, per, per))
+        M, N, Kd = 512, 256, 256
+        dy, x = torch.randn(M, N, device=DEV).bfloat16(), torch.randn(M, Kd, device=DEV).bfloat16()
+        ref_ = cu.GradRef(sink, 256 * 128, N, Kd)
+        cu.gemm_bf16(dy, x[:, :128], a_mn=True, b_mn=True, out=ref_.col_range(0, 128), accumulate=True)
+        cu.gemm_bf16(dy, x[:, 128:], a_mn=True, b_mn=True, out=ref_.col_range(128, 128), accumulate=True)
+        cu.accumulate_main_grad(cu.GradRef(sink, 0, 8, 128), torch.ones(8, 128, device=DEV))
+        torch.cuda.synchronize()
+        _status_clean(dy)
+        want = dy.float().t() @ x.float()
+        got = shard[256 * 128 : 256 * 128 + N * Kd].view(N, Kd)
+        _close(got, want, 2e-2 * float(want.abs().max()) * 1e-1, 1e-2, "wgrad through a virtual sink")
+        assert float(shard[: 8 * 128].min()) == 1.0 and float(shard[8 * 128 : 256 * 128].abs().max()) == 0.0
+    finally:
+        cu.K.clear_grad_sinks()

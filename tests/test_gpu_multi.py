@@ -48,3 +48,11 @@ def test_sequence_parallel_matches_single_gpu():
 
 def test_engine_sp_step_runs():
     _run("sp_engine_step")
+
+
+def test_full_shard_engine_matches_replicated():
+    _run("engine_full_shard_vs_replicated")
+
+
+def test_sharded_checkpoint_resume_matches_uninterrupted():
+    _run("engine_ckpt_roundtrip")

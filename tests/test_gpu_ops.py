@@ -375,6 +375,47 @@ def test_collective_kernels_single_rank():
     assert torch.equal(vec, keep)
 
 
+def test_peer_wait_runs_out_and_reports():
+    """A wait for a flag that nothing sets ends after its time limit: the kernel returns, the host raises
+    KernelTimeout naming the wait site, and the next launch works. The "peers" are this GPU's own zeroed
+    buffers and the limit is 20 ms, so nothing hangs."""
+    import time
+
+    from gdnet_b200 import _ext
+
+    cu = _cu()
+    _ext.check_status(torch.zeros(1, device=DEV))
+    budget = 20_000_000
+    # halo exchange as rank 1 of 2: nothing to push (rank 1 is the last), waits for rank 0's flag
+    slots = torch.zeros(4096, dtype=torch.uint8, device=DEV)
+    flags = torch.zeros(64, dtype=torch.int32, device=DEV)
+    two = lambda t: torch.tensor([t.data_ptr(), t.data_ptr()], dtype=torch.int64, device=DEV)
+    tail = torch.ones(2, 3, 64, device=DEV, dtype=BF)
+    halo = torch.full_like(tail, 7.0)
+    t0 = time.perf_counter()
+    cu.K.halo_push_wait(tail, halo, two(slots), two(flags), 0, 0, 1, 2, 1, False, budget)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.5, "the wait did not honour its 20 ms limit"
+    with pytest.raises(_ext.KernelTimeout, match="site 40"):
+        _ext.check_status(tail)
+    assert float(halo.abs().max()) == 0.0, "a halo that never arrived must read as zeros"
+    # MAX all-reduce as rank 0 of 2: rank 1's flag never comes
+    area = torch.zeros(2 * 2 * 256, device=DEV)
+    fl = torch.zeros(64, dtype=torch.int32, device=DEV)
+    vec = torch.rand(100, device=DEV)
+    keep = vec.clone()
+    cu.K.max_allreduce(vec, two(area), two(fl), 256, 0, 2, 1, budget)
+    torch.cuda.synchronize()
+    with pytest.raises(_ext.KernelTimeout, match="site 50"):
+        _ext.check_status(vec)
+    assert torch.equal(vec, keep), "after a timeout the vector keeps this rank's values"
+    # the context is intact: a normal launch right after
+    cu.K.max_allreduce(vec, _ptr_table(area), _ptr_table(fl), 256, 0, 1, 2)
+    torch.cuda.synchronize()
+    _ext.check_status(vec)
+    assert torch.equal(vec, keep)
+
+
 def test_engine_gradient_buffers_match_autograd():
     """Every parameter's task and information gradient, as the engine's kernels leave them in the two flat
     fp32 buffers (weight-gradient epilogues, packed small-parameter delivery, conv taps through their base
