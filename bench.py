@@ -1,6 +1,6 @@
 """Flagship benchmark: GDNet ~350M training throughput (tokens/s) on N B200s of one node.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 350m|tiny]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 350m|1.3b|1.3b-sp|tiny|...]
 
 Config: d_model 1024, 24 layers, 2 cycles, dwconv width 4, vocab 32000,
 seq_len 4096, micro-batch 8 per GPU, FP8 e4m3 linears, AdamW, projected-gradient step with 4
@@ -35,17 +35,21 @@ CONFIGS = {
                  micro_batch=8, n_write=4),
     "tiny": dict(vocab_size=4096, d_embed=256, d=256, n_layers=2, n_cycles=2, kernel_size=4, seq_len=512,
                  micro_batch=2, n_write=2),
-    # ~1.3B, gradients and optimizer state sharded over the ranks: the weight-gradient GEMM epilogues add into the
-    # owner's shard over NVLink, the update kernel does AdamW on the shard and writes the new parameters to all ranks;
-    # every FP8 weight is quantised by one rank, whose kernel stores the e4m3 copies into all ranks' caches
+    # ~1.3B fully sharded: every large layer matrix (bf16 master, fp32 gradients, AdamW moments) lives on one owner
+    # rank; the GEMMs of a layer step gather the operands they need from the owners over NVLink (the copies ride on
+    # the tensor-core kernels), the weight-gradient epilogues add into the owner's shard, the update kernel does
+    # projection + AdamW on the shard
     "1.3b": dict(vocab_size=32000, d_embed=2048, d=2048, n_layers=24, n_cycles=2, kernel_size=4, seq_len=8192,
-                 micro_batch=2, n_write=4, comm="scatter", share_fp8=True),
+                 micro_batch=2, n_write=4, shard="full"),
     # ~1.3B, one 65536-token sequence split into contiguous shards over the ranks (sequence parallel): conv halos
-    # and their gradients cross ranks inside the push/flag/wait kernel
+    # and their gradients cross ranks inside the conv kernels, every shard reads a memory that holds the summaries
+    # of the shards before it, and the layer matrices are sharded over the same ranks (gathered by the GEMMs)
     "1.3b-sp": dict(vocab_size=32000, d_embed=2048, d=2048, n_layers=24, n_cycles=2, kernel_size=4, seq_len=65536,
-                    micro_batch=1, n_write=0, mode="sp"),
+                    micro_batch=1, n_write=4, mode="sp", shard="full"),
     "tiny-sp": dict(vocab_size=4096, d_embed=256, d=256, n_layers=2, n_cycles=2, kernel_size=4, seq_len=2048,
-                    micro_batch=1, n_write=0, mode="sp"),
+                    micro_batch=1, n_write=2, mode="sp", shard="full"),
+    "tiny-shard": dict(vocab_size=4096, d_embed=256, d=256, n_layers=2, n_cycles=2, kernel_size=4, seq_len=512,
+                       micro_batch=2, n_write=2, shard="full"),
 }
 
 
@@ -111,6 +115,9 @@ def make_batches(cfg, n_batches: int, seed: int, rank: int = 0, world: int = 1):
             tl = T // world
             seq = full[:, rank * tl : (rank + 1) * tl + 1].contiguous()
             wc = None
+            if W > 0:       # earlier sequences of the same stream, cut into the same shards
+                wc = torch.randint(1, V, (B, W, T), generator=g)[:, :, rank * tl : (rank + 1) * tl].contiguous()
+                wc = wc.pin_memory() if pin else wc
         else:
             seq, _, _ = synthetic_packed_batch(B, T, V, 1024.0, g)
             wc = None
@@ -142,7 +149,8 @@ def build_ours(cfg, device, world):
     share = os.environ.get("GDNET_SHARE_FP8", "1" if cfg.get("share_fp8") else "0") == "1"
     engine = TrainEngine(model, lr=1e-3, precision="fp8", sp_group=sp_group,
                          comm=os.environ.get("GDNET_COMM", cfg.get("comm", "fused")), share_fp8_weights=share,
-                         fused_ce=os.environ.get("GDNET_FUSED_CE", "1") == "1")
+                         fused_ce=os.environ.get("GDNET_FUSED_CE", "1") == "1",
+                         shard=os.environ.get("GDNET_SHARD", cfg.get("shard", "none")))
 
     def step(tokens, targets, write_chunks):
         return engine.projected_step(tokens, targets, write_chunks=write_chunks)
@@ -182,15 +190,24 @@ def build_reference(cfg, device, world, local_rank):
 
     torch.set_float32_matmul_precision("high")
     torch.manual_seed(0)
+    sp = cfg.get("mode") == "sp" and world > 1
+    # sequence parallel as the reference's scripts/throughput.py:218-252 sets it up: all ranks in one SP group,
+    # the model's chunk size is the local shard, DDP over the (single-rank) data-parallel group
+    chunk = cfg["seq_len"] // world if sp else cfg["seq_len"]
     model = GDNet(vocab_size=cfg["vocab_size"], d_embed=cfg["d_embed"], d=cfg["d"], n_layers=cfg["n_layers"],
-                  n_cycles=cfg["n_cycles"], kernel_size=cfg["kernel_size"], chunk_size=cfg["seq_len"]).to(device)
+                  n_cycles=cfg["n_cycles"], kernel_size=cfg["kernel_size"], chunk_size=chunk).to(device)
     model.embed.weight.data = model.embed.weight.data.bfloat16()
     convert_to_fp8(model)
     base = model
+    sp_group = None
     if world > 1:
         from torch.nn.parallel import DistributedDataParallel as DDP
 
-        init_process_groups(1)
+        init_process_groups(world if sp else 1)
+        if sp:
+            from gdnet.utils.distributed import get_sp_group
+
+            sp_group = get_sp_group()
         model = DDP(model, device_ids=[local_rank], process_group=get_dp_group(), static_graph=True,
                     bucket_cap_mb=200, broadcast_buffers=False)
     optimizer = torch.optim.AdamW(model.parameters(), lr=1e-3)
@@ -198,7 +215,8 @@ def build_reference(cfg, device, world, local_rank):
     counter = {"i": 0}
 
     def step(tokens, targets, write_chunks):
-        loss = projected_step(model, params, optimizer, tokens, targets, precision="fp8", write_chunks=write_chunks)
+        loss = projected_step(model, params, optimizer, tokens, targets, precision="fp8", write_chunks=write_chunks,
+                              sp_group=sp_group)
         if counter["i"] % 16 == 0:
             update_fp8_scales(base)
         counter["i"] += 1
@@ -251,10 +269,6 @@ def main() -> None:
 
     W, K = max(args.warmup, 0), args.steps
     sp = cfg.get("mode") == "sp"
-    if sp and args.impl == "reference":
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "the sequence-parallel configs are not wired to the reference arm"}))
-        return
     batches = make_batches(cfg, W + 2 * K, seed=1234 + (0 if sp else rank), rank=rank, world=world)
     T = cfg["seq_len"]
 
@@ -282,6 +296,8 @@ def main() -> None:
     eng = getattr(step, "engine", None)
     if eng is not None:
         eng.time_updates = True
+    ws = getattr(eng, "weight_stream", None) if eng is not None else None
+    gathered0 = ws.gathered_bytes if ws is not None else 0
     sampler = ClockSampler(local_rank)
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -292,6 +308,7 @@ def main() -> None:
     sync_all()
     clocks = sampler.stop()
     n_launch = launches() - n0
+    gathered = (ws.gathered_bytes - gathered0) / K if ws is not None else None
     ms_dev = ev0.elapsed_time(ev1) / K
     update_ms = None
     if eng is not None:
@@ -342,6 +359,10 @@ def main() -> None:
             # device time of the update phase per step (gradient collective + projection + AdamW + parameter
             # all-gather, waits for slower ranks included), max over ranks; on one GPU it is the optimizer alone
             "update_phase_ms": update_ms,
+            # bytes of parameters, gradient buffers and AdamW moments resident on rank 0, and (fully sharded layer
+            # matrices) the bytes of GEMM operands it pulled from their owner ranks per step
+            "resident_bytes": eng.resident_bytes() if eng is not None else None,
+            "gathered_bytes_per_step": gathered,
             "last_loss": last,
         }))
     if world > 1:

@@ -401,7 +401,7 @@ void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out, OptT q,
   if (halo.has_value()) TORCH_CHECK(halo->is_contiguous() && halo->size(0) == B && halo->size(1) == k - 1 && halo->size(2) == d, "dwconv: halo must be (B, k-1, d)");
   TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (out.stride(1) * 2) % 16 == 0, "dwconv: rows must be 16-byte aligned");
   gd::ConvArgs a{bf16_ptr(x, "x"), opt_bf16(halo, "halo"), f32_ptr(w, "w"), bf16_mut(out, "out"), B, T, d, k,
-                 x.stride(1), out.stride(1), row_quant_out(q, qs, qp, (int64_t)B * T, d)};
+                 x.stride(1), out.stride(1), row_quant_out(q, qs, qp, (int64_t)B * T, d), {}};
   GD_LAUNCH(gd::launch_dwconv_fwd(a, stream_of(x)));
 }
 
@@ -422,6 +422,74 @@ void dwconv_bwd(const Tensor& dc, const Tensor& x, OptT halo, const Tensor& w, O
                     opt_bf16(tail_add, "tail_add"), bf16_mut(dx, "dx"),
                     dhalo.has_value() ? bf16_mut(*dhalo, "dhalo") : nullptr, f32_mut(dw, "dw"), B, T, d, k,
                     dc.stride(1), x.stride(1)};
+  GD_LAUNCH(gd::launch_dwconv_bwd(a, stream_of(x)));
+}
+
+gd::ConvSp conv_sp(const Tensor& slot_ptrs, const Tensor& flag_ptrs, Tensor& counter, int64_t slot_offset, int64_t flag_index,
+                   int64_t rank, int64_t world, int64_t seq, int64_t budget_ns, const Tensor& like) {
+  TORCH_CHECK(slot_ptrs.is_cuda() && slot_ptrs.scalar_type() == at::kLong && slot_ptrs.numel() == world &&
+              flag_ptrs.is_cuda() && flag_ptrs.scalar_type() == at::kLong && flag_ptrs.numel() == world,
+              "halo exchange: one slot pointer and one flag pointer per rank");
+  TORCH_CHECK(counter.is_cuda() && counter.scalar_type() == at::kInt && counter.numel() >= 1, "halo exchange: counter must be int32");
+  TORCH_CHECK(rank >= 0 && rank < world && slot_offset % 16 == 0 && flag_index >= 0, "halo exchange: rank / offsets");
+  gd::ConvSp sp{};
+  sp.slots = reinterpret_cast<uint8_t* const*>(slot_ptrs.data_ptr<int64_t>());
+  sp.flags = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
+  sp.slot_offset = slot_offset;
+  sp.flag_index = (int)flag_index;
+  sp.rank = (int)rank;
+  sp.world = (int)world;
+  sp.seq = (uint32_t)seq;
+  sp.counter = reinterpret_cast<uint32_t*>(counter.data_ptr<int>());
+  sp.budget_ns = budget_ns > 0 ? (uint64_t)budget_ns : 0;
+  sp.halo_out = nullptr;
+  sp.status = status_ptr(like);
+  return sp;
+}
+
+// Causal conv of a sequence shard with the neighbour exchange inside the kernel: the last k-1 input rows go to the
+// next rank's slot, the previous rank's rows are waited for (bounded) and read from this rank's slot; they are
+// also written to halo_out for the backward pass.
+void dwconv_fwd_sp(const Tensor& x, const Tensor& w, Tensor out, Tensor halo_out, const Tensor& slot_ptrs,
+                   const Tensor& flag_ptrs, Tensor counter, int64_t slot_offset, int64_t flag_index, int64_t rank,
+                   int64_t world, int64_t seq, int64_t budget_ns, OptT q, OptT qs, OptT qp) {
+  c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
+  TORCH_CHECK(x.dim() == 3 && out.dim() == 3, "dwconv: x and out must be (B, T, d)");
+  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv: taps must be (k, d) contiguous (transposed)");
+  TORCH_CHECK(x.stride(0) == x.stride(1) * T && out.stride(0) == out.stride(1) * T, "dwconv: batch stride must be T rows");
+  TORCH_CHECK(out.size(0) == B && out.size(1) == T && out.size(2) == d, "dwconv: out shape");
+  TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (out.stride(1) * 2) % 16 == 0, "dwconv: rows must be 16-byte aligned");
+  TORCH_CHECK(k == 4 && T % 8 == 0 && d % 8 == 0, "dwconv_fwd_sp: needs k == 4, T % 8 == 0, d % 8 == 0");
+  TORCH_CHECK(halo_out.is_contiguous() && halo_out.dim() == 3 && halo_out.size(0) == B && halo_out.size(1) == k - 1 &&
+              halo_out.size(2) == d, "dwconv_fwd_sp: halo_out must be (B, k-1, d)");
+  gd::ConvArgs a{bf16_ptr(x, "x"), nullptr, f32_ptr(w, "w"), bf16_mut(out, "out"), B, T, d, k,
+                 x.stride(1), out.stride(1), row_quant_out(q, qs, qp, (int64_t)B * T, d), {}};
+  a.sp = conv_sp(slot_ptrs, flag_ptrs, counter, slot_offset, flag_index, rank, world, seq, budget_ns, x);
+  a.sp.halo_out = bf16_mut(halo_out, "halo_out");
+  GD_LAUNCH(gd::launch_dwconv_fwd(a, stream_of(x)));
+}
+
+// Backward of dwconv_fwd_sp: the gradient of the received rows goes to the previous rank's slot, the next rank's
+// is waited for (bounded) and added to the last k-1 rows of dx inside the kernel; dw as in dwconv_bwd.
+void dwconv_bwd_sp(const Tensor& dc, const Tensor& x, const Tensor& halo, const Tensor& w, Tensor dx, Tensor dw,
+                   const Tensor& slot_ptrs, const Tensor& flag_ptrs, Tensor counter, int64_t slot_offset,
+                   int64_t flag_index, int64_t rank, int64_t world, int64_t seq, int64_t budget_ns) {
+  c10::cuda::CUDAGuard guard(x.device());
+  OpRange gd_range_(__func__);
+  TORCH_CHECK(x.dim() == 3 && dc.dim() == 3 && dx.dim() == 3, "dwconv_bwd: tensors must be (B, T, d)");
+  const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv_bwd: taps must be (k, d) contiguous (transposed)");
+  TORCH_CHECK(dx.is_contiguous() && dw.is_contiguous() && dw.size(0) == d && dw.size(1) == k, "dwconv_bwd: dx/dw layout");
+  TORCH_CHECK(x.stride(0) == x.stride(1) * T && dc.stride(0) == dc.stride(1) * T, "dwconv_bwd: batch stride must be T rows");
+  TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (dc.stride(1) * 2) % 16 == 0, "dwconv_bwd: rows must be 16-byte aligned");
+  TORCH_CHECK(k == 4 && T % 8 == 0 && d % 8 == 0, "dwconv_bwd_sp: needs k == 4, T % 8 == 0, d % 8 == 0");
+  TORCH_CHECK(halo.is_contiguous() && halo.dim() == 3 && halo.size(0) == B && halo.size(1) == k - 1 && halo.size(2) == d,
+              "dwconv_bwd_sp: halo must be (B, k-1, d)");
+  gd::ConvBwdArgs a{bf16_ptr(dc, "dc"), bf16_ptr(x, "x"), bf16_ptr(halo, "halo"), f32_ptr(w, "w"), nullptr,
+                    bf16_mut(dx, "dx"), nullptr, f32_mut(dw, "dw"), B, T, d, k, dc.stride(1), x.stride(1), {}};
+  a.sp = conv_sp(slot_ptrs, flag_ptrs, counter, slot_offset, flag_index, rank, world, seq, budget_ns, x);
   GD_LAUNCH(gd::launch_dwconv_bwd(a, stream_of(x)));
 }
 
@@ -760,7 +828,7 @@ void peer_add_at(int64_t sink, int64_t off, const Tensor& src) {
 }
 
 void max_allreduce(Tensor vec, const Tensor& area_ptrs, const Tensor& flag_ptrs, int64_t slot_elems, int64_t rank,
-                   int64_t world, int64_t seq, int64_t budget_ns) {
+                   int64_t world, int64_t seq, int64_t budget_ns, OptT gather_out) {
   c10::cuda::CUDAGuard guard(vec.device());
   OpRange gd_range_(__func__);
   TORCH_CHECK(vec.is_contiguous() && vec.scalar_type() == at::kFloat, "max_allreduce: vec must be contiguous fp32");
@@ -773,6 +841,12 @@ void max_allreduce(Tensor vec, const Tensor& area_ptrs, const Tensor& flag_ptrs,
   a.slot_elems = (int)slot_elems;
   a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq;
   a.budget_ns = budget_ns > 0 ? (uint64_t)budget_ns : 0;
+  a.gather_out = nullptr;
+  if (gather_out.has_value()) {
+    TORCH_CHECK(gather_out->is_contiguous() && gather_out->scalar_type() == at::kFloat && gather_out->numel() == world * vec.numel(),
+                "max_allreduce: gather_out must be contiguous fp32 (world, n)");
+    a.gather_out = gather_out->data_ptr<float>();
+  }
   a.status = status_ptr(vec);
   GD_LAUNCH(gd::launch_max_allreduce(a, stream_of(vec)));
 }
@@ -807,6 +881,8 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("gemm_fp8_mx(Tensor a8, Tensor pa, Tensor b8, Tensor pb, Tensor(a!) out, bool accumulate, Tensor? bias, Tensor? row_scale, Tensor? aux, int aux_mode, Tensor(b!)? pre_out, int act, Tensor(c!)? q8=None, Tensor(d!)? q8_p=None, bool q8_silu=False, bool store_out=True) -> ()", &gemm_fp8_mx);
   m.def("dwconv_fwd(Tensor x, Tensor? halo, Tensor w, Tensor(a!) out, Tensor(b!)? q=None, Tensor(c!)? qs=None, Tensor(d!)? qp=None) -> ()", &dwconv_fwd);
   m.def("dwconv_bwd(Tensor dc, Tensor x, Tensor? halo, Tensor w, Tensor? tail_add, Tensor(a!) dx, Tensor(b!)? dhalo, Tensor(c!) dw) -> ()", &dwconv_bwd);
+  m.def("dwconv_fwd_sp(Tensor x, Tensor w, Tensor(a!) out, Tensor(b!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, Tensor(c!) counter, int slot_offset, int flag_index, int rank, int world, int seq, int budget_ns=0, Tensor(d!)? q=None, Tensor(e!)? qs=None, Tensor(f!)? qp=None) -> ()", &dwconv_fwd_sp);
+  m.def("dwconv_bwd_sp(Tensor dc, Tensor x, Tensor halo, Tensor w, Tensor(a!) dx, Tensor(b!) dw, Tensor slot_ptrs, Tensor flag_ptrs, Tensor(c!) counter, int slot_offset, int flag_index, int rank, int world, int seq, int budget_ns=0) -> ()", &dwconv_bwd_sp);
   m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r, Tensor(f!)? q=None, Tensor(g!)? qs=None, Tensor(h!)? qp=None) -> ()", &gate_update_fwd);
   m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r, Tensor(h!)? q=None, Tensor(i!)? qs=None, Tensor(j!)? qp=None) -> ()", &gate_update_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!)? rstd, float eps) -> ()", &rmsnorm_fwd);
@@ -835,6 +911,6 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("attach_b_ready(Tensor b_ready, Tensor sfb_ready, int b_target, int sfb_target) -> ()", &attach_b_ready);
   m.def("gather_jobs(Tensor jobs) -> ()", &gather_jobs);
   m.def("peer_add(Tensor(a!) dst, Tensor src) -> ()", &peer_add);
-  m.def("max_allreduce(Tensor(a!) vec, Tensor area_ptrs, Tensor flag_ptrs, int slot_elems, int rank, int world, int seq, int budget_ns=0) -> ()", &max_allreduce);
+  m.def("max_allreduce(Tensor(a!) vec, Tensor area_ptrs, Tensor flag_ptrs, int slot_elems, int rank, int world, int seq, int budget_ns=0, Tensor(b!)? gather_out=None) -> ()", &max_allreduce);
   m.def("halo_push_wait(Tensor tail, Tensor(a!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, int slot_offset_bytes, int flag_index, int rank, int world, int seq, bool reverse, int budget_ns=0) -> ()", &halo_push_wait);
 }

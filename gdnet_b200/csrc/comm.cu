@@ -4,34 +4,6 @@
 
 namespace gd {
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Bounded wait until *p >= want (sequence numbers only grow). false = budget exhausted.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, uint64_t budget_ns = GD_WAIT_BUDGET_NS) {
-  for (int i = 0; i < 2048; ++i)
-    if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
-  const uint64_t t0 = globaltimer_ns();
-  while (true) {
-    for (int i = 0; i < 256; ++i) {
-      if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
-      __nanosleep(200);
-    }
-    if (globaltimer_ns() - t0 > budget_ns) return false;
-  }
-}
-
-__device__ __forceinline__ uint64_t budget_or_default(uint64_t budget_ns) {
-  return budget_ns != 0 ? budget_ns : (uint64_t)GD_WAIT_BUDGET_NS;
-}
-
 // ---------------------------------------------------------------------------------------
 // gradient reduce-scatter + projection + AdamW + parameter all-gather
 // ---------------------------------------------------------------------------------------
@@ -261,6 +233,11 @@ max_allreduce_kernel(const MaxAllReduceArgs a) {
   __syncthreads();
   if (!ok_all) return;      // the vector keeps this rank's own values
   const float* mine = a.areas[a.rank] + set;
+  if (a.gather_out != nullptr) {     // all-gather: every rank's vector, in rank order
+    for (int r = 0; r < a.world; ++r)
+      for (int i = threadIdx.x; i < a.n; i += blockDim.x) a.gather_out[(size_t)r * a.n + i] = __ldcv(mine + (size_t)r * a.slot_elems + i);
+    return;
+  }
   for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
     float m = __ldcv(mine + i);
     for (int r = 1; r < a.world; ++r) m = fmaxf(m, __ldcv(mine + (size_t)r * a.slot_elems + i));

@@ -70,6 +70,7 @@ struct MaxAllReduceArgs {
   int rank, world;
   uint32_t seq;             // strictly increasing per call
   uint64_t budget_ns;       // time limit of the wait for the peers' flags; 0 = the library default (2 s)
+  float* gather_out;        // null: element-wise MAX into vec. Else an all-gather: gather_out[r * n + i] = rank r's vec[i]
   Status* status;
 };
 const char* launch_max_allreduce(const MaxAllReduceArgs& a, cudaStream_t st);

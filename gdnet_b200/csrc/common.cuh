@@ -86,6 +86,35 @@ __device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* p, uint32_t wan
   }
 }
 
+// System-scope flags: written by one GPU, read by another over NVLink.
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait until *p >= want (sequence numbers only grow). false = budget exhausted.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, uint64_t budget_ns = GD_WAIT_BUDGET_NS) {
+  for (int i = 0; i < 2048; ++i)
+    if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    for (int i = 0; i < 256; ++i) {
+      if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+      __nanosleep(200);
+    }
+    if (globaltimer_ns() - t0 > budget_ns) return false;
+  }
+}
+
+__device__ __forceinline__ uint64_t budget_or_default(uint64_t budget_ns) {
+  return budget_ns != 0 ? budget_ns : (uint64_t)GD_WAIT_BUDGET_NS;
+}
+
 // A gather job copies `n_vec` 16-byte vectors from `src` (usually another GPU's memory, read with plain
 // uncached loads over NVLink) to `dst` (this GPU's memory) and then adds one to the counter `*flag` (release,
 // device scope; may be null). Jobs are four int64 words each: src, dst, flag, n_vec. A range that a consumer

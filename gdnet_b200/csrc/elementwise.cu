@@ -104,36 +104,88 @@ dwconv_fwd_pt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 // sequence, keeps the last KT-1 input rows in registers and loads every further row once (TT + KT - 1 row loads
 // for TT outputs instead of KT per output). The loads of a strip are independent, so the compiler keeps them
 // all in flight.
-template <int KT, int TT>
+// After a warp has stored its rows into a neighbour's slot: count it, and let the last one raise the flag.
+__device__ __forceinline__ void sp_signal_after_store(const ConvSp& sp, int dst, uint32_t total) {
+  __threadfence_system();
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) {
+    const uint32_t prev = atomicAdd(sp.counter, 1u);
+    if (prev == total - 1) {
+      *sp.counter = 0u;               // ready for the next launch that uses this word
+      __threadfence_system();
+      st_release_sys(sp.flags[dst] + sp.flag_index, sp.seq);
+    }
+  }
+}
+
+// One lane polls this rank's flag; the result is broadcast. false = the wait ran out (reported).
+__device__ __forceinline__ bool sp_wait_neighbour(const ConvSp& sp, int src, int site) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    ok = wait_flag_ge(sp.flags[sp.rank] + sp.flag_index, sp.seq, budget_or_default(sp.budget_ns)) ? 1u : 0u;
+    if (!ok) report(sp.status, STATUS_TIMEOUT_PEER_FLAG, site, src);
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+template <int KT, int TT, bool SP>
 __global__ void __launch_bounds__(256)
 dwconv_fwd_sw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
                      const float* __restrict__ wt, __nv_bfloat16* __restrict__ out, int B, int T, int d,
-                     int64_t x_ld, int64_t out_ld, const RowQuantOut qo) {
+                     int64_t x_ld, int64_t out_ld, const RowQuantOut qo, const ConvSp sp) {
   pdl_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
-  const int strip = blockIdx.x * 8 + warp;          // T % TT == 0: a strip never crosses a sequence boundary
+  int strip = blockIdx.x * 8 + warp;          // T % TT == 0: a strip never crosses a sequence boundary
+  const int n_strips = B * (T / TT);
+  if (strip >= n_strips) return;              // warp-uniform
+  // sequence parallel: the strips that hold the rows the next rank waits for run first, the strips that wait
+  // for the previous rank's rows run last
+  if (SP) strip = n_strips - 1 - strip;
   const int row0 = strip * TT;
-  if (row0 >= B * T || ch >= d) return;
   const int b = row0 / T, t0 = row0 - b * T;
+  const bool live = ch < d;
+  if (!SP && !live) return;
   float tap[KT][8];
 #pragma unroll
   for (int i = 0; i < KT; ++i) {
-    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch);
-    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch + 4);
+    const float4 w0 = live ? *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch) : make_float4(0, 0, 0, 0);
+    const float4 w1 = live ? *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch + 4) : make_float4(0, 0, 0, 0);
     tap[i][0] = w0.x; tap[i][1] = w0.y; tap[i][2] = w0.z; tap[i][3] = w0.w;
     tap[i][4] = w1.x; tap[i][5] = w1.y; tap[i][6] = w1.z; tap[i][7] = w1.w;
   }
   uint4 in[TT + KT - 1];     // rows kept packed (bf16); unpacked at each use to stay within the register budget
 #pragma unroll
+  for (int j = 0; j < TT; ++j)
+    in[KT - 1 + j] = live ? *reinterpret_cast<const uint4*>(x + (int64_t)(row0 + j) * x_ld + ch) : make_uint4(0, 0, 0, 0);
+  if (SP && t0 + TT == T && sp.rank + 1 < sp.world) {
+    // the last KT-1 rows of this sequence are the next rank's halo: straight from registers into its slot
+    if (live) {
+      uint4* dst = reinterpret_cast<uint4*>(sp.slots[sp.rank + 1] + sp.slot_offset);
+#pragma unroll
+      for (int i = 0; i < KT - 1; ++i)
+        dst[((int64_t)b * (KT - 1) + i) * (d / 8) + ch / 8] = in[TT + i];
+    }
+    sp_signal_after_store(sp, sp.rank + 1, (uint32_t)B * gridDim.y);
+  }
+  bool halo_ok = true;
+  if (SP && t0 == 0 && sp.rank > 0) halo_ok = sp_wait_neighbour(sp, sp.rank - 1, 41);
+  if (!live) return;
+#pragma unroll
   for (int i = 0; i < KT - 1; ++i) {
     const int t = t0 - (KT - 1) + i;
     in[i] = make_uint4(0, 0, 0, 0);
-    if (t >= 0) in[i] = *reinterpret_cast<const uint4*>(x + ((int64_t)b * T + t) * x_ld + ch);
-    else if (halo != nullptr) in[i] = *reinterpret_cast<const uint4*>(halo + ((int64_t)b * (KT - 1) + (t + KT - 1)) * d + ch);
+    if (t >= 0) {
+      in[i] = *reinterpret_cast<const uint4*>(x + ((int64_t)b * T + t) * x_ld + ch);
+    } else if (SP) {
+      const int64_t at = ((int64_t)b * (KT - 1) + (t + KT - 1)) * (d / 8) + ch / 8;
+      if (sp.rank > 0 && halo_ok)
+        in[i] = __ldcv(reinterpret_cast<const uint4*>(sp.slots[sp.rank] + sp.slot_offset) + at);
+      reinterpret_cast<uint4*>(sp.halo_out)[at] = in[i];
+    } else if (halo != nullptr) {
+      in[i] = *reinterpret_cast<const uint4*>(halo + ((int64_t)b * (KT - 1) + (t + KT - 1)) * d + ch);
+    }
   }
-#pragma unroll
-  for (int j = 0; j < TT; ++j) in[KT - 1 + j] = *reinterpret_cast<const uint4*>(x + (int64_t)(row0 + j) * x_ld + ch);
 #pragma unroll
   for (int j = 0; j < TT; ++j) {
     float acc[8];
@@ -206,23 +258,25 @@ dwconv_dx_pt_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restric
 
 // Sliding-window form of dx for t in [0, T): a thread owns 8 channels and TT consecutive time steps and loads
 // the TT + KT - 1 rows of dc it needs once (rows past the end of the sequence are zero).
-template <int KT, int TT>
+template <int KT, int TT, bool SP>
 __global__ void __launch_bounds__(256)
 dwconv_dx_sw_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restrict__ wt,
                     const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx, int B, int T, int d,
-                    int64_t dc_ld) {
+                    int64_t dc_ld, const ConvSp sp) {
   pdl_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = (blockIdx.y * 32 + lane) * 8;
   const int strip = blockIdx.x * 8 + warp;
   const int row0 = strip * TT;
-  if (row0 >= B * T || ch >= d) return;
+  if (row0 >= B * T) return;                  // warp-uniform
+  const bool live = ch < d;
+  if (!SP && !live) return;
   const int b = row0 / T, t0 = row0 - b * T;
   float tap[KT][8];      // tap[j] multiplies dc[t + j]: w[KT-1-j]
 #pragma unroll
   for (int j = 0; j < KT; ++j) {
-    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)(KT - 1 - j) * d + ch);
-    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)(KT - 1 - j) * d + ch + 4);
+    const float4 w0 = live ? *reinterpret_cast<const float4*>(wt + (int64_t)(KT - 1 - j) * d + ch) : make_float4(0, 0, 0, 0);
+    const float4 w1 = live ? *reinterpret_cast<const float4*>(wt + (int64_t)(KT - 1 - j) * d + ch + 4) : make_float4(0, 0, 0, 0);
     tap[j][0] = w0.x; tap[j][1] = w0.y; tap[j][2] = w0.z; tap[j][3] = w0.w;
     tap[j][4] = w1.x; tap[j][5] = w1.y; tap[j][6] = w1.z; tap[j][7] = w1.w;
   }
@@ -230,8 +284,40 @@ dwconv_dx_sw_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restric
 #pragma unroll
   for (int i = 0; i < TT + KT - 1; ++i) {
     g[i] = make_uint4(0, 0, 0, 0);
-    if (t0 + i < T) g[i] = *reinterpret_cast<const uint4*>(dc + (int64_t)(row0 + i) * dc_ld + ch);
+    if (live && t0 + i < T) g[i] = *reinterpret_cast<const uint4*>(dc + (int64_t)(row0 + i) * dc_ld + ch);
   }
+  if (SP && t0 == 0 && sp.rank > 0) {
+    // gradient of the halo rows t = -(KT-1) .. -1 (they are the previous rank's last rows): into its slot
+    if (live) {
+      uint4* dst = reinterpret_cast<uint4*>(sp.slots[sp.rank - 1] + sp.slot_offset);
+#pragma unroll
+      for (int r = 0; r < KT - 1; ++r) {        // row t = r - (KT-1): dc[t + j] exists for j >= KT-1-r
+        float acc[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+#pragma unroll
+        for (int j = KT - 1 - r; j < KT; ++j) {
+          const uint4 gv = g[r - (KT - 1) + j];
+          const uint32_t w[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float2 f = unpack_bf16x2(w[c]);
+            acc[2 * c] = fmaf(tap[j][2 * c], f.x, acc[2 * c]);
+            acc[2 * c + 1] = fmaf(tap[j][2 * c + 1], f.y, acc[2 * c + 1]);
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        dst[((int64_t)b * (KT - 1) + r) * (d / 8) + ch / 8] = o;
+      }
+    }
+    sp_signal_after_store(sp, sp.rank - 1, (uint32_t)B * gridDim.y);
+  }
+  bool tail_ok = true;
+  const bool has_tail = SP && t0 + TT == T && sp.rank + 1 < sp.world;
+  if (has_tail) tail_ok = sp_wait_neighbour(sp, sp.rank + 1, 42);
+  if (!live) return;
 #pragma unroll
   for (int i = 0; i < TT; ++i) {
     float acc[8];
@@ -248,7 +334,19 @@ dwconv_dx_sw_kernel(const __nv_bfloat16* __restrict__ dc, const float* __restric
       }
     }
     const int t = t0 + i;
-    if (dx_tail_add != nullptr && t >= T - (KT - 1)) {
+    if (has_tail && tail_ok && t >= T - (KT - 1)) {
+      // the next rank's halo gradient belongs to these rows: add it before they are stored
+      const uint4 e = __ldcv(reinterpret_cast<const uint4*>(sp.slots[sp.rank] + sp.slot_offset) +
+                             ((int64_t)b * (KT - 1) + (t - (T - (KT - 1)))) * (d / 8) + ch / 8);
+      const uint32_t w[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 f = unpack_bf16x2(w[c]);
+        acc[2 * c] += f.x;
+        acc[2 * c + 1] += f.y;
+      }
+    }
+    if (!SP && dx_tail_add != nullptr && t >= T - (KT - 1)) {
       float extra[8];
       load_bf16_vec<8>(dx_tail_add + ((int64_t)b * (KT - 1) + (t - (T - (KT - 1)))) * d + ch, extra);
 #pragma unroll
@@ -369,9 +467,13 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if ((int64_t)a.B * (a.T + 16) >= (1ll << 31)) return "dwconv: B*T must be below 2^31";
   dim3 grid((unsigned)(((int64_t)a.B * a.T + 7) / 8), (a.d + 255) / 256);
   if (a.quant.q != nullptr && a.d % 128 != 0) return "dwconv: a quantised output needs d % 128 == 0";
+  if (a.sp.slots != nullptr && !(a.k == 4 && a.T % 8 == 0)) return "dwconv: the in-kernel halo exchange needs k == 4 and T % 8 == 0";
   if (a.k == 4 && a.T % 8 == 0) {
     dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
-    launch_pdl(dwconv_fwd_sw_kernel<4, 8>, sgrid, dim3(256), 0, st, a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant);
+    if (a.sp.slots != nullptr)
+      dwconv_fwd_sw_kernel<4, 8, true><<<sgrid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant, a.sp);
+    else
+      launch_pdl(dwconv_fwd_sw_kernel<4, 8, false>, sgrid, dim3(256), 0, st, a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant, a.sp);
     return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
   }
   if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld, a.quant);
@@ -385,9 +487,13 @@ const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   if ((int64_t)a.B * (a.T + 16) >= (1ll << 31)) return "dwconv: B*T must be below 2^31";
   const int rows_per_b = a.T + (a.dhalo != nullptr ? a.k - 1 : 0);
   dim3 grid((unsigned)(((int64_t)a.B * rows_per_b + 7) / 8), (a.d + 255) / 256);
+  if (a.sp.slots != nullptr && !(a.k == 4 && a.T % 8 == 0)) return "dwconv: the in-kernel halo exchange needs k == 4 and T % 8 == 0";
   if (a.k == 4 && a.T % 8 == 0) {
     dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
-    launch_pdl(dwconv_dx_sw_kernel<4, 8>, sgrid, dim3(256), 0, st, a.dc, a.w, a.dx_tail_add, a.dx, a.B, a.T, a.d, a.dc_ld);
+    if (a.sp.slots != nullptr)
+      dwconv_dx_sw_kernel<4, 8, true><<<sgrid, 256, 0, st>>>(a.dc, a.w, a.dx_tail_add, a.dx, a.B, a.T, a.d, a.dc_ld, a.sp);
+    else
+      launch_pdl(dwconv_dx_sw_kernel<4, 8, false>, sgrid, dim3(256), 0, st, a.dc, a.w, a.dx_tail_add, a.dx, a.B, a.T, a.d, a.dc_ld, a.sp);
     if (a.dhalo != nullptr) {
       dim3 hgrid((unsigned)((a.B * (a.k - 1) + 7) / 8), (a.d + 255) / 256);
       dwconv_dhalo_kernel<<<hgrid, 256, 0, st>>>(a.dc, a.w, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);

@@ -14,6 +14,25 @@ namespace gd {
 struct Status;
 
 // ---- causal depthwise conv ------------------------------------------------------------------
+// Sequence-parallel neighbour exchange done by the conv kernels themselves (slots == nullptr: off). Forward:
+// the warps that own the last k-1 rows of a sequence store them into the next rank's slot and the last of
+// them raises that rank's flag; the warps that own the first rows wait (bounded) for this rank's own flag and
+// read the previous rank's rows from this rank's slot. Backward runs the other way: the halo gradient goes to
+// the previous rank, and the next rank's halo gradient is added to the last k-1 rows of dx before they are
+// stored. Blocks are ordered so that the stores come first and the waits last.
+struct ConvSp {
+  uint8_t* const* slots;    // [world] base of every rank's slot area (peer-mapped)
+  uint32_t* const* flags;   // [world] base of every rank's flag area
+  int64_t slot_offset;      // byte offset of this exchange's slot
+  int flag_index;
+  int rank, world;
+  uint32_t seq;             // sequence number of this exchange (grows with every use of the slot)
+  uint32_t* counter;        // local word, zero between launches: warps that have stored their rows
+  uint64_t budget_ns;       // time limit of the wait; 0 = the library default
+  __nv_bfloat16* halo_out;  // forward: the rows received (zeros on the first rank), (B, k-1, d), kept for backward
+  Status* status;
+};
+
 struct ConvArgs {
   const __nv_bfloat16* x;     // (B, T, d), row pitch x_ld
   const __nv_bfloat16* halo;  // (B, k-1, d) or null (zeros)
@@ -22,6 +41,7 @@ struct ConvArgs {
   int B, T, d, k;
   int64_t x_ld, out_ld;
   RowQuantOut quant;          // optional 1x128-quantised copy of out (d % 128 == 0)
+  ConvSp sp;                  // in-kernel halo exchange (k == 4 and T % 8 == 0 only)
 };
 
 struct ConvBwdArgs {
@@ -35,6 +55,7 @@ struct ConvBwdArgs {
   float* dw;                  // (d, k), accumulated with atomics
   int B, T, d, k;
   int64_t dc_ld, x_ld;
+  ConvSp sp;                  // in-kernel halo-gradient exchange (k == 4 and T % 8 == 0 only)
 };
 
 const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st);

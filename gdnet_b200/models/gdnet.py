@@ -15,6 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as ops
+from ..ops import reference as ref
 from .layer import GDLayer
 from .memory import Memory as CAM
 from .operators import TransitionOperators
@@ -63,6 +64,10 @@ class GDNet(nn.Module):
         self.chunk_size, self.kernel_size = chunk_size, kernel_size
         self.cam_enabled = True
         self.trans_enabled = True
+        # sequence parallel: a shard reads a memory that already holds the summaries of the shards before it, as if the
+        # shards had been processed one after the other as chunks (False: every shard sees only the buffers it is
+        # given, which is what the reference does, scripts/training.py:379)
+        self.sp_state_carry = True
 
     # -- trunk ------------------------------------------------------------------------
 
@@ -108,7 +113,7 @@ class GDNet(nn.Module):
 
     def features_from(self, fwd: torch.Tensor) -> torch.Tensor:
         """Input of the vocabulary projection: ``proj_out(norm_out(fwd))``."""
-        eps = self.norm_out.eps if self.norm_out.eps is not None else float(torch.finfo(fwd.dtype).eps)
+        eps = self.norm_out.eps if self.norm_out.eps is not None else ref.default_rms_eps(fwd.dtype)
         return self.proj_out(ops.rmsnorm(fwd, self.norm_out.weight, eps))
 
     def logits_from(self, fwd: torch.Tensor) -> torch.Tensor:
@@ -139,12 +144,33 @@ class GDNet(nn.Module):
         fwd_last = fwd[:, -1, :]
         cam_weights = None
         logits = None
+        if need_logits and sp_group is not None and self.cam_enabled and self.sp_state_carry:
+            buffer_tags, buffer_vals = self.carry_sp_state(fwd_last, side, buffer_tags, buffer_vals, sp_group)
         if need_logits:
             if self.cam_enabled:
                 fwd, cam_weights = self.cam.read(fwd, side[0], buffer_tags, buffer_vals)
             # "features": stop before the vocabulary projection (the caller fuses it with the loss)
             logits = self.features_from(fwd) if need_logits == "features" else self.logits_from(fwd)
         return logits, side, buffer_tags, buffer_vals, gate_vals, cam_weights, fwd_last
+
+    @torch.no_grad()
+    def carry_sp_state(self, fwd_last, side, buffer_tags, buffer_vals, sp_group, upto: int | None = None):
+        """Sequence parallel: write the chunk summaries of the shards before this one (all shards with
+        ``upto="all"``) into the buffers, in shard order. Every shard computes its summary
+        ``(W_tag fwd_last, W_c mean_t side[0])`` locally; one small all-gather hands them round."""
+        import torch.distributed as dist
+
+        from ..parallel.sp import gather_states
+
+        n = dist.get_world_size(sp_group)
+        if n == 1:
+            return buffer_tags, buffer_vals
+        states = gather_states(self.cam.summary(fwd_last, side[0].mean(dim=1)), sp_group)     # (n, B, d_sig + d_c)
+        last = n if upto == "all" else dist.get_rank(sp_group)
+        for r in range(last):
+            buffer_tags, buffer_vals = self.cam.push(states[r, :, : self.cam.d_sig], states[r, :, self.cam.d_sig :],
+                                                     buffer_tags, buffer_vals)
+        return buffer_tags, buffer_vals
 
     def write_cam(self, fwd_last, side, buffer_tags, buffer_vals):
         """Store this chunk's summary ``(fwd_last, mean_t side[0])``; no-op when CAM is off."""

@@ -69,6 +69,18 @@ class Memory(nn.Module):
         new_vals = torch.cat([val.unsqueeze(1), buffer_vals[:, :-1]], dim=1)
         return new_tags, new_vals
 
+    def push(self, tag, val, buffer_tags, buffer_vals):
+        """The slot shift of :meth:`write` for an already projected ``(tag (B, d_sig), val (B, d_c))`` pair."""
+        new_tags = torch.cat([tag.to(buffer_tags.dtype).unsqueeze(1), buffer_tags[:, :-1]], dim=1)
+        new_vals = torch.cat([val.to(buffer_vals.dtype).unsqueeze(1), buffer_vals[:, :-1]], dim=1)
+        return new_tags, new_vals
+
+    @torch.no_grad()
+    def summary(self, tag_input, val_input):
+        """``[W_tag(tag_input) | W_c(val_input)]`` ``(B, d_sig + d_c)``: what :meth:`write` would store, as one
+        vector (the state a sequence shard hands to the shards after it)."""
+        return torch.cat([self.W_tag(tag_input).float(), self.W_c(val_input).float()], dim=-1)
+
     # -- read -------------------------------------------------------------------------
 
     def _alpha(self) -> torch.Tensor:

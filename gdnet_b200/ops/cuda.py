@@ -15,6 +15,7 @@ copies cached per parameter version.
 
 from __future__ import annotations
 
+import os
 import weakref
 
 import torch
@@ -960,7 +961,7 @@ class _LayerStepFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, s, halo, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1, gnw, gW2, gb2, fp8, eps_r, eps_g,
-                want_gate_sum, side_q8=None):
+                want_gate_sum, side_q8=None, sp=None):
         B, T, d = x.shape
         M = B * T
         dev = x.device
@@ -978,9 +979,16 @@ class _LayerStepFn(torch.autograd.Function):
             else:
                 u8, su, pu = _alloc_u8(M, d, dev)
                 quantize_rows_mx(s2, q=u8[:, :d], s=su[:kb], p=pu[:, :kb])
-            K.dwconv_fwd(x, halo, taps_t(conv_w), c3, u8[:, d:], su[kb:], pu[:, kb:])
+            qargs = (u8[:, d:], su[kb:], pu[:, kb:])
         else:
-            K.dwconv_fwd(x, halo, taps_t(conv_w), c3)
+            qargs = ()
+        if sp is not None:
+            # sequence parallel: the kernel itself sends this shard's last rows to the next rank and waits for the
+            # previous rank's; what it received is kept for the backward pass
+            halo = torch.empty(B, conv_w.shape[1] - 1, d, dtype=BF16, device=dev)
+            K.dwconv_fwd_sp(x, taps_t(conv_w), c3, halo, *sp.fwd_args(), 0, *qargs)
+        else:
+            K.dwconv_fwd(x, halo, taps_t(conv_w), c3, *qargs)
 
         # recovery MLP: z = W2r silu(W1r [s ; c] + b1r) + b2r
         h1_pre = torch.empty(M, d, dtype=BF16, device=dev)
@@ -1044,6 +1052,7 @@ class _LayerStepFn(torch.autograd.Function):
                                   z, hg_pre, h, ssq, g_pre, rstd_z, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1, gnw,
                                   gW2, gb2)
             ctx.cfg = (B, T, d, fp8, eps_g, halo is not None)
+            ctx.sp = sp
             ctx.conv_param = getattr(conv_w, "base_param", None)   # the taps are a view of this parameter
         return fwd_out, side_out, gate_sum
 
@@ -1133,8 +1142,14 @@ class _LayerStepFn(torch.autograd.Function):
 
         # ---- conv ----
         dx = torch.empty(B, T, d, dtype=BF16, device=dev)
-        dhalo = torch.empty_like(halo) if halo is not None else None
-        K.dwconv_bwd(dsc.view(B, T, 2 * d)[:, :, d:], x, halo, taps_t(conv_w), None, dx, dhalo, dwc)
+        if ctx.sp is not None:
+            # the gradient of the received rows goes to the previous rank and the next rank's is added to the last
+            # rows of dx, both inside the kernel
+            dhalo = None
+            K.dwconv_bwd_sp(dsc.view(B, T, 2 * d)[:, :, d:], x, halo, taps_t(conv_w), dx, dwc, *ctx.sp.bwd_args(), 0)
+        else:
+            dhalo = torch.empty_like(halo) if halo is not None else None
+            K.dwconv_bwd(dsc.view(B, T, 2 * d)[:, :, d:], x, halo, taps_t(conv_w), None, dx, dhalo, dwc)
         ds = dsc.view(B, T, 2 * d)[:, :, :d]
 
         g_gW2 = None if main2 else tgt2.to(gW2.dtype)
@@ -1147,7 +1162,7 @@ class _LayerStepFn(torch.autograd.Function):
         g_gb2, g_rnw, g_rb2, g_gnw, g_gb1, g_rb1, g_conv = _sink_vecs(
             smalls, vec, (db2g, dw_r, db2r, dgnw, db1g, db1r, dwc), mgs)
         return (dx, ds, dhalo, g_conv, g_rW1, g_rb1, g_rW2, g_rb2, g_rnw, g_gW1, g_gb1, g_gnw, g_gW2, g_gb2,
-                None, None, None, None, None)
+                None, None, None, None, None, None)
 
 
 def _fused_step_ok(fwd, side, layer, r) -> bool:
@@ -1165,12 +1180,22 @@ def layer_step(fwd, side, layer, conv_name, g, r, sp_group=None, sp_slot=None, r
     w1r, w2r, nr = getattr(layer, f"{r}_W1"), getattr(layer, f"{r}_W2"), getattr(layer, f"{r}_norm")
     w1g, w2g, ng = getattr(layer, f"{g}_W1"), getattr(layer, f"{g}_W2"), getattr(layer, f"{g}_norm")
     halo = None
+    sp = None
+    fused = return_gate is not True and _fused_step_ok(fwd, side, layer, r)
     if sp_group is not None and k > 1:
-        from ..parallel.sp import halo_exchange
+        import torch.distributed as dist
 
-        halo = halo_exchange(ref.conv_tail(fwd, k).contiguous(), sp_group, sp_slot)
+        B, T, d = fwd.shape
+        in_kernel = (fused and k == 4 and T % 8 == 0 and dist.get_world_size(sp_group) > 1 and sp_slot is not None
+                     and os.environ.get("GDNET_SP_TRANSPORT", "symm") == "symm" and os.environ.get("GDNET_SP_INKERNEL", "1") == "1")
+        if in_kernel:
+            sp = SpExchange(sp_group, int(sp_slot), B * (k - 1) * d * 2, fwd.device)
+        else:
+            from ..parallel.sp import halo_exchange
 
-    if return_gate is True or not _fused_step_ok(fwd, side, layer, r):
+            halo = halo_exchange(ref.conv_tail(fwd, k).contiguous(), sp_group, sp_slot)
+
+    if not fused:
         return _composed_step(fwd, side, halo, conv, w1r, w2r, nr, w1g, w2g, ng, return_gate)
 
     fp8 = isinstance(w1r, FP8Linear) and isinstance(w2r, FP8Linear) and w1r.recipe == "block"
@@ -1179,7 +1204,7 @@ def layer_step(fwd, side, layer, conv_name, g, r, sp_group=None, sp_slot=None, r
     fo, so, gsum = _LayerStepFn.apply(
         fwd, side.to(BF16), halo, conv.taps, w1r.weight, w1r.bias, w2r.weight, w2r.bias, nr.weight,
         w1g.weight, w1g.bias, ng.weight, w2g.weight, w2g.bias, fp8, float(eps_r), ref.GATE_EPS,
-        return_gate == "mean", side_q8,
+        return_gate == "mean", side_q8, sp,
     )
     if fp8:
         _offer_side_q8(so)
@@ -1363,9 +1388,38 @@ def _halo_ctx(group, nbytes, device):
         data = get_buffer(("halo_data", slot_bytes), total * slot_bytes, group, device)
         flags = get_buffer(("halo_flags", slot_bytes), total * 4, group, device)
         st = {"slot_bytes": slot_bytes, "data": data, "flags": flags, "pass_fwd": {}, "rank": dist.get_rank(group),
-              "world": dist.get_world_size(group)}
+              "world": dist.get_world_size(group),
+              "counters": torch.zeros(total, dtype=torch.int32, device=device)}
         _halo_state[key] = st
     return st
+
+
+class SpExchange:
+    """One halo exchange done inside the conv kernels: the forward use of a slot and, when the step is
+    differentiated, the gradient exchanges that answer it (up to two per forward use with a retained graph; each
+    has its own sequence number and ring position, so a fast rank cannot overwrite a message that was not read)."""
+
+    def __init__(self, group, slot, nbytes, device):
+        if slot >= HALO_SLOTS:
+            raise ValueError("halo exchange over symmetric memory needs a slot index below HALO_SLOTS")
+        st = _halo_ctx(group, nbytes, device)
+        self.st, self.slot = st, slot
+        self.n_use = st["pass_fwd"].get(slot, 0) + 1        # counted identically on all ranks
+        st["pass_fwd"][slot] = self.n_use
+        self.bwd_runs = 0
+
+    def _args(self, idx, seq):
+        st = self.st
+        return (st["data"].ptr_table, st["flags"].ptr_table, st["counters"][idx : idx + 1], idx * st["slot_bytes"], idx,
+                st["rank"], st["world"], seq)
+
+    def fwd_args(self):
+        return self._args((self.n_use % HALO_RING) * HALO_SLOTS + self.slot, self.n_use)
+
+    def bwd_args(self):
+        self.bwd_runs += 1
+        seq = self.n_use * 2 + min(self.bwd_runs, 2) - 1
+        return self._args(HALO_RING * HALO_SLOTS + (seq % HALO_RING) * HALO_SLOTS + self.slot, seq)
 
 
 class _HaloExchangeSymm(torch.autograd.Function):

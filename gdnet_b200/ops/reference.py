@@ -73,9 +73,17 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return (xf * rstd * w.float()).to(x.dtype)
 
 
-def default_rms_eps(dtype: torch.dtype) -> float:
-    """``nn.RMSNorm(eps=None)`` uses the machine epsilon of the input dtype."""
-    return float(torch.finfo(dtype).eps)
+RMS_EPS_DEFAULT = float(torch.finfo(torch.float32).eps)
+
+
+def default_rms_eps(dtype: torch.dtype | None = None) -> float:
+    """The epsilon of an ``nn.RMSNorm(eps=None)`` as the reference runs it, i.e. on a CUDA tensor: torch's fused
+    CUDA kernel does not take the machine epsilon of the *input* dtype (7.8e-3 for bfloat16, which is what the
+    CPU composite uses) but a float32-sized one, whatever the input dtype. The difference is not cosmetic: the
+    streams of a freshly initialised model have an RMS of a few hundredths, so 7.8e-3 under the square root would
+    scale every normalised activation down several times. The same value is used on every device and dtype here, so
+    the CPU statement of an op and its CUDA kernel agree."""
+    return RMS_EPS_DEFAULT
 
 
 def gate_stream_update(g_pre, c, s, R):

@@ -109,6 +109,24 @@ def state_exchange(summary: torch.Tensor, group) -> torch.Tensor:
         return _HaloExchangeP2P.apply(summary.detach(), group)
 
 
+def gather_states(payload: torch.Tensor, group) -> torch.Tensor:
+    """``(sp_size, *payload.shape)``: every shard's state vector (the chunk summary a shard would write into the
+    content-addressed memory), in shard order, on every rank. Not differentiable: the reference fills the memory
+    without a graph (gdnet/loss.py:54-85). On CUDA one peer-memory kernel (push to all, flags, bounded wait)."""
+    n = dist.get_world_size(group)
+    with torch.no_grad():
+        flat = payload.detach().float().contiguous().view(-1)
+        if flat.is_cuda and os.environ.get("GDNET_SP_TRANSPORT", "symm") == "symm":
+            from .symm import all_gather_small
+
+            out = all_gather_small(flat, group)
+        else:
+            parts = [torch.empty_like(flat) for _ in range(n)]
+            dist.all_gather(parts, flat, group=group)
+            out = torch.stack(parts)
+    return out.view(n, *payload.shape)
+
+
 # -- names kept from the reference ---------------------------------------------------
 
 class FusedHaloConvSP:

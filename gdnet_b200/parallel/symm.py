@@ -65,7 +65,7 @@ def halo_exchange_symm(tail: torch.Tensor, group, slot):
 _MAXRED: dict = {}
 
 
-def max_allreduce_(vec: torch.Tensor, group=None) -> torch.Tensor:
+def max_allreduce_(vec: torch.Tensor, group=None, gather_out: torch.Tensor | None = None) -> torch.Tensor:
     """In-place element-wise MAX of a small fp32 CUDA vector over the ranks of ``group``: every rank stores
     its vector into every peer's exchange area and waits (bounded) for the peers' flags, one kernel, no
     NCCL call (``csrc/comm.cu:max_allreduce_kernel``). Reference counterpart: the MAX all-reduce of the amax
@@ -83,5 +83,14 @@ def max_allreduce_(vec: torch.Tensor, group=None) -> torch.Tensor:
         st["area"].barrier()
         _MAXRED[id(group)] = st
     st["seq"] += 1
-    cuda_ops.K.max_allreduce(vec, st["area"].ptr_table, st["flags"].ptr_table, st["slot"], rank, world, st["seq"])
-    return vec
+    cuda_ops.K.max_allreduce(vec, st["area"].ptr_table, st["flags"].ptr_table, st["slot"], rank, world, st["seq"], 0, gather_out)
+    return vec if gather_out is None else gather_out
+
+
+def all_gather_small(vec: torch.Tensor, group=None) -> torch.Tensor:
+    """``(world, n)``: every rank's small fp32 CUDA vector, in rank order. Same kernel and exchange area as
+    :func:`max_allreduce_` (every rank stores its vector into its slot of every peer's area, flags, bounded wait),
+    reading the slots out instead of reducing them."""
+    group = group if group is not None else dist.group.WORLD
+    out = torch.empty(dist.get_world_size(group), vec.numel(), dtype=torch.float32, device=vec.device)
+    return max_allreduce_(vec.contiguous().view(-1), group, gather_out=out)

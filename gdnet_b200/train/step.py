@@ -101,6 +101,17 @@ def build_cam_buffer(model: nn.Module, write_chunks: torch.Tensor, sp_group=None
         stacked = write_chunks[:, g0 : g0 + n].transpose(0, 1).reshape(n * B, T)      # chunk-major
         _, side, _, _, _, _, fwd_last = raw(stacked, None, None, sp_group=sp_group, need_logits=False)
         summary = side[0].mean(dim=1)
+        if sp_group is not None and getattr(raw, "sp_state_carry", False) and dist.get_world_size(sp_group) > 1:
+            # sequence parallel with state carry: every write chunk is one earlier sequence cut into shards; all of
+            # its shards' summaries go into the memory, in order, on every rank
+            from ..parallel.sp import gather_states
+
+            states = gather_states(raw.cam.summary(fwd_last, summary), sp_group)       # (shards, n * B, d_sig + d_c)
+            ds = raw.cam.d_sig
+            for i in range(n):
+                for r in range(states.shape[0]):
+                    tags, vals = raw.cam.push(states[r, i * B : (i + 1) * B, :ds], states[r, i * B : (i + 1) * B, ds:], tags, vals)
+            continue
         for i in range(n):
             tags, vals = raw.cam.write(fwd_last[i * B : (i + 1) * B], summary[i * B : (i + 1) * B], tags, vals)
     return tags, vals

@@ -94,6 +94,61 @@ def test_sequence_parallel_equals_unsplit_cpu():
     _spawn(_sp_worker, 2)
 
 
+def _sp_carry_worker(rank, world):
+    """State carry: shard r reads a memory that holds the summaries of shards 0..r-1, exactly what processing the
+    shards one after the other as chunks would have written."""
+    from gdnet_b200.model import GDNet
+    from gdnet_b200.train.step import build_cam_buffer
+
+    torch.manual_seed(0)
+    T = 32 * world
+    model = GDNet(vocab_size=64, d_embed=16, d=32, n_layers=2, n_cycles=2, chunk_size=T, kernel_size=4, n_slots=6)
+    with torch.no_grad():
+        model.cam.rho.fill_(0.7)
+        model.cam.W_pos.weight.normal_(std=0.3)
+    model.eval()      # the spectral norm of the read-out gate would otherwise advance its power iteration per call
+    tok = torch.randint(0, 64, (2, T), generator=torch.Generator().manual_seed(1))
+    t_loc = T // world
+    sl = slice(rank * t_loc, (rank + 1) * t_loc)
+    with torch.no_grad():
+        # oracle from the unsplit trunk: summaries of the shards before this one, then the read-out of this shard
+        fwd, side, _ = model.trunk(tok)
+        tags = torch.zeros(2, 6, model.cam.d_sig)
+        vals = torch.zeros(2, 6, model.cam.d_c)
+        for r in range(rank):
+            seg = slice(r * t_loc, (r + 1) * t_loc)
+            tags, vals = model.cam.write(fwd[:, seg][:, -1], side[0][:, seg].mean(dim=1), tags, vals)
+        out, _ = model.cam.read(fwd[:, sl], side[0][:, sl], tags, vals)
+        want = model.logits_from(out)
+        got, _, gt, gv, _, _, _ = model(tok[:, sl], sp_group=dist.group.WORLD)
+        assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+        assert torch.allclose(gt, tags, atol=1e-6) and torch.allclose(gv, vals, atol=1e-6)
+        if rank > 0:
+            model.sp_state_carry = False
+            plain = model(tok[:, sl], sp_group=dist.group.WORLD)[0]
+            model.sp_state_carry = True
+            assert not torch.allclose(plain, want, atol=1e-4), "the carried state made no difference"
+        else:
+            model.sp_state_carry = False
+            model(tok[:, sl], sp_group=dist.group.WORLD)
+            model.sp_state_carry = True
+        # memory-filling passes: every shard of every write chunk ends up in the buffers, chunk by chunk
+        wc = torch.randint(0, 64, (2, 2, T), generator=torch.Generator().manual_seed(2))
+        ft, fv = build_cam_buffer(model, wc[:, :, sl], sp_group=dist.group.WORLD)
+        tags = torch.zeros(2, 6, model.cam.d_sig)
+        vals = torch.zeros(2, 6, model.cam.d_c)
+        for i in range(2):
+            fwd, side, _ = model.trunk(wc[:, i])
+            for r in range(world):
+                seg = slice(r * t_loc, (r + 1) * t_loc)
+                tags, vals = model.cam.write(fwd[:, seg][:, -1], side[0][:, seg].mean(dim=1), tags, vals)
+        assert torch.allclose(ft, tags, atol=1e-5) and torch.allclose(fv, vals, atol=1e-5)
+
+
+def test_sequence_parallel_state_carry_equals_sequential_chunks():
+    _spawn(_sp_carry_worker, 2)
+
+
 def _step_worker(rank, world, tmp):
     from gdnet_b200.loss import projected_step
     from gdnet_b200.model import GDNet

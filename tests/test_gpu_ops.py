@@ -375,6 +375,58 @@ def test_collective_kernels_single_rank():
     assert torch.equal(vec, keep)
 
 
+@pytest.mark.parametrize("B,T,d", [(1, 64, 256), (3, 40, 128), (2, 8, 320)])
+def test_conv_kernels_exchange_halo_in_kernel(B, T, d):
+    """The sequence-parallel form of the conv kernels on one GPU: two "ranks" are two launches in stream order over
+    two halves of one sequence, and every rank's slot and flag area is a plain local buffer. Forward: rank 0 stores
+    its last rows into rank 1's slot and raises the flag, rank 1 finds it raised. Backward runs rank 1 first (its
+    halo gradient goes to rank 0's slot). Outputs and all gradients must equal the conv over the whole sequence."""
+    from gdnet_b200 import _ext
+
+    cu = _cu()
+    k = 4
+    torch.manual_seed(B * 100 + T)
+    x = torch.randn(B, 2 * T, d, device=DEV).to(BF)
+    w = (torch.randn(d, k, device=DEV) * 0.5)
+    dc = torch.randn(B, 2 * T, d, device=DEV).to(BF)
+    xr = x.float().requires_grad_()
+    wr = w.clone().requires_grad_()
+    want = ref.causal_dwconv(xr, wr)
+    want.backward(dc.float())
+    wt = w.t().contiguous()
+    nbytes = B * (k - 1) * d * 2
+    slots = [torch.zeros(2 * nbytes, dtype=torch.uint8, device=DEV) for _ in range(2)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(2)]
+    tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=DEV)
+    cnt = torch.zeros(2, dtype=torch.int32, device=DEV)
+    halves = [x[:, :T].contiguous(), x[:, T:].contiguous()]
+    outs, halos = [], []
+    for rank in (0, 1):
+        out = torch.empty(B, T, d, device=DEV, dtype=BF)
+        halo = torch.full((B, k - 1, d), 9.0, device=DEV, dtype=BF)
+        cu.K.dwconv_fwd_sp(halves[rank], wt, out, halo, tab(slots), tab(flags), cnt[0:1], 0, 0, rank, 2, 1, 50_000_000)
+        outs.append(out)
+        halos.append(halo)
+    torch.cuda.synchronize()
+    _ext.check_status(x)
+    assert float(halos[0].abs().max()) == 0.0 and torch.equal(halos[1], x[:, T - (k - 1) : T])
+    _check(torch.cat(outs, dim=1), want, 1e-2, "conv over two shards")
+    assert int(cnt[0]) == 0 and int(flags[1][0]) == 1
+    dxs = [None, None]
+    dw = torch.zeros(d, k, device=DEV)
+    dcs = [dc[:, :T].contiguous(), dc[:, T:].contiguous()]
+    for rank in (1, 0):
+        dx = torch.empty(B, T, d, device=DEV, dtype=BF)
+        cu.K.dwconv_bwd_sp(dcs[rank], halves[rank], halos[rank], wt, dx, dw, tab(slots), tab(flags), cnt[1:2], nbytes, 1,
+                           rank, 2, 1, 50_000_000)
+        dxs[rank] = dx
+    torch.cuda.synchronize()
+    _ext.check_status(x)
+    _check(torch.cat(dxs, dim=1), xr.grad, 1e-2, "dx over two shards (halo gradient added in-kernel)")
+    _check(dw, wr.grad, 1e-2, "dw over two shards")
+    assert int(cnt[1]) == 0 and int(flags[0][1]) == 1
+
+
 def test_peer_wait_runs_out_and_reports():
     """A wait for a flag that nothing sets ends after its time limit: the kernel returns, the host raises
     KernelTimeout naming the wait site, and the next launch works. The "peers" are this GPU's own zeroed
