@@ -311,8 +311,10 @@ def main() -> None:
     gathered = (ws.gathered_bytes - gathered0) / K if ws is not None else None
     ms_dev = ev0.elapsed_time(ev1) / K
     update_ms = None
+    breakdown = None
     if eng is not None:
         ts = sorted(eng.update_times_ms())
+        breakdown = eng.update_breakdown_ms()
         eng.time_updates = False
         update_ms = ts[len(ts) // 2] if ts else None
 
@@ -359,6 +361,9 @@ def main() -> None:
             # device time of the update phase per step (gradient collective + projection + AdamW + parameter
             # all-gather, waits for slower ranks included), max over ranks; on one GPU it is the optimizer alone
             "update_phase_ms": update_ms,
+            # rank 0's last update kernel, by device timestamps: wait for the slowest rank at its opening barrier,
+            # pulling the peers' gradients + projection + AdamW + storing the parameters to all ranks, closing barrier
+            "update_breakdown_ms": breakdown,
             # bytes of parameters, gradient buffers and AdamW moments resident on rank 0, and (fully sharded layer
             # matrices) the bytes of GEMM operands it pulled from their owner ranks per step
             "resident_bytes": eng.resident_bytes() if eng is not None else None,

@@ -396,7 +396,7 @@ void dwconv_fwd(const Tensor& x, OptT halo, const Tensor& w, Tensor out, OptT q,
   TORCH_CHECK(x.dim() == 3 && out.dim() == 3, "dwconv: x and out must be (B, T, d)");
   const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
   TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv: taps must be (k, d) contiguous (transposed)");
-  TORCH_CHECK(x.stride(0) == x.stride(1) * T && out.stride(0) == out.stride(1) * T, "dwconv: batch stride must be T rows");
+  TORCH_CHECK(B == 1 || (x.stride(0) == x.stride(1) * T && out.stride(0) == out.stride(1) * T), "dwconv: batch stride must be T rows");
   TORCH_CHECK(out.size(0) == B && out.size(1) == T && out.size(2) == d, "dwconv: out shape");
   if (halo.has_value()) TORCH_CHECK(halo->is_contiguous() && halo->size(0) == B && halo->size(1) == k - 1 && halo->size(2) == d, "dwconv: halo must be (B, k-1, d)");
   TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (out.stride(1) * 2) % 16 == 0, "dwconv: rows must be 16-byte aligned");
@@ -413,7 +413,7 @@ void dwconv_bwd(const Tensor& dc, const Tensor& x, OptT halo, const Tensor& w, O
   const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
   TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv_bwd: taps must be (k, d) contiguous (transposed)");
   TORCH_CHECK(dx.is_contiguous() && dw.is_contiguous() && dw.size(0) == d && dw.size(1) == k, "dwconv_bwd: dx/dw layout");
-  TORCH_CHECK(x.stride(0) == x.stride(1) * T && dc.stride(0) == dc.stride(1) * T, "dwconv_bwd: batch stride must be T rows");
+  TORCH_CHECK(B == 1 || (x.stride(0) == x.stride(1) * T && dc.stride(0) == dc.stride(1) * T), "dwconv_bwd: batch stride must be T rows");
   TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (dc.stride(1) * 2) % 16 == 0, "dwconv_bwd: rows must be 16-byte aligned");
   if (halo.has_value()) TORCH_CHECK(halo->is_contiguous() && halo->size(1) == k - 1, "dwconv_bwd: halo");
   if (tail_add.has_value()) TORCH_CHECK(tail_add->is_contiguous() && tail_add->size(1) == k - 1, "dwconv_bwd: tail_add");
@@ -458,7 +458,7 @@ void dwconv_fwd_sp(const Tensor& x, const Tensor& w, Tensor out, Tensor halo_out
   TORCH_CHECK(x.dim() == 3 && out.dim() == 3, "dwconv: x and out must be (B, T, d)");
   const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
   TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv: taps must be (k, d) contiguous (transposed)");
-  TORCH_CHECK(x.stride(0) == x.stride(1) * T && out.stride(0) == out.stride(1) * T, "dwconv: batch stride must be T rows");
+  TORCH_CHECK(B == 1 || (x.stride(0) == x.stride(1) * T && out.stride(0) == out.stride(1) * T), "dwconv: batch stride must be T rows");
   TORCH_CHECK(out.size(0) == B && out.size(1) == T && out.size(2) == d, "dwconv: out shape");
   TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (out.stride(1) * 2) % 16 == 0, "dwconv: rows must be 16-byte aligned");
   TORCH_CHECK(k == 4 && T % 8 == 0 && d % 8 == 0, "dwconv_fwd_sp: needs k == 4, T % 8 == 0, d % 8 == 0");
@@ -482,7 +482,7 @@ void dwconv_bwd_sp(const Tensor& dc, const Tensor& x, const Tensor& halo, const 
   const int B = (int)x.size(0), T = (int)x.size(1), d = (int)x.size(2), k = (int)w.size(0);
   TORCH_CHECK(w.dim() == 2 && w.size(1) == d && w.is_contiguous(), "dwconv_bwd: taps must be (k, d) contiguous (transposed)");
   TORCH_CHECK(dx.is_contiguous() && dw.is_contiguous() && dw.size(0) == d && dw.size(1) == k, "dwconv_bwd: dx/dw layout");
-  TORCH_CHECK(x.stride(0) == x.stride(1) * T && dc.stride(0) == dc.stride(1) * T, "dwconv_bwd: batch stride must be T rows");
+  TORCH_CHECK(B == 1 || (x.stride(0) == x.stride(1) * T && dc.stride(0) == dc.stride(1) * T), "dwconv_bwd: batch stride must be T rows");
   TORCH_CHECK((x.stride(1) * 2) % 16 == 0 && (dc.stride(1) * 2) % 16 == 0, "dwconv_bwd: rows must be 16-byte aligned");
   TORCH_CHECK(k == 4 && T % 8 == 0 && d % 8 == 0, "dwconv_bwd_sp: needs k == 4, T % 8 == 0, d % 8 == 0");
   TORCH_CHECK(halo.is_contiguous() && halo.dim() == 3 && halo.size(0) == B && halo.size(1) == k - 1 && halo.size(2) == d,
@@ -630,6 +630,117 @@ void quant_tensor(const Tensor& x, const Tensor& scale, Tensor q_row, OptT q_col
                                     stream_of(x)));
 }
 
+gd::GateMixArgs gate_mix_common(const Tensor& g_pre, const Tensor& c, const Tensor& s, const Tensor& R) {
+  TORCH_CHECK(g_pre.dim() == 2 && g_pre.is_contiguous(), "gate_mix: g_pre must be contiguous (rows, d)");
+  const int64_t rows = g_pre.size(0), d = g_pre.size(1);
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&c, &s, &R}) {
+    TORCH_CHECK(t->dim() == 2 && t->size(0) == rows && t->size(1) == d && t->stride(1) == 1 && (t->stride(0) * 2) % 16 == 0,
+                "gate_mix: c, s and R must be (rows, d) with unit column stride and 16-byte aligned rows");
+  }
+  gd::GateMixArgs a{};
+  a.g_pre = bf16_ptr(g_pre, "g_pre");
+  a.c = bf16_ptr(c, "c");
+  a.s = bf16_ptr(s, "s");
+  a.R = bf16_ptr(R, "R");
+  a.rows = rows;
+  a.d = (int)d;
+  a.c_ld = c.stride(0);
+  a.s_ld = s.stride(0);
+  a.r_ld = R.stride(0);
+  return a;
+}
+
+void gate_mix_fwd(const Tensor& g_pre, const Tensor& c, const Tensor& s, const Tensor& R, Tensor fwd_out, Tensor side_out) {
+  c10::cuda::CUDAGuard guard(c.device());
+  OpRange gd_range_(__func__);
+  gd::GateMixArgs a = gate_mix_common(g_pre, c, s, R);
+  TORCH_CHECK(fwd_out.is_contiguous() && side_out.is_contiguous() && fwd_out.numel() == g_pre.numel() &&
+              side_out.numel() == g_pre.numel(), "gate_mix: outputs must be contiguous (rows, d)");
+  a.fwd_out = bf16_mut(fwd_out, "fwd_out");
+  a.side_out = bf16_mut(side_out, "side_out");
+  GD_LAUNCH(gd::launch_gate_mix_fwd(a, stream_of(c)));
+}
+
+void gate_mix_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, const Tensor& c, const Tensor& s, const Tensor& R,
+                  OptT ssq, OptT b2, double eps, Tensor dgp, OptT dq, Tensor dc, Tensor ds, Tensor dR, OptT rowcoef) {
+  c10::cuda::CUDAGuard guard(c.device());
+  OpRange gd_range_(__func__);
+  gd::GateMixArgs a = gate_mix_common(g_pre, c, s, R);
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&dF, &dS, &dgp, &dc, &ds, &dR})
+    TORCH_CHECK(t->is_contiguous() && t->numel() == g_pre.numel(), "gate_mix_bwd: gradients must be contiguous (rows, d)");
+  a.dF = bf16_ptr(dF, "dF");
+  a.dS = bf16_ptr(dS, "dS");
+  if (ssq.has_value()) {
+    TORCH_CHECK(ssq->dim() == 2 && ssq->size(0) == a.rows && ssq->is_contiguous(), "gate_mix_bwd: ssq must be (rows, parts)");
+    a.ssq = f32_ptr(*ssq, "ssq");
+    a.ssq_parts = (int)ssq->size(1);
+  }
+  if (b2.has_value()) {
+    TORCH_CHECK(b2->numel() == a.d, "gate_mix_bwd: b2 must have d elements");
+    a.b2 = f32_ptr(*b2, "b2");
+  }
+  a.eps = (float)eps;
+  a.dgp = bf16_mut(dgp, "dgp");
+  if (dq.has_value()) {
+    TORCH_CHECK(dq->is_contiguous() && dq->numel() == g_pre.numel(), "gate_mix_bwd: dq must be contiguous (rows, d)");
+    a.dq = bf16_mut(*dq, "dq");
+  }
+  a.dc = bf16_mut(dc, "dc");
+  a.ds = bf16_mut(ds, "ds");
+  a.dR = bf16_mut(dR, "dR");
+  if (rowcoef.has_value()) {
+    TORCH_CHECK(rowcoef->numel() == a.rows, "gate_mix_bwd: rowcoef must have one value per row");
+    a.rowcoef = f32_mut(*rowcoef, "rowcoef");
+  }
+  GD_LAUNCH(gd::launch_gate_mix_bwd(a, stream_of(c)));
+}
+
+gd::CamBlendArgs cam_blend_common(const Tensor& z, const Tensor& fwd, const Tensor& retr, const Tensor& w, int64_t T, double eps) {
+  TORCH_CHECK(z.dim() == 2 && z.is_contiguous() && fwd.is_contiguous() && fwd.numel() == z.numel(), "cam_blend: z and fwd must be contiguous (rows, d)");
+  const int64_t rows = z.size(0), d = z.size(1);
+  TORCH_CHECK(T >= 1 && rows % T == 0 && retr.is_contiguous() && retr.numel() == (rows / T) * d, "cam_blend: retrieved must be (rows / T, d)");
+  TORCH_CHECK(w.numel() == d, "cam_blend: one norm weight per column");
+  gd::CamBlendArgs a{};
+  a.z = bf16_ptr(z, "z");
+  a.fwd = bf16_ptr(fwd, "fwd");
+  a.retr = bf16_ptr(retr, "retrieved");
+  a.w = f32_ptr(w, "w");
+  a.rows = rows;
+  a.T = (int)T;
+  a.d = (int)d;
+  a.eps = (float)eps;
+  return a;
+}
+
+void cam_blend_fwd(const Tensor& z, const Tensor& fwd, const Tensor& retr, const Tensor& w, int64_t T, double eps,
+                   Tensor out, Tensor rstd) {
+  c10::cuda::CUDAGuard guard(z.device());
+  OpRange gd_range_(__func__);
+  gd::CamBlendArgs a = cam_blend_common(z, fwd, retr, w, T, eps);
+  TORCH_CHECK(out.is_contiguous() && out.numel() == z.numel() && rstd.numel() == z.size(0), "cam_blend: outputs");
+  a.out = bf16_mut(out, "out");
+  a.rstd = f32_mut(rstd, "rstd");
+  GD_LAUNCH(gd::launch_cam_blend_fwd(a, stream_of(z)));
+}
+
+void cam_blend_bwd(const Tensor& dout, const Tensor& z, const Tensor& fwd, const Tensor& retr, const Tensor& w,
+                   const Tensor& rstd, int64_t T, double eps, Tensor dz, Tensor dfwd, Tensor dretr, Tensor dw) {
+  c10::cuda::CUDAGuard guard(z.device());
+  OpRange gd_range_(__func__);
+  gd::CamBlendArgs a = cam_blend_common(z, fwd, retr, w, T, eps);
+  TORCH_CHECK(dout.is_contiguous() && dz.is_contiguous() && dfwd.is_contiguous() && dout.numel() == z.numel() &&
+              dz.numel() == z.numel() && dfwd.numel() == z.numel(), "cam_blend_bwd: gradients must be contiguous (rows, d)");
+  TORCH_CHECK(dretr.is_contiguous() && dretr.numel() == retr.numel() && dw.numel() == z.size(1) && rstd.numel() == z.size(0),
+              "cam_blend_bwd: dretr (B, d), dw (d), rstd (rows)");
+  a.rstd = const_cast<float*>(f32_ptr(rstd, "rstd"));
+  a.dout = bf16_ptr(dout, "dout");
+  a.dz = bf16_mut(dz, "dz");
+  a.dfwd = bf16_mut(dfwd, "dfwd");
+  a.dretr = f32_mut(dretr, "dretr");
+  a.dw = f32_mut(dw, "dw");
+  GD_LAUNCH(gd::launch_cam_blend_bwd(a, stream_of(z)));
+}
+
 void colsum(const Tensor& x, Tensor out) {
   c10::cuda::CUDAGuard guard(x.device());
   OpRange gd_range_(__func__);
@@ -764,7 +875,8 @@ void batched_gemv(const Tensor& mats, const Tensor& vecs, const Tensor& outs, co
 void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, const Tensor& ptr_table_p,
                      const Tensor& signal_table, Tensor m, Tensor v, const Tensor& scalars, int64_t n, int64_t rank,
                      int64_t world, int64_t seq, int64_t phase, bool p_is_bf16, double beta_proj, double lr, double beta1,
-                     double beta2, double eps, double weight_decay, int64_t step, Tensor shard_sums, bool gather_params) {
+                     double beta2, double eps, double weight_decay, int64_t step, Tensor shard_sums, bool gather_params,
+                     OptT t_red, OptT timing) {
   c10::cuda::CUDAGuard guard(m.device());
   OpRange gd_range_(__func__);
   gd::FusedReduceAdamWArgs a{};
@@ -778,6 +890,14 @@ void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, con
   a.shard_sums = f32_mut(shard_sums, "shard_sums");
   a.n = n; a.rank = (int)rank; a.world = (int)world; a.seq = (uint32_t)seq; a.phase = (int)phase; a.p_is_bf16 = p_is_bf16;
   a.gather_params = gather_params;
+  a.t_red = nullptr;
+  if (t_red.has_value()) a.t_red = f32_mut(*t_red, "t_red");
+  a.timing = nullptr;
+  if (timing.has_value()) {
+    TORCH_CHECK(timing->is_cuda() && timing->scalar_type() == at::kLong && timing->numel() >= 4 && timing->is_contiguous(),
+                "timing must be 4 int64 words on the device");
+    a.timing = reinterpret_cast<unsigned long long*>(timing->data_ptr<int64_t>());
+  }
   a.beta_proj = (float)beta_proj; a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2;
   a.eps = (float)eps; a.weight_decay = (float)weight_decay;
   a.bc1 = (float)(1.0 - std::pow(beta1, (double)step));
@@ -885,6 +1005,10 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("dwconv_bwd_sp(Tensor dc, Tensor x, Tensor halo, Tensor w, Tensor(a!) dx, Tensor(b!) dw, Tensor slot_ptrs, Tensor flag_ptrs, Tensor(c!) counter, int slot_offset, int flag_index, int rank, int world, int seq, int budget_ns=0) -> ()", &dwconv_bwd_sp);
   m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r, Tensor(f!)? q=None, Tensor(g!)? qs=None, Tensor(h!)? qp=None) -> ()", &gate_update_fwd);
   m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r, Tensor(h!)? q=None, Tensor(i!)? qs=None, Tensor(j!)? qp=None) -> ()", &gate_update_bwd);
+  m.def("gate_mix_fwd(Tensor g_pre, Tensor c, Tensor s, Tensor R, Tensor(a!) fwd_out, Tensor(b!) side_out) -> ()", &gate_mix_fwd);
+  m.def("gate_mix_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor c, Tensor s, Tensor R, Tensor? ssq, Tensor? b2, float eps, Tensor(a!) dgp, Tensor(b!)? dq, Tensor(c!) dc, Tensor(d!) ds, Tensor(e!) dR, Tensor(f!)? rowcoef) -> ()", &gate_mix_bwd);
+  m.def("cam_blend_fwd(Tensor z, Tensor fwd, Tensor retr, Tensor w, int T, float eps, Tensor(a!) out, Tensor(b!) rstd) -> ()", &cam_blend_fwd);
+  m.def("cam_blend_bwd(Tensor dout, Tensor z, Tensor fwd, Tensor retr, Tensor w, Tensor rstd, int T, float eps, Tensor(a!) dz, Tensor(b!) dfwd, Tensor(c!) dretr, Tensor(d!) dw) -> ()", &cam_blend_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!)? rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw) -> ()", &rmsnorm_bwd);
   m.def("quant_tile(Tensor x, bool pre_silu, Tensor(a!)? q_row, Tensor(b!)? s_row, int row_mode, Tensor(c!)? q_col, Tensor(d!)? s_col, int col_mode, bool pow2=False, Tensor(e!)? p_row=None, Tensor(f!)? p_col=None, Tensor? peer_delta=None) -> ()", &quant_tile);
@@ -900,7 +1024,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("projected_adamw(Tensor(a!) p, Tensor gt, Tensor? gi, Tensor(b!) m, Tensor(c!) v, Tensor scalars, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()", &projected_adamw);
   m.def("batched_outer_add(Tensor dsts, Tensor ys, Tensor vecs, Tensor coef, Tensor rows, Tensor cols, int max_rows) -> ()", &batched_outer_add);
   m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
-  m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums, bool gather_params=True) -> ()", &allreduce_adamw);
+  m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums, bool gather_params=True, Tensor(d!)? t_red=None, Tensor(e!)? timing=None) -> ()", &allreduce_adamw);
   m.def("gemm_pair_capacity() -> int", []() -> int64_t { return gd::gemm_pair_capacity(); });
   m.def("gemm_set_mx_pair(int on) -> ()", [](int64_t on) { gd::gemm_set_mx_pair((int)on); });
   m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> ()", &register_grad_sink);

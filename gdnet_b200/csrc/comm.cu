@@ -34,16 +34,35 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
   shard_range(a.n, a.rank, a.world, lo, hi);
   // phases 0-2: the peers' buffers hold per-rank gradients and this kernel reduces them;
   // phases 3-5: the shard already holds the sum over ranks (added there by the producers' epilogues)
-  const bool scattered = a.phase >= 3;
-  const bool do_open = a.phase == 0 || a.phase == 1 || a.phase == 3 || a.phase == 5;
+  const bool task_only = a.phase == 6;
+  const bool scattered = a.phase >= 3 && !task_only;
+  const bool do_open = a.phase == 0 || a.phase == 1 || a.phase == 3 || a.phase == 5 || task_only;
   const bool do_reduce = a.phase == 0 || a.phase == 1;
-  const bool do_dots = do_open;
+  const bool do_dots = do_open && !task_only;
   const bool do_update = a.phase == 0 || a.phase == 2 || a.phase == 4 || a.phase == 5;
   const float inv_world = 1.0f / (float)a.world;
+  if (a.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.timing[0] = globaltimer_ns();
 
   if (do_open) {
     __threadfence_system();
-    if (!rank_barrier(a, 0, a.seq)) return;   // every rank's gradients are complete
+    // every rank's gradients are complete (the task-only pass has a flag slot of its own: it runs beside backward)
+    if (!rank_barrier(a, task_only ? 2 : 0, a.seq)) return;
+  }
+  if (a.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.timing[1] = globaltimer_ns();
+
+  if (task_only) {
+    const int64_t stride6 = (int64_t)gridDim.x * blockDim.x * 4;
+    for (int64_t i = lo + ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < hi; i += stride6) {
+      float4 T = make_float4(0, 0, 0, 0);
+      for (int r = 0; r < a.world; ++r) {
+        const int peer = (a.rank + r) % a.world;
+        const float4 t = *reinterpret_cast<const float4*>(a.gt[peer] + i);
+        T.x += t.x; T.y += t.y; T.z += t.z; T.w += t.w;
+      }
+      T.x *= inv_world; T.y *= inv_world; T.z *= inv_world; T.w *= inv_world;
+      *reinterpret_cast<float4*>(a.t_red + (i - lo)) = T;
+    }
+    return;
   }
 
   const float coef = a.scalars[0], gscale = a.scalars[1];
@@ -57,14 +76,23 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
     if (do_reduce) {
       T = make_float4(0, 0, 0, 0);
       I = make_float4(0, 0, 0, 0);
-      for (int r = 0; r < a.world; ++r) {
-        const int peer = (a.rank + r) % a.world;   // start at the local copy, spread peers
-        const float4 t = *reinterpret_cast<const float4*>(a.gt[peer] + i);
-        const float4 f = *reinterpret_cast<const float4*>(a.gi[peer] + i);
-        T.x += t.x; T.y += t.y; T.z += t.z; T.w += t.w;
-        I.x += f.x; I.y += f.y; I.z += f.z; I.w += f.w;
+      if (a.t_red != nullptr) {        // the task gradient of this shard was reduced while backward ran
+        for (int r = 0; r < a.world; ++r) {
+          const int peer = (a.rank + r) % a.world;
+          const float4 f = *reinterpret_cast<const float4*>(a.gi[peer] + i);
+          I.x += f.x; I.y += f.y; I.z += f.z; I.w += f.w;
+        }
+        T = *reinterpret_cast<const float4*>(a.t_red + (i - lo));
+      } else {
+        for (int r = 0; r < a.world; ++r) {
+          const int peer = (a.rank + r) % a.world;   // start at the local copy, spread peers
+          const float4 t = *reinterpret_cast<const float4*>(a.gt[peer] + i);
+          const float4 f = *reinterpret_cast<const float4*>(a.gi[peer] + i);
+          T.x += t.x; T.y += t.y; T.z += t.z; T.w += t.w;
+          I.x += f.x; I.y += f.y; I.z += f.z; I.w += f.w;
+        }
+        T.x *= inv_world; T.y *= inv_world; T.z *= inv_world; T.w *= inv_world;
       }
-      T.x *= inv_world; T.y *= inv_world; T.z *= inv_world; T.w *= inv_world;
       I.x *= inv_world; I.y *= inv_world; I.z *= inv_world; I.w *= inv_world;
       s_tt += T.x * T.x + T.y * T.y + T.z * T.z + T.w * T.w;
       s_ti += T.x * I.x + T.y * I.y + T.z * I.z + T.w * I.w;
@@ -141,6 +169,7 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
     }
   }
 
+  if (a.timing != nullptr && threadIdx.x == 0) atomicMax(a.timing + 2, (unsigned long long)globaltimer_ns());
   if (do_update && a.world > 1) {
     // closing barrier: the last block to finish tells every peer that this rank's parameter
     // writes are done, then waits until every peer has said the same
@@ -157,8 +186,10 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
       if (threadIdx.x < a.world && (int)threadIdx.x != a.rank) {
         st_release_sys(a.signals[threadIdx.x] + 1 * a.world + a.rank, a.seq);
         if (!wait_flag_ge(a.signals[a.rank] + 1 * a.world + threadIdx.x, a.seq))
-          report(a.status, STATUS_TIMEOUT_PEER_FLAG, 32, (int)threadIdx.x);
+          report(a.status, STATUS_TIMEOUT_PEER_FLAG, 33, (int)threadIdx.x);
       }
+      __syncthreads();
+      if (a.timing != nullptr && threadIdx.x == 0) a.timing[3] = globaltimer_ns();
     }
   }
 }
@@ -171,6 +202,8 @@ const char* launch_fused_reduce_adamw(const FusedReduceAdamWArgs& a, cudaStream_
   (void)lo;
   int64_t blocks = (per / 4 + 511) / 512;
   if (blocks > 148 * 2) blocks = 148 * 2;
+  if (a.phase == 6 && blocks > 32) blocks = 32;    // runs beside the second backward pass: leave it the SMs
+  if (a.phase == 6 && a.t_red == nullptr) return "fused_reduce_adamw: the task-only pass needs t_red";
   if (blocks < 1) blocks = 1;
   fused_reduce_adamw_kernel<<<(unsigned)blocks, 512, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? nullptr : "fused_reduce_adamw launch failed";

@@ -27,6 +27,11 @@ struct Status;
 //   phase 3: barrier, shard dot products of the mean gradients
 //   phase 4: AdamW on the shard, all-gather of the parameters, shard cleared, closing barrier
 //   phase 5: 3 and 4 in one launch (scalars known beforehand)
+//
+// Overlap with backward: the task gradient is final after the first backward pass of a step, so
+//   phase 6: barrier (its own flag slot), reduce this rank's shard of the TASK gradient only, mean into t_red
+// runs on a side stream while the second backward pass computes the information gradient. Phases 0-2 then take
+// the reduced task shard from t_red and pull only the information gradient: half the bytes after backward.
 struct FusedReduceAdamWArgs {
   float* const* gt;        // [world] task-gradient buffers (fp32, n elements each)
   float* const* gi;        // [world] info-gradient buffers
@@ -36,6 +41,9 @@ struct FusedReduceAdamWArgs {
   float* v;
   const float* scalars;    // [coef, grad_scale]
   float* shard_sums;       // [3] += sum GT^2, sum GT*GI, sum GI^2 over the reduced shard; [4] block counter
+  float* t_red;            // shard_len floats or null: the reduced task gradient of this rank's shard (see phase 6)
+  unsigned long long* timing;  // null or 4 words of %globaltimer (ns): kernel start, opening barrier passed,
+                               // last block done with its elements, closing barrier passed
   int64_t n;
   int rank, world;
   uint32_t seq;            // strictly increasing per call pair

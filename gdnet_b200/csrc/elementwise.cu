@@ -515,6 +515,95 @@ const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
 __device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&o)[8]) { load_bf16_vec<8>(p, o); }
 __device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&v)[8]) { store_bf16_vec<8>(p, v); }
 
+// ---------------------------------------------------------------------------------------
+// stream update with both gates given (public kernel API): one warp per row
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gate_mix_fwd_kernel(const GateMixArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < a.rows; row += (int64_t)gridDim.x * wpb) {
+    for (int col = lane * 8; col < a.d; col += 256) {
+      float gp[8], cv[8], sv[8], rv[8], fo[8], so[8];
+      ld8(a.g_pre + row * a.d + col, gp);
+      ld8(a.c + row * a.c_ld + col, cv);
+      ld8(a.s + row * a.s_ld + col, sv);
+      ld8(a.R + row * a.r_ld + col, rv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float g = sigmoidf_(gp[i]);
+        fo[i] = cv[i] * g + sv[i] * rv[i];
+        so[i] = cv[i] * (1.0f - g) + sv[i] * (1.0f - rv[i]);
+      }
+      st8(a.fwd_out + row * a.d + col, fo);
+      st8(a.side_out + row * a.d + col, so);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+gate_mix_bwd_kernel(const GateMixArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < a.rows; row += (int64_t)gridDim.x * wpb) {
+    float r = 1.0f;
+    if (a.ssq != nullptr) {
+      float t = 0.0f;
+      for (int p = lane; p < a.ssq_parts; p += 32) t += a.ssq[row * a.ssq_parts + p];
+      t = warp_sum(t);
+      r = rsqrtf(t / (float)a.d + a.eps);
+    }
+    float rowsum = 0.0f;
+    for (int col = lane * 8; col < a.d; col += 256) {
+      float gp[8], cv[8], sv[8], rv[8], df[8], dsv[8], dgp[8], dq[8], dc[8], ds[8], dR[8];
+      ld8(a.g_pre + row * a.d + col, gp);
+      ld8(a.c + row * a.c_ld + col, cv);
+      ld8(a.s + row * a.s_ld + col, sv);
+      ld8(a.R + row * a.r_ld + col, rv);
+      ld8(a.dF + row * a.d + col, df);
+      ld8(a.dS + row * a.d + col, dsv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float g = sigmoidf_(gp[i]);
+        const float diff = df[i] - dsv[i];
+        dgp[i] = diff * cv[i] * g * (1.0f - g);
+        dc[i] = df[i] * g + dsv[i] * (1.0f - g);
+        ds[i] = df[i] * rv[i] + dsv[i] * (1.0f - rv[i]);
+        dR[i] = diff * sv[i];
+        dq[i] = dgp[i] * r;
+        const float b = a.b2 != nullptr ? a.b2[col + i] : 0.0f;
+        rowsum = fmaf(dgp[i], gp[i] - b, rowsum);
+      }
+      st8(a.dgp + row * a.d + col, dgp);
+      if (a.dq != nullptr) st8(a.dq + row * a.d + col, dq);
+      st8(a.dc + row * a.d + col, dc);
+      st8(a.ds + row * a.d + col, ds);
+      st8(a.dR + row * a.d + col, dR);
+    }
+    if (a.rowcoef != nullptr) {
+      rowsum = warp_sum(rowsum);
+      if (lane == 0) a.rowcoef[row] = r * r / (float)a.d * rowsum;
+    }
+  }
+}
+
+static int gate_mix_blocks(int64_t rows) {
+  int64_t b = (rows + 7) / 8;
+  return (int)(b < 148 * 8 ? (b < 1 ? 1 : b) : 148 * 8);
+}
+
+const char* launch_gate_mix_fwd(const GateMixArgs& a, cudaStream_t st) {
+  if (a.d % 8 != 0) return "gate_mix: d must be a multiple of 8";
+  if (a.rows == 0) return nullptr;
+  gate_mix_fwd_kernel<<<gate_mix_blocks(a.rows), 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_mix_fwd launch failed";
+}
+
+const char* launch_gate_mix_bwd(const GateMixArgs& a, cudaStream_t st) {
+  if (a.d % 8 != 0) return "gate_mix: d must be a multiple of 8";
+  if (a.rows == 0) return nullptr;
+  gate_mix_bwd_kernel<<<gate_mix_blocks(a.rows), 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_mix_bwd launch failed";
+}
+
 // fwd' = c*g + s*R, side' = c*(1-g) + s*(1-R) with g = sigmoid(g_pre),
 // R = sigmoid(z * rstd(z) * w_r). Also writes rstd(z) per row, optionally g, and adds the
 // sum of g over the block's rows to gate_sum (for the mean forward-gate value).
@@ -796,6 +885,121 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
   __syncthreads();
   for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dw + i, colacc[i]);
+}
+
+// ---------------------------------------------------------------------------------------
+// read-out blend of the content-addressed memory: one warp per row
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+cam_blend_fwd_kernel(const CamBlendArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < a.rows; row += (int64_t)gridDim.x * wpb) {
+    const __nv_bfloat16* zr = a.z + row * a.d;
+    const __nv_bfloat16* rr = a.retr + (row / a.T) * a.d;
+    float ssq = 0.0f;
+    for (int col = lane * 8; col < a.d; col += 256) {
+      float zv[8];
+      ld8(zr + col, zv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ssq = fmaf(zv[i], zv[i], ssq);
+    }
+    ssq = warp_sum(ssq);
+    const float rstd = rsqrtf(ssq / (float)a.d + a.eps);
+    if (lane == 0) a.rstd[row] = rstd;
+    for (int col = lane * 8; col < a.d; col += 256) {
+      float zv[8], fv[8], rv[8], o[8];
+      ld8(zr + col, zv);
+      ld8(a.fwd + row * a.d + col, fv);
+      ld8(rr + col, rv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float R = sigmoidf_(zv[i] * rstd * a.w[col + i]);
+        o[i] = fv[i] + (rv[i] - fv[i]) * R;
+      }
+      st8(a.out + row * a.d + col, o);
+    }
+  }
+}
+
+// A block walks CAM_ROWS consecutive rows (all of one batch row when T % CAM_ROWS == 0), sums the column terms of
+// dw and dretrieved in shared memory and adds them once per column at the end.
+constexpr int CAM_ROWS = 32;
+
+__global__ void __launch_bounds__(256)
+cam_blend_bwd_kernel(const CamBlendArgs a) {
+  extern __shared__ float cam_acc[];     // [2][d]: dw, dretr
+  float* acc_w = cam_acc;
+  float* acc_r = cam_acc + a.d;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < 2 * a.d; i += blockDim.x) cam_acc[i] = 0.0f;
+  __syncthreads();
+  const int64_t row0 = (int64_t)blockIdx.x * CAM_ROWS;
+  const int64_t b0 = row0 / a.T;
+  for (int64_t row = row0 + warp; row < row0 + CAM_ROWS && row < a.rows; row += wpb) {
+    const bool same = (row / a.T) == b0;     // rows of another batch row add to global memory directly
+    const __nv_bfloat16* rr = a.retr + (row / a.T) * a.d;
+    const float rstd = a.rstd[row];
+    float dot = 0.0f;
+    for (int col = lane * 8; col < a.d; col += 256) {
+      float zv[8], fv[8], rv[8], g[8];
+      ld8(a.z + row * a.d + col, zv);
+      ld8(a.fwd + row * a.d + col, fv);
+      ld8(rr + col, rv);
+      ld8(a.dout + row * a.d + col, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float zh = zv[i] * rstd;
+        const float R = sigmoidf_(zh * a.w[col + i]);
+        const float dzn = g[i] * (rv[i] - fv[i]) * R * (1.0f - R);
+        dot = fmaf(dzn * a.w[col + i], zh, dot);
+      }
+    }
+    dot = warp_sum(dot) / (float)a.d;
+    for (int col = lane * 8; col < a.d; col += 256) {
+      float zv[8], fv[8], rv[8], g[8], dz[8], df[8];
+      ld8(a.z + row * a.d + col, zv);
+      ld8(a.fwd + row * a.d + col, fv);
+      ld8(rr + col, rv);
+      ld8(a.dout + row * a.d + col, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float zh = zv[i] * rstd;
+        const float R = sigmoidf_(zh * a.w[col + i]);
+        const float dzn = g[i] * (rv[i] - fv[i]) * R * (1.0f - R);
+        dz[i] = rstd * (dzn * a.w[col + i] - zh * dot);
+        df[i] = g[i] * (1.0f - R);
+        atomicAdd(&acc_w[col + i], dzn * zh);
+        if (same) atomicAdd(&acc_r[col + i], g[i] * R);
+        else atomicAdd(a.dretr + (row / a.T) * a.d + col + i, g[i] * R);
+      }
+      st8(a.dz + row * a.d + col, dz);
+      st8(a.dfwd + row * a.d + col, df);
+    }
+  }
+  __syncthreads();
+  if (row0 < a.rows) {
+    for (int i = threadIdx.x; i < a.d; i += blockDim.x) {
+      atomicAdd(a.dw + i, acc_w[i]);
+      atomicAdd(a.dretr + b0 * a.d + i, acc_r[i]);
+    }
+  }
+}
+
+const char* launch_cam_blend_fwd(const CamBlendArgs& a, cudaStream_t st) {
+  if (a.d % 8 != 0 || a.T < 1) return "cam_blend: d must be a multiple of 8";
+  if (a.rows == 0) return nullptr;
+  const int64_t blocks = (a.rows + 7) / 8;
+  cam_blend_fwd_kernel<<<(int)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "cam_blend_fwd launch failed";
+}
+
+const char* launch_cam_blend_bwd(const CamBlendArgs& a, cudaStream_t st) {
+  if (a.d % 8 != 0 || a.d > 6144 || a.T < 1) return "cam_blend_bwd: d must be a multiple of 8 and at most 6144";
+  if (a.rows == 0) return nullptr;
+  const int64_t blocks = (a.rows + CAM_ROWS - 1) / CAM_ROWS;
+  if (blocks >= (1ll << 31)) return "cam_blend_bwd: too many rows";
+  cam_blend_bwd_kernel<<<(unsigned)blocks, 256, 2 * a.d * sizeof(float), st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "cam_blend_bwd launch failed";
 }
 
 const char* launch_rmsnorm_fwd(const __nv_bfloat16* x, const float* w, __nv_bfloat16* y, float* rstd, int64_t rows,

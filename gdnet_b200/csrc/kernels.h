@@ -113,6 +113,63 @@ struct GateBwdArgs {
 const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st);
 const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st);
 
+// Stream update with both gates given (the stand-alone form of the reference's K4 / K5 kernels,
+// gdnet/kernel/gated_causal_depthwise_conv/gate_norm.py:34-102): g = sigmoid(g_pre),
+//   fwd' = c g + s R,  side' = c (1 - g) + s (1 - R).
+// Backward also prepares the gate MLP's backward: dgp = (dF - dS) c g (1 - g); with r = rstd of the row of the
+// normalised hidden layer (from the ssq partials, r = rsqrt(sum / d + eps)): dq = r dgp and
+// rowcoef = r^2 / d * sum_n dgp (g_pre - b2).
+struct GateMixArgs {
+  const __nv_bfloat16* g_pre;  // (rows, d) contiguous
+  const __nv_bfloat16* c;      // (rows, d), pitch c_ld
+  const __nv_bfloat16* s;      // (rows, d), pitch s_ld
+  const __nv_bfloat16* R;      // (rows, d), pitch r_ld
+  int64_t rows;
+  int d;
+  int64_t c_ld, s_ld, r_ld;
+  // forward
+  __nv_bfloat16* fwd_out;      // (rows, d) contiguous
+  __nv_bfloat16* side_out;
+  // backward
+  const __nv_bfloat16* dF;     // (rows, d) contiguous
+  const __nv_bfloat16* dS;
+  const float* ssq;            // (rows, parts) or null (then dq = dgp and rowcoef is not written)
+  int ssq_parts;
+  const float* b2;             // (d) or null
+  float eps;
+  __nv_bfloat16* dgp;          // (rows, d)
+  __nv_bfloat16* dq;           // (rows, d) or null
+  __nv_bfloat16* dc;           // (rows, d)
+  __nv_bfloat16* ds;
+  __nv_bfloat16* dR;
+  float* rowcoef;              // (rows) or null
+};
+const char* launch_gate_mix_fwd(const GateMixArgs& a, cudaStream_t st);
+const char* launch_gate_mix_bwd(const GateMixArgs& a, cudaStream_t st);
+
+// Read-out blend of the content-addressed memory (reference: gdnet/memory.py:127-139, after the two linears):
+//   R = sigmoid(RMSNorm(z; w, eps)),  out[b, t] = fwd[b, t] (1 - R) + retrieved[b] R
+// with z, fwd, out (rows = B * T, d) and retrieved (B, d) constant along T. Backward gives dz (through the sigmoid
+// and the norm), dfwd, dretrieved (B, d; summed over T) and dw (d), the last two accumulated with atomics.
+struct CamBlendArgs {
+  const __nv_bfloat16* z;      // (rows, d) contiguous
+  const __nv_bfloat16* fwd;    // (rows, d) contiguous
+  const __nv_bfloat16* retr;   // (B, d) contiguous
+  const float* w;              // (d)
+  int64_t rows;
+  int T, d;
+  float eps;
+  __nv_bfloat16* out;          // forward: (rows, d)
+  float* rstd;                 // forward: written; backward: read. (rows)
+  const __nv_bfloat16* dout;   // backward
+  __nv_bfloat16* dz;
+  __nv_bfloat16* dfwd;
+  float* dretr;                // (B, d) fp32, accumulated
+  float* dw;                   // (d) fp32, accumulated
+};
+const char* launch_cam_blend_fwd(const CamBlendArgs& a, cudaStream_t st);
+const char* launch_cam_blend_bwd(const CamBlendArgs& a, cudaStream_t st);
+
 const char* launch_rmsnorm_fwd(const __nv_bfloat16* x, const float* w, __nv_bfloat16* y, float* rstd, int64_t rows,
                                int d, float eps, cudaStream_t st);
 const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* rstd,

@@ -39,22 +39,45 @@ class CausalDWConvFunctionSP:
         return ops.causal_dwconv(x, W_conv, halo)
 
 
+def _cuda_rows(*ts) -> bool:
+    return all(t.is_cuda for t in ts) and ts[0].dim() == 2 and ts[0].shape[1] % 8 == 0
+
+
 def rmsnorm_fwd(H, W_norm, eps, BLOCK_D=None):
-    """Returns ``(H_norm, rstd)`` like the reference's launcher (gate_norm.py:133-152)."""
+    """Returns ``(H_norm, rstd)`` like the reference's launcher (gate_norm.py:133-152); bf16 CUDA rows run the
+    sm_100a kernel."""
+    if H.is_cuda and H.dtype == torch.bfloat16 and H.dim() == 2 and H.shape[1] % 8 == 0 and H.is_contiguous():
+        from ...ops import cuda as cu
+
+        return cu.rmsnorm_fwd(H, W_norm, eps)
     rstd = torch.rsqrt(H.float().pow(2).mean(-1) + eps)
     return ops.rmsnorm(H, W_norm, eps), rstd
 
 
 def gate_stream_update_fwd(g_pre, conv_flat, side_flat, R_flat, BLOCK_D=None):
+    """``(fwd', side')`` from the gate pre-activation and both streams (gate_norm.py:155-190); differentiable in all
+    four inputs. CUDA tensors run the sm_100a kernel (bf16), CPU tensors the plain-PyTorch statement."""
+    if _cuda_rows(g_pre, conv_flat, side_flat, R_flat):
+        from ...ops import cuda as cu
+
+        return cu.gate_stream_update(g_pre, conv_flat, side_flat, R_flat)
     fo, so, _ = ref.gate_stream_update(g_pre, conv_flat, side_flat, R_flat)
     return fo, so
 
 
 def gated_output(conv_flat, side, R, W1, b1, W_norm, W2, b2, eps: float = 1e-6):
     """Gate MLP + stream update over a pre-computed conv output ``(n_rows, d)``
-    (reference: gdnet/kernel/gated_causal_depthwise_conv/function.py:90-131)."""
+    (reference: gdnet/kernel/gated_causal_depthwise_conv/function.py:90-131). On CUDA with ``d`` and the row count
+    multiples of 128 this is one autograd node on the tensor-core GEMMs and the update kernels; other shapes and
+    CPU tensors take the plain-PyTorch statement."""
     n, d = conv_flat.shape
     dt = conv_flat.dtype
+    if conv_flat.is_cuda:
+        from ...ops import cuda as cu
+
+        if cu.gated_output_ok(conv_flat, W1, W2):
+            fo, so = cu.gated_output(conv_flat, side.reshape(n, d), R.reshape(n, d), W1, b1, W_norm, W2, b2, eps)
+            return fo.to(dt), so.to(dt)
     g_pre = ref.gate_pre(conv_flat, W1, b1, W_norm, W2, b2, eps)
     fo, so, _ = ref.gate_stream_update(g_pre, conv_flat, side.to(dt).reshape(n, d), R.to(dt).reshape(n, d))
     return fo, so

@@ -99,9 +99,31 @@ class Memory(nn.Module):
         retrieved_c, w = ops.fused_mem_read(q, gamma, e, buffer_tags, buffer_vals, self._alpha())
         retrieved = self.W_up(retrieved_c.to(q.dtype))
         h = ref.retrieval_entropy(w, self.n_slots).to(fwd.dtype)
+        if fwd.is_cuda:
+            from ..ops import cuda as cu
+
+            if cu.cam_readout_ok(fwd, self.W_r2.weight):
+                return self._read_out_cuda(cu, side, fwd, retrieved, h), w.detach()
         R = self._blend_gate(side, fwd, retrieved, h)
         rexp = retrieved.unsqueeze(1)
         return fwd * (1 - R) + rexp * R, w.detach()
+
+    def _sn_weight(self):
+        """``W_r1.weight`` after the spectral-norm pre-forward hook, run by hand: it refreshes ``weight`` from
+        ``weight_orig`` (one power iteration in training mode), as a module call would."""
+        for hook in self.W_r1._forward_pre_hooks.values():
+            hook(self.W_r1, None)
+        return self.W_r1.weight
+
+    def _read_out_cuda(self, cu, side, fwd, retrieved, h):
+        """The blend on the sm_100a kernels (``ops/cuda.py:_CamReadoutFn``): the two token-sized blocks of
+        ``W_r1`` and ``W_r2`` on the tensor-core GEMM, norm + sigmoid + blend in one kernel."""
+        d = self.d
+        W = self._sn_weight().to(fwd.dtype)
+        row_bias = F.linear(retrieved, W[:, 2 * d : 3 * d]) + h.unsqueeze(1) * W[:, 3 * d] + self.W_r1.bias.to(fwd.dtype)
+        eps = self.r_norm.eps if self.r_norm.eps is not None else ref.default_rms_eps(fwd.dtype)
+        return cu.cam_readout(side, fwd, retrieved, row_bias, W[:, :d], W[:, d : 2 * d], self.W_r2.weight, self.W_r2.bias,
+                              self.r_norm.weight, eps)
 
     def _blend_gate(self, side, fwd, retrieved, h):
         """``sigmoid(r_norm(W_r2 silu(W_r1 [side, fwd, retrieved, h])))``.
@@ -111,11 +133,7 @@ class Memory(nn.Module):
         ``(B, T, 3d+1)`` concatenation is never built.
         """
         d = self.d
-        # run the spectral-norm pre-forward hook by hand: it refreshes ``weight`` from
-        # ``weight_orig`` (one power iteration in training mode), as a module call would
-        for hook in self.W_r1._forward_pre_hooks.values():
-            hook(self.W_r1, None)
-        W = self.W_r1.weight.to(fwd.dtype)          # (d, 3d+1), already divided by sigma
+        W = self._sn_weight().to(fwd.dtype)          # (d, 3d+1), already divided by sigma
         b = self.W_r1.bias.to(fwd.dtype)
         row_bias = F.linear(retrieved, W[:, 2 * d : 3 * d]) + h.unsqueeze(1) * W[:, 3 * d] + b
         pre = F.linear(side.to(fwd.dtype), W[:, :d]) + F.linear(fwd, W[:, d : 2 * d]) + row_bias.unsqueeze(1)

@@ -919,7 +919,6 @@ def _folded_w2(W2, w_norm):
 # The update kernel of a step also writes the FP8 copy of its side output, straight into the operand buffer
 # of the step that will consume it. The hand-over is keyed on the identity (and version) of the side tensor.
 _side_offers: dict = {}     # id(side tensor) -> (weak reference, version, (u8, su, pu))
-_pending_q8 = None
 
 
 def _alloc_u8(M, d, dev):
@@ -928,13 +927,9 @@ def _alloc_u8(M, d, dev):
             packed_buffer(M, 2 * d, dev))
 
 
-def _offer_side_q8(side_out) -> None:
-    """After a step: remember the buffers its update kernel filled for ``side_out`` (every layer keeps its own
-    side stream, so several offers are open at a time; one dies with its tensor)."""
-    global _pending_q8
-    bufs, _pending_q8 = _pending_q8, None
-    if bufs is None:
-        return
+def _offer_side_q8(side_out, bufs) -> None:
+    """After a step: remember the buffers ``bufs = (u8, su, pu)`` its update kernel filled for ``side_out`` (every
+    layer keeps its own side stream, so several offers are open at a time; one dies with its tensor)."""
     key = id(side_out)
     _side_offers[key] = (weakref.ref(side_out, lambda _r, k=key: _side_offers.pop(k, None)), side_out._version, bufs)
 
@@ -1040,9 +1035,8 @@ class _LayerStepFn(torch.autograd.Function):
             nu8, nsu, npu = _alloc_u8(M, d, dev)      # the next step's [s ; c] operand: this kernel fills the s half
             K.gate_update_fwd(g_pre, z, c, s2, f32(rnw), fwd_out.view(M, d), side_out.view(M, d), None, rstd_z,
                               gate_sum if want_gate_sum else None, eps_r, nu8[:, :d], nsu[:kb], npu[:, :kb])
-            global _pending_q8
-            _pending_q8 = (nu8, nsu, npu)
         else:
+            nu8 = nsu = npu = None
             K.gate_update_fwd(g_pre, z, c, s2, f32(rnw), fwd_out.view(M, d), side_out.view(M, d), None, rstd_z,
                               gate_sum if want_gate_sum else None, eps_r)
 
@@ -1054,10 +1048,13 @@ class _LayerStepFn(torch.autograd.Function):
             ctx.cfg = (B, T, d, fp8, eps_g, halo is not None)
             ctx.sp = sp
             ctx.conv_param = getattr(conv_w, "base_param", None)   # the taps are a view of this parameter
-        return fwd_out, side_out, gate_sum
+        if nu8 is not None:
+            ctx.mark_non_differentiable(nu8, nsu, npu)
+        # the last three: the next step's [s ; c] operand with its s half filled (FP8 mode), handed to the caller
+        return fwd_out, side_out, gate_sum, nu8, nsu, npu
 
     @staticmethod
-    def backward(ctx, dF, dS, dgsum):
+    def backward(ctx, dF, dS, dgsum, _du8=None, _dsu=None, _dpu=None):
         (x, s2, halo, c, h1_pre, a1, z, hg_pre, h, ssq, g_pre, rstd_z, conv_w, rW1, rb1, rW2, rb2, rnw, gW1, gb1,
          gnw, gW2, gb2) = ctx.saved_tensors
         B, T, d, fp8, eps_g, has_halo = ctx.cfg
@@ -1165,6 +1162,178 @@ class _LayerStepFn(torch.autograd.Function):
                 None, None, None, None, None, None)
 
 
+# --------------------------------------------------------------------------------------
+# public kernel API: gate MLP + stream update with the recovery gate given
+# --------------------------------------------------------------------------------------
+class _GateMixFn(torch.autograd.Function):
+    """``fwd' = c g + s R``, ``side' = c (1 - g) + s (1 - R)`` with ``g = sigmoid(g_pre)``; all four inputs get
+    gradients (reference kernels: gdnet/kernel/gated_causal_depthwise_conv/gate_norm.py:34-102)."""
+
+    @staticmethod
+    def forward(ctx, g_pre, c, s, R):
+        M, d = g_pre.shape
+        fo = torch.empty(M, d, dtype=BF16, device=g_pre.device)
+        so = torch.empty(M, d, dtype=BF16, device=g_pre.device)
+        K.gate_mix_fwd(g_pre, c, s, R, fo, so)
+        ctx.save_for_backward(g_pre, c, s, R)
+        return fo, so
+
+    @staticmethod
+    def backward(ctx, dF, dS):
+        g_pre, c, s, R = ctx.saved_tensors
+        outs = [torch.empty_like(g_pre) for _ in range(4)]
+        K.gate_mix_bwd(dF.contiguous(), dS.contiguous(), g_pre, c, s, R, None, None, 0.0, outs[0], None, outs[1], outs[2],
+                       outs[3], None)
+        return tuple(outs)
+
+
+def _rows_bf16(t, M, d):
+    t = t.reshape(M, d)
+    if t.dtype != BF16:
+        t = t.to(BF16)
+    return t if t.stride(1) == 1 and (t.stride(0) * 2) % 16 == 0 else t.contiguous()
+
+
+def gate_stream_update(g_pre, c, s, R):
+    """CUDA form of the stand-alone stream update; ``(fwd', side')`` bf16 ``(rows, d)``."""
+    M, d = g_pre.shape
+    return _GateMixFn.apply(_rows_bf16(g_pre, M, d).contiguous(), _rows_bf16(c, M, d), _rows_bf16(s, M, d), _rows_bf16(R, M, d))
+
+
+class _GatedOutputFn(torch.autograd.Function):
+    """The reference's ``GatedCausalDepthwiseConvFunction`` (gdnet/kernel/gated_causal_depthwise_conv/function.py:11-87)
+    on the sm_100a kernels: gate MLP ``g_pre = W2 RMSNorm(silu(W1 c + b1)) + b2`` as two tensor-core GEMMs (silu and
+    the row sums of squares in the first epilogue, the norm as a per-row scale in the second, with the norm weight
+    folded into ``W2``'s columns), then the stream update with the recovery gate ``R`` given. Backward: one kernel
+    for the update and the row terms of the norm, then weight- and data-gradient GEMMs; gradients for all nine inputs."""
+
+    @staticmethod
+    def forward(ctx, c, s, R, W1, b1, Wn, W2, b2, eps):
+        M, d = c.shape
+        dev = c.device
+        ssq = torch.empty(M, (d + 127) // 128, dtype=F32, device=dev)
+        h_pre = torch.empty(M, d, dtype=BF16, device=dev)
+        h = gemm_bf16(c, W1, bias=f32(b1), act=ACT_SILU, pre_out=h_pre, ssq_out=ssq)
+        W2w = torch.empty(W2.shape, dtype=BF16, device=dev)
+        K.scale_cols(W2.detach().contiguous(), f32(Wn), W2w)
+        g_pre = gemm_bf16(h, W2w, bias=f32(b2), ssq_in=ssq, norm_dim=d, norm_eps=eps)
+        fo = torch.empty(M, d, dtype=BF16, device=dev)
+        so = torch.empty(M, d, dtype=BF16, device=dev)
+        K.gate_mix_fwd(g_pre, c, s, R, fo, so)
+        ctx.save_for_backward(c, s, R, W1, b1, Wn, W2, b2, h_pre, h, ssq, g_pre, W2w)
+        ctx.eps = eps
+        return fo, so
+
+    @staticmethod
+    def backward(ctx, dF, dS):
+        c, s, R, W1, b1, Wn, W2, b2, h_pre, h, ssq, g_pre, W2w = ctx.saved_tensors
+        M, d = c.shape
+        dev = c.device
+        dgp, dq, dc, ds, dR = (torch.empty(M, d, dtype=BF16, device=dev) for _ in range(5))
+        rowcoef = torch.empty(M, dtype=F32, device=dev)
+        K.gate_mix_bwd(dF.contiguous(), dS.contiguous(), g_pre, c, s, R, ssq, f32(b2), ctx.eps, dgp, dq, dc, ds, dR, rowcoef)
+        db2 = torch.zeros(d, dtype=F32, device=dev)
+        K.colsum(dgp, db2)
+        dW2w = gemm_bf16(dq, h, a_mn=True, b_mn=True, out_dtype=F32)
+        dW2 = torch.zeros(W2.shape, dtype=F32, device=dev)
+        dWn = torch.zeros(d, dtype=F32, device=dev)
+        K.unscale_cols_bwd(dW2w, W2.detach().contiguous(), f32(Wn), dW2, dWn)
+        dh_pre = gemm_bf16(dq, W2w, b_mn=True, aux=h_pre, aux_mode=AUX_RMS_SILU_BWD, rowcoef=rowcoef)
+        db1 = torch.zeros(d, dtype=F32, device=dev)
+        K.colsum(dh_pre, db1)
+        dW1 = gemm_bf16(dh_pre, c, a_mn=True, b_mn=True, out_dtype=F32)
+        gemm_bf16(dh_pre, W1, b_mn=True, out=dc, aux=dc, aux_mode=AUX_ADD)
+        return (dc, ds, dR, dW1.to(W1.dtype), db1.to(b1.dtype), dWn.to(Wn.dtype), dW2.to(W2.dtype), db2.to(b2.dtype), None)
+
+
+def gated_output_ok(c, W1, W2) -> bool:
+    M, d = c.shape
+    return c.is_cuda and d % 128 == 0 and M % 128 == 0 and W1.shape == (d, d) and W2.shape == (d, d)
+
+
+def gated_output(c, s, R, W1, b1, Wn, W2, b2, eps):
+    M, d = c.shape
+    w1 = W1 if W1.dtype == BF16 and W1.is_contiguous() else W1.to(BF16).contiguous()
+    w2 = W2 if W2.dtype == BF16 and W2.is_contiguous() else W2.to(BF16).contiguous()
+    return _GatedOutputFn.apply(_rows_bf16(c, M, d), _rows_bf16(s, M, d), _rows_bf16(R, M, d), w1, b1, Wn, w2, b2, float(eps))
+
+
+def rmsnorm_fwd(x2, w, eps):
+    """``(y, rstd)`` of a bf16 ``(rows, d)`` tensor, one kernel (no autograd)."""
+    y = torch.empty_like(x2)
+    rstd = torch.empty(x2.shape[0], dtype=F32, device=x2.device)
+    K.rmsnorm_fwd(x2, f32(w), y, rstd, float(eps))
+    return y, rstd
+
+
+# --------------------------------------------------------------------------------------
+# read-out of the content-addressed memory
+# --------------------------------------------------------------------------------------
+class _CamReadoutFn(torch.autograd.Function):
+    """``out = fwd (1 - R) + retrieved R`` with ``R = sigmoid(RMSNorm(W2 silu(Ws side + Wf fwd + row_bias) + b2))``
+    (reference: gdnet/memory.py:127-139; ``Ws`` / ``Wf`` are the side and forward-stream blocks of the
+    spectral-normalised ``W_r1``, the retrieved vector and the entropy enter as ``row_bias (B, d)``, constant along
+    T). The token-sized GEMMs run on the tcgen05 kernels, one launch per batch row so that the per-row bias is an
+    ordinary column bias; silu is an epilogue; norm, sigmoid and blend are one kernel forward and one backward."""
+
+    @staticmethod
+    def forward(ctx, side, fwd, retrieved, row_bias, Ws, Wf, W2, b2, wn, eps):
+        B, T, d = fwd.shape
+        M = B * T
+        dev = fwd.device
+        side2, fwd2 = side.reshape(M, d), fwd.reshape(M, d)
+        pre = torch.empty(M, d, dtype=BF16, device=dev)
+        a = torch.empty(M, d, dtype=BF16, device=dev)
+        rb = row_bias.to(F32).contiguous()
+        for b in range(B):
+            rows = slice(b * T, (b + 1) * T)
+            gemm_bf16(side2[rows], Ws, out=pre[rows])
+            gemm_bf16(fwd2[rows], Wf, out=a[rows], bias=rb[b], aux=pre[rows], aux_mode=AUX_ADD, pre_out=pre[rows], act=ACT_SILU)
+        z = gemm_bf16(a, W2, bias=f32(b2))
+        out = torch.empty(M, d, dtype=BF16, device=dev)
+        rstd = torch.empty(M, dtype=F32, device=dev)
+        retr = retrieved.to(BF16).contiguous()
+        K.cam_blend_fwd(z, fwd2, retr, f32(wn), T, eps, out, rstd)
+        ctx.save_for_backward(side2, fwd2, retr, Ws, Wf, W2, b2, wn, pre, a, z, rstd)
+        ctx.cfg = (B, T, d, eps, retrieved.dtype, row_bias.dtype)
+        return out.view(B, T, d)
+
+    @staticmethod
+    def backward(ctx, dout):
+        side2, fwd2, retr, Ws, Wf, W2, b2, wn, pre, a, z, rstd = ctx.saved_tensors
+        B, T, d, eps, retr_dtype, rb_dtype = ctx.cfg
+        M = B * T
+        dev = fwd2.device
+        dout2 = dout.reshape(M, d).contiguous()
+        dz = torch.empty(M, d, dtype=BF16, device=dev)
+        dfwd = torch.empty(M, d, dtype=BF16, device=dev)
+        dretr = torch.zeros(B, d, dtype=F32, device=dev)
+        dwn = torch.zeros(d, dtype=F32, device=dev)
+        K.cam_blend_bwd(dout2, z, fwd2, retr, f32(wn), rstd, T, eps, dz, dfwd, dretr, dwn)
+        g_W2 = _wgrad_bf16(dz, a, W2)
+        g_b2 = _bias_grad(dz, b2)
+        dpre = gemm_bf16(dz, W2, b_mn=True, aux=pre, aux_mode=AUX_MUL_SILU_GRAD)
+        drb = torch.zeros(B, d, dtype=F32, device=dev)
+        for b in range(B):
+            K.colsum(dpre[b * T : (b + 1) * T], drb[b])
+        dside = gemm_bf16(dpre, Ws, b_mn=True)
+        gemm_bf16(dpre, Wf, b_mn=True, out=dfwd, aux=dfwd, aux_mode=AUX_ADD)
+        dWs = gemm_bf16(dpre, side2, a_mn=True, b_mn=True, out_dtype=F32)
+        dWf = gemm_bf16(dpre, fwd2, a_mn=True, b_mn=True, out_dtype=F32)
+        return (dside.view(B, T, d), dfwd.view(B, T, d), dretr.to(retr_dtype), drb.to(rb_dtype), dWs.to(Ws.dtype),
+                dWf.to(Wf.dtype), g_W2, g_b2, _sink_vec(wn, dwn), None)
+
+
+def cam_readout_ok(fwd, W2) -> bool:
+    B, T, d = fwd.shape
+    return fwd.is_cuda and fwd.dtype == BF16 and W2.dtype == BF16 and d % 128 == 0 and T % 128 == 0 and d <= 6144
+
+
+def cam_readout(side, fwd, retrieved, row_bias, Ws, Wf, W2, b2, wn, eps):
+    return _CamReadoutFn.apply(side.to(BF16).contiguous(), fwd.contiguous(), retrieved, row_bias, Ws.to(BF16).contiguous(),
+                               Wf.to(BF16).contiguous(), W2, b2, wn, float(eps))
+
+
 def _fused_step_ok(fwd, side, layer, r) -> bool:
     d = fwd.shape[-1]
     M = fwd.shape[0] * fwd.shape[1]
@@ -1201,13 +1370,13 @@ def layer_step(fwd, side, layer, conv_name, g, r, sp_group=None, sp_slot=None, r
     fp8 = isinstance(w1r, FP8Linear) and isinstance(w2r, FP8Linear) and w1r.recipe == "block"
     eps_r = nr.eps if nr.eps is not None else ref.default_rms_eps(BF16)
     side_q8 = _claim_side_q8(side) if fp8 and side.dtype == BF16 and side.is_contiguous() else None
-    fo, so, gsum = _LayerStepFn.apply(
+    fo, so, gsum, nu8, nsu, npu = _LayerStepFn.apply(
         fwd, side.to(BF16), halo, conv.taps, w1r.weight, w1r.bias, w2r.weight, w2r.bias, nr.weight,
         w1g.weight, w1g.bias, ng.weight, w2g.weight, w2g.bias, fp8, float(eps_r), ref.GATE_EPS,
         return_gate == "mean", side_q8, sp,
     )
-    if fp8:
-        _offer_side_q8(so)
+    if fp8 and nu8 is not None:
+        _offer_side_q8(so, (nu8, nsu, npu))
     if return_gate == "mean":
         return fo, so, gsum / float(fo.numel())
     return fo, so

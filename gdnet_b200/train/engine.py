@@ -172,7 +172,8 @@ class TrainEngine(nn.Module):
     def __init__(self, model: nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 1e-2, precision: str = "fp8", process_group=None, sp_group=None,
                  comm: str = "fused", broadcast: bool = True, projection: str = "local",
-                 share_fp8_weights: bool = False, fused_ce: bool = True, shard: str = "none"):
+                 share_fp8_weights: bool = False, fused_ce: bool = True, shard: str = "none",
+                 overlap_task_reduce: bool = True):
         super().__init__()
         self.module = model
         self.precision = precision
@@ -252,6 +253,17 @@ class TrainEngine(nn.Module):
                     cu.K.register_grad_sink(g.g_info, g._sgi.ptr_table, g.per)
             cu.set_spread_grads(True)
         self.scalars = torch.zeros(2, dtype=torch.float32, device=dev)
+        # comm="fused": the task gradient is complete after the first backward pass, so its reduce-scatter runs on a
+        # side stream while the second pass computes the information gradient; the update kernel then pulls only the
+        # information gradient from the peers
+        self.overlap_task_reduce = bool(overlap_task_reduce) and self.comm == "fused"
+        self.task_seq = 0
+        self._task_event = None
+        if self.overlap_task_reduce:
+            self._side_stream = torch.cuda.Stream(device=dev)
+            for g in self.groups:
+                g.t_red = torch.zeros(g.per, dtype=torch.float32, device=dev)
+        self._timing = torch.zeros(4, dtype=torch.int64, device=dev) if dev.type == "cuda" else None
         if dev.type == "cuda":
             from ..ops import cuda as cu
 
@@ -384,6 +396,8 @@ class TrainEngine(nn.Module):
             self._point_main_grad("task")
             loss_task.backward(retain_graph=True)
             self._fold_autograd_grads()
+            if self.overlap_task_reduce and i == accum_steps - 1:
+                self._start_task_reduce()
             with make_autocast(self.precision, dev_type):
                 loss_info = info_losses(base, side, gate_vals, accum_steps)
             self._point_main_grad("info")
@@ -407,6 +421,32 @@ class TrainEngine(nn.Module):
             self.weight_stream.refresh()    # owners re-derive the GEMM operands of their matrices (collective)
             self.weight_stream.end_step()
         return total
+
+    def _start_task_reduce(self) -> None:
+        """Reduce-scatter of the (final) task gradient on the side stream, beside the second backward pass."""
+        from ..ops import cuda as cu
+
+        done = torch.cuda.Event()
+        done.record()
+        self.task_seq += 1
+        with torch.cuda.stream(self._side_stream):
+            self._side_stream.wait_event(done)
+            for gi, g in enumerate(self.groups):
+                cu.K.allreduce_adamw(g.tab_gt, g.tab_gi, g.tab_p, self._flags.ptr_table, g.m, g.v, self.scalars, g.n,
+                                     self.rank, self.world, self.task_seq * 8 + gi, 6, g.dtype == torch.bfloat16,
+                                     0.0, 0.0, 0.9, 0.9, 1e-8, 0.0, 1, g.sums, True, g.t_red)
+            self._task_event = torch.cuda.Event()
+            self._task_event.record()
+
+    def update_breakdown_ms(self) -> dict | None:
+        """Of the last update kernel of the largest group (``time_updates`` on, several GPUs): time spent waiting for
+        the other ranks at the opening barrier, moving and updating the shard, and in the closing barrier."""
+        if self._timing is None or self.comm not in ("fused", "scatter"):
+            return None
+        t = self._timing.tolist()
+        if not all(t):
+            return None
+        return {"wait_ms": (t[1] - t[0]) / 1e6, "transfer_update_ms": (t[2] - t[1]) / 1e6, "close_ms": (t[3] - t[2]) / 1e6}
 
     def update_times_ms(self) -> list[float]:
         """Device time of the update phase (gradient collective + projection + AdamW + parameter all-gather,
@@ -464,6 +504,14 @@ class TrainEngine(nn.Module):
 
         # fused: reduce-scatter + projection + AdamW + all-gather over peer memory
         self.comm_seq += 1
+        t_reds = [None] * len(self.groups)
+        if self._task_event is not None:        # the task gradient's shard was reduced beside the second backward pass
+            torch.cuda.current_stream().wait_event(self._task_event)
+            self._task_event = None
+            t_reds = [g.t_red for g in self.groups]
+        big = max(range(len(self.groups)), key=lambda i: self.groups[i].n)
+        if self.time_updates:
+            self._timing.zero_()
         phases = (0,) if grad_clip <= 0.0 and not glob else (1, 2)
         for phase in phases:
             if phase == 2:
@@ -479,7 +527,9 @@ class TrainEngine(nn.Module):
             for gi, g in enumerate(self.groups):
                 K.allreduce_adamw(g.tab_gt, g.tab_gi, g.tab_p, self._flags.ptr_table,
                                   g.m, g.v, self.scalars, g.n, self.rank, self.world,
-                                  self.comm_seq * 8 + gi, phase, g.dtype == torch.bfloat16, *common, g.sums)
+                                  self.comm_seq * 8 + gi, phase, g.dtype == torch.bfloat16, *common, g.sums, True,
+                                  t_reds[gi] if phase != 2 else None,
+                                  self._timing if self.time_updates and gi == big and phase in (0, 2) else None)
 
     def _update_scattered(self, beta: float, grad_clip: float) -> None:
         """Gradients were reduce-scattered by the producers. Barrier + shard dot products, one tiny

@@ -319,7 +319,7 @@ def test_collective_kernels_single_rank():
     cu = _cu()
     n = 128 * 64
     torch.manual_seed(4)
-    for phases in ((0,), (1, 2), (3, 4), (5,)):
+    for phases in ((0,), (1, 2), (3, 4), (5,), (6, 0), (6, 1, 2)):
         gt, gi = torch.randn(n, device=DEV), torch.randn(n, device=DEV)
         gt0, gi0 = gt.clone(), gi.clone()
         p = torch.randn(n, device=DEV).bfloat16()
@@ -329,9 +329,20 @@ def test_collective_kernels_single_rank():
         flags = torch.zeros(1024, dtype=torch.int32, device=DEV)
         scal = torch.tensor([0.3, 1.0], device=DEV)
         sums = torch.zeros(8, device=DEV)
+        # phase 6 reduces the task gradient alone into t_red (here: a copy), the later phases then take it from there
+        t_red = torch.full((n,), 7.0, device=DEV) if 6 in phases else None
+        timing = torch.zeros(4, dtype=torch.int64, device=DEV)
         for ph in phases:
             cu.K.allreduce_adamw(_ptr_table(gt), _ptr_table(gi), _ptr_table(p), _ptr_table(flags), m, v, scal, n, 0, 1,
-                                 8, ph, True, 0.1, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, sums)
+                                 8, ph, True, 0.1, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, sums, True, t_red if ph != 2 else None,
+                                 timing if ph == 0 else None)
+            if ph == 6:
+                torch.cuda.synchronize()
+                assert torch.equal(t_red, gt0), "task-only pass must leave the mean task gradient in t_red"
+                gt.fill_(float("nan"))        # from here on the task gradient must come from t_red
+        if 0 in phases:
+            t = timing.tolist()
+            assert 0 < t[0] <= t[1] <= t[2], t
         cu.K.projected_adamw(p_ref, gt0, gi0, m_r, v_r, scal, 0.1, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1)
         torch.cuda.synchronize()
         assert torch.equal(p, p_ref), f"phases {phases}: parameters differ from the plain update"
@@ -399,7 +410,7 @@ def test_conv_kernels_exchange_halo_in_kernel(B, T, d):
     flags = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(2)]
     tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=DEV)
     cnt = torch.zeros(2, dtype=torch.int32, device=DEV)
-    halves = [x[:, :T].contiguous(), x[:, T:].contiguous()]
+    halves = [x[:, :T].clone(memory_format=torch.contiguous_format), x[:, T:].clone(memory_format=torch.contiguous_format)]
     outs, halos = [], []
     for rank in (0, 1):
         out = torch.empty(B, T, d, device=DEV, dtype=BF)
@@ -414,7 +425,7 @@ def test_conv_kernels_exchange_halo_in_kernel(B, T, d):
     assert int(cnt[0]) == 0 and int(flags[1][0]) == 1
     dxs = [None, None]
     dw = torch.zeros(d, k, device=DEV)
-    dcs = [dc[:, :T].contiguous(), dc[:, T:].contiguous()]
+    dcs = [dc[:, :T].clone(memory_format=torch.contiguous_format), dc[:, T:].clone(memory_format=torch.contiguous_format)]
     for rank in (1, 0):
         dx = torch.empty(B, T, d, device=DEV, dtype=BF)
         cu.K.dwconv_bwd_sp(dcs[rank], halves[rank], halos[rank], wt, dx, dw, tab(slots), tab(flags), cnt[1:2], nbytes, 1,
@@ -425,6 +436,47 @@ def test_conv_kernels_exchange_halo_in_kernel(B, T, d):
     _check(torch.cat(dxs, dim=1), xr.grad, 1e-2, "dx over two shards (halo gradient added in-kernel)")
     _check(dw, wr.grad, 1e-2, "dw over two shards")
     assert int(cnt[1]) == 0 and int(flags[0][1]) == 1
+
+
+def test_cam_read_out_on_own_kernels_matches_composition():
+    """``Memory.read`` on bf16 CUDA tensors (token-sized GEMMs on the tensor-core kernel, norm + sigmoid + blend in
+    one kernel) against the same module in fp32, which takes the plain-PyTorch composition: output and the gradients
+    of both streams, the buffers and the read-out parameters."""
+    import copy
+
+    from gdnet_b200.models.memory import Memory
+
+    torch.manual_seed(3)
+    B, T, d = 2, 128, 128
+    mem = Memory(d, 32, 16, 8, T).to(DEV)
+    with torch.no_grad():
+        mem.rho.fill_(0.6)
+        mem.W_pos.weight.normal_(std=0.3)
+        mem.W_r2.weight.normal_(std=0.2)
+    mem.eval()                                   # keeps the spectral-norm vectors fixed over the two evaluations
+    m32, mbf = copy.deepcopy(mem), copy.deepcopy(mem).to(BF)
+    fwd = torch.randn(B, T, d, device=DEV).to(BF)
+    side = torch.randn(B, T, d, device=DEV).to(BF)
+    tags = torch.randn(B, 8, 16, device=DEV).to(BF)
+    vals = torch.randn(B, 8, 32, device=DEV).to(BF)
+    wt = torch.randn(B, T, d, device=DEV).to(BF).float()
+    res = []
+    for m, dt in ((m32, torch.float32), (mbf, BF)):
+        ins = [t.to(dt).clone().requires_grad_() for t in (fwd, side, tags, vals)]
+        out, w = m.read(*ins)
+        (out.float() * wt).sum().backward()
+        grads = {n: p.grad.float() for n, p in m.named_parameters() if p.grad is not None}
+        res.append((out.float(), [t.grad.float() for t in ins], grads, w))
+    (o32, g32, p32, w32), (obf, gbf, pbf, wbf) = res
+    _check(obf, o32, 1e-2, "blended forward stream")
+    _check(wbf, w32, 1e-2, "retrieval weights")
+    for name, a, b in zip(("fwd", "side", "tags", "vals"), gbf, g32):
+        _check(a, b, 4e-2, f"gradient of {name}")
+    assert set(pbf) == set(p32), sorted(set(pbf) ^ set(p32))
+    for n in p32:
+        if p32[n].norm() > 1e-6:
+            _check(pbf[n], p32[n], 6e-2, f"gradient of {n}")
+    _status(fwd)
 
 
 def test_peer_wait_runs_out_and_reports():

@@ -91,6 +91,13 @@ def _pair(dev, seed=0):
     with torch.no_grad():
         r.cam.rho.fill_(0.5)
         o.cam.rho.fill_(0.5)
+    # the reference's projection (gdnet/loss.py:238-239) multiplies by a 0-dim float32 coefficient, which turns the
+    # gradient of a 0-dim bfloat16 parameter into float32 and torch refuses to assign it: its step only runs when
+    # the two 0-dim parameters are float32, as they are in its FP8 mode (which leaves trans_ops untouched)
+    for m in (r, o):
+        for name in ("log_tau", "log_temp"):
+            prm = getattr(m.trans_ops, name)
+            prm.data = prm.data.float()
     return ref, r, o
 
 
@@ -135,8 +142,8 @@ def test_forward_and_task_gradient_match_reference():
 @pytest.mark.parametrize("n_write,accum", [(0, 1), (2, 1), (2, 2)])
 def test_projected_step_matches_reference(n_write, accum):
     """One step of the reference's ``gdnet.loss.projected_step`` (three backward passes) against this
-    framework's (two passes: information and transition losses summed first), plain SGD so that the parameter
-    change is the projected gradient itself."""
+    framework's (two passes: information and transition losses summed first); the optimizer is SGD with a zero
+    learning rate, so the projected gradient both steps hand to it can be read from ``p.grad`` afterwards."""
     dev = "cuda"
     ref, r, o = _pair(dev, seed=1)
     from gdnet_b200.loss import projected_step
@@ -145,21 +152,20 @@ def test_projected_step_matches_reference(n_write, accum):
     tok = torch.randint(0, 512, (4, 128), generator=g).to(dev)
     tgt = torch.randint(0, 512, (4, 128), generator=g).to(dev)
     wc = torch.randint(0, 512, (4, n_write, 128), generator=g).to(dev) if n_write else None
-    before = {n: p.detach().float().clone() for n, p in r.named_parameters()}
     res = []
     for m, step in ((r, ref.loss.projected_step), (o, projected_step)):
         m.train()
         params = [p for p in m.parameters() if p.requires_grad]
-        opt = torch.optim.SGD(params, lr=0.5)
+        opt = torch.optim.SGD(params, lr=0.0)       # the step leaves the projected gradient in p.grad
         torch.manual_seed(5)
         loss = step(m, params, opt, tok, tgt, beta=0.1, precision="bf16", write_chunks=wc, accum_steps=accum)
-        res.append((float(loss), {n: p.detach().float() - before[n] for n, p in m.named_parameters()}))
+        res.append((float(loss), {n: p.grad.detach().float().clone() for n, p in m.named_parameters() if p.grad is not None}))
     (lr_, dr), (lo_, do) = res
     assert abs(lo_ - lr_) < 5e-3 * abs(lr_), (lo_, lr_)
+    assert set(dr) == set(do)
     flat_r = torch.cat([dr[n].reshape(-1) for n in sorted(dr)])
     flat_o = torch.cat([do[n].reshape(-1) for n in sorted(dr)])
-    # bf16 parameters: an update smaller than half an ulp of the weight is lost on both sides in the same way, the
-    # rest is compared as one vector and for the largest matrices one by one
-    assert _rel(flat_o, flat_r) < 0.08, f"parameter update differs: {_rel(flat_o, flat_r)}"
-    for n in ("layers.0.rf_W1.weight", "layers.1.gf_W2.weight", "proj_out.weight", "embed.weight"):
-        assert _rel(do[n], dr[n]) < 0.15, f"update of {n} differs: {_rel(do[n], dr[n])}"
+    assert _rel(flat_o, flat_r) < 0.05, f"projected gradient differs: {_rel(flat_o, flat_r)}"
+    for n in ("layers.0.rf_W1.weight", "layers.1.gf_W2.weight", "layers.0.conv_fwd.conv.weight", "proj_out.weight",
+              "embed.weight", "cam.W_up.weight"):
+        assert _rel(do[n], dr[n]) < 0.10, f"projected gradient of {n} differs: {_rel(do[n], dr[n])}"
