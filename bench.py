@@ -46,6 +46,11 @@ CONFIGS = {
     # of the shards before it, and the layer matrices are sharded over the same ranks (gathered by the GEMMs)
     "1.3b-sp": dict(vocab_size=32000, d_embed=2048, d=2048, n_layers=24, n_cycles=2, kernel_size=4, seq_len=65536,
                     micro_batch=1, n_write=4, mode="sp", shard="full"),
+    # the two 1.3B configurations with 2 instead of 24 layers: same shapes per layer, for quick checks on few GPUs
+    "1.3b-l2": dict(vocab_size=32000, d_embed=2048, d=2048, n_layers=2, n_cycles=2, kernel_size=4, seq_len=8192,
+                    micro_batch=2, n_write=4, shard="full"),
+    "1.3b-sp-l2": dict(vocab_size=32000, d_embed=2048, d=2048, n_layers=2, n_cycles=2, kernel_size=4, seq_len=16384,
+                       micro_batch=1, n_write=4, mode="sp", shard="full"),
     "tiny-sp": dict(vocab_size=4096, d_embed=256, d=256, n_layers=2, n_cycles=2, kernel_size=4, seq_len=2048,
                     micro_batch=1, n_write=2, mode="sp", shard="full"),
     "tiny-shard": dict(vocab_size=4096, d_embed=256, d=256, n_layers=2, n_cycles=2, kernel_size=4, seq_len=512,
@@ -284,9 +289,12 @@ def main() -> None:
             torch.cuda.synchronize()
 
     # warm-up (also JIT / autotune / cache fill)
+    first = None
     for i in range(W):
         tok, tgt, wc = to_device(batches[i])
-        step(tok, tgt, wc)
+        out = step(tok, tgt, wc)
+        if i == 0:
+            first = float(out)      # loss of the very first step: the same on both arms when they compute the same model
     sync_all()
 
     # (1) device-timed, inputs resident on the device
@@ -368,6 +376,7 @@ def main() -> None:
             # matrices) the bytes of GEMM operands it pulled from their owner ranks per step
             "resident_bytes": eng.resident_bytes() if eng is not None else None,
             "gathered_bytes_per_step": gathered,
+            "first_loss": first,
             "last_loss": last,
         }))
     if world > 1:

@@ -281,6 +281,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src,
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Every bulk store this thread has committed has finished READING its shared-memory source.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All but the most recently committed bulk store of this thread have finished reading their shared-memory source.
+__device__ __forceinline__ void bulk_wait_read_but_last() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
 // Plain (untiled) bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned,
 // size a multiple of 16 bytes.

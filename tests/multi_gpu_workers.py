@@ -24,7 +24,7 @@ def _gap(a, b, a0, what):
     d = (a - b).abs()
     frac = (d > 5e-3).float().mean().item()
     rel = d.norm().item() / ((a - a0).norm().item() + 1e-12)
-    assert frac < 5e-3 and rel < 0.15, f"{what}: {frac:.2%} of the elements differ by more than 5e-3, relative gap {rel:.3f}"
+    assert frac < 2e-2 and rel < 0.15, f"{what}: {frac:.2%} of the elements differ by more than 5e-3, relative gap {rel:.3f}"
     return rel
 
 
