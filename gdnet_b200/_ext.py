@@ -11,7 +11,10 @@ from pathlib import Path
 
 import torch
 
-_LIB = Path(__file__).resolve().parent / "_C.so"
+import os
+
+# GDNET_LIB: another build of the same library (kernel experiments compare two builds in one session)
+_LIB = Path(os.environ["GDNET_LIB"]) if os.environ.get("GDNET_LIB") else Path(__file__).resolve().parent / "_C.so"
 _loaded = False
 
 

@@ -525,12 +525,11 @@ void gate_update_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, co
   TORCH_CHECK(dsc.size(0) == rows && dsc.size(1) == 2 * d, "gate_update_bwd: dsc must be (rows, 2d)");
   TORCH_CHECK(ssq_g.dim() == 2 && ssq_g.size(0) == rows && ssq_g.is_contiguous(), "gate_update_bwd: ssq_g");
   TORCH_CHECK(db2g.numel() == d && dw_r.numel() == d && db2r.numel() == d && rowcoef.numel() == rows, "gate_update_bwd: sizes");
-  Tensor row_scratch = at::empty({2, rows}, rstd_z.options());
   gd::GateBwdArgs a{bf16_ptr(dF, "dF"), bf16_ptr(dS, "dS"), bf16_ptr(g_pre, "g_pre"), bf16_ptr(z, "z"), bf16_ptr(c, "c"),
                     bf16_ptr(s, "s"), f32_ptr(w_r, "w_r"), f32_ptr(b2g, "b2g"), 1, f32_ptr(rstd_z, "rstd_z"),
                     f32_ptr(ssq_g, "ssq_g"), (int)ssq_g.size(1), (float)eps_g, opt_f32(dgate_mean, "dgate_mean"),
                     bf16_mut(dq, "dq"), bf16_mut(dz, "dz"), bf16_mut(dsc, "dsc"), f32_mut(rowcoef, "rowcoef"),
-                    row_scratch.data_ptr<float>(), row_scratch.data_ptr<float>() + rows, f32_mut(db2g, "db2g"), f32_mut(dw_r, "dw_r"), f32_mut(db2r, "db2r"), rows, d,
+                    nullptr, nullptr, f32_mut(db2g, "db2g"), f32_mut(dw_r, "dw_r"), f32_mut(db2r, "db2r"), rows, d,
                     dF.stride(0), dS.stride(0), c.stride(0), s.stride(0), row_quant_out(q, qs, qp, rows, d)};
   GD_LAUNCH(gd::launch_gate_update_bwd(a, stream_of(c)));
 }

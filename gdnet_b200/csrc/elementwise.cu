@@ -681,10 +681,11 @@ const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st) {
 //   dc_dir = dF*g + dS*(1-g),  ds_dir = dF*R + dS*(1-R)
 //   dy = D*s*R(1-R),  dzh = dy*w_r,  dz = rstd*(dzh - zh*mean_n(dzh*zh))
 //   column sums: db2g += dg_pre, dw_r += dy*zh, db2r += dz
-// Two kernels. (1) row statistics, one warp per row: mean_n(dzh*zh), rstd_g and
-// rowcoef = rstd_g^2/d * T_row. (2) outputs and column sums: a lane owns 8 columns and walks a strip
-// of rows, so the three column sums live in registers; the 8 warps of a block (8 strips of the same
-// 256 columns) are reduced in shared memory before one atomic per column.
+// One kernel, one warp per row, two passes over the row. The first pass gives the row statistics (mean_n(dzh*zh),
+// rstd_g, rowcoef = rstd_g^2/d * T_row); the second reads the row again, which the first pass has just brought
+// into L1 / L2, so HBM sees every input once, and writes the outputs. The three column sums are added into
+// shared memory per element (native shared-memory float adds, laid out so that a warp's lanes hit different
+// banks) and leave the block with one global atomic per column.
 struct GateElem {
   float dgp, dy, zh, g, R;
 };
@@ -701,68 +702,49 @@ __device__ __forceinline__ GateElem gate_elem(float dF, float dS, float z, float
   return e;
 }
 
-__global__ void __launch_bounds__(256)
-gate_bwd_rowstats_kernel(const GateBwdArgs a) {
-  pdl_enter();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
-  if (row >= a.rows) return;
-  const float dgm = (a.dgate_mean != nullptr) ? a.dgate_mean[0] / ((float)a.rows * (float)a.d) : 0.0f;
-  const float rstd = a.rstd_z[row];
-  float ssum = 0.0f;
-  for (int p = lane; p < a.ssq_parts; p += 32) ssum += a.ssq_g[row * a.ssq_parts + p];
-  ssum = warp_sum(ssum);
-  const float rstd_g = rsqrtf(ssum / (float)a.d + a.eps_g);
-  float dot_z = 0.0f, t_row = 0.0f;
-  for (int col = lane * 8; col < a.d; col += 256) {
-    float dF[8], dS[8], zv[8], sv[8], gp[8], cv[8];
-    ld8(a.dF + row * a.dF_ld + col, dF);
-    ld8(a.dS + row * a.dS_ld + col, dS);
-    ld8(a.z + row * a.d + col, zv);
-    ld8(a.s + row * a.s_ld + col, sv);
-    ld8(a.g_pre + row * a.d + col, gp);
-    ld8(a.c + row * a.c_ld + col, cv);
-    const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
-    const float4 b0 = *reinterpret_cast<const float4*>(a.b2g + col), b1 = *reinterpret_cast<const float4*>(a.b2g + col + 4);
-    const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    const float b2[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const GateElem e = gate_elem(dF[i], dS[i], zv[i], sv[i], gp[i], cv[i], wr[i], rstd, dgm);
-      dot_z = fmaf(e.dy * wr[i], e.zh, dot_z);
-      t_row = fmaf(e.dgp, gp[i] - b2[i], t_row);
-    }
-  }
-  dot_z = warp_sum(dot_z) / (float)a.d;
-  t_row = warp_sum(t_row);
-  if (lane == 0) {
-    a.rowcoef[row] = rstd_g * rstd_g / (float)a.d * t_row;
-    a.row_dotz[row] = dot_z;
-    a.row_rstdg[row] = rstd_g;
-  }
-}
+// column c of the row lives at slot (c / 256) * 256 + (c % 8) * 32 + (c % 256) / 8 of a column-sum array: the eight
+// columns of a lane are 32 words apart, so the 32 lanes of a warp add into 32 different banks
+__device__ __forceinline__ int colsum_slot(int col0, int lane, int i) { return col0 - lane * 8 + i * 32 + lane; }
 
-constexpr int GATE_STRIP = 16;   // rows per warp in the column kernel
-
-__global__ void __launch_bounds__(256, 2)
-gate_bwd_cols_kernel(const GateBwdArgs a) {
+__global__ void __launch_bounds__(256, 3)
+gate_update_bwd_kernel(const GateBwdArgs a) {
   pdl_enter();
-  __shared__ float part[3][256];     // column sums of the block's 8 strips, added with shared-memory atomics
-  for (int i = threadIdx.x; i < 3 * 256; i += 256) (&part[0][0])[i] = 0.0f;
+  extern __shared__ float gate_acc[];      // [3][dpad]: db2g, dw_r, db2r
+  const int dpad = (a.d + 255) / 256 * 256;
+  for (int i = threadIdx.x; i < 3 * dpad; i += blockDim.x) gate_acc[i] = 0.0f;
   __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int col = blockIdx.y * 256 + lane * 8;
-  const int64_t r0 = ((int64_t)blockIdx.x * 8 + warp) * GATE_STRIP;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
   const float dgm = (a.dgate_mean != nullptr) ? a.dgate_mean[0] / ((float)a.rows * (float)a.d) : 0.0f;
-  float sg[8], sw[8], sb[8];
+  for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < a.rows; row += (int64_t)gridDim.x * wpb) {
+    const float rstd = a.rstd_z[row];
+    float ssum = 0.0f;
+    for (int p = lane; p < a.ssq_parts; p += 32) ssum += a.ssq_g[row * a.ssq_parts + p];
+    ssum = warp_sum(ssum);
+    const float rstd_g = rsqrtf(ssum / (float)a.d + a.eps_g);
+    float dot_z = 0.0f, t_row = 0.0f;
+    for (int col = lane * 8; col < a.d; col += 256) {
+      float dF[8], dS[8], zv[8], sv[8], gp[8], cv[8];
+      ld8(a.dF + row * a.dF_ld + col, dF);
+      ld8(a.dS + row * a.dS_ld + col, dS);
+      ld8(a.z + row * a.d + col, zv);
+      ld8(a.s + row * a.s_ld + col, sv);
+      ld8(a.g_pre + row * a.d + col, gp);
+      ld8(a.c + row * a.c_ld + col, cv);
+      const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(a.b2g + col), b1 = *reinterpret_cast<const float4*>(a.b2g + col + 4);
+      const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      const float b2[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) sg[i] = sw[i] = sb[i] = 0.0f;
-  if (col < a.d) {
-    const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
-    const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    const int64_t r_end = r0 + GATE_STRIP < a.rows ? r0 + GATE_STRIP : a.rows;
-#pragma unroll 2
-    for (int64_t row = r0; row < r_end; ++row) {
+      for (int i = 0; i < 8; ++i) {
+        const GateElem e = gate_elem(dF[i], dS[i], zv[i], sv[i], gp[i], cv[i], wr[i], rstd, dgm);
+        dot_z = fmaf(e.dy * wr[i], e.zh, dot_z);
+        t_row = fmaf(e.dgp, gp[i] - b2[i], t_row);
+      }
+    }
+    dot_z = warp_sum(dot_z) / (float)a.d;
+    t_row = warp_sum(t_row);
+    if (lane == 0) a.rowcoef[row] = rstd_g * rstd_g / (float)a.d * t_row;
+    for (int col = lane * 8; col < a.d; col += 256) {
       float dF[8], dS[8], zv[8], sv[8], gp[8], cv[8], dq[8], dz[8], dcd[8], dsd[8];
       ld8(a.dF + row * a.dF_ld + col, dF);
       ld8(a.dS + row * a.dS_ld + col, dS);
@@ -770,7 +752,8 @@ gate_bwd_cols_kernel(const GateBwdArgs a) {
       ld8(a.s + row * a.s_ld + col, sv);
       ld8(a.g_pre + row * a.d + col, gp);
       ld8(a.c + row * a.c_ld + col, cv);
-      const float rstd = a.rstd_z[row], rstd_g = a.row_rstdg[row], dot_z = a.row_dotz[row];
+      const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
+      const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const GateElem e = gate_elem(dF[i], dS[i], zv[i], sv[i], gp[i], cv[i], wr[i], rstd, dgm);
@@ -779,9 +762,10 @@ gate_bwd_cols_kernel(const GateBwdArgs a) {
         dz[i] = dzv;
         dcd[i] = dF[i] * e.g + dS[i] * (1.0f - e.g);
         dsd[i] = dF[i] * e.R + dS[i] * (1.0f - e.R);
-        sg[i] += e.dgp;
-        sw[i] = fmaf(e.dy, e.zh, sw[i]);
-        sb[i] += dzv;
+        const int slot = colsum_slot(col, lane, i);
+        atomicAdd(&gate_acc[slot], e.dgp);
+        atomicAdd(&gate_acc[dpad + slot], e.dy * e.zh);
+        atomicAdd(&gate_acc[2 * dpad + slot], dzv);
       }
       st8(a.dq + row * a.d + col, dq);
       st8(a.dz + row * a.d + col, dz);
@@ -794,33 +778,33 @@ gate_bwd_cols_kernel(const GateBwdArgs a) {
       }
     }
   }
-  // element i of lane l is column l * 8 + i; stored at i * 32 + l so that the lanes of a warp hit different banks
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    atomicAdd(&part[0][i * 32 + lane], sg[i]);
-    atomicAdd(&part[1][i * 32 + lane], sw[i]);
-    atomicAdd(&part[2][i * 32 + lane], sb[i]);
-  }
   __syncthreads();
-  const int c = blockIdx.y * 256 + threadIdx.x;
-  if (c < a.d) {
-    const int slot = (threadIdx.x & 7) * 32 + (threadIdx.x >> 3);
-    atomicAdd(a.db2g + c, part[0][slot]);
-    atomicAdd(a.dw_r + c, part[1][slot]);
-    atomicAdd(a.db2r + c, part[2][slot]);
+  for (int c = threadIdx.x; c < a.d; c += blockDim.x) {
+    const int in = c & 255;
+    const int slot = (c - in) + (in & 7) * 32 + (in >> 3);
+    atomicAdd(a.db2g + c, gate_acc[slot]);
+    atomicAdd(a.dw_r + c, gate_acc[dpad + slot]);
+    atomicAdd(a.db2r + c, gate_acc[2 * dpad + slot]);
   }
 }
 
 const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update_bwd: d must be a multiple of 8";
   if (!a.b2g_f32) return "gate_update_bwd: the gate bias must be fp32";
-  if (a.row_dotz == nullptr || a.row_rstdg == nullptr) return "gate_update_bwd: row scratch missing";
   if (a.quant_dz.q != nullptr && a.d % 128 != 0) return "gate_update_bwd: a quantised dz needs d % 128 == 0";
-  launch_pdl(gate_bwd_rowstats_kernel, dim3((unsigned)((a.rows + 7) / 8)), dim3(256), 0, st, a);
-  if (cudaGetLastError() != cudaSuccess) return "gate_bwd_rowstats launch failed";
-  dim3 grid((unsigned)((a.rows + 8 * GATE_STRIP - 1) / (8 * GATE_STRIP)), (a.d + 255) / 256);
-  launch_pdl(gate_bwd_cols_kernel, grid, dim3(256), 0, st, a);
-  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_bwd_cols launch failed";
+  const int dpad = (a.d + 255) / 256 * 256;
+  const size_t smem = 3 * (size_t)dpad * sizeof(float);
+  if (smem > 96 * 1024) return "gate_update_bwd: d too large for the column sums in shared memory";
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(gate_update_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    attr = true;
+  }
+  // enough blocks to fill the GPU, few enough that the per-block global atomics of the column sums stay cheap
+  int64_t blocks = (a.rows + 7) / 8;
+  if (blocks > 148 * 6) blocks = 148 * 6;
+  launch_pdl(gate_update_bwd_kernel, dim3((unsigned)blocks), dim3(256), smem, st, a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_update_bwd launch failed";
 }
 
 // =======================================================================================

@@ -125,21 +125,6 @@ __device__ __forceinline__ float row_scale_for(const GemmEpilogue& e, int m) {
 // instruction. The 16-byte slots are XOR-swizzled so both access patterns are free of bank conflicts.
 constexpr int EPI_STAGE_BYTES_PER_WARP = 32 * 64;
 constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_STAGE_BYTES_PER_WARP;
-// The CTA-pair kernels give every epilogue warp two such areas and alternate between them: a bulk store reads its
-// source asynchronously, and with one area the next chunk had to wait until the previous chunk's store had read it
-// (the whole latency of the copy engine, per 32-column chunk). With two, a store only waits for the one before the
-// previous one.
-constexpr int EPI_STAGE_BYTES_RING = 2 * EPI_STAGE_BYTES;
-
-struct Stage {
-  uint8_t* cur;   // the area the next store writes
-  uint8_t* nxt;   // the other one (== cur without a ring)
-  bool ring;
-};
-
-__device__ __forceinline__ Stage make_stage(uint8_t* base, bool ring) {
-  return Stage{base, ring ? base + EPI_STAGE_BYTES_PER_WARP : base, ring};
-}
 
 __device__ __forceinline__ uint32_t stage_off(int row, int slot) {
   return (uint32_t)(row * 64 + ((slot ^ ((row >> 1) & 3)) << 4));
@@ -157,15 +142,9 @@ __device__ __forceinline__ void stage_acquire() {
 // the tensor behind tmap, as one tiled bulk store: the rows are laid down in the staging area in the 64-byte-swizzle
 // order and an elected lane hands them to the copy engine, so the warp neither reads them back nor issues the
 // global stores itself. Rows and columns outside the tensor are clipped by the copy. Warp-collective.
-__device__ __forceinline__ void store_rows_tma(Stage& st, int lane, const uint32_t (&w)[16], const CUtensorMap* tmap,
+__device__ __forceinline__ void store_rows_tma(uint8_t* stage, int lane, const uint32_t (&w)[16], const CUtensorMap* tmap,
                                                int x, int m_warp) {
-  // the store that last used this area is the one before the previous one (ring) or the previous one
-  if (elect_one()) {
-    if (st.ring) bulk_wait_read_but_last();
-    else bulk_wait_read_all();
-  }
-  __syncwarp();
-  uint8_t* stage = st.cur;
+  stage_acquire();
 #pragma unroll
   for (int q = 0; q < 4; ++q)
     *reinterpret_cast<uint4*>(stage + stage_off(lane, q)) = make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
@@ -176,13 +155,10 @@ __device__ __forceinline__ void store_rows_tma(Stage& st, int lane, const uint32
     bulk_commit_group();
   }
   __syncwarp();
-  st.cur = st.nxt;
-  st.nxt = stage;
 }
 
-__device__ __forceinline__ void store_rows_bf16(Stage& st, int lane, const uint32_t (&w)[16],
+__device__ __forceinline__ void store_rows_bf16(uint8_t* stage, int lane, const uint32_t (&w)[16],
                                                 __nv_bfloat16* base, int64_t ld, int rows_valid) {
-  uint8_t* stage = st.cur;
   stage_acquire();
 #pragma unroll
   for (int q = 0; q < 4; ++q)
@@ -199,9 +175,8 @@ __device__ __forceinline__ void store_rows_bf16(Stage& st, int lane, const uint3
 }
 
 // global rows base[row * ld + 0..31] -> this lane's row in w (rows >= rows_valid read as zero)
-__device__ __forceinline__ void load_rows_bf16(Stage& st, int lane, uint32_t (&w)[16],
+__device__ __forceinline__ void load_rows_bf16(uint8_t* stage, int lane, uint32_t (&w)[16],
                                                const __nv_bfloat16* base, int64_t ld, int rows_valid) {
-  uint8_t* stage = st.cur;
   stage_acquire();
   const int r_in = lane >> 2, slot = lane & 3;
 #pragma unroll
@@ -227,7 +202,7 @@ __device__ __forceinline__ void load_rows_bf16(Stage& st, int lane, uint32_t (&w
 // box (128 bytes, 16-byte pieces XOR-swizzled with the row number), the chunk starting at piece aux_piece0;
 // null to read the auxiliary values from global memory here.
 __device__ __forceinline__ float epilogue_chunk(const GemmEpilogue& e, int M, int N, int m_warp, int lane, int n0,
-                                                float rs, float rowcoef, float (&v)[32], Stage& stage,
+                                                float rs, float rowcoef, float (&v)[32], uint8_t* stage,
                                                 float bias_lane, const uint8_t* aux_row, int aux_piece0,
                                                 bool aux64 = false, const CUtensorMap* t_out = nullptr,
                                                 const CUtensorMap* t_pre = nullptr) {
@@ -539,7 +514,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     const int ew = warp - 2;
-    Stage stage = make_stage(stage_all + ew * EPI_STAGE_BYTES_PER_WARP, false);
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;        // TMEM lane quarter this warp may access
     const int col_half = ew >> 2;        // which 128 of the tile's 256 columns
     int acc = 0;
@@ -653,7 +628,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_all = smem + STAGES * PAIR_STAGE_BYTES;
-  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES_RING;
+  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES;
   PipeBars* bars = reinterpret_cast<PipeBars*>(aux_all + (AUX ? BF16_AUX_BYTES : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -789,7 +764,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
   } else {
     const int ew = warp - 2;
-    Stage stage = make_stage(stage_all + ew * 2 * EPI_STAGE_BYTES_PER_WARP, true);
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;        // TMEM lane quarter this warp may access
     const int col_half = ew >> 2;        // which 128 of the tile's 256 columns
     const uint32_t tempty_lead0 = map_to_cta(tempty0, 0);
@@ -993,7 +968,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else {
     const int ew = warp - 2;
-    Stage stage = make_stage(stage_all + ew * EPI_STAGE_BYTES_PER_WARP, false);
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;
     const int col_half = ew >> 2;  // which 64 of the tile's 128 columns
     int acc = 0;
@@ -1085,7 +1060,7 @@ constexpr int MX_SF_COL0 = MX_ACC * MX_BN;                                   // 
 // 32), one power-of-two scale per row, for the GEMM that consumes this output as its A operand. The values are
 // the bf16-rounded outputs (after silu when q8_silu is set). Warp-collective.
 __device__ __forceinline__ void mx_emit_q8(const GemmEpilogue& e, int M, int m_warp, int nq, int lane, int col_half,
-                                           float (&va)[32], float (&vb)[32], Stage& stage,
+                                           float (&va)[32], float (&vb)[32], uint8_t* stage,
                                            const CUtensorMap* t_q8 = nullptr) {
   const int m = m_warp + lane;
   float amax = 0.0f;
@@ -1235,7 +1210,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
   } else {
     const int ew = warp - 2;
-    Stage stage = make_stage(stage_all + ew * EPI_STAGE_BYTES_PER_WARP, false);
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;
     const int col_half = ew >> 2;        // which 64 of the tile's 128 columns
     int acc = 0;
@@ -1326,8 +1301,8 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 constexpr int MXP_B_ROWS = MX_BN / 2;
 constexpr int MXP_B_BYTES = MXP_B_ROWS * STAGE_ROW_BYTES;
 constexpr int MXP_STAGE_BYTES = MX_A_BYTES + MXP_B_BYTES + 2 * MX_SF_BYTES;   // 25 KB, a multiple of 1024
-constexpr int MXP_STAGES_PLAIN = 7;    // 175 KB of operand stages + 32 KB of epilogue staging
-constexpr int MXP_STAGES_AUX = 6;
+constexpr int MXP_STAGES_PLAIN = 8;
+constexpr int MXP_STAGES_AUX = 7;
 
 template <bool AUX>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -1340,7 +1315,7 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_all = smem + STAGES * MXP_STAGE_BYTES;
-  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES_RING;
+  uint8_t* aux_all = stage_all + EPI_STAGE_BYTES;
   PipeBars* bars = reinterpret_cast<PipeBars*>(aux_all + (AUX ? MX_AUX_BYTES : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -1483,7 +1458,7 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
   } else {
     const int ew = warp - 2;
-    Stage stage = make_stage(stage_all + ew * 2 * EPI_STAGE_BYTES_PER_WARP, true);
+    uint8_t* stage = stage_all + ew * EPI_STAGE_BYTES_PER_WARP;
     const int quarter = warp & 3;
     const int col_half = ew >> 2;        // which 64 of the tile's 128 columns
     const uint32_t tempty_lead0 = map_to_cta(tempty0, 0);
@@ -1746,8 +1721,8 @@ static const char* launch_gemm_bf16_pair(const GemmOperands& op, const GemmShape
   *launched = false;
   static int pairs_plain = -1, pairs_aux = -1;
   const bool aux = e.aux != nullptr;
-  const int smem_plain = 6 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES_RING + (int)sizeof(PipeBars) + 1024;
-  const int smem_aux = 4 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES_RING + BF16_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_plain = 6 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_aux = 4 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + BF16_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
   if (pairs_plain < 0) {
     pairs_plain = pairs_aux = 0;
     if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) == cudaSuccess &&
@@ -1788,7 +1763,7 @@ static const char* launch_gemm_bf16_pair(const GemmOperands& op, const GemmShape
 }
 
 int gemm_pair_capacity() {
-  const int smem_plain = 6 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES_RING + (int)sizeof(PipeBars) + 1024;
+  const int smem_plain = 6 * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
   if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) != cudaSuccess) {
     (void)cudaGetLastError();
     return -1;
@@ -1895,8 +1870,8 @@ static const char* launch_gemm_fp8_mx_pair(const GemmOperands& op, const GemmSha
   *launched = false;
   static int pairs_plain = -1, pairs_aux = -1;
   const bool aux = e.aux != nullptr;
-  const int smem_plain = MXP_STAGES_PLAIN * MXP_STAGE_BYTES + EPI_STAGE_BYTES_RING + (int)sizeof(PipeBars) + 1024;
-  const int smem_aux = MXP_STAGES_AUX * MXP_STAGE_BYTES + EPI_STAGE_BYTES_RING + MX_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_plain = MXP_STAGES_PLAIN * MXP_STAGE_BYTES + EPI_STAGE_BYTES + (int)sizeof(PipeBars) + 1024;
+  const int smem_aux = MXP_STAGES_AUX * MXP_STAGE_BYTES + EPI_STAGE_BYTES + MX_AUX_BYTES + (int)sizeof(PipeBars) + 1024;
   if (pairs_plain < 0) {
     pairs_plain = pairs_aux = 0;
     if (cudaFuncSetAttribute(gemm_fp8_mx_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_plain) == cudaSuccess &&

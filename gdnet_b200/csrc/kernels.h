@@ -99,8 +99,8 @@ struct GateBwdArgs {
   __nv_bfloat16* dz;         // (rows, d)
   __nv_bfloat16* dsc;        // (rows, 2d): [ds_dir | dc_dir]
   float* rowcoef;            // (rows)
-  float* row_dotz;           // (rows) scratch: mean_n(dzh*zh) per row
-  float* row_rstdg;          // (rows) scratch: rstd of the gate RMSNorm per row
+  float* row_dotz;           // unused (the row statistics stay in registers between the two passes of the kernel)
+  float* row_rstdg;          // unused
   float* db2g;               // (d) accumulated
   float* dw_r;               // (d) accumulated
   float* db2r;               // (d) accumulated

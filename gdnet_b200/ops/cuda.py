@@ -961,6 +961,9 @@ class _LayerStepFn(torch.autograd.Function):
         M = B * T
         dev = x.device
         train = any(ctx.needs_input_grad)
+        # outputs nobody differentiates (the FP8 buffers handed to the next step, an unused stream) arrive in backward
+        # as None instead of freshly zero-filled tensors
+        ctx.set_materialize_grads(False)
         x = x if x.is_contiguous() else x.contiguous()
         s2 = s.reshape(M, d) if s.stride(-1) == 1 else s.contiguous().reshape(M, d)
         c3 = torch.empty(B, T, d, dtype=BF16, device=dev)

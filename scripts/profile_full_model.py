@@ -4,8 +4,15 @@
 
 Prints the kernels of a projected step sorted by total device time with their launch counts and
 shares, the peak memory, and optionally writes a chrome trace. Numbers taken under the profiler
-are for *shares* only; throughput is measured by bench.py. Reference counterpart:
-scripts/profile_full_model.py (torch.profiler + cProfile over five steps).
+are for *shares* only; throughput is measured by bench.py.
+
+The host side of the reference's script (scripts/profile_full_model.py:163-211) is here too:
+``--cprofile`` runs the same steps under cProfile and prints the top functions by cumulative time (where the
+Python driver of the step spends its time between launches); ``--memory FILE`` records the allocator's history
+over the profiled steps and writes a snapshot for torch's memory visualiser plus the peak allocated / reserved
+figures; ``--audit`` lists the hidden-copy sites (``.contiguous()``, ``.to()``, ``.clone()``, ``cat`` / ``stack``)
+in the model's hot files by walking their syntax trees (scripts/audit_copies.py), which answers the question the
+reference put to a bytecode listing of ``GDNet.forward``.
 """
 
 from __future__ import annotations
@@ -30,6 +37,9 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--trace", default="")
     ap.add_argument("--top", type=int, default=40)
+    ap.add_argument("--cprofile", action="store_true", help="also profile the Python side of the steps with cProfile")
+    ap.add_argument("--memory", default="", help="write an allocator-history snapshot (pickle) to this file")
+    ap.add_argument("--audit", action="store_true", help="list hidden-copy sites in the hot files")
     args = ap.parse_args()
     cfg = bench.CONFIGS[args.config]
     dev = torch.device("cuda", 0)
@@ -44,6 +54,36 @@ def main():
         run(b)
     torch.cuda.synchronize()
     torch.cuda.reset_peak_memory_stats()
+    host_lines: list[str] = []
+    if args.cprofile:
+        import cProfile
+        import io
+        import pstats
+
+        pr = cProfile.Profile()
+        pr.enable()
+        for b in batches[args.warmup :]:
+            run(b)
+        torch.cuda.synchronize()
+        pr.disable()
+        buf = io.StringIO()
+        pstats.Stats(pr, stream=buf).sort_stats("cumulative").print_stats(40)
+        host_lines += ["", "cProfile, top 40 by cumulative time (host side of the profiled steps):", buf.getvalue()]
+    if args.memory:
+        torch.cuda.memory._record_memory_history(max_entries=200_000)
+        for b in batches[args.warmup :]:
+            run(b)
+        torch.cuda.synchronize()
+        torch.cuda.memory._dump_snapshot(args.memory)
+        torch.cuda.memory._record_memory_history(enabled=None)
+        host_lines += ["", f"allocator history written to {args.memory} (open with torch's memory visualiser); "
+                       f"peak allocated {torch.cuda.max_memory_allocated() / 2**30:.2f} GiB, "
+                       f"peak reserved {torch.cuda.max_memory_reserved() / 2**30:.2f} GiB"]
+    if args.audit:
+        import subprocess
+
+        out = subprocess.run([sys.executable, os.path.join(ROOT, "scripts", "audit_copies.py")], capture_output=True, text=True)
+        host_lines += ["", "hidden-copy sites in the hot files (scripts/audit_copies.py):", out.stdout[-6000:]]
     from torch.profiler import ProfilerActivity, profile
 
     with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
@@ -78,7 +118,7 @@ def main():
     lines.append(f"device idle between kernels: {idle / 1e3 / args.steps:.1f} ms/step; largest waits before:")
     for name, (t, n) in sorted(gaps.items(), key=lambda kv: -kv[1][0])[:12]:
         lines.append(f"       {t / 1e3 / args.steps:9.3f} ms {n / args.steps:8.0f} gaps  {name[:100]}")
-    text = "\n".join(lines)
+    text = "\n".join(lines + host_lines)
     print(text)
     if args.out:
         os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)

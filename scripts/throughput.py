@@ -7,7 +7,8 @@ Same grid, model (d_embed 512, d 2048, 8 layers, 2 cycles, k 9, vocab 100277) an
 reference's scripts/throughput.py; with several ranks the sequence is split over ``--sp-size`` ranks
 (default: all of them) and the batch over the rest. Per configuration: 5 warm-up and 30 timed
 projected steps; reported are device-timed ms/step (CUDA events, max over ranks), tokens/s and peak
-memory. Out-of-memory configurations are reported as such and the sweep continues.
+memory. Out-of-memory configurations are reported as such and the sweep continues. On a terminal the results and a
+read-only NVML view of the GPUs (utilisation, memory, power, SM clock) are shown as live tables (``--plain`` for lines).
 """
 
 from __future__ import annotations
@@ -107,6 +108,8 @@ def main() -> None:
     ap.add_argument("--only", default="", help="comma list like 8x4096,4x8192")
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--json", default="")
+    ap.add_argument("--plain", action="store_true", help="plain lines instead of the live tables")
+    ap.add_argument("--no-monitor", action="store_true", help="do not sample the GPUs through NVML")
     args = ap.parse_args()
 
     init_distributed()
@@ -121,12 +124,22 @@ def main() -> None:
     if args.only:
         grid = [tuple(int(v) for v in item.split("x")) for item in args.only.split(",")]
     rows = []
+    monitor, tables = None, None
+    if is_main_process() and on_gpu and not args.no_monitor:
+        from gdnet_b200.runtime.monitor import GpuMonitor
+
+        monitor = GpuMonitor()
+        monitor.start()
     try:
         for cam in ([True, False] if args.cam == "both" else [args.cam == "on"]):
             args.cam_now = cam
             if is_main_process():
-                print(f"precision={args.precision} cam={'on' if cam else 'off'} gpus={world} sp={sp} dp={dp} model={args.model}")
-                print(f"{'B':>4} {'T':>6} {'ms/step':>10} {'tok/s':>12} {'params(M)':>10} {'mem(GiB)':>9}")
+                from gdnet_b200.runtime.monitor import LiveTables
+
+                if tables is not None:
+                    tables.close()
+                tables = LiveTables(f"precision={args.precision} cam={'on' if cam else 'off'} gpus={world} sp={sp} dp={dp} "
+                                    f"model={args.model}", monitor, force_plain=args.plain)
             for B, T in grid:
                 if T % sp or B % dp:
                     continue
@@ -137,10 +150,13 @@ def main() -> None:
                     torch.cuda.empty_cache()
                     row = dict(B=B, T=T, ms=float("nan"), tok_s=float("nan"), params=0, mem_gib=0.0, cam=cam, oom=True)
                 rows.append(row)
-                if is_main_process():
-                    tag = "  OOM" if row.get("oom") else ""
-                    print(f"{B:>4} {T:>6} {row['ms']:>10.1f} {row['tok_s']:>12,.0f} {row['params'] / 1e6:>10.1f} {row['mem_gib']:>9.1f}{tag}", flush=True)
+                if tables is not None:
+                    tables.add(row)
     finally:
+        if tables is not None:
+            tables.close()
+        if monitor is not None:
+            monitor.stop()
         if args.json and is_main_process():
             json.dump(rows, open(args.json, "w"), indent=1)
         destroy()

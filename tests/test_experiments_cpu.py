@@ -120,3 +120,53 @@ def test_script_runs_one_epoch(script, extra):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     assert r.stdout.strip()
+
+
+def test_gpu_monitor_and_live_tables_with_a_fake_nvml():
+    """The throughput sweep's GPU monitor only reads, and does so through a handful of NVML calls: run it against a
+    stand-in, and render the tables as plain lines."""
+    import io
+    import types
+
+    from gdnet_b200.runtime.monitor import GpuMonitor, LiveTables
+
+    calls = []
+
+    class FakeNvml:
+        NVML_CLOCK_SM = 1
+
+        def nvmlInit(self):
+            calls.append("init")
+
+        def nvmlDeviceGetCount(self):
+            return 2
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return i
+
+        def nvmlDeviceGetUtilizationRates(self, h):
+            return types.SimpleNamespace(gpu=90 + h, memory=10)
+
+        def nvmlDeviceGetMemoryInfo(self, h):
+            return types.SimpleNamespace(used=(40 + h) * 2**30, total=180 * 2**30)
+
+        def nvmlDeviceGetPowerUsage(self, h):
+            return 900_000
+
+        def nvmlDeviceGetClockInfo(self, h, which):
+            return 1700
+
+        def __getattr__(self, name):          # anything that would change a setting is not part of the stand-in
+            raise AssertionError(f"unexpected NVML call {name}")
+
+    mon = GpuMonitor(period=0.01, nvml=FakeNvml())
+    rows = mon.sample()
+    assert [r["util"] for r in rows] == [90, 91] and rows[1]["mem_gib"] == 41.0 and rows[0]["sm_mhz"] == 1700
+    mon.latest = rows
+    buf = io.StringIO()
+    t = LiveTables("sweep", mon, force_plain=True, stream=buf)
+    t.add(dict(B=8, T=4096, ms=432.1, tok_s=75800.0, params=300.5e6, mem_gib=61.2))
+    t.add(dict(B=64, T=8192, ms=float("nan"), tok_s=float("nan"), params=0, mem_gib=0.0, oom=True))
+    t.close()
+    text = buf.getvalue()
+    assert "sweep" in text and "75,800" in text and "OOM" in text and "gpu 1: util 91 %" in text
