@@ -1,6 +1,8 @@
 """Launch one memory-bound kernel a few times on the training shape, for an ncu capture of a small case.
 
     python benchmarks/profile_one_elementwise.py --kernel conv_fwd|conv_bwd|gate_fwd|gate_bwd|quant_rows|quant_tile|rmsnorm|cross_entropy|mem_read|adamw|gemv
+                                                          |mem_read_bwd|rmsnorm_bwd|quant_tensor|colsum|unscale_cols|gate_mix|cam_blend
+                                                          |gemm_fp8_aux|gemm_bf16_aux|fused_update|max_allreduce|gather_jobs
                                                  [--B 8] [--T 4096] [--d 1024] [--iters 3]
 
 Inputs of one launch are a few hundred MB (larger than L2); nothing else runs before the kernel of interest
@@ -91,6 +93,75 @@ def main():
         mats = [rnd(d, 2 * d) for _ in range(96)]
         vecs = [torch.nn.functional.normalize(torch.randn(2 * d, device=dev), dim=0) for _ in mats]
         fn = lambda: cu.sigma_estimates(mats, vecs)
+    elif args.kernel == "mem_read_bwd":
+        Bq, S, dsig, dc = 4096, 64, 128, 128
+        f = lambda *s: torch.randn(*s, device=dev)  # noqa: E731
+        q, gamma, e, tags, vals, alpha = f(Bq, dsig), f(Bq, dsig), f(S, dsig), f(Bq, S, dsig), f(Bq, S, dc), f(1)
+        wts = torch.softmax(f(Bq, S), dim=-1)
+        d_out = f(Bq, dc)
+        outs = [torch.empty_like(q), torch.empty_like(gamma), torch.zeros_like(e), torch.empty_like(tags), torch.empty_like(vals),
+                torch.zeros(1, device=dev)]
+        fn = lambda: K.mem_read_bwd(d_out, q, gamma, e, tags, vals, wts, alpha, *outs)
+    elif args.kernel == "rmsnorm_bwd":
+        x, dy, w = rnd(M, d), rnd(M, d), torch.ones(d, device=dev)
+        rstd, dx, dw = torch.rand(M, device=dev) + 0.5, torch.empty(M, d, device=dev, dtype=bf), torch.zeros(d, device=dev)
+        fn = lambda: K.rmsnorm_bwd(dy, x, w, rstd, dx, dw)
+    elif args.kernel == "quant_tensor":
+        x, scale = rnd(M, d), torch.full((1,), 100.0, device=dev)
+        fn = lambda: cu.quantize_fp8_tensor(x, scale, True)
+    elif args.kernel == "colsum":
+        x, out = rnd(M, d), torch.zeros(d, device=dev)
+        fn = lambda: K.colsum(x, out)
+    elif args.kernel == "unscale_cols":
+        W2, g = rnd(4 * d, 4 * d), torch.randn(4 * d, 4 * d, device=dev)
+        colw, dW2, dcol = torch.ones(4 * d, device=dev), torch.zeros(4 * d, 4 * d, device=dev), torch.zeros(4 * d, device=dev)
+        fn = lambda: K.unscale_cols_bwd(g, W2, colw, dW2, dcol)
+    elif args.kernel == "gate_mix":
+        gp, c, s2, R = rnd(M, d), rnd(M, d), rnd(M, d), torch.rand(M, d, device=dev).to(bf)
+        fo, so = torch.empty(M, d, device=dev, dtype=bf), torch.empty(M, d, device=dev, dtype=bf)
+        fn = lambda: K.gate_mix_fwd(gp, c, s2, R, fo, so)
+    elif args.kernel == "cam_blend":
+        z, f2, retr = rnd(M, d), rnd(M, d), rnd(B, d)
+        out, rstd = torch.empty(M, d, device=dev, dtype=bf), torch.empty(M, device=dev)
+        fn = lambda: K.cam_blend_fwd(z, f2, retr, torch.ones(d, device=dev), T, 1e-6, out, rstd)
+    elif args.kernel in ("gemm_fp8_aux", "gemm_bf16_aux"):
+        # the pair GEMMs with an auxiliary input and a second output (the <true> instantiations): layer shapes
+        a, w = rnd(M, d), rnd(d, d) * 0.05
+        aux, pre, bias = rnd(M, d), torch.empty(M, d, device=dev, dtype=bf), torch.zeros(d, device=dev)
+        out = torch.empty(M, d, device=dev, dtype=bf)
+        if args.kernel == "gemm_fp8_aux":
+            a8, _, pa = cu.quantize_rows_mx(a)
+            qw = cu.quantize_weight(w)
+            fn = lambda: cu.gemm_fp8_mx(a8, pa, qw.q, qw.p, out=out, bias=bias, aux=aux, aux_mode=cu.AUX_ADD, pre_out=pre, act=cu.ACT_SILU)
+        else:
+            fn = lambda: cu.gemm_bf16(a, w, out=out, bias=bias, aux=aux, aux_mode=cu.AUX_ADD, pre_out=pre, act=cu.ACT_SILU)
+    elif args.kernel in ("fused_update", "max_allreduce", "gather_jobs"):
+        # the peer-memory kernels with a world of one: every "peer" table holds this GPU's own buffer, nothing waits
+        tab = lambda t: torch.tensor([t.data_ptr()], dtype=torch.int64, device=dev)  # noqa: E731
+        if args.kernel == "fused_update":
+            n = 64 * 1024 * 1024
+            gt, gi = torch.randn(n, device=dev), torch.randn(n, device=dev)
+            p_, m_, v_ = torch.zeros(n, device=dev, dtype=bf), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+            flags, scal, sums = torch.zeros(1024, dtype=torch.int32, device=dev), torch.tensor([0.1, 1.0], device=dev), torch.zeros(8, device=dev)
+            seq = [0]
+
+            def fn():
+                seq[0] += 1
+                K.allreduce_adamw(tab(gt), tab(gi), tab(p_), tab(flags), m_, v_, scal, n, 0, 1, seq[0], 0, True, 0.1, 1e-3, 0.9,
+                                  0.999, 1e-8, 0.01, 1, sums)
+        elif args.kernel == "max_allreduce":
+            area, fl, vec = torch.zeros(2 * 4096, device=dev), torch.zeros(64, dtype=torch.int32, device=dev), torch.rand(4096, device=dev)
+            seq = [0]
+
+            def fn():
+                seq[0] += 1
+                K.max_allreduce(vec, tab(area), tab(fl), 4096, 0, 1, seq[0])
+        else:
+            n = 256 * 1024 * 1024
+            src, dst = torch.randint(0, 255, (n,), dtype=torch.uint8, device=dev), torch.empty(n, dtype=torch.uint8, device=dev)
+            rows = [[src.data_ptr() + o, dst.data_ptr() + o, 0, 65536 // 16] for o in range(0, n, 65536)]
+            table = torch.tensor(rows, dtype=torch.int64, device=dev)
+            fn = lambda: K.gather_jobs(table)
     else:
         raise SystemExit(f"unknown kernel {args.kernel}")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

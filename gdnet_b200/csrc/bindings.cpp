@@ -94,14 +94,20 @@ Tensor kernel_status(const Tensor& like) { return status_tensor(like.get_device(
 // peer_add whose destination lies inside a registered buffer adds into the owner rank's copy instead.
 struct GradSink {
   uintptr_t base;
-  int64_t elems;
+  int64_t elems;    // > 0: a local full-size buffer starts at `base`; < 0: virtual (|elems| flat elements, no local buffer)
   Tensor table;     // int64 device tensor: the buffer's address on every rank
   int64_t shard_elems;
+  int64_t id;
 };
 
 std::vector<GradSink>& grad_sinks() {
   static std::vector<GradSink> sinks;
   return sinks;
+}
+
+int64_t next_sink_id() {
+  static int64_t next = 0;
+  return next++;
 }
 
 const GradSink* find_sink(const void* p) {
@@ -111,29 +117,46 @@ const GradSink* find_sink(const void* p) {
   return nullptr;
 }
 
-void register_grad_sink(const Tensor& flat, const Tensor& ptr_table, int64_t shard_elems) {
+// Every training engine registers the buffers it spreads over the ranks and removes them again when it is closed, so
+// several engines can live in one process. Returns the handle for unregister_grad_sink.
+int64_t register_grad_sink(const Tensor& flat, const Tensor& ptr_table, int64_t shard_elems) {
   TORCH_CHECK(flat.is_cuda() && flat.scalar_type() == at::kFloat && flat.is_contiguous(), "grad sink must be flat fp32");
   TORCH_CHECK(ptr_table.is_cuda() && ptr_table.scalar_type() == at::kLong, "ptr_table must be an int64 CUDA tensor");
   TORCH_CHECK(shard_elems > 0 && shard_elems % 128 == 0, "shard_elems must be a positive multiple of 128");
   TORCH_CHECK(flat.numel() <= shard_elems * ptr_table.numel(), "shards do not cover the buffer");
-  grad_sinks().push_back({reinterpret_cast<uintptr_t>(flat.data_ptr()), flat.numel(), ptr_table, shard_elems});
+  const int64_t id = next_sink_id();
+  grad_sinks().push_back({reinterpret_cast<uintptr_t>(flat.data_ptr()), flat.numel(), ptr_table, shard_elems, id});
+  return id;
 }
 
 // A sink without a local full-size buffer (parameters sharded over the ranks: every rank holds only its own
-// shard of the flat gradient). Gradients are addressed by (sink index, flat element offset); ptr_table[r] is
+// shard of the flat gradient). Gradients are addressed by (sink handle, flat element offset); ptr_table[r] is
 // rank r's shard base minus r * shard_elems elements, so that table[idx / shard_elems] + idx is element idx.
 int64_t register_virtual_grad_sink(const Tensor& ptr_table, int64_t total_elems, int64_t shard_elems) {
   TORCH_CHECK(ptr_table.is_cuda() && ptr_table.scalar_type() == at::kLong, "ptr_table must be an int64 CUDA tensor");
   TORCH_CHECK(shard_elems > 0 && shard_elems % 128 == 0, "shard_elems must be a positive multiple of 128");
   TORCH_CHECK(total_elems <= shard_elems * ptr_table.numel(), "shards do not cover the buffer");
-  grad_sinks().push_back({0, -total_elems, ptr_table, shard_elems});     // elems < 0: never matched by address
-  return (int64_t)grad_sinks().size() - 1;
+  const int64_t id = next_sink_id();
+  grad_sinks().push_back({0, -total_elems, ptr_table, shard_elems, id});     // elems < 0: never matched by address
+  return id;
 }
 
-const GradSink& sink_at(int64_t i) {
-  TORCH_CHECK(i >= 0 && i < (int64_t)grad_sinks().size(), "unknown gradient sink ", i);
-  return grad_sinks()[(size_t)i];
+void unregister_grad_sink(int64_t id) {
+  auto& v = grad_sinks();
+  for (size_t i = 0; i < v.size(); ++i)
+    if (v[i].id == id) {
+      v.erase(v.begin() + (long)i);
+      return;
+    }
 }
+
+const GradSink& sink_at(int64_t id) {
+  for (const GradSink& s : grad_sinks())
+    if (s.id == id) return s;
+  TORCH_CHECK(false, "unknown gradient sink ", id);
+}
+
+bool is_spread(const Tensor& t) { return t.is_cuda() && find_sink(t.data_ptr()) != nullptr; }
 
 // One-shot attachments for the next tensor-core GEMM launched from this thread: a list of peer -> local gather
 // jobs that the launch carries, and the counters that tell the hardware-scaled fp8 GEMM when its own B has landed.
@@ -870,6 +893,20 @@ void batched_gemv(const Tensor& mats, const Tensor& vecs, const Tensor& outs, co
                                     cols.data_ptr<int>(), is_bf16.data_ptr<int>(), n, (int)max_rows, stream_of(mats)));
 }
 
+void sn_power_iter(const Tensor& W, Tensor u, Tensor v, Tensor sigma, bool do_iter, double eps) {
+  c10::cuda::CUDAGuard guard(W.device());
+  OpRange gd_range_(__func__);
+  TORCH_CHECK(W.is_cuda() && W.dim() == 2 && W.is_contiguous(), "sn_power_iter: W must be a contiguous CUDA matrix");
+  TORCH_CHECK(W.scalar_type() == at::kBFloat16 || W.scalar_type() == at::kFloat, "sn_power_iter: W must be bf16 or fp32");
+  TORCH_CHECK(u.is_contiguous() && v.is_contiguous() && u.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat &&
+              u.numel() == W.size(0) && v.numel() == W.size(1) && sigma.scalar_type() == at::kFloat && sigma.numel() >= 1,
+              "sn_power_iter: u (rows), v (cols), sigma (1) must be contiguous fp32");
+  Tensor t = at::empty({W.size(0)}, u.options());
+  GD_LAUNCH(gd::launch_sn_power_iter(W.data_ptr(), W.scalar_type() == at::kBFloat16, u.data_ptr<float>(), v.data_ptr<float>(),
+                                     t.data_ptr<float>(), sigma.data_ptr<float>(), (int)W.size(0), (int)W.size(1), do_iter,
+                                     (float)eps, stream_of(W)));
+}
+
 // ---- communication kernels over peer memory (comm.cu) -----------------------------------------
 void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, const Tensor& ptr_table_p,
                      const Tensor& signal_table, Tensor m, Tensor v, const Tensor& scalars, int64_t n, int64_t rank,
@@ -1022,11 +1059,14 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("grad_dots(Tensor gt, Tensor? gi, Tensor(a!) sums) -> ()", &grad_dots);
   m.def("projected_adamw(Tensor(a!) p, Tensor gt, Tensor? gi, Tensor(b!) m, Tensor(c!) v, Tensor scalars, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()", &projected_adamw);
   m.def("batched_outer_add(Tensor dsts, Tensor ys, Tensor vecs, Tensor coef, Tensor rows, Tensor cols, int max_rows) -> ()", &batched_outer_add);
+  m.def("sn_power_iter(Tensor W, Tensor(a!) u, Tensor(b!) v, Tensor(c!) sigma, bool do_iter, float eps) -> ()", &sn_power_iter);
   m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
   m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums, bool gather_params=True, Tensor(d!)? t_red=None, Tensor(e!)? timing=None) -> ()", &allreduce_adamw);
   m.def("gemm_pair_capacity() -> int", []() -> int64_t { return gd::gemm_pair_capacity(); });
   m.def("gemm_set_mx_pair(int on) -> ()", [](int64_t on) { gd::gemm_set_mx_pair((int)on); });
-  m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> ()", &register_grad_sink);
+  m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> int", &register_grad_sink);
+  m.def("unregister_grad_sink(int id) -> ()", &unregister_grad_sink);
+  m.def("is_spread(Tensor t) -> bool", &is_spread);
   m.def("clear_grad_sinks() -> ()", &clear_grad_sinks);
   m.def("register_virtual_grad_sink(Tensor ptr_table, int total_elems, int shard_elems) -> int", &register_virtual_grad_sink);
   m.def("peer_add_at(int sink, int off, Tensor src) -> ()", &peer_add_at);

@@ -254,6 +254,11 @@ struct AdamWArgs {
 const char* launch_projected_adamw(const AdamWArgs& a, cudaStream_t st);
 
 // y_i = W_i v_i for a batch of bf16/fp32 matrices given by pointer tables (spectral estimates)
+// One power iteration of torch's spectral norm (v <- normalize(W^T u), u <- normalize(W v)) and sigma = u^T W v for one
+// row-major matrix, bf16 or fp32, any shape; u (rows), v (cols), t (rows, scratch) fp32. do_iter = 0: sigma only.
+const char* launch_sn_power_iter(const void* W, int w_is_bf16, float* u, float* v, float* t, float* sigma_out, int rows,
+                                 int cols, int do_iter, float eps, cudaStream_t st);
+
 const char* launch_batched_gemv(const void* const* mats, const float* const* vecs, float* const* outs,
                                 const int* rows, const int* cols, const int* is_bf16, int n_mats, int max_rows,
                                 cudaStream_t st);

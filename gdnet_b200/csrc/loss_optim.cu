@@ -417,6 +417,91 @@ const char* launch_batched_outer_add(float* const* dsts, const float* const* ys,
   return cudaGetLastError() == cudaSuccess ? nullptr : "batched_outer_add launch failed";
 }
 
+// =======================================================================================
+// hard spectral norm: one power iteration and sigma for one matrix, in one block
+// =======================================================================================
+// torch.nn.utils.spectral_norm (what the reference wraps cam.W_r1 in, gdnet/memory.py:68) does, per training forward,
+//   v <- normalize(W^T u),  u <- normalize(W v),  sigma = u^T W v
+// and divides the weight by sigma. The matrix is small (d x (3d+1)), so one block of 1024 threads does all of it
+// without any cross-block synchronisation; rows and columns may be odd (scalar loads). u, v: fp32, updated in
+// place when do_iter is set. sigma_out[0] = u^T W v with the final u, v.
+template <typename T>
+__device__ __forceinline__ float sn_load(const T* w, int64_t i);
+template <>
+__device__ __forceinline__ float sn_load<float>(const float* w, int64_t i) { return w[i]; }
+template <>
+__device__ __forceinline__ float sn_load<__nv_bfloat16>(const __nv_bfloat16* w, int64_t i) { return __bfloat162float(w[i]); }
+
+__device__ __forceinline__ float block_sum_1024(float x, float* red) {
+  x = warp_sum(x);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = x;
+  __syncthreads();
+  float t = (threadIdx.x < 32) ? red[threadIdx.x] : 0.0f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+sn_power_iter_kernel(const T* __restrict__ W, float* __restrict__ u, float* __restrict__ v, float* __restrict__ t,
+                     float* __restrict__ sigma_out, int rows, int cols, int do_iter, float eps) {
+  __shared__ float red[33];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (do_iter) {
+    // v = W^T u: a thread owns columns tid, tid + 1024, ... (consecutive threads read consecutive addresses)
+    float ssq = 0.0f;
+    for (int c = tid; c < cols; c += 1024) {
+      float acc = 0.0f;
+      for (int r = 0; r < rows; ++r) acc = fmaf(sn_load(W, (int64_t)r * cols + c), u[r], acc);
+      v[c] = acc;
+      ssq = fmaf(acc, acc, ssq);
+    }
+    const float nv = sqrtf(block_sum_1024(ssq, red));
+    const float iv = 1.0f / fmaxf(nv, eps);
+    for (int c = tid; c < cols; c += 1024) v[c] *= iv;
+    __syncthreads();
+  }
+  // t = W v: one warp per row
+  float ssq_t = 0.0f, dot_ut = 0.0f;
+  for (int r = warp; r < rows; r += 32) {
+    float acc = 0.0f;
+    for (int c = lane; c < cols; c += 32) acc = fmaf(sn_load(W, (int64_t)r * cols + c), v[c], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      t[r] = acc;
+      ssq_t = fmaf(acc, acc, ssq_t);
+      dot_ut = fmaf(u[r], acc, dot_ut);
+    }
+  }
+  const float nt = sqrtf(block_sum_1024(ssq_t, red));
+  if (do_iter) {
+    const float it = 1.0f / fmaxf(nt, eps);
+    for (int r = tid; r < rows; r += 1024) u[r] = t[r] * it;
+    // sigma = u^T W v with the new u = t / |t|
+    if (tid == 0) sigma_out[0] = nt * nt * it;
+  } else {
+    const float s = block_sum_1024(dot_ut, red);
+    if (tid == 0) sigma_out[0] = s;
+  }
+}
+
+const char* launch_sn_power_iter(const void* W, int w_is_bf16, float* u, float* v, float* t, float* sigma_out, int rows,
+                                 int cols, int do_iter, float eps, cudaStream_t st) {
+  if (rows < 1 || cols < 1) return "sn_power_iter: empty matrix";
+  if (w_is_bf16)
+    sn_power_iter_kernel<__nv_bfloat16><<<1, 1024, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(W), u, v, t, sigma_out, rows,
+                                                            cols, do_iter, eps);
+  else
+    sn_power_iter_kernel<float><<<1, 1024, 0, st>>>(reinterpret_cast<const float*>(W), u, v, t, sigma_out, rows, cols, do_iter, eps);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "sn_power_iter launch failed";
+}
+
 }  // namespace gd
 
 // =======================================================================================

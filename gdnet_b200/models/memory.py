@@ -111,6 +111,11 @@ class Memory(nn.Module):
     def _sn_weight(self):
         """``W_r1.weight`` after the spectral-norm pre-forward hook, run by hand: it refreshes ``weight`` from
         ``weight_orig`` (one power iteration in training mode), as a module call would."""
+        w = self.W_r1.weight_orig
+        if w.is_cuda and w.dtype in (torch.bfloat16, torch.float32):
+            from ..ops import cuda as cu
+
+            return cu.spectral_weight(self.W_r1)     # same arithmetic, one kernel for the iteration and sigma
         for hook in self.W_r1._forward_pre_hooks.values():
             hook(self.W_r1, None)
         return self.W_r1.weight

@@ -179,31 +179,41 @@ class SharedWeights:
         self.epoch = _param_epoch
 
 
-_shared_weights: SharedWeights | None = None
+# Providers installed by training engines (each engine owns its own and removes it when it is closed, so several
+# engines can live in one process): shared FP8 weight caches and the weight streams of fully sharded engines.
+_shared_list: list = []
+_weight_streams: list = []
 
 
 def share_fp8_weights(weights, group, device) -> SharedWeights:
-    """Install the shared FP8 weight cache for ``weights`` (2-D bf16, both dims multiples of 128)."""
-    global _shared_weights
-    _shared_weights = SharedWeights(list(weights), group, device)
-    return _shared_weights
+    """Install a shared FP8 weight cache for ``weights`` (2-D bf16, both dims multiples of 128)."""
+    sw = SharedWeights(list(weights), group, device)
+    _shared_list.append(sw)
+    return sw
 
 
-def refresh_shared_weights() -> None:
-    """Collective: bring the shared FP8 weight cache up to date now. The training engine calls this right after
-    every optimizer update, where all ranks are in lockstep, so that a later forward on one rank only (an
-    evaluation on rank 0) never reaches the collective refresh by itself."""
-    if _shared_weights is not None and _shared_weights.epoch != _param_epoch:
-        _shared_weights.refresh()
+def remove_provider(obj) -> None:
+    for lst in (_shared_list, _weight_streams):
+        if obj in lst:
+            lst.remove(obj)
+
+
+def refresh_shared_weights(sw=None) -> None:
+    """Collective: bring a shared FP8 weight cache (default: all installed) up to date now. The training engine
+    calls this right after every optimizer update, where all ranks are in lockstep, so that a later forward on one
+    rank only (an evaluation on rank 0) never reaches the collective refresh by itself."""
+    for s_ in ([sw] if sw is not None else list(_shared_list)):
+        if s_.epoch != _param_epoch:
+            s_.refresh()
 
 
 def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
     key = (w.data_ptr(), w.numel(), w.dtype)
-    if _shared_weights is not None:
-        ent = _shared_weights.entries.get(key)
+    for sw in _shared_list:
+        ent = sw.entries.get(key)
         if ent is not None:
-            if _shared_weights.epoch != _param_epoch:
-                _shared_weights.refresh()
+            if sw.epoch != _param_epoch:
+                sw.refresh()
             return ent
     hit = _wq_cache.get(key)
     stamp = (w._version, _param_epoch)
@@ -228,9 +238,7 @@ def quantize_weight(w: torch.Tensor) -> QuantizedWeight:
 
 
 def clear_caches() -> None:
-    global _shared_weights, _weight_stream
-    _shared_weights = None
-    _weight_stream = None
+    """Drop every derived copy (they are rebuilt on demand). Providers installed by engines stay."""
     _f32_cache.clear()
     _wq_cache.clear()
     _taps_cache.clear()
@@ -261,7 +269,6 @@ class GradRef:
         return (self.rows, self.cols)
 
 
-_weight_stream = None
 _shape_dummies: dict = {}
 
 
@@ -274,16 +281,25 @@ def _shape_only(device, M, N):
     return d.expand(M, N)
 
 
-def set_weight_stream(ws) -> None:
-    """Install (or remove, with None) the provider of fully sharded layer weights
-    (:class:`gdnet_b200.parallel.weight_stream.WeightStream`)."""
-    global _weight_stream
-    _weight_stream = ws
+def add_weight_stream(ws) -> None:
+    """Install the provider of an engine's fully sharded layer weights
+    (:class:`gdnet_b200.parallel.weight_stream.WeightStream`); ``remove_provider`` takes it out again."""
+    _weight_streams.append(ws)
+
+
+def _stream_for(rW1):
+    """The weight stream that owns the layer step whose first recovery matrix is ``rW1``, or None."""
+    for ws in _weight_streams:
+        if ws.owns(rW1):
+            return ws
+    return None
 
 
 def _attach_gather() -> None:
-    if _weight_stream is not None:
-        _weight_stream.attach()
+    for ws in _weight_streams:
+        if ws.pending:
+            ws.attach()
+            return
 
 
 # --------------------------------------------------------------------------------------
@@ -463,14 +479,13 @@ def quantize_fp8_tensor(x, scale, need_col=True, out_row=None, out_col=None, ama
 # --------------------------------------------------------------------------------------
 # gradient sinks: fp32 main_grad (training engine) or autograd
 # --------------------------------------------------------------------------------------
-_spread_grads = False
-
-
 def set_spread_grads(on: bool) -> None:
-    """Tell the gradient sinks that ``main_grad`` views belong to flat buffers spread over the ranks
-    (registered with ``register_grad_sink``): every addition then goes to the owner rank's copy."""
-    global _spread_grads
-    _spread_grads = bool(on)
+    """Kept for callers of earlier versions: whether a gradient buffer is spread over the ranks is now asked per
+    tensor (``_is_spread``: it lies inside a buffer registered with ``register_grad_sink``, or it is a ``GradRef``)."""
+
+
+def _is_spread(mg) -> bool:
+    return isinstance(mg, GradRef) or (mg is not None and mg.is_cuda and bool(K.is_spread(mg)))
 
 
 def _main_grad(p):
@@ -487,8 +502,8 @@ def accumulate_main_grad(mg, g) -> None:
             for r in range(mg.rows):
                 K.peer_add_at(mg.sink, mg.off + r * mg.ld, g[r].contiguous())
         return
-    if _spread_grads:
-        K.peer_add(mg, g.contiguous())
+    if mg.is_cuda and mg.dtype == F32 and mg.is_contiguous():
+        K.peer_add(mg, g.contiguous())       # a plain local add when mg lies in no spread buffer
     else:
         mg.add_(g.view_as(mg))
 
@@ -512,8 +527,10 @@ def _sink_vecs(params, packed, views, mgs=None):
     or gradients spread over ranks) go one by one."""
     if mgs is None:
         mgs = [_main_grad(p) for p in params]
-    batch = [] if _spread_grads else [i for i, m in enumerate(mgs) if m is not None and not isinstance(m, GradRef)
-                                      and m.dtype == F32 and m.is_contiguous()]
+    batch = [i for i, m in enumerate(mgs) if m is not None and not isinstance(m, GradRef) and m.dtype == F32
+             and m.is_contiguous()]
+    if batch and _is_spread(mgs[batch[0]]):      # the small parameters of a step share one flat buffer
+        batch = []
     out = [None] * len(params)
     for i, (p, v) in enumerate(zip(params, views)):
         if i not in batch:
@@ -993,10 +1010,11 @@ class _LayerStepFn(torch.autograd.Function):
         # fully sharded weights: the operands of this step come from the weight stream (gathered from their owners
         # by the GEMMs themselves); otherwise they are derived from the local parameters and cached
         W = None
-        if _weight_stream is not None and _weight_stream.owns(rW1):
+        ws = _stream_for(rW1)
+        if ws is not None:
             if not fp8:
                 raise RuntimeError("fully sharded layer weights need the FP8 block recipe for the recovery MLP")
-            W = _weight_stream.acquire(rW1, "F")
+            W = ws.acquire(rW1, "F")
         if fp8 and W is not None:
             q1q, q1p, q2q, q2p = W.q1, W.p1, W.q2, W.p2
         elif fp8:
@@ -1098,14 +1116,15 @@ class _LayerStepFn(torch.autograd.Function):
 
         # ---- gate MLP ----
         W = None
-        if _weight_stream is not None and _weight_stream.owns(rW1):
-            W = _weight_stream.acquire(rW1, "B")       # gathered by the first GEMM below (or prefetched by the last step)
+        ws = _stream_for(rW1)
+        if ws is not None:
+            W = ws.acquire(rW1, "B")       # gathered by the first GEMM below (or prefetched by the last step)
         W2w = _folded_w2(gW2, gnw) if W is None else W.W2w
         gW1_op = gW1 if W is None else W.gW1
         gW2_raw = gW2.detach() if W is None else W.gW2
         dW2w = gemm_bf16(dq, h, a_mn=True, b_mn=True, out_dtype=F32)
         tgt2, main2 = _wgrad_target(gW2)
-        if main2 and _spread_grads:
+        if main2 and _is_spread(tgt2):
             dW2 = torch.zeros_like(dW2w)
             K.unscale_cols_bwd(dW2w, gW2_raw, f32(gnw), dW2, dgnw)
             accumulate_main_grad(tgt2, dW2)
@@ -1157,7 +1176,7 @@ class _LayerStepFn(torch.autograd.Function):
         mgs = [_main_grad(p) for p in smalls]
         if mgs[-1] is None and ctx.conv_param is not None:
             mg = _main_grad(ctx.conv_param)          # the buffer installed for THIS backward pass
-            if mg is not None and not _spread_grads:
+            if mg is not None and not _is_spread(mg):
                 mgs[-1] = mg.view(conv_w.shape)
         g_gb2, g_rnw, g_rb2, g_gnw, g_gb1, g_rb1, g_conv = _sink_vecs(
             smalls, vec, (db2g, dw_r, db2r, dgnw, db1g, db1r, dwc), mgs)
@@ -1267,6 +1286,45 @@ def rmsnorm_fwd(x2, w, eps):
     rstd = torch.empty(x2.shape[0], dtype=F32, device=x2.device)
     K.rmsnorm_fwd(x2, f32(w), y, rstd, float(eps))
     return y, rstd
+
+
+# --------------------------------------------------------------------------------------
+# hard spectral norm of one linear (torch.nn.utils.spectral_norm's arithmetic on one kernel)
+# --------------------------------------------------------------------------------------
+class _SpectralScaleFn(torch.autograd.Function):
+    """``W / sigma`` with ``sigma = u^T W v`` for fixed ``u, v``: ``dW = (dWn - <dWn, Wn> u v^T) / sigma``."""
+
+    @staticmethod
+    def forward(ctx, W, sigma, u, v):
+        Wn = (W.float() / sigma).to(W.dtype)
+        ctx.save_for_backward(Wn, sigma, u, v)
+        return Wn
+
+    @staticmethod
+    def backward(ctx, dWn):
+        Wn, sigma, u, v = ctx.saved_tensors
+        g = dWn.float()
+        inner = (g * Wn.float()).sum()
+        return ((g - inner * torch.outer(u, v)) / sigma).to(Wn.dtype), None, None, None
+
+
+def spectral_weight(mod):
+    """The weight of a module wrapped by ``torch.nn.utils.spectral_norm`` (parameters ``weight_orig``, buffers
+    ``weight_u`` / ``weight_v``), computed as torch's pre-forward hook computes it: in training mode one power
+    iteration that updates ``u`` and ``v`` in place, then ``weight_orig / (u^T W v)`` with the gradient flowing through
+    the division and through sigma. The iteration and sigma are one single-block kernel
+    (``csrc/loss_optim.cu:sn_power_iter_kernel``); reference: gdnet/memory.py:68."""
+    W = mod.weight_orig
+    u, v = mod.weight_u, mod.weight_v
+    Wm = W.detach().reshape(W.shape[0], -1).contiguous()
+    u32, v32 = u.detach().float().contiguous(), v.detach().float().contiguous()
+    sigma = torch.empty(1, dtype=F32, device=W.device)
+    K.sn_power_iter(Wm, u32, v32, sigma, bool(mod.training), 1e-12)
+    if mod.training:
+        with torch.no_grad():
+            u.copy_(u32)
+            v.copy_(v32)
+    return _SpectralScaleFn.apply(W, sigma, u32, v32)
 
 
 # --------------------------------------------------------------------------------------
@@ -1490,7 +1548,8 @@ class _SigmaFn(torch.autograd.Function):
         sig, y_flat, v_flat = ctx.saved_tensors
         coef = (dsig / sig.clamp(min=1e-12)).to(F32).contiguous()
         mgs = [_main_grad(W) for W in mats]
-        if not _spread_grads and all(m is not None and m.dtype == F32 and m.is_contiguous() for m in mgs):
+        if all(m is not None and not isinstance(m, GradRef) and m.dtype == F32 and m.is_contiguous() for m in mgs) \
+                and not _is_spread(mgs[0]):
             # rebuild the y / v pointer tables for the saved copies (same layout, different base)
             dy = y_flat.data_ptr() - plan.y_flat.data_ptr()
             dv = v_flat.data_ptr() - plan.v_flat.data_ptr()

@@ -209,10 +209,8 @@ class TrainEngine(nn.Module):
                 raise ValueError('shard="full" needs CUDA and precision="fp8"')
             self.comm = "scatter"           # gradients go to their owner from the weight-gradient epilogues
         symmetric = self.comm in ("fused", "scatter")
-        if self.comm == "scatter":
-            from ..ops import cuda as cu
-
-            cu.K.clear_grad_sinks()
+        self._sink_ids: list[int] = []
+        self._shared = None
 
         params = [p for p in model.parameters() if p.requires_grad]
         sharded_params = self._layer_matrices(model) if self.shard == "full" else []
@@ -248,10 +246,11 @@ class TrainEngine(nn.Module):
             from ..ops import cuda as cu
 
             for g in self.groups:
-                if not g.sharded:
-                    cu.K.register_grad_sink(g.g_task, g._sgt.ptr_table, g.per)
-                    cu.K.register_grad_sink(g.g_info, g._sgi.ptr_table, g.per)
-            cu.set_spread_grads(True)
+                if g.sharded:
+                    self._sink_ids += [g.sink_task, g.sink_info]
+                else:
+                    self._sink_ids.append(int(cu.K.register_grad_sink(g.g_task, g._sgt.ptr_table, g.per)))
+                    self._sink_ids.append(int(cu.K.register_grad_sink(g.g_info, g._sgi.ptr_table, g.per)))
         self.scalars = torch.zeros(2, dtype=torch.float32, device=dev)
         # comm="fused": the task gradient is complete after the first backward pass, so its reduce-scatter runs on a
         # side stream while the second pass computes the information gradient; the update kernel then pulls only the
@@ -267,7 +266,6 @@ class TrainEngine(nn.Module):
         if dev.type == "cuda":
             from ..ops import cuda as cu
 
-            cu.set_spread_grads(self.comm == "scatter")
             cu.clear_caches()     # cached copies made from the pre-flattening parameter storages
             if share_fp8_weights and symmetric and precision == "fp8":
                 # each FP8 weight is quantised by one rank per update and stored into every rank's cache by
@@ -282,7 +280,7 @@ class TrainEngine(nn.Module):
                         seen.add(w.data_ptr())
                         uniq.append(w)
                 if uniq:
-                    cu.share_fp8_weights(uniq, self.pg, dev)
+                    self._shared = cu.share_fp8_weights(uniq, self.pg, dev)
             self.weight_stream = None
             if self.shard == "full":
                 from ..parallel.weight_stream import LayerSet, WeightStream
@@ -294,7 +292,24 @@ class TrainEngine(nn.Module):
                                              getattr(layer, f"{g_}_W1").weight, getattr(layer, f"{g_}_W2").weight,
                                              getattr(layer, f"{g_}_norm").weight))
                 self.weight_stream = WeightStream(self.pg, dev, self.groups[-1], sets)
-                cu.set_weight_stream(self.weight_stream)
+                cu.add_weight_stream(self.weight_stream)
+
+    def close(self) -> None:
+        """Take this engine's registrations out of the op layer (gradient sinks spread over the ranks, the shared FP8
+        cache, the weight stream). Collective in the sense that every rank should close at the same point; the
+        engine must not step afterwards."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import cuda as cu
+
+        for sid in self._sink_ids:
+            cu.K.unregister_grad_sink(sid)
+        self._sink_ids = []
+        for obj in (self._shared, getattr(self, "weight_stream", None)):
+            if obj is not None:
+                cu.remove_provider(obj)
+        self._shared = None
+        self.weight_stream = None
 
     @staticmethod
     def _layer_matrices(model):
@@ -416,7 +431,8 @@ class TrainEngine(nn.Module):
         from ..ops import cuda as cu
 
         cu.invalidate_param_caches()
-        cu.refresh_shared_weights()     # collective, here where every rank is at the same point of the step
+        if self._shared is not None:
+            cu.refresh_shared_weights(self._shared)     # collective, here where every rank is at the same point of the step
         if getattr(self, "weight_stream", None) is not None:
             self.weight_stream.refresh()    # owners re-derive the GEMM operands of their matrices (collective)
             self.weight_stream.end_step()

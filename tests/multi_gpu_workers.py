@@ -78,7 +78,6 @@ def engine_scatter_vs_nccl(rank, world, dev):
         clip = 1.0 if step == 2 else 0.0
         losses = []
         for eng in (e_nccl, e_fused, e_sc):
-            cu.set_spread_grads(eng.comm == "scatter")
             torch.manual_seed(7 + step)
             losses.append(float(eng.projected_step(tok, tgt, grad_clip=clip)))
         assert max(losses) - min(losses) < 5e-2 * max(1.0, abs(losses[0])), losses
@@ -107,7 +106,7 @@ def engine_shared_fp8_weights(rank, world, dev):
     results = []
     for shared in (False, True):
         eng = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="fused", share_fp8_weights=shared)
-        assert (cu._shared_weights is not None) == shared
+        assert (eng._shared is not None) == shared
         if not shared:
             init = [gr.flat.float().clone() for gr in eng.groups]
         losses = []
@@ -118,14 +117,14 @@ def engine_shared_fp8_weights(rank, world, dev):
         _ext.check_status(tok)
         results.append((losses, [gr.flat.clone() for gr in eng.groups]))
         if shared:
-            assert len(cu._shared_weights.owned) < len(cu._shared_weights.entries), "this rank quantised every weight"
+            assert len(eng._shared.owned) < len(eng._shared.entries), "this rank quantised every weight"
     (l0, p0), (l1, p1) = results
     # the weight-gradient GEMMs add their split-K shares with atomics, so two runs agree to rounding noise only
     assert l0[0] == l1[0] and all(abs(a - b) < 5e-3 * abs(a) for a, b in zip(l0, l1)), (l0, l1)
     for a, b, a0 in zip(p0, p1, init):
         _gap(a, b, a0, "parameters with private and with shared caches")
     # the arena must hold exactly what a private quantisation of the current weights gives, on every rank
-    sw = cu._shared_weights
+    sw = eng._shared
     sw.refresh()
     torch.cuda.synchronize()
     for (_, _, _), qw in sw.entries.items():
@@ -192,7 +191,7 @@ def sp_matches_single(rank, world, dev):
     logits_loc = model(tok_loc, sp_group=dist.group.WORLD)[0]
     want = logits_full[:, rank * t_loc : (rank + 1) * t_loc]
     err = (logits_loc.float() - want.float()).abs().max().item()
-    assert err < 0.15 * want.float().abs().max().item() + 1e-2, f"SP logits differ: {err}"
+    assert err < 0.03 * want.float().abs().max().item() + 1e-2, f"SP logits differ: {err}"
     (logits_loc.float().pow(2).sum() / logits_full.numel()).backward()
     torch.cuda.synchronize()
     _ext.check_status(tok)
@@ -203,7 +202,7 @@ def sp_matches_single(rank, world, dev):
         dist.all_reduce(g)
         denom = g_full[n].norm().item() + 1e-6
         rel = (g - g_full[n]).norm().item() / denom
-        assert rel < 0.2, f"SP gradient of {n} differs: rel {rel}"
+        assert rel < 0.05, f"SP gradient of {n} differs: rel {rel}"
 
 
 def sp_engine_step(rank, world, dev):
@@ -243,7 +242,8 @@ def engine_full_shard_vs_replicated(rank, world, dev):
         torch.cuda.synchronize()
         _ext.check_status(tok)
         sd = {k: v.float().clone() for k, v in eng.full_state_dict().items() if v.is_floating_point()}
-        results[shard] = (losses, sd, eng.resident_bytes())
+        results[shard] = (losses, sd, eng.resident_bytes(),
+                          sum(p.numel() * 2 for p in eng.groups[-1].params) if shard == "full" else 0)
         if shard == "full":
             ws = eng.weight_stream
             assert ws is not None and ws.order, "the order of the layer sets was not learnt"
@@ -259,16 +259,17 @@ def engine_full_shard_vs_replicated(rank, world, dev):
             torch.cuda.synchronize()
             _ext.check_status(tok)
         dist.barrier()
-        cu.set_weight_stream(None)
+        eng.close()
         cu.clear_caches()
         del eng
-    (l0, p0, b0), (l1, p1, b1) = results["none"], results["full"]
+    (l0, p0, b0, _), (l1, p1, b1, layer_bytes) = results["none"], results["full"]
     assert all(abs(a - b) < 5e-3 * max(1.0, abs(a)) for a, b in zip(l0, l1)), (l0, l1)
     sd0 = {k: v.float() for k, v in base.state_dict().items() if v.is_floating_point()}
     moved = [k for k in p0 if (p0[k] - sd0[k]).norm().item() > 0]
     worst = max(_gap(p0[k], p1[k], sd0[k], f"full-shard vs replicated {k}") for k in moved if p0[k].numel() >= 1024)
-    layer_bytes = sum(v.numel() * 2 for k, v in p1.items() if k.startswith("layers.") and v.dim() == 2 and v.shape[0] >= 128)
+    # of the sharded matrices a rank keeps 1 / world (whole matrices, balanced by size)
     assert b0["params"] - b1["params"] >= layer_bytes * (world - 1) // world - 4096 * world, (b0, b1, layer_bytes)
+    assert b0["grads"] - b1["grads"] >= 4 * layer_bytes * (world - 1) // world - 4096 * world, (b0, b1, layer_bytes)
     if rank == 0:
         print(f"full-shard: losses {l1}, largest relative parameter gap {worst:.3g}, resident bytes {b1} against {b0}")
 
@@ -301,7 +302,7 @@ def engine_ckpt_roundtrip(rank, world, dev):
         want_p = {k: v.float().clone() for k, v in eng.full_state_dict().items() if v.is_floating_point()}
         want_m = [gr.m.clone() for gr in eng.groups]
         dist.barrier()
-        cu.set_weight_stream(None)
+        eng.close()
         cu.clear_caches()
         del eng
         torch.manual_seed(123)       # other initial weights: everything must come from the checkpoint
@@ -320,7 +321,7 @@ def engine_ckpt_roundtrip(rank, world, dev):
         for a, b in zip(want_m, [gr.m for gr in eng2.groups]):
             assert (a - b).abs().max().item() < 1e-3 * (a.abs().max().item() + 1e-6) + 1e-6, f"{shard}: AdamW moments differ after resume"
         dist.barrier()
-        cu.set_weight_stream(None)
+        eng2.close()
         cu.clear_caches()
         del eng2
 
