@@ -5,6 +5,10 @@
 
 * gradient reduce-scatter + projection + AdamW + parameter all-gather in one kernel
   (``fused_reduce_adamw_kernel``) against NCCL all-reduce of both gradient buffers + the local AdamW kernel;
+* the task gradient's reduce-scatter alone (the part that runs beside the second backward pass) and the update kernel
+  that is left after backward (pulls the information gradient only);
+* the parameter gather of the fully sharded engine: 32 MB pulled from a peer by gather jobs, stand-alone and carried by
+  a tensor-core GEMM;
 * halo push/flag/wait kernel against ``dist.batch_isend_irecv`` of the same message;
 * one-shot MAX all-reduce of a small vector against ``dist.all_reduce(MAX)``.
 
@@ -85,8 +89,24 @@ def main():
         dist.all_reduce(g2)
         K.projected_adamw(p_l, g1, g2, m2, v2, scalars, 0.1, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1)
 
+    t_red = torch.zeros(per, device=dev)
+    tseq = [0]
+
+    def task_reduce():            # what runs beside the second backward pass
+        tseq[0] += 1
+        K.allreduce_adamw(sgt.ptr_table, sgi.ptr_table, sp.ptr_table, flags.ptr_table, m, v, scalars, n, rank, world,
+                          tseq[0] * 8, 6, True, 0.0, 0.0, 0.9, 0.9, 1e-8, 0.0, 1, sums, True, t_red)
+
+    def fused_info_only():        # what is left after backward: pulls the information gradient only
+        seq[0] += 1
+        K.allreduce_adamw(sgt.ptr_table, sgi.ptr_table, sp.ptr_table, flags.ptr_table, m, v, scalars, n, rank, world,
+                          seq[0] * 8, 0, True, 0.1, 1e-3, 0.9, 0.999, 1e-8, 0.01, seq[0], sums, True, t_red)
+
     res = {"world": world, "params": n}
     res["fused_update_ms"] = timed(fused, args.iters)
+    res["task_reduce_side_stream_ms"] = timed(task_reduce, args.iters)
+    res["fused_update_info_only_ms"] = timed(fused_info_only, args.iters)
+    res["info_only_roofline_ms"] = max((world - 1) * per * 4, (world - 1) * per * 2) / 770e9 * 1e3
     res["nccl_allreduce_plus_adamw_ms"] = timed(nccl, args.iters)
     link = 770e9
     pulled, pushed = (world - 1) * per * 8, (world - 1) * per * 2      # bytes in / out per rank
@@ -116,6 +136,35 @@ def main():
     with torch.no_grad():
         res["halo_kernel_us"] = timed(halo_kernel, 50) * 1e3
         res["halo_nccl_sendrecv_us"] = timed(halo_nccl, 50) * 1e3
+
+    # parameter gather of the fully sharded engine: 64 KB jobs pulling from the next rank's memory into local
+    # staging, stand-alone and carried by a tensor-core GEMM (8192 x 2048 x 2048 bf16, about 45 us of math)
+    nbytes = 32 * 1024 * 1024
+    src_buf = SymmBuffer(nbytes, grp, dev)
+    src_buf.local.random_(0, 255)
+    src_buf.barrier()
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    peer = (rank + 1) % world
+    rows = [[src_buf.ptrs[peer] + o, dst.data_ptr() + o, 0, 65536 // 16] for o in range(0, nbytes, 65536)]
+    table = torch.tensor(rows, dtype=torch.int64, device=dev)
+    a_, b_ = torch.randn(8192, 2048, device=dev).bfloat16(), torch.randn(2048, 2048, device=dev).bfloat16()
+    out_ = torch.empty(8192, 2048, device=dev, dtype=torch.bfloat16)
+
+    def gemm_plain():
+        cu.gemm_bf16(a_, b_, out=out_)
+
+    def gemm_carrying():
+        K.attach_gather_jobs(table)
+        cu.gemm_bf16(a_, b_, out=out_)
+
+    t_alone = timed(lambda: K.gather_jobs(table), 20)
+    t_plain = timed(gemm_plain, 20)
+    t_carry = timed(gemm_carrying, 20)
+    res["gather_32MB_stand_alone_us"] = t_alone * 1e3
+    res["gather_stand_alone_GBs"] = nbytes / t_alone / 1e6
+    res["gemm_plain_us"] = t_plain * 1e3
+    res["gemm_carrying_32MB_gather_us"] = t_carry * 1e3
+    res["gather_inside_gemm_GBs"] = nbytes / t_carry / 1e6
 
     vec = torch.rand(512, device=dev)
     res["max_allreduce_kernel_us"] = timed(lambda: max_allreduce_(vec), 50) * 1e3

@@ -368,6 +368,9 @@ __host__ __device__ constexpr uint32_t make_instr_desc_mx(uint32_t M, uint32_t N
   return (b_sf_id << 4) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (a_sf_id << 29);
 }
 
+// Descriptor bits that make an MMA read byte ``k`` (0..3) of each row's 32-bit scale word, for both operands.
+__host__ __device__ constexpr uint32_t mx_sf_ids(uint32_t k) { return (k << 4) | (k << 29); }
+
 // The mbarrier receives one arrival once every MMA issued so far by this thread is done.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)

@@ -1043,8 +1043,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 // ---------------------------------------------------------------------------------------
 // Same pipeline as the bf16 kernel (whole-K accumulation in TMEM, two accumulator stages). Each stage
 // also carries the two 512-byte packed scale chunks of its K block; the MMA thread copies them into
-// TMEM (tcgen05.cp) in front of the four MMAs that use them. Scales must be powers of two; with 1x128
-// activation and 128x128 weight blocks the four K steps of a stage share their scale bytes.
+// TMEM (tcgen05.cp) in front of the four MMAs that use them. Scales must be powers of two. A chunk holds four
+// bytes per row, one per 32-element K step; K step k of a stage reads byte k of both operands' scale words
+// (operands with 1x128 / 128x128 blocks repeat one byte four times, the epilogue's quantised copy has 1x64 blocks).
 constexpr int MX_BN = 128;
 constexpr int MX_BK = 128;
 constexpr int MX_ACC = 2;
@@ -1193,8 +1194,8 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             tmem_cp_scales(sfb_t, desc_at(sf_hi, sf_lo0 + off + (MX_SF_BYTES >> 4)));
 #pragma unroll
             for (int k = 0; k < MX_BK / 32; ++k)
-              mma_mxfp8(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2), idesc,
-                        (k == 0) ? accumulate : 1u, sfa_t, sfb_t);
+              mma_mxfp8(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2),
+                        idesc | mx_sf_ids(k), (k == 0) ? accumulate : 1u, sfa_t, sfb_t);
             mma_commit(empty0 + 8 * s);
           }
           __syncwarp();
@@ -1438,8 +1439,8 @@ gemm_fp8_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             tmem_cp_scales_pair(sfb_t, desc_at(sf_hi, sf_lo0 + off + (MX_SF_BYTES >> 4)));
 #pragma unroll
             for (int k = 0; k < MX_BK / 32; ++k)
-              mma_mxfp8_pair(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2), idesc,
-                             (k == 0) ? accumulate : 1u, sfa_t, sfb_t);
+              mma_mxfp8_pair(d_tmem, desc_at(a_hi, a_lo0 + off + k * 2), desc_at(b_hi, b_lo0 + off + k * 2),
+                             idesc | mx_sf_ids(k), (k == 0) ? accumulate : 1u, sfa_t, sfb_t);
             mma_commit_pair(empty0 + 8 * s);
           }
           __syncwarp();

@@ -271,6 +271,16 @@ def test_gemm_fp8_mx_quantised_output():
     deq = q8.float().view(M, N // 64, 64) * s64[:, :, None]
     err = float((deq.view(M, N) - act).norm() / act.norm())
     assert err < 0.05, f"quantised copy differs from silu(out): rel err {err}"
+    # the copy as the A operand of a second GEMM: every 32-column K step must be scaled by its own byte (the two
+    # halves of a 128-column block differ here, unlike operands quantised in 1x128 blocks)
+    assert bool((s64[:, 0::2] != s64[:, 1::2]).any()), "test needs rows whose two 64-column scales differ"
+    w8, sw = ref.quantize_128x128(torch.randn(256, N, device=DEV) * 0.05, pow2=True)
+    second = cu.gemm_fp8_mx(q8, p8, w8, ref.pack_ue8m0_blocks(sw), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    _status_clean(a8)
+    wq = w8.float() * sw.repeat_interleave(128, 0).repeat_interleave(128, 1)
+    want2 = deq.view(M, N) @ wq.t()
+    _close(second, want2, 2e-3 * float(want2.abs().max()), 2e-3, "GEMM on the quantised copy")
     # without storing out
     q8b = torch.empty_like(q8)
     p8b = cu.packed_buffer(M, N, DEV)
