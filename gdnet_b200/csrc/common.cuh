@@ -282,7 +282,22 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // Every bulk store this thread has committed has finished READING its shared-memory source.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // All but the most recently committed bulk store of this thread have finished reading their shared-memory source.
-__device__ __forceinline__ void bulk_wait_read_but_last() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+
+// Per-thread asynchronous copy of 8 bytes from global to shared memory (zeros when !valid; src must still be a
+// mapped address). The data is visible to the issuing thread after cp_async_wait_but<N>().
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(smem_dst)), "l"(src), "r"(valid ? 8 : 0)
+               : "memory");
+}
+// The same for 16 bytes, not kept in L1.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(src), "r"(valid ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// all of this thread's copy groups but the N most recent ones are complete
+template <int N>
+__device__ __forceinline__ void cp_async_wait_but() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Plain (untiled) bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned,
 // size a multiple of 16 bytes.

@@ -4,6 +4,8 @@
 //
 // All of them move 16-byte vectors, keep running windows / row statistics in registers and
 // read every input exactly once from HBM.
+#include <algorithm>
+#include <cstdlib>
 #include "kernels.h"
 
 #include "common.cuh"
@@ -207,6 +209,108 @@ dwconv_fwd_sw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       for (int c = 0; c < 8; ++c) acc[c] = __bfloat162float(__float2bfloat16(acc[c]));
       quant_emit_8(qo, acc, row0 + j, ch, true);
     }
+  }
+}
+
+// The forward conv as a walk on a persistent grid (no sequence parallelism): a warp owns 256 channels (8 per lane)
+// and walks segments of `seg_rows` consecutive time steps of one sequence in strips of 8, the last KT-1 input rows
+// of a strip staying in registers for the next. The rows of the next strip are on their way (per-thread
+// asynchronous copies into a shared-memory slot of the thread's own) while the current strip is computed and
+// quantised, so a warp always has 8 row loads in flight. Channel groups sit on blockIdx.x so that the blocks
+// running at the same time cover whole rows of the same time steps.
+constexpr int FWALK_SLOTS = 8 + 3;                // 8 strip rows, 3 window rows at a segment start (KT = 4)
+constexpr int FWALK_SMEM = FWALK_SLOTS * 256 * 16;
+
+template <int KT>
+__global__ void __launch_bounds__(256, 2)
+dwconv_fwd_walk_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ halo,
+                       const float* __restrict__ wt, __nv_bfloat16* __restrict__ out, int B, int T, int d,
+                       int64_t x_ld, int64_t out_ld, const RowQuantOut qo, int seg_rows) {
+  pdl_enter();
+  constexpr int TT = 8;
+  static_assert(FWALK_SLOTS == TT + KT - 1, "slot layout");
+  extern __shared__ __align__(16) uint8_t walk_smem[];
+  uint4* buf = reinterpret_cast<uint4*>(walk_smem) + threadIdx.x;      // slot i of this thread: buf[i * 256]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ch = (blockIdx.x * 32 + lane) * 8;
+  if (ch >= d) return;                    // with a quantised output d % 128 == 0: whole 16-lane groups leave
+  const int n_segs = (int)((int64_t)B * T / seg_rows);
+  const int strips_per_seg = seg_rows / TT;
+  const int seg_step = gridDim.y * 8;
+  float tap[KT][8];
+#pragma unroll
+  for (int i = 0; i < KT; ++i) {
+    const float4 w0 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch);
+    const float4 w1 = *reinterpret_cast<const float4*>(wt + (int64_t)i * d + ch + 4);
+    tap[i][0] = w0.x; tap[i][1] = w0.y; tap[i][2] = w0.z; tap[i][3] = w0.w;
+    tap[i][4] = w1.x; tap[i][5] = w1.y; tap[i][6] = w1.z; tap[i][7] = w1.w;
+  }
+  auto prefetch = [&](int seg, int sidx) {
+    const int64_t row0 = (int64_t)seg * seg_rows;
+    const int b = (int)(row0 / T), t0 = (int)(row0 - (int64_t)b * T), ts = t0 + sidx * TT;
+    const __nv_bfloat16* x_b = x + (int64_t)b * T * x_ld + ch;
+#pragma unroll
+    for (int i = 0; i < TT; ++i) cp_async_16(buf + i * 256, x_b + (int64_t)(ts + i) * x_ld, true);
+    if (sidx == 0) {
+#pragma unroll
+      for (int i = 0; i < KT - 1; ++i) {
+        const int t = t0 - (KT - 1) + i;
+        const __nv_bfloat16* src = x_b;
+        bool valid = true;
+        if (t >= 0) src = x_b + (int64_t)t * x_ld;
+        else if (halo != nullptr) src = halo + ((int64_t)b * (KT - 1) + (t + KT - 1)) * d + ch;
+        else valid = false;
+        cp_async_16(buf + (TT + i) * 256, src, valid);
+      }
+    }
+    cp_async_commit();
+  };
+  int seg = blockIdx.y * 8 + warp, sidx = 0;
+  uint4 in[TT + KT - 1];     // in[i] = xpad[ts - (KT-1) + i], packed bf16
+  if (seg < n_segs) prefetch(seg, 0);
+  while (seg < n_segs) {
+    const int64_t row0 = (int64_t)seg * seg_rows + sidx * TT;
+    cp_async_wait_but<0>();
+    if (sidx == 0) {
+#pragma unroll
+      for (int i = 0; i < KT - 1; ++i) in[i] = buf[(TT + i) * 256];
+    } else {
+#pragma unroll
+      for (int i = 0; i < KT - 1; ++i) in[i] = in[TT + i];
+    }
+#pragma unroll
+    for (int i = 0; i < TT; ++i) in[KT - 1 + i] = buf[i * 256];
+    // the slot is free again (its rows are in registers): start the next strip's copies before computing this one
+    int nseg = seg, nsidx = sidx + 1;
+    if (nsidx == strips_per_seg) {
+      nsidx = 0;
+      nseg = seg + seg_step;
+    }
+    if (nseg < n_segs) prefetch(nseg, nsidx);
+#pragma unroll
+    for (int j = 0; j < TT; ++j) {
+      float acc[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+#pragma unroll
+      for (int i = 0; i < KT; ++i) {
+        const uint32_t w[4] = {in[j + i].x, in[j + i].y, in[j + i].z, in[j + i].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float2 f = unpack_bf16x2(w[c]);
+          acc[2 * c] = fmaf(tap[i][2 * c], f.x, acc[2 * c]);
+          acc[2 * c + 1] = fmaf(tap[i][2 * c + 1], f.y, acc[2 * c + 1]);
+        }
+      }
+      store_bf16_vec<8>(out + (row0 + j) * out_ld + ch, acc);
+      if (qo.q != nullptr) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = __bfloat162float(__float2bfloat16(acc[c]));
+        quant_emit_8(qo, acc, row0 + j, ch, true);
+      }
+    }
+    seg = nseg;
+    sidx = nsidx;
   }
 }
 
@@ -453,12 +557,195 @@ dwconv_dw_kernel(const __nv_bfloat16* __restrict__ dc, const __nv_bfloat16* __re
   }
 }
 
+// dx and dw in one walk over the rows. A warp owns 128 channels (4 per lane) and walks segments of `seg_rows`
+// consecutive time steps of one sequence in strips of 8: the last KT-1 rows of dc and of x of a strip stay in
+// registers for the next one, so within a segment every row of dc and of x is loaded exactly once (plus KT-1 rows
+// at its start) and dx is written once. The rows of the next strip are on their way (per-thread asynchronous
+// copies into a shared-memory slot of the thread's own) while the current strip is computed, so a warp always has
+// 16 row loads in flight. The grid is persistent (about two blocks per SM): a warp takes every (gridDim.y * 8)-th
+// segment and sums the tap gradients in registers over all of them; the 8 warps of a block combine in shared
+// memory and leave one atomic per (channel, tap) and block. Channel groups sit on blockIdx.x so that the blocks
+// running at the same time cover whole rows of the same time steps.
+constexpr int WALK_SLOTS = 2 * 8 + 2 * 3;      // 8 + 8 strip rows, 3 + 3 window rows at a segment start (KT = 4)
+constexpr int WALK_DEPTH = 1;                   // strips on their way per warp (2 measured slower: 59.8 against 53.1 us)
+constexpr int WALK_COPY_BYTES = WALK_DEPTH * WALK_SLOTS * 256 * 8;
+constexpr int WALK_SMEM = WALK_COPY_BYTES + 8 * 4 * (128 + 1) * 4;      // + the block's partial tap sums
+
+template <int KT>
+__global__ void __launch_bounds__(256, 2)
+dwconv_bwd_walk_kernel(const __nv_bfloat16* __restrict__ dc, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ halo, const float* __restrict__ wt,
+                       const __nv_bfloat16* __restrict__ dx_tail_add, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw, int B, int T, int d, int64_t dc_ld, int64_t x_ld, int seg_rows) {
+  pdl_enter();
+  constexpr int TT = 8, W = TT + KT - 1;
+  static_assert(WALK_SLOTS == 2 * TT + 2 * (KT - 1), "slot layout");
+  extern __shared__ __align__(16) uint8_t walk_smem[];
+  uint2* buf0 = reinterpret_cast<uint2*>(walk_smem) + threadIdx.x;     // slot i of this thread in buffer n: buf0[(n * WALK_SLOTS + i) * 256]
+  float (*part)[KT][128 + 1] = reinterpret_cast<float (*)[KT][128 + 1]>(walk_smem + WALK_COPY_BYTES);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cgroup = blockIdx.x;
+  const int ch = (cgroup * 32 + lane) * 4;
+  const int n_segs = (int)((int64_t)B * T / seg_rows);
+  const int strips_per_seg = seg_rows / TT;
+  const int seg_step = gridDim.y * 8;
+  float acc[KT][4];
+#pragma unroll
+  for (int m = 0; m < KT; ++m)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[m][c] = 0.0f;
+  if (ch < d) {
+    float tap[KT][4];      // tap[j] multiplies dc[t + j]: w[KT-1-j]
+#pragma unroll
+    for (int j = 0; j < KT; ++j) {
+      const float4 w4 = *reinterpret_cast<const float4*>(wt + (int64_t)(KT - 1 - j) * d + ch);
+      tap[j][0] = w4.x; tap[j][1] = w4.y; tap[j][2] = w4.z; tap[j][3] = w4.w;
+    }
+    // the rows of strip `sidx` of segment `seg`: dc[ts + KT-1 .. +TT), x[ts .. ts + TT), and at a segment start also
+    // dc[t0 .. t0 + KT-1) and xpad[t0 - (KT-1) .. t0)
+    auto prefetch = [&](int seg, int sidx, uint2* buf) {
+      const int64_t row0 = (int64_t)seg * seg_rows;
+      const int b = (int)(row0 / T), t0 = (int)(row0 - (int64_t)b * T), ts = t0 + sidx * TT;
+      const __nv_bfloat16* dc_b = dc + (int64_t)b * T * dc_ld + ch;
+      const __nv_bfloat16* x_b = x + (int64_t)b * T * x_ld + ch;
+#pragma unroll
+      for (int i = 0; i < TT; ++i) {
+        const int tg = ts + KT - 1 + i;
+        cp_async_8(buf + i * 256, dc_b + (int64_t)(tg < T ? tg : 0) * dc_ld, tg < T);
+        cp_async_8(buf + (TT + i) * 256, x_b + (int64_t)(ts + i) * x_ld, true);
+      }
+      if (sidx == 0) {
+#pragma unroll
+        for (int i = 0; i < KT - 1; ++i) {
+          cp_async_8(buf + (2 * TT + i) * 256, dc_b + (int64_t)(t0 + i) * dc_ld, true);     // seg_rows >= TT > KT-1
+          const int t = t0 - (KT - 1) + i;
+          const __nv_bfloat16* src = x_b;
+          bool valid = true;
+          if (t >= 0) src = x_b + (int64_t)t * x_ld;
+          else if (halo != nullptr) src = halo + ((int64_t)b * (KT - 1) + (t + KT - 1)) * d + ch;
+          else valid = false;
+          cp_async_8(buf + (2 * TT + KT - 1 + i) * 256, src, valid);
+        }
+      }
+      cp_async_commit();
+    };
+    auto advance = [&](int& seg, int& sidx) {
+      if (++sidx == strips_per_seg) {
+        sidx = 0;
+        seg += seg_step;
+      }
+    };
+    int seg = blockIdx.y * 8 + warp, sidx = 0;
+    uint2 g[W], xq[W];     // within a strip at ts: g[i] = dc[ts + i], xq[i] = xpad[ts - (KT-1) + i]
+    // WALK_DEPTH strips ahead: pseg/psidx is the next strip to ask for, `cur` the buffer of the strip to compute
+    int pseg = seg, psidx = 0, cur = 0;
+#pragma unroll
+    for (int i = 0; i < WALK_DEPTH; ++i) {
+      if (pseg < n_segs) prefetch(pseg, psidx, buf0 + i * WALK_SLOTS * 256);
+      else cp_async_commit();                       // keeps the group count uniform
+      advance(pseg, psidx);
+    }
+    while (seg < n_segs) {
+      const int64_t row0 = (int64_t)seg * seg_rows;
+      const int b = (int)(row0 / T), ts = (int)(row0 - (int64_t)b * T) + sidx * TT;
+      uint2* buf = buf0 + cur * WALK_SLOTS * 256;
+      cp_async_wait_but<WALK_DEPTH - 1>();
+      if (sidx == 0) {
+#pragma unroll
+        for (int i = 0; i < KT - 1; ++i) {
+          g[i] = buf[(2 * TT + i) * 256];
+          xq[i] = buf[(2 * TT + KT - 1 + i) * 256];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < KT - 1; ++i) {
+          g[i] = g[TT + i];
+          xq[i] = xq[TT + i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < TT; ++i) {
+        g[KT - 1 + i] = buf[i * 256];
+        xq[KT - 1 + i] = buf[(TT + i) * 256];
+      }
+      // the buffer is free again (its rows are in registers): ask for the strip after the next one before computing
+      if (pseg < n_segs) prefetch(pseg, psidx, buf);
+      else cp_async_commit();
+      advance(pseg, psidx);
+      cur = (cur + 1) % WALK_DEPTH;
+#pragma unroll
+      for (int i = 0; i < TT; ++i) {
+        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int j = 0; j < KT; ++j) {
+          const float2 lo = unpack_bf16x2(g[i + j].x), hi = unpack_bf16x2(g[i + j].y);
+          o[0] = fmaf(tap[j][0], lo.x, o[0]);
+          o[1] = fmaf(tap[j][1], lo.y, o[1]);
+          o[2] = fmaf(tap[j][2], hi.x, o[2]);
+          o[3] = fmaf(tap[j][3], hi.y, o[3]);
+        }
+        const float2 glo = unpack_bf16x2(g[i].x), ghi = unpack_bf16x2(g[i].y);
+#pragma unroll
+        for (int m = 0; m < KT; ++m) {
+          const float2 lo = unpack_bf16x2(xq[i + m].x), hi = unpack_bf16x2(xq[i + m].y);
+          acc[m][0] = fmaf(glo.x, lo.x, acc[m][0]);
+          acc[m][1] = fmaf(glo.y, lo.y, acc[m][1]);
+          acc[m][2] = fmaf(ghi.x, hi.x, acc[m][2]);
+          acc[m][3] = fmaf(ghi.y, hi.y, acc[m][3]);
+        }
+        const int t = ts + i;
+        if (dx_tail_add != nullptr && t >= T - (KT - 1)) {
+          float extra[4];
+          load_bf16_vec<4>(dx_tail_add + ((int64_t)b * (KT - 1) + (t - (T - (KT - 1)))) * d + ch, extra);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) o[c] += extra[c];
+        }
+        *reinterpret_cast<uint2*>(dx + ((int64_t)b * T + t) * d + ch) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+      }
+      advance(seg, sidx);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < KT; ++m)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) part[warp][m][lane * 4 + c] = acc[m][c];
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < KT * 128; idx += blockDim.x) {
+    const int m = idx >> 7, cc = idx & 127;
+    const int chan = cgroup * 128 + cc;
+    if (chan >= d) continue;
+    float sum = 0.0f;
+#pragma unroll
+    for (int wq = 0; wq < 8; ++wq) sum += part[wq][m][cc];
+    if (sum != 0.0f) atomicAdd(dw + (int64_t)chan * KT + m, sum);
+  }
+}
+
 template <int KMAX>
 static const char* conv_dw_launch(const ConvBwdArgs& a, cudaStream_t st) {
   const int strips = a.B * ((a.T + DW_TT - 1) / DW_TT);
   dim3 grid((strips + 7) / 8, (a.d + 127) / 128);
   launch_pdl(dwconv_dw_kernel<KMAX>, grid, dim3(256), 0, st, a.dc, a.x, a.halo, a.dw, a.B, a.T, a.d, a.k, a.dc_ld, a.x_ld);
   return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_dw launch failed";
+}
+
+// Segment length and grid of a walk kernel: `ch_per_block` channels per block, about two blocks per SM; the segment
+// length trades the KT-1 rows re-read at every segment start against an even spread of the segments over the warps.
+static void walk_plan(int64_t rows, int T, int d, int ch_per_block, int& seg, dim3& grid) {
+  const int cgroups = (d + ch_per_block - 1) / ch_per_block;
+  const int walkers_max = std::max(1, 148 * 2 / cgroups) * 8;          // warps per channel group
+  seg = 8;
+  double best = 0.0;
+  for (int cand : {64, 32, 16, 8}) {
+    if (T % cand != 0) continue;
+    const int64_t n = rows / cand;
+    const int64_t walkers = std::min<int64_t>(walkers_max, (n + 7) / 8 * 8);
+    const double balance = (double)n / (double)((n + walkers - 1) / walkers * walkers);
+    const double score = balance * cand / (cand + 3.0);
+    if (score > best) { best = score; seg = cand; }
+  }
+  const int64_t n_segs = rows / seg;
+  grid = dim3(cgroups, (unsigned)std::min<int64_t>(walkers_max / 8, (n_segs + 7) / 8));
 }
 
 const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
@@ -470,10 +757,23 @@ const char* launch_dwconv_fwd(const ConvArgs& a, cudaStream_t st) {
   if (a.sp.slots != nullptr && !(a.k == 4 && a.T % 8 == 0)) return "dwconv: the in-kernel halo exchange needs k == 4 and T % 8 == 0";
   if (a.k == 4 && a.T % 8 == 0) {
     dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
-    if (a.sp.slots != nullptr)
+    static const bool walk_off = getenv("GDNET_CONV_WALK") != nullptr && atoi(getenv("GDNET_CONV_WALK")) == 0;
+    if (a.sp.slots != nullptr) {
       dwconv_fwd_sw_kernel<4, 8, true><<<sgrid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant, a.sp);
-    else
+    } else if (!walk_off && a.x_ld % 8 == 0 && a.out_ld % 8 == 0) {
+      int seg;
+      dim3 wgrid;
+      walk_plan((int64_t)a.B * a.T, a.T, a.d, 256, seg, wgrid);
+      static bool attr = false;
+      if (!attr) {
+        cudaFuncSetAttribute(dwconv_fwd_walk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWALK_SMEM);
+        attr = true;
+      }
+      launch_pdl(dwconv_fwd_walk_kernel<4>, wgrid, dim3(256), FWALK_SMEM, st, a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld,
+                 a.out_ld, a.quant, seg);
+    } else {
       launch_pdl(dwconv_fwd_sw_kernel<4, 8, false>, sgrid, dim3(256), 0, st, a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.x_ld, a.out_ld, a.quant, a.sp);
+    }
     return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_fwd launch failed";
   }
   if (a.k == 4) dwconv_fwd_pt_kernel<4><<<grid, 256, 0, st>>>(a.x, a.halo, a.w, a.out, a.B, a.T, a.d, a.k, a.x_ld, a.out_ld, a.quant);
@@ -488,6 +788,27 @@ const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
   const int rows_per_b = a.T + (a.dhalo != nullptr ? a.k - 1 : 0);
   dim3 grid((unsigned)(((int64_t)a.B * rows_per_b + 7) / 8), (a.d + 255) / 256);
   if (a.sp.slots != nullptr && !(a.k == 4 && a.T % 8 == 0)) return "dwconv: the in-kernel halo exchange needs k == 4 and T % 8 == 0";
+  static const bool walk_off = getenv("GDNET_CONV_WALK") != nullptr && atoi(getenv("GDNET_CONV_WALK")) == 0;
+  if (!walk_off && a.k == 4 && a.T % 8 == 0 && a.sp.slots == nullptr && a.x != nullptr && a.dw != nullptr && a.dx != nullptr &&
+      a.dc_ld % 4 == 0 && a.x_ld % 4 == 0) {
+    // one walk for dx and dw on a persistent grid
+    int seg;
+    dim3 wgrid;
+    walk_plan((int64_t)a.B * a.T, a.T, a.d, 128, seg, wgrid);
+    if (const char* e = getenv("GDNET_CONV_RPW")) { const int v = atoi(e); if (v >= 8 && a.T % v == 0) seg = v; }
+    static bool attr = false;
+    if (!attr) {
+      cudaFuncSetAttribute(dwconv_bwd_walk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, WALK_SMEM);
+      attr = true;
+    }
+    launch_pdl(dwconv_bwd_walk_kernel<4>, wgrid, dim3(256), WALK_SMEM, st, a.dc, a.x, a.halo, a.w, a.dx_tail_add, a.dx, a.dw, a.B, a.T,
+               a.d, a.dc_ld, a.x_ld, seg);
+    if (a.dhalo != nullptr) {
+      dim3 hgrid((unsigned)((a.B * (a.k - 1) + 7) / 8), (a.d + 255) / 256);
+      dwconv_dhalo_kernel<<<hgrid, 256, 0, st>>>(a.dc, a.w, a.dhalo, a.B, a.T, a.d, a.k, a.dc_ld);
+    }
+    return cudaGetLastError() == cudaSuccess ? nullptr : "dwconv_bwd launch failed";
+  }
   if (a.k == 4 && a.T % 8 == 0) {
     dim3 sgrid((unsigned)(((int64_t)a.B * a.T / 8 + 7) / 8), (a.d + 255) / 256);
     if (a.sp.slots != nullptr)
@@ -835,7 +1156,12 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 }
 
 // dx = rstd * (dy*w - xh * mean(dy*w*xh)), dw += sum_rows dy * xh
-__global__ void __launch_bounds__(256)
+// One warp per row. NCH > 0: d == NCH * 256; a lane keeps its 8 * NCH elements of dy and x in registers between the
+// row dot product and the output (one read of each row) and sums its columns of dw in registers over all its rows;
+// the warps of a block combine through shared memory and add once per column. NCH == 0: any d (a multiple of 8),
+// two reads per row and shared-memory atomics for the column sums.
+template <int NCH>
+__global__ void __launch_bounds__(256, NCH <= 4 ? 2 : 1)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const float* __restrict__ w, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw, int64_t rows, int d) {
@@ -843,28 +1169,87 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
   for (int i = threadIdx.x; i < d; i += blockDim.x) colacc[i] = 0.0f;
   __syncthreads();
-  for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < rows; row += (int64_t)gridDim.x * wpb) {
-    const float rstd = rstd_in[row];
-    float dot = 0.0f;
-    for (int col = lane * 8; col < d; col += 256) {
-      float g[8], v[8];
-      ld8(dy + row * d + col, g);
-      ld8(x + row * d + col, v);
+  if constexpr (NCH > 0) {
+    float acc[NCH][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dot = fmaf(g[i] * w[col + i], v[i] * rstd, dot);
+    for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[c][i] = 0.0f;
     }
-    dot = warp_sum(dot) / (float)d;
-    for (int col = lane * 8; col < d; col += 256) {
-      float g[8], v[8], o[8];
-      ld8(dy + row * d + col, g);
-      ld8(x + row * d + col, v);
+    for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < rows; row += (int64_t)gridDim.x * wpb) {
+      const float rstd = rstd_in[row];
+      uint4 gq[NCH], vq[NCH];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float xh = v[i] * rstd;
-        o[i] = rstd * (g[i] * w[col + i] - xh * dot);
-        atomicAdd(&colacc[col + i], g[i] * xh);
+      for (int c = 0; c < NCH; ++c) {
+        gq[c] = __ldg(reinterpret_cast<const uint4*>(dy + row * d + c * 256 + lane * 8));
+        vq[c] = __ldg(reinterpret_cast<const uint4*>(x + row * d + c * 256 + lane * 8));
       }
-      st8(dx + row * d + col, o);
+      float dot = 0.0f;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gq[c]);
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vq[c]);
+        const float4 wa = __ldg(reinterpret_cast<const float4*>(w + c * 256 + lane * 8));
+        const float4 wb = __ldg(reinterpret_cast<const float4*>(w + c * 256 + lane * 8 + 4));
+        const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 g = unpack_bf16x2(gw[t]), v = unpack_bf16x2(vw[t]);
+          dot = fmaf(g.x * wv[2 * t], v.x, dot);
+          dot = fmaf(g.y * wv[2 * t + 1], v.y, dot);
+        }
+      }
+      dot *= rstd;
+      dot = warp_sum(dot) / (float)d;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gq[c]);
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vq[c]);
+        const float4 wa = __ldg(reinterpret_cast<const float4*>(w + c * 256 + lane * 8));
+        const float4 wb = __ldg(reinterpret_cast<const float4*>(w + c * 256 + lane * 8 + 4));
+        const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 g = unpack_bf16x2(gw[t]), v = unpack_bf16x2(vw[t]);
+          const float xh0 = v.x * rstd, xh1 = v.y * rstd;
+          acc[c][2 * t] = fmaf(g.x, xh0, acc[c][2 * t]);
+          acc[c][2 * t + 1] = fmaf(g.y, xh1, acc[c][2 * t + 1]);
+          ow[t] = pack_bf16x2(rstd * (g.x * wv[2 * t] - xh0 * dot), rstd * (g.y * wv[2 * t + 1] - xh1 * dot));
+        }
+        *reinterpret_cast<uint4*>(dx + row * d + c * 256 + lane * 8) = o;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&colacc[c * 256 + lane * 8 + i], acc[c][i]);
+    }
+  } else {
+    for (int64_t row = (int64_t)blockIdx.x * wpb + warp; row < rows; row += (int64_t)gridDim.x * wpb) {
+      const float rstd = rstd_in[row];
+      float dot = 0.0f;
+      for (int col = lane * 8; col < d; col += 256) {
+        float g[8], v[8];
+        ld8(dy + row * d + col, g);
+        ld8(x + row * d + col, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(g[i] * w[col + i], v[i] * rstd, dot);
+      }
+      dot = warp_sum(dot) / (float)d;
+      for (int col = lane * 8; col < d; col += 256) {
+        float g[8], v[8], o[8];
+        ld8(dy + row * d + col, g);
+        ld8(x + row * d + col, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xh = v[i] * rstd;
+          o[i] = rstd * (g[i] * w[col + i] - xh * dot);
+          atomicAdd(&colacc[col + i], g[i] * xh);
+        }
+        st8(dx + row * d + col, o);
+      }
     }
   }
   __syncthreads();
@@ -998,13 +1383,17 @@ const char* launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
                                __nv_bfloat16* dx, float* dw, int64_t rows, int d, cudaStream_t st) {
   if (d % 8 != 0 || d > 16384) return "rmsnorm_bwd: d must be a multiple of 8 and at most 16384";
   const int64_t blocks = (rows + 7) / 8;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    attr = true;
-  }
-  rmsnorm_bwd_kernel<<<(int)(blocks < 148 * 4 ? blocks : 148 * 4), 256, d * sizeof(float), st>>>(dy, x, w, rstd, dx,
-                                                                                                dw, rows, d);
+  const int grid = (int)(blocks < 148 * 4 ? blocks : 148 * 4);
+  auto go = [&](auto kern) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    kern<<<grid, 256, d * sizeof(float), st>>>(dy, x, w, rstd, dx, dw, rows, d);
+  };
+  const bool vec = (reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx)) % 16 == 0;
+  if (vec && d == 1024) go(rmsnorm_bwd_kernel<4>);
+  else if (vec && d == 2048) go(rmsnorm_bwd_kernel<8>);
+  else if (vec && d == 512) go(rmsnorm_bwd_kernel<2>);
+  else if (vec && d == 256) go(rmsnorm_bwd_kernel<1>);
+  else go(rmsnorm_bwd_kernel<0>);
   return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm_bwd launch failed";
 }
 
@@ -1253,9 +1642,59 @@ quant_tensor_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   }
 }
 
+// The same for whole 64 x 64 tiles and 16-byte aligned rows: a thread converts 16 consecutive elements (two 16-byte
+// loads, one 16-byte store) and the transposed copy leaves shared memory in 16-byte pieces.
+__global__ void __launch_bounds__(256)
+quant_tensor_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale, uint8_t* __restrict__ q_row,
+                        uint8_t* __restrict__ q_col, float* __restrict__ amax_out, int64_t rows, int cols) {
+  __shared__ __align__(16) uint8_t s_t[64][64 + 16];
+  __shared__ float s_max[8];
+  const int64_t r0 = (int64_t)blockIdx.y * 64;
+  const int c0 = blockIdx.x * 64;
+  const float sc = scale[0];
+  const int rr = threadIdx.x >> 2, cc = (threadIdx.x & 3) * 16;
+  const __nv_bfloat16* src = x + (r0 + rr) * cols + c0 + cc;
+  float va[8], vb[8], v[16];
+  ld8(src, va);
+  ld8(src + 8, vb);
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float t = i < 8 ? va[i] : vb[i - 8];
+    amax = fmaxf(amax, fabsf(t));
+    v[i] = fminf(fmaxf(t * sc, -448.0f), 448.0f);
+  }
+  uint4 q;
+  q.x = pack4_e4m3(v[0], v[1], v[2], v[3]);
+  q.y = pack4_e4m3(v[4], v[5], v[6], v[7]);
+  q.z = pack4_e4m3(v[8], v[9], v[10], v[11]);
+  q.w = pack4_e4m3(v[12], v[13], v[14], v[15]);
+  *reinterpret_cast<uint4*>(q_row + (r0 + rr) * cols + c0 + cc) = q;
+  if (q_col != nullptr) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s_t[cc + i][rr] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0 && amax_out != nullptr) {
+    float m = 0.0f;
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, s_max[i]);
+    atomicMax(reinterpret_cast<int*>(amax_out), __float_as_int(m));  // valid for non-negative floats
+  }
+  if (q_col != nullptr)   // here rr indexes the source column and cc the first of 16 source rows
+    *reinterpret_cast<uint4*>(q_col + (int64_t)(c0 + rr) * rows + r0 + cc) = *reinterpret_cast<const uint4*>(&s_t[rr][cc]);
+}
+
 const char* launch_quant_tensor(const __nv_bfloat16* x, const float* scale, uint8_t* q_row, uint8_t* q_col,
                                 float* amax_out, int64_t rows, int cols, cudaStream_t st) {
   dim3 grid((cols + 63) / 64, (unsigned)((rows + 63) / 64));
+  const uintptr_t align = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q_row) | reinterpret_cast<uintptr_t>(q_col);
+  if (rows % 64 == 0 && cols % 64 == 0 && align % 16 == 0 && q_row != nullptr) {
+    quant_tensor_vec_kernel<<<grid, 256, 0, st>>>(x, scale, q_row, q_col, amax_out, rows, cols);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "quant_tensor launch failed";
+  }
   quant_tensor_kernel<<<grid, 256, 0, st>>>(x, scale, q_row, q_col, amax_out, rows, cols);
   return cudaGetLastError() == cudaSuccess ? nullptr : "quant_tensor launch failed";
 }

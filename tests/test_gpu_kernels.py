@@ -172,9 +172,10 @@ def test_quantize_weight_both_layouts():
     assert cu.quantize_weight(w) is qw
 
 
-def test_quantize_per_tensor():
+@pytest.mark.parametrize("rows,cols", [(70, 130), (192, 320)])    # ragged tiles; whole tiles (the 16-byte path)
+def test_quantize_per_tensor(rows, cols):
     cu = _cu()
-    x = torch.randn(70, 130, device=DEV).bfloat16()
+    x = torch.randn(rows, cols, device=DEV).bfloat16()
     scale = torch.tensor([448.0 / 4.0], device=DEV)
     q, qc, amax = cu.quantize_fp8_tensor(x, scale)
     want = (x.float() * scale).clamp(-448, 448).to(torch.float8_e4m3fn)

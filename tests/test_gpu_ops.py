@@ -28,7 +28,9 @@ def _check(got, want, tol, what):
     assert r < tol, f"{what}: relative error {r:.4g} (tol {tol}); max abs {float((got.float()-want.float()).abs().max()):.4g}"
 
 
-@pytest.mark.parametrize("B,T,d,k", [(2, 64, 128, 4), (2, 300, 256, 7), (1, 129, 64, 9), (3, 40, 32, 1), (1, 5, 8, 4)])
+# the last two shapes make the fused dx + dw backward walk 16 and 32 rows per warp (it picks the walk by the grid size)
+@pytest.mark.parametrize("B,T,d,k", [(2, 64, 128, 4), (2, 300, 256, 7), (1, 129, 64, 9), (3, 40, 32, 1), (1, 5, 8, 4),
+                                     (3, 200, 136, 4), (8, 4096, 1024, 4), (2, 8192, 4096, 4)])
 @pytest.mark.parametrize("use_halo", [False, True])
 def test_causal_dwconv_fwd_bwd(B, T, d, k, use_halo):
     cu = _cu()
@@ -52,10 +54,11 @@ def test_causal_dwconv_fwd_bwd(B, T, d, k, use_halo):
         _check(halo.grad, hr.grad, 1e-2, "conv dhalo")
 
 
-def test_rmsnorm_fwd_bwd():
+@pytest.mark.parametrize("rows,d", [(300, 256), (4100, 1024), (130, 384)])   # register path (d = 256 * n) and the generic one
+def test_rmsnorm_fwd_bwd(rows, d):
     cu = _cu()
-    x = torch.randn(300, 256, device=DEV, dtype=BF, requires_grad=True)
-    w = (torch.rand(256, device=DEV) + 0.5).requires_grad_()
+    x = torch.randn(rows, d, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.rand(d, device=DEV) + 0.5).requires_grad_()
     y = cu.rmsnorm(x, w, 1e-6)
     gy = torch.randn_like(y)
     y.backward(gy)
