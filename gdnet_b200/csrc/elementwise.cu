@@ -1109,10 +1109,187 @@ gate_update_bwd_kernel(const GateBwdArgs a) {
   }
 }
 
+// The same computation for d == NW * 256 (NW = 1, 2, 4, 8) with every input read once and every element evaluated
+// once. NW warps share a row, each lane owning 8 of its columns; the 8 warps of a block work on 8 / NW rows at a
+// time on a persistent grid. A lane keeps what the second pass needs of its 8 elements in registers, the NW warps
+// of a row exchange their partial row sums through shared memory (one named barrier per row), and the three column
+// sums stay in registers over all rows of the lane (its columns never change), leaving the block through shared
+// memory once at the end. The next rows' inputs are on their way (per-thread asynchronous copies) while the
+// current ones are computed.
+template <int NW>
+__global__ void __launch_bounds__(256, 2)
+gate_update_bwd_rows_kernel(const GateBwdArgs a) {
+  pdl_enter();
+  constexpr int RPI = 8 / NW;                          // rows per block iteration
+  extern __shared__ __align__(16) uint8_t gate_smem[];
+  uint4* buf = reinterpret_cast<uint4*>(gate_smem) + threadIdx.x;               // slot i of this thread: buf[i * 256]
+  float* gate_acc = reinterpret_cast<float*>(gate_smem + 6 * 256 * 16);         // [3][d]: db2g, dw_r, db2r
+  float* part = gate_acc + 3 * a.d;                                             // [2][8 warps][2]
+  for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) gate_acc[i] = 0.0f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rslot = warp / NW, wchunk = warp % NW;
+  const int col = wchunk * 256 + lane * 8;
+  const float dgm = (a.dgate_mean != nullptr) ? a.dgate_mean[0] / ((float)a.rows * (float)a.d) : 0.0f;
+  float wr[8];
+  {
+    const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
+    wr[0] = w0.x; wr[1] = w0.y; wr[2] = w0.z; wr[3] = w0.w; wr[4] = w1.x; wr[5] = w1.y; wr[6] = w1.z; wr[7] = w1.w;
+  }
+  float cs[3][8];
+#pragma unroll
+  for (int k = 0; k < 3; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cs[k][i] = 0.0f;
+  const int64_t n_groups = (a.rows + RPI - 1) / RPI;
+  auto prefetch = [&](int64_t grp) {
+    const int64_t row = grp * RPI + rslot;
+    const bool ok = row < a.rows;
+    const int64_t r = ok ? row : 0;
+    cp_async_16(buf + 0 * 256, a.dF + r * a.dF_ld + col, ok);
+    cp_async_16(buf + 1 * 256, a.dS + r * a.dS_ld + col, ok);
+    cp_async_16(buf + 2 * 256, a.z + r * a.d + col, ok);
+    cp_async_16(buf + 3 * 256, a.s + r * a.s_ld + col, ok);
+    cp_async_16(buf + 4 * 256, a.g_pre + r * a.d + col, ok);
+    cp_async_16(buf + 5 * 256, a.c + r * a.c_ld + col, ok);
+    cp_async_commit();
+  };
+  int64_t grp = blockIdx.x;
+  int par = 0;
+  if (grp < n_groups) prefetch(grp);
+  for (; grp < n_groups; grp += gridDim.x, par ^= 1) {
+    const int64_t row = grp * RPI + rslot;
+    const bool live = row < a.rows;                    // warp-uniform
+    cp_async_wait_but<0>();
+    uint4 q[6];
+#pragma unroll
+    for (int i = 0; i < 6; ++i) q[i] = buf[i * 256];
+    if (grp + gridDim.x < n_groups) prefetch(grp + gridDim.x);
+    const float rstd = live ? a.rstd_z[row] : 0.0f;
+    float ssum = 0.0f;
+    if (live && lane < a.ssq_parts) ssum = a.ssq_g[row * a.ssq_parts + lane];
+    ssum = warp_sum(ssum);
+    const float rstd_g = rsqrtf(ssum / (float)a.d + a.eps_g);
+    float dgp[8], dy[8], zh[8], gg[8], RR[8];
+    float dot_z = 0.0f, t_row = 0.0f;
+    {
+      const float4 b0 = *reinterpret_cast<const float4*>(a.b2g + col), b1 = *reinterpret_cast<const float4*>(a.b2g + col + 4);
+      const float b2[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&q[0]);
+      const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&q[1]);
+      const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&q[2]);
+      const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&q[3]);
+      const uint32_t* w4 = reinterpret_cast<const uint32_t*>(&q[4]);
+      const uint32_t* w5 = reinterpret_cast<const uint32_t*>(&q[5]);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 dF = unpack_bf16x2(w0[t]), dS = unpack_bf16x2(w1[t]), zv = unpack_bf16x2(w2[t]);
+        const float2 sv = unpack_bf16x2(w3[t]), gp = unpack_bf16x2(w4[t]), cv = unpack_bf16x2(w5[t]);
+        const GateElem e0 = gate_elem(dF.x, dS.x, zv.x, sv.x, gp.x, cv.x, wr[2 * t], rstd, dgm);
+        const GateElem e1 = gate_elem(dF.y, dS.y, zv.y, sv.y, gp.y, cv.y, wr[2 * t + 1], rstd, dgm);
+        dgp[2 * t] = e0.dgp; dy[2 * t] = e0.dy; zh[2 * t] = e0.zh; gg[2 * t] = e0.g; RR[2 * t] = e0.R;
+        dgp[2 * t + 1] = e1.dgp; dy[2 * t + 1] = e1.dy; zh[2 * t + 1] = e1.zh; gg[2 * t + 1] = e1.g; RR[2 * t + 1] = e1.R;
+        dot_z = fmaf(e0.dy * wr[2 * t], e0.zh, dot_z);
+        dot_z = fmaf(e1.dy * wr[2 * t + 1], e1.zh, dot_z);
+        t_row = fmaf(e0.dgp, gp.x - b2[2 * t], t_row);
+        t_row = fmaf(e1.dgp, gp.y - b2[2 * t + 1], t_row);
+      }
+    }
+    dot_z = warp_sum(dot_z);
+    t_row = warp_sum(t_row);
+    if (NW > 1) {
+      float* mine = part + (par * 8 + rslot * NW) * 2;
+      if (lane == 0) {
+        mine[wchunk * 2] = dot_z;
+        mine[wchunk * 2 + 1] = t_row;
+      }
+      // barrier 1 + rslot, with the number as an immediate: a number from a register makes the block claim all 16
+      // hardware barriers and lets only one block live on an SM
+      if (rslot == 0) asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+      else if (rslot == 1) asm volatile("bar.sync 2, %0;" ::"n"(NW * 32) : "memory");
+      else if (rslot == 2) asm volatile("bar.sync 3, %0;" ::"n"(NW * 32) : "memory");
+      else asm volatile("bar.sync 4, %0;" ::"n"(NW * 32) : "memory");
+      dot_z = 0.0f;
+      t_row = 0.0f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        dot_z += mine[w * 2];
+        t_row += mine[w * 2 + 1];
+      }
+    }
+    dot_z /= (float)a.d;
+    if (!live) continue;
+    if (lane == 0 && wchunk == 0) a.rowcoef[row] = rstd_g * rstd_g / (float)a.d * t_row;
+    float dq[8], dz[8], dcd[8], dsd[8];
+    const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&q[0]);
+    const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&q[1]);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 dF = unpack_bf16x2(w0[t]), dS = unpack_bf16x2(w1[t]);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = 2 * t + h;
+        const float f = h ? dF.y : dF.x, sg = h ? dS.y : dS.x;
+        const float dzv = rstd * (dy[i] * wr[i] - zh[i] * dot_z);
+        dq[i] = dgp[i] * rstd_g;
+        dz[i] = dzv;
+        dcd[i] = fmaf(f - sg, gg[i], sg);         // dF*g + dS*(1-g)
+        dsd[i] = fmaf(f - sg, RR[i], sg);
+        cs[0][i] += dgp[i];
+        cs[1][i] = fmaf(dy[i], zh[i], cs[1][i]);
+        cs[2][i] += dzv;
+      }
+    }
+    st8(a.dq + row * a.d + col, dq);
+    st8(a.dz + row * a.d + col, dz);
+    st8(a.dsc + row * 2 * a.d + col, dsd);
+    st8(a.dsc + row * 2 * a.d + a.d + col, dcd);
+    if (a.quant_dz.q != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dz[i] = __bfloat162float(__float2bfloat16(dz[i]));
+      quant_emit_8(a.quant_dz, dz, row, col, true);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 3; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) atomicAdd(&gate_acc[k * a.d + wchunk * 256 + i * 32 + lane], cs[k][i]);   // lanes on 32 banks
+  __syncthreads();
+  for (int c = threadIdx.x; c < a.d; c += blockDim.x) {
+    const int in = c & 255;
+    const int slot = (c - in) + (in & 7) * 32 + (in >> 3);
+    atomicAdd(a.db2g + c, gate_acc[slot]);
+    atomicAdd(a.dw_r + c, gate_acc[a.d + slot]);
+    atomicAdd(a.db2r + c, gate_acc[2 * a.d + slot]);
+  }
+}
+
+template <int NW>
+static const char* gate_bwd_rows_launch(const GateBwdArgs& a, cudaStream_t st) {
+  const size_t smem = 6 * 256 * 16 + 3 * (size_t)a.d * sizeof(float) + 2 * 8 * 2 * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(gate_update_bwd_rows_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    attr = true;
+  }
+  const int64_t groups = (a.rows + 8 / NW - 1) / (8 / NW);
+  launch_pdl(gate_update_bwd_rows_kernel<NW>, dim3((unsigned)std::min<int64_t>(groups, 148 * 2)), dim3(256), smem, st, a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_update_bwd launch failed";
+}
+
 const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update_bwd: d must be a multiple of 8";
   if (!a.b2g_f32) return "gate_update_bwd: the gate bias must be fp32";
   if (a.quant_dz.q != nullptr && a.d % 128 != 0) return "gate_update_bwd: a quantised dz needs d % 128 == 0";
+  static const bool rows_off = getenv("GDNET_GATE_ROWS") != nullptr && atoi(getenv("GDNET_GATE_ROWS")) == 0;
+  const uintptr_t ptrs = reinterpret_cast<uintptr_t>(a.dF) | reinterpret_cast<uintptr_t>(a.dS) | reinterpret_cast<uintptr_t>(a.z) |
+                         reinterpret_cast<uintptr_t>(a.s) | reinterpret_cast<uintptr_t>(a.g_pre) | reinterpret_cast<uintptr_t>(a.c);
+  if (!rows_off && ptrs % 16 == 0 && (a.dF_ld | a.dS_ld | a.c_ld | a.s_ld) % 8 == 0 && a.ssq_parts <= 32) {
+    if (a.d == 256) return gate_bwd_rows_launch<1>(a, st);
+    if (a.d == 512) return gate_bwd_rows_launch<2>(a, st);
+    if (a.d == 1024) return gate_bwd_rows_launch<4>(a, st);
+    if (a.d == 2048) return gate_bwd_rows_launch<8>(a, st);
+  }
   const int dpad = (a.d + 255) / 256 * 256;
   const size_t smem = 3 * (size_t)dpad * sizeof(float);
   if (smem > 96 * 1024) return "gate_update_bwd: d too large for the column sums in shared memory";

@@ -170,7 +170,11 @@ def test_gate_update_fwd_kernel(rows, d, quant):
         assert torch.equal(qp, ref.pack_ue8m0_rows(s_ref)), "packed UE8M0 chunks of the quantised side stream"
 
 
-@pytest.mark.parametrize("rows,d,quant", [(256, 128, True), (384, 256, False)])
+# d = 256 * n runs the kernel in which n warps share a row (row counts that leave the last group of rows partly empty
+# included); other widths the one-warp-per-row form
+@pytest.mark.parametrize("rows,d,quant", [(256, 128, True), (384, 256, True), (131, 256, False), (301, 512, False),
+                                          (256, 512, True), (515, 1024, False), (384, 1024, True), (77, 2048, False),
+                                          (128, 2048, True), (64, 384, False)])
 def test_gate_update_bwd_kernel(rows, d, quant):
     """Every output of the fused backward of the stream update against autograd through the fp32 statement."""
     cu = _cu()
