@@ -986,8 +986,139 @@ gate_update_fwd_kernel(const GateFwdArgs a) {
   }
 }
 
+// Barrier number 1 + slot (slot 0..3) for `threads` threads, with the number as an immediate: a number from a register
+// makes the block claim all 16 hardware barriers and lets only one block live on an SM.
+template <int THREADS>
+__device__ __forceinline__ void row_group_barrier(int slot) {
+  if (slot == 0) asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
+  else if (slot == 1) asm volatile("bar.sync 2, %0;" ::"n"(THREADS) : "memory");
+  else if (slot == 2) asm volatile("bar.sync 3, %0;" ::"n"(THREADS) : "memory");
+  else asm volatile("bar.sync 4, %0;" ::"n"(THREADS) : "memory");
+}
+
+// The same for d == NW * 256 (NW = 1, 2, 4, 8) with every input read once: NW warps share a row, each lane owning 8
+// of its columns, the 8 warps of a block work on 8 / NW rows at a time on a persistent grid, the warps of a row
+// exchange their partial sums of squares through shared memory, and the next rows' inputs are on their way
+// (per-thread asynchronous copies) while the current ones are computed.
+template <int NW>
+__global__ void __launch_bounds__(256, 3)
+gate_update_fwd_rows_kernel(const GateFwdArgs a) {
+  pdl_enter();
+  constexpr int RPI = 8 / NW;
+  extern __shared__ __align__(16) uint8_t gate_smem[];
+  uint4* buf = reinterpret_cast<uint4*>(gate_smem) + threadIdx.x;               // slot i of this thread: buf[i * 256]
+  float* part = reinterpret_cast<float*>(gate_smem + 4 * 256 * 16);             // [2][8 warps], then [8] for the gate sum
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rslot = warp / NW, wchunk = warp % NW;
+  const int col = wchunk * 256 + lane * 8;
+  float wr[8];
+  {
+    const float4 w0 = *reinterpret_cast<const float4*>(a.w_r + col), w1 = *reinterpret_cast<const float4*>(a.w_r + col + 4);
+    wr[0] = w0.x; wr[1] = w0.y; wr[2] = w0.z; wr[3] = w0.w; wr[4] = w1.x; wr[5] = w1.y; wr[6] = w1.z; wr[7] = w1.w;
+  }
+  const int64_t n_groups = (a.rows + RPI - 1) / RPI;
+  auto prefetch = [&](int64_t grp) {
+    const int64_t row = grp * RPI + rslot;
+    const bool ok = row < a.rows;
+    const int64_t r = ok ? row : 0;
+    cp_async_16(buf + 0 * 256, a.z + r * a.d + col, ok);
+    cp_async_16(buf + 1 * 256, a.g_pre + r * a.d + col, ok);
+    cp_async_16(buf + 2 * 256, a.c + r * a.c_ld + col, ok);
+    cp_async_16(buf + 3 * 256, a.s + r * a.s_ld + col, ok);
+    cp_async_commit();
+  };
+  float gsum = 0.0f;
+  int64_t grp = blockIdx.x;
+  int par = 0;
+  if (grp < n_groups) prefetch(grp);
+  for (; grp < n_groups; grp += gridDim.x, par ^= 1) {
+    const int64_t row = grp * RPI + rslot;
+    const bool live = row < a.rows;                    // warp-uniform
+    cp_async_wait_but<0>();
+    uint4 q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = buf[i * 256];
+    if (grp + gridDim.x < n_groups) prefetch(grp + gridDim.x);
+    const uint32_t* zw = reinterpret_cast<const uint32_t*>(&q[0]);
+    const uint32_t* gw = reinterpret_cast<const uint32_t*>(&q[1]);
+    const uint32_t* cw = reinterpret_cast<const uint32_t*>(&q[2]);
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(&q[3]);
+    float ssq = 0.0f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 zv = unpack_bf16x2(zw[t]);
+      ssq = fmaf(zv.x, zv.x, ssq);
+      ssq = fmaf(zv.y, zv.y, ssq);
+    }
+    ssq = warp_sum(ssq);
+    if (NW > 1) {
+      float* mine = part + par * 8 + rslot * NW;
+      if (lane == 0) mine[wchunk] = ssq;
+      row_group_barrier<NW * 32>(rslot);
+      ssq = 0.0f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) ssq += mine[w];
+    }
+    if (!live) continue;
+    const float rstd = rsqrtf(ssq / (float)a.d + a.eps_r);
+    if (lane == 0 && wchunk == 0 && a.rstd_out != nullptr) a.rstd_out[row] = rstd;
+    float fo[8], so[8], gv[8];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 zv = unpack_bf16x2(zw[t]), gp = unpack_bf16x2(gw[t]), cv = unpack_bf16x2(cw[t]), sv = unpack_bf16x2(sw[t]);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = 2 * t + h;
+        const float zz = h ? zv.y : zv.x, gg = h ? gp.y : gp.x, cc = h ? cv.y : cv.x, ss = h ? sv.y : sv.x;
+        const float R = sigmoidf_(zz * rstd * wr[i]);
+        const float g = sigmoidf_(gg);
+        gv[i] = g;
+        gsum += g;
+        fo[i] = cc * g + ss * R;
+        so[i] = cc * (1.0f - g) + ss * (1.0f - R);
+      }
+    }
+    st8(a.fwd_out + row * a.d + col, fo);
+    st8(a.side_out + row * a.d + col, so);
+    if (a.gate_out != nullptr) st8(a.gate_out + row * a.d + col, gv);
+    if (a.quant.q != nullptr) {   // the next step's recovery GEMM reads the side stream in FP8
+#pragma unroll
+      for (int i = 0; i < 8; ++i) so[i] = __bfloat162float(__float2bfloat16(so[i]));
+      quant_emit_8(a.quant, so, row, col, true);
+    }
+  }
+  if (a.gate_sum != nullptr) {
+    gsum = warp_sum(gsum);
+    float* gpart = part + 16;
+    if (lane == 0) gpart[warp] = gsum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.0f;
+      for (int i = 0; i < 8; ++i) t += gpart[i];
+      atomicAdd(a.gate_sum, t);
+    }
+  }
+}
+
+template <int NW>
+static const char* gate_fwd_rows_launch(const GateFwdArgs& a, cudaStream_t st) {
+  const size_t smem = 4 * 256 * 16 + 24 * sizeof(float);
+  const int64_t groups = (a.rows + 8 / NW - 1) / (8 / NW);
+  launch_pdl(gate_update_fwd_rows_kernel<NW>, dim3((unsigned)std::min<int64_t>(groups, 148 * 3)), dim3(256), smem, st, a);
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_update_fwd launch failed";
+}
+
 const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_update: d must be a multiple of 8";
+  static const bool rows_off = getenv("GDNET_GATE_ROWS") != nullptr && atoi(getenv("GDNET_GATE_ROWS")) == 0;
+  const uintptr_t ptrs = reinterpret_cast<uintptr_t>(a.z) | reinterpret_cast<uintptr_t>(a.s) | reinterpret_cast<uintptr_t>(a.g_pre) |
+                         reinterpret_cast<uintptr_t>(a.c);
+  if (!rows_off && ptrs % 16 == 0 && (a.c_ld | a.s_ld) % 8 == 0) {
+    if (a.d == 256) return gate_fwd_rows_launch<1>(a, st);
+    if (a.d == 512) return gate_fwd_rows_launch<2>(a, st);
+    if (a.d == 1024) return gate_fwd_rows_launch<4>(a, st);
+    if (a.d == 2048) return gate_fwd_rows_launch<8>(a, st);
+  }
   const int64_t blocks = (a.rows + 7) / 8;
   const int grid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
   launch_pdl(gate_update_fwd_kernel, dim3(grid), dim3(256), 0, st, a);
@@ -1203,12 +1334,7 @@ gate_update_bwd_rows_kernel(const GateBwdArgs a) {
         mine[wchunk * 2] = dot_z;
         mine[wchunk * 2 + 1] = t_row;
       }
-      // barrier 1 + rslot, with the number as an immediate: a number from a register makes the block claim all 16
-      // hardware barriers and lets only one block live on an SM
-      if (rslot == 0) asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
-      else if (rslot == 1) asm volatile("bar.sync 2, %0;" ::"n"(NW * 32) : "memory");
-      else if (rslot == 2) asm volatile("bar.sync 3, %0;" ::"n"(NW * 32) : "memory");
-      else asm volatile("bar.sync 4, %0;" ::"n"(NW * 32) : "memory");
+      row_group_barrier<NW * 32>(rslot);
       dot_z = 0.0f;
       t_row = 0.0f;
 #pragma unroll

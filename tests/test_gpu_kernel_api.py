@@ -134,7 +134,10 @@ def _gate_oracle(g_pre, z, c, s, w_r, eps_r):
     return fo, so, g, rstd.squeeze(-1)
 
 
-@pytest.mark.parametrize("rows,d,quant", [(256, 128, True), (384, 256, True), (50, 64, False)])
+# d = 256 * n runs the kernel in which n warps share a row (see the backward test below)
+@pytest.mark.parametrize("rows,d,quant", [(256, 128, True), (384, 256, True), (50, 64, False), (131, 256, False),
+                                          (301, 512, False), (256, 512, True), (515, 1024, False), (384, 1024, True),
+                                          (77, 2048, False), (128, 2048, True)])
 def test_gate_update_fwd_kernel(rows, d, quant):
     cu = _cu()
     torch.manual_seed(rows)
