@@ -795,7 +795,6 @@ const char* launch_dwconv_bwd(const ConvBwdArgs& a, cudaStream_t st) {
     int seg;
     dim3 wgrid;
     walk_plan((int64_t)a.B * a.T, a.T, a.d, 128, seg, wgrid);
-    if (const char* e = getenv("GDNET_CONV_RPW")) { const int v = atoi(e); if (v >= 8 && a.T % v == 0) seg = v; }
     static bool attr = false;
     if (!attr) {
       cudaFuncSetAttribute(dwconv_bwd_walk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, WALK_SMEM);
