@@ -102,8 +102,20 @@ def main():
         K.allreduce_adamw(sgt.ptr_table, sgi.ptr_table, sp.ptr_table, flags.ptr_table, m, v, scalars, n, rank, world,
                           seq[0] * 8, 0, True, 0.1, 1e-3, 0.9, 0.999, 1e-8, 0.01, seq[0], sums, True, t_red)
 
+    mc = (sgt.multicast_ptr, sgi.multicast_ptr, sp.multicast_ptr)
+
+    def fused_multicast():        # the same kernel reading through the NVLink multicast address (in-switch sum, one-store broadcast)
+        seq[0] += 1
+        K.allreduce_adamw(sgt.ptr_table, sgi.ptr_table, sp.ptr_table, flags.ptr_table, m, v, scalars, n, rank, world,
+                          seq[0] * 8, 0, True, 0.1, 1e-3, 0.9, 0.999, 1e-8, 0.01, seq[0], sums, True, None, None, *mc)
+
     res = {"world": world, "params": n}
     res["fused_update_ms"] = timed(fused, args.iters)
+    if all(mc) and os.environ.get("GDNET_MULTIMEM", "1") != "0":
+        res["fused_update_multicast_ms"] = timed(fused_multicast, args.iters)
+        # the sum is formed in the switch, so a rank receives its reduced shard only once; but every rank still has to
+        # send the other ranks' shards of its two fp32 buffers: the outbound side sets the same bound as the peer loads
+        res["multicast_roofline_ms"] = (world - 1) * per * 8 / 770e9 * 1e3
     res["task_reduce_side_stream_ms"] = timed(task_reduce, args.iters)
     res["fused_update_info_only_ms"] = timed(fused_info_only, args.iters)
     res["info_only_roofline_ms"] = max((world - 1) * per * 4, (world - 1) * per * 2) / 770e9 * 1e3

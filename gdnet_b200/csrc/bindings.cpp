@@ -912,7 +912,7 @@ void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, con
                      const Tensor& signal_table, Tensor m, Tensor v, const Tensor& scalars, int64_t n, int64_t rank,
                      int64_t world, int64_t seq, int64_t phase, bool p_is_bf16, double beta_proj, double lr, double beta1,
                      double beta2, double eps, double weight_decay, int64_t step, Tensor shard_sums, bool gather_params,
-                     OptT t_red, OptT timing) {
+                     OptT t_red, OptT timing, int64_t mc_gt, int64_t mc_gi, int64_t mc_p) {
   c10::cuda::CUDAGuard guard(m.device());
   OpRange gd_range_(__func__);
   gd::FusedReduceAdamWArgs a{};
@@ -928,6 +928,10 @@ void allreduce_adamw(const Tensor& ptr_table_gt, const Tensor& ptr_table_gi, con
   a.gather_params = gather_params;
   a.t_red = nullptr;
   if (t_red.has_value()) a.t_red = f32_mut(*t_red, "t_red");
+  TORCH_CHECK(mc_gt % 16 == 0 && mc_gi % 16 == 0 && mc_p % 16 == 0, "multicast addresses must be 16-byte aligned");
+  a.gt_mc = reinterpret_cast<const float*>(mc_gt);
+  a.gi_mc = reinterpret_cast<const float*>(mc_gi);
+  a.p_mc = reinterpret_cast<void*>(mc_p);
   a.timing = nullptr;
   if (timing.has_value()) {
     TORCH_CHECK(timing->is_cuda() && timing->scalar_type() == at::kLong && timing->numel() >= 4 && timing->is_contiguous(),
@@ -1061,7 +1065,7 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("batched_outer_add(Tensor dsts, Tensor ys, Tensor vecs, Tensor coef, Tensor rows, Tensor cols, int max_rows) -> ()", &batched_outer_add);
   m.def("sn_power_iter(Tensor W, Tensor(a!) u, Tensor(b!) v, Tensor(c!) sigma, bool do_iter, float eps) -> ()", &sn_power_iter);
   m.def("batched_gemv(Tensor mats, Tensor vecs, Tensor outs, Tensor rows, Tensor cols, Tensor is_bf16, int max_rows) -> ()", &batched_gemv);
-  m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums, bool gather_params=True, Tensor(d!)? t_red=None, Tensor(e!)? timing=None) -> ()", &allreduce_adamw);
+  m.def("allreduce_adamw(Tensor ptr_table_gt, Tensor ptr_table_gi, Tensor ptr_table_p, Tensor signal_table, Tensor(a!) m, Tensor(b!) v, Tensor scalars, int n, int rank, int world, int seq, int phase, bool p_is_bf16, float beta_proj, float lr, float beta1, float beta2, float eps, float weight_decay, int step, Tensor(c!) shard_sums, bool gather_params=True, Tensor(d!)? t_red=None, Tensor(e!)? timing=None, int mc_gt=0, int mc_gi=0, int mc_p=0) -> ()", &allreduce_adamw);
   m.def("gemm_pair_capacity() -> int", []() -> int64_t { return gd::gemm_pair_capacity(); });
   m.def("gemm_set_mx_pair(int on) -> ()", [](int64_t on) { gd::gemm_set_mx_pair((int)on); });
   m.def("register_grad_sink(Tensor flat, Tensor ptr_table, int shard_elems) -> int", &register_grad_sink);

@@ -54,10 +54,14 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
     const int64_t stride6 = (int64_t)gridDim.x * blockDim.x * 4;
     for (int64_t i = lo + ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < hi; i += stride6) {
       float4 T = make_float4(0, 0, 0, 0);
-      for (int r = 0; r < a.world; ++r) {
-        const int peer = (a.rank + r) % a.world;
-        const float4 t = *reinterpret_cast<const float4*>(a.gt[peer] + i);
-        T.x += t.x; T.y += t.y; T.z += t.z; T.w += t.w;
+      if (a.gt_mc != nullptr) {
+        T = multimem_ld_reduce_add_f32x4(a.gt_mc + i);
+      } else {
+        for (int r = 0; r < a.world; ++r) {
+          const int peer = (a.rank + r) % a.world;
+          const float4 t = *reinterpret_cast<const float4*>(a.gt[peer] + i);
+          T.x += t.x; T.y += t.y; T.z += t.z; T.w += t.w;
+        }
       }
       T.x *= inv_world; T.y *= inv_world; T.z *= inv_world; T.w *= inv_world;
       *reinterpret_cast<float4*>(a.t_red + (i - lo)) = T;
@@ -77,12 +81,20 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
       T = make_float4(0, 0, 0, 0);
       I = make_float4(0, 0, 0, 0);
       if (a.t_red != nullptr) {        // the task gradient of this shard was reduced while backward ran
-        for (int r = 0; r < a.world; ++r) {
-          const int peer = (a.rank + r) % a.world;
-          const float4 f = *reinterpret_cast<const float4*>(a.gi[peer] + i);
-          I.x += f.x; I.y += f.y; I.z += f.z; I.w += f.w;
+        if (a.gi_mc != nullptr) {
+          I = multimem_ld_reduce_add_f32x4(a.gi_mc + i);
+        } else {
+          for (int r = 0; r < a.world; ++r) {
+            const int peer = (a.rank + r) % a.world;
+            const float4 f = *reinterpret_cast<const float4*>(a.gi[peer] + i);
+            I.x += f.x; I.y += f.y; I.z += f.z; I.w += f.w;
+          }
         }
         T = *reinterpret_cast<const float4*>(a.t_red + (i - lo));
+      } else if (a.gt_mc != nullptr && a.gi_mc != nullptr) {
+        T = multimem_ld_reduce_add_f32x4(a.gt_mc + i);
+        I = multimem_ld_reduce_add_f32x4(a.gi_mc + i);
+        T.x *= inv_world; T.y *= inv_world; T.z *= inv_world; T.w *= inv_world;
       } else {
         for (int r = 0; r < a.world; ++r) {
           const int peer = (a.rank + r) % a.world;   // start at the local copy, spread peers
@@ -138,9 +150,13 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
         const uint2 nw = make_uint2(pack_bf16x2(p01.x * decay - upd[0], p01.y * decay - upd[1]),
                                     pack_bf16x2(p23.x * decay - upd[2], p23.y * decay - upd[3]));
         const int n_dst = a.gather_params ? a.world : 1;
-        for (int r = 0; r < n_dst; ++r) {
-          const int peer = (a.rank + r) % a.world;
-          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.p[peer]) + i) = nw;
+        if (a.p_mc != nullptr && a.gather_params) {
+          multimem_st_bf16x4(reinterpret_cast<__nv_bfloat16*>(a.p_mc) + i, nw);
+        } else {
+          for (int r = 0; r < n_dst; ++r) {
+            const int peer = (a.rank + r) % a.world;
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.p[peer]) + i) = nw;
+          }
         }
       } else {
         float* pl = reinterpret_cast<float*>(a.p[a.rank]) + i;
@@ -148,9 +164,13 @@ fused_reduce_adamw_kernel(const FusedReduceAdamWArgs a) {
         const float4 nw = make_float4(old.x * decay - upd[0], old.y * decay - upd[1], old.z * decay - upd[2],
                                       old.w * decay - upd[3]);
         const int n_dst = a.gather_params ? a.world : 1;
-        for (int r = 0; r < n_dst; ++r) {
-          const int peer = (a.rank + r) % a.world;
-          *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.p[peer]) + i) = nw;
+        if (a.p_mc != nullptr && a.gather_params) {
+          multimem_st_f32x4(reinterpret_cast<float*>(a.p_mc) + i, nw);
+        } else {
+          for (int r = 0; r < n_dst; ++r) {
+            const int peer = (a.rank + r) % a.world;
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.p[peer]) + i) = nw;
+          }
         }
       }
     }

@@ -42,6 +42,9 @@ struct FusedReduceAdamWArgs {
   const float* scalars;    // [coef, grad_scale]
   float* shard_sums;       // [3] += sum GT^2, sum GT*GI, sum GI^2 over the reduced shard; [4] block counter
   float* t_red;            // shard_len floats or null: the reduced task gradient of this rank's shard (see phase 6)
+  const float* gt_mc;      // null, or the NVLink multicast address of the task-gradient buffers (every rank's buffer
+  const float* gi_mc;      // bound at the same offset): the sum over ranks is then one multimem.ld_reduce per vector,
+  void* p_mc;              // added inside the switch, and the updated shard reaches every rank by one multimem.st
   unsigned long long* timing;  // null or 4 words of %globaltimer (ns): kernel start, opening barrier passed,
                                // last block done with its elements, closing barrier passed
   int64_t n;

@@ -289,6 +289,25 @@ __device__ __forceinline__ void cp_async_8(void* smem_dst, const void* src, bool
   asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(smem_dst)), "l"(src), "r"(valid ? 8 : 0)
                : "memory");
 }
+// NVLink multicast (NVLS): one load returns the sum over all GPUs bound to the multicast address, added inside the
+// switch; one store reaches all of them. Addresses must be 16-byte (v4.f32) or 8-byte (v2.bf16x2) aligned.
+__device__ __forceinline__ float4 multimem_ld_reduce_add_f32x4(const float* mc_addr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st_f32x4(float* mc_addr, const float4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_st_bf16x4(void* mc_addr, const uint2& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.bf16x2 [%0], {%1, %2};" ::"l"(mc_addr), "r"(v.x), "r"(v.y) : "memory");
+}
+
 // The same for 16 bytes, not kept in L1.
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(src), "r"(valid ? 16 : 0)

@@ -61,6 +61,44 @@ def engine_fused_vs_nccl(rank, world, dev):
         assert torch.equal(ref, a), "ranks hold different parameters after the fused all-gather"
 
 
+def engine_multimem_vs_peer(rank, world, dev):
+    """The update kernel reading its shard through the NVLink multicast address (sum formed inside the switch, updated
+    parameters broadcast by one store) against the same kernel on plain peer loads and stores. Without a multicast
+    address on the box there is nothing to compare."""
+    import os
+
+    base = _model(dev)
+    os.environ["GDNET_MULTIMEM"] = "1"
+    e_mc = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="fused")
+    os.environ["GDNET_MULTIMEM"] = "0"
+    e_pp = TrainEngine(copy.deepcopy(base), lr=1e-2, precision="fp8", comm="fused")
+    assert not any(any(gr.mc) for gr in e_pp.groups)
+    if not all(all(gr.mc) for gr in e_mc.groups):
+        print("no multicast address for the gradient buffers on this box: nothing to compare", flush=True)
+        return
+    init = [gr.flat.float().clone() for gr in e_pp.groups]
+    g = torch.Generator(device="cpu").manual_seed(300 + rank)
+    for step in range(3):
+        tok = torch.randint(0, 1024, (2, 256), generator=g).to(dev)
+        tgt = torch.randint(0, 1024, (2, 256), generator=g).to(dev)
+        clip = 1.0 if step == 2 else 0.0          # also the two-phase (clipped) path
+        torch.manual_seed(7 + step)
+        l1 = e_mc.projected_step(tok, tgt, grad_clip=clip)
+        torch.manual_seed(7 + step)
+        l2 = e_pp.projected_step(tok, tgt, grad_clip=clip)
+        assert abs(float(l1) - float(l2)) < 5e-2 * max(1.0, abs(float(l2))), (float(l1), float(l2))
+    torch.cuda.synchronize()
+    _ext.check_status(tok)
+    for ga, gb, a0 in zip(e_mc.groups, e_pp.groups, init):
+        a, b = ga.flat.float(), gb.flat.float()
+        _gap(a, b, a0, "multicast vs peer-load parameters")
+        ref = a.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(ref, a), "ranks hold different parameters after the multicast store"
+    e_mc.close()
+    e_pp.close()
+
+
 def engine_scatter_vs_nccl(rank, world, dev):
     """Gradients reduce-scattered from the weight-gradient GEMM epilogues (NVLink atomics into the owner's
     shard) against NCCL all-reduce, both with the projection coefficient of the reduced gradients."""

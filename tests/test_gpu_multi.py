@@ -1,7 +1,7 @@
 """Multi-GPU tests (2 ranks on 2 GPUs, spawned as child processes): fused gradient collective +
 AdamW against the NCCL path, and the sequence-parallel halo exchange over symmetric memory against
 the single-GPU model. Skipped with fewer than 2 GPUs. NVLS is off in NCCL for these runs and the
-kernels use plain peer loads/stores only."""
+kernels use plain peer loads/stores only (``GDNET_MULTIMEM=0``), except in the one test of the multicast path."""
 
 import os
 import subprocess
@@ -17,7 +17,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _run(worker: str, nproc: int = 2, timeout: int = 600):
     if torch.cuda.device_count() < nproc:
         pytest.skip(f"needs {nproc} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", GDNET_MULTIMEM="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", "29533",
            os.path.join(ROOT, "tests", "multi_gpu_workers.py"), worker]
@@ -28,6 +28,11 @@ def _run(worker: str, nproc: int = 2, timeout: int = 600):
 
 def test_fused_collective_matches_nccl():
     _run("engine_fused_vs_nccl")
+
+
+def test_multicast_update_matches_peer_loads():
+    """The one test that uses ``multimem`` instructions (the worker switches them on for one of its two engines)."""
+    _run("engine_multimem_vs_peer")
 
 
 def test_epilogue_reduce_scatter_matches_nccl():
