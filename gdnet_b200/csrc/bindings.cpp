@@ -535,6 +535,41 @@ void gate_update_fwd(const Tensor& g_pre, const Tensor& z, const Tensor& c, cons
   GD_LAUNCH(gd::launch_gate_update_fwd(a, stream_of(c)));
 }
 
+void gate_only_fwd(const Tensor& g_pre, const Tensor& c, Tensor fwd_out, Tensor side_out, OptT gate_sum, OptT q, OptT qs,
+                   OptT qp) {
+  c10::cuda::CUDAGuard guard(c.device());
+  OpRange gd_range_(__func__);
+  const int64_t rows = g_pre.size(0);
+  const int d = (int)g_pre.size(1);
+  TORCH_CHECK(g_pre.dim() == 2 && c.dim() == 2 && g_pre.is_contiguous() && fwd_out.is_contiguous() && side_out.is_contiguous(),
+              "gate_only_fwd: g_pre and outputs must be contiguous (rows, d)");
+  TORCH_CHECK(c.size(0) == rows && c.size(1) == d && c.stride(1) == 1 && fwd_out.numel() == rows * d && side_out.numel() == rows * d,
+              "gate_only_fwd: shapes");
+  gd::GateOnlyFwdArgs a{bf16_ptr(g_pre, "g_pre"), bf16_ptr(c, "c"), bf16_mut(fwd_out, "fwd_out"), bf16_mut(side_out, "side_out"),
+                        gate_sum.has_value() ? f32_mut(*gate_sum, "gate_sum") : nullptr, rows, d, c.stride(0),
+                        row_quant_out(q, qs, qp, rows, d)};
+  GD_LAUNCH(gd::launch_gate_only_fwd(a, stream_of(c)));
+}
+
+void gate_only_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, const Tensor& c, const Tensor& b2g,
+                   const Tensor& ssq_g, double eps_g, OptT dgate_mean, Tensor dq, Tensor dc, Tensor rowcoef, Tensor db2g) {
+  c10::cuda::CUDAGuard guard(c.device());
+  OpRange gd_range_(__func__);
+  const int64_t rows = g_pre.size(0);
+  const int d = (int)g_pre.size(1);
+  TORCH_CHECK(g_pre.dim() == 2 && g_pre.is_contiguous() && dq.is_contiguous() && dc.is_contiguous(), "gate_only_bwd: contiguity");
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&dF, &dS, &c})
+    TORCH_CHECK(t->dim() == 2 && t->size(0) == rows && t->size(1) == d && t->stride(1) == 1, "gate_only_bwd: shapes");
+  TORCH_CHECK(dq.numel() == rows * d && dc.numel() == rows * d, "gate_only_bwd: output shapes");
+  TORCH_CHECK(ssq_g.dim() == 2 && ssq_g.size(0) == rows && ssq_g.is_contiguous(), "gate_only_bwd: ssq_g");
+  TORCH_CHECK(db2g.numel() == d && b2g.numel() == d && rowcoef.numel() == rows, "gate_only_bwd: sizes");
+  gd::GateOnlyBwdArgs a{bf16_ptr(dF, "dF"), bf16_ptr(dS, "dS"), bf16_ptr(g_pre, "g_pre"), bf16_ptr(c, "c"), f32_ptr(b2g, "b2g"),
+                        f32_ptr(ssq_g, "ssq_g"), (int)ssq_g.size(1), (float)eps_g, opt_f32(dgate_mean, "dgate_mean"),
+                        bf16_mut(dq, "dq"), bf16_mut(dc, "dc"), f32_mut(rowcoef, "rowcoef"), f32_mut(db2g, "db2g"), rows, d,
+                        dF.stride(0), dS.stride(0), c.stride(0)};
+  GD_LAUNCH(gd::launch_gate_only_bwd(a, stream_of(c)));
+}
+
 void gate_update_bwd(const Tensor& dF, const Tensor& dS, const Tensor& g_pre, const Tensor& z, const Tensor& c,
                      const Tensor& s, const Tensor& w_r, const Tensor& b2g, const Tensor& rstd_z, const Tensor& ssq_g,
                      double eps_g, OptT dgate_mean, Tensor dq, Tensor dz, Tensor dsc, Tensor rowcoef, Tensor db2g,
@@ -1044,6 +1079,8 @@ TORCH_LIBRARY(gdnet_b200, m) {
   m.def("dwconv_fwd_sp(Tensor x, Tensor w, Tensor(a!) out, Tensor(b!) halo_out, Tensor slot_ptrs, Tensor flag_ptrs, Tensor(c!) counter, int slot_offset, int flag_index, int rank, int world, int seq, int budget_ns=0, Tensor(d!)? q=None, Tensor(e!)? qs=None, Tensor(f!)? qp=None) -> ()", &dwconv_fwd_sp);
   m.def("dwconv_bwd_sp(Tensor dc, Tensor x, Tensor halo, Tensor w, Tensor(a!) dx, Tensor(b!) dw, Tensor slot_ptrs, Tensor flag_ptrs, Tensor(c!) counter, int slot_offset, int flag_index, int rank, int world, int seq, int budget_ns=0) -> ()", &dwconv_bwd_sp);
   m.def("gate_update_fwd(Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_out, Tensor(d!)? rstd_out, Tensor(e!)? gate_sum, float eps_r, Tensor(f!)? q=None, Tensor(g!)? qs=None, Tensor(h!)? qp=None) -> ()", &gate_update_fwd);
+  m.def("gate_only_fwd(Tensor g_pre, Tensor c, Tensor(a!) fwd_out, Tensor(b!) side_out, Tensor(c!)? gate_sum, Tensor(d!)? q=None, Tensor(e!)? qs=None, Tensor(f!)? qp=None) -> ()", &gate_only_fwd);
+  m.def("gate_only_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor c, Tensor b2g, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dc, Tensor(c!) rowcoef, Tensor(d!) db2g) -> ()", &gate_only_bwd);
   m.def("gate_update_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor z, Tensor c, Tensor s, Tensor w_r, Tensor b2g, Tensor rstd_z, Tensor ssq_g, float eps_g, Tensor? dgate_mean, Tensor(a!) dq, Tensor(b!) dz, Tensor(c!) dsc, Tensor(d!) rowcoef, Tensor(e!) db2g, Tensor(f!) dw_r, Tensor(g!) db2r, Tensor(h!)? q=None, Tensor(i!)? qs=None, Tensor(j!)? qp=None) -> ()", &gate_update_bwd);
   m.def("gate_mix_fwd(Tensor g_pre, Tensor c, Tensor s, Tensor R, Tensor(a!) fwd_out, Tensor(b!) side_out) -> ()", &gate_mix_fwd);
   m.def("gate_mix_bwd(Tensor dF, Tensor dS, Tensor g_pre, Tensor c, Tensor s, Tensor R, Tensor? ssq, Tensor? b2, float eps, Tensor(a!) dgp, Tensor(b!)? dq, Tensor(c!) dc, Tensor(d!) ds, Tensor(e!) dR, Tensor(f!)? rowcoef) -> ()", &gate_mix_bwd);

@@ -1431,6 +1431,207 @@ const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st) {
 }
 
 // =======================================================================================
+// stream update of a step with an all-zero side stream
+// =======================================================================================
+// One warp per row (NCH chunks of 256 columns, 8 per lane and chunk), persistent grid, the next row's inputs on
+// their way (per-thread asynchronous copies) while the current one is computed.
+template <int NCH>
+__global__ void __launch_bounds__(256, 2)
+gate_only_fwd_kernel(const GateOnlyFwdArgs a) {
+  pdl_enter();
+  extern __shared__ __align__(16) uint8_t gate_smem[];
+  uint4* buf = reinterpret_cast<uint4*>(gate_smem) + threadIdx.x;               // slot i of this thread: buf[i * 256]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t step = (int64_t)gridDim.x * 8;
+  auto prefetch = [&](int64_t row) {
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      cp_async_16(buf + (2 * ch) * 256, a.g_pre + row * a.d + ch * 256 + lane * 8, true);
+      cp_async_16(buf + (2 * ch + 1) * 256, a.c + row * a.c_ld + ch * 256 + lane * 8, true);
+    }
+    cp_async_commit();
+  };
+  float gsum = 0.0f;
+  int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row < a.rows) prefetch(row);
+  for (; row < a.rows; row += step) {
+    cp_async_wait_but<0>();
+    uint4 q[2 * NCH];
+#pragma unroll
+    for (int i = 0; i < 2 * NCH; ++i) q[i] = buf[i * 256];
+    if (row + step < a.rows) prefetch(row + step);
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int col = ch * 256 + lane * 8;
+      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&q[2 * ch]);
+      const uint32_t* cw = reinterpret_cast<const uint32_t*>(&q[2 * ch + 1]);
+      float fo[8], so[8];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 gp = unpack_bf16x2(gw[t]), cv = unpack_bf16x2(cw[t]);
+        const float g0 = sigmoidf_(gp.x), g1 = sigmoidf_(gp.y);
+        gsum += g0 + g1;
+        fo[2 * t] = cv.x * g0;
+        fo[2 * t + 1] = cv.y * g1;
+        so[2 * t] = cv.x * (1.0f - g0);
+        so[2 * t + 1] = cv.y * (1.0f - g1);
+      }
+      st8(a.fwd_out + row * a.d + col, fo);
+      st8(a.side_out + row * a.d + col, so);
+      if (a.quant.q != nullptr) {   // the next step's recovery GEMM reads the side stream in FP8
+#pragma unroll
+        for (int i = 0; i < 8; ++i) so[i] = __bfloat162float(__float2bfloat16(so[i]));
+        quant_emit_8(a.quant, so, row, col, true);
+      }
+    }
+  }
+  if (a.gate_sum != nullptr) {
+    gsum = warp_sum(gsum);
+    __shared__ float gpart[8];
+    if (lane == 0) gpart[warp] = gsum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.0f;
+      for (int i = 0; i < 8; ++i) t += gpart[i];
+      atomicAdd(a.gate_sum, t);
+    }
+  }
+}
+
+// A row is worked through in NP parts of CH chunks (CH <= 2, so that a part's inputs fit the registers); the
+// prefetch runs one part ahead.
+template <int NCH>
+__global__ void __launch_bounds__(256, 2)
+gate_only_bwd_kernel(const GateOnlyBwdArgs a) {
+  pdl_enter();
+  constexpr int CH = NCH > 2 ? 2 : NCH, NP = NCH / CH;
+  extern __shared__ __align__(16) uint8_t gate_smem[];
+  uint4* buf = reinterpret_cast<uint4*>(gate_smem) + threadIdx.x;               // slot i of this thread: buf[i * 256]
+  float* colacc = reinterpret_cast<float*>(gate_smem + 4 * CH * 256 * 16);      // [d]
+  for (int i = threadIdx.x; i < a.d; i += blockDim.x) colacc[i] = 0.0f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float dgm = (a.dgate_mean != nullptr) ? a.dgate_mean[0] / ((float)a.rows * (float)a.d) : 0.0f;
+  const int64_t step = (int64_t)gridDim.x * 8;
+  auto prefetch = [&](int64_t row, int part) {
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) {
+      const int col = (part * CH + ch) * 256 + lane * 8;
+      cp_async_16(buf + (4 * ch) * 256, a.dF + row * a.dF_ld + col, true);
+      cp_async_16(buf + (4 * ch + 1) * 256, a.dS + row * a.dS_ld + col, true);
+      cp_async_16(buf + (4 * ch + 2) * 256, a.g_pre + row * a.d + col, true);
+      cp_async_16(buf + (4 * ch + 3) * 256, a.c + row * a.c_ld + col, true);
+    }
+    cp_async_commit();
+  };
+  float cs[NCH][8];
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cs[ch][i] = 0.0f;
+  int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row < a.rows) prefetch(row, 0);
+  for (; row < a.rows; row += step) {
+    float ssum = 0.0f;
+    if (lane < a.ssq_parts) ssum = a.ssq_g[row * a.ssq_parts + lane];
+    ssum = warp_sum(ssum);
+    const float rstd_g = rsqrtf(ssum / (float)a.d + a.eps_g);
+    float t_row = 0.0f;
+#pragma unroll
+    for (int part = 0; part < NP; ++part) {
+      cp_async_wait_but<0>();
+      uint4 q[4 * CH];
+#pragma unroll
+      for (int i = 0; i < 4 * CH; ++i) q[i] = buf[i * 256];
+      if (part + 1 < NP) prefetch(row, part + 1);
+      else if (row + step < a.rows) prefetch(row + step, 0);
+#pragma unroll
+      for (int ch = 0; ch < CH; ++ch) {
+        const int col = (part * CH + ch) * 256 + lane * 8;
+        const uint32_t* fw = reinterpret_cast<const uint32_t*>(&q[4 * ch]);
+        const uint32_t* sw = reinterpret_cast<const uint32_t*>(&q[4 * ch + 1]);
+        const uint32_t* gw = reinterpret_cast<const uint32_t*>(&q[4 * ch + 2]);
+        const uint32_t* cw = reinterpret_cast<const uint32_t*>(&q[4 * ch + 3]);
+        const float4 b0 = *reinterpret_cast<const float4*>(a.b2g + col), b1 = *reinterpret_cast<const float4*>(a.b2g + col + 4);
+        const float b2[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float dq[8], dc[8];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 dF = unpack_bf16x2(fw[t]), dS = unpack_bf16x2(sw[t]), gp = unpack_bf16x2(gw[t]), cv = unpack_bf16x2(cw[t]);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int i = 2 * t + h;
+            const float f = h ? dF.y : dF.x, sg = h ? dS.y : dS.x, gpre = h ? gp.y : gp.x, cc = h ? cv.y : cv.x;
+            const float g = sigmoidf_(gpre);
+            const float D = f - sg;
+            const float dgp = (D * cc + dgm) * g * (1.0f - g);
+            t_row = fmaf(dgp, gpre - b2[i], t_row);
+            dq[i] = dgp * rstd_g;
+            dc[i] = fmaf(D, g, sg);               // dF g + dS (1 - g)
+            cs[part * CH + ch][i] += dgp;
+          }
+        }
+        st8(a.dq + row * a.d + col, dq);
+        st8(a.dc + row * a.d + col, dc);
+      }
+    }
+    t_row = warp_sum(t_row);
+    if (lane == 0) a.rowcoef[row] = rstd_g * rstd_g / (float)a.d * t_row;
+  }
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) atomicAdd(&colacc[ch * 256 + i * 32 + lane], cs[ch][i]);      // lanes on 32 banks
+  __syncthreads();
+  for (int c = threadIdx.x; c < a.d; c += blockDim.x) {
+    const int in = c & 255;
+    atomicAdd(a.db2g + c, colacc[(c - in) + (in & 7) * 32 + (in >> 3)]);
+  }
+}
+
+template <int NCH>
+static void gate_only_launch_both(const GateOnlyFwdArgs* f, const GateOnlyBwdArgs* b, cudaStream_t st) {
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(gate_only_fwd_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * NCH * 256 * 16);
+    cudaFuncSetAttribute(gate_only_bwd_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (NCH > 2 ? 2 : NCH) * 256 * 16 + NCH * 256 * 4);
+    attr = true;
+  }
+  const int64_t rows = f != nullptr ? f->rows : b->rows;
+  const unsigned grid = (unsigned)std::min<int64_t>((rows + 7) / 8, 148 * 2);
+  if (f != nullptr) launch_pdl(gate_only_fwd_kernel<NCH>, dim3(grid), dim3(256), (size_t)2 * NCH * 256 * 16, st, *f);
+  else launch_pdl(gate_only_bwd_kernel<NCH>, dim3(grid), dim3(256), (size_t)4 * (NCH > 2 ? 2 : NCH) * 256 * 16 + NCH * 256 * 4, st, *b);
+}
+
+static const char* gate_only_dispatch(int d, const GateOnlyFwdArgs* f, const GateOnlyBwdArgs* b, cudaStream_t st) {
+  switch (d / 256) {
+    case 1: gate_only_launch_both<1>(f, b, st); break;
+    case 2: gate_only_launch_both<2>(f, b, st); break;
+    case 4: gate_only_launch_both<4>(f, b, st); break;
+    case 8: gate_only_launch_both<8>(f, b, st); break;
+    default: return "gate_only: d must be 256, 512, 1024 or 2048";
+  }
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gate_only launch failed";
+}
+
+const char* launch_gate_only_fwd(const GateOnlyFwdArgs& a, cudaStream_t st) {
+  if (a.d % 256 != 0) return "gate_only: d must be 256, 512, 1024 or 2048";
+  if (a.c_ld % 8 != 0 || (reinterpret_cast<uintptr_t>(a.g_pre) | reinterpret_cast<uintptr_t>(a.c)) % 16 != 0)
+    return "gate_only: rows must be 16-byte aligned";
+  return gate_only_dispatch(a.d, &a, nullptr, st);
+}
+
+const char* launch_gate_only_bwd(const GateOnlyBwdArgs& a, cudaStream_t st) {
+  if (a.d % 256 != 0) return "gate_only: d must be 256, 512, 1024 or 2048";
+  if ((a.c_ld | a.dF_ld | a.dS_ld) % 8 != 0 ||
+      (reinterpret_cast<uintptr_t>(a.g_pre) | reinterpret_cast<uintptr_t>(a.c) | reinterpret_cast<uintptr_t>(a.dF) |
+       reinterpret_cast<uintptr_t>(a.dS)) % 16 != 0)
+    return "gate_only: rows must be 16-byte aligned";
+  if (a.ssq_parts > 32) return "gate_only: at most 32 partial sums of squares per row";
+  return gate_only_dispatch(a.d, nullptr, &a, st);
+}
+
+// =======================================================================================
 // RMSNorm forward / backward (generic rows x d, d multiple of 8)
 // =======================================================================================
 __global__ void __launch_bounds__(256)

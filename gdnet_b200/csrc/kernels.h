@@ -111,6 +111,43 @@ struct GateBwdArgs {
 };
 
 const char* launch_gate_update_fwd(const GateFwdArgs& a, cudaStream_t st);
+
+// The stream update of a step whose side stream is identically zero (the first forward step of every layer):
+// fwd' = c g, side' = c (1 - g); the recovery gate multiplies zero and is not evaluated. d = 256 n, n <= 8.
+struct GateOnlyFwdArgs {
+  const __nv_bfloat16* g_pre;  // (rows, d)
+  const __nv_bfloat16* c;      // (rows, d) pitch c_ld
+  __nv_bfloat16* fwd_out;      // (rows, d)
+  __nv_bfloat16* side_out;     // (rows, d)
+  float* gate_sum;             // scalar accumulator or null
+  int64_t rows;
+  int d;
+  int64_t c_ld;
+  RowQuantOut quant;           // optional 1x128-quantised copy of side_out
+};
+const char* launch_gate_only_fwd(const GateOnlyFwdArgs& a, cudaStream_t st);
+
+// Its backward: dg_pre = ((dF - dS) c + dgm) g (1 - g), dq = dg_pre rstd_g, dc = dS + (dF - dS) g,
+// rowcoef = rstd_g^2 / d * sum_n dg_pre (g_pre - b2g), db2g += column sums of dg_pre.
+struct GateOnlyBwdArgs {
+  const __nv_bfloat16* dF;     // (rows, d) pitch dF_ld
+  const __nv_bfloat16* dS;     // (rows, d) pitch dS_ld
+  const __nv_bfloat16* g_pre;  // (rows, d)
+  const __nv_bfloat16* c;      // (rows, d) pitch c_ld
+  const float* b2g;            // (d)
+  const float* ssq_g;          // (rows, ssq_parts)
+  int ssq_parts;
+  float eps_g;
+  const float* dgate_mean;     // scalar or null
+  __nv_bfloat16* dq;           // (rows, d)
+  __nv_bfloat16* dc;           // (rows, d)
+  float* rowcoef;              // (rows)
+  float* db2g;                 // (d) accumulated
+  int64_t rows;
+  int d;
+  int64_t dF_ld, dS_ld, c_ld;
+};
+const char* launch_gate_only_bwd(const GateOnlyBwdArgs& a, cudaStream_t st);
 const char* launch_gate_update_bwd(const GateBwdArgs& a, cudaStream_t st);
 
 // Stream update with both gates given (the stand-alone form of the reference's K4 / K5 kernels,

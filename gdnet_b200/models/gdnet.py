@@ -97,11 +97,13 @@ class GDNet(nn.Module):
         """Embedding plus all cycles. Returns ``(fwd, side, gate_vals)``."""
         B, T = tokens.shape
         fwd = self._embed(tokens)
-        side = [
-            torch.zeros(B, T, self.d, dtype=fwd.dtype, device=fwd.device,
-                        requires_grad=torch.is_grad_enabled())
-            for _ in self.layers
-        ]
+        # every layer's side stream starts at zero (reference: gdnet/model.py:142-146); ``None`` says so to the first
+        # forward step, which then leaves out the recovery gate (it only multiplies the side stream) instead of
+        # reading a tensor of zeros
+        if type(self).one_cycle is GDNet.one_cycle:
+            side: list = [None for _ in self.layers]
+        else:          # a subclass with its own cycle (the experiments add position codes to the side stream) gets tensors
+            side = [torch.zeros(B, T, self.d, dtype=fwd.dtype, device=fwd.device) for _ in self.layers]
         gate_vals: list[torch.Tensor] = []
         for cyc in range(self.n_cycles):
             fwd, side = self.one_cycle(

@@ -1184,6 +1184,135 @@ class _LayerStepFn(torch.autograd.Function):
                 None, None, None, None, None, None)
 
 
+class _LayerStepZeroSideFn(torch.autograd.Function):
+    """The layer step for a side stream that is identically zero (the first forward step of every layer: the model
+    starts its side streams at zero, reference gdnet/model.py:142-146): ``fwd' = c g``, ``side' = c (1 - g)``.
+
+    The recovery gate only ever multiplies the side stream (``fwd' = c g + s R``, gdnet/layer.py:123-145), so with
+    ``s = 0`` its value does not reach the outputs and its parameters receive exactly zero gradient from this step;
+    the two recovery GEMMs, their data- and weight-gradient GEMMs and the recovery half of the update kernels are
+    not run. Outputs and gradients are those of :class:`_LayerStepFn` fed an explicit zero tensor
+    (``tests/test_gpu_ops.py::test_zero_side_step_matches_explicit_zeros``).
+
+    Inputs: x (B,T,d) bf16; halo or None; the conv taps and the five gate parameters; ``rW1`` only names the layer
+    for the weight stream. Outputs as :class:`_LayerStepFn`."""
+
+    @staticmethod
+    def forward(ctx, x, halo, conv_w, rW1, gW1, gb1, gnw, gW2, gb2, fp8, eps_g, want_gate_sum, sp=None):
+        B, T, d = x.shape
+        M = B * T
+        dev = x.device
+        train = any(ctx.needs_input_grad)
+        ctx.set_materialize_grads(False)
+        x = x if x.is_contiguous() else x.contiguous()
+        c3 = torch.empty(B, T, d, dtype=BF16, device=dev)
+        c = c3.view(M, d)
+        if sp is not None:
+            halo = torch.empty(B, conv_w.shape[1] - 1, d, dtype=BF16, device=dev)
+            K.dwconv_fwd_sp(x, taps_t(conv_w), c3, halo, *sp.fwd_args(), 0)
+        else:
+            K.dwconv_fwd(x, halo, taps_t(conv_w), c3)
+        W = None
+        ws = _stream_for(rW1)
+        if ws is not None:
+            W = ws.acquire(rW1, "F")         # keeps the stream's request order; the gate operands come from it
+        parts = (d + 127) // 128
+        ssq = torch.empty(M, parts, dtype=F32, device=dev)
+        hg_pre = torch.empty(M, d, dtype=BF16, device=dev) if train else None
+        h = gemm_bf16(c, gW1 if W is None else W.gW1, bias=f32(gb1), act=ACT_SILU, pre_out=hg_pre, ssq_out=ssq)
+        W2w = _folded_w2(gW2, gnw) if W is None else W.W2w
+        g_pre = gemm_bf16(h, W2w, bias=f32(gb2), ssq_in=ssq, norm_dim=d, norm_eps=eps_g)
+        fwd_out = torch.empty(B, T, d, dtype=BF16, device=dev)
+        side_out = torch.empty(B, T, d, dtype=BF16, device=dev)
+        gate_sum = torch.zeros((), dtype=F32, device=dev) if want_gate_sum else None
+        if fp8:
+            kb = d // 128
+            nu8, nsu, npu = _alloc_u8(M, d, dev)      # the next step's [s ; c] operand: this kernel fills the s half
+            K.gate_only_fwd(g_pre, c, fwd_out.view(M, d), side_out.view(M, d), gate_sum, nu8[:, :d], nsu[:kb], npu[:, :kb])
+        else:
+            nu8 = nsu = npu = None
+            K.gate_only_fwd(g_pre, c, fwd_out.view(M, d), side_out.view(M, d), gate_sum)
+        if train:
+            empty = x.new_empty(0)
+            ctx.save_for_backward(x, halo if halo is not None else empty, c, hg_pre, h, ssq, g_pre, conv_w, rW1, gW1, gb1,
+                                  gnw, gW2, gb2)
+            ctx.cfg = (B, T, d, eps_g, halo is not None)
+            ctx.sp = sp
+            ctx.conv_param = getattr(conv_w, "base_param", None)
+        if nu8 is not None:
+            ctx.mark_non_differentiable(nu8, nsu, npu)
+        return fwd_out, side_out, gate_sum, nu8, nsu, npu
+
+    @staticmethod
+    def backward(ctx, dF, dS, dgsum, _du8=None, _dsu=None, _dpu=None):
+        x, halo, c, hg_pre, h, ssq, g_pre, conv_w, rW1, gW1, gb1, gnw, gW2, gb2 = ctx.saved_tensors
+        B, T, d, eps_g, has_halo = ctx.cfg
+        M = B * T
+        dev = x.device
+        halo = halo if has_halo else None
+
+        def rows(t):
+            t = t.reshape(M, d) if t.stride(-1) == 1 else t.contiguous().reshape(M, d)
+            return t if (t.stride(0) * 2) % 16 == 0 else t.contiguous()
+
+        dF2 = rows(dF) if dF is not None else torch.zeros(M, d, dtype=BF16, device=dev)
+        dS2 = rows(dS) if dS is not None else torch.zeros(M, d, dtype=BF16, device=dev)
+        dgm = None
+        if dgsum is not None:
+            dgm = (dgsum.to(F32) * float(M * d)).reshape(1)
+        dq = torch.empty(M, d, dtype=BF16, device=dev)
+        dc = torch.empty(M, d, dtype=BF16, device=dev)
+        rowcoef = torch.empty(M, dtype=F32, device=dev)
+        k_taps = conv_w.shape[1]
+        vec = torch.zeros(3 * d + d * k_taps, dtype=F32, device=dev)        # gb2, gnw, gb1, conv taps
+        db2g, dgnw, db1g = (vec[i * d : (i + 1) * d] for i in range(3))
+        dwc = vec[3 * d :].view(d, k_taps)
+        K.gate_only_bwd(dF2, dS2, g_pre, c, f32(gb2), ssq, eps_g, dgm, dq, dc, rowcoef, db2g)
+
+        W = None
+        ws = _stream_for(rW1)
+        if ws is not None:
+            W = ws.acquire(rW1, "B")
+        W2w = _folded_w2(gW2, gnw) if W is None else W.W2w
+        gW1_op = gW1 if W is None else W.gW1
+        gW2_raw = gW2.detach() if W is None else W.gW2
+        dW2w = gemm_bf16(dq, h, a_mn=True, b_mn=True, out_dtype=F32)
+        tgt2, main2 = _wgrad_target(gW2)
+        if main2 and _is_spread(tgt2):
+            dW2 = torch.zeros_like(dW2w)
+            K.unscale_cols_bwd(dW2w, gW2_raw, f32(gnw), dW2, dgnw)
+            accumulate_main_grad(tgt2, dW2)
+        else:
+            K.unscale_cols_bwd(dW2w, gW2_raw, f32(gnw), tgt2, dgnw)
+        dh_pre = gemm_bf16(dq, W2w, b_mn=True, aux=hg_pre, aux_mode=AUX_RMS_SILU_BWD, rowcoef=rowcoef)
+        K.colsum(dh_pre, db1g)
+        g_gW1 = _wgrad_bf16(dh_pre, c, gW1)
+        gemm_bf16(dh_pre, gW1_op, b_mn=True, out=dc, aux=dc, aux_mode=AUX_ADD)
+
+        dx = torch.empty(B, T, d, dtype=BF16, device=dev)
+        if ctx.sp is not None:
+            dhalo = None
+            K.dwconv_bwd_sp(dc.view(B, T, d), x, halo, taps_t(conv_w), dx, dwc, *ctx.sp.bwd_args(), 0)
+        else:
+            dhalo = torch.empty_like(halo) if halo is not None else None
+            K.dwconv_bwd(dc.view(B, T, d), x, halo, taps_t(conv_w), None, dx, dhalo, dwc)
+
+        g_gW2 = None if main2 else tgt2.to(gW2.dtype)
+        smalls = (gb2, gnw, gb1, conv_w)
+        mgs = [_main_grad(p) for p in smalls]
+        if mgs[-1] is None and ctx.conv_param is not None:
+            mg = _main_grad(ctx.conv_param)
+            if mg is not None and not _is_spread(mg):
+                mgs[-1] = mg.view(conv_w.shape)
+        g_gb2, g_gnw, g_gb1, g_conv = _sink_vecs(smalls, vec, (db2g, dgnw, db1g, dwc), mgs)
+        return (dx, dhalo, g_conv, None, g_gW1, g_gb1, g_gnw, g_gW2, g_gb2, None, None, None, None)
+
+
+def zero_side_step_ok(fwd, layer, r) -> bool:
+    """The zero-side form of the fused step covers the widths of its update kernels."""
+    return fwd.is_cuda and fwd.shape[-1] in (256, 512, 1024, 2048) and _fused_step_ok(fwd, None, layer, r)
+
+
 # --------------------------------------------------------------------------------------
 # public kernel API: gate MLP + stream update with the recovery gate given
 # --------------------------------------------------------------------------------------
@@ -1411,6 +1540,10 @@ def layer_step(fwd, side, layer, conv_name, g, r, sp_group=None, sp_slot=None, r
     w1g, w2g, ng = getattr(layer, f"{g}_W1"), getattr(layer, f"{g}_W2"), getattr(layer, f"{g}_norm")
     halo = None
     sp = None
+    zero_side = side is None
+    if zero_side and not (return_gate is not True and zero_side_step_ok(fwd, layer, r)):
+        side = torch.zeros_like(fwd)          # shapes the zero-side node does not cover: the general step on explicit zeros
+        zero_side = False
     fused = return_gate is not True and _fused_step_ok(fwd, side, layer, r)
     if sp_group is not None and k > 1:
         import torch.distributed as dist
@@ -1429,6 +1562,15 @@ def layer_step(fwd, side, layer, conv_name, g, r, sp_group=None, sp_slot=None, r
         return _composed_step(fwd, side, halo, conv, w1r, w2r, nr, w1g, w2g, ng, return_gate)
 
     fp8 = isinstance(w1r, FP8Linear) and isinstance(w2r, FP8Linear) and w1r.recipe == "block"
+    if zero_side:
+        fo, so, gsum, nu8, nsu, npu = _LayerStepZeroSideFn.apply(
+            fwd, halo, conv.taps, w1r.weight, w1g.weight, w1g.bias, ng.weight, w2g.weight, w2g.bias, fp8, ref.GATE_EPS,
+            return_gate == "mean", sp)
+        if fp8 and nu8 is not None:
+            _offer_side_q8(so, (nu8, nsu, npu))
+        if return_gate == "mean":
+            return fo, so, gsum / float(fo.numel())
+        return fo, so
     eps_r = nr.eps if nr.eps is not None else ref.default_rms_eps(BF16)
     side_q8 = _claim_side_q8(side) if fp8 and side.dtype == BF16 and side.is_contiguous() else None
     fo, so, gsum, nu8, nsu, npu = _LayerStepFn.apply(

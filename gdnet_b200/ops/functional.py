@@ -99,12 +99,15 @@ def layer_step(fwd, side, layer, conv_name: str, g: str, r: str, sp_group=None, 
     """Run one step of ``layer`` with the parameter set ``(conv_name, g, r)``.
 
     Returns ``(fwd', side')`` or ``(fwd', side', gate)`` where ``gate`` is the forward
-    gate tensor (``return_gate=True``) or its mean (``return_gate="mean"``).
+    gate tensor (``return_gate=True``) or its mean (``return_gate="mean"``). ``side=None`` stands for an
+    all-zero side stream: the CUDA path then leaves out the recovery gate, which only ever multiplies it.
     """
     conv = getattr(layer, conv_name)
     k = conv.size
     if _on_gpu(fwd):
         return _cuda().layer_step(fwd, side, layer, conv_name, g, r, sp_group, sp_slot, return_gate)
+    if side is None:          # ``None`` stands for an all-zero side stream (the first forward step of a layer)
+        side = torch.zeros_like(fwd)
 
     halo = None
     if sp_group is not None and k > 1:

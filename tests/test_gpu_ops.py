@@ -296,6 +296,48 @@ def test_layer_step_matches_reference(fp8, step):
     assert getattr(layer, _STEP_PREFIXES[other][0]).conv.weight.grad is None
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+def test_zero_side_step_matches_explicit_zeros(fp8):
+    """``side=None`` (the first forward step of a layer: its side stream is all zeros) leaves out the recovery gate,
+    which only multiplies the side stream. Outputs must be bit-equal to the general step on an explicit zero tensor,
+    the gradients equal up to the summation order of the weight-gradient GEMMs, and the recovery parameters must get
+    no gradient from either."""
+    import copy
+
+    from gdnet_b200.models.layer import _STEP_PREFIXES
+
+    B, T, d, k = 2, 128, 256, 4
+    la = _make_layer(d, k, fp8)
+    lb = copy.deepcopy(la)
+    torch.manual_seed(3)
+    x = torch.randn(B, T, d, device=DEV, dtype=BF)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    fa, sa, ga = la._step("fwd", xa, None, return_gate="mean")
+    fb, sb, gb = lb._step("fwd", xb, torch.zeros_like(x), return_gate="mean")
+    assert torch.equal(fa, fb) and torch.equal(sa, sb), "outputs differ from the step on explicit zeros"
+    assert abs(float(ga) - float(gb)) < 1e-6
+    gF, gS = torch.randn_like(fa), torch.randn_like(sa)
+    (fa.float() * gF).sum().add((sa.float() * gS).sum()).add(3.0 * ga).backward()
+    (fb.float() * gF).sum().add((sb.float() * gS).sum()).add(3.0 * gb).backward()
+    _check(xa.grad, xb.grad, 2e-3, "dx")
+    conv, g, r = _STEP_PREFIXES["fwd"]
+    for name in (f"{g}_W1", f"{g}_W2"):
+        _check(getattr(la, name).weight.grad, getattr(lb, name).weight.grad, 5e-3, f"d{name}.weight")
+        _check(getattr(la, name).bias.grad, getattr(lb, name).bias.grad, 5e-3, f"d{name}.bias")
+    _check(getattr(la, f"{g}_norm").weight.grad, getattr(lb, f"{g}_norm").weight.grad, 5e-3, "dgnorm")
+    _check(getattr(la, conv).conv.weight.grad, getattr(lb, conv).conv.weight.grad, 5e-3, "dconv_w")
+    for name in (f"{r}_W1", f"{r}_W2"):
+        for prm in (getattr(lb, name).weight, getattr(lb, name).bias):
+            assert prm.grad is None or float(prm.grad.float().abs().max()) == 0.0, f"{name}: non-zero gradient from a zero side stream"
+        for prm in (getattr(la, name).weight, getattr(la, name).bias):
+            assert prm.grad is None or float(prm.grad.float().abs().max()) == 0.0
+    # the FP8 copy of side' that the step hands to the next one must be the one the general step hands over
+    if fp8:
+        f2a, s2a = la._step("bwd", fa.detach(), sa.detach())
+        f2b, s2b = lb._step("bwd", fb.detach(), sb.detach())
+        assert torch.equal(f2a, f2b) and torch.equal(s2a, s2b)
+
+
 def test_layer_step_main_grad_accumulates():
     B, T, d, k = 1, 128, 128, 4
     layer = _make_layer(d, k, True)
