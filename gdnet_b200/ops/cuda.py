@@ -1216,6 +1216,7 @@ class _LayerStepZeroSideFn(torch.autograd.Function):
         ws = _stream_for(rW1)
         if ws is not None:
             W = ws.acquire(rW1, "F")         # keeps the stream's request order; the gate operands come from it
+            ws.settle()                      # the first GEMM here is a bf16 one: it cannot wait on arriving operands
         parts = (d + 127) // 128
         ssq = torch.empty(M, parts, dtype=F32, device=dev)
         hg_pre = torch.empty(M, d, dtype=BF16, device=dev) if train else None

@@ -37,16 +37,6 @@ def _align(n: int, a: int = 1024) -> int:
     return -(-n // a) * a
 
 
-class _Operand:
-    """One gathered tensor of a set: where it lives on the owner and how it is cut into jobs."""
-
-    __slots__ = ("name", "src_off", "src_space", "nbytes", "chunk_bytes", "shape", "dtype", "flags")
-
-    def __init__(self, name, src_space, src_off, nbytes, chunk_bytes, shape, dtype, flags):
-        self.name, self.src_space, self.src_off, self.nbytes = name, src_space, src_off, nbytes
-        self.chunk_bytes, self.shape, self.dtype, self.flags = chunk_bytes, shape, dtype, flags
-
-
 class LayerSet:
     """What one layer step reads: the two recovery matrices (FP8) and the two gate matrices (bf16)."""
 
@@ -297,6 +287,14 @@ class WeightStream:
             if self.pending_ready is not None:
                 cu.K.attach_b_ready(*self.pending_ready)
                 self.pending_ready = None
+
+    def settle(self) -> None:
+        """For a step whose first GEMM cannot wait for operands that are still arriving (it is not the block-scaled
+        FP8 GEMM): the jobs of the current set that were meant to ride on that GEMM run now, as a launch of their
+        own; jobs that prefetch the next set stay pending."""
+        if self.pending_ready is not None:
+            cu.K.gather_jobs(self.pending.pop(0))
+            self.pending_ready = None
 
     def _flush(self) -> None:
         while self.pending:
