@@ -59,6 +59,10 @@ def engine_fused_vs_nccl(rank, world, dev):
         ref = a.clone()
         dist.broadcast(ref, src=0)
         assert torch.equal(ref, a), "ranks hold different parameters after the fused all-gather"
+    # what the update kernels must leave behind: clean status, counters at zero, every peer's flags at the last sequence number
+    from gdnet_b200.runtime.checked import engine_invariants
+
+    engine_invariants(e_fused)
 
 
 def engine_multimem_vs_peer(rank, world, dev):

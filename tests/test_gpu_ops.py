@@ -338,6 +338,25 @@ def test_zero_side_step_matches_explicit_zeros(fp8):
         assert torch.equal(f2a, f2b) and torch.equal(s2a, s2b)
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+def test_fused_layer_steps_keep_their_red_zones(fp8):
+    """Every output and scratch buffer of the fused steps (general and zero-side, forward and backward) is allocated
+    with a canary-filled red zone behind it; no kernel may write there."""
+    from gdnet_b200.runtime.checked import RedZones
+
+    B, T, d, k = 2, 128, 256, 4
+    layer = _make_layer(d, k, fp8)
+    x = torch.randn(B, T, d, device=DEV, dtype=BF, requires_grad=True)
+    with RedZones(torch.device(DEV, torch.cuda.current_device())) as rz:
+        f1, s1, g1 = layer._step("fwd", x, None, return_gate="mean")
+        f2, s2 = layer._step("bwd", f1, s1)
+        (f2.float().sum() + s2.float().sum() + g1).backward()
+        torch.cuda.synchronize()
+        assert rz.check() > 20
+    _ext_status = __import__("gdnet_b200._ext", fromlist=["check_status"])
+    _ext_status.check_status(x)
+
+
 def test_layer_step_main_grad_accumulates():
     B, T, d, k = 1, 128, 128, 4
     layer = _make_layer(d, k, True)
