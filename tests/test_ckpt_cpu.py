@@ -39,8 +39,8 @@ def test_single_file_round_trip_with_extra(tmp_path):
 
 
 def test_single_file_keys_are_the_references(tmp_path):
-    """The saved model keys are the reference's parameter names (the layout SURVEY of the reference lists them;
-    spot-check the ones that differ most from a plain module tree)."""
+    """The saved model keys are the reference's parameter names (gdnet/model.py, gdnet/layer.py, gdnet/memory.py,
+    gdnet/operators.py); spot-check the ones that differ most from a plain module tree."""
     m = _model(0)
     save_ckpt(tmp_path / "a.pt", 0, m)
     keys = set(torch.load(tmp_path / "a.pt", weights_only=True)["model"])
