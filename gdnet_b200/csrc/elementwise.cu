@@ -1874,10 +1874,65 @@ const char* launch_cam_blend_bwd(const CamBlendArgs& a, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? nullptr : "cam_blend_bwd launch failed";
 }
 
+// d == NCH * 256: a lane keeps its 8 * NCH elements of the row in registers between the sum of squares and the
+// output, so the row is read once (the generic kernel reads it twice).
+template <int NCH>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                        float* __restrict__ rstd_out, int64_t rows, float eps) {
+  constexpr int d = NCH * 256;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t row = (int64_t)blockIdx.x * 8 + warp; row < rows; row += (int64_t)gridDim.x * 8) {
+    uint4 q[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) q[c] = __ldg(reinterpret_cast<const uint4*>(x + row * d + c * 256 + lane * 8));
+    float ssq = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(&q[c]);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 v = unpack_bf16x2(xw[t]);
+        ssq = fmaf(v.x, v.x, ssq);
+        ssq = fmaf(v.y, v.y, ssq);
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(ssq) / (float)d + eps);
+    if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(&q[c]);
+      const float4 wa = __ldg(reinterpret_cast<const float4*>(w + c * 256 + lane * 8));
+      const float4 wb = __ldg(reinterpret_cast<const float4*>(w + c * 256 + lane * 8 + 4));
+      const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 v = unpack_bf16x2(xw[t]);
+        ow[t] = pack_bf16x2(v.x * rstd * wv[2 * t], v.y * rstd * wv[2 * t + 1]);
+      }
+      *reinterpret_cast<uint4*>(y + row * d + c * 256 + lane * 8) = o;
+    }
+  }
+}
+
 const char* launch_rmsnorm_fwd(const __nv_bfloat16* x, const float* w, __nv_bfloat16* y, float* rstd, int64_t rows,
                                int d, float eps, cudaStream_t st) {
   if (d % 8 != 0) return "rmsnorm: d must be a multiple of 8";
   const int64_t blocks = (rows + 7) / 8;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w)) % 16 == 0 && rows > 0) {
+    const int grid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+    bool done = true;
+    switch (d) {
+      case 256: rmsnorm_fwd_rows_kernel<1><<<grid, 256, 0, st>>>(x, w, y, rstd, rows, eps); break;
+      case 512: rmsnorm_fwd_rows_kernel<2><<<grid, 256, 0, st>>>(x, w, y, rstd, rows, eps); break;
+      case 1024: rmsnorm_fwd_rows_kernel<4><<<grid, 256, 0, st>>>(x, w, y, rstd, rows, eps); break;
+      case 2048: rmsnorm_fwd_rows_kernel<8><<<grid, 256, 0, st>>>(x, w, y, rstd, rows, eps); break;
+      default: done = false;
+    }
+    if (done) return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm_fwd launch failed";
+  }
   rmsnorm_fwd_kernel<<<(int)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(x, w, y, rstd, rows, d, eps);
   return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm_fwd launch failed";
 }

@@ -54,7 +54,7 @@ def test_causal_dwconv_fwd_bwd(B, T, d, k, use_halo):
         _check(halo.grad, hr.grad, 1e-2, "conv dhalo")
 
 
-@pytest.mark.parametrize("rows,d", [(300, 256), (4100, 1024), (130, 384)])   # register path (d = 256 * n) and the generic one
+@pytest.mark.parametrize("rows,d", [(300, 256), (4100, 1024), (130, 384), (203, 512), (77, 2048)])   # register paths (d = 256 * n) and the generic one
 def test_rmsnorm_fwd_bwd(rows, d):
     cu = _cu()
     x = torch.randn(rows, d, device=DEV, dtype=BF, requires_grad=True)
