@@ -905,6 +905,34 @@ gate_mix_bwd_kernel(const GateMixArgs a) {
   }
 }
 
+// The forward for contiguous inputs: one 8-element vector per thread, as many blocks as vectors / 256, streaming
+// stores. For this purely element-wise op the plain form measured faster than a persistent grid with asynchronous
+// prefetch (234 against 251 us at 65536 x 2048, 62 against 66 us at 32768 x 1024).
+__global__ void __launch_bounds__(256)
+gate_mix_fwd_onevec_kernel(const GateMixArgs a) {
+  const int64_t n_vec = a.rows * (int64_t)(a.d / 8);
+  const int64_t v = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (v >= n_vec) return;
+  const uint4 qg = __ldg(reinterpret_cast<const uint4*>(a.g_pre + v * 8)), qc = __ldg(reinterpret_cast<const uint4*>(a.c + v * 8));
+  const uint4 qs = __ldg(reinterpret_cast<const uint4*>(a.s + v * 8)), qr = __ldg(reinterpret_cast<const uint4*>(a.R + v * 8));
+  const uint32_t* gw = reinterpret_cast<const uint32_t*>(&qg);
+  const uint32_t* cw = reinterpret_cast<const uint32_t*>(&qc);
+  const uint32_t* sw = reinterpret_cast<const uint32_t*>(&qs);
+  const uint32_t* rw = reinterpret_cast<const uint32_t*>(&qr);
+  uint4 of, os;
+  uint32_t* fw = reinterpret_cast<uint32_t*>(&of);
+  uint32_t* ow = reinterpret_cast<uint32_t*>(&os);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 gp = unpack_bf16x2(gw[t]), cv = unpack_bf16x2(cw[t]), sv = unpack_bf16x2(sw[t]), rv = unpack_bf16x2(rw[t]);
+    const float g0 = sigmoidf_(gp.x), g1 = sigmoidf_(gp.y);
+    fw[t] = pack_bf16x2(cv.x * g0 + sv.x * rv.x, cv.y * g1 + sv.y * rv.y);
+    ow[t] = pack_bf16x2(cv.x * (1.0f - g0) + sv.x * (1.0f - rv.x), cv.y * (1.0f - g1) + sv.y * (1.0f - rv.y));
+  }
+  __stcs(reinterpret_cast<uint4*>(a.fwd_out + v * 8), of);
+  __stcs(reinterpret_cast<uint4*>(a.side_out + v * 8), os);
+}
+
 static int gate_mix_blocks(int64_t rows) {
   int64_t b = (rows + 7) / 8;
   return (int)(b < 148 * 8 ? (b < 1 ? 1 : b) : 148 * 8);
@@ -913,6 +941,15 @@ static int gate_mix_blocks(int64_t rows) {
 const char* launch_gate_mix_fwd(const GateMixArgs& a, cudaStream_t st) {
   if (a.d % 8 != 0) return "gate_mix: d must be a multiple of 8";
   if (a.rows == 0) return nullptr;
+  const uintptr_t ptrs = reinterpret_cast<uintptr_t>(a.g_pre) | reinterpret_cast<uintptr_t>(a.c) | reinterpret_cast<uintptr_t>(a.s) |
+                         reinterpret_cast<uintptr_t>(a.R) | reinterpret_cast<uintptr_t>(a.fwd_out) | reinterpret_cast<uintptr_t>(a.side_out);
+  if (a.c_ld == a.d && a.s_ld == a.d && a.r_ld == a.d && ptrs % 16 == 0) {
+    const int64_t blocks = (a.rows * (int64_t)(a.d / 8) + 255) / 256;
+    if (blocks < (1ll << 31)) {
+      gate_mix_fwd_onevec_kernel<<<(unsigned)blocks, 256, 0, st>>>(a);
+      return cudaGetLastError() == cudaSuccess ? nullptr : "gate_mix_fwd launch failed";
+    }
+  }
   gate_mix_fwd_kernel<<<gate_mix_blocks(a.rows), 256, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gate_mix_fwd launch failed";
 }
