@@ -59,6 +59,46 @@ def test_return_gate_does_not_change_outputs():
     assert not torch.equal(a[0], layer.bwd_step(fwd, side)[0])
 
 
+def test_none_side_stream_is_a_zero_side_stream():
+    """``side=None`` stands for the all-zero side stream every layer starts from: same outputs as explicit zeros, and
+    the recovery-gate parameters get an all-zero gradient either way (the gate only multiplies the side stream)."""
+    layer = GDLayer(16, 3)
+    fwd = torch.randn(2, 8, 16)
+    a = layer.fwd_step(fwd, None, return_gate="mean")
+    b = layer.fwd_step(fwd, torch.zeros_like(fwd), return_gate="mean")
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    (b[0].sum() + (b[1] * b[1]).sum()).backward()
+    for name, p in layer.named_parameters():
+        if name.startswith("rf"):
+            assert p.grad is None or float(p.grad.abs().max()) == 0.0, name
+
+
+def test_trunk_hands_tensors_to_an_overridden_cycle():
+    """The model's own cycle receives ``None`` for the zero side streams; a subclass with its own ``one_cycle`` (the
+    experiments add position codes to the side stream) still gets tensors."""
+    from gdnet_b200.model import GDNet
+
+    seen = []
+
+    class Sub(GDNet):
+        def one_cycle(self, fwd, side, *a, **kw):
+            seen.append([type(s) for s in side])
+            return super().one_cycle(fwd, side, *a, **kw)
+
+    torch.manual_seed(0)
+    kw = dict(vocab_size=64, d_embed=16, d=16, n_layers=2, n_cycles=2, kernel_size=3, chunk_size=8)
+    tok = torch.randint(0, 64, (2, 8))
+    torch.manual_seed(1)
+    base = GDNet(**kw)
+    sub = Sub(**kw)
+    sub.load_state_dict(base.state_dict())
+    f1, s1, _ = base.trunk(tok)
+    f2, s2, _ = sub.trunk(tok)
+    assert all(t is torch.Tensor for t in seen[0])
+    assert torch.allclose(f1, f2, atol=1e-6) and all(torch.allclose(x, y, atol=1e-6) for x, y in zip(s1, s2))
+
+
 def test_init_matches_reference_recipe():
     layer = GDLayer(32, 4)
     for p in ("gf", "gb"):
