@@ -7,7 +7,8 @@ exchange:
 
 * **symmetric-memory kernels** (CUDA tensors, extension built): the conv kernels push
   the tail rows into the next rank's slot and wait on a sequence-numbered flag, all
-  from inside the kernel over NVLink peer memory (``csrc/halo.cu``);
+  from inside the kernel over NVLink peer memory (``csrc/elementwise.cu``: ``dwconv_fwd_sw_kernel<.., true>``,
+  ``dwconv_dx_sw_kernel<.., true>``; stand-alone form ``csrc/comm.cu``: ``halo_push_wait_kernel``);
 * **point-to-point messages** (CPU/gloo, or NCCL when ``GDNET_SP_TRANSPORT=p2p``): plain
   ``isend``/``irecv``; this is what the CPU tests run.
 
