@@ -114,10 +114,10 @@ def engine_invariants(engine) -> None:
     from .. import _ext
 
     dev = next(engine.parameters()).device
-    if dev.type != "cuda":
-        return
-    torch.cuda.synchronize(dev)
-    _ext.check_status(torch.empty(1, device=dev))
+    on_gpu = dev.type == "cuda"
+    if on_gpu:
+        torch.cuda.synchronize(dev)
+        _ext.check_status(torch.empty(1, device=dev))
     for g in engine.groups:
         counter = g.sums[4:5].view(torch.int32)
         if int(counter) != 0:
@@ -125,8 +125,9 @@ def engine_invariants(engine) -> None:
     flags = getattr(engine, "_flags", None)
     if flags is None or engine.world == 1:
         return
-    dist.barrier(group=engine.pg)
-    torch.cuda.synchronize(dev)
+    if on_gpu:
+        dist.barrier(group=engine.pg)
+        torch.cuda.synchronize(dev)
     words = flags.view(torch.int32, 3 * engine.world).tolist()
     last_gi = len(engine.groups) - 1
     expect = {0: engine.comm_seq * 8 + last_gi, 1: engine.comm_seq * 8 + last_gi}

@@ -47,3 +47,39 @@ def test_layer_step_under_red_zones_cpu():
         (got_f.sum() + got_s.sum()).backward()
         assert rz.check() > 0
     assert torch.allclose(got_f, want_f) and torch.allclose(got_s, want_s)
+
+
+class _FakeFlags:
+    def __init__(self, words):
+        self.words = torch.tensor(words, dtype=torch.int32)
+
+    def view(self, dtype, n):
+        return self.words[:n]
+
+
+def _fake_engine(flag_words, counter=0, comm_seq=5, task_seq=5, world=2, rank=0, n_groups=2):
+    import types
+
+    sums = torch.zeros(8)
+    sums[4:5].view(torch.int32)[0] = counter
+    groups = [types.SimpleNamespace(sums=sums.clone()) for _ in range(n_groups)]
+    eng = types.SimpleNamespace(groups=groups, world=world, rank=rank, comm="fused", comm_seq=comm_seq, task_seq=task_seq,
+                                overlap_task_reduce=True, pg=None, _flags=_FakeFlags(flag_words))
+    eng.parameters = lambda: iter([torch.zeros(1)])
+    return eng
+
+
+def test_engine_invariants_accept_a_finished_step_and_name_what_is_off():
+    """Flag words are [slot][writer]; after a step every peer's word equals seq * 8 + (number of groups - 1)."""
+    from gdnet_b200.runtime.checked import engine_invariants
+
+    want = 5 * 8 + 1
+    good = [0, want, 0, want, 0, want]          # rank 0 of 2: its own words are never written
+    engine_invariants(_fake_engine(good))
+    with pytest.raises(AssertionError, match="a signal is missing"):
+        engine_invariants(_fake_engine([0, want, 0, want - 8, 0, want]))
+    with pytest.raises(AssertionError, match="a rank ran ahead"):
+        engine_invariants(_fake_engine([0, want + 8, 0, want, 0, want]))
+    with pytest.raises(AssertionError, match="block counter"):
+        engine_invariants(_fake_engine(good, counter=3))
+    engine_invariants(_fake_engine([0] * 6, world=1))          # one rank: nothing to check beyond the counters
